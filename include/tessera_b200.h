@@ -1,0 +1,181 @@
+/*
+ * tessera_b200 — C ABI of the B200 (sm_100a) kernels that stand in for tessera's
+ * matmul and attention lowering rules.
+ *
+ * Every entry point takes plain device pointers and sizes, enqueues work on the
+ * given CUDA stream and returns without synchronising.  Nothing here allocates
+ * device memory: scratch space is a caller-owned workspace whose size comes from
+ * the matching *_workspace_bytes call, the way a tessera plan owns every buffer
+ * its steps touch (engine/plan/run/src/device.rs:397-402).  Arguments are checked
+ * on the host before any launch; a bad argument returns TS_ERR_BAD_INPUT and
+ * launches nothing.  There is no CPU fallback: without a CUDA device the compute
+ * calls return TS_ERR_CUDA.
+ *
+ * Data types: activations, weights and kept K/V rows are bf16 (little-endian u16,
+ * engine/ir/mem/src/form.rs:220-231); sums are f32; the residual stream, norm
+ * gains and router scores are f32; ids, slots, positions and page tables are u32.
+ */
+#ifndef TESSERA_B200_H
+#define TESSERA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TS_ABI_VERSION 1
+
+/* Status codes.  0..5 mirror the reference's device ABI
+ * (engine/rules/device/include/tessera/core.h:104-111); 6 wraps a CUDA error the way
+ * tessera_run::Error::Launch wraps a failed cuLaunchKernel
+ * (engine/plan/run/src/device.rs:138-141). */
+typedef enum {
+    TS_OK = 0,
+    TS_ERR_ABI = 1,
+    TS_ERR_PEER = 2,
+    TS_ERR_BAD_INPUT = 3,
+    TS_ERR_TIMEOUT = 4,
+    TS_ERR_PROTOCOL = 5,
+    TS_ERR_CUDA = 6
+} ts_status;
+
+/* Message of the last failure on the calling thread (never NULL). */
+const char *ts_last_error(void);
+int ts_abi_version(void);
+
+/* Element types of an output buffer. */
+typedef enum { TS_BF16 = 0, TS_F32 = 1 } ts_dtype;
+
+/* ---------------------------------------------------------------------------
+ * Linear: out[m, n] = sum_k x[m, k] * w[n, k], then one fused epilogue stage.
+ * Replaces the matmul rules `tiled*`, `parts_*` (engine/rules/linear/src/tiled.rs:295-304,
+ * 577-591), `lanes` (engine/rules/linear/src/lanes.rs:20-65) and `thin`
+ * (engine/rules/linear/src/thin.rs:31-55); the epilogue stands for the fused stage
+ * chain of engine/plan/lower/src/sites/matmul.rs:148-176.
+ *
+ *   x   [m, k] bf16 row-major          w   [n, k] bf16 row-major ("[Out, In]")
+ *   a0  epilogue operand or NULL       out [m, n] (or [m, n/2] for SWIGLU)
+ *
+ * k must be a multiple of 64 and x, w, out 16-byte aligned.
+ * ------------------------------------------------------------------------- */
+typedef enum {
+    TS_EPI_NONE = 0,
+    TS_EPI_ADD = 1,    /* out = acc + a0;  a0 f32 [m, n] (the residual add, Stage::Add) */
+    TS_EPI_SWIGLU = 2, /* w holds gate rows [0, n/2) then up rows [n/2, n):
+                          out[m, j] = silu(acc[m, j]) * acc[m, n/2 + j]  (Stage::Act + Stage::Mul) */
+    TS_EPI_SCALE = 3,  /* out = acc * scale (Stage::Scale) */
+    TS_EPI_GEGLU = 4   /* as SWIGLU with the tanh GELU (Act::GeluTanh) */
+} ts_epilogue;
+
+/* Which kernel family runs a linear.  AUTO picks by m. */
+typedef enum {
+    TS_LINEAR_AUTO = 0,
+    TS_LINEAR_SKINNY = 1, /* decode-sized m: vector loads + warp MMA, split-K */
+    TS_LINEAR_UMMA = 2    /* tcgen05 / TMEM accumulators fed by TMA */
+} ts_linear_path;
+
+/* Bytes of workspace ts_linear_bf16 needs for these sizes (0 when none). */
+size_t ts_linear_workspace_bytes(uint32_t m, uint32_t n, uint32_t k, int epilogue, int path);
+
+int ts_linear_bf16(const void *x, const void *w, const void *a0, void *out, uint32_t m, uint32_t n,
+                   uint32_t k, int epilogue, float scale, int out_dtype, int path, void *workspace,
+                   size_t workspace_bytes, void *stream);
+
+/* ---------------------------------------------------------------------------
+ * Kept rows (paged KV).  Layouts follow engine/plan/codegen/src/kept.rs:135-194:
+ *   dense        row = slot * kept_scalar + position          (kept_scalar = kept_stride)
+ *   interleaved  row = position * kept_scalar + slot          (kept_scalar = kept_slots)
+ *   paged(page)  entry = slot * kept_scalar + (position >> log2 page)   (kept_scalar = kept_pages)
+ *                row = (table[entry] << log2 page) | (position & (page - 1))
+ * K and V buffers are [rows, kv_heads, width] bf16.
+ * ------------------------------------------------------------------------- */
+typedef enum { TS_KEPT_DENSE = 0, TS_KEPT_INTERLEAVED = 1, TS_KEPT_PAGED = 2 } ts_kept_kind;
+
+typedef struct {
+    int kind;              /* ts_kept_kind */
+    uint32_t page;         /* rows per page, a power of two (64 = "paged", 16 = "paged16") */
+    uint32_t kept_scalar;  /* kept_stride | kept_slots | kept_pages: the layout's last scalar */
+    const uint32_t *table; /* device, slots * kept_pages entries; NULL unless paged */
+    uint32_t table_len;    /* entries in table */
+    uint32_t rows;         /* rows the K/V buffers hold (bounds check) */
+} ts_kept;
+
+/* Ragged attention over kept rows, causal: row r (slot slots[r], position positions[r]) reads
+ * keys [max(0, pos - back), min(pos + 1, keys)) of its slot.  Replaces `attend_rows`
+ * (engine/rules/attention/src/attend.rs:124-167, arguments 182-201) and `flash_rows`
+ * (engine/rules/attention/src/flash.rs:505-580).  The score scale, a separate `map` launch in
+ * the reference (engine/rules/attention/src/lib.rs:22-31), is an argument here.
+ *   q [rows, heads, width] bf16; out [rows, heads, width] bf16; width must be 128 or 256. */
+size_t ts_attend_rows_workspace_bytes(uint32_t rows, uint32_t keys, uint32_t heads, uint32_t kv_heads,
+                                      uint32_t width);
+
+int ts_attend_rows_bf16(const void *q, const void *k, const void *v, void *out, const uint32_t *slots,
+                        const uint32_t *positions, const ts_kept *kept, uint32_t rows, uint32_t keys,
+                        uint32_t heads, uint32_t kv_heads, uint32_t width, uint32_t back, float scale,
+                        void *workspace, size_t workspace_bytes, void *stream);
+
+/* Writes rows of x at kept_row(slot, position).  Replaces `scatter`
+ * (engine/plan/lower/src/kernels/scatter.rs:11-83).  x [rows, width] bf16, out [kept rows, width]. */
+int ts_scatter_bf16(const void *x, const uint32_t *slots, const uint32_t *positions, void *out,
+                    const ts_kept *kept, uint32_t rows, uint32_t width, void *stream);
+
+/* The decoder's per-head step between the projections and attention, fused: per-head RMS norm of
+ * q and k (gains q_norm, k_norm [width] f32, or NULL for none), half-pair rotation at the row's
+ * position (angle = position * inv_freq[j] for the pair (j, j + width/2); inv_freq is a device
+ * array of width/2 f32 that ts_rope_inv_freq fills on the host, the reference's `angles` table,
+ * engine/rules/kernels/src/rope.rs:38-45), then q -> q_out and k, v -> kept rows.  Stands for the reference's lane_norm + rope +
+ * scatter K + scatter V launches (engine/models/src/decoder.rs:354-389;
+ * engine/rules/kernels/src/{lane_norm,rope}.rs).
+ *   qkv [rows, (heads + 2 kv_heads) * width] bf16 (q heads, then k heads, then v heads). */
+int ts_qk_norm_rope_append_bf16(const void *qkv, const float *q_norm, const float *k_norm,
+                                const float *inv_freq, const uint32_t *slots, const uint32_t *positions,
+                                void *q_out, void *k_rows, void *v_rows, const ts_kept *kept,
+                                uint32_t rows, uint32_t heads, uint32_t kv_heads, uint32_t width,
+                                float eps, void *stream);
+
+/* out[j] = theta^(-2j / width) for j < width/2, in f32 on the host (engine/ir/interp/src/cpu.rs:31-34). */
+void ts_rope_inv_freq(float theta, uint32_t width, float *out);
+
+/* ---------------------------------------------------------------------------
+ * Row kernels the decode loop needs around the two hot rules.
+ * ------------------------------------------------------------------------- */
+
+/* out = rms_norm(x) * w.  Replaces `lane_norm` / `rms_norm` (engine/rules/kernels/src/lane_norm.rs:10-17).
+ * x f32 or bf16 [rows, width]; w f32 [width] or NULL (Stage::Rms); out bf16 or f32. */
+int ts_rms_norm(const void *x, int x_dtype, const float *w, void *out, int out_dtype, uint32_t rows,
+                uint32_t width, float eps, void *stream);
+
+/* out[r] = table[ids[r]] widened to out_dtype; rows outside [first, first + table_rows) read zero.
+ * Replaces `gather` (engine/ir/interp/src/cpu.rs:510-525). table bf16 [table_rows, width]. */
+int ts_gather_bf16(const void *table, const uint32_t *ids, void *out, int out_dtype, uint32_t rows,
+                   uint32_t table_rows, uint32_t width, uint32_t first, void *stream);
+
+/* ids[r, 0..k) = indices of the k largest entries of x[r, :], best first; ties keep the lower
+ * index, -inf and NaN are never picked, spare slots hold `width`.  Replaces `top_k`
+ * (engine/rules/kernels/src/argmax.rs:38-70); k = 1 is `peaks` + `argmax` (argmax.rs:72-114).
+ * x f32 or bf16 [rows, width]; k <= 32; workspace from ts_top_k_workspace_bytes. */
+size_t ts_top_k_workspace_bytes(uint32_t rows, uint32_t width, uint32_t k);
+int ts_top_k(const void *x, int x_dtype, uint32_t *ids, uint32_t rows, uint32_t width, uint32_t k,
+             void *workspace, size_t workspace_bytes, void *stream);
+
+/* gates[r, :] = softmax(x[r, ids[r, :]]) — the router's `take` + `softmax`
+ * (engine/models/src/decoder.rs:73-75).  x f32 [rows, width], ids u32 [rows, k], gates f32. */
+int ts_take_softmax(const float *x, const uint32_t *ids, float *gates, uint32_t rows, uint32_t width,
+                    uint32_t k, void *stream);
+
+/* Programmatic dependent launch on every kernel of this library (off by default): a kernel's
+ * weight prefetch then overlaps the tail of the kernel before it, as the reference's `pdl` launch
+ * setting does (engine/gpu/gpukit/src/cuda/context.rs:126-148). Process-wide. */
+int ts_set_pdl(int enabled);
+
+/* Reads and clears the device-side status word: TS_OK, or TS_ERR_TIMEOUT when a bounded wait
+ * inside a tcgen05 kernel gave up (engine/rules/device/include/tessera/status.h:9-39 keeps the same
+ * kind of record).  Synchronises the device. */
+int ts_device_status(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,83 @@
+/*
+ * tessera_b200 runner — the host side that replays a decoder's plan of launches on one GPU.
+ *
+ * It plays the part of tessera-run's CUDA backend for the Qwen3-shaped decoder graph
+ * (engine/plan/run/src/run.rs:122-345: load, feed, submit, read; engine/plan/run/src/device.rs:
+ * 128-242: bind arguments, launch, CUDA-graph replay keyed by the bound sizes) with the step list
+ * of engine/models/src/decoder.rs:281-389 fixed at creation: gather, then per layer rms_norm,
+ * fused q|k|v linear, per-head norm + rotation + kept-row append, ragged attention over kept rows,
+ * o linear + residual, rms_norm, gate|up linear with SwiGLU, down linear + residual; final
+ * rms_norm, tied unembedding, greedy top-1.
+ *
+ * Ownership follows the reference: the runner owns every plan buffer (allocated once at creation,
+ * zeroed, freed at destroy), weights are uploaded once with ts_decoder_load, and nothing on the
+ * step path allocates.  One runner per thread; calls take a CUDA stream.
+ */
+#ifndef TESSERA_B200_RUN_H
+#define TESSERA_B200_RUN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#include "tessera_b200.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct ts_decoder ts_decoder;
+
+typedef struct {
+    uint32_t layers, hidden, heads, kv_heads, head_dim, ffn, vocab;
+    uint32_t slots;    /* sequences the kept store holds (engine `Seqs`) */
+    uint32_t context;  /* positions per slot (engine `Context`) */
+    uint32_t page;     /* 64 ("paged"), 16 ("paged16") or 0 (dense kept rows) */
+    uint32_t max_rows; /* most rows one launch carries (engine `Rows`) */
+    float eps, theta;
+    int qk_norm;       /* per-head RMS norm on q and k (Qwen3) */
+    int graphs;        /* replay steps as CUDA graphs (engine/plan/lower/src/recipe.rs:51-57 `launch.graphs`) */
+    int pdl;           /* programmatic dependent launch between steps (`launch.pdl`) */
+} ts_decoder_config;
+
+/* Allocates the plan's buffers on the current device.  The page table starts as the identity
+ * (engine/engine/src/lanes.rs:4-65). */
+int ts_decoder_create(const ts_decoder_config *config, ts_decoder **out);
+void ts_decoder_destroy(ts_decoder *dec);
+
+/* Uploads one weight from host memory (tessera_run::Run::load_weight, run.rs:204-250).  Names follow the
+ * declaration order of engine/models/src/decoder.rs:225-255: "embed", "layers.<i>.ln1", ".q", ".k", ".v",
+ * ".q_norm", ".k_norm", ".o", ".ln2", ".mlp.gate", ".mlp.up", ".mlp.down", "norm".  Linears are bf16
+ * [out, in]; norm gains are f32. */
+int ts_decoder_load(ts_decoder *dec, const char *name, const void *host_data, size_t bytes);
+
+/* Replaces the page table (slots * ceil(context / page) entries; every entry < that count). */
+int ts_decoder_set_table(ts_decoder *dec, const uint32_t *host_table, uint32_t entries);
+
+/* One launch: feeds `rows` (token, slot, position) triples from host memory, runs the step list and
+ * returns the greedy token of each row listed in `out_rows` (n_out indices into the launch's rows;
+ * NULL = every row) in `out_ids` (host).  Synchronises the stream before returning, like
+ * Run::submit (run.rs:140-141).  Rows are validated on the host first: a slot, position or token
+ * out of range returns TS_ERR_BAD_INPUT and launches nothing. */
+int ts_decoder_step(ts_decoder *dec, const uint32_t *tokens, const uint32_t *slots, const uint32_t *positions,
+                    uint32_t rows, const uint32_t *out_rows, uint32_t n_out, uint32_t *out_ids, void *stream);
+
+/* Device-resident decode: after a ts_decoder_step that left one row per slot, runs `steps` further
+ * launches in which each row's token is the id it just produced and its position moves on by one,
+ * without host traffic.  ts_decoder_read_ids copies the latest ids (rows entries) to the host. */
+int ts_decoder_run_resident(ts_decoder *dec, uint32_t steps, void *stream);
+int ts_decoder_read_ids(ts_decoder *dec, uint32_t *out_ids, uint32_t rows, void *stream);
+
+/* Final normed hidden rows of the last launch, bf16 [rows, hidden], to the host (for parity checks). */
+int ts_decoder_read_hidden(ts_decoder *dec, void *out_bf16, uint32_t rows, void *stream);
+/* Logits of the last launch, f32 [n_out, vocab], to the host. */
+int ts_decoder_read_logits(ts_decoder *dec, float *out, uint32_t n_out, void *stream);
+
+/* Kernel launches one step enqueues for `rows` rows at `keys` visible positions, and how many steps
+ * have been replayed from a captured graph so far. */
+uint32_t ts_decoder_launches_per_step(ts_decoder *dec, uint32_t rows, uint32_t keys);
+uint64_t ts_decoder_graph_replays(ts_decoder *dec);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,260 @@
+// The C ABI: argument checks on the host, then a launch.  Nothing here synchronises or allocates.
+#include <cstdarg>
+#include <cstring>
+#include <mutex>
+
+#include "ts_common.cuh"
+#include "ts_kernels.cuh"
+#include "ts_ptx.cuh"
+
+namespace ts {
+
+// ---- error text, device facts, switches ----
+static thread_local char g_error[512] = "";
+
+int fail(int code, const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int sm_count() {
+    static int cached = 0;
+    if (cached == 0) {
+        int dev = 0, n = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess &&
+            cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
+            cached = n;
+        else
+            return 148;  // B200; only reached without a device, where nothing launches anyway
+    }
+    return cached;
+}
+
+static bool g_pdl = false;
+bool pdl_enabled() { return g_pdl; }
+void set_pdl(bool enabled) { g_pdl = enabled; }
+
+int kept_to_dev(const ts_kept *kept, KeptDev *out) {
+    TS_REQUIRE(kept != nullptr, "kept layout is NULL");
+    TS_REQUIRE(kept->kind >= TS_KEPT_DENSE && kept->kind <= TS_KEPT_PAGED, "kept layout kind %d is unknown", kept->kind);
+    out->kind = kept->kind;
+    out->scalar = kept->kept_scalar;
+    out->shift = 0;
+    out->table = kept->table;
+    if (kept->kind == TS_KEPT_PAGED) {
+        TS_REQUIRE(kept->page >= 1 && (kept->page & (kept->page - 1)) == 0, "page of %u rows is not a power of two",
+                   kept->page);
+        TS_REQUIRE(kept->table != nullptr, "a paged layout needs its page table");
+        uint32_t shift = 0;
+        while ((1u << shift) < kept->page) shift++;
+        out->shift = shift;
+    }
+    return TS_OK;
+}
+
+// ---- tensor maps ----
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+int make_tensor_map_2d(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, uint64_t row_stride,
+                       uint32_t box_rows, uint32_t box_cols) {
+    EncodeTiledFn fn = encode_tiled();
+    if (!fn) return fail(TS_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {row_stride * 2};
+    cuuint32_t box[2] = {box_cols, box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(TS_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for a %llu x %llu tensor, box %u x %u", (int)r,
+                    (unsigned long long)rows, (unsigned long long)cols, box_rows, box_cols);
+    return TS_OK;
+}
+
+int make_tensor_map_3d(CUtensorMap *map, const void *base, uint64_t outer, uint64_t rows, uint64_t cols,
+                       uint64_t outer_stride, uint64_t row_stride, uint32_t box_rows, uint32_t box_cols) {
+    EncodeTiledFn fn = encode_tiled();
+    if (!fn) return fail(TS_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[3] = {cols, rows, outer};
+    cuuint64_t strides[2] = {row_stride * 2, outer_stride * 2};
+    cuuint32_t box[3] = {box_cols, box_rows, 1};
+    cuuint32_t elem[3] = {1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(TS_ERR_CUDA, "cuTensorMapEncodeTiled (3-D) failed (%d)", (int)r);
+    return TS_OK;
+}
+
+static int pick_linear_path(uint32_t m, uint32_t n, uint32_t k, int epilogue, int path) {
+    if (path == TS_LINEAR_SKINNY || path == TS_LINEAR_UMMA) return path;
+    // Small m: the warp-MMA streamer; otherwise the tcgen05 kernel.
+    if (m <= 16 && skinny_supports(m, n, k, epilogue)) return TS_LINEAR_SKINNY;
+    if (umma_supports(m, n, k, epilogue)) return TS_LINEAR_UMMA;
+    if (skinny_supports(m, n, k, epilogue)) return TS_LINEAR_SKINNY;
+    return -1;
+}
+
+}  // namespace ts
+
+using namespace ts;
+
+#pragma GCC visibility push(default)
+extern "C" {
+
+const char *ts_last_error(void) { return g_error; }
+int ts_abi_version(void) { return TS_ABI_VERSION; }
+
+int ts_set_pdl(int enabled) {
+    g_pdl = enabled != 0;
+    return TS_OK;
+}
+
+int ts_device_status(void) { return umma_take_status(); }
+
+size_t ts_linear_workspace_bytes(uint32_t m, uint32_t n, uint32_t k, int epilogue, int path) {
+    const bool gated = epilogue == TS_EPI_SWIGLU || epilogue == TS_EPI_GEGLU;
+    size_t a = 0, b = 0;
+    if (path != TS_LINEAR_UMMA && skinny_supports(m, n, k, epilogue)) a = skinny_workspace_bytes(m, n, k, gated);
+    if (path != TS_LINEAR_SKINNY && umma_supports(m, n, k, epilogue)) b = umma_workspace_bytes(m, n, k, epilogue);
+    return a > b ? a : b;
+}
+
+int ts_linear_bf16(const void *x, const void *w, const void *a0, void *out, uint32_t m, uint32_t n, uint32_t k,
+                   int epilogue, float scale, int out_dtype, int path, void *workspace, size_t workspace_bytes,
+                   void *stream) {
+    TS_REQUIRE(x && w && out, "linear: x, w and out must not be NULL");
+    TS_REQUIRE(aligned16(x) && aligned16(w) && aligned16(out), "linear: x, w and out must be 16-byte aligned");
+    TS_REQUIRE(epilogue >= TS_EPI_NONE && epilogue <= TS_EPI_GEGLU, "linear: epilogue %d is unknown", epilogue);
+    TS_REQUIRE(out_dtype == TS_BF16 || out_dtype == TS_F32, "linear: out dtype %d is unknown", out_dtype);
+    TS_REQUIRE(epilogue != TS_EPI_ADD || a0 != nullptr, "linear: the add epilogue needs its operand");
+    TS_REQUIRE(a0 == nullptr || aligned16(a0), "linear: the epilogue operand must be 16-byte aligned");
+    TS_REQUIRE(k % 64 == 0 && k > 0, "linear: k = %u is not a positive multiple of 64", k);
+    if (m == 0 || n == 0) return TS_OK;
+    const int chosen = pick_linear_path(m, n, k, epilogue, path);
+    TS_REQUIRE(chosen > 0, "linear: no kernel takes m=%u n=%u k=%u epilogue=%d", m, n, k, epilogue);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (chosen == TS_LINEAR_SKINNY) {
+        TS_REQUIRE(skinny_supports(m, n, k, epilogue), "linear (skinny): needs m <= 64 and k %% 256 == 0 (m=%u k=%u)", m,
+                   k);
+        return linear_skinny(x, w, a0, out, m, n, k, epilogue, scale, out_dtype, workspace, workspace_bytes, s);
+    }
+    return linear_umma(x, w, a0, out, m, n, k, epilogue, scale, out_dtype, workspace, workspace_bytes, s);
+}
+
+static int check_kept(const ts_kept *kept, KeptDev *dev, bool *contiguous) {
+    int rc = kept_to_dev(kept, dev);
+    if (rc != TS_OK) return rc;
+    *contiguous = kept->kind == TS_KEPT_DENSE || (kept->kind == TS_KEPT_PAGED && kept->page >= 32);
+    return TS_OK;
+}
+
+size_t ts_attend_rows_workspace_bytes(uint32_t rows, uint32_t keys, uint32_t heads, uint32_t kv_heads,
+                                      uint32_t width) {
+    return attend_rows_workspace_bytes(rows, keys, heads, kv_heads, width);
+}
+
+int ts_attend_rows_bf16(const void *q, const void *k, const void *v, void *out, const uint32_t *slots,
+                        const uint32_t *positions, const ts_kept *kept, uint32_t rows, uint32_t keys,
+                        uint32_t heads, uint32_t kv_heads, uint32_t width, uint32_t back, float scale,
+                        void *workspace, size_t workspace_bytes, void *stream) {
+    TS_REQUIRE(q && k && v && out && slots && positions, "attend_rows: a buffer is NULL");
+    TS_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out), "attend_rows: buffers must be 16-byte aligned");
+    TS_REQUIRE(width == 64 || width == 128 || width == 256, "attend_rows: width %u is not 64, 128 or 256", width);
+    TS_REQUIRE(kv_heads > 0 && heads % kv_heads == 0, "attend_rows: %u heads do not split over %u kv heads", heads, kv_heads);
+    KeptDev dev;
+    bool contiguous;
+    int rc = check_kept(kept, &dev, &contiguous);
+    if (rc != TS_OK) return rc;
+    if (rows == 0 || keys == 0) return TS_OK;
+    return attend_rows(q, k, v, out, slots, positions, dev, contiguous, rows, keys, heads, kv_heads, width, back, scale,
+                       workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+int ts_scatter_bf16(const void *x, const uint32_t *slots, const uint32_t *positions, void *out, const ts_kept *kept,
+                    uint32_t rows, uint32_t width, void *stream) {
+    TS_REQUIRE(x && slots && positions && out, "scatter: a buffer is NULL");
+    TS_REQUIRE(width % 8 == 0 && aligned16(x) && aligned16(out), "scatter: rows must be 16-byte multiples and aligned");
+    KeptDev dev;
+    bool contiguous;
+    int rc = check_kept(kept, &dev, &contiguous);
+    if (rc != TS_OK) return rc;
+    return scatter_rows(x, slots, positions, out, dev, rows, width, (cudaStream_t)stream);
+}
+
+void ts_rope_inv_freq(float theta, uint32_t width, float *out) {
+    // engine/ir/interp/src/cpu.rs:31-34: theta^(-2j / width), in f32
+    for (uint32_t j = 0; j < width / 2; j++) out[j] = powf(theta, -((float)(2 * j)) / (float)width);
+}
+
+int ts_qk_norm_rope_append_bf16(const void *qkv, const float *q_norm, const float *k_norm, const float *inv_freq,
+                                const uint32_t *slots, const uint32_t *positions, void *q_out, void *k_rows,
+                                void *v_rows, const ts_kept *kept, uint32_t rows, uint32_t heads, uint32_t kv_heads,
+                                uint32_t width, float eps, void *stream) {
+    TS_REQUIRE(qkv && inv_freq && slots && positions && q_out && k_rows && v_rows, "qk_norm_rope_append: a buffer is NULL");
+    TS_REQUIRE(aligned16(qkv) && aligned16(q_out) && aligned16(k_rows) && aligned16(v_rows),
+               "qk_norm_rope_append: buffers must be 16-byte aligned");
+    KeptDev dev;
+    bool contiguous;
+    int rc = check_kept(kept, &dev, &contiguous);
+    if (rc != TS_OK) return rc;
+    return qk_norm_rope_append(qkv, q_norm, k_norm, inv_freq, slots, positions, q_out, k_rows, v_rows, dev, rows, heads,
+                               kv_heads, width, eps, (cudaStream_t)stream);
+}
+
+int ts_rms_norm(const void *x, int x_dtype, const float *w, void *out, int out_dtype, uint32_t rows, uint32_t width,
+                float eps, void *stream) {
+    TS_REQUIRE(x && out, "rms_norm: a buffer is NULL");
+    TS_REQUIRE((x_dtype == TS_BF16 || x_dtype == TS_F32) && (out_dtype == TS_BF16 || out_dtype == TS_F32),
+               "rms_norm: unknown dtype");
+    TS_REQUIRE(width > 0, "rms_norm: width is zero");
+    return rms_norm(x, x_dtype, w, out, out_dtype, rows, width, eps, nullptr, (cudaStream_t)stream);
+}
+
+int ts_gather_bf16(const void *table, const uint32_t *ids, void *out, int out_dtype, uint32_t rows,
+                   uint32_t table_rows, uint32_t width, uint32_t first, void *stream) {
+    TS_REQUIRE(table && ids && out, "gather: a buffer is NULL");
+    TS_REQUIRE(out_dtype == TS_BF16 || out_dtype == TS_F32, "gather: unknown dtype");
+    return gather_rows(table, ids, out, out_dtype, rows, table_rows, width, first, (cudaStream_t)stream);
+}
+
+size_t ts_top_k_workspace_bytes(uint32_t rows, uint32_t width, uint32_t k) {
+    return top_k_workspace_bytes(rows, width, k);
+}
+
+int ts_top_k(const void *x, int x_dtype, uint32_t *ids, uint32_t rows, uint32_t width, uint32_t k, void *workspace,
+             size_t workspace_bytes, void *stream) {
+    TS_REQUIRE(x && ids, "top_k: a buffer is NULL");
+    TS_REQUIRE(x_dtype == TS_BF16 || x_dtype == TS_F32, "top_k: unknown dtype");
+    TS_REQUIRE(width > 0, "top_k: width is zero");
+    return top_k(x, x_dtype, ids, rows, width, k, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+int ts_take_softmax(const float *x, const uint32_t *ids, float *gates, uint32_t rows, uint32_t width, uint32_t k,
+                    void *stream) {
+    TS_REQUIRE(x && ids && gates, "take_softmax: a buffer is NULL");
+    TS_REQUIRE(k >= 1 && k <= 32, "take_softmax: k = %u is outside 1..32", k);
+    return take_softmax(x, ids, gates, rows, width, k, (cudaStream_t)stream);
+}
+
+}  // extern "C"
+#pragma GCC visibility pop

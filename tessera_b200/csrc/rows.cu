@@ -1,0 +1,435 @@
+// Row kernels around the two hot rules: RMS norm, embedding gather, the fused per-head
+// norm + rotation + kept-row append, plain scatter, top-k / argmax, and the router's
+// take + softmax.  Each follows the reference kernel it replaces (cited per kernel).
+#include <cmath>
+
+#include "ts_common.cuh"
+
+namespace ts {
+namespace {
+
+__device__ __forceinline__ float block_sum(float v, float *scratch) {
+    v = warp_sum(v);
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    const uint32_t warps = (blockDim.x + 31) / 32;
+    float t = 0.0f;
+    for (uint32_t w = 0; w < warps; w++) t += scratch[w];  // fixed order
+    __syncthreads();
+    return t;
+}
+
+// ---- rms_norm: engine/rules/kernels/src/lane_norm.rs:10-17; math engine/ir/interp/src/cpu.rs:371-377, 491-495
+template <typename TIn, typename TOut>
+__global__ void __launch_bounds__(256) rms_norm_kernel(const TIn *x, const float *w, TOut *out, uint32_t width,
+                                                       float eps, const uint32_t *row_ids) {
+    __shared__ float scratch[8];
+    pdl_wait();
+    // With row_ids, output row i reads input row row_ids[i] (the rows whose logits are wanted).
+    const size_t base = (size_t)(row_ids ? row_ids[blockIdx.x] : blockIdx.x) * width;
+    const size_t obase = (size_t)blockIdx.x * width;
+    float ss = 0.0f;
+    for (uint32_t i = threadIdx.x; i < width; i += blockDim.x) {
+        float v;
+        if constexpr (sizeof(TIn) == 4) v = x[base + i];
+        else v = __uint_as_float((uint32_t)x[base + i] << 16);
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    pdl_launch_dependents();
+    const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+    for (uint32_t i = threadIdx.x; i < width; i += blockDim.x) {
+        float v;
+        if constexpr (sizeof(TIn) == 4) v = x[base + i];
+        else v = __uint_as_float((uint32_t)x[base + i] << 16);
+        float r = w ? v * (inv * w[i]) : v * inv;
+        if constexpr (sizeof(TOut) == 4) out[obase + i] = r;
+        else out[obase + i] = bf16_bits(r);
+    }
+}
+
+// ---- gather: engine/ir/interp/src/cpu.rs:510-525 (rows outside the table read zero)
+template <typename TOut>
+__global__ void __launch_bounds__(128) gather_kernel(const uint16_t *table, const uint32_t *ids, TOut *out,
+                                                     uint32_t table_rows, uint32_t width, uint32_t first) {
+    pdl_wait();
+    const uint32_t id = ids[blockIdx.x];
+    const bool inside = id >= first && id - first < table_rows;
+    const uint16_t *src = table + (size_t)(inside ? id - first : 0) * width;
+    for (uint32_t i = threadIdx.x; i < width; i += blockDim.x) {
+        uint16_t b = inside ? src[i] : (uint16_t)0;
+        if constexpr (sizeof(TOut) == 4) out[(size_t)blockIdx.x * width + i] = __uint_as_float((uint32_t)b << 16);
+        else out[(size_t)blockIdx.x * width + i] = b;
+    }
+    pdl_launch_dependents();
+}
+
+// ---- scatter: engine/plan/lower/src/kernels/scatter.rs:11-27
+__global__ void __launch_bounds__(128) scatter_kernel(const uint16_t *x, const uint32_t *slots,
+                                                      const uint32_t *positions, uint16_t *out, KeptDev kept,
+                                                      uint32_t width) {
+    pdl_wait();
+    const uint32_t r = blockIdx.x;
+    const size_t dst = (size_t)kept_row(kept, slots[r], positions[r]) * width;
+    const uint4 *src = reinterpret_cast<const uint4 *>(x + (size_t)r * width);
+    uint4 *d = reinterpret_cast<uint4 *>(out + dst);
+    for (uint32_t i = threadIdx.x; i < width / 8; i += blockDim.x) d[i] = src[i];
+    pdl_launch_dependents();
+}
+
+// ---- per-head norm + rotation + append.  One warp per (row, head of q|k|v).
+// Norm: engine/ir/interp/src/cpu.rs:371-377; rotation with half pairs (j, j + width/2), angle =
+// position * inv_freq[j]: cpu.rs:31-47; append at kept_row(slot, position): scatter.rs:11-27.
+template <int WIDTH>
+__global__ void __launch_bounds__(128) qk_norm_rope_append_kernel(
+    const uint16_t *qkv, const float *q_norm, const float *k_norm, const float *inv_freq, const uint32_t *slots,
+    const uint32_t *positions, uint16_t *q_out, uint16_t *k_rows, uint16_t *v_rows, KeptDev kept, uint32_t rows,
+    uint32_t heads, uint32_t kv_heads, float eps) {
+    constexpr int PER = WIDTH / 64;  // pairs per lane
+    pdl_wait();
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t unit = blockIdx.x * 4 + (threadIdx.x >> 5);
+    const uint32_t per_row = heads + 2 * kv_heads;
+    if (unit >= rows * per_row) return;
+    const uint32_t r = unit / per_row, h = unit % per_row;
+    const uint16_t *src = qkv + ((size_t)r * per_row + h) * WIDTH;
+    const uint32_t pos = positions[r];
+
+    uint16_t *dst;
+    const float *gain = nullptr;
+    bool turn = true;
+    if (h < heads) {
+        dst = q_out + ((size_t)r * heads + h) * WIDTH;
+        gain = q_norm;
+    } else {
+        const uint32_t kvh = (h - heads) % kv_heads;
+        const bool is_v = h >= heads + kv_heads;
+        const size_t at = ((size_t)kept_row(kept, slots[r], pos) * kv_heads + kvh) * WIDTH;
+        dst = (is_v ? v_rows : k_rows) + at;
+        gain = is_v ? nullptr : k_norm;
+        turn = !is_v;
+    }
+    if (!turn) {
+        // values pass through
+        for (uint32_t i = lane; i < WIDTH / 8; i += 32)
+            reinterpret_cast<uint4 *>(dst)[i] = reinterpret_cast<const uint4 *>(src)[i];
+        return;
+    }
+    // lane owns pairs j = lane * PER + e: elements j and j + WIDTH/2
+    float a[PER], b[PER];
+    float ss = 0.0f;
+#pragma unroll
+    for (int e = 0; e < PER; e++) {
+        const uint32_t j = lane * PER + e;
+        a[e] = __uint_as_float((uint32_t)src[j] << 16);
+        b[e] = __uint_as_float((uint32_t)src[j + WIDTH / 2] << 16);
+        ss = fmaf(a[e], a[e], ss);
+        ss = fmaf(b[e], b[e], ss);
+    }
+    if (gain) {
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)WIDTH + eps);
+#pragma unroll
+        for (int e = 0; e < PER; e++) {
+            const uint32_t j = lane * PER + e;
+            a[e] = a[e] * (inv * gain[j]);
+            b[e] = b[e] * (inv * gain[j + WIDTH / 2]);
+        }
+    }
+#pragma unroll
+    for (int e = 0; e < PER; e++) {
+        const uint32_t j = lane * PER + e;
+        float sn, cs;
+        sincosf((float)pos * inv_freq[j], &sn, &cs);
+        const float ra = a[e] * cs - b[e] * sn;
+        const float rb = a[e] * sn + b[e] * cs;
+        dst[j] = bf16_bits(ra);
+        dst[j + WIDTH / 2] = bf16_bits(rb);
+    }
+}
+
+// ---- top-k: engine/rules/kernels/src/argmax.rs:38-114; order engine/ir/interp/src/run.rs:577-591.
+// `a` ranks before `b` when its value is larger, or equal with the lower index.  -inf and NaN never rank.
+struct Cand {
+    float v;
+    uint32_t i;
+};
+
+__device__ __forceinline__ bool ranks_before(float av, uint32_t ai, float bv, uint32_t bi) {
+    return av > bv || (av == bv && ai < bi);
+}
+
+__device__ __forceinline__ Cand best_of(Cand a, Cand b, uint32_t none) {
+    if (a.i == none) return b;
+    if (b.i == none) return a;
+    return ranks_before(a.v, a.i, b.v, b.i) ? a : b;
+}
+
+template <typename TIn>
+__device__ __forceinline__ float load_score(const TIn *x, size_t at) {
+    if constexpr (sizeof(TIn) == 4) return x[at];
+    else return __uint_as_float((uint32_t)x[at] << 16);
+}
+
+// One block per row; round r finds the best entry that ranks after round r - 1's pick.
+template <typename TIn>
+__global__ void __launch_bounds__(256) top_k_kernel(const TIn *x, uint32_t *ids, uint32_t width, uint32_t k) {
+    __shared__ float sv[8];
+    __shared__ uint32_t si[8];
+    __shared__ Cand picked;
+    pdl_wait();
+    const size_t base = (size_t)blockIdx.x * width;
+    const uint32_t none = width;
+    Cand prev = {INFINITY, 0};
+    bool have_prev = false;
+    for (uint32_t round = 0; round < k; round++) {
+        Cand best = {0.0f, none};
+        for (uint32_t i = threadIdx.x; i < width; i += blockDim.x) {
+            const float v = load_score(x, base + i);
+            if (!(v > -INFINITY)) continue;  // -inf and NaN never rank
+            if (have_prev && !ranks_before(prev.v, prev.i, v, i)) continue;  // already taken
+            best = best_of(best, Cand{v, i}, none);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            Cand other = {__shfl_xor_sync(0xFFFFFFFFu, best.v, o), __shfl_xor_sync(0xFFFFFFFFu, best.i, o)};
+            best = best_of(best, other, none);
+        }
+        if ((threadIdx.x & 31) == 0) {
+            sv[threadIdx.x >> 5] = best.v;
+            si[threadIdx.x >> 5] = best.i;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            Cand b = {sv[0], si[0]};
+            for (uint32_t w = 1; w < blockDim.x / 32; w++) b = best_of(b, Cand{sv[w], si[w]}, none);
+            picked = b;
+            ids[(size_t)blockIdx.x * k + round] = b.i;
+        }
+        __syncthreads();
+        prev = picked;
+        have_prev = true;
+        if (prev.i == none) {
+            // nothing left: spare slots hold the width
+            if (threadIdx.x == 0)
+                for (uint32_t r2 = round + 1; r2 < k; r2++) ids[(size_t)blockIdx.x * k + r2] = none;
+            break;
+        }
+        __syncthreads();
+    }
+    pdl_launch_dependents();
+}
+
+// k = 1 over wide rows, two stages (the reference's `peaks` + `argmax`, argmax.rs:72-114):
+// stage 1 writes each part's best (value, index), stage 2 folds the parts in order.
+template <typename TIn>
+__global__ void __launch_bounds__(256) peaks_kernel(const TIn *x, float *peak_v, uint32_t *peak_i, uint32_t width,
+                                                    uint32_t parts) {
+    __shared__ float sv[8];
+    __shared__ uint32_t si[8];
+    pdl_wait();
+    const uint32_t row = blockIdx.y, part = blockIdx.x;
+    const uint32_t span = (width + parts - 1) / parts;
+    const uint32_t lo = part * span, hi = min(width, lo + span);
+    const uint32_t none = width;
+    Cand best = {0.0f, none};
+    for (uint32_t i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        const float v = load_score(x, (size_t)row * width + i);
+        if (!(v > -INFINITY)) continue;
+        best = best_of(best, Cand{v, i}, none);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        Cand other = {__shfl_xor_sync(0xFFFFFFFFu, best.v, o), __shfl_xor_sync(0xFFFFFFFFu, best.i, o)};
+        best = best_of(best, other, none);
+    }
+    if ((threadIdx.x & 31) == 0) {
+        sv[threadIdx.x >> 5] = best.v;
+        si[threadIdx.x >> 5] = best.i;
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+    if (threadIdx.x == 0) {
+        Cand b = {sv[0], si[0]};
+        for (uint32_t w = 1; w < blockDim.x / 32; w++) b = best_of(b, Cand{sv[w], si[w]}, none);
+        peak_v[(size_t)row * parts + part] = b.v;
+        peak_i[(size_t)row * parts + part] = b.i;
+    }
+}
+
+__global__ void __launch_bounds__(32) argmax_kernel(const float *peak_v, const uint32_t *peak_i, uint32_t *ids,
+                                                    uint32_t width, uint32_t parts) {
+    pdl_wait();
+    const uint32_t row = blockIdx.x, none = width;
+    Cand best = {0.0f, none};
+    for (uint32_t i = threadIdx.x; i < parts; i += 32)
+        best = best_of(best, Cand{peak_v[(size_t)row * parts + i], peak_i[(size_t)row * parts + i]}, none);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        Cand other = {__shfl_xor_sync(0xFFFFFFFFu, best.v, o), __shfl_xor_sync(0xFFFFFFFFu, best.i, o)};
+        best = best_of(best, other, none);
+    }
+    pdl_launch_dependents();
+    if (threadIdx.x == 0) ids[row] = best.i;
+}
+
+// ---- take + softmax over the picks: engine/ir/interp/src/cpu.rs:497-508, 49-59
+__global__ void __launch_bounds__(32) take_softmax_kernel(const float *x, const uint32_t *ids, float *gates,
+                                                          uint32_t width, uint32_t k) {
+    pdl_wait();
+    const uint32_t row = blockIdx.x, lane = threadIdx.x;
+    float v = -INFINITY;
+    if (lane < k) {
+        const uint32_t id = ids[(size_t)row * k + lane];
+        v = id < width ? x[(size_t)row * width + id] : 0.0f;  // out-of-range ids read zero
+    }
+    const float mx = warp_max(v);
+    const float e = lane < k ? expf(v - mx) : 0.0f;
+    // sum in pick order, as the reference's sequential loop does
+    float sum = 0.0f;
+    for (uint32_t j = 0; j < k; j++) sum += __shfl_sync(0xFFFFFFFFu, e, j);
+    pdl_launch_dependents();
+    if (lane < k) gates[(size_t)row * k + lane] = e / sum;
+}
+
+// The device-resident decode loop's feedback: each row's next token is the id it just produced
+// and its position moves on by one (engine/engine/src/lib.rs:166-200 does this on the host).
+__global__ void advance_rows_kernel(const uint32_t *ids, uint32_t *tokens, uint32_t *positions, uint32_t rows) {
+    pdl_wait();
+    const uint32_t r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r < rows) {
+        tokens[r] = ids[r];
+        positions[r] += 1;
+    }
+    pdl_launch_dependents();
+}
+
+constexpr uint32_t kPeakParts = 64;
+
+}  // namespace
+
+int advance_rows(const uint32_t *ids, uint32_t *tokens, uint32_t *positions, uint32_t rows, cudaStream_t stream) {
+    if (rows == 0) return TS_OK;
+    cudaError_t e = launch(advance_rows_kernel, dim3(ceil_div(rows, 128)), dim3(128), 0, stream, pdl_enabled(), ids,
+                           tokens, positions, rows);
+    if (e != cudaSuccess) return fail(TS_ERR_CUDA, "launch of advance_rows failed: %s", cudaGetErrorString(e));
+    return TS_OK;
+}
+
+int rms_norm(const void *x, int x_dtype, const float *w, void *out, int out_dtype, uint32_t rows, uint32_t width,
+             float eps, const uint32_t *row_ids, cudaStream_t stream) {
+    if (rows == 0) return TS_OK;
+    cudaError_t e;
+    const uint32_t threads = width >= 1024 ? 256 : 128;
+    const bool pdl = pdl_enabled();
+    if (x_dtype == TS_F32 && out_dtype == TS_BF16)
+        e = launch(rms_norm_kernel<float, uint16_t>, dim3(rows), dim3(threads), 0, stream, pdl, (const float *)x, w,
+                   (uint16_t *)out, width, eps, row_ids);
+    else if (x_dtype == TS_F32)
+        e = launch(rms_norm_kernel<float, float>, dim3(rows), dim3(threads), 0, stream, pdl, (const float *)x, w,
+                   (float *)out, width, eps, row_ids);
+    else if (out_dtype == TS_BF16)
+        e = launch(rms_norm_kernel<uint16_t, uint16_t>, dim3(rows), dim3(threads), 0, stream, pdl,
+                   (const uint16_t *)x, w, (uint16_t *)out, width, eps, row_ids);
+    else
+        e = launch(rms_norm_kernel<uint16_t, float>, dim3(rows), dim3(threads), 0, stream, pdl, (const uint16_t *)x,
+                   w, (float *)out, width, eps, row_ids);
+    if (e != cudaSuccess) return fail(TS_ERR_CUDA, "launch of rms_norm failed: %s", cudaGetErrorString(e));
+    return TS_OK;
+}
+
+int gather_rows(const void *table, const uint32_t *ids, void *out, int out_dtype, uint32_t rows,
+                uint32_t table_rows, uint32_t width, uint32_t first, cudaStream_t stream) {
+    if (rows == 0) return TS_OK;
+    cudaError_t e;
+    if (out_dtype == TS_F32)
+        e = launch(gather_kernel<float>, dim3(rows), dim3(128), 0, stream, pdl_enabled(), (const uint16_t *)table, ids,
+                   (float *)out, table_rows, width, first);
+    else
+        e = launch(gather_kernel<uint16_t>, dim3(rows), dim3(128), 0, stream, pdl_enabled(), (const uint16_t *)table,
+                   ids, (uint16_t *)out, table_rows, width, first);
+    if (e != cudaSuccess) return fail(TS_ERR_CUDA, "launch of gather failed: %s", cudaGetErrorString(e));
+    return TS_OK;
+}
+
+int scatter_rows(const void *x, const uint32_t *slots, const uint32_t *positions, void *out, const KeptDev &kept,
+                 uint32_t rows, uint32_t width, cudaStream_t stream) {
+    if (rows == 0) return TS_OK;
+    cudaError_t e = launch(scatter_kernel, dim3(rows), dim3(128), 0, stream, pdl_enabled(), (const uint16_t *)x, slots,
+                           positions, (uint16_t *)out, kept, width);
+    if (e != cudaSuccess) return fail(TS_ERR_CUDA, "launch of scatter failed: %s", cudaGetErrorString(e));
+    return TS_OK;
+}
+
+int qk_norm_rope_append(const void *qkv, const float *q_norm, const float *k_norm, const float *inv_freq,
+                        const uint32_t *slots, const uint32_t *positions, void *q_out, void *k_rows, void *v_rows,
+                        const KeptDev &kept, uint32_t rows, uint32_t heads, uint32_t kv_heads, uint32_t width,
+                        float eps, cudaStream_t stream) {
+    if (rows == 0) return TS_OK;
+    const uint32_t units = rows * (heads + 2 * kv_heads);
+    dim3 grid(ceil_div(units, 4));
+    cudaError_t e;
+    if (width == 128)
+        e = launch(qk_norm_rope_append_kernel<128>, grid, dim3(128), 0, stream, pdl_enabled(), (const uint16_t *)qkv,
+                   q_norm, k_norm, inv_freq, slots, positions, (uint16_t *)q_out, (uint16_t *)k_rows,
+                   (uint16_t *)v_rows, kept, rows, heads, kv_heads, eps);
+    else if (width == 256)
+        e = launch(qk_norm_rope_append_kernel<256>, grid, dim3(128), 0, stream, pdl_enabled(), (const uint16_t *)qkv,
+                   q_norm, k_norm, inv_freq, slots, positions, (uint16_t *)q_out, (uint16_t *)k_rows,
+                   (uint16_t *)v_rows, kept, rows, heads, kv_heads, eps);
+    else if (width == 64)
+        e = launch(qk_norm_rope_append_kernel<64>, grid, dim3(128), 0, stream, pdl_enabled(), (const uint16_t *)qkv,
+                   q_norm, k_norm, inv_freq, slots, positions, (uint16_t *)q_out, (uint16_t *)k_rows,
+                   (uint16_t *)v_rows, kept, rows, heads, kv_heads, eps);
+    else
+        return fail(TS_ERR_BAD_INPUT, "qk_norm_rope_append: width %u is not 64, 128 or 256", width);
+    if (e != cudaSuccess) return fail(TS_ERR_CUDA, "launch of qk_norm_rope_append failed: %s", cudaGetErrorString(e));
+    return TS_OK;
+}
+
+size_t top_k_workspace_bytes(uint32_t rows, uint32_t width, uint32_t k) {
+    if (k == 1 && width > 8192) return (size_t)rows * kPeakParts * 8;
+    return 0;
+}
+
+int top_k(const void *x, int x_dtype, uint32_t *ids, uint32_t rows, uint32_t width, uint32_t k, void *workspace,
+          size_t workspace_bytes, cudaStream_t stream) {
+    if (rows == 0 || k == 0) return TS_OK;
+    cudaError_t e;
+    const bool pdl = pdl_enabled();
+    if (k == 1 && width > 8192) {
+        size_t need = top_k_workspace_bytes(rows, width, k);
+        TS_REQUIRE(workspace && workspace_bytes >= need, "top_k: workspace of %zu bytes is smaller than the %zu needed",
+                   workspace_bytes, need);
+        float *pv = (float *)workspace;
+        uint32_t *pi = (uint32_t *)(pv + (size_t)rows * kPeakParts);
+        if (x_dtype == TS_F32)
+            e = launch(peaks_kernel<float>, dim3(kPeakParts, rows), dim3(256), 0, stream, pdl, (const float *)x, pv, pi,
+                       width, kPeakParts);
+        else
+            e = launch(peaks_kernel<uint16_t>, dim3(kPeakParts, rows), dim3(256), 0, stream, pdl, (const uint16_t *)x,
+                       pv, pi, width, kPeakParts);
+        if (e != cudaSuccess) return fail(TS_ERR_CUDA, "launch of peaks failed: %s", cudaGetErrorString(e));
+        e = launch(argmax_kernel, dim3(rows), dim3(32), 0, stream, pdl, (const float *)pv, (const uint32_t *)pi, ids,
+                   width, kPeakParts);
+        if (e != cudaSuccess) return fail(TS_ERR_CUDA, "launch of argmax failed: %s", cudaGetErrorString(e));
+        return TS_OK;
+    }
+    if (x_dtype == TS_F32)
+        e = launch(top_k_kernel<float>, dim3(rows), dim3(256), 0, stream, pdl, (const float *)x, ids, width, k);
+    else
+        e = launch(top_k_kernel<uint16_t>, dim3(rows), dim3(256), 0, stream, pdl, (const uint16_t *)x, ids, width, k);
+    if (e != cudaSuccess) return fail(TS_ERR_CUDA, "launch of top_k failed: %s", cudaGetErrorString(e));
+    return TS_OK;
+}
+
+int take_softmax(const float *x, const uint32_t *ids, float *gates, uint32_t rows, uint32_t width, uint32_t k,
+                 cudaStream_t stream) {
+    if (rows == 0) return TS_OK;
+    cudaError_t e = launch(take_softmax_kernel, dim3(rows), dim3(32), 0, stream, pdl_enabled(), x, ids, gates, width, k);
+    if (e != cudaSuccess) return fail(TS_ERR_CUDA, "launch of take_softmax failed: %s", cudaGetErrorString(e));
+    return TS_OK;
+}
+
+}  // namespace ts

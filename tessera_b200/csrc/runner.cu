@@ -1,0 +1,448 @@
+// The host side of the decoder: owns the plan's buffers, binds arguments, enqueues the step
+// list and replays it as a CUDA graph keyed by the bound sizes - the part tessera-run's CUDA
+// backend plays for a lowered plan (engine/plan/run/src/device.rs:128-242, 348-419;
+// engine/plan/run/src/run.rs:122-345).  The step list is the Qwen3-shaped decoder of
+// engine/models/src/decoder.rs:281-389.
+#include <cstring>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "tessera_b200_run.h"
+#include "ts_kernels.cuh"
+
+using namespace ts;
+
+struct ts_decoder {
+    ts_decoder_config c;
+    uint32_t qkv_n, page_rows, kept_pages, kept_total_rows;
+    // weights
+    uint16_t *embed = nullptr;
+    float *norm = nullptr;
+    struct Layer {
+        uint16_t *wqkv, *wo, *wgu, *wdown;
+        float *ln1, *ln2, *q_norm, *k_norm;
+        uint16_t *k_rows, *v_rows;
+    };
+    std::vector<Layer> layers;
+    // plan buffers
+    float *x = nullptr;          // residual rows [max_rows, hidden] f32
+    uint16_t *h = nullptr;       // normed rows [max_rows, hidden]
+    uint16_t *qkv = nullptr;     // [max_rows, qkv_n]
+    uint16_t *q = nullptr;       // [max_rows, heads * head_dim]
+    uint16_t *attn = nullptr;    // [max_rows, heads * head_dim]
+    uint16_t *act = nullptr;     // [max_rows, ffn]
+    uint16_t *h_out = nullptr;   // final normed rows of the wanted rows [max_rows, hidden]
+    float *logits = nullptr;     // [max_out, vocab]
+    uint32_t max_out = 0;
+    uint32_t *tokens = nullptr, *slots = nullptr, *positions = nullptr, *out_rows = nullptr, *ids = nullptr;
+    uint32_t *table = nullptr;
+    float *inv_freq = nullptr;
+    void *workspace = nullptr;
+    size_t workspace_bytes = 0;
+    // pinned staging for feeds and reads
+    uint32_t *stage = nullptr;   // 5 * max_rows u32
+    // graphs keyed by (rows, keys, n_out, resident)
+    std::map<uint64_t, cudaGraphExec_t> graphs;
+    uint64_t replays = 0;
+    uint32_t last_rows = 0, last_out = 0, last_keys = 0;
+    std::vector<uint32_t> host_positions;  // of the last launch, to follow the resident loop
+    std::vector<void *> owned;
+};
+
+namespace {
+
+template <typename T>
+int dev_alloc(ts_decoder *d, T **out, size_t count) {
+    void *p = nullptr;
+    size_t bytes = count * sizeof(T);
+    if (bytes == 0) bytes = 16;
+    TS_CUDA(cudaMalloc(&p, bytes));
+    TS_CUDA(cudaMemset(p, 0, bytes));  // plan buffers start zeroed (device.rs:397-402)
+    d->owned.push_back(p);
+    *out = (T *)p;
+    return TS_OK;
+}
+
+ts_kept kept_of(const ts_decoder *d) {
+    ts_kept k = {};
+    if (d->c.page == 0) {
+        k.kind = TS_KEPT_DENSE;
+        k.page = 1;
+        k.kept_scalar = d->c.context;
+    } else {
+        k.kind = TS_KEPT_PAGED;
+        k.page = d->c.page;
+        k.kept_scalar = d->kept_pages;
+        k.table = d->table;
+        k.table_len = d->c.slots * d->kept_pages;
+    }
+    k.rows = d->kept_total_rows;
+    return k;
+}
+
+size_t max_size(size_t a, size_t b) { return a > b ? a : b; }
+
+// The step list for `rows` rows that see at most `keys` positions; logits for n_out rows.
+int enqueue(ts_decoder *d, uint32_t rows, uint32_t keys, uint32_t n_out, bool feedback, cudaStream_t s,
+            uint32_t *count) {
+    const ts_decoder_config &c = d->c;
+    const uint32_t H = c.hidden, D = c.head_dim, QW = c.heads * D;
+    uint32_t launches = 0;
+    int rc;
+    ts_kept kept = kept_of(d);
+    KeptDev kd;
+    if ((rc = kept_to_dev(&kept, &kd)) != TS_OK) return rc;
+    const bool contiguous = kept.kind == TS_KEPT_DENSE || kept.page >= 32;
+    const float scale = 1.0f / sqrtf((float)D);
+#define STEP(expr)                        \
+    do {                                  \
+        if ((rc = (expr)) != TS_OK) return rc; \
+        launches++;                       \
+    } while (0)
+    auto linear = [&](const void *xin, const void *w, const void *a0, void *out, uint32_t n, uint32_t k, int epi,
+                      int out_dtype) -> int {
+        const bool skinny = rows <= 16 && skinny_supports(rows, n, k, epi);
+        if (skinny) return linear_skinny(xin, w, a0, out, rows, n, k, epi, 1.0f, out_dtype, d->workspace,
+                                         d->workspace_bytes, s);
+        return linear_umma(xin, w, a0, out, rows, n, k, epi, 1.0f, out_dtype, d->workspace, d->workspace_bytes, s);
+    };
+    if (feedback) STEP(advance_rows(d->ids, d->tokens, d->positions, rows, s));
+    STEP(gather_rows(d->embed, d->tokens, d->x, TS_F32, rows, c.vocab, H, 0, s));
+    for (uint32_t l = 0; l < c.layers; l++) {
+        ts_decoder::Layer &L = d->layers[l];
+        STEP(rms_norm(d->x, TS_F32, L.ln1, d->h, TS_BF16, rows, H, c.eps, nullptr, s));
+        STEP(linear(d->h, L.wqkv, nullptr, d->qkv, d->qkv_n, H, TS_EPI_NONE, TS_BF16));
+        STEP(qk_norm_rope_append(d->qkv, c.qk_norm ? L.q_norm : nullptr, c.qk_norm ? L.k_norm : nullptr, d->inv_freq,
+                                 d->slots, d->positions, d->q, L.k_rows, L.v_rows, kd, rows, c.heads, c.kv_heads, D,
+                                 c.eps, s));
+        STEP(attend_rows(d->q, L.k_rows, L.v_rows, d->attn, d->slots, d->positions, kd, contiguous, rows, keys, c.heads,
+                         c.kv_heads, D, 0xFFFFFFFFu, scale, d->workspace, d->workspace_bytes, s));
+        if (attend_rows_workspace_bytes(rows, keys, c.heads, c.kv_heads, D) > 0) launches++;
+        STEP(linear(d->attn, L.wo, d->x, d->x, H, QW, TS_EPI_ADD, TS_F32));
+        STEP(rms_norm(d->x, TS_F32, L.ln2, d->h, TS_BF16, rows, H, c.eps, nullptr, s));
+        STEP(linear(d->h, L.wgu, nullptr, d->act, 2 * c.ffn, H, TS_EPI_SWIGLU, TS_BF16));
+        STEP(linear(d->act, L.wdown, d->x, d->x, H, c.ffn, TS_EPI_ADD, TS_F32));
+    }
+    // Only the wanted rows go through the final norm and the unembedding.
+    STEP(rms_norm(d->x, TS_F32, d->norm, d->h_out, TS_BF16, n_out, H, c.eps, n_out == rows ? nullptr : d->out_rows, s));
+    {
+        const bool skinny = n_out <= 16 && skinny_supports(n_out, c.vocab, H, TS_EPI_NONE);
+        if (skinny)
+            STEP(linear_skinny(d->h_out, d->embed, nullptr, d->logits, n_out, c.vocab, H, TS_EPI_NONE, 1.0f, TS_F32,
+                               d->workspace, d->workspace_bytes, s));
+        else
+            STEP(linear_umma(d->h_out, d->embed, nullptr, d->logits, n_out, c.vocab, H, TS_EPI_NONE, 1.0f, TS_F32,
+                             d->workspace, d->workspace_bytes, s));
+    }
+    STEP(top_k(d->logits, TS_F32, d->ids, n_out, c.vocab, 1, d->workspace, d->workspace_bytes, s));
+    launches++;  // top-1 over the vocabulary is two launches
+#undef STEP
+    if (count) *count = launches;
+    return TS_OK;
+}
+
+// Replays the captured graph for these sizes, capturing it on first sight.
+int submit(ts_decoder *d, uint32_t rows, uint32_t keys, uint32_t n_out, bool feedback, cudaStream_t s) {
+    set_pdl(d->c.pdl != 0);
+    if (!d->c.graphs) return enqueue(d, rows, keys, n_out, feedback, s, nullptr);
+    const uint64_t key = ((uint64_t)rows << 40) | ((uint64_t)keys << 16) | ((uint64_t)(n_out & 0x7FFF) << 1) |
+                         (feedback ? 1 : 0);
+    auto it = d->graphs.find(key);
+    if (it == d->graphs.end()) {
+        cudaGraph_t graph = nullptr;
+        TS_CUDA(cudaStreamBeginCapture(s, cudaStreamCaptureModeRelaxed));
+        int rc = enqueue(d, rows, keys, n_out, feedback, s, nullptr);
+        cudaError_t e = cudaStreamEndCapture(s, &graph);
+        if (rc != TS_OK) {
+            if (graph) cudaGraphDestroy(graph);
+            return rc;
+        }
+        if (e != cudaSuccess) return fail(TS_ERR_CUDA, "cudaStreamEndCapture failed: %s", cudaGetErrorString(e));
+        cudaGraphExec_t exec = nullptr;
+        e = cudaGraphInstantiate(&exec, graph, 0);
+        cudaGraphDestroy(graph);
+        if (e != cudaSuccess) return fail(TS_ERR_CUDA, "cudaGraphInstantiate failed: %s", cudaGetErrorString(e));
+        it = d->graphs.emplace(key, exec).first;
+    }
+    TS_CUDA(cudaGraphLaunch(it->second, s));
+    d->replays++;
+    return TS_OK;
+}
+
+uint32_t keys_bucket(const ts_decoder *d, uint32_t furthest) {
+    uint32_t k = (furthest + 127) / 128 * 128;
+    return k > d->c.context ? d->c.context : k;
+}
+
+}  // namespace
+
+#pragma GCC visibility push(default)
+extern "C" {
+
+int ts_decoder_create(const ts_decoder_config *config, ts_decoder **out) {
+    TS_REQUIRE(config && out, "decoder: config and out must not be NULL");
+    const ts_decoder_config &c = *config;
+    TS_REQUIRE(c.layers && c.hidden && c.heads && c.kv_heads && c.head_dim && c.ffn && c.vocab && c.slots &&
+                   c.context && c.max_rows,
+               "decoder: every size must be positive");
+    TS_REQUIRE(c.heads % c.kv_heads == 0, "decoder: %u heads do not split over %u kv heads", c.heads, c.kv_heads);
+    TS_REQUIRE(c.head_dim == 64 || c.head_dim == 128 || c.head_dim == 256, "decoder: head_dim %u is not 64, 128 or 256",
+               c.head_dim);
+    TS_REQUIRE(c.page == 0 || c.page == 16 || c.page == 64, "decoder: page %u is not 0, 16 or 64", c.page);
+    TS_REQUIRE(c.hidden % 256 == 0 && c.ffn % 256 == 0 && (c.heads * c.head_dim) % 256 == 0,
+               "decoder: hidden, ffn and heads * head_dim must be multiples of 256");
+    int dev_count = 0;
+    if (cudaGetDeviceCount(&dev_count) != cudaSuccess || dev_count == 0)
+        return fail(TS_ERR_CUDA, "decoder: no CUDA device (there is no CPU path)");
+    ts_decoder *d = new ts_decoder();
+    d->c = c;
+    d->qkv_n = (c.heads + 2 * c.kv_heads) * c.head_dim;
+    d->page_rows = c.page ? c.page : 1;
+    d->kept_pages = c.page ? (c.context + c.page - 1) / c.page : c.context;
+    d->kept_total_rows = c.page ? c.slots * d->kept_pages * c.page : c.slots * c.context;
+    d->max_out = c.max_rows < 256 ? c.max_rows : 256;
+    int rc = TS_OK;
+    auto A = [&](int r) { if (rc == TS_OK) rc = r; };
+    const size_t H = c.hidden, QW = (size_t)c.heads * c.head_dim, KW = (size_t)c.kv_heads * c.head_dim;
+    A(dev_alloc(d, &d->embed, (size_t)c.vocab * H));
+    A(dev_alloc(d, &d->norm, H));
+    d->layers.resize(c.layers);
+    for (uint32_t l = 0; l < c.layers && rc == TS_OK; l++) {
+        ts_decoder::Layer &L = d->layers[l];
+        A(dev_alloc(d, &L.wqkv, (size_t)d->qkv_n * H));
+        A(dev_alloc(d, &L.wo, H * QW));
+        A(dev_alloc(d, &L.wgu, (size_t)2 * c.ffn * H));
+        A(dev_alloc(d, &L.wdown, H * c.ffn));
+        A(dev_alloc(d, &L.ln1, H));
+        A(dev_alloc(d, &L.ln2, H));
+        A(dev_alloc(d, &L.q_norm, c.head_dim));
+        A(dev_alloc(d, &L.k_norm, c.head_dim));
+        A(dev_alloc(d, &L.k_rows, (size_t)d->kept_total_rows * KW));
+        A(dev_alloc(d, &L.v_rows, (size_t)d->kept_total_rows * KW));
+    }
+    const size_t R = c.max_rows;
+    A(dev_alloc(d, &d->x, R * H));
+    A(dev_alloc(d, &d->h, R * H));
+    A(dev_alloc(d, &d->qkv, R * d->qkv_n));
+    A(dev_alloc(d, &d->q, R * QW));
+    A(dev_alloc(d, &d->attn, R * QW));
+    A(dev_alloc(d, &d->act, R * c.ffn));
+    A(dev_alloc(d, &d->h_out, R * H));
+    A(dev_alloc(d, &d->logits, (size_t)d->max_out * c.vocab));
+    A(dev_alloc(d, &d->tokens, R));
+    A(dev_alloc(d, &d->slots, R));
+    A(dev_alloc(d, &d->positions, R));
+    A(dev_alloc(d, &d->out_rows, R));
+    A(dev_alloc(d, &d->ids, R));
+    A(dev_alloc(d, &d->table, (size_t)c.slots * d->kept_pages));
+    A(dev_alloc(d, &d->inv_freq, c.head_dim / 2));
+    // One workspace for every step: the largest any of them asks for at max_rows.
+    size_t ws = 0;
+    for (uint32_t rows : {1u, 8u, 16u, 32u, 64u, 128u, c.max_rows, d->max_out}) {
+        if (rows > c.max_rows) continue;
+        const bool g = true;
+        (void)g;
+        auto need = [&](uint32_t n, uint32_t k, int epi) {
+            size_t a = skinny_supports(rows, n, k, epi) ? skinny_workspace_bytes(rows, n, k, epi == TS_EPI_SWIGLU) : 0;
+            size_t b = umma_supports(rows, n, k, epi) ? umma_workspace_bytes(rows, n, k, epi) : 0;
+            return max_size(a, b);
+        };
+        ws = max_size(ws, need(d->qkv_n, c.hidden, TS_EPI_NONE));
+        ws = max_size(ws, need(c.hidden, c.heads * c.head_dim, TS_EPI_ADD));
+        ws = max_size(ws, need(2 * c.ffn, c.hidden, TS_EPI_SWIGLU));
+        ws = max_size(ws, need(c.hidden, c.ffn, TS_EPI_ADD));
+        if (rows <= d->max_out) ws = max_size(ws, need(c.vocab, c.hidden, TS_EPI_NONE));
+        ws = max_size(ws, attend_rows_workspace_bytes(rows, c.context, c.heads, c.kv_heads, c.head_dim));
+        ws = max_size(ws, top_k_workspace_bytes(rows, c.vocab, 1));
+    }
+    d->workspace_bytes = ws + 256;
+    if (rc == TS_OK) {
+        void *p = nullptr;
+        cudaError_t e = cudaMalloc(&p, d->workspace_bytes);
+        if (e != cudaSuccess) rc = fail(TS_ERR_CUDA, "cudaMalloc of the workspace failed: %s", cudaGetErrorString(e));
+        else { d->workspace = p; d->owned.push_back(p); }
+    }
+    if (rc == TS_OK) {
+        cudaError_t e = cudaMallocHost((void **)&d->stage, 6 * R * sizeof(uint32_t));
+        if (e != cudaSuccess) rc = fail(TS_ERR_CUDA, "cudaMallocHost failed: %s", cudaGetErrorString(e));
+    }
+    if (rc == TS_OK) {
+        std::vector<float> f(c.head_dim / 2);
+        for (uint32_t j = 0; j < c.head_dim / 2; j++) f[j] = powf(c.theta, -((float)(2 * j)) / (float)c.head_dim);
+        cudaError_t e = cudaMemcpy(d->inv_freq, f.data(), f.size() * 4, cudaMemcpyHostToDevice);
+        std::vector<uint32_t> t((size_t)c.slots * d->kept_pages);
+        for (size_t i = 0; i < t.size(); i++) t[i] = (uint32_t)i;  // identity: lanes.rs:4-65
+        if (e == cudaSuccess) e = cudaMemcpy(d->table, t.data(), t.size() * 4, cudaMemcpyHostToDevice);
+        if (e != cudaSuccess) rc = fail(TS_ERR_CUDA, "initial uploads failed: %s", cudaGetErrorString(e));
+    }
+    if (rc != TS_OK) {
+        ts_decoder_destroy(d);
+        return rc;
+    }
+    *out = d;
+    return TS_OK;
+}
+
+void ts_decoder_destroy(ts_decoder *d) {
+    if (!d) return;
+    for (auto &g : d->graphs) cudaGraphExecDestroy(g.second);
+    for (void *p : d->owned) cudaFree(p);
+    if (d->stage) cudaFreeHost(d->stage);
+    delete d;
+}
+
+int ts_decoder_load(ts_decoder *d, const char *name, const void *host, size_t bytes) {
+    TS_REQUIRE(d && name && host, "decoder load: NULL argument");
+    const ts_decoder_config &c = d->c;
+    const size_t H = c.hidden, D = c.head_dim, QW = (size_t)c.heads * D, KW = (size_t)c.kv_heads * D, F = c.ffn;
+    void *dst = nullptr;
+    size_t want = 0;
+    std::string n(name);
+    if (n == "embed") { dst = d->embed; want = (size_t)c.vocab * H * 2; }
+    else if (n == "norm") { dst = d->norm; want = H * 4; }
+    else if (n.rfind("layers.", 0) == 0) {
+        size_t dot = n.find('.', 7);
+        TS_REQUIRE(dot != std::string::npos, "decoder load: weight name '%s' is malformed", name);
+        const uint32_t l = (uint32_t)atoi(n.substr(7, dot - 7).c_str());
+        TS_REQUIRE(l < c.layers, "decoder load: layer %u is past the %u layers", l, c.layers);
+        ts_decoder::Layer &L = d->layers[l];
+        const std::string f = n.substr(dot + 1);
+        if (f == "ln1") { dst = L.ln1; want = H * 4; }
+        else if (f == "ln2") { dst = L.ln2; want = H * 4; }
+        else if (f == "q_norm") { dst = L.q_norm; want = D * 4; }
+        else if (f == "k_norm") { dst = L.k_norm; want = D * 4; }
+        else if (f == "q") { dst = L.wqkv; want = QW * H * 2; }
+        else if (f == "k") { dst = L.wqkv + QW * H; want = KW * H * 2; }
+        else if (f == "v") { dst = L.wqkv + (QW + KW) * H; want = KW * H * 2; }
+        else if (f == "o") { dst = L.wo; want = H * QW * 2; }
+        else if (f == "mlp.gate") { dst = L.wgu; want = F * H * 2; }
+        else if (f == "mlp.up") { dst = L.wgu + F * H; want = F * H * 2; }
+        else if (f == "mlp.down") { dst = L.wdown; want = H * F * 2; }
+    }
+    TS_REQUIRE(dst != nullptr, "decoder load: no weight is called '%s'", name);
+    TS_REQUIRE(bytes == want, "decoder load: '%s' wants %zu bytes, got %zu", name, want, bytes);
+    TS_CUDA(cudaMemcpy(dst, host, bytes, cudaMemcpyHostToDevice));
+    return TS_OK;
+}
+
+int ts_decoder_set_table(ts_decoder *d, const uint32_t *host_table, uint32_t entries) {
+    TS_REQUIRE(d && host_table, "decoder table: NULL argument");
+    TS_REQUIRE(d->c.page != 0, "decoder table: the kept rows are dense, there is no table");
+    const uint32_t want = d->c.slots * d->kept_pages;
+    TS_REQUIRE(entries == want, "decoder table: wants %u entries, got %u", want, entries);
+    for (uint32_t i = 0; i < entries; i++)
+        TS_REQUIRE(host_table[i] < want, "decoder table: entry %u names page %u of %u", i, host_table[i], want);
+    TS_CUDA(cudaMemcpy(d->table, host_table, (size_t)entries * 4, cudaMemcpyHostToDevice));
+    return TS_OK;
+}
+
+int ts_decoder_step(ts_decoder *d, const uint32_t *tokens, const uint32_t *slots, const uint32_t *positions,
+                    uint32_t rows, const uint32_t *out_rows, uint32_t n_out, uint32_t *out_ids, void *stream) {
+    TS_REQUIRE(d && tokens && slots && positions, "decoder step: NULL argument");
+    const ts_decoder_config &c = d->c;
+    TS_REQUIRE(rows >= 1 && rows <= c.max_rows, "decoder step: %u rows, the plan takes 1..%u", rows, c.max_rows);
+    if (!out_rows) n_out = rows;
+    TS_REQUIRE(n_out >= 1 && n_out <= d->max_out, "decoder step: %u output rows, the plan takes 1..%u", n_out, d->max_out);
+    uint32_t furthest = 0;
+    for (uint32_t r = 0; r < rows; r++) {
+        TS_REQUIRE(slots[r] < c.slots, "decoder step: row %u at slot %u is outside the %u slots", r, slots[r], c.slots);
+        TS_REQUIRE(positions[r] < c.context, "decoder step: row %u at position %u is past the context of %u", r,
+                   positions[r], c.context);
+        TS_REQUIRE(tokens[r] < c.vocab, "decoder step: row %u holds token %u of a %u vocabulary", r, tokens[r], c.vocab);
+        if (positions[r] + 1 > furthest) furthest = positions[r] + 1;
+    }
+    for (uint32_t i = 0; out_rows && i < n_out; i++)
+        TS_REQUIRE(out_rows[i] < rows, "decoder step: output row %u is past the %u rows", out_rows[i], rows);
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t R = c.max_rows;
+    uint32_t *st = d->stage;
+    memcpy(st, tokens, rows * 4);
+    memcpy(st + R, slots, rows * 4);
+    memcpy(st + 2 * R, positions, rows * 4);
+    TS_CUDA(cudaMemcpyAsync(d->tokens, st, rows * 4, cudaMemcpyHostToDevice, s));
+    TS_CUDA(cudaMemcpyAsync(d->slots, st + R, rows * 4, cudaMemcpyHostToDevice, s));
+    TS_CUDA(cudaMemcpyAsync(d->positions, st + 2 * R, rows * 4, cudaMemcpyHostToDevice, s));
+    if (out_rows) {
+        memcpy(st + 3 * R, out_rows, n_out * 4);
+        TS_CUDA(cudaMemcpyAsync(d->out_rows, st + 3 * R, n_out * 4, cudaMemcpyHostToDevice, s));
+    }
+    const uint32_t keys = keys_bucket(d, furthest);
+    int rc = submit(d, rows, keys, n_out, false, s);
+    if (rc != TS_OK) return rc;
+    d->last_rows = rows;
+    d->last_out = n_out;
+    d->last_keys = furthest;
+    d->host_positions.assign(positions, positions + rows);
+    if (out_ids) {
+        TS_CUDA(cudaMemcpyAsync(st + 4 * R, d->ids, n_out * 4, cudaMemcpyDeviceToHost, s));
+        TS_CUDA(cudaStreamSynchronize(s));
+        memcpy(out_ids, st + 4 * R, n_out * 4);
+    } else {
+        TS_CUDA(cudaStreamSynchronize(s));
+    }
+    return TS_OK;
+}
+
+int ts_decoder_run_resident(ts_decoder *d, uint32_t steps, void *stream) {
+    TS_REQUIRE(d, "decoder: NULL");
+    TS_REQUIRE(d->last_rows > 0 && d->last_out == d->last_rows,
+               "decoder resident loop: the last launch must have produced one id per row");
+    cudaStream_t s = (cudaStream_t)stream;
+    for (uint32_t i = 0; i < steps; i++) {
+        const uint32_t furthest = d->last_keys + 1;
+        TS_REQUIRE(furthest <= d->c.context, "decoder resident loop: position %u is past the context of %u",
+                   furthest - 1, d->c.context);
+        int rc = submit(d, d->last_rows, keys_bucket(d, furthest), d->last_rows, true, s);
+        if (rc != TS_OK) return rc;
+        d->last_keys = furthest;
+        for (auto &p : d->host_positions) p++;
+    }
+    return TS_OK;
+}
+
+int ts_decoder_read_ids(ts_decoder *d, uint32_t *out_ids, uint32_t rows, void *stream) {
+    TS_REQUIRE(d && out_ids && rows <= d->c.max_rows, "decoder read: bad argument");
+    cudaStream_t s = (cudaStream_t)stream;
+    TS_CUDA(cudaMemcpyAsync(d->stage + 4 * (size_t)d->c.max_rows, d->ids, rows * 4, cudaMemcpyDeviceToHost, s));
+    TS_CUDA(cudaStreamSynchronize(s));
+    memcpy(out_ids, d->stage + 4 * (size_t)d->c.max_rows, rows * 4);
+    return TS_OK;
+}
+
+int ts_decoder_read_hidden(ts_decoder *d, void *out_bf16, uint32_t rows, void *stream) {
+    TS_REQUIRE(d && out_bf16 && rows <= d->c.max_rows, "decoder read: bad argument");
+    cudaStream_t s = (cudaStream_t)stream;
+    TS_CUDA(cudaMemcpyAsync(out_bf16, d->h_out, (size_t)rows * d->c.hidden * 2, cudaMemcpyDeviceToHost, s));
+    TS_CUDA(cudaStreamSynchronize(s));
+    return TS_OK;
+}
+
+int ts_decoder_read_logits(ts_decoder *d, float *out, uint32_t n_out, void *stream) {
+    TS_REQUIRE(d && out && n_out <= d->max_out, "decoder read: bad argument");
+    cudaStream_t s = (cudaStream_t)stream;
+    TS_CUDA(cudaMemcpyAsync(out, d->logits, (size_t)n_out * d->c.vocab * 4, cudaMemcpyDeviceToHost, s));
+    TS_CUDA(cudaStreamSynchronize(s));
+    return TS_OK;
+}
+
+uint32_t ts_decoder_launches_per_step(ts_decoder *d, uint32_t rows, uint32_t keys) {
+    if (!d) return 0;
+    // Count by walking the same decisions enqueue makes, without launching.
+    const ts_decoder_config &c = d->c;
+    auto lin = [&](uint32_t m, uint32_t n, uint32_t k, int epi) -> uint32_t {
+        const bool skinny = m <= 16 && skinny_supports(m, n, k, epi);
+        size_t ws = skinny ? skinny_workspace_bytes(m, n, k, epi == TS_EPI_SWIGLU) : umma_workspace_bytes(m, n, k, epi);
+        return ws > 0 ? 2 : 1;
+    };
+    uint32_t per_layer = 2 /*norms*/ + 1 /*append*/ + 1 /*attention*/ +
+                         (attend_rows_workspace_bytes(rows, keys, c.heads, c.kv_heads, c.head_dim) > 0 ? 1 : 0) +
+                         lin(rows, d->qkv_n, c.hidden, TS_EPI_NONE) + lin(rows, c.hidden, c.heads * c.head_dim, TS_EPI_ADD) +
+                         lin(rows, 2 * c.ffn, c.hidden, TS_EPI_SWIGLU) + lin(rows, c.hidden, c.ffn, TS_EPI_ADD);
+    return 1 /*gather*/ + c.layers * per_layer + 1 /*final norm*/ + lin(rows, c.vocab, c.hidden, TS_EPI_NONE) + 2 /*top-1*/;
+}
+
+uint64_t ts_decoder_graph_replays(ts_decoder *d) { return d ? d->replays : 0; }
+
+}  // extern "C"
+#pragma GCC visibility pop

@@ -1,0 +1,45 @@
+// Host-side entry points of the kernels, one per translation unit; the C ABI and the runner call these.
+#pragma once
+
+#include "ts_common.cuh"
+
+namespace ts {
+
+bool skinny_supports(uint32_t m, uint32_t n, uint32_t k, int epilogue);
+size_t skinny_workspace_bytes(uint32_t m, uint32_t n, uint32_t k, bool gated);
+int linear_skinny(const void *x, const void *w, const void *a0, void *out, uint32_t m, uint32_t n, uint32_t k,
+                  int epilogue, float scale, int out_dtype, void *workspace, size_t workspace_bytes,
+                  cudaStream_t stream);
+bool umma_supports(uint32_t m, uint32_t n, uint32_t k, int epilogue);
+size_t umma_workspace_bytes(uint32_t m, uint32_t n, uint32_t k, int epilogue);
+int umma_take_status();
+int linear_umma(const void *x, const void *w, const void *a0, void *out, uint32_t m, uint32_t n, uint32_t k,
+                int epilogue, float scale, int out_dtype, void *workspace, size_t workspace_bytes,
+                cudaStream_t stream);
+size_t attend_rows_workspace_bytes(uint32_t rows, uint32_t keys, uint32_t heads, uint32_t kv_heads, uint32_t width);
+int attend_rows(const void *q, const void *k, const void *v, void *out, const uint32_t *slots,
+                const uint32_t *positions, const KeptDev &kept, bool contiguous, uint32_t rows, uint32_t keys,
+                uint32_t heads, uint32_t kv_heads, uint32_t width, uint32_t back, float scale, void *workspace,
+                size_t workspace_bytes, cudaStream_t stream);
+int rms_norm(const void *x, int x_dtype, const float *w, void *out, int out_dtype, uint32_t rows, uint32_t width,
+             float eps, const uint32_t *row_ids, cudaStream_t stream);
+int advance_rows(const uint32_t *ids, uint32_t *tokens, uint32_t *positions, uint32_t rows, cudaStream_t stream);
+int gather_rows(const void *table, const uint32_t *ids, void *out, int out_dtype, uint32_t rows,
+                uint32_t table_rows, uint32_t width, uint32_t first, cudaStream_t stream);
+int scatter_rows(const void *x, const uint32_t *slots, const uint32_t *positions, void *out, const KeptDev &kept,
+                 uint32_t rows, uint32_t width, cudaStream_t stream);
+int qk_norm_rope_append(const void *qkv, const float *q_norm, const float *k_norm, const float *inv_freq,
+                        const uint32_t *slots, const uint32_t *positions, void *q_out, void *k_rows, void *v_rows,
+                        const KeptDev &kept, uint32_t rows, uint32_t heads, uint32_t kv_heads, uint32_t width,
+                        float eps, cudaStream_t stream);
+size_t top_k_workspace_bytes(uint32_t rows, uint32_t width, uint32_t k);
+int top_k(const void *x, int x_dtype, uint32_t *ids, uint32_t rows, uint32_t width, uint32_t k, void *workspace,
+          size_t workspace_bytes, cudaStream_t stream);
+int take_softmax(const float *x, const uint32_t *ids, float *gates, uint32_t rows, uint32_t width, uint32_t k,
+                 cudaStream_t stream);
+
+
+// Sets the process-wide programmatic-dependent-launch switch.
+void set_pdl(bool enabled);
+
+}  // namespace ts

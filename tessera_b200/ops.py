@@ -1,0 +1,165 @@
+"""Each C-ABI entry point over torch CUDA tensors.
+
+torch is plumbing here: device memory and the current stream.  Every function passes raw
+device pointers to libtessera_b200.so and raises TesseraError on a non-zero status.  A call
+with tensors that are not on a CUDA device is refused; there is no CPU path.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+from ._lib import EPILOGUE, KEPT_KIND, KEPT_PAGE, LINEAR_PATH, TS_BF16, TS_F32, TsKept, check, lib
+
+_workspaces: dict = {}
+
+
+def _stream() -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise _lib.TesseraError(_lib.TS_ERR_BAD_INPUT, "tensors must live on a CUDA device (there is no CPU path)")
+    if not t.is_contiguous():
+        raise _lib.TesseraError(_lib.TS_ERR_BAD_INPUT, "tensors must be contiguous")
+    return C.c_void_p(t.data_ptr())
+
+
+def _dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.bfloat16:
+        return TS_BF16
+    if dtype == torch.float32:
+        return TS_F32
+    raise _lib.TesseraError(_lib.TS_ERR_BAD_INPUT, f"dtype {dtype} is not bf16 or f32")
+
+
+def workspace(nbytes: int, device) -> torch.Tensor | None:
+    """A caller-owned scratch buffer, grown on demand and reused (one per device)."""
+    if nbytes == 0:
+        return None
+    key = torch.device(device).index or 0
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+def set_pdl(enabled: bool) -> None:
+    check(lib.ts_set_pdl(1 if enabled else 0))
+
+
+def device_status() -> int:
+    return lib.ts_device_status()
+
+
+def linear(x, w, a0=None, *, epilogue="none", scale=1.0, out_dtype=torch.bfloat16, path="auto", out=None):
+    """out[m, n] = sum_k x[m, k] w[n, k] (+ epilogue): ts_linear_bf16."""
+    m, k = x.shape
+    n = w.shape[0]
+    assert w.shape[1] == k and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    gated = epilogue in ("swiglu", "geglu")
+    if out is None:
+        out = torch.empty((m, n // 2 if gated else n), dtype=out_dtype, device=x.device)
+    nbytes = lib.ts_linear_workspace_bytes(m, n, k, EPILOGUE[epilogue], LINEAR_PATH[path])
+    ws = workspace(nbytes, x.device)
+    check(lib.ts_linear_bf16(_ptr(x), _ptr(w), _ptr(a0), _ptr(out), m, n, k, EPILOGUE[epilogue], scale,
+                             _dtype_code(out.dtype), LINEAR_PATH[path], _ptr(ws), nbytes, _stream()))
+    return out
+
+
+@dataclass
+class Kept:
+    """Where a slot's row at a position lives (engine/plan/codegen/src/kept.rs:8-24)."""
+    layout: str            # dense | interleaved | paged | paged16
+    scalar: int            # kept_stride | kept_slots | kept_pages
+    table: torch.Tensor | None = None  # u32 (stored as int32) [slots * kept_pages]
+    rows: int = 0
+
+    def c(self) -> TsKept:
+        t = self.table
+        return TsKept(KEPT_KIND[self.layout], KEPT_PAGE[self.layout], self.scalar,
+                      t.data_ptr() if t is not None else None, t.numel() if t is not None else 0, self.rows)
+
+
+def attend_rows(q, k_rows, v_rows, slots, positions, kept: Kept, keys: int, *, scale: float, back=0xFFFFFFFF,
+                out=None):
+    """Ragged causal attention over kept rows: ts_attend_rows_bf16."""
+    rows, heads, width = q.shape
+    kv_heads = k_rows.shape[-2]
+    if out is None:
+        out = torch.empty_like(q)
+    nbytes = lib.ts_attend_rows_workspace_bytes(rows, keys, heads, kv_heads, width)
+    ws = workspace(nbytes, q.device)
+    kc = kept.c()
+    check(lib.ts_attend_rows_bf16(_ptr(q), _ptr(k_rows), _ptr(v_rows), _ptr(out), _ptr(slots), _ptr(positions),
+                                  C.byref(kc), rows, keys, heads, kv_heads, width, back, scale, _ptr(ws), nbytes,
+                                  _stream()))
+    return out
+
+
+def scatter(x, slots, positions, out, kept: Kept):
+    rows = x.shape[0]
+    width = x.numel() // max(rows, 1)
+    kc = kept.c()
+    check(lib.ts_scatter_bf16(_ptr(x), _ptr(slots), _ptr(positions), _ptr(out), C.byref(kc), rows, width, _stream()))
+    return out
+
+
+def rope_inv_freq(theta: float, width: int, device) -> torch.Tensor:
+    buf = (C.c_float * (width // 2))()
+    lib.ts_rope_inv_freq(theta, width, buf)
+    return torch.tensor(list(buf), dtype=torch.float32, device=device)
+
+
+def qk_norm_rope_append(qkv, q_norm, k_norm, inv_freq, slots, positions, q_out, k_rows, v_rows, kept: Kept, heads,
+                        kv_heads, width, eps):
+    rows = qkv.shape[0]
+    kc = kept.c()
+    check(lib.ts_qk_norm_rope_append_bf16(_ptr(qkv), _ptr(q_norm), _ptr(k_norm), _ptr(inv_freq), _ptr(slots),
+                                          _ptr(positions), _ptr(q_out), _ptr(k_rows), _ptr(v_rows), C.byref(kc), rows,
+                                          heads, kv_heads, width, eps, _stream()))
+    return q_out
+
+
+def rms_norm(x, w=None, eps=1e-6, out_dtype=torch.bfloat16, out=None):
+    width = x.shape[-1]
+    rows = x.numel() // width
+    if out is None:
+        out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    check(lib.ts_rms_norm(_ptr(x), _dtype_code(x.dtype), _ptr(w), _ptr(out), _dtype_code(out.dtype), rows, width, eps,
+                          _stream()))
+    return out
+
+
+def gather(table, ids, out_dtype=torch.float32, first=0):
+    rows = ids.numel()
+    table_rows, width = table.shape
+    out = torch.empty(tuple(ids.shape) + (width,), dtype=out_dtype, device=table.device)
+    check(lib.ts_gather_bf16(_ptr(table), _ptr(ids), _ptr(out), _dtype_code(out_dtype), rows, table_rows, width, first,
+                             _stream()))
+    return out
+
+
+def top_k(x, k: int):
+    width = x.shape[-1]
+    rows = x.numel() // width
+    ids = torch.empty(x.shape[:-1] + (k,), dtype=torch.int32, device=x.device)
+    nbytes = lib.ts_top_k_workspace_bytes(rows, width, k)
+    ws = workspace(nbytes, x.device)
+    check(lib.ts_top_k(_ptr(x), _dtype_code(x.dtype), _ptr(ids), rows, width, k, _ptr(ws), nbytes, _stream()))
+    return ids
+
+
+def take_softmax(x, ids):
+    rows, width = x.shape
+    k = ids.shape[-1]
+    gates = torch.empty((rows, k), dtype=torch.float32, device=x.device)
+    check(lib.ts_take_softmax(_ptr(x), _ptr(ids), _ptr(gates), rows, width, k, _stream()))
+    return gates

@@ -1,0 +1,136 @@
+"""Linear kernels against the CPU checker on the same seeded inputs.
+
+Tolerance: bf16 outputs with f32 sums must sit within 1e-2 of the checker relative to the
+output's largest magnitude (the bar the build states for floating-point outputs); f32 outputs
+(the residual-add epilogue) within 1e-4, which is summation-order noise.  One-hot inputs must
+read weights back bit-exactly, as engine/rules/linear/tests/lanes_test.rs:96-106 demands.
+"""
+import numpy as np
+import pytest
+import torch
+
+import oracle as O
+from tests.util import from_bits, normal_bf16, rel_error, widen
+
+pytestmark = pytest.mark.gpu
+
+BF16_TOL = 1e-2
+F32_TOL = 1e-4
+
+
+def _case(m, n, k, seed):
+    rng = np.random.default_rng(seed)
+    x = normal_bf16(rng, (m, k), 1.0)
+    w = normal_bf16(rng, (n, k), 0.02)
+    return x, w
+
+
+def _run(x_bits, w_bits, path, **kw):
+    from tessera_b200 import ops
+    out = ops.linear(from_bits(x_bits), from_bits(w_bits), path=path, **kw)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    return out
+
+
+SKINNY = [(1, 2048, 1024), (5, 1024, 1024), (16, 1024, 2048), (33, 6144, 1024), (64, 1024, 3072),
+          (64, 2048, 1024), (7, 1000, 512), (64, 72, 256)]
+UMMA = [(1, 2048, 1024), (16, 1024, 2048), (64, 1024, 3072), (64, 6144, 1024), (100, 2048, 1024),
+        (128, 1024, 1024), (200, 512, 1024), (384, 1024, 512), (1024, 640, 256), (129, 200, 64)]
+
+
+@pytest.mark.parametrize("m,n,k", SKINNY)
+def test_skinny_matches_oracle(m, n, k):
+    x, w = _case(m, n, k, seed=m * 7 + n + k)
+    want = O.matmul(O.bf16_widen(x), w)
+    got = widen(_run(x, w, "skinny"))
+    assert rel_error(got, want) <= BF16_TOL
+    got32 = widen(_run(x, w, "skinny", out_dtype=torch.float32))
+    assert rel_error(got32, want) <= F32_TOL
+
+
+@pytest.mark.parametrize("m,n,k", UMMA)
+def test_umma_matches_oracle(m, n, k):
+    x, w = _case(m, n, k, seed=m * 11 + n + k)
+    want = O.matmul(O.bf16_widen(x), w)
+    got = widen(_run(x, w, "umma"))
+    assert rel_error(got, want) <= BF16_TOL
+    got32 = widen(_run(x, w, "umma", out_dtype=torch.float32))
+    assert rel_error(got32, want) <= F32_TOL
+
+
+@pytest.mark.parametrize("path,m", [("skinny", 8), ("umma", 8), ("umma", 160)])
+def test_one_hot_rows_read_weights_back(path, m):
+    # engine/rules/linear/tests/lanes_test.rs:96-106
+    n, k = 256, 512
+    rng = np.random.default_rng(5)
+    w = normal_bf16(rng, (n, k), 0.02)
+    hot = rng.integers(0, k, size=m)
+    x = np.zeros((m, k), np.float32)
+    x[np.arange(m), hot] = 1.0
+    got = _run(O.bf16_bits(x), w, path)
+    from tests.util import to_bits
+    assert np.array_equal(to_bits(got), w[:, hot].T)
+
+
+@pytest.mark.parametrize("path", ["skinny", "umma"])
+@pytest.mark.parametrize("m", [3, 64])
+def test_residual_add_epilogue(path, m):
+    n, k = 1024, 2048
+    x, w = _case(m, n, k, seed=90 + m)
+    rng = np.random.default_rng(91)
+    res = rng.standard_normal((m, n), dtype=np.float32)
+    want = O.matmul(O.bf16_widen(x), w) + res
+    got = widen(_run(x, w, path, a0=torch.from_numpy(res).cuda(), epilogue="add", out_dtype=torch.float32))
+    assert rel_error(got, want) <= F32_TOL
+
+
+@pytest.mark.parametrize("path,m", [("skinny", 4), ("skinny", 64), ("umma", 64), ("umma", 256)])
+@pytest.mark.parametrize("act", ["swiglu", "geglu"])
+def test_gated_epilogue(path, m, act):
+    ffn, k = 768, 512
+    x, w = _case(m, 2 * ffn, k, seed=33 + m)
+    xs = O.bf16_widen(x)
+    gate, up = O.matmul(xs, w[:ffn]), O.matmul(xs, w[ffn:])
+    want = O.act(gate, "silu" if act == "swiglu" else "gelu_tanh") * up
+    got = widen(_run(x, w, path, epilogue=act))
+    assert got.shape == (m, ffn)
+    assert rel_error(got, want) <= BF16_TOL
+
+
+@pytest.mark.parametrize("path", ["skinny", "umma"])
+def test_scale_epilogue(path):
+    x, w = _case(9, 512, 256, seed=3)
+    want = O.matmul(O.bf16_widen(x), w) * np.float32(0.125)
+    got = widen(_run(x, w, path, epilogue="scale", scale=0.125, out_dtype=torch.float32))
+    assert rel_error(got, want) <= F32_TOL
+
+
+def test_lm_head_shape_small_batch():
+    # (151936, 1024): the tied unembedding, at the decode parity batch
+    m, n, k = 2, 151936, 1024
+    x, w = _case(m, n, k, seed=1)
+    want = O.matmul(O.bf16_widen(x), w)
+    for path in ("skinny", "umma"):
+        got = widen(_run(x, w, path, out_dtype=torch.float32))
+        assert rel_error(got, want) <= F32_TOL
+
+
+def test_rerun_is_bit_identical():
+    # Order::PerConfig (engine/ir/graph/src/numerics.rs:26-35): one configuration, one sum order
+    x, w = _case(64, 1024, 3072, seed=8)
+    for path in ("skinny", "umma"):
+        a = _run(x, w, path, out_dtype=torch.float32)
+        b = _run(x, w, path, out_dtype=torch.float32)
+        assert torch.equal(a, b)
+
+
+def test_bad_arguments_are_refused():
+    from tessera_b200 import TesseraError, ops
+    x = torch.zeros((4, 100), dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros((8, 100), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(TesseraError) as e:
+        ops.linear(x, w)
+    assert e.value.code == 3  # TS_ERR_BAD_INPUT: k is not a multiple of 64
+    with pytest.raises(TesseraError):
+        ops.linear(x.cpu(), w.cpu())

@@ -1,0 +1,88 @@
+"""Row kernels against the CPU checker: RMS norm, gather, top-k (bit-exact), take + softmax."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import oracle as O
+from tests.util import dev_u32, from_bits, normal_bf16, rel_error, to_bits, u32, widen
+
+pytestmark = pytest.mark.gpu
+
+
+def test_rms_norm_f32_to_bf16():
+    from tessera_b200 import ops
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((37, 1024), dtype=np.float32) * 3
+    w = rng.standard_normal(1024, dtype=np.float32)
+    want = O.rms_norm(x, w, 1e-6)
+    got = ops.rms_norm(torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda(), 1e-6)
+    assert rel_error(widen(got), want) <= 1e-2
+    got32 = ops.rms_norm(torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda(), 1e-6, out_dtype=torch.float32)
+    assert rel_error(widen(got32), want) <= 1e-5
+    plain = ops.rms_norm(torch.from_numpy(x).cuda(), None, 1e-6, out_dtype=torch.float32)
+    assert rel_error(widen(plain), O.rms_norm(x, None, 1e-6)) <= 1e-5
+
+
+def test_rms_known_answer():
+    # engine/ir/interp/src/cpu_test.rs:131-149, through the device kernel
+    from tessera_b200 import ops
+    x = torch.tensor([[1., -3., 5., -1.], [2., 0., 0., -2.]], device="cuda")
+    w = torch.tensor([1., 2., -1., 0.5], device="cuda")
+    got = widen(ops.rms_norm(x, w, 7.0, out_dtype=torch.float32)).reshape(-1)
+    want = np.array([0.25, -1.5, -1.25, -0.125, 2. / 3., 0., 0., -1. / 3.], np.float32)
+    assert np.allclose(got, want, rtol=1e-5, atol=1e-6)
+
+
+def test_gather_rows():
+    from tessera_b200 import ops
+    rng = np.random.default_rng(1)
+    table = normal_bf16(rng, (50, 64))
+    ids = np.array([3, 0, 49, 50, 3, 7], np.uint32)  # 50 is past the table: zeros
+    got = ops.gather(from_bits(table), dev_u32(ids), out_dtype=torch.bfloat16)
+    assert np.array_equal(to_bits(got), O.gather(table, ids))
+    got32 = ops.gather(from_bits(table), dev_u32(ids), out_dtype=torch.float32)
+    assert np.array_equal(widen(got32), O.bf16_widen(O.gather(table, ids)))
+    shifted = ops.gather(from_bits(table), dev_u32(ids + 10), out_dtype=torch.bfloat16, first=10)
+    assert np.array_equal(to_bits(shifted), O.gather(table, ids + 10, first=10))
+
+
+def test_top_k_ties_known_answer():
+    # engine/ir/interp/src/run_test.rs:54-67, on the device
+    from tessera_b200 import ops
+    inf, nan = math.inf, math.nan
+    x = torch.tensor([2., 7., 7., -1., -inf, 3., nan, -inf, -0.0, 0.0, -0.0, inf], device="cuda").reshape(3, 4)
+    got = u32(ops.top_k(x, 3)).reshape(-1).tolist()
+    assert got == [1, 2, 0, 1, 4, 4, 3, 0, 1]
+
+
+@pytest.mark.parametrize("rows,width,k", [(256, 128, 8), (64, 128, 1), (5, 1000, 32), (3, 7, 4)])
+def test_top_k_is_bit_exact(rows, width, k):
+    from tessera_b200 import ops
+    x = O.Noise(rows + width).draw(rows, width)
+    x[0, 1] = x[0, width - 1]  # ties keep the lower index
+    x[rows - 1, :] = 0.25      # a whole row of ties
+    want = O.top_k(x, k)
+    got = u32(ops.top_k(torch.from_numpy(x).cuda(), k))
+    assert np.array_equal(got, want)
+
+
+def test_argmax_over_the_vocabulary():
+    from tessera_b200 import ops
+    rng = np.random.default_rng(9)
+    x = rng.standard_normal((6, 151936), dtype=np.float32)
+    x[2, 77] = x[2, 150000] = 9.0  # a tie across parts: the lower index wins
+    x[3, :] = -np.inf              # nothing ranks: the spare value is the width
+    want = O.top_k(x, 1)
+    got = u32(ops.top_k(torch.from_numpy(x).cuda(), 1))
+    assert np.array_equal(got, want)
+
+
+def test_take_softmax():
+    from tessera_b200 import ops
+    x = O.Noise(3).draw(40, 128) * 4
+    ids = O.top_k(x, 8)
+    want = O.softmax(O.take(x, ids))
+    got = ops.take_softmax(torch.from_numpy(x).cuda(), dev_u32(ids))
+    assert rel_error(widen(got), want) <= 1e-5
