@@ -1,0 +1,339 @@
+#!/usr/bin/env python
+"""Headline benchmark: Qwen3-0.6B-shaped bf16 decode throughput at batch 64 per GPU.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one decode launch over the whole batch (one new token per sequence).  Weights are
+random-init from a seed (N(0, 0.02), norms 1, tied embeddings), prompts are 128 uniform token ids
+per sequence, the kept K/V rows sit in 64-row pages behind a seeded random page table: synthetic
+stand-ins of the configuration's shapes, nothing is read from disk but MEASURED_PEAKS.json.
+
+  value  tokens/s with every input resident in HBM: the device-resident decode loop (each row's next
+         token is the id it just produced), K graph replays timed with CUDA events on the launch stream.
+  e2e    the same steps through ts_decoder_step with host buffers: tokens/slots/positions copied host to
+         device and the ids read back device to host inside the timed region, every step.
+  roofline  the kernel with the largest share of a step, timed live with CUDA events per kernel
+         (ts_decoder_profile) right after the timed region; algorithmic bytes / that duration.
+  cpu_baseline  the reference's native CPU rules restated in C (oracle/cpu_rules.c), timed on this
+         host's cores on a bounded sample of the same step.
+
+With N > 1 (torchrun, one rank per GPU) every rank decodes its own 64 sequences with replicated weights
+and no collective on the data path: weak scaling; the time is the maximum over ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+BATCH = 64
+PROMPT = 128
+FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used only when MEASURED_PEAKS.json is absent
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu captures
+# (profiles/*.md name the command); None until a capture of that kernel exists.
+NCU_TRAFFIC_BYTES = {}
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--pdl", type=int, default=1)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        return float(json.load(open(path))["hbm_gbs"]), "measured"
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 100 ms while running."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.gpu), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        self.lines += [l for l in out.splitlines() if l.strip()]
+        self.proc = None
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, f[5:9]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def kernel_bytes(name: str, cfg: dict, rows: int, ctx_sum: int) -> float:
+    """Algorithmic bytes one launch of a step-list kernel must move (bf16 = 2 bytes)."""
+    h, d = cfg["hidden"], cfg["head_dim"]
+    qw, kw, f, v = cfg["heads"] * d, cfg["kv_heads"] * d, cfg["ffn"], cfg["vocab"]
+    lin = lambda n, k, out_b: 2.0 * n * k + 2.0 * rows * k + out_b
+    if name == "attend_rows":  # every visible K and V row once, q in, out
+        return ctx_sum * kw * 2.0 * 2 + rows * qw * 2.0 * 2
+    if name == "linear_qkv":
+        return lin(qw + 2 * kw, h, 2.0 * rows * (qw + 2 * kw))
+    if name == "linear_o":
+        return lin(h, qw, 8.0 * rows * h)  # f32 residual in and out
+    if name == "linear_gate_up":
+        return lin(2 * f, h, 2.0 * rows * f)
+    if name == "linear_down":
+        return lin(h, f, 8.0 * rows * h)
+    if name == "linear_unembed":
+        return lin(v, h, 4.0 * rows * v)
+    return 0.0
+
+
+def cpu_weights(cfg, seed):
+    from tessera_b200 import synth
+    w = {k: [] for k in ("q", "k", "v", "o", "gate", "up", "down", "ln1", "ln2", "q_norm", "k_norm")}
+    named = []
+    for name, a in synth.decoder_weights(cfg, seed):
+        named.append((name, a))
+        if name in ("embed", "norm"):
+            w[name] = a
+        else:
+            w[name.split(".", 2)[2].replace("mlp.", "")].append(a)
+    return named, w
+
+
+def cpu_step_rate(cfg, weights, rows, position, budget_s, min_steps=1, max_steps=8):
+    """tokens/s of the CPU rules on `rows` sequences at `position` (earlier kept rows zero-filled)."""
+    import oracle as O
+    dec = O.CpuRulesDecoder(dict(cfg, context=position + max_steps + 1, slots=rows), weights)
+    toks = np.arange(rows, dtype=np.uint32) % cfg["vocab"]
+    slots = np.arange(rows, dtype=np.uint32)
+    times = []
+    t_all = time.perf_counter()
+    for i in range(max_steps):
+        t0 = time.perf_counter()
+        toks = dec.step(toks, slots, np.full(rows, position + i, np.uint32))
+        times.append(time.perf_counter() - t0)
+        if i + 1 >= min_steps and time.perf_counter() - t_all > budget_s:
+            break
+    best = min(times)
+    return rows / best, dec.threads, len(times), best
+
+
+def run_reference(args, rank):
+    """The reference's CPU path for this step (restated: the Rust workspace cannot be built here),
+    all host threads, each step a bounded sample of the batch."""
+    if rank != 0:
+        return
+    from tessera_b200 import synth
+    cfg = synth.QWEN3_0_6B
+    _, w = cpu_weights(cfg, 0)
+    # one full-batch step sizes the per-step sample so that warmup + steps fit in about two minutes
+    full_rate, threads, _, t_full = cpu_step_rate(cfg, w, BATCH, PROMPT, 0.0, 1, 1)
+    total = args.steps + args.warmup
+    rows = int(max(1, min(BATCH, BATCH * 120.0 / (total * t_full))))
+    import oracle as O
+    dec = O.CpuRulesDecoder(dict(cfg, context=PROMPT + total + 1, slots=rows), w)
+    toks = np.arange(rows, dtype=np.uint32)
+    slots = np.arange(rows, dtype=np.uint32)
+    for i in range(args.warmup):
+        toks = dec.step(toks, slots, np.full(rows, PROMPT + i, np.uint32))
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        toks = dec.step(toks, slots, np.full(rows, PROMPT + args.warmup + i, np.uint32))
+    dt = time.perf_counter() - t0
+    value = rows * args.steps / dt
+    sample = f"{rows} of {BATCH} sequences per step at positions {PROMPT}+, kept rows before the prompt end zero-filled"
+    print(json.dumps({
+        "impl": "reference", "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32 activations, bf16 weights", "data": "synthetic",
+        "config": {"workload": "Qwen3-0.6B-shaped decode, batch 64, prompt 128 (CPU rules restated in C; the "
+                               "reference's Rust/Cranelift path is unavailable on this box)", "batch": BATCH,
+                   "prompt": PROMPT},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+    from tessera_b200 import runner, synth
+
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    cfg = synth.QWEN3_0_6B
+    K, W = args.steps, args.warmup
+    profile_steps = 3
+    context = PROMPT + 2 * (K + W) + profile_steps + 8
+    context = (context + 63) // 64 * 64
+    dec = runner.Decoder(cfg, slots=BATCH, context=context, max_rows=2048, page=64, graphs=True, pdl=bool(args.pdl))
+    named, cpu_w = cpu_weights(cfg, 0)
+    dec.load_all(named)
+    dec.set_table(synth.page_permutation(BATCH * dec.pages, seed=4 + rank))
+    side = torch.cuda.Stream()  # the legacy NULL stream cannot be captured into graphs
+    torch.cuda.set_stream(side)
+    stream = side.cuda_stream
+    prompts = [synth.prompt_tokens(cfg["vocab"], PROMPT, seed=1000 * rank + s) for s in range(BATCH)]
+    slots = np.arange(BATCH, dtype=np.uint32)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    sampler = ClockSampler(local_rank)
+    first = dec.prefill(prompts)
+    pos = PROMPT
+    cur = dec.step(first, slots, np.full(BATCH, pos, np.uint32), stream=stream)  # one row per slot on the device
+    pos += 1
+
+    # ---- value: device-resident loop ----
+    dec.run_resident(W, stream)
+    pos += W
+    barrier()
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    dec.run_resident(K, stream)
+    e1.record()
+    torch.cuda.synchronize()
+    sampler.stop()
+    resident_s = max_over_ranks(e0.elapsed_time(e1) / 1e3)
+    ctx_mid = pos + K / 2.0  # mean visible positions per row over the timed steps
+    pos += K
+    barrier()
+    cur = dec.read_ids(BATCH, stream)
+
+    # ---- e2e: host buffers in and out every step ----
+    for i in range(W):
+        cur = dec.step(cur, slots, np.full(BATCH, pos, np.uint32), stream=stream)
+        pos += 1
+    barrier()
+    sampler.start()
+    t0 = time.perf_counter()
+    for i in range(K):
+        cur = dec.step(cur, slots, np.full(BATCH, pos, np.uint32), stream=stream)
+        pos += 1
+    torch.cuda.synchronize()
+    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    sampler.stop()
+    barrier()
+
+    launches_per_step = dec.launches_per_step(BATCH, min(context, (pos + 127) // 128 * 128))
+    # ---- per-kernel device time, live, for the roofline of the dominant kernel ----
+    prof = dec.profile(profile_steps, stream)
+    ctx_prof = pos + (profile_steps + 1) / 2.0
+    step_ms = sum(ms for ms, _ in prof.values()) / profile_steps
+    shares = {k: ms / profile_steps / step_ms for k, (ms, n) in prof.items()}
+    top = max(prof, key=lambda k: prof[k][0])
+    top_ms, top_n = prof[top]
+    per_launch_s = top_ms / top_n / 1e3
+    peak, peak_kind = peaks()
+    algo = kernel_bytes(top, cfg, BATCH, int(BATCH * ctx_prof))
+    achieved = algo / per_launch_s / 1e9
+    roofline = {"kernel": top, "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "traffic": NCU_TRAFFIC_BYTES.get(top),
+                "algorithmic_bytes_per_launch": algo, "avg_launch_us": per_launch_s * 1e6,
+                "step_share": shares[top], "kernel_shares": {k: round(v, 4) for k, v in sorted(shares.items())},
+                "per_kernel_gbs": {k: round(kernel_bytes(k, cfg, BATCH, int(BATCH * ctx_prof)) / (ms / n / 1e3) / 1e9, 1)
+                                   for k, (ms, n) in prof.items() if kernel_bytes(k, cfg, BATCH, 1) > 0}}
+    dec.close()
+    if world > 1:
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+
+    value = world * BATCH * K / resident_s
+    step_bytes = sum(kernel_bytes(k, cfg, BATCH, int(BATCH * ctx_mid)) * (1 if k == "linear_unembed" else cfg["layers"])
+                     for k in ("attend_rows", "linear_qkv", "linear_o", "linear_gate_up", "linear_down", "linear_unembed"))
+    out = {
+        "metric": "decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": resident_s / K * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "Qwen3-0.6B-shaped decode (28 layers, hidden 1024, 16q/8kv heads x 128, ffn 3072, "
+                               "vocab 151936, tied), batch 64 per GPU, prompt 128, greedy, paged KV (64-row pages, "
+                               "random page table)", "batch_per_gpu": BATCH, "prompt": PROMPT,
+                   "context_at_timed_steps": [int(ctx_mid - K / 2), int(ctx_mid + K / 2)],
+                   "l2": "each step streams 1.19 GB of weights plus the kept rows: inputs larger than the 126 MB L2",
+                   "parallelism": f"dp{world} (independent sequences, replicated weights, no collective)",
+                   "graphs": True, "pdl": bool(args.pdl)},
+        "e2e": {"value": world * BATCH * K / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": 3 * BATCH * 4,
+                "d2h_bytes_per_step": BATCH * 4, "ms_per_step": e2e_s / K * 1e3},
+        "gpu_launches": (launches_per_step + 1) * K,
+        "step_algorithmic_gb": step_bytes / 1e9, "step_hbm_frac": step_bytes / (resident_s / K) / 1e9 / peak,
+        "roofline": roofline, "clocks": sampler.summary(),
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        try:
+            rate, threads, n, best = cpu_step_rate(cfg, cpu_w, BATCH, PROMPT, 12.0, 2, 8)
+            out["cpu_baseline"] = {"value": rate, "unit": "tokens/s", "cores": threads, "kind": "port",
+                                   "sample": f"best of {n} full-batch decode steps (64 rows at positions {PROMPT}+, "
+                                             f"kept rows before them zero-filled), {best:.2f} s per step"}
+        except Exception as e:  # the baseline is a report, never a reason to lose the GPU numbers
+            out["cpu_baseline"] = {"value": None, "unit": "tokens/s", "cores": 0, "kind": "port", "sample": f"failed: {e}"}
+    print(json.dumps(out))
+
+
+def main():
+    args = parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -77,6 +77,14 @@ int ts_decoder_read_logits(ts_decoder *dec, float *out, uint32_t n_out, void *st
 uint32_t ts_decoder_launches_per_step(ts_decoder *dec, uint32_t rows, uint32_t keys);
 uint64_t ts_decoder_graph_replays(ts_decoder *dec);
 
+/* Per-kernel device time, the reference's Run::profiling / take_profile (engine/plan/run/src/run.rs:
+ * 165-177; stamps behind a gate kernel so host launch gaps are excluded, device.rs:144-200).
+ * ts_decoder_profile runs `steps` further device-resident decode launches without graphs, with a CUDA
+ * event after every kernel of the step list; ts_decoder_take_profile writes the totals as JSON text
+ * {"kernel name": [milliseconds, intervals], ...} into `out` and clears them. */
+int ts_decoder_profile(ts_decoder *dec, uint32_t steps, void *stream);
+int ts_decoder_take_profile(ts_decoder *dec, char *out, size_t capacity);
+
 #ifdef __cplusplus
 }
 #endif

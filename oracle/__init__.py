@@ -406,3 +406,57 @@ class Decoder:
         if rc:
             raise ValueError("a row sits outside the kept store")
         return ids, logits, hidden
+
+
+# ---- the timed CPU baseline (cpu_rules.c) ----------------------------------
+
+_RULES_PATH = os.path.join(_HERE, "libtessera_cpu_rules.so")
+_rules = None
+
+
+def build_rules(force: bool = False) -> str:
+    src = os.path.join(_HERE, "cpu_rules.c")
+    if force or not os.path.exists(_RULES_PATH) or os.path.getmtime(_RULES_PATH) < os.path.getmtime(src):
+        subprocess.check_call(["make", "-C", _HERE, "libtessera_cpu_rules.so"], stdout=subprocess.DEVNULL)
+    return _RULES_PATH
+
+
+def rules() -> C.CDLL:
+    global _rules
+    if _rules is None:
+        _rules = C.CDLL(build_rules())
+        _rules.cr_threads.restype = C.c_int
+    return _rules
+
+
+class CpuRulesDecoder:
+    """The reference's native CPU rules restated (threads + SIMD), for the timed baseline:
+    f32 activations, bf16 weights widened per block, dense f32 kept rows."""
+
+    def __init__(self, cfg: dict, weights: dict):
+        self.cfg = DecoderConfig(**cfg)
+        L = self.cfg.layers
+        self._keep = []
+        sw = _DecoderWeights()
+        sw.embed = weights["embed"].ctypes.data
+        sw.norm = weights["norm"].ctypes.data
+        for name in ("q", "k", "v", "o", "gate", "up", "down", "ln1", "ln2", "q_norm", "k_norm"):
+            arr = (C.c_void_p * L)(*[weights[name][l].ctypes.data for l in range(L)])
+            self._keep.append(arr)
+            setattr(sw, name, C.cast(arr, C.POINTER(C.c_void_p)))
+        self._sw = sw
+        self.w = weights
+        kw = self.cfg.kv_heads * self.cfg.head_dim
+        shape = (self.cfg.slots, self.cfg.context, kw)
+        self.keys = [np.zeros(shape, np.float32) for _ in range(L)]
+        self.values = [np.zeros(shape, np.float32) for _ in range(L)]
+        self._kp = (C.c_void_p * L)(*[a.ctypes.data for a in self.keys])
+        self._vp = (C.c_void_p * L)(*[a.ctypes.data for a in self.values])
+        self.threads = int(rules().cr_threads())
+
+    def step(self, tokens, slots, positions) -> np.ndarray:
+        tokens, slots, positions = _u(tokens), _u(slots), _u(positions)
+        ids = np.empty(tokens.size, np.uint32)
+        rules().cr_decoder_step(C.byref(self.cfg), C.byref(self._sw), self._kp, self._vp, _p(tokens), _p(slots),
+                                _p(positions), _z(tokens.size), _p(ids))
+        return ids

@@ -305,9 +305,24 @@ __global__ void advance_rows_kernel(const uint32_t *ids, uint32_t *tokens, uint3
     pdl_launch_dependents();
 }
 
+// Holds the stream until the host sets *flag, so that launches queued behind it run back to back
+// and per-kernel event intervals exclude host launch gaps.  One thread; gives up after `spins` reads
+// (engine/gpu/gpukit/src/gate.cu does the same with 2^21).
+__global__ void gate_kernel(const volatile uint32_t *flag, uint32_t spins) {
+    for (uint32_t i = 0; i < spins; i++)
+        if (*flag) return;
+}
+
 constexpr uint32_t kPeakParts = 64;
 
 }  // namespace
+
+int gate(const volatile uint32_t *flag, cudaStream_t stream) {
+    gate_kernel<<<1, 1, 0, stream>>>(flag, 1u << 21);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(TS_ERR_CUDA, "launch of gate failed: %s", cudaGetErrorString(e));
+    return TS_OK;
+}
 
 int advance_rows(const uint32_t *ids, uint32_t *tokens, uint32_t *positions, uint32_t rows, cudaStream_t stream) {
     if (rows == 0) return TS_OK;

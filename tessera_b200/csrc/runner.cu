@@ -48,6 +48,14 @@ struct ts_decoder {
     uint32_t last_rows = 0, last_out = 0, last_keys = 0;
     std::vector<uint32_t> host_positions;  // of the last launch, to follow the resident loop
     std::vector<void *> owned;
+    // per-kernel device time (tessera_run::Run::profiling / take_profile, run.rs:165-177)
+    bool profiling = false;
+    std::vector<cudaEvent_t> events;
+    size_t events_used = 0;
+    std::vector<const char *> event_names;
+    std::map<std::string, std::pair<double, uint64_t>> profile;  // name -> (ms, intervals)
+    cudaStream_t own_stream = nullptr;  // used when the caller passes the NULL stream, which cannot capture
+    volatile uint32_t *gate_flag = nullptr;  // pinned; the gate kernel holds the stream until it is set
 };
 
 namespace {
@@ -95,10 +103,22 @@ int enqueue(ts_decoder *d, uint32_t rows, uint32_t keys, uint32_t n_out, bool fe
     if ((rc = kept_to_dev(&kept, &kd)) != TS_OK) return rc;
     const bool contiguous = kept.kind == TS_KEPT_DENSE || kept.page >= 32;
     const float scale = 1.0f / sqrtf((float)D);
-#define STEP(expr)                        \
-    do {                                  \
+    auto mark = [&](const char *name) -> int {
+        if (!d->profiling) return TS_OK;
+        if (d->events_used == d->events.size()) {
+            cudaEvent_t e;
+            TS_CUDA(cudaEventCreate(&e));
+            d->events.push_back(e);
+        }
+        TS_CUDA(cudaEventRecord(d->events[d->events_used++], s));
+        d->event_names.push_back(name);
+        return TS_OK;
+    };
+#define STEP(name, expr)                       \
+    do {                                       \
         if ((rc = (expr)) != TS_OK) return rc; \
-        launches++;                       \
+        if ((rc = mark(name)) != TS_OK) return rc; \
+        launches++;                            \
     } while (0)
     auto linear = [&](const void *xin, const void *w, const void *a0, void *out, uint32_t n, uint32_t k, int epi,
                       int out_dtype) -> int {
@@ -107,35 +127,36 @@ int enqueue(ts_decoder *d, uint32_t rows, uint32_t keys, uint32_t n_out, bool fe
                                          d->workspace_bytes, s);
         return linear_umma(xin, w, a0, out, rows, n, k, epi, 1.0f, out_dtype, d->workspace, d->workspace_bytes, s);
     };
-    if (feedback) STEP(advance_rows(d->ids, d->tokens, d->positions, rows, s));
-    STEP(gather_rows(d->embed, d->tokens, d->x, TS_F32, rows, c.vocab, H, 0, s));
+    if ((rc = mark("")) != TS_OK) return rc;  // interval origin
+    if (feedback) STEP("advance_rows", advance_rows(d->ids, d->tokens, d->positions, rows, s));
+    STEP("gather", gather_rows(d->embed, d->tokens, d->x, TS_F32, rows, c.vocab, H, 0, s));
     for (uint32_t l = 0; l < c.layers; l++) {
         ts_decoder::Layer &L = d->layers[l];
-        STEP(rms_norm(d->x, TS_F32, L.ln1, d->h, TS_BF16, rows, H, c.eps, nullptr, s));
-        STEP(linear(d->h, L.wqkv, nullptr, d->qkv, d->qkv_n, H, TS_EPI_NONE, TS_BF16));
-        STEP(qk_norm_rope_append(d->qkv, c.qk_norm ? L.q_norm : nullptr, c.qk_norm ? L.k_norm : nullptr, d->inv_freq,
+        STEP("rms_norm", rms_norm(d->x, TS_F32, L.ln1, d->h, TS_BF16, rows, H, c.eps, nullptr, s));
+        STEP("linear_qkv", linear(d->h, L.wqkv, nullptr, d->qkv, d->qkv_n, H, TS_EPI_NONE, TS_BF16));
+        STEP("qk_norm_rope_append", qk_norm_rope_append(d->qkv, c.qk_norm ? L.q_norm : nullptr, c.qk_norm ? L.k_norm : nullptr, d->inv_freq,
                                  d->slots, d->positions, d->q, L.k_rows, L.v_rows, kd, rows, c.heads, c.kv_heads, D,
                                  c.eps, s));
-        STEP(attend_rows(d->q, L.k_rows, L.v_rows, d->attn, d->slots, d->positions, kd, contiguous, rows, keys, c.heads,
+        STEP("attend_rows", attend_rows(d->q, L.k_rows, L.v_rows, d->attn, d->slots, d->positions, kd, contiguous, rows, keys, c.heads,
                          c.kv_heads, D, 0xFFFFFFFFu, scale, d->workspace, d->workspace_bytes, s));
         if (attend_rows_workspace_bytes(rows, keys, c.heads, c.kv_heads, D) > 0) launches++;
-        STEP(linear(d->attn, L.wo, d->x, d->x, H, QW, TS_EPI_ADD, TS_F32));
-        STEP(rms_norm(d->x, TS_F32, L.ln2, d->h, TS_BF16, rows, H, c.eps, nullptr, s));
-        STEP(linear(d->h, L.wgu, nullptr, d->act, 2 * c.ffn, H, TS_EPI_SWIGLU, TS_BF16));
-        STEP(linear(d->act, L.wdown, d->x, d->x, H, c.ffn, TS_EPI_ADD, TS_F32));
+        STEP("linear_o", linear(d->attn, L.wo, d->x, d->x, H, QW, TS_EPI_ADD, TS_F32));
+        STEP("rms_norm", rms_norm(d->x, TS_F32, L.ln2, d->h, TS_BF16, rows, H, c.eps, nullptr, s));
+        STEP("linear_gate_up", linear(d->h, L.wgu, nullptr, d->act, 2 * c.ffn, H, TS_EPI_SWIGLU, TS_BF16));
+        STEP("linear_down", linear(d->act, L.wdown, d->x, d->x, H, c.ffn, TS_EPI_ADD, TS_F32));
     }
     // Only the wanted rows go through the final norm and the unembedding.
-    STEP(rms_norm(d->x, TS_F32, d->norm, d->h_out, TS_BF16, n_out, H, c.eps, n_out == rows ? nullptr : d->out_rows, s));
+    STEP("rms_norm", rms_norm(d->x, TS_F32, d->norm, d->h_out, TS_BF16, n_out, H, c.eps, n_out == rows ? nullptr : d->out_rows, s));
     {
         const bool skinny = n_out <= 16 && skinny_supports(n_out, c.vocab, H, TS_EPI_NONE);
         if (skinny)
-            STEP(linear_skinny(d->h_out, d->embed, nullptr, d->logits, n_out, c.vocab, H, TS_EPI_NONE, 1.0f, TS_F32,
+            STEP("linear_unembed", linear_skinny(d->h_out, d->embed, nullptr, d->logits, n_out, c.vocab, H, TS_EPI_NONE, 1.0f, TS_F32,
                                d->workspace, d->workspace_bytes, s));
         else
-            STEP(linear_umma(d->h_out, d->embed, nullptr, d->logits, n_out, c.vocab, H, TS_EPI_NONE, 1.0f, TS_F32,
+            STEP("linear_unembed", linear_umma(d->h_out, d->embed, nullptr, d->logits, n_out, c.vocab, H, TS_EPI_NONE, 1.0f, TS_F32,
                              d->workspace, d->workspace_bytes, s));
     }
-    STEP(top_k(d->logits, TS_F32, d->ids, n_out, c.vocab, 1, d->workspace, d->workspace_bytes, s));
+    STEP("top_1", top_k(d->logits, TS_F32, d->ids, n_out, c.vocab, 1, d->workspace, d->workspace_bytes, s));
     launches++;  // top-1 over the vocabulary is two launches
 #undef STEP
     if (count) *count = launches;
@@ -168,6 +189,12 @@ int submit(ts_decoder *d, uint32_t rows, uint32_t keys, uint32_t n_out, bool fee
     TS_CUDA(cudaGraphLaunch(it->second, s));
     d->replays++;
     return TS_OK;
+}
+
+// The legacy NULL stream cannot be captured into a graph: fall back to the runner's own stream
+// (a blocking stream, so it still orders against work on the NULL stream).
+cudaStream_t stream_of(ts_decoder *d, void *stream) {
+    return stream ? (cudaStream_t)stream : d->own_stream;
 }
 
 uint32_t keys_bucket(const ts_decoder *d, uint32_t furthest) {
@@ -268,6 +295,10 @@ int ts_decoder_create(const ts_decoder_config *config, ts_decoder **out) {
         if (e != cudaSuccess) rc = fail(TS_ERR_CUDA, "cudaMallocHost failed: %s", cudaGetErrorString(e));
     }
     if (rc == TS_OK) {
+        cudaError_t e = cudaStreamCreate(&d->own_stream);
+        if (e != cudaSuccess) rc = fail(TS_ERR_CUDA, "cudaStreamCreate failed: %s", cudaGetErrorString(e));
+    }
+    if (rc == TS_OK) {
         std::vector<float> f(c.head_dim / 2);
         for (uint32_t j = 0; j < c.head_dim / 2; j++) f[j] = powf(c.theta, -((float)(2 * j)) / (float)c.head_dim);
         cudaError_t e = cudaMemcpy(d->inv_freq, f.data(), f.size() * 4, cudaMemcpyHostToDevice);
@@ -289,6 +320,9 @@ void ts_decoder_destroy(ts_decoder *d) {
     for (auto &g : d->graphs) cudaGraphExecDestroy(g.second);
     for (void *p : d->owned) cudaFree(p);
     if (d->stage) cudaFreeHost(d->stage);
+    if (d->gate_flag) cudaFreeHost((void *)d->gate_flag);
+    if (d->own_stream) cudaStreamDestroy(d->own_stream);
+    for (cudaEvent_t e : d->events) cudaEventDestroy(e);
     delete d;
 }
 
@@ -354,7 +388,7 @@ int ts_decoder_step(ts_decoder *d, const uint32_t *tokens, const uint32_t *slots
     }
     for (uint32_t i = 0; out_rows && i < n_out; i++)
         TS_REQUIRE(out_rows[i] < rows, "decoder step: output row %u is past the %u rows", out_rows[i], rows);
-    cudaStream_t s = (cudaStream_t)stream;
+    cudaStream_t s = stream_of(d, stream);
     const size_t R = c.max_rows;
     uint32_t *st = d->stage;
     memcpy(st, tokens, rows * 4);
@@ -388,7 +422,7 @@ int ts_decoder_run_resident(ts_decoder *d, uint32_t steps, void *stream) {
     TS_REQUIRE(d, "decoder: NULL");
     TS_REQUIRE(d->last_rows > 0 && d->last_out == d->last_rows,
                "decoder resident loop: the last launch must have produced one id per row");
-    cudaStream_t s = (cudaStream_t)stream;
+    cudaStream_t s = stream_of(d, stream);
     for (uint32_t i = 0; i < steps; i++) {
         const uint32_t furthest = d->last_keys + 1;
         TS_REQUIRE(furthest <= d->c.context, "decoder resident loop: position %u is past the context of %u",
@@ -403,7 +437,7 @@ int ts_decoder_run_resident(ts_decoder *d, uint32_t steps, void *stream) {
 
 int ts_decoder_read_ids(ts_decoder *d, uint32_t *out_ids, uint32_t rows, void *stream) {
     TS_REQUIRE(d && out_ids && rows <= d->c.max_rows, "decoder read: bad argument");
-    cudaStream_t s = (cudaStream_t)stream;
+    cudaStream_t s = stream_of(d, stream);
     TS_CUDA(cudaMemcpyAsync(d->stage + 4 * (size_t)d->c.max_rows, d->ids, rows * 4, cudaMemcpyDeviceToHost, s));
     TS_CUDA(cudaStreamSynchronize(s));
     memcpy(out_ids, d->stage + 4 * (size_t)d->c.max_rows, rows * 4);
@@ -412,7 +446,7 @@ int ts_decoder_read_ids(ts_decoder *d, uint32_t *out_ids, uint32_t rows, void *s
 
 int ts_decoder_read_hidden(ts_decoder *d, void *out_bf16, uint32_t rows, void *stream) {
     TS_REQUIRE(d && out_bf16 && rows <= d->c.max_rows, "decoder read: bad argument");
-    cudaStream_t s = (cudaStream_t)stream;
+    cudaStream_t s = stream_of(d, stream);
     TS_CUDA(cudaMemcpyAsync(out_bf16, d->h_out, (size_t)rows * d->c.hidden * 2, cudaMemcpyDeviceToHost, s));
     TS_CUDA(cudaStreamSynchronize(s));
     return TS_OK;
@@ -420,7 +454,7 @@ int ts_decoder_read_hidden(ts_decoder *d, void *out_bf16, uint32_t rows, void *s
 
 int ts_decoder_read_logits(ts_decoder *d, float *out, uint32_t n_out, void *stream) {
     TS_REQUIRE(d && out && n_out <= d->max_out, "decoder read: bad argument");
-    cudaStream_t s = (cudaStream_t)stream;
+    cudaStream_t s = stream_of(d, stream);
     TS_CUDA(cudaMemcpyAsync(out, d->logits, (size_t)n_out * d->c.vocab * 4, cudaMemcpyDeviceToHost, s));
     TS_CUDA(cudaStreamSynchronize(s));
     return TS_OK;
@@ -443,6 +477,56 @@ uint32_t ts_decoder_launches_per_step(ts_decoder *d, uint32_t rows, uint32_t key
 }
 
 uint64_t ts_decoder_graph_replays(ts_decoder *d) { return d ? d->replays : 0; }
+
+int ts_decoder_profile(ts_decoder *d, uint32_t steps, void *stream) {
+    TS_REQUIRE(d, "decoder: NULL");
+    TS_REQUIRE(d->last_rows > 0 && d->last_out == d->last_rows,
+               "decoder profile: the last launch must have produced one id per row");
+    cudaStream_t s = stream_of(d, stream);
+    if (!d->gate_flag) TS_CUDA(cudaHostAlloc((void **)&d->gate_flag, 64, cudaHostAllocMapped));
+    set_pdl(false);
+    for (uint32_t i = 0; i < steps; i++) {
+        const uint32_t furthest = d->last_keys + 1;
+        TS_REQUIRE(furthest <= d->c.context, "decoder profile: position %u is past the context of %u", furthest - 1,
+                   d->c.context);
+        d->events_used = 0;
+        d->event_names.clear();
+        *d->gate_flag = 0;
+        int rc = gate(d->gate_flag, s);
+        if (rc != TS_OK) return rc;
+        d->profiling = true;
+        rc = enqueue(d, d->last_rows, keys_bucket(d, furthest), d->last_rows, true, s, nullptr);
+        d->profiling = false;
+        *d->gate_flag = 1;  // every launch of the step is queued: let them run back to back
+        if (rc != TS_OK) return rc;
+        TS_CUDA(cudaStreamSynchronize(s));
+        for (size_t e = 1; e < d->events_used; e++) {
+            float ms = 0.0f;
+            TS_CUDA(cudaEventElapsedTime(&ms, d->events[e - 1], d->events[e]));
+            auto &slot = d->profile[d->event_names[e]];
+            slot.first += ms;
+            slot.second += 1;
+        }
+        d->last_keys = furthest;
+    }
+    return TS_OK;
+}
+
+int ts_decoder_take_profile(ts_decoder *d, char *out, size_t capacity) {
+    TS_REQUIRE(d && out && capacity > 2, "decoder profile: bad argument");
+    std::string text = "{";
+    for (auto &kv : d->profile) {
+        char line[160];
+        snprintf(line, sizeof(line), "%s\"%s\": [%.6f, %llu]", text.size() > 1 ? ", " : "", kv.first.c_str(),
+                 kv.second.first, (unsigned long long)kv.second.second);
+        text += line;
+    }
+    text += "}";
+    TS_REQUIRE(text.size() + 1 <= capacity, "decoder profile: %zu bytes do not fit in %zu", text.size() + 1, capacity);
+    memcpy(out, text.c_str(), text.size() + 1);
+    d->profile.clear();
+    return TS_OK;
+}
 
 }  // extern "C"
 #pragma GCC visibility pop

@@ -23,6 +23,7 @@ int attend_rows(const void *q, const void *k, const void *v, void *out, const ui
                 size_t workspace_bytes, cudaStream_t stream);
 int rms_norm(const void *x, int x_dtype, const float *w, void *out, int out_dtype, uint32_t rows, uint32_t width,
              float eps, const uint32_t *row_ids, cudaStream_t stream);
+int gate(const volatile uint32_t *flag, cudaStream_t stream);
 int advance_rows(const uint32_t *ids, uint32_t *tokens, uint32_t *positions, uint32_t rows, cudaStream_t stream);
 int gather_rows(const void *table, const uint32_t *ids, void *out, int out_dtype, uint32_t rows,
                 uint32_t table_rows, uint32_t width, uint32_t first, cudaStream_t stream);

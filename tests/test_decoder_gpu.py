@@ -1,0 +1,125 @@
+"""The decode runner end to end against the CPU checker's decoder, same seeded weights.
+
+Greedy ids are integer outputs and must match exactly; the final hidden rows are bf16 with
+f32 sums and must sit within 1e-2 of the checker relative to their largest magnitude.
+"""
+import json
+import os
+
+import numpy as np
+import pytest
+
+import oracle as O
+from tessera_b200 import synth
+from tests.golden.make_qwen3_tokens import oracle_weights
+from tests.util import rel_error
+
+pytestmark = pytest.mark.gpu
+
+SMALL = dict(layers=2, hidden=256, heads=4, kv_heads=2, head_dim=64, ffn=512, vocab=1000, eps=1e-6, theta=1e4)
+MID = dict(layers=2, hidden=1024, heads=16, kv_heads=8, head_dim=128, ffn=3072, vocab=20000, eps=1e-6, theta=1e6)
+
+
+def _oracle_generate(cfg, seed, prompts, new, context, gains):
+    dec = O.Decoder(dict(cfg, context=context, slots=len(prompts)), oracle_weights(cfg, seed, gains))
+    toks = [t for p in prompts for t in p]
+    slts = [s for s, p in enumerate(prompts) for _ in p]
+    poss = [i for p in prompts for i in range(len(p))]
+    ids, _, hidden = dec.step(toks, slts, poss, want_hidden=True)
+    ends = np.cumsum([len(p) for p in prompts]) - 1
+    out = np.zeros((len(prompts), new), np.uint32)
+    out[:, 0] = ids[ends]
+    pos = np.array([len(p) for p in prompts], np.uint32)
+    last_hidden = hidden[ends]
+    for t in range(1, new):
+        ids, _, last_hidden = dec.step(out[:, t - 1], np.arange(len(prompts)), pos, want_hidden=True)
+        out[:, t] = ids
+        pos += 1
+    return out, last_hidden
+
+
+def _device(cfg, seed, slots, context, max_rows, gains, **kw):
+    from tessera_b200 import runner
+    dec = runner.Decoder(cfg, slots, context, max_rows, **kw)
+    dec.load_all(synth.decoder_weights(cfg, seed, gains=gains))
+    return dec
+
+
+@pytest.mark.parametrize("cfg,page", [(SMALL, 16), (SMALL, 0), (MID, 64)])
+def test_greedy_tokens_match_oracle(cfg, page):
+    rng = np.random.default_rng(3)
+    prompts = [rng.integers(0, cfg["vocab"], size=n).tolist() for n in (5, 17, 1)]
+    want, want_hidden = _oracle_generate(cfg, 7, prompts, 12, 64, "near_one")
+    dec = _device(cfg, 7, slots=3, context=64, max_rows=16, gains="near_one", page=page)
+    got = dec.generate(prompts, 12)
+    assert np.array_equal(got, want)
+    hidden = O.bf16_widen(dec.read_hidden(3))
+    assert rel_error(hidden, want_hidden) <= 1e-2
+    dec.close()
+
+
+def test_page_table_is_a_pure_permutation():
+    # Any page-to-slot map gives the same tokens (kept.rs:155-194 is address arithmetic only).
+    cfg = SMALL
+    rng = np.random.default_rng(5)
+    prompts = [rng.integers(0, cfg["vocab"], size=n).tolist() for n in (33, 20)]
+    runs = []
+    for table in (None, "reversed", "random"):
+        dec = _device(cfg, 1, slots=2, context=64, max_rows=32, gains="ones", page=16)
+        entries = 2 * dec.pages
+        if table == "reversed":
+            dec.set_table(np.arange(entries)[::-1])
+        elif table == "random":
+            dec.set_table(synth.page_permutation(entries, seed=9))
+        runs.append(dec.generate(prompts, 10))
+        dec.close()
+    assert np.array_equal(runs[0], runs[1]) and np.array_equal(runs[0], runs[2])
+
+
+@pytest.mark.parametrize("graphs,pdl", [(True, False), (False, False), (True, True)])
+def test_resident_loop_equals_host_loop(graphs, pdl):
+    cfg = SMALL
+    rng = np.random.default_rng(8)
+    prompts = [rng.integers(0, cfg["vocab"], size=9).tolist() for _ in range(4)]
+    dec = _device(cfg, 2, slots=4, context=64, max_rows=64, gains="ones", page=16, graphs=graphs, pdl=pdl)
+    want = dec.generate(prompts, 8)
+    dec.close()
+    dec = _device(cfg, 2, slots=4, context=64, max_rows=64, gains="ones", page=16, graphs=graphs, pdl=pdl)
+    first = dec.prefill(prompts)
+    ids = dec.step(first, np.arange(4), np.full(4, 9))  # leaves one row per slot on the device
+    assert np.array_equal(first, want[:, 0]) and np.array_equal(ids, want[:, 1])
+    dec.run_resident(6)
+    assert np.array_equal(dec.read_ids(4), want[:, 7])
+    if graphs:
+        assert dec.graph_replays() >= 7
+    dec.close()
+
+
+def test_bad_rows_are_refused_before_any_launch():
+    from tessera_b200 import TesseraError
+    dec = _device(SMALL, 0, slots=2, context=32, max_rows=8, gains="ones", page=16)
+    for toks, slts, poss in (([1], [2], [0]), ([1], [0], [32]), ([1000], [0], [0]), ([1] * 9, [0] * 9, list(range(9)))):
+        with pytest.raises(TesseraError) as e:
+            dec.step(toks, slts, poss)
+        assert e.value.code == 3
+    with pytest.raises(TesseraError):
+        dec.set_table([0, 1, 2, 99])
+    # the runner is still usable afterwards
+    assert dec.step([1], [0], [0]).shape == (1,)
+    dec.close()
+
+
+def test_qwen3_0p6b_greedy_tokens_match_golden():
+    """Batch 1, 128-token prompt, 64 greedy steps at full size; the first 32 generated ids must equal
+    the CPU checker's (tests/golden/qwen3_0p6b_greedy.json, written by make_qwen3_tokens.py)."""
+    path = os.path.join(os.path.dirname(__file__), "golden", "qwen3_0p6b_greedy.json")
+    gold = json.load(open(path))
+    cfg = gold["config"]
+    prompt = synth.prompt_tokens(cfg["vocab"], gold["prompt_len"], seed=gold["prompt_seed"])
+    assert prompt[:8].tolist() == gold["prompt_head"]
+    dec = _device(cfg, gold["seed"], slots=1, context=192, max_rows=128, gains="ones", page=64)
+    got = dec.generate([prompt.tolist()], gold["new"])[0].tolist()
+    dec.close()
+    assert got[:32] == gold["tokens"][:32]
+    same = sum(1 for a, b in zip(got, gold["tokens"]) if a == b)
+    print(f"{same} of {len(got)} greedy ids equal the checker's")
