@@ -52,6 +52,12 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--pdl", type=int, default=1)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--case", default=None,
+                    help="time one kernel of the step list alone at the benchmark's shapes (attend_rows, linear_qkv, "
+                         "linear_o, linear_gate_up, linear_down, linear_unembed); used for ncu captures")
+    ap.add_argument("--ctx", type=int, default=192, help="--case attend_rows: context length of every row")
+    ap.add_argument("--rows", type=int, default=BATCH, help="--case: rows (batch) of the launch")
+    ap.add_argument("--path", default="auto", choices=["auto", "skinny", "umma", "stream"], help="--case linear_*: kernel family")
     return ap.parse_args()
 
 
@@ -324,8 +330,76 @@ def run_ours(args, rank, world, local_rank):
     print(json.dumps(out))
 
 
+def run_case(args):
+    """One kernel alone, at the step's shapes, through the C ABI: `steps` launches replayed from a CUDA
+    graph over buffers rotated through more than the L2's 126 MB, timed with CUDA events."""
+    import torch
+    from tessera_b200 import ops, synth
+    cfg = synth.QWEN3_0_6B
+    rows = args.rows
+    h, d = cfg["hidden"], cfg["head_dim"]
+    qw, kw, f, v = cfg["heads"] * d, cfg["kv_heads"] * d, cfg["ffn"], cfg["vocab"]
+    torch.manual_seed(0)
+    side = torch.cuda.Stream()
+    torch.cuda.set_stream(side)
+    bf = lambda *shape, std=1.0: (torch.randn(*shape, device="cuda") * std).to(torch.bfloat16)
+    calls = []
+    if args.case == "attend_rows":
+        ctx, page = args.ctx, 64
+        pages = -(-ctx // page)
+        copies = max(2, int(400e6 // (rows * pages * page * kw * 4)) + 1)
+        slots = torch.arange(rows, dtype=torch.int32, device="cuda")
+        positions = torch.full((rows,), ctx - 1, dtype=torch.int32, device="cuda")
+        q = bf(rows, cfg["heads"], d)
+        for c in range(copies):
+            table = torch.from_numpy(synth.page_permutation(rows * pages, seed=c).view(np.int32)).cuda()
+            kept = ops.Kept("paged", pages, table, rows * pages * page)
+            k, vv = bf(rows * pages * page, cfg["kv_heads"], d), bf(rows * pages * page, cfg["kv_heads"], d)
+            out = torch.empty_like(q)
+            calls.append(lambda k=k, vv=vv, kept=kept, out=out: ops.attend_rows(
+                q, k, vv, slots, positions, kept, ctx, scale=d ** -0.5, out=out))
+        algo = kernel_bytes("attend_rows", cfg, rows, rows * ctx)
+    else:
+        shapes = {"linear_qkv": (qw + 2 * kw, h, "none", torch.bfloat16), "linear_o": (h, qw, "add", torch.float32),
+                  "linear_gate_up": (2 * f, h, "swiglu", torch.bfloat16), "linear_down": (h, f, "add", torch.float32),
+                  "linear_unembed": (v, h, "none", torch.float32)}
+        n, k, epi, odt = shapes[args.case]
+        copies = min(64, max(2, int(400e6 // (n * k * 2)) + 1))
+        x = bf(rows, k)
+        res = torch.randn(rows, n, device="cuda") if epi == "add" else None
+        for c in range(copies):
+            w = bf(n, k, std=0.02)
+            out = torch.empty((rows, n // 2 if epi == "swiglu" else n), dtype=odt, device="cuda")
+            calls.append(lambda w=w, out=out: ops.linear(x, w, res, epilogue=epi, out_dtype=odt, out=out, path=args.path))
+        algo = kernel_bytes(args.case, cfg, rows, 0)
+    ops.set_pdl(bool(args.pdl))
+    for i in range(max(3, args.warmup)):
+        calls[i % len(calls)]()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        for i in range(args.steps):
+            calls[i % len(calls)]()
+    graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / args.steps
+    peak, kind = peaks()
+    print(json.dumps({"case": args.case, "rows": rows, "ctx": args.ctx if args.case == "attend_rows" else None,
+                      "us_per_launch": us, "algorithmic_bytes": algo, "GBs": algo / us / 1e3,
+                      "frac": algo / us / 1e3 / peak, "peak_kind": kind, "launches": args.steps, "copies": len(calls),
+                      "status": ops.device_status()}))
+
+
 def main():
     args = parse_args()
+    if args.case:
+        run_case(args)
+        return
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

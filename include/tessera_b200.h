@@ -73,7 +73,9 @@ typedef enum {
 typedef enum {
     TS_LINEAR_AUTO = 0,
     TS_LINEAR_SKINNY = 1, /* decode-sized m: vector loads + warp MMA, split-K */
-    TS_LINEAR_UMMA = 2    /* tcgen05 / TMEM accumulators fed by TMA */
+    TS_LINEAR_UMMA = 2,   /* tiled tcgen05 / TMEM accumulators fed by TMA (prefill-sized m) */
+    TS_LINEAR_STREAM = 3  /* m <= 128: weight-streaming tcgen05, k split over a thread-block cluster and
+                             reduced through distributed shared memory, epilogue fused */
 } ts_linear_path;
 
 /* Bytes of workspace ts_linear_bf16 needs for these sizes (0 when none). */

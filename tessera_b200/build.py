@@ -26,7 +26,7 @@ NVCC_FLAGS = [
     "--expt-relaxed-constexpr",
     "-I", os.path.join(ROOT, "include"),
     "-I", CSRC,
-]
+] + os.environ.get("TS_NVCC_EXTRA", "").split()
 
 
 def _nvcc() -> str:

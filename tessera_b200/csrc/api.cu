@@ -105,10 +105,12 @@ int make_tensor_map_3d(CUtensorMap *map, const void *base, uint64_t outer, uint6
     return TS_OK;
 }
 
-static int pick_linear_path(uint32_t m, uint32_t n, uint32_t k, int epilogue, int path) {
-    if (path == TS_LINEAR_SKINNY || path == TS_LINEAR_UMMA) return path;
-    // Small m: the warp-MMA streamer; otherwise the tcgen05 kernel.
+int pick_linear_path(uint32_t m, uint32_t n, uint32_t k, int epilogue, int path) {
+    if (path == TS_LINEAR_SKINNY || path == TS_LINEAR_UMMA || path == TS_LINEAR_STREAM) return path;
+    // m <= 16: the warp-MMA streamer; m <= 128: the weight-streaming tcgen05 kernel with its cluster
+    // reduce; larger m: the tiled tcgen05 kernel.
     if (m <= 16 && skinny_supports(m, n, k, epilogue)) return TS_LINEAR_SKINNY;
+    if (m <= 128 && stream_supports(m, n, k, epilogue)) return TS_LINEAR_STREAM;
     if (umma_supports(m, n, k, epilogue)) return TS_LINEAR_UMMA;
     if (skinny_supports(m, n, k, epilogue)) return TS_LINEAR_SKINNY;
     return -1;
@@ -129,13 +131,17 @@ int ts_set_pdl(int enabled) {
     return TS_OK;
 }
 
-int ts_device_status(void) { return umma_take_status(); }
+int ts_device_status(void) {
+    const int a = umma_take_status(), b = stream_take_status();
+    return a ? a : b;
+}
 
 size_t ts_linear_workspace_bytes(uint32_t m, uint32_t n, uint32_t k, int epilogue, int path) {
     const bool gated = epilogue == TS_EPI_SWIGLU || epilogue == TS_EPI_GEGLU;
     size_t a = 0, b = 0;
-    if (path != TS_LINEAR_UMMA && skinny_supports(m, n, k, epilogue)) a = skinny_workspace_bytes(m, n, k, gated);
-    if (path != TS_LINEAR_SKINNY && umma_supports(m, n, k, epilogue)) b = umma_workspace_bytes(m, n, k, epilogue);
+    const bool any = path == TS_LINEAR_AUTO;
+    if ((any || path == TS_LINEAR_SKINNY) && skinny_supports(m, n, k, epilogue)) a = skinny_workspace_bytes(m, n, k, gated);
+    if ((any || path == TS_LINEAR_UMMA) && umma_supports(m, n, k, epilogue)) b = umma_workspace_bytes(m, n, k, epilogue);
     return a > b ? a : b;
 }
 
@@ -157,6 +163,10 @@ int ts_linear_bf16(const void *x, const void *w, const void *a0, void *out, uint
         TS_REQUIRE(skinny_supports(m, n, k, epilogue), "linear (skinny): needs m <= 64 and k %% 256 == 0 (m=%u k=%u)", m,
                    k);
         return linear_skinny(x, w, a0, out, m, n, k, epilogue, scale, out_dtype, workspace, workspace_bytes, s);
+    }
+    if (chosen == TS_LINEAR_STREAM) {
+        TS_REQUIRE(stream_supports(m, n, k, epilogue), "linear (stream): needs m <= 128 (m=%u n=%u k=%u)", m, n, k);
+        return linear_stream(x, w, a0, out, m, n, k, epilogue, scale, out_dtype, s);
     }
     return linear_umma(x, w, a0, out, m, n, k, epilogue, scale, out_dtype, workspace, workspace_bytes, s);
 }

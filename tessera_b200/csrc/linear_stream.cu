@@ -1,0 +1,522 @@
+// Decode-sized linear on tcgen05: out[m, n] = sum_k x[m, k] * w[n, k] for m <= 128, with the
+// epilogue stage fused and no second kernel.
+//
+// Weight rows sit on the 128 TMEM lanes (the MMA's M), batch rows on its columns (N = BN >= m).  A
+// block loads its k slice of x once by TMA and keeps it in shared memory; 128-row weight tiles then
+// stream HBM -> shared memory (TMA, 128-byte swizzle) -> tensor core exactly once.
+//
+// Small matrices do not have enough 128-row tiles to fill 148 SMs, so k is split over the S blocks of
+// a thread-block cluster.  Each block ends with a 128 x BN f32 partial in TMEM; the cluster reduces
+// it through distributed shared memory: block r owns batch columns [r BN/S, (r+1) BN/S), every block
+// writes its partial of those columns into block r's receive buffer (st.shared::cluster) and arrives
+// on block r's mbarrier; block r then adds the S partials in rank order (a fixed order: a re-run
+// gives the same bits), applies the epilogue (residual add, SwiGLU/GeGLU, scale) and stores.  No
+// partial sums touch global memory and nothing is launched afterwards.
+//
+// Gated epilogues pair gate row j with up row j + n/2: a gated tile is 64 gate rows and their 64 up
+// rows, so both meet in the owner's receive buffer.
+//
+// Warp roles: 0 = TMA producer, 1 = MMA issuer (owns TMEM), 2..9 = epilogue (lane quarter = warp % 4,
+// column half = (warp - 2) / 4).  With S == 1 blocks are persistent over tiles and two TMEM
+// accumulator stages overlap a tile's epilogue with the next tile's MMAs.
+//
+// Stands in for the reference's `lanes` / `thin` / `tiled*` rules at decode sizes
+// (engine/rules/linear/src/lanes.rs:20-65, tiled.rs:295-446) with their fused epilogue chain
+// (engine/plan/lower/src/sites/matmul.rs:148-176).
+#include "ts_common.cuh"
+#include "ts_ptx.cuh"
+
+namespace ts {
+namespace {
+
+using namespace ptx;
+
+constexpr uint32_t kRows = 128;    // weight rows per tile = TMEM lanes
+constexpr uint32_t kBlockK = 64;   // bf16 per k block = one 128-byte swizzle row
+constexpr uint32_t kEpiWarps = 8;
+constexpr uint32_t kThreads = (2 + kEpiWarps) * 32;
+constexpr uint32_t kAccStages = 2;
+constexpr uint32_t kABytes = kRows * kBlockK * 2;
+
+struct StreamParams {
+    uint32_t m, n, k;        // out is [m, n] (or [m, n/2] when gated)
+    uint32_t kb_total;       // k / 64
+    uint32_t splits;         // S = cluster size along grid y
+    uint32_t tiles;          // weight-row tiles
+    uint32_t stages;
+    uint32_t kb_max;         // most k blocks any split holds (sizes the resident x slice)
+    uint32_t gated;
+    uint32_t use_recv;       // reduce / pair through the receive buffer (S > 1 or gated)
+    uint32_t chunk_shift;    // log2(BN / S): batch columns each block owns after the reduce
+    int epilogue, out_dtype;
+    float scale;
+    const float *a0;
+    void *out;
+    int *status;
+};
+
+struct StreamSmem {
+    uint32_t a_off, b_off, recv_off, bar_off, total;
+};
+
+__host__ __device__ inline StreamSmem stream_smem(uint32_t bn, uint32_t stages, uint32_t kb_max, bool recv) {
+    StreamSmem l;
+    l.a_off = 0;
+    l.b_off = stages * kABytes;
+    l.recv_off = l.b_off + kb_max * bn * kBlockK * 2;
+    l.bar_off = l.recv_off + (recv ? kRows * (bn + 32) * 4 : 0);  // rows padded by 4 floats per sender
+    l.total = l.bar_off + 256 + 1024;  // barriers, then slack for the 1024-byte alignment of the base
+    return l;
+}
+
+__device__ __forceinline__ bool wait_bounded(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_flag,
+                                             bool cluster_scope = false) {
+    uint64_t start = 0;
+    for (uint32_t i = 0; i < kSpinLimit; i++) {
+        if (cluster_scope ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
+        if ((i & 255u) == 255u) {
+            if (*abort_flag) return false;
+            uint64_t now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            if (start == 0) start = now;
+            else if (now - start > 2000000000ull) break;  // two seconds
+        }
+    }
+    *abort_flag = 1;
+    return false;
+}
+
+// CW consecutive f32 columns of this warp's TMEM lanes.
+template <uint32_t CW>
+__device__ __forceinline__ void load_columns(uint32_t taddr, float (&v)[CW]) {
+    if constexpr (CW == 8) {
+        uint32_t r[8];
+        tmem_ld_32x8(taddr, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = __uint_as_float(r[i]);
+    } else if constexpr (CW == 16) {
+        uint32_t r[16];
+        tmem_ld_32x16(taddr, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
+    } else {
+#pragma unroll
+        for (uint32_t c0 = 0; c0 < CW; c0 += 32) {
+            uint32_t r[32];
+            tmem_ld_32x32(taddr + c0, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; i++) v[c0 + i] = __uint_as_float(r[i]);
+        }
+    }
+}
+
+__device__ __forceinline__ void store_out(void *out, int out_dtype, size_t at, float v) {
+    if (out_dtype == TS_F32) reinterpret_cast<float *>(out)[at] = v;
+    else reinterpret_cast<uint16_t *>(out)[at] = bf16_bits(v);
+}
+
+template <uint32_t BN>
+__global__ void __launch_bounds__(kThreads, 1)
+linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                     const StreamParams p) {
+    constexpr uint32_t CW = BN / 2;  // columns per epilogue warp
+    constexpr uint32_t kBBytes = BN * kBlockK * 2;
+    constexpr uint32_t kTmemCols = kAccStages * BN < 32 ? 32 : kAccStages * BN;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char *smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const StreamSmem L = stream_smem(BN, p.stages, p.kb_max, p.use_recv != 0);
+    unsigned char *smem_a = smem + L.a_off;
+    unsigned char *smem_b = smem + L.b_off;
+    float *recv = reinterpret_cast<float *>(smem + L.recv_off);  // [S][128][BN / S]
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + L.bar_off);  // [8]
+    uint64_t *empty = full + 8;                                       // [8]
+    uint64_t *acc_full = empty + 8;                                   // [2]
+    uint64_t *acc_empty = acc_full + 2;                               // [2]
+    uint64_t *b_full = acc_empty + 2;
+    uint64_t *recv_full = b_full + 1;
+    uint64_t *recv_free = recv_full + 1;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(recv_free + 1);
+    volatile uint32_t *abort_flag = tmem_slot + 1;
+
+    const uint32_t S = p.splits;
+    const uint32_t rank = blockIdx.y;  // == cluster rank: the cluster spans grid y
+    const uint32_t kb_begin = (uint32_t)(((uint64_t)rank * p.kb_total) / S);
+    const uint32_t kb_end = (uint32_t)(((uint64_t)(rank + 1) * p.kb_total) / S);
+    const uint32_t kbs = kb_end - kb_begin;
+    const uint32_t chunk = BN / S;  // batch columns this block owns after the reduce
+
+    const uint32_t half_n = p.n / 2;
+    const uint32_t my_tiles = blockIdx.x < p.tiles ? (p.tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const uint32_t total_its = my_tiles * kbs;
+    // Stage `it` of this block's stream of weight tiles: tile and k block.
+    auto load_weights = [&](uint32_t it) {
+        const uint32_t tile = blockIdx.x + (it / kbs) * gridDim.x, kb = it % kbs, s = it % p.stages;
+        const int32_t kx = (int32_t)((kb_begin + kb) * kBlockK);
+        mbar_expect_tx(&full[s], kABytes);
+        unsigned char *dst = smem_a + s * kABytes;
+        if (p.gated) {  // 64 gate rows, then their 64 up rows
+            tma_load_2d(dst, &map_w, &full[s], kx, (int32_t)(tile * 64));
+            tma_load_2d(dst + kABytes / 2, &map_w, &full[s], kx, (int32_t)(half_n + tile * 64));
+        } else {
+            tma_load_2d(dst, &map_w, &full[s], kx, (int32_t)(tile * kRows));
+        }
+    };
+    const uint32_t early = min(p.stages, total_its);
+
+    if (threadIdx.x == 0) STAMP(0);
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < p.stages; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (uint32_t s = 0; s < kAccStages; s++) {
+            mbar_init(&acc_full[s], 1);
+            mbar_init(&acc_empty[s], kEpiWarps);
+        }
+        mbar_init(b_full, 1);
+        // S > 1: one local arrival announces the bytes and the senders' asynchronous stores complete
+        // them; S == 1: plain stores, one arrival per warp.
+        mbar_init(recv_full, S > 1 ? 1 : kEpiWarps);
+        mbar_init(recv_free, kEpiWarps);
+        *abort_flag = 0;
+        fence_barrier_init();
+        // Weights never depend on the upstream kernel, and this thread is the only one that
+        // touches the stage barriers before the block-wide sync: the first stages go out now, while
+        // the other warps are still setting up.
+        for (uint32_t it = 0; it < early; it++) load_weights(it);
+        STAMP(1);
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    if (S > 1) cluster_sync();  // every block's barriers exist before anyone arrives on them remotely
+    const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) STAMP(2);
+
+    if (warp == 0) {
+        if (lane == 0) {
+            bool ok = true;
+            // x is what the upstream kernel wrote: wait for it, then fetch this block's k slice once.
+            pdl_wait();
+            mbar_expect_tx(b_full, kbs * kBBytes);
+            for (uint32_t j = 0; j < kbs; j++)
+                tma_load_2d(smem_b + j * kBBytes, &map_x, b_full, (int32_t)((kb_begin + j) * kBlockK), 0);
+            uint32_t it = early;
+            for (; it < total_its; it++) {
+                ok = wait_bounded(&empty[it % p.stages], ((it / p.stages) & 1) ^ 1, abort_flag);
+                if (!ok) break;
+                load_weights(it);
+            }
+            STAMP(3);
+            pdl_launch_dependents();
+            if (ok) {  // every copy this thread issued has landed once its stage was released
+                for (uint32_t back = 0; back < p.stages && back < total_its; back++) {
+                    const uint32_t j = total_its - 1 - back;
+                    if (!wait_bounded(&empty[j % p.stages], (j / p.stages) & 1, abort_flag)) break;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc_bf16(kRows, BN);
+            uint32_t it = 0;
+            bool ok = wait_bounded(b_full, 0, abort_flag);
+            STAMP(4);
+            for (uint32_t acc_it = 0; acc_it < my_tiles && ok; acc_it++) {
+                const uint32_t as = acc_it % kAccStages, aph = (acc_it / kAccStages) & 1;
+                ok = wait_bounded(&acc_empty[as], aph ^ 1, abort_flag);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + as * BN;
+                for (uint32_t kb = 0; kb < kbs; kb++, it++) {
+                    const uint32_t s = it % p.stages, ph = (it / p.stages) & 1;
+                    ok = wait_bounded(&full[s], ph, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    const uint64_t da = umma_desc_k_sw128(smem_addr(smem_a + s * kABytes));
+                    const uint64_t db = umma_desc_k_sw128(smem_addr(smem_b + kb * kBBytes));
+#pragma unroll
+                    for (uint32_t k16 = 0; k16 < kBlockK / 16; k16++)
+                        umma_bf16(d_tmem, da + 2 * k16, db + 2 * k16, idesc, (kb | k16) != 0);
+                    umma_commit(&empty[s]);
+                }
+                if (ok) umma_commit(&acc_full[as]);
+                STAMP(5);
+            }
+        }
+    } else {
+        // ---- epilogue ----
+        const uint32_t q = warp & 3, hcol = (warp - 2) >> 2;
+        const uint32_t row = q * 32 + lane;           // tile row (TMEM lane) this thread owns
+        const uint32_t col0 = hcol * CW;              // first batch column this thread owns
+        const uint32_t out_n = p.gated ? half_n : p.n;
+        const uint32_t shift = p.chunk_shift;         // chunk = 1 << shift batch columns per owner
+        const uint32_t rs = chunk + 4;                // receive-buffer row stride in floats (bank spread)
+        const uint32_t recv_base = smem_addr(recv);
+        const uint32_t bar_local = smem_addr(recv_full);
+        bool ok = true;
+        for (uint32_t acc_it = 0; acc_it < my_tiles && ok; acc_it++) {
+            const uint32_t tile = blockIdx.x + acc_it * gridDim.x;
+            const uint32_t as = acc_it % kAccStages, aph = (acc_it / kAccStages) & 1;
+            ok = wait_bounded(&acc_full[as], aph, abort_flag);
+            if (!ok) break;
+            tc_fence_after_sync();
+            if (warp == 2 && lane == 0) STAMP(6);
+            float v[CW];
+            load_columns<CW>(tmem_base + ((q * 32u) << 16) + as * BN + col0, v);
+            // The accumulator stage is free as soon as it sits in registers.
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[as]);
+
+            if (!p.use_recv) {
+                // One block holds the whole sum: store straight from registers.  Consecutive lanes
+                // are consecutive output columns n; column c of the tile is batch row col0 + c.
+                const uint32_t n_idx = tile * kRows + row;
+                if (n_idx < p.n) {
+                    size_t at = (size_t)col0 * p.n + n_idx;
+#pragma unroll
+                    for (uint32_t c = 0; c < CW; c++, at += p.n) {
+                        if (col0 + c < p.m) {
+                            float r = v[c];
+                            if (p.epilogue == TS_EPI_ADD) r += p.a0[at];
+                            if (p.epilogue == TS_EPI_SCALE) r *= p.scale;
+                            store_out(p.out, p.out_dtype, at, r);
+                        }
+                    }
+                }
+                continue;
+            }
+
+            // The receive buffer of the previous tile must have been read by all of this block.
+            if (acc_it > 0) {
+                ok = wait_bounded(recv_free, (acc_it - 1) & 1, abort_flag);
+                if (!ok) break;
+            }
+            if (S > 1) {
+                // This block will receive S x 128 rows x chunk columns of f32 for the tile.
+                if (warp == 2 && lane == 0) mbar_expect_tx(recv_full, S * kRows * chunk * 4);
+                // Send: columns [col0, col0 + CW) go to the blocks that own them as asynchronous
+                // 16-byte stores that credit the owner's barrier; the sender does not wait for them.
+#pragma unroll
+                for (uint32_t c = 0; c < CW; c += 4) {
+                    const uint32_t col = col0 + c;
+                    const uint32_t dest = col >> shift, within = col & (chunk - 1);
+                    const uint32_t local = recv_base + ((rank * kRows + row) * rs + within) * 4;
+                    st_async_f32x4(map_to_rank(local, dest), map_to_rank(bar_local, dest), v[c], v[c + 1], v[c + 2],
+                                   v[c + 3]);
+                }
+            } else {
+                // One block: the buffer only pairs gate rows with up rows.  Plain stores, then one
+                // arrival per warp.
+#pragma unroll
+                for (uint32_t c = 0; c < CW; c += 4)
+                    *reinterpret_cast<float4 *>(recv + row * rs + col0 + c) = make_float4(v[c], v[c + 1], v[c + 2], v[c + 3]);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(recv_full);
+            }
+            if (warp == 2 && lane == 0) STAMP(7);
+            ok = wait_bounded(recv_full, acc_it & 1, abort_flag);
+            if (!ok) break;
+            if (warp == 2 && lane == 0) STAMP(8);
+
+            // Reduce the S partials of this block's columns in rank order, finish, store.  Thread
+            // (row, hcol) takes chunk / 2 consecutive columns of its row.
+            const bool active = !p.gated || row < 64;
+            const uint32_t n_idx = p.gated ? tile * 64 + row : tile * kRows + row;
+            if (active && n_idx < out_n) {
+                const uint32_t per = chunk >> 1;
+                for (uint32_t cc = hcol * per; cc < (hcol + 1) * per; cc += 4) {
+                    const float *src = recv + row * rs + cc;
+                    float4 sum = *reinterpret_cast<const float4 *>(src);
+                    float4 up = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    if (p.gated) up = *reinterpret_cast<const float4 *>(src + 64 * rs);
+                    for (uint32_t s = 1; s < S; s++) {
+                        const float4 t = *reinterpret_cast<const float4 *>(src + (size_t)s * kRows * rs);
+                        sum.x += t.x; sum.y += t.y; sum.z += t.z; sum.w += t.w;
+                        if (p.gated) {
+                            const float4 u = *reinterpret_cast<const float4 *>(src + ((size_t)s * kRows + 64) * rs);
+                            up.x += u.x; up.y += u.y; up.z += u.z; up.w += u.w;
+                        }
+                    }
+                    const float r4[4] = {sum.x, sum.y, sum.z, sum.w};
+                    const float u4[4] = {up.x, up.y, up.z, up.w};
+                    const uint32_t m0 = rank * chunk + cc;
+                    size_t at = (size_t)m0 * out_n + n_idx;
+#pragma unroll
+                    for (uint32_t j = 0; j < 4; j++, at += out_n) {
+                        if (m0 + j < p.m) {
+                            float r = r4[j];
+                            if (p.gated) r = (p.epilogue == TS_EPI_SWIGLU ? silu(r) : gelu_tanh(r)) * u4[j];
+                            if (p.epilogue == TS_EPI_ADD) r += p.a0[at];
+                            if (p.epilogue == TS_EPI_SCALE) r *= p.scale;
+                            store_out(p.out, p.out_dtype, at, r);
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(recv_free);
+            if (warp == 2 && lane == 0) STAMP(9);
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (threadIdx.x == 0) STAMP(10);
+    if (S > 1) cluster_sync();  // no block leaves while a peer may still write to it
+    if (threadIdx.x == 0 && *abort_flag) atomicExch(p.status, TS_ERR_TIMEOUT);
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+struct StreamPlan {
+    uint32_t bn, splits, tiles, stages, kb_total, kb_max, blocks;
+    bool gated, use_recv;
+    StreamSmem layout;
+};
+
+constexpr uint32_t kSmemBudget = 225 * 1024;
+
+bool plan_stream(uint32_t m, uint32_t n, uint32_t k, int epilogue, StreamPlan *out) {
+    StreamPlan s = {};
+    s.gated = epilogue == TS_EPI_SWIGLU || epilogue == TS_EPI_GEGLU;
+    if (m == 0 || m > 128 || n == 0 || k == 0 || k % kBlockK != 0) return false;
+    if (s.gated && (n % 2 != 0 || (n / 2) % 64 != 0)) return false;
+    s.bn = m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128;
+    s.kb_total = k / kBlockK;
+    s.tiles = s.gated ? (n / 2) / 64 : ceil_div(n, kRows);
+    const uint32_t sms = (uint32_t)sm_count();
+    auto layout = [&](uint32_t splits, uint32_t stages) {
+        const uint32_t kb_max = ceil_div(s.kb_total, splits);
+        return stream_smem(s.bn, stages, kb_max, splits > 1 || s.gated);
+    };
+    // The largest power-of-two split that still fits one wave; more if the resident x slice needs it.
+    uint32_t splits = 1;
+    const uint32_t max_splits = std::min<uint32_t>(std::min<uint32_t>(8, s.bn / 8), s.kb_total);
+    while (splits * 2 <= max_splits && s.tiles * splits * 2 <= sms) splits *= 2;
+    while (layout(splits, 2).total > kSmemBudget && splits * 2 <= max_splits) splits *= 2;
+    if (layout(splits, 2).total > kSmemBudget) return false;
+    s.splits = splits;
+    s.kb_max = ceil_div(s.kb_total, splits);
+    s.use_recv = splits > 1 || s.gated;
+    uint32_t stages = 8;
+    while (stages > 2 && layout(splits, stages).total > kSmemBudget) stages--;
+    s.stages = stages;
+    s.layout = layout(splits, stages);
+    s.blocks = splits > 1 ? s.tiles : std::min(s.tiles, sms);
+    *out = s;
+    return true;
+}
+
+__device__ int g_stream_status = 0;
+
+template <uint32_t BN>
+cudaError_t launch_stream(const CUtensorMap &mw, const CUtensorMap &mx, const StreamParams &p, const StreamPlan &s,
+                          cudaStream_t stream) {
+    auto kernel = linear_stream_kernel<BN>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(s.blocks, s.splits);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = s.layout.total;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    unsigned n_attr = 0;
+    if (s.splits > 1) {
+        attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+        attr[n_attr].val.clusterDim.x = 1;
+        attr[n_attr].val.clusterDim.y = s.splits;
+        attr[n_attr].val.clusterDim.z = 1;
+        n_attr++;
+    }
+    if (pdl_enabled()) {
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        n_attr++;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n_attr;
+    return cudaLaunchKernelEx(&cfg, kernel, mw, mx, p);
+}
+
+}  // namespace
+
+#ifdef TS_DEBUG_STAMPS
+extern "C" __attribute__((visibility("default"))) int ts_debug_stamps(unsigned long long *out) {
+    return cudaMemcpyFromSymbol(out, g_stamps, sizeof(unsigned long long) * 16 * 32) == cudaSuccess ? 0 : 6;
+}
+#endif
+
+bool stream_supports(uint32_t m, uint32_t n, uint32_t k, int epilogue) {
+    StreamPlan s;
+    return plan_stream(m, n, k, epilogue, &s);
+}
+
+int stream_take_status() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_stream_status, sizeof(int)) != cudaSuccess) return TS_ERR_CUDA;
+    if (v != 0) cudaMemcpyToSymbol(g_stream_status, &zero, sizeof(int));
+    return v;
+}
+
+int linear_stream(const void *x, const void *w, const void *a0, void *out, uint32_t m, uint32_t n, uint32_t k,
+                  int epilogue, float scale, int out_dtype, cudaStream_t stream) {
+    StreamPlan s;
+    if (!plan_stream(m, n, k, epilogue, &s))
+        return fail(TS_ERR_BAD_INPUT, "linear (stream): unsupported shape m=%u n=%u k=%u epilogue=%d", m, n, k, epilogue);
+    CUtensorMap map_w, map_x;
+    int rc = make_tensor_map_2d(&map_w, w, n, k, k, s.gated ? 64 : kRows, kBlockK);
+    if (rc != TS_OK) return rc;
+    rc = make_tensor_map_2d(&map_x, x, m, k, k, s.bn, kBlockK);
+    if (rc != TS_OK) return rc;
+    StreamParams p = {};
+    p.m = m;
+    p.n = n;
+    p.k = k;
+    p.kb_total = s.kb_total;
+    p.splits = s.splits;
+    p.tiles = s.tiles;
+    p.stages = s.stages;
+    p.kb_max = s.kb_max;
+    p.gated = s.gated;
+    p.use_recv = s.use_recv;
+    {
+        uint32_t chunk = s.bn / s.splits, sh = 0;
+        while ((1u << sh) < chunk) sh++;
+        p.chunk_shift = sh;
+    }
+    p.epilogue = epilogue;
+    p.out_dtype = out_dtype;
+    p.scale = scale;
+    p.a0 = (const float *)a0;
+    p.out = out;
+    int *status = nullptr;
+    TS_CUDA(cudaGetSymbolAddress((void **)&status, g_stream_status));
+    p.status = status;
+    cudaError_t e;
+    switch (s.bn) {
+    case 16: e = launch_stream<16>(map_w, map_x, p, s, stream); break;
+    case 32: e = launch_stream<32>(map_w, map_x, p, s, stream); break;
+    case 64: e = launch_stream<64>(map_w, map_x, p, s, stream); break;
+    default: e = launch_stream<128>(map_w, map_x, p, s, stream); break;
+    }
+    if (e != cudaSuccess)
+        return fail(TS_ERR_CUDA, "launch of linear_stream failed: %s (%d) %s", cudaGetErrorName(e), (int)e,
+                    cudaGetErrorString(e));
+    return TS_OK;
+}
+
+}  // namespace ts

@@ -110,6 +110,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     constexpr uint32_t kABytes = kBlockA * kBlockK * 2;
     constexpr uint32_t kBBytes = BN * kBlockK * 2;
 
+    if (threadIdx.x == 0) STAMP(0);
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < p.stages; s++) {
             mbar_init(&full[s], 1);
@@ -132,6 +133,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) STAMP(1);
 
     // Row of w where the up half of a gated tile starts.
     const uint32_t gate_rows_b = p.n / 2;
@@ -142,6 +144,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             // Weights never depend on the upstream kernel; x does.  In the swapped layout A is the
             // weight, so only B has to wait.
             if (!p.swapped) pdl_wait();
+            STAMP(2);
             uint32_t it = 0;
             bool ok = true;
             if (p.b_resident) {
@@ -173,6 +176,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     }
                 }
             }
+            STAMP(3);
             pdl_launch_dependents();
             // Copies still in flight must land before the block's shared memory goes away: wait for
             // the consumer to release every stage this thread filled (bounded).
@@ -192,6 +196,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             uint32_t it = 0, acc_it = 0;
             bool ok = true;
             if (p.b_resident) ok = wait_or_abort(b_full, 0, abort_flag);
+            STAMP(4);
             for (uint32_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, acc_it++) {
                 const uint32_t as = acc_it % kAccStages, aph = (acc_it / kAccStages) & 1;
                 ok = wait_or_abort(&acc_empty[as], aph ^ 1, abort_flag);
@@ -214,6 +219,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     umma_commit(&empty[s]);
                 }
                 if (ok) umma_commit(&acc_full[as]);
+                STAMP(5);
             }
         }
     } else {
@@ -229,6 +235,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             ok = wait_or_abort(&acc_full[as], aph, abort_flag);
             if (!ok) break;
             tc_fence_after_sync();
+            if (warp == 2 && lane == 0) STAMP(6);
             const uint32_t row = q * 32 + lane;  // row of the 128 x BN tile this thread owns
             const uint32_t gi = ti * kBlockA + row;
             const uint32_t taddr = tmem_base + ((q * 32u) << 16) + as * BN;
@@ -370,6 +377,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     }
                 }
             }
+            if (warp == 2 && lane == 0) STAMP(7);
             // Release the accumulator stage: one arrival per epilogue warp.
             tc_fence_before_sync();
             __syncwarp();
@@ -379,6 +387,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 
     tc_fence_before_sync();
     __syncthreads();
+    if (threadIdx.x == 0) STAMP(8);
     if (threadIdx.x == 0 && *abort_flag) atomicExch(p.status, TS_ERR_TIMEOUT);
     if (warp == 1) {
         tc_fence_after_sync();

@@ -91,6 +91,25 @@ ts_kept kept_of(const ts_decoder *d) {
 
 size_t max_size(size_t a, size_t b) { return a > b ? a : b; }
 
+// One linear through the kernel family the sizes pick.
+int linear_any(ts_decoder *d, const void *x, const void *w, const void *a0, void *out, uint32_t m, uint32_t n,
+               uint32_t k, int epi, int out_dtype, cudaStream_t s) {
+    const int path = pick_linear_path(m, n, k, epi, TS_LINEAR_AUTO);
+    if (path == TS_LINEAR_SKINNY)
+        return linear_skinny(x, w, a0, out, m, n, k, epi, 1.0f, out_dtype, d->workspace, d->workspace_bytes, s);
+    if (path == TS_LINEAR_STREAM) return linear_stream(x, w, a0, out, m, n, k, epi, 1.0f, out_dtype, s);
+    if (path == TS_LINEAR_UMMA)
+        return linear_umma(x, w, a0, out, m, n, k, epi, 1.0f, out_dtype, d->workspace, d->workspace_bytes, s);
+    return fail(TS_ERR_BAD_INPUT, "decoder: no linear kernel takes m=%u n=%u k=%u", m, n, k);
+}
+
+size_t linear_workspace(uint32_t m, uint32_t n, uint32_t k, int epi) {
+    const int path = pick_linear_path(m, n, k, epi, TS_LINEAR_AUTO);
+    if (path == TS_LINEAR_SKINNY) return skinny_workspace_bytes(m, n, k, epi == TS_EPI_SWIGLU || epi == TS_EPI_GEGLU);
+    if (path == TS_LINEAR_UMMA) return umma_workspace_bytes(m, n, k, epi);
+    return 0;
+}
+
 // The step list for `rows` rows that see at most `keys` positions; logits for n_out rows.
 int enqueue(ts_decoder *d, uint32_t rows, uint32_t keys, uint32_t n_out, bool feedback, cudaStream_t s,
             uint32_t *count) {
@@ -122,10 +141,7 @@ int enqueue(ts_decoder *d, uint32_t rows, uint32_t keys, uint32_t n_out, bool fe
     } while (0)
     auto linear = [&](const void *xin, const void *w, const void *a0, void *out, uint32_t n, uint32_t k, int epi,
                       int out_dtype) -> int {
-        const bool skinny = rows <= 16 && skinny_supports(rows, n, k, epi);
-        if (skinny) return linear_skinny(xin, w, a0, out, rows, n, k, epi, 1.0f, out_dtype, d->workspace,
-                                         d->workspace_bytes, s);
-        return linear_umma(xin, w, a0, out, rows, n, k, epi, 1.0f, out_dtype, d->workspace, d->workspace_bytes, s);
+        return linear_any(d, xin, w, a0, out, rows, n, k, epi, out_dtype, s);
     };
     if ((rc = mark("")) != TS_OK) return rc;  // interval origin
     if (feedback) STEP("advance_rows", advance_rows(d->ids, d->tokens, d->positions, rows, s));
@@ -147,15 +163,7 @@ int enqueue(ts_decoder *d, uint32_t rows, uint32_t keys, uint32_t n_out, bool fe
     }
     // Only the wanted rows go through the final norm and the unembedding.
     STEP("rms_norm", rms_norm(d->x, TS_F32, d->norm, d->h_out, TS_BF16, n_out, H, c.eps, n_out == rows ? nullptr : d->out_rows, s));
-    {
-        const bool skinny = n_out <= 16 && skinny_supports(n_out, c.vocab, H, TS_EPI_NONE);
-        if (skinny)
-            STEP("linear_unembed", linear_skinny(d->h_out, d->embed, nullptr, d->logits, n_out, c.vocab, H, TS_EPI_NONE, 1.0f, TS_F32,
-                               d->workspace, d->workspace_bytes, s));
-        else
-            STEP("linear_unembed", linear_umma(d->h_out, d->embed, nullptr, d->logits, n_out, c.vocab, H, TS_EPI_NONE, 1.0f, TS_F32,
-                             d->workspace, d->workspace_bytes, s));
-    }
+    STEP("linear_unembed", linear_any(d, d->h_out, d->embed, nullptr, d->logits, n_out, c.vocab, H, TS_EPI_NONE, TS_F32, s));
     STEP("top_1", top_k(d->logits, TS_F32, d->ids, n_out, c.vocab, 1, d->workspace, d->workspace_bytes, s));
     launches++;  // top-1 over the vocabulary is two launches
 #undef STEP
@@ -270,11 +278,7 @@ int ts_decoder_create(const ts_decoder_config *config, ts_decoder **out) {
         if (rows > c.max_rows) continue;
         const bool g = true;
         (void)g;
-        auto need = [&](uint32_t n, uint32_t k, int epi) {
-            size_t a = skinny_supports(rows, n, k, epi) ? skinny_workspace_bytes(rows, n, k, epi == TS_EPI_SWIGLU) : 0;
-            size_t b = umma_supports(rows, n, k, epi) ? umma_workspace_bytes(rows, n, k, epi) : 0;
-            return max_size(a, b);
-        };
+        auto need = [&](uint32_t n, uint32_t k, int epi) { return linear_workspace(rows, n, k, epi); };
         ws = max_size(ws, need(d->qkv_n, c.hidden, TS_EPI_NONE));
         ws = max_size(ws, need(c.hidden, c.heads * c.head_dim, TS_EPI_ADD));
         ws = max_size(ws, need(2 * c.ffn, c.hidden, TS_EPI_SWIGLU));
@@ -465,9 +469,7 @@ uint32_t ts_decoder_launches_per_step(ts_decoder *d, uint32_t rows, uint32_t key
     // Count by walking the same decisions enqueue makes, without launching.
     const ts_decoder_config &c = d->c;
     auto lin = [&](uint32_t m, uint32_t n, uint32_t k, int epi) -> uint32_t {
-        const bool skinny = m <= 16 && skinny_supports(m, n, k, epi);
-        size_t ws = skinny ? skinny_workspace_bytes(m, n, k, epi == TS_EPI_SWIGLU) : umma_workspace_bytes(m, n, k, epi);
-        return ws > 0 ? 2 : 1;
+        return linear_workspace(m, n, k, epi) > 0 ? 2 : 1;
     };
     uint32_t per_layer = 2 /*norms*/ + 1 /*append*/ + 1 /*attention*/ +
                          (attend_rows_workspace_bytes(rows, keys, c.heads, c.kv_heads, c.head_dim) > 0 ? 1 : 0) +

@@ -122,3 +122,19 @@ cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
 bool pdl_enabled();
 
 }  // namespace ts
+
+// Debug builds only (-DTS_DEBUG_STAMPS): per-block %globaltimer stamps, the reference's TS_MARK idea
+// (engine/plan/run/src/marks.cuh).  Compiled out of the shipped library.
+#ifdef TS_DEBUG_STAMPS
+static __device__ unsigned long long g_stamps[16 * 32];  // one copy per translation unit
+#define STAMP(slot)                                                         \
+    do {                                                                    \
+        if (blockIdx.x < 4 && blockIdx.y < 4) {                             \
+            unsigned long long t__;                                         \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__));         \
+            g_stamps[(blockIdx.x * 4 + blockIdx.y) * 32 + (slot)] = t__;    \
+        }                                                                   \
+    } while (0)
+#else
+#define STAMP(slot) do { } while (0)
+#endif

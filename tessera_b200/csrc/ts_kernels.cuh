@@ -16,6 +16,12 @@ int umma_take_status();
 int linear_umma(const void *x, const void *w, const void *a0, void *out, uint32_t m, uint32_t n, uint32_t k,
                 int epilogue, float scale, int out_dtype, void *workspace, size_t workspace_bytes,
                 cudaStream_t stream);
+bool stream_supports(uint32_t m, uint32_t n, uint32_t k, int epilogue);
+int stream_take_status();
+int linear_stream(const void *x, const void *w, const void *a0, void *out, uint32_t m, uint32_t n, uint32_t k,
+                  int epilogue, float scale, int out_dtype, cudaStream_t stream);
+// Picks the kernel family for a linear: TS_LINEAR_SKINNY, TS_LINEAR_STREAM, TS_LINEAR_UMMA, or -1.
+int pick_linear_path(uint32_t m, uint32_t n, uint32_t k, int epilogue, int path);
 size_t attend_rows_workspace_bytes(uint32_t rows, uint32_t keys, uint32_t heads, uint32_t kv_heads, uint32_t width);
 int attend_rows(const void *q, const void *k, const void *v, void *out, const uint32_t *slots,
                 const uint32_t *positions, const KeptDev &kept, bool contiguous, uint32_t rows, uint32_t keys,

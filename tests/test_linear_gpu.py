@@ -39,6 +39,20 @@ UMMA = [(1, 2048, 1024), (16, 1024, 2048), (64, 1024, 3072), (64, 6144, 1024), (
         (128, 1024, 1024), (200, 512, 1024), (384, 1024, 512), (1024, 640, 256), (129, 200, 64)]
 
 
+STREAM = [(1, 2048, 1024), (16, 1024, 2048), (64, 1024, 3072), (64, 6144, 1024), (100, 2048, 1024),
+          (128, 1024, 1024), (64, 4096, 1024), (33, 1000, 512), (64, 72, 256), (17, 128, 64), (64, 20000, 1024)]
+
+
+@pytest.mark.parametrize("m,n,k", STREAM)
+def test_stream_matches_oracle(m, n, k):
+    x, w = _case(m, n, k, seed=m * 13 + n + k)
+    want = O.matmul(O.bf16_widen(x), w)
+    got = widen(_run(x, w, "stream"))
+    assert rel_error(got, want) <= BF16_TOL
+    got32 = widen(_run(x, w, "stream", out_dtype=torch.float32))
+    assert rel_error(got32, want) <= F32_TOL
+
+
 @pytest.mark.parametrize("m,n,k", SKINNY)
 def test_skinny_matches_oracle(m, n, k):
     x, w = _case(m, n, k, seed=m * 7 + n + k)
@@ -59,7 +73,7 @@ def test_umma_matches_oracle(m, n, k):
     assert rel_error(got32, want) <= F32_TOL
 
 
-@pytest.mark.parametrize("path,m", [("skinny", 8), ("umma", 8), ("umma", 160)])
+@pytest.mark.parametrize("path,m", [("skinny", 8), ("umma", 8), ("umma", 160), ("stream", 8), ("stream", 77)])
 def test_one_hot_rows_read_weights_back(path, m):
     # engine/rules/linear/tests/lanes_test.rs:96-106
     n, k = 256, 512
@@ -73,7 +87,7 @@ def test_one_hot_rows_read_weights_back(path, m):
     assert np.array_equal(to_bits(got), w[:, hot].T)
 
 
-@pytest.mark.parametrize("path", ["skinny", "umma"])
+@pytest.mark.parametrize("path", ["skinny", "umma", "stream"])
 @pytest.mark.parametrize("m", [3, 64])
 def test_residual_add_epilogue(path, m):
     n, k = 1024, 2048
@@ -85,7 +99,8 @@ def test_residual_add_epilogue(path, m):
     assert rel_error(got, want) <= F32_TOL
 
 
-@pytest.mark.parametrize("path,m", [("skinny", 4), ("skinny", 64), ("umma", 64), ("umma", 256)])
+@pytest.mark.parametrize("path,m", [("skinny", 4), ("skinny", 64), ("umma", 64), ("umma", 256), ("stream", 4),
+                                    ("stream", 64), ("stream", 128)])
 @pytest.mark.parametrize("act", ["swiglu", "geglu"])
 def test_gated_epilogue(path, m, act):
     ffn, k = 768, 512
@@ -98,7 +113,17 @@ def test_gated_epilogue(path, m, act):
     assert rel_error(got, want) <= BF16_TOL
 
 
-@pytest.mark.parametrize("path", ["skinny", "umma"])
+def test_stream_gated_wide_enough_for_one_block_per_tile():
+    # (n/2) / 64 tiles >= SM count: no cluster, the pairing goes through the block's own buffer
+    m, ffn, k = 20, 64 * 160, 128
+    x, w = _case(m, 2 * ffn, k, seed=77)
+    xs = O.bf16_widen(x)
+    want = O.act(O.matmul(xs, w[:ffn]), "silu") * O.matmul(xs, w[ffn:])
+    got = widen(_run(x, w, "stream", epilogue="swiglu"))
+    assert rel_error(got, want) <= BF16_TOL
+
+
+@pytest.mark.parametrize("path", ["skinny", "umma", "stream"])
 def test_scale_epilogue(path):
     x, w = _case(9, 512, 256, seed=3)
     want = O.matmul(O.bf16_widen(x), w) * np.float32(0.125)
@@ -111,7 +136,7 @@ def test_lm_head_shape_small_batch():
     m, n, k = 2, 151936, 1024
     x, w = _case(m, n, k, seed=1)
     want = O.matmul(O.bf16_widen(x), w)
-    for path in ("skinny", "umma"):
+    for path in ("skinny", "umma", "stream"):
         got = widen(_run(x, w, path, out_dtype=torch.float32))
         assert rel_error(got, want) <= F32_TOL
 
@@ -119,7 +144,7 @@ def test_lm_head_shape_small_batch():
 def test_rerun_is_bit_identical():
     # Order::PerConfig (engine/ir/graph/src/numerics.rs:26-35): one configuration, one sum order
     x, w = _case(64, 1024, 3072, seed=8)
-    for path in ("skinny", "umma"):
+    for path in ("skinny", "umma", "stream"):
         a = _run(x, w, path, out_dtype=torch.float32)
         b = _run(x, w, path, out_dtype=torch.float32)
         assert torch.equal(a, b)
