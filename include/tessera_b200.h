@@ -162,6 +162,20 @@ size_t ts_top_k_workspace_bytes(uint32_t rows, uint32_t width, uint32_t k);
 int ts_top_k(const void *x, int x_dtype, uint32_t *ids, uint32_t rows, uint32_t width, uint32_t k,
              void *workspace, size_t workspace_bytes, void *stream);
 
+/* Greedy top-1 (ts_top_k with k = 1) for callers that have no scratch memory to give.  It has no
+ * counterpart in the reference.  A host runtime that fixed all of its device buffers when it planned,
+ * or a process whose memory budget is already spent, cannot supply the workspace ts_top_k asks for and
+ * cannot allocate one; this entry point needs none from them: its scratch is a 512 KiB device array
+ * built into the library (so every GPU that loads the library holds those 512 KiB until exit), and it
+ * calls no allocator of any kind.
+ *   x f32 or bf16 [rows, width]; ids u32 [rows]; same ordering rules and same results as ts_top_k.
+ *   rows must not exceed 1024 (the size of the built-in scratch): more returns TS_ERR_BAD_INPUT.
+ * The first call on each device looks up the array's device address (with that device current); make
+ * that first call before starting any stream capture.  All calls share the one array - nothing in it
+ * has to be cleared, each call overwrites what it reads - so two calls that overlap on the GPU (two
+ * streams, two threads) race: serialise them. */
+int ts_top_1_static(const void *x, int x_dtype, uint32_t *ids, uint32_t rows, uint32_t width, void *stream);
+
 /* gates[r, :] = softmax(x[r, ids[r, :]]) — the router's `take` + `softmax`
  * (engine/models/src/decoder.rs:73-75).  x f32 [rows, width], ids u32 [rows, k], gates f32. */
 int ts_take_softmax(const float *x, const uint32_t *ids, float *gates, uint32_t rows, uint32_t width,

@@ -259,6 +259,13 @@ int ts_top_k(const void *x, int x_dtype, uint32_t *ids, uint32_t rows, uint32_t 
     return top_k(x, x_dtype, ids, rows, width, k, workspace, workspace_bytes, (cudaStream_t)stream);
 }
 
+int ts_top_1_static(const void *x, int x_dtype, uint32_t *ids, uint32_t rows, uint32_t width, void *stream) {
+    TS_REQUIRE(x && ids, "top_1_static: a buffer is NULL");
+    TS_REQUIRE(x_dtype == TS_BF16 || x_dtype == TS_F32, "top_1_static: unknown dtype");
+    TS_REQUIRE(width > 0, "top_1_static: width is zero");
+    return top_1_static(x, x_dtype, ids, rows, width, (cudaStream_t)stream);
+}
+
 int ts_take_softmax(const float *x, const uint32_t *ids, float *gates, uint32_t rows, uint32_t width, uint32_t k,
                     void *stream) {
     TS_REQUIRE(x && ids && gates, "take_softmax: a buffer is NULL");

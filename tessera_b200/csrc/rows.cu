@@ -439,6 +439,59 @@ int top_k(const void *x, int x_dtype, uint32_t *ids, uint32_t rows, uint32_t wid
     return TS_OK;
 }
 
+// ---- greedy top-1 that brings its own scratch -----------------------------------------------
+// The two-stage top-1 above needs rows x 64 (value, index) pairs of scratch between its launches.
+// Some hosts cannot hand a kernel any: a plug-in inside a runtime that sized every device buffer
+// when it built its plan (tessera's runner does, and gives kernels no allocator), or a caller whose
+// memory budget is fixed and already spent.  For them the scratch lives in this library's image: a
+// file-scope device array of kStaticTopRows * 64 * 8 bytes (512 KiB), which every GPU that loads the
+// library carries until the process exits.
+constexpr uint32_t kStaticTopRows = 1024;
+static __device__ __align__(256) unsigned char g_top1_scratch[kStaticTopRows * kPeakParts * 8];
+
+// In host code `g_top1_scratch` is only a stand-in for the symbol, not a device address: the real
+// address is looked up once per device, with that device current, and cached.
+static void *g_top1_scratch_addr[64] = {};
+
+static int top1_scratch(void **out) {
+    int dev = -1;
+    TS_CUDA(cudaGetDevice(&dev));
+    TS_REQUIRE(dev >= 0 && dev < 64, "top_1_static: device ordinal %d is outside 0..63", dev);
+    if (g_top1_scratch_addr[dev] == nullptr) {
+        void *p = nullptr;
+        TS_CUDA(cudaGetSymbolAddress(&p, g_top1_scratch));
+        g_top1_scratch_addr[dev] = p;
+    }
+    *out = g_top1_scratch_addr[dev];
+    return TS_OK;
+}
+
+int top_1_static(const void *x, int x_dtype, uint32_t *ids, uint32_t rows, uint32_t width, cudaStream_t stream) {
+    TS_REQUIRE(rows <= kStaticTopRows, "top_1_static: %u rows, the built-in scratch holds at most %u", rows,
+               kStaticTopRows);
+    if (rows == 0) return TS_OK;
+    void *scratch = nullptr;
+    int rc = top1_scratch(&scratch);
+    if (rc != TS_OK) return rc;
+    // Stage 1 writes every (row, part) pair before stage 2 reads it, so nothing has to start at zero;
+    // what an earlier call left behind is simply overwritten.
+    float *pv = (float *)scratch;
+    uint32_t *pi = (uint32_t *)(pv + (size_t)kStaticTopRows * kPeakParts);
+    const bool pdl = pdl_enabled();
+    cudaError_t e;
+    if (x_dtype == TS_F32)
+        e = launch(peaks_kernel<float>, dim3(kPeakParts, rows), dim3(256), 0, stream, pdl, (const float *)x, pv, pi,
+                   width, kPeakParts);
+    else
+        e = launch(peaks_kernel<uint16_t>, dim3(kPeakParts, rows), dim3(256), 0, stream, pdl, (const uint16_t *)x, pv,
+                   pi, width, kPeakParts);
+    if (e != cudaSuccess) return fail(TS_ERR_CUDA, "launch of peaks failed: %s", cudaGetErrorString(e));
+    e = launch(argmax_kernel, dim3(rows), dim3(32), 0, stream, pdl, (const float *)pv, (const uint32_t *)pi, ids, width,
+               kPeakParts);
+    if (e != cudaSuccess) return fail(TS_ERR_CUDA, "launch of argmax failed: %s", cudaGetErrorString(e));
+    return TS_OK;
+}
+
 int take_softmax(const float *x, const uint32_t *ids, float *gates, uint32_t rows, uint32_t width, uint32_t k,
                  cudaStream_t stream) {
     if (rows == 0) return TS_OK;

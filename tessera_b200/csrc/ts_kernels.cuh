@@ -42,6 +42,7 @@ int qk_norm_rope_append(const void *qkv, const float *q_norm, const float *k_nor
 size_t top_k_workspace_bytes(uint32_t rows, uint32_t width, uint32_t k);
 int top_k(const void *x, int x_dtype, uint32_t *ids, uint32_t rows, uint32_t width, uint32_t k, void *workspace,
           size_t workspace_bytes, cudaStream_t stream);
+int top_1_static(const void *x, int x_dtype, uint32_t *ids, uint32_t rows, uint32_t width, cudaStream_t stream);
 int take_softmax(const float *x, const uint32_t *ids, float *gates, uint32_t rows, uint32_t width, uint32_t k,
                  cudaStream_t stream);
 
