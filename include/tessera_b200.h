@@ -140,6 +140,27 @@ int ts_qk_norm_rope_append_bf16(const void *qkv, const float *q_norm, const floa
 /* out[j] = theta^(-2j / width) for j < width/2, in f32 on the host (engine/ir/interp/src/cpu.rs:31-34). */
 void ts_rope_inv_freq(float theta, uint32_t width, float *out);
 
+/* Whole-sequence attention.  Replaces `flash*` (engine/rules/attention/src/flash.rs:415-502,
+ * arguments 648-668) and `attend` (engine/rules/attention/src/attend.rs:80-123).  Query t of a
+ * sequence sits at position past + t with past = keys - queries (0 when keys < queries under a
+ * two-sided mask) and sees keys [max(0, pos - back), min(keys, pos + ahead + 1))
+ * (engine/ir/graph/src/node.rs:162-187); causal: back = UINT32_MAX, ahead = 0; bidirectional: both
+ * UINT32_MAX; Within(n): both n; Back(n): back = n, ahead = 0.  The score scale (> 0) is applied to
+ * the dot products, where the reference runs a separate `map` launch on q.
+ *   q [seqs, queries, heads, width], k/v [seqs, keys, kv_heads, width], out like q; all bf16.
+ * With cu_seqlens (device u32 [seqs + 1], width 128 only) the sequences are packed back to back:
+ * q/k/v/out are [total, heads|kv_heads, width], sequence s owns rows [cu[s], cu[s+1]) as both its
+ * queries and its keys, `queries` bounds the longest sequence and `keys` is the total row count.
+ * Width 128 runs on tcgen05 (no workspace); widths 64 and 256 take the ragged-rows kernel and need
+ * the workspace ts_attend_workspace_bytes reports. */
+size_t ts_attend_workspace_bytes(uint32_t seqs, uint32_t queries, uint32_t keys, uint32_t heads,
+                                 uint32_t kv_heads, uint32_t width);
+
+int ts_attend_bf16(const void *q, const void *k, const void *v, void *out, const uint32_t *cu_seqlens,
+                   uint32_t seqs, uint32_t queries, uint32_t keys, uint32_t heads, uint32_t kv_heads,
+                   uint32_t width, uint32_t back, uint32_t ahead, float scale, void *workspace,
+                   size_t workspace_bytes, void *stream);
+
 /* ---------------------------------------------------------------------------
  * Row kernels the decode loop needs around the two hot rules.
  * ------------------------------------------------------------------------- */

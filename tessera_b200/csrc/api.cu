@@ -132,8 +132,8 @@ int ts_set_pdl(int enabled) {
 }
 
 int ts_device_status(void) {
-    const int a = umma_take_status(), b = stream_take_status();
-    return a ? a : b;
+    const int a = umma_take_status(), b = stream_take_status(), c = flash_take_status();
+    return a ? a : b ? b : c;
 }
 
 size_t ts_linear_workspace_bytes(uint32_t m, uint32_t n, uint32_t k, int epilogue, int path) {
@@ -198,6 +198,49 @@ int ts_attend_rows_bf16(const void *q, const void *k, const void *v, void *out, 
     if (rows == 0 || keys == 0) return TS_OK;
     return attend_rows(q, k, v, out, slots, positions, dev, contiguous, rows, keys, heads, kv_heads, width, back, scale,
                        workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+size_t ts_attend_workspace_bytes(uint32_t seqs, uint32_t queries, uint32_t keys, uint32_t heads, uint32_t kv_heads,
+                                 uint32_t width) {
+    if (flash_supports(width)) return 0;
+    // fallback: slot and position of every query row, then the rows kernel's own scratch
+    const size_t rows = (size_t)seqs * queries;
+    return align_up(rows * 8, 256) + attend_rows_workspace_bytes((uint32_t)rows, keys, heads, kv_heads, width);
+}
+
+int ts_attend_bf16(const void *q, const void *k, const void *v, void *out, const uint32_t *cu_seqlens, uint32_t seqs,
+                   uint32_t queries, uint32_t keys, uint32_t heads, uint32_t kv_heads, uint32_t width, uint32_t back,
+                   uint32_t ahead, float scale, void *workspace, size_t workspace_bytes, void *stream) {
+    TS_REQUIRE(q && k && v && out, "attend: a buffer is NULL");
+    TS_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out), "attend: buffers must be 16-byte aligned");
+    TS_REQUIRE(kv_heads > 0 && heads % kv_heads == 0, "attend: %u heads do not split over %u kv heads", heads, kv_heads);
+    TS_REQUIRE(scale > 0.0f, "attend: the score scale must be positive");
+    if (seqs == 0 || queries == 0) return TS_OK;
+    const bool causal = ahead == 0;
+    TS_REQUIRE(!(causal && keys < queries && !cu_seqlens), "attend: %u queries, %u keys under a causal mask", queries,
+               keys);  // engine/ir/interp/src/cpu.rs:62-68
+    cudaStream_t s = (cudaStream_t)stream;
+    if (flash_supports(width)) {
+        // With cu_seqlens the rows are packed and `queries` bounds the longest sequence.
+        const uint32_t total_q = cu_seqlens ? 0xFFFFFFFFu : seqs * queries;
+        (void)total_q;
+        return attend_flash(q, k, v, out, cu_seqlens, seqs, queries, keys, cu_seqlens ? keys : seqs * queries,
+                            cu_seqlens ? keys : seqs * keys, heads, kv_heads, back, ahead, scale, s);
+    }
+    TS_REQUIRE(!cu_seqlens, "attend: packed sequences need width 128 (got %u)", width);
+    TS_REQUIRE(width == 64 || width == 256, "attend: width %u is not 64, 128 or 256", width);
+    const size_t rows = (size_t)seqs * queries;
+    const size_t need = ts_attend_workspace_bytes(seqs, queries, keys, heads, kv_heads, width);
+    TS_REQUIRE(workspace && workspace_bytes >= need, "attend: workspace of %zu bytes is smaller than the %zu needed",
+               workspace_bytes, need);
+    uint32_t *slots = (uint32_t *)workspace, *positions = slots + rows;
+    const uint32_t past = keys > queries ? keys - queries : 0;
+    int rc = iota_rows(slots, positions, seqs, queries, past, s);
+    if (rc != TS_OK) return rc;
+    KeptDev dense = {TS_KEPT_DENSE, 0, keys, nullptr};
+    const size_t head = align_up(rows * 8, 256);
+    return attend_rows(q, k, v, out, slots, positions, dense, true, (uint32_t)rows, keys, heads, kv_heads, width, back,
+                       scale, (char *)workspace + head, workspace_bytes - head, s, ahead, nullptr);
 }
 
 int ts_scatter_bf16(const void *x, const uint32_t *slots, const uint32_t *positions, void *out, const ts_kept *kept,

@@ -32,7 +32,8 @@ struct RowsParams {
     uint16_t *out;
     const uint32_t *slots, *positions;
     KeptDev kept;
-    uint32_t rows, keys, heads, kv_heads, back;
+    uint32_t rows, keys, heads, kv_heads, back, ahead;
+    const uint32_t *lens;  // per slot: keys that exist, or NULL
     uint32_t chunk, chunks;  // keys per chunk, chunks per row
     float scale;
     float *part_o;   // [rows, heads, chunks, WIDTH]
@@ -65,7 +66,11 @@ __global__ void __launch_bounds__(kThreads) attend_rows_kernel(const RowsParams 
 
     pdl_wait();
     const uint32_t slot = p.slots[row], pos = p.positions[row];
-    const uint32_t last = min(pos + 1, p.keys);
+    // Visible keys [first, last): engine/ir/graph/src/node.rs:162-187 with ends aligned.
+    uint32_t reach = pos + p.ahead;
+    if (reach < pos || reach == 0xFFFFFFFFu) reach = 0xFFFFFFFEu;  // saturate so that reach + 1 cannot wrap
+    uint32_t last = min(reach + 1, p.keys);
+    if (p.lens) last = min(last, p.lens[slot]);
     const uint32_t first = pos > p.back ? pos - p.back : 0;
     const uint32_t lo = max(first, chunk * p.chunk), hi = min(last, (chunk + 1) * p.chunk);
 
@@ -304,7 +309,7 @@ size_t attend_rows_workspace_bytes(uint32_t rows, uint32_t keys, uint32_t heads,
 int attend_rows(const void *q, const void *k, const void *v, void *out, const uint32_t *slots,
                 const uint32_t *positions, const KeptDev &kept, bool contiguous, uint32_t rows, uint32_t keys,
                 uint32_t heads, uint32_t kv_heads, uint32_t width, uint32_t back, float scale, void *workspace,
-                size_t workspace_bytes, cudaStream_t stream) {
+                size_t workspace_bytes, cudaStream_t stream, uint32_t ahead, const uint32_t *lens) {
     RowsPlan s = plan_rows(rows, keys, heads, kv_heads);
     size_t need = s.chunks > 1 ? (size_t)rows * heads * s.chunks * (width + 2) * sizeof(float) : 0;
     TS_REQUIRE(workspace_bytes >= need && (need == 0 || workspace != nullptr),
@@ -322,6 +327,8 @@ int attend_rows(const void *q, const void *k, const void *v, void *out, const ui
     p.heads = heads;
     p.kv_heads = kv_heads;
     p.back = back;
+    p.ahead = ahead;
+    p.lens = lens;
     p.chunk = s.chunk;
     p.chunks = s.chunks;
     p.scale = scale;

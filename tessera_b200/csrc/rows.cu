@@ -305,6 +305,17 @@ __global__ void advance_rows_kernel(const uint32_t *ids, uint32_t *tokens, uint3
     pdl_launch_dependents();
 }
 
+__global__ void iota_rows_kernel(uint32_t *slots, uint32_t *positions, uint32_t total, uint32_t queries,
+                                 uint32_t past) {
+    pdl_wait();
+    const uint32_t r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r < total) {
+        slots[r] = r / queries;
+        positions[r] = past + r % queries;
+    }
+    pdl_launch_dependents();
+}
+
 // Holds the stream until the host sets *flag, so that launches queued behind it run back to back
 // and per-kernel event intervals exclude host launch gaps.  One thread; gives up after `spins` reads
 // (engine/gpu/gpukit/src/gate.cu does the same with 2^21).
@@ -316,6 +327,16 @@ __global__ void gate_kernel(const volatile uint32_t *flag, uint32_t spins) {
 constexpr uint32_t kPeakParts = 64;
 
 }  // namespace
+
+int iota_rows(uint32_t *slots, uint32_t *positions, uint32_t seqs, uint32_t queries, uint32_t past,
+              cudaStream_t stream) {
+    const uint32_t total = seqs * queries;
+    if (total == 0) return TS_OK;
+    cudaError_t e = launch(iota_rows_kernel, dim3(ceil_div(total, 256)), dim3(256), 0, stream, pdl_enabled(), slots,
+                           positions, total, queries, past);
+    if (e != cudaSuccess) return fail(TS_ERR_CUDA, "launch of iota_rows failed: %s", cudaGetErrorString(e));
+    return TS_OK;
+}
 
 int gate(const volatile uint32_t *flag, cudaStream_t stream) {
     gate_kernel<<<1, 1, 0, stream>>>(flag, 1u << 21);

@@ -104,6 +104,34 @@ def attend_rows(q, k_rows, v_rows, slots, positions, kept: Kept, keys: int, *, s
     return out
 
 
+FAR = 0xFFFFFFFF
+MASKS = {"causal": (FAR, 0), "bidirectional": (FAR, FAR)}
+
+
+def attend(q, k, v, *, mask="causal", scale: float, cu_seqlens=None, max_len=None, out=None):
+    """Whole-sequence attention: ts_attend_bf16.  mask: 'causal' | 'bidirectional' | ('within', n) | ('back', n).
+    Fixed layout: q [seqs, queries, heads, width], k/v [seqs, keys, kv_heads, width].
+    Packed: q/k/v [total, heads, width] with cu_seqlens (int32 [seqs + 1]) and max_len."""
+    if isinstance(mask, tuple):
+        back, ahead = (mask[1], mask[1]) if mask[0] == "within" else (mask[1], 0)
+    else:
+        back, ahead = MASKS[mask]
+    if cu_seqlens is None:
+        seqs, queries, heads, width = q.shape
+        keys, kv_heads = k.shape[1], k.shape[2]
+    else:
+        total, heads, width = q.shape
+        kv_heads = k.shape[1]
+        seqs, queries, keys = cu_seqlens.numel() - 1, int(max_len), total
+    if out is None:
+        out = torch.empty_like(q)
+    nbytes = lib.ts_attend_workspace_bytes(seqs, queries, keys, heads, kv_heads, width)
+    ws = workspace(nbytes, q.device)
+    check(lib.ts_attend_bf16(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(cu_seqlens), seqs, queries, keys, heads,
+                             kv_heads, width, back, ahead, scale, _ptr(ws), nbytes, _stream()))
+    return out
+
+
 def scatter(x, slots, positions, out, kept: Kept):
     rows = x.shape[0]
     width = x.numel() // max(rows, 1)

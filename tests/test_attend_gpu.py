@@ -1,0 +1,99 @@
+"""Whole-sequence attention (tcgen05 path at width 128, ragged-rows path at widths 64 / 256)
+against the CPU checker, over the case grid of engine/rules/attention/tests/attention_test.rs:43-102
+(sequence/row/key counts x masks x head shapes).  bf16 outputs with f32 sums: within 1e-2 of the
+checker relative to the largest output."""
+import numpy as np
+import pytest
+import torch
+
+import oracle as O
+from tests.util import dev_u32, from_bits, normal_bf16, rel_error, widen
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+
+CASES = [(1, 128, 128), (2, 200, 200), (2, 70, 300), (1, 513, 513), (3, 1, 257), (1, 1000, 1000)]
+MASKS = ["causal", "bidirectional", ("within", 17), ("back", 33), ("back", 300)]
+HEADS = [(16, 8, 128), (4, 4, 128), (8, 2, 128)]
+
+
+def _run(q, k, v, mask, scale, **kw):
+    from tessera_b200 import ops
+    out = ops.attend(from_bits(q), from_bits(k), from_bits(v), mask=mask, scale=scale, **kw)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    return widen(out)
+
+
+@pytest.mark.parametrize("seqs,queries,keys", CASES)
+@pytest.mark.parametrize("mask", MASKS)
+def test_flash_matches_oracle(seqs, queries, keys, mask):
+    heads, kv_heads, width = 4, 2, 128
+    rng = np.random.default_rng(seqs * 1000 + queries + keys)
+    q = normal_bf16(rng, (seqs, queries, heads, width))
+    k = normal_bf16(rng, (seqs, keys, kv_heads, width))
+    v = normal_bf16(rng, (seqs, keys, kv_heads, width))
+    scale = float(1.0 / np.sqrt(width))
+    want = O.attend(O.bf16_widen(q), O.bf16_widen(k), O.bf16_widen(v), mask, scale)
+    got = _run(q, k, v, mask, scale)
+    assert rel_error(got, want) <= TOL
+
+
+@pytest.mark.parametrize("heads,kv_heads,width", HEADS + [(4, 2, 64), (3, 1, 256)])
+@pytest.mark.parametrize("mask", ["causal", "bidirectional"])
+def test_head_shapes(heads, kv_heads, width, mask):
+    rng = np.random.default_rng(heads * 7 + width)
+    seqs, n = 2, 160
+    q = normal_bf16(rng, (seqs, n, heads, width))
+    k = normal_bf16(rng, (seqs, n, kv_heads, width))
+    v = normal_bf16(rng, (seqs, n, kv_heads, width))
+    scale = float(1.0 / np.sqrt(width))
+    want = O.attend(O.bf16_widen(q), O.bf16_widen(k), O.bf16_widen(v), mask, scale)
+    got = _run(q, k, v, mask, scale)
+    assert rel_error(got, want) <= TOL
+
+
+@pytest.mark.parametrize("mask", ["causal", "bidirectional"])
+def test_packed_sequences(mask):
+    # ragged lengths packed back to back, the embedding batch's shape (lengths 32..512)
+    rng = np.random.default_rng(5)
+    lens = [32, 300, 129, 512, 1, 77]
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.uint32)
+    total, heads, kv_heads, width = int(cu[-1]), 4, 2, 128
+    q = normal_bf16(rng, (total, heads, width))
+    k = normal_bf16(rng, (total, kv_heads, width))
+    v = normal_bf16(rng, (total, kv_heads, width))
+    scale = 0.1
+    got = _run(q, k, v, mask, scale, cu_seqlens=dev_u32(cu), max_len=max(lens))
+    for s, n in enumerate(lens):
+        a, b = int(cu[s]), int(cu[s + 1])
+        want = O.attend(O.bf16_widen(q[a:b])[None], O.bf16_widen(k[a:b])[None], O.bf16_widen(v[a:b])[None], mask, scale)[0]
+        assert rel_error(got[a:b], want) <= TOL, (s, n)
+
+
+def test_causal_first_row_reads_first_value():
+    # engine/ir/interp/src/interp_test.rs:76-86 on the device: causal row 0 equals V row 0
+    rng = np.random.default_rng(1)
+    q = normal_bf16(rng, (2, 130, 4, 128))
+    k = normal_bf16(rng, (2, 130, 4, 128))
+    v = normal_bf16(rng, (2, 130, 4, 128))
+    got = _run(q, k, v, "causal", 0.5)
+    assert np.array_equal(got[:, 0], O.bf16_widen(v)[:, 0])
+
+
+def test_prefill_shape_spot_check():
+    # batch 1 x 2048 tokens of the isolated attention configuration (16q / 8kv heads, 128 wide), causal;
+    # the checker on a sample of query rows (full checker cost grows with tokens squared)
+    rng = np.random.default_rng(3)
+    n, heads, kv_heads, width = 2048, 16, 8, 128
+    q = normal_bf16(rng, (1, n, heads, width))
+    k = normal_bf16(rng, (1, n, kv_heads, width))
+    v = normal_bf16(rng, (1, n, kv_heads, width))
+    scale = float(1.0 / np.sqrt(width))
+    got = _run(q, k, v, "causal", scale)
+    rows = [0, 1, 127, 128, 129, 1000, 2047]
+    kd, vd = O.bf16_widen(k), O.bf16_widen(v)
+    want = O.attend_rows(O.bf16_widen(q)[0, rows], kd, vd, [0] * len(rows), rows, "causal", scale)
+    assert rel_error(got[0, rows], want) <= TOL
+    again = _run(q, k, v, "causal", scale)
+    assert np.array_equal(got, again)  # same bits on a re-run
