@@ -202,6 +202,38 @@ int ts_top_1_static(const void *x, int x_dtype, uint32_t *ids, uint32_t rows, ui
 int ts_take_softmax(const float *x, const uint32_t *ids, float *gates, uint32_t rows, uint32_t width,
                     uint32_t k, void *stream);
 
+/* ---------------------------------------------------------------------------
+ * Routed experts.  Replaces the `picked` matmuls (engine/rules/linear/src/picked.rs:28-60, arguments
+ * `x, w, ids, out, rows, n, k, count, stride, offset, repeat, first`; engine/ir/interp/src/cpu.rs:89-105)
+ * and the `mix` (cpu.rs:449-473) of the reference's MoE block (engine/models/src/decoder.rs:70-84):
+ *     expert_e(x) = (silu(x W_gate[e]^T) * (x W_up[e]^T)) W_down[e]^T
+ *   w_in  [experts, 2 * ffn, hidden] bf16: each expert's gate rows, then its up rows
+ *   w_out [experts, hidden, ffn] bf16
+ * `experts` is the number of experts in these tables and `first` the global id of the first one: a
+ * pick whose id falls outside [first, first + experts) contributes zeros, the reference's rule for
+ * experts another rank holds (picked.rs:49-59).  The inner rows pass through bf16.
+ * ------------------------------------------------------------------------- */
+size_t ts_moe_workspace_bytes(uint32_t picks, uint32_t experts, uint32_t hidden, uint32_t ffn);
+
+/* out[i, :] = expert_{ids[i]}(x[i / repeat, :]) for i < picks; x bf16 [picks / repeat, hidden], out f32. */
+int ts_moe_experts_bf16(const void *x, const uint32_t *ids, const void *w_in, const void *w_out, float *out,
+                        uint32_t picks, uint32_t repeat, uint32_t experts, uint32_t first, uint32_t hidden,
+                        uint32_t ffn, void *workspace, size_t workspace_bytes, void *stream);
+
+/* y[r, :] = sum_p gates[r, p] * expert_{ids[r, p]}(h[r, :]) in pick order p = 0..top-1, plus add[r, :]
+ * when add is not NULL (the shared expert's output, engine/models/src/mla.rs:466-467).
+ *   h bf16 [rows, hidden]; ids u32 [rows, top]; gates f32 [rows, top]; add, y f32 [rows, hidden]. */
+int ts_moe_bf16(const void *h, const uint32_t *ids, const float *gates, const float *add, const void *w_in,
+                const void *w_out, float *y, uint32_t rows, uint32_t top, uint32_t experts, uint32_t first,
+                uint32_t hidden, uint32_t ffn, void *workspace, size_t workspace_bytes, void *stream);
+
+/* The token permutation alone (integer work, the same bits on every run): order[j] = index of the
+ * j-th pick when picks are sorted by expert, stable in pick index; place[i] = j with order[j] = i, or
+ * UINT32_MAX for a pick of an expert outside [first, first + experts); offsets[e] = first j of expert e
+ * (experts + 1 entries); batch_tiles[e] = prefix sum of ceil(count_e / 32) (experts + 1 entries). */
+int ts_moe_permutation(const uint32_t *ids, uint32_t *order, uint32_t *place, uint32_t *offsets,
+                       uint32_t *batch_tiles, uint32_t picks, uint32_t experts, uint32_t first, void *stream);
+
 /* Programmatic dependent launch on every kernel of this library (off by default): a kernel's
  * weight prefetch then overlaps the tail of the kernel before it, as the reference's `pdl` launch
  * setting does (engine/gpu/gpukit/src/cuda/context.rs:126-148). Process-wide. */

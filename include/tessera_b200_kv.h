@@ -1,0 +1,87 @@
+/*
+ * tessera_b200 KV page pool — the host-side allocator that produces the page tables the paged
+ * attention kernel walks.  It restates tessera-kv's `Pool` (engine/ir/kv/src/pool.rs:71-305): runs of
+ * kept rows hold pages of `page` rows; forks share a source's pages (reference counts per page, live
+ * and retained holders apart); a write into a shared partial page first copies it (`PageCopy`);
+ * admission refuses anything that would keep some live run from reaching its worst case; retained
+ * runs are reclaimed oldest first; pages are handed out lowest-free-first; every error leaves the
+ * pool unchanged (pool.rs:25-40).  Pure host code: no CUDA call except ts_kv_copy_pages.
+ */
+#ifndef TESSERA_B200_KV_H
+#define TESSERA_B200_KV_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct ts_kv_pool ts_kv_pool;
+
+/* A run's place in the pool; stale ids fail (pool.rs:6-11). */
+typedef struct {
+    uint32_t at, generation;
+} ts_kv_run;
+
+/* Rows to copy between pages before the launch writes (pool.rs:17-23). */
+typedef struct {
+    uint32_t from, to, rows;
+} ts_kv_copy;
+
+/* pool.rs:25-40.  `detail` of the last failure: the page count of NO_ROOM, the bound of PAST_*. */
+typedef enum {
+    TS_KV_OK = 0,
+    TS_KV_NO_ROOM = 1,
+    TS_KV_PAST_WORST = 2,
+    TS_KV_PAST_SOURCE = 3,
+    TS_KV_LIVE = 4,
+    TS_KV_RETAINED = 5,
+    TS_KV_UNKNOWN = 6,
+    TS_KV_BAD_ARGUMENT = 7
+} ts_kv_status;
+
+/* pool.rs:56-68. */
+typedef struct {
+    uint64_t size, active, worst, live_runs, kept_runs;
+} ts_kv_stats;
+
+ts_kv_pool *ts_kv_pool_new(uint32_t pages, uint32_t page_rows);
+void ts_kv_pool_free(ts_kv_pool *pool);
+uint64_t ts_kv_last_detail(const ts_kv_pool *pool);
+
+/* pool.rs:139-156, 158-191, 193-222, 224-246, 248-262, 264-300, 302-308. */
+int ts_kv_reserve(ts_kv_pool *pool, uint64_t tag, uint64_t rows, uint64_t worst, ts_kv_run *out);
+int ts_kv_fork(ts_kv_pool *pool, ts_kv_run source, uint64_t rows, uint64_t worst, ts_kv_run *out);
+int ts_kv_grow(ts_kv_pool *pool, ts_kv_run run, uint64_t rows, ts_kv_copy *copies, uint32_t capacity,
+               uint32_t *n_copies);
+int ts_kv_truncate(ts_kv_pool *pool, ts_kv_run run, uint64_t rows);
+int ts_kv_retain(ts_kv_pool *pool, ts_kv_run run);
+int ts_kv_adopt(ts_kv_pool *pool, ts_kv_run run, uint64_t rows, uint64_t worst, ts_kv_run *out);
+int ts_kv_release(ts_kv_pool *pool, ts_kv_run run);
+
+/* pool.rs:87-97: the run's pages in order (writes at most `capacity`, reports the count), rows, tag. */
+int ts_kv_pages(const ts_kv_pool *pool, ts_kv_run run, uint32_t *out, uint32_t capacity, uint32_t *count);
+int ts_kv_rows(const ts_kv_pool *pool, ts_kv_run run, uint64_t *rows);
+int ts_kv_tag(const ts_kv_pool *pool, ts_kv_run run, uint64_t *tag);
+
+/* pool.rs:99-137, 310-332, 433-449. */
+uint64_t ts_kv_spare(const ts_kv_pool *pool);
+uint64_t ts_kv_promised(const ts_kv_pool *pool);
+void ts_kv_get_stats(const ts_kv_pool *pool, ts_kv_stats *out);
+uint64_t ts_kv_digest(const ts_kv_pool *pool);
+int ts_kv_consistent(const ts_kv_pool *pool);
+
+/* Writes the run's pages into row `slot` of a page table of `kept_pages` entries per slot (the
+ * layout ts_kept / ts_decoder_set_table take); entries past the run's pages keep their value. */
+int ts_kv_fill_table(const ts_kv_pool *pool, ts_kv_run run, uint32_t *table, uint32_t slot, uint32_t kept_pages);
+
+/* Performs page copies on the device before the launch that writes: for each copy, the first `rows`
+ * rows of page `from` go to page `to` in a kept buffer of `row_bytes` bytes per row. */
+int ts_kv_copy_pages(void *kept_rows, const ts_kv_copy *copies, uint32_t n_copies, uint32_t page_rows,
+                     size_t row_bytes, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

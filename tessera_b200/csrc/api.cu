@@ -132,8 +132,8 @@ int ts_set_pdl(int enabled) {
 }
 
 int ts_device_status(void) {
-    const int a = umma_take_status(), b = stream_take_status(), c = flash_take_status();
-    return a ? a : b ? b : c;
+    const int a = umma_take_status(), b = stream_take_status(), c = flash_take_status(), d = moe_take_status();
+    return a ? a : b ? b : c ? c : d;
 }
 
 size_t ts_linear_workspace_bytes(uint32_t m, uint32_t n, uint32_t k, int epilogue, int path) {
@@ -314,6 +314,51 @@ int ts_take_softmax(const float *x, const uint32_t *ids, float *gates, uint32_t 
     TS_REQUIRE(x && ids && gates, "take_softmax: a buffer is NULL");
     TS_REQUIRE(k >= 1 && k <= 32, "take_softmax: k = %u is outside 1..32", k);
     return take_softmax(x, ids, gates, rows, width, k, (cudaStream_t)stream);
+}
+
+size_t ts_moe_workspace_bytes(uint32_t picks, uint32_t experts, uint32_t hidden, uint32_t ffn) {
+    return moe_workspace_bytes(picks, experts, hidden, ffn);
+}
+
+static int check_moe(const void *x, const uint32_t *ids, const void *w_in, const void *w_out, const void *out,
+                     uint32_t experts, uint32_t hidden, uint32_t ffn) {
+    TS_REQUIRE(x && ids && w_in && w_out && out, "moe: a buffer is NULL");
+    TS_REQUIRE(aligned16(x) && aligned16(w_in) && aligned16(w_out) && aligned16(out), "moe: buffers must be 16-byte aligned");
+    TS_REQUIRE(experts >= 1 && experts <= 4096, "moe: %u experts is outside 1..4096", experts);
+    TS_REQUIRE(hidden % 128 == 0 && ffn % 64 == 0, "moe: hidden must be a multiple of 128 and ffn of 64 (got %u, %u)",
+               hidden, ffn);
+    return TS_OK;
+}
+
+int ts_moe_experts_bf16(const void *x, const uint32_t *ids, const void *w_in, const void *w_out, float *out,
+                        uint32_t picks, uint32_t repeat, uint32_t experts, uint32_t first, uint32_t hidden,
+                        uint32_t ffn, void *workspace, size_t workspace_bytes, void *stream) {
+    int rc = check_moe(x, ids, w_in, w_out, out, experts, hidden, ffn);
+    if (rc != TS_OK) return rc;
+    TS_REQUIRE(repeat >= 1, "moe: repeat must be at least 1");
+    if (picks == 0) return TS_OK;
+    return moe_experts(x, ids, nullptr, nullptr, w_in, w_out, out, picks, repeat, 1, 0, experts, first, hidden, ffn,
+                       workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+int ts_moe_bf16(const void *h, const uint32_t *ids, const float *gates, const float *add, const void *w_in,
+                const void *w_out, float *y, uint32_t rows, uint32_t top, uint32_t experts, uint32_t first,
+                uint32_t hidden, uint32_t ffn, void *workspace, size_t workspace_bytes, void *stream) {
+    int rc = check_moe(h, ids, w_in, w_out, y, experts, hidden, ffn);
+    if (rc != TS_OK) return rc;
+    TS_REQUIRE(gates != nullptr, "moe: gates is NULL");
+    TS_REQUIRE(top >= 1 && top <= 32, "moe: top = %u is outside 1..32", top);
+    if (rows == 0) return TS_OK;
+    return moe_experts(h, ids, gates, add, w_in, w_out, y, rows * top, top, top, 1, experts, first, hidden, ffn, workspace,
+                       workspace_bytes, (cudaStream_t)stream);
+}
+
+int ts_moe_permutation(const uint32_t *ids, uint32_t *order, uint32_t *place, uint32_t *offsets, uint32_t *batch_tiles,
+                       uint32_t picks, uint32_t experts, uint32_t first, void *stream) {
+    TS_REQUIRE(ids && order && place && offsets && batch_tiles, "moe permutation: a buffer is NULL");
+    TS_REQUIRE(experts >= 1 && experts <= 4096, "moe: %u experts is outside 1..4096", experts);
+    if (picks == 0) return TS_OK;
+    return moe_permutation(ids, order, place, offsets, batch_tiles, picks, experts, first, (cudaStream_t)stream);
 }
 
 }  // extern "C"

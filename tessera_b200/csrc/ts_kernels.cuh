@@ -54,6 +54,15 @@ int take_softmax(const float *x, const uint32_t *ids, float *gates, uint32_t row
                  cudaStream_t stream);
 
 
+int moe_take_status();
+size_t moe_workspace_bytes(uint32_t picks, uint32_t experts, uint32_t hidden, uint32_t ffn);
+int moe_permutation(const uint32_t *ids, uint32_t *order, uint32_t *place, uint32_t *offsets, uint32_t *btiles,
+                    uint32_t picks, uint32_t experts, uint32_t first, cudaStream_t stream);
+int moe_experts(const void *x, const uint32_t *ids, const float *gates, const float *add, const void *w_in,
+                const void *w_out, float *out, uint32_t picks, uint32_t repeat, uint32_t top, int mix, uint32_t experts,
+                uint32_t first, uint32_t hidden, uint32_t ffn, void *workspace, size_t workspace_bytes,
+                cudaStream_t stream);
+
 // Sets the process-wide programmatic-dependent-launch switch.
 void set_pdl(bool enabled);
 

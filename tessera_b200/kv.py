@@ -1,0 +1,145 @@
+"""Python face of the host page pool (include/tessera_b200_kv.h; tessera-kv's Pool restated)."""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from ._lib import lib
+
+u32, u64, vp, i32 = C.c_uint32, C.c_uint64, C.c_void_p, C.c_int
+
+
+class Run(C.Structure):
+    _fields_ = [("at", u32), ("generation", u32)]
+
+    def __eq__(self, other):
+        return isinstance(other, Run) and (self.at, self.generation) == (other.at, other.generation)
+
+    def __hash__(self):
+        return hash((self.at, self.generation))
+
+    def __repr__(self):
+        return f"Run(at={self.at}, generation={self.generation})"
+
+
+class PageCopy(C.Structure):
+    _fields_ = [("src", u32), ("dst", u32), ("rows", u32)]
+
+
+class Stats(C.Structure):
+    _fields_ = [(n, u64) for n in ("size", "active", "worst", "live_runs", "kept_runs")]
+
+
+KV_SIGNATURES = {
+    "ts_kv_pool_new": (vp, [u32, u32]),
+    "ts_kv_pool_free": (None, [vp]),
+    "ts_kv_last_detail": (u64, [vp]),
+    "ts_kv_reserve": (i32, [vp, u64, u64, u64, C.POINTER(Run)]),
+    "ts_kv_fork": (i32, [vp, Run, u64, u64, C.POINTER(Run)]),
+    "ts_kv_grow": (i32, [vp, Run, u64, C.POINTER(PageCopy), u32, C.POINTER(u32)]),
+    "ts_kv_truncate": (i32, [vp, Run, u64]),
+    "ts_kv_retain": (i32, [vp, Run]),
+    "ts_kv_adopt": (i32, [vp, Run, u64, u64, C.POINTER(Run)]),
+    "ts_kv_release": (i32, [vp, Run]),
+    "ts_kv_pages": (i32, [vp, Run, vp, u32, C.POINTER(u32)]),
+    "ts_kv_rows": (i32, [vp, Run, C.POINTER(u64)]),
+    "ts_kv_tag": (i32, [vp, Run, C.POINTER(u64)]),
+    "ts_kv_spare": (u64, [vp]),
+    "ts_kv_promised": (u64, [vp]),
+    "ts_kv_get_stats": (None, [vp, C.POINTER(Stats)]),
+    "ts_kv_digest": (u64, [vp]),
+    "ts_kv_consistent": (i32, [vp]),
+    "ts_kv_fill_table": (i32, [vp, Run, vp, u32, u32]),
+    "ts_kv_copy_pages": (i32, [vp, C.POINTER(PageCopy), u32, u32, C.c_size_t, vp]),
+}
+for _name, (_res, _args) in KV_SIGNATURES.items():
+    _fn = getattr(lib, _name)
+    _fn.restype, _fn.argtypes = _res, _args
+
+ERRORS = {1: "NoRoom", 2: "PastWorst", 3: "PastSource", 4: "Live", 5: "Retained", 6: "Unknown", 7: "BadArgument"}
+
+
+class PoolError(Exception):
+    """engine/ir/kv/src/pool.rs:25-40: every error leaves the pool as it was."""
+
+    def __init__(self, code: int, detail: int):
+        super().__init__(f"{ERRORS.get(code, code)}({detail})")
+        self.kind, self.detail = ERRORS.get(code, str(code)), detail
+
+
+class Pool:
+    def __init__(self, pages: int, page: int):
+        self._h = lib.ts_kv_pool_new(pages, page)
+        self.page = page
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            lib.ts_kv_pool_free(self._h)
+            self._h = None
+
+    def _check(self, code):
+        if code:
+            raise PoolError(code, int(lib.ts_kv_last_detail(self._h)))
+
+    def reserve(self, tag: int, rows: int, worst: int) -> Run:
+        out = Run()
+        self._check(lib.ts_kv_reserve(self._h, tag, rows, worst, C.byref(out)))
+        return out
+
+    def fork(self, source: Run, rows: int, worst: int) -> Run:
+        out = Run()
+        self._check(lib.ts_kv_fork(self._h, source, rows, worst, C.byref(out)))
+        return out
+
+    def grow(self, run: Run, rows: int) -> list:
+        copies, n = (PageCopy * 2)(), u32(0)
+        self._check(lib.ts_kv_grow(self._h, run, rows, copies, 2, C.byref(n)))
+        return [(c.src, c.dst, c.rows) for c in copies[: n.value]]
+
+    def truncate(self, run: Run, rows: int):
+        self._check(lib.ts_kv_truncate(self._h, run, rows))
+
+    def retain(self, run: Run):
+        self._check(lib.ts_kv_retain(self._h, run))
+
+    def adopt(self, run: Run, rows: int, worst: int) -> Run:
+        out = Run()
+        self._check(lib.ts_kv_adopt(self._h, run, rows, worst, C.byref(out)))
+        return out
+
+    def release(self, run: Run):
+        self._check(lib.ts_kv_release(self._h, run))
+
+    def pages(self, run: Run) -> list:
+        n = u32(0)
+        self._check(lib.ts_kv_pages(self._h, run, None, 0, C.byref(n)))
+        buf = (u32 * max(n.value, 1))()
+        self._check(lib.ts_kv_pages(self._h, run, buf, n.value, C.byref(n)))
+        return list(buf[: n.value])
+
+    def rows(self, run: Run) -> int:
+        out = u64(0)
+        self._check(lib.ts_kv_rows(self._h, run, C.byref(out)))
+        return out.value
+
+    def stats(self) -> Stats:
+        s = Stats()
+        lib.ts_kv_get_stats(self._h, C.byref(s))
+        return s
+
+    def spare(self) -> int:
+        return int(lib.ts_kv_spare(self._h))
+
+    def promised(self) -> int:
+        return int(lib.ts_kv_promised(self._h))
+
+    def digest(self) -> int:
+        return int(lib.ts_kv_digest(self._h))
+
+    def consistent(self) -> bool:
+        return bool(lib.ts_kv_consistent(self._h))
+
+    def fill_table(self, run: Run, table: np.ndarray, slot: int, kept_pages: int):
+        assert table.dtype == np.uint32 and table.flags.c_contiguous
+        self._check(lib.ts_kv_fill_table(self._h, run, table.ctypes.data_as(vp), slot, kept_pages))

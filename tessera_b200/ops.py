@@ -191,3 +191,40 @@ def take_softmax(x, ids):
     gates = torch.empty((rows, k), dtype=torch.float32, device=x.device)
     check(lib.ts_take_softmax(_ptr(x), _ptr(ids), _ptr(gates), rows, width, k, _stream()))
     return gates
+
+
+def moe_permutation(ids, experts: int, first: int = 0):
+    """ts_moe_permutation: (order, place, offsets, batch_tiles) of the picks in `ids` (int32, any shape)."""
+    picks = ids.numel()
+    dev = ids.device
+    order = torch.empty(picks, dtype=torch.int32, device=dev)
+    place = torch.empty(picks, dtype=torch.int32, device=dev)
+    offsets = torch.empty(experts + 1, dtype=torch.int32, device=dev)
+    tiles = torch.empty(experts + 1, dtype=torch.int32, device=dev)
+    check(lib.ts_moe_permutation(_ptr(ids), _ptr(order), _ptr(place), _ptr(offsets), _ptr(tiles), picks, experts, first,
+                                 _stream()))
+    return order, place, offsets, tiles
+
+
+def moe_experts(x, ids, w_in, w_out, *, repeat: int = 1, first: int = 0):
+    """out[i] = expert_{ids[i]}(x[i // repeat]): ts_moe_experts_bf16.  w_in [E, 2F, H], w_out [E, H, F]."""
+    experts, two_f, hidden = w_in.shape
+    picks = ids.numel()
+    out = torch.empty((picks, hidden), dtype=torch.float32, device=x.device)
+    nbytes = lib.ts_moe_workspace_bytes(picks, experts, hidden, two_f // 2)
+    ws = workspace(nbytes, x.device)
+    check(lib.ts_moe_experts_bf16(_ptr(x), _ptr(ids), _ptr(w_in), _ptr(w_out), _ptr(out), picks, repeat, experts, first,
+                                  hidden, two_f // 2, _ptr(ws), nbytes, _stream()))
+    return out
+
+
+def moe(h, ids, gates, w_in, w_out, *, add=None, first: int = 0):
+    """y[r] = sum_p gates[r, p] expert_{ids[r, p]}(h[r]) (+ add[r]): ts_moe_bf16."""
+    experts, two_f, hidden = w_in.shape
+    rows, top = ids.shape
+    y = torch.empty((rows, hidden), dtype=torch.float32, device=h.device)
+    nbytes = lib.ts_moe_workspace_bytes(rows * top, experts, hidden, two_f // 2)
+    ws = workspace(nbytes, h.device)
+    check(lib.ts_moe_bf16(_ptr(h), _ptr(ids), _ptr(gates), _ptr(add), _ptr(w_in), _ptr(w_out), _ptr(y), rows, top,
+                          experts, first, hidden, two_f // 2, _ptr(ws), nbytes, _stream()))
+    return y

@@ -19,7 +19,7 @@ def _declared(header):
 
 def test_library_exports_every_declared_symbol():
     from tessera_b200 import _lib
-    names = _declared("tessera_b200.h") + _declared("tessera_b200_run.h")
+    names = _declared("tessera_b200.h") + _declared("tessera_b200_run.h") + _declared("tessera_b200_kv.h")
     assert len(names) > 20
     for name in names:
         assert hasattr(_lib.lib, name), f"{name} is declared but not exported"
@@ -31,6 +31,8 @@ def test_python_signatures_cover_the_header():
     declared = set(_declared("tessera_b200.h"))
     assert declared == set(_lib.SIGNATURES), declared ^ set(_lib.SIGNATURES)
     assert set(_declared("tessera_b200_run.h")) == set(runner.RUN_SIGNATURES)
+    from tessera_b200 import kv
+    assert set(_declared("tessera_b200_kv.h")) == set(kv.KV_SIGNATURES)
 
 
 def test_bad_arguments_are_refused_on_the_host():
