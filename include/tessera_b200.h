@@ -227,6 +227,12 @@ int ts_moe_bf16(const void *h, const uint32_t *ids, const float *gates, const fl
                 const void *w_out, float *y, uint32_t rows, uint32_t top, uint32_t experts, uint32_t first,
                 uint32_t hidden, uint32_t ffn, void *workspace, size_t workspace_bytes, void *stream);
 
+/* The `mix` alone (engine/ir/interp/src/cpu.rs:449-473): out[r, :] = sum_p gates[r, p] * y_picks[r * top + p, :]
+ * in pick order, plus add[r, :] when add is not NULL.  For expert-parallel runs, where the per-pick outputs
+ * come back from the ranks that hold the experts.  All f32. */
+int ts_moe_mix(const float *y_picks, const float *gates, const float *add, float *out, uint32_t rows, uint32_t top,
+               uint32_t hidden, void *stream);
+
 /* The token permutation alone (integer work, the same bits on every run): order[j] = index of the
  * j-th pick when picks are sorted by expert, stable in pick index; place[i] = j with order[j] = i, or
  * UINT32_MAX for a pick of an expert outside [first, first + experts); offsets[e] = first j of expert e

@@ -55,6 +55,7 @@ SIGNATURES = {
     "ts_moe_workspace_bytes": (sz, [u32, u32, u32, u32]),
     "ts_moe_experts_bf16": (i32, [vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u32, vp, sz, vp]),
     "ts_moe_bf16": (i32, [vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u32, vp, sz, vp]),
+    "ts_moe_mix": (i32, [vp, vp, vp, vp, u32, u32, u32, vp]),
     "ts_moe_permutation": (i32, [vp, vp, vp, vp, vp, u32, u32, u32, vp]),
     "ts_take_softmax": (i32, [vp, vp, vp, u32, u32, u32, vp]),
 }

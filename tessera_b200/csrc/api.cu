@@ -353,6 +353,13 @@ int ts_moe_bf16(const void *h, const uint32_t *ids, const float *gates, const fl
                        workspace_bytes, (cudaStream_t)stream);
 }
 
+int ts_moe_mix(const float *y_picks, const float *gates, const float *add, float *out, uint32_t rows, uint32_t top,
+               uint32_t hidden, void *stream) {
+    TS_REQUIRE(y_picks && gates && out, "moe mix: a buffer is NULL");
+    TS_REQUIRE(top >= 1, "moe mix: top must be at least 1");
+    return moe_mix(y_picks, gates, add, out, rows, top, hidden, (cudaStream_t)stream);
+}
+
 int ts_moe_permutation(const uint32_t *ids, uint32_t *order, uint32_t *place, uint32_t *offsets, uint32_t *batch_tiles,
                        uint32_t picks, uint32_t experts, uint32_t first, void *stream) {
     TS_REQUIRE(ids && order && place && offsets && batch_tiles, "moe permutation: a buffer is NULL");

@@ -322,7 +322,7 @@ __global__ void __launch_bounds__(256) moe_scatter_mix_kernel(const float *y, co
         } else {
             float acc = 0.0f;
             for (uint32_t t = 0; t < top; t++) {
-                const uint32_t at = place[r * top + t];
+                const uint32_t at = place ? place[r * top + t] : r * top + t;
                 const float v = at == kNone ? 0.0f : y[(size_t)at * width + j];
                 acc = __fadd_rn(acc, __fmul_rn(v, gates[r * top + t]));
             }
@@ -438,6 +438,16 @@ int moe_experts(const void *x, const uint32_t *ids, const float *gates, const fl
     e = launch(moe_scatter_mix_kernel, dim3(out_rows), dim3(256), 0, stream, pdl_enabled(), (const float *)ws.y,
                (const uint32_t *)ws.place, gates, add, out, hidden, top, mix);
     if (e != cudaSuccess) return fail(TS_ERR_CUDA, "launch of moe_scatter_mix failed: %s", cudaGetErrorString(e));
+    return TS_OK;
+}
+
+// y_picks [rows * top, width] already in pick order: out[r] = sum_p gates[r, p] * y_picks[r * top + p] (+ add).
+int moe_mix(const float *y_picks, const float *gates, const float *add, float *out, uint32_t rows, uint32_t top,
+            uint32_t width, cudaStream_t stream) {
+    if (rows == 0) return TS_OK;
+    cudaError_t e = launch(moe_scatter_mix_kernel, dim3(rows), dim3(256), 0, stream, pdl_enabled(), y_picks,
+                           (const uint32_t *)nullptr, gates, add, out, width, top, 1);
+    if (e != cudaSuccess) return fail(TS_ERR_CUDA, "launch of moe_mix failed: %s", cudaGetErrorString(e));
     return TS_OK;
 }
 

@@ -63,6 +63,9 @@ int moe_experts(const void *x, const uint32_t *ids, const float *gates, const fl
                 uint32_t first, uint32_t hidden, uint32_t ffn, void *workspace, size_t workspace_bytes,
                 cudaStream_t stream);
 
+int moe_mix(const float *y_picks, const float *gates, const float *add, float *out, uint32_t rows, uint32_t top,
+            uint32_t width, cudaStream_t stream);
+
 // Sets the process-wide programmatic-dependent-launch switch.
 void set_pdl(bool enabled);
 

@@ -1,0 +1,110 @@
+"""The routed block of a decoder layer, on one GPU or expert-parallel over several.
+
+Mirrors engine/models/src/decoder.rs:70-84 (`Moe::apply`): scores = h router^T, ids = top_k(scores),
+gates = softmax(take(scores, ids)), y = sum_p gates[p] expert_{ids[p]}(h) in pick order, plus a shared
+expert (engine/models/src/mla.rs:466-467).
+
+Expert parallel: rank r of g holds experts [r E/g, (r+1) E/g) - the reference's axis-0 split with its
+`first` / `count` (engine/plan/lower/src/sites/matmul.rs:64, engine/rules/linear/src/picked.rs:49-53) -
+and its own share of the token rows.  Where the reference lets every rank compute zeros for foreign
+picks and all-reduces, this module moves the picks: counts all-to-all, rows to the owning rank
+(NCCL all_to_all over NVLink), grouped expert kernels there, per-pick outputs back, gate-weighted sum
+at the source in pick order.  The exchange logic is device-agnostic (tested on CPU ranks over gloo with
+injected compute); the compute callbacks default to the CUDA kernels of this library.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass
+class MoeWeights:
+    router: torch.Tensor   # bf16 [E, H] (all experts, replicated)
+    w_in: torch.Tensor     # bf16 [E_local, 2F, H] gate rows then up rows
+    w_out: torch.Tensor    # bf16 [E_local, H, F]
+    shared_in: torch.Tensor | None = None   # bf16 [2Fs, H]
+    shared_out: torch.Tensor | None = None  # bf16 [H, Fs]
+    first: int = 0         # global id of the first local expert
+    experts_total: int = 0
+
+
+def _cuda_route(h, w: MoeWeights, top: int):
+    from . import ops
+    scores = ops.linear(h, w.router, out_dtype=torch.float32)
+    ids = ops.top_k(scores, top)
+    return ids, ops.take_softmax(scores, ids)
+
+
+def _cuda_experts(x, ids, w: MoeWeights):
+    from . import ops
+    return ops.moe_experts(x, ids, w.w_in, w.w_out, repeat=1, first=w.first)
+
+
+def _cuda_shared(h, w: MoeWeights):
+    from . import ops
+    if w.shared_in is None:
+        return None
+    inner = ops.linear(h, w.shared_in, epilogue="swiglu")
+    return ops.linear(inner, w.shared_out, out_dtype=torch.float32)
+
+
+def _cuda_mix(y_picks, gates, add):
+    from . import ops
+    return ops.moe_mix(y_picks, gates, add)
+
+
+def moe_forward(h, w: MoeWeights, top: int):
+    """Single GPU: every expert is local."""
+    from . import ops
+    ids, gates = _cuda_route(h, w, top)
+    return ops.moe(h, ids, gates, w.w_in, w.w_out, add=_cuda_shared(h, w), first=w.first), ids, gates
+
+
+class ExpertParallel:
+    """Dispatch / combine of picks between ranks.  `experts_fn(x [n, H], ids [n]) -> [n, H] f32` runs on
+    the rank that holds the experts; `mix_fn(y_picks [rows * top, H], gates, add) -> [rows, H]` at the source."""
+
+    def __init__(self, group=None, experts_fn: Callable | None = None, route_fn: Callable | None = None,
+                 shared_fn: Callable | None = None, mix_fn: Callable | None = None):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.experts_fn = experts_fn or _cuda_experts
+        self.route_fn = route_fn or _cuda_route
+        self.shared_fn = shared_fn or _cuda_shared
+        self.mix_fn = mix_fn or _cuda_mix
+
+    def plan(self, ids: torch.Tensor, experts_total: int):
+        """Which rank owns each pick, the stable order that groups picks by owner, and per-owner counts."""
+        per = experts_total // self.world
+        owner = (ids.reshape(-1).to(torch.int64) // per).clamp_(max=self.world - 1)
+        order = torch.argsort(owner, stable=True)
+        counts = torch.bincount(owner, minlength=self.world)
+        return order, counts
+
+    def forward(self, h, w: MoeWeights, top: int):
+        rows, hidden = h.shape
+        ids, gates = self.route_fn(h, w, top)
+        order, send_counts = self.plan(ids, w.experts_total)
+        recv_counts = torch.empty_like(send_counts)
+        dist.all_to_all_single(recv_counts, send_counts, group=self.group)
+        send = [int(v) for v in send_counts.tolist()]   # the exchange sizes must be known on the host
+        recv = [int(v) for v in recv_counts.tolist()]
+        flat_ids = ids.reshape(-1)
+        x_send = h[(order // top)].contiguous()          # pick i reads row i // top
+        id_send = flat_ids[order].contiguous()
+        x_recv = torch.empty((sum(recv), hidden), dtype=h.dtype, device=h.device)
+        id_recv = torch.empty(sum(recv), dtype=flat_ids.dtype, device=h.device)
+        dist.all_to_all_single(x_recv, x_send, recv, send, group=self.group)
+        dist.all_to_all_single(id_recv, id_send, recv, send, group=self.group)
+        y_recv = self.experts_fn(x_recv, id_recv, w) if sum(recv) else torch.empty((0, hidden), dtype=torch.float32,
+                                                                                    device=h.device)
+        y_back = torch.empty((sum(send), hidden), dtype=torch.float32, device=h.device)
+        dist.all_to_all_single(y_back, y_recv.contiguous(), send, recv, group=self.group)
+        y_picks = torch.empty_like(y_back)
+        y_picks[order] = y_back                           # back to pick order
+        return self.mix_fn(y_picks, gates, self.shared_fn(h, w)), ids, gates

@@ -228,3 +228,12 @@ def moe(h, ids, gates, w_in, w_out, *, add=None, first: int = 0):
     check(lib.ts_moe_bf16(_ptr(h), _ptr(ids), _ptr(gates), _ptr(add), _ptr(w_in), _ptr(w_out), _ptr(y), rows, top,
                           experts, first, hidden, two_f // 2, _ptr(ws), nbytes, _stream()))
     return y
+
+
+def moe_mix(y_picks, gates, add=None):
+    """out[r] = sum_p gates[r, p] y_picks[r * top + p] (+ add[r]) in pick order: ts_moe_mix."""
+    rows, top = gates.shape
+    hidden = y_picks.shape[-1]
+    out = torch.empty((rows, hidden), dtype=torch.float32, device=y_picks.device)
+    check(lib.ts_moe_mix(_ptr(y_picks), _ptr(gates), _ptr(add), _ptr(out), rows, top, hidden, _stream()))
+    return out
