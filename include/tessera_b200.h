@@ -148,10 +148,10 @@ void ts_rope_inv_freq(float theta, uint32_t width, float *out);
  * UINT32_MAX; Within(n): both n; Back(n): back = n, ahead = 0.  The score scale (> 0) is applied to
  * the dot products, where the reference runs a separate `map` launch on q.
  *   q [seqs, queries, heads, width], k/v [seqs, keys, kv_heads, width], out like q; all bf16.
- * With cu_seqlens (device u32 [seqs + 1], width 128 only) the sequences are packed back to back:
+ * With cu_seqlens (device u32 [seqs + 1], widths 128 and 256) the sequences are packed back to back:
  * q/k/v/out are [total, heads|kv_heads, width], sequence s owns rows [cu[s], cu[s+1]) as both its
  * queries and its keys, `queries` bounds the longest sequence and `keys` is the total row count.
- * Width 128 runs on tcgen05 (no workspace); widths 64 and 256 take the ragged-rows kernel and need
+ * Widths 128 and 256 run on tcgen05 (no workspace); width 64 takes the ragged-rows kernel and needs
  * the workspace ts_attend_workspace_bytes reports. */
 size_t ts_attend_workspace_bytes(uint32_t seqs, uint32_t queries, uint32_t keys, uint32_t heads,
                                  uint32_t kv_heads, uint32_t width);
@@ -196,6 +196,12 @@ int ts_top_k(const void *x, int x_dtype, uint32_t *ids, uint32_t rows, uint32_t 
  * has to be cleared, each call overwrites what it reads - so two calls that overlap on the GPU (two
  * streams, two threads) race: serialise them. */
 int ts_top_1_static(const void *x, int x_dtype, uint32_t *ids, uint32_t rows, uint32_t width, void *stream);
+
+/* out[s, :] = mean over the rows [cu_seqlens[s], cu_seqlens[s + 1]) of x (the graph's `.mean(1)`,
+ * engine/models/src/eg2.rs:249; sums x / count in row order as engine/ir/interp/src/cpu.rs:449-473), then
+ * with normalize != 0 scaled to unit length (frontend/tasks/src/embed.rs:47-52).  x, out f32. */
+int ts_mean_pool(const float *x, const uint32_t *cu_seqlens, float *out, uint32_t seqs, uint32_t width,
+                 int normalize, void *stream);
 
 /* gates[r, :] = softmax(x[r, ids[r, :]]) — the router's `take` + `softmax`
  * (engine/models/src/decoder.rs:73-75).  x f32 [rows, width], ids u32 [rows, k], gates f32. */

@@ -57,6 +57,7 @@ SIGNATURES = {
     "ts_moe_bf16": (i32, [vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u32, vp, sz, vp]),
     "ts_moe_mix": (i32, [vp, vp, vp, vp, u32, u32, u32, vp]),
     "ts_moe_permutation": (i32, [vp, vp, vp, vp, vp, u32, u32, u32, vp]),
+    "ts_mean_pool": (i32, [vp, vp, vp, u32, u32, i32, vp]),
     "ts_take_softmax": (i32, [vp, vp, vp, u32, u32, u32, vp]),
 }
 

@@ -225,10 +225,10 @@ int ts_attend_bf16(const void *q, const void *k, const void *v, void *out, const
         const uint32_t total_q = cu_seqlens ? 0xFFFFFFFFu : seqs * queries;
         (void)total_q;
         return attend_flash(q, k, v, out, cu_seqlens, seqs, queries, keys, cu_seqlens ? keys : seqs * queries,
-                            cu_seqlens ? keys : seqs * keys, heads, kv_heads, back, ahead, scale, s);
+                            cu_seqlens ? keys : seqs * keys, heads, kv_heads, width, back, ahead, scale, s);
     }
-    TS_REQUIRE(!cu_seqlens, "attend: packed sequences need width 128 (got %u)", width);
-    TS_REQUIRE(width == 64 || width == 256, "attend: width %u is not 64, 128 or 256", width);
+    TS_REQUIRE(!cu_seqlens, "attend: packed sequences need width 128 or 256 (got %u)", width);
+    TS_REQUIRE(width == 64, "attend: width %u is not 64, 128 or 256", width);
     const size_t rows = (size_t)seqs * queries;
     const size_t need = ts_attend_workspace_bytes(seqs, queries, keys, heads, kv_heads, width);
     TS_REQUIRE(workspace && workspace_bytes >= need, "attend: workspace of %zu bytes is smaller than the %zu needed",
@@ -307,6 +307,13 @@ int ts_top_1_static(const void *x, int x_dtype, uint32_t *ids, uint32_t rows, ui
     TS_REQUIRE(x_dtype == TS_BF16 || x_dtype == TS_F32, "top_1_static: unknown dtype");
     TS_REQUIRE(width > 0, "top_1_static: width is zero");
     return top_1_static(x, x_dtype, ids, rows, width, (cudaStream_t)stream);
+}
+
+int ts_mean_pool(const float *x, const uint32_t *cu_seqlens, float *out, uint32_t seqs, uint32_t width, int normalize,
+                 void *stream) {
+    TS_REQUIRE(x && cu_seqlens && out, "mean_pool: a buffer is NULL");
+    TS_REQUIRE(width > 0, "mean_pool: width is zero");
+    return mean_pool(x, cu_seqlens, out, seqs, width, normalize, (cudaStream_t)stream);
 }
 
 int ts_take_softmax(const float *x, const uint32_t *ids, float *gates, uint32_t rows, uint32_t width, uint32_t k,

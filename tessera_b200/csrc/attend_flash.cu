@@ -1,18 +1,22 @@
-// Whole-sequence (prefill) attention on the 5th-generation tensor cores.
+// Whole-sequence (prefill) attention on the 5th-generation tensor cores, head widths 128 and 256.
 //
-// One block owns 128 queries of one (sequence, head) and walks the visible keys 128 at a time:
-//   S  = Q K^T   tcgen05.mma 128x128x16, Q and K tiles K-major in shared memory (TMA, 128 B swizzle),
+// One block owns 128 queries of one (sequence, head) and walks the visible keys BK at a time (128 keys
+// at width 128, 64 at width 256):
+//   S  = Q K^T   tcgen05.mma 128 x BK x 16, Q and K tiles K-major in shared memory (TMA, 128 B swizzle),
 //                S (f32) in tensor memory, two buffers
-//   P  = exp2(S * scale*log2e - max)   one softmax thread per query row reads its S row from TMEM
-//                (no shuffles: the row is private to the thread), applies the mask window, keeps the
-//                running max / sum, and writes P as bf16 pairs back into the same TMEM columns
-//   PV = P V     tcgen05.mma with A from TMEM (P) and V as an MN-major shared-memory operand (the V
-//                tile is stored [key][dim] as TMA delivers it), result in a second pair of TMEM buffers
-//   O  = (O + PV_prev) * alpha   accumulated in registers by the row's thread, normalised at the end.
-// The MMA thread runs one block ahead (S of block j+1 is computed while block j is in softmax) and
-// TMA keeps two K and two V tiles in flight.  Warp roles: 0 = TMA, 1 = MMA (owns TMEM), 2..5 =
-// softmax / output.  Masks are the reference's per-query window [pos - back, pos + ahead] with
-// query and key ends aligned (engine/ir/graph/src/node.rs:162-187; engine/ir/interp/src/cpu.rs:61-77).
+//   P  = exp2(S * scale*log2e - m)   one softmax thread per query row reads its S row from TMEM (no
+//                shuffles: the row is private to the thread), applies the mask window, and writes P as
+//                bf16 pairs back into the same TMEM columns
+//   O += P V     tcgen05.mma with A from TMEM (P) and V as an MN-major shared-memory operand (the V tile
+//                is stored [key][dim] as TMA delivers it); O (f32, 128 x width) accumulates in TMEM over
+//                all key blocks
+// The maximum m the probabilities are taken against may lag the true running maximum by up to 8 (log2
+// units): O and the running sum are rescaled (TMEM load, multiply, store) only when the maximum runs
+// further ahead, which is rare after the first blocks, so the softmax thread's steady-state work is two
+// passes over S.  The MMA thread runs one block ahead (S of block j+1 while block j is in softmax) and
+// TMA keeps two K and two V tiles in flight.  Warp roles: 0 = TMA, 1 = MMA (owns TMEM), 2..5 = softmax
+// and output.  Masks are the reference's per-query window [pos - back, pos + ahead] with query and key
+// ends aligned (engine/ir/graph/src/node.rs:162-187; engine/ir/interp/src/cpu.rs:61-77).
 //
 // Stands in for the `flash*` rules (engine/rules/attention/src/flash.rs:415-502, launch 648-668).
 #include <cmath>
@@ -25,11 +29,9 @@ namespace {
 
 using namespace ptx;
 
-constexpr uint32_t kTile = 128;     // queries per block, keys per step
-constexpr uint32_t kD = 128;        // head width
+constexpr uint32_t kTile = 128;     // queries per block = TMEM lanes
 constexpr uint32_t kThreads = 192;
-constexpr uint32_t kChunkBytes = kTile * 64 * 2;  // one 64-wide slice of a 128-row tile: 16 KiB
-constexpr uint32_t kTileBytes = 2 * kChunkBytes;  // 128 x 128 bf16
+constexpr float kRescaleStep = 8.0f;  // log2 units the row maximum may run ahead of the one in use
 
 struct FlashParams {
     uint16_t *out;
@@ -41,12 +43,23 @@ struct FlashParams {
     int *status;
 };
 
-struct FlashSmem {
+// D: head width (128 or 256).  BK keys per step: 128 at width 128, 64 at width 256, so that Q plus
+// two K and two V tiles fit shared memory and S (2 buffers) plus O fit the 512 TMEM columns.
+template <uint32_t D>
+struct FlashShape {
+    static constexpr uint32_t BK = D == 128 ? 128 : 64;
+    static constexpr uint32_t chunks = D / 64;                 // 64-wide slices of the head width
+    static constexpr uint32_t q_chunk = kTile * 128;           // bytes of one slice of the Q tile
+    static constexpr uint32_t kv_chunk = BK * 128;             // bytes of one slice of a K or V tile
+    static constexpr uint32_t q_bytes = chunks * q_chunk;
+    static constexpr uint32_t kv_bytes = chunks * kv_chunk;
     static constexpr uint32_t q_off = 0;
-    static constexpr uint32_t k_off = kTileBytes;
-    static constexpr uint32_t v_off = k_off + 2 * kTileBytes;
-    static constexpr uint32_t bar_off = v_off + 2 * kTileBytes;
+    static constexpr uint32_t k_off = q_bytes;
+    static constexpr uint32_t v_off = k_off + 2 * kv_bytes;
+    static constexpr uint32_t bar_off = v_off + 2 * kv_bytes;
     static constexpr uint32_t total = bar_off + 256 + 1024;
+    static constexpr uint32_t s_col = 0;                       // S / P buffers at 0 and BK
+    static constexpr uint32_t o_col = 2 * BK;                  // O: D columns
 };
 
 __device__ __forceinline__ uint32_t sat_add(uint32_t a, uint32_t b) {
@@ -54,16 +67,19 @@ __device__ __forceinline__ uint32_t sat_add(uint32_t a, uint32_t b) {
     return s < a ? 0xFFFFFFFFu : s;
 }
 
+template <uint32_t D>
 __global__ void __launch_bounds__(kThreads, 1)
 attend_flash_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, const FlashParams p) {
+    using Sh = FlashShape<D>;
+    constexpr uint32_t BK = Sh::BK;
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    unsigned char *smem_q = smem + FlashSmem::q_off;
-    unsigned char *smem_k = smem + FlashSmem::k_off;
-    unsigned char *smem_v = smem + FlashSmem::v_off;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + FlashSmem::bar_off);
+    unsigned char *smem_q = smem + Sh::q_off;
+    unsigned char *smem_k = smem + Sh::k_off;
+    unsigned char *smem_v = smem + Sh::v_off;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + Sh::bar_off);
     uint64_t *q_full = bars;          // [1]
     uint64_t *k_full = bars + 1;      // [2]
     uint64_t *v_full = bars + 3;      // [2]
@@ -71,9 +87,8 @@ attend_flash_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     uint64_t *v_empty = bars + 7;     // [2]
     uint64_t *s_full = bars + 9;      // [2]
     uint64_t *p_full = bars + 11;     // [2]
-    uint64_t *pv_full = bars + 13;    // [2]
-    uint64_t *pv_empty = bars + 15;   // [2]
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 17);
+    uint64_t *pv_done = bars + 13;    // [2]
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 15);
     volatile uint32_t *abort_flag = tmem_slot + 1;
 
     // Heavier tiles (later queries see more keys under a causal mask) first.
@@ -97,8 +112,8 @@ attend_flash_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const uint32_t pos_first = past + t0, pos_last = past + t0 + rows_here - 1;
     const uint32_t lo = pos_first > p.back ? pos_first - p.back : 0;
     const uint32_t hi = min(k_len, sat_add(sat_add(pos_last, p.ahead), 1));
-    const uint32_t jb0 = lo / kTile;
-    const uint32_t nb = hi > lo ? (hi + kTile - 1) / kTile - jb0 : 0;
+    const uint32_t jb0 = lo / BK;
+    const uint32_t nb = hi > lo ? (hi + BK - 1) / BK - jb0 : 0;
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
@@ -109,8 +124,7 @@ attend_flash_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             mbar_init(&v_empty[s], 1);
             mbar_init(&s_full[s], 1);
             mbar_init(&p_full[s], 4);
-            mbar_init(&pv_full[s], 1);
-            mbar_init(&pv_empty[s], 4);
+            mbar_init(&pv_done[s], 1);
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -125,31 +139,30 @@ attend_flash_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-    // TMEM columns: S/P buffers at 0 and 128, PV buffers at 256 and 384.
 
     if (warp == 0) {
         if (lane == 0 && nb > 0) {
             pdl_wait();
-            mbar_expect_tx(q_full, kTileBytes);
-            for (uint32_t c = 0; c < 2; c++)
-                tma_load_2d(smem_q + c * kChunkBytes, &map_q, q_full, (int32_t)(head * kD + c * 64),
+            mbar_expect_tx(q_full, Sh::q_bytes);
+            for (uint32_t c = 0; c < Sh::chunks; c++)
+                tma_load_2d(smem_q + c * Sh::q_chunk, &map_q, q_full, (int32_t)(head * D + c * 64),
                             (int32_t)(q_begin + t0));
             bool ok = true;
             for (uint32_t j = 0; j < nb && ok; j++) {
                 const uint32_t s = j & 1, ph = (j >> 1) & 1;
-                const int32_t krow = (int32_t)(k_begin + (jb0 + j) * kTile);
+                const int32_t krow = (int32_t)(k_begin + (jb0 + j) * BK);
                 ok = mbar_wait_or_abort(&k_empty[s], ph ^ 1, abort_flag);
                 if (!ok) break;
-                mbar_expect_tx(&k_full[s], kTileBytes);
-                for (uint32_t c = 0; c < 2; c++)
-                    tma_load_2d(smem_k + s * kTileBytes + c * kChunkBytes, &map_k, &k_full[s],
-                                (int32_t)(kvh * kD + c * 64), krow);
+                mbar_expect_tx(&k_full[s], Sh::kv_bytes);
+                for (uint32_t c = 0; c < Sh::chunks; c++)
+                    tma_load_2d(smem_k + s * Sh::kv_bytes + c * Sh::kv_chunk, &map_k, &k_full[s],
+                                (int32_t)(kvh * D + c * 64), krow);
                 ok = mbar_wait_or_abort(&v_empty[s], ph ^ 1, abort_flag);
                 if (!ok) break;
-                mbar_expect_tx(&v_full[s], kTileBytes);
-                for (uint32_t c = 0; c < 2; c++)
-                    tma_load_2d(smem_v + s * kTileBytes + c * kChunkBytes, &map_v, &v_full[s],
-                                (int32_t)(kvh * kD + c * 64), krow);
+                mbar_expect_tx(&v_full[s], Sh::kv_bytes);
+                for (uint32_t c = 0; c < Sh::chunks; c++)
+                    tma_load_2d(smem_v + s * Sh::kv_bytes + c * Sh::kv_chunk, &map_v, &v_full[s],
+                                (int32_t)(kvh * D + c * 64), krow);
             }
             pdl_launch_dependents();
             // Copies in flight land before the MMAs that release their stages; wait for those releases.
@@ -161,18 +174,18 @@ attend_flash_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         }
     } else if (warp == 1) {
         if (lane == 0 && nb > 0) {
-            const uint32_t idesc_qk = umma_idesc_bf16(kTile, kTile, false, false);
-            const uint32_t idesc_pv = umma_idesc_bf16(kTile, kD, false, true);  // V is MN-major
+            const uint32_t idesc_qk = umma_idesc_bf16(kTile, BK, false, false);
+            const uint32_t idesc_pv = umma_idesc_bf16(kTile, D, false, true);  // V is MN-major
             bool ok = mbar_wait_or_abort(q_full, 0, abort_flag);
             auto issue_qk = [&](uint32_t j) -> bool {
                 const uint32_t s = j & 1, ph = (j >> 1) & 1;
                 if (!mbar_wait_or_abort(&k_full[s], ph, abort_flag)) return false;
                 tc_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + s * 128;
+                const uint32_t d_tmem = tmem_base + Sh::s_col + s * BK;
 #pragma unroll
-                for (uint32_t c = 0; c < 2; c++) {
-                    const uint64_t da = umma_desc_k_sw128(smem_addr(smem_q + c * kChunkBytes));
-                    const uint64_t db = umma_desc_k_sw128(smem_addr(smem_k + s * kTileBytes + c * kChunkBytes));
+                for (uint32_t c = 0; c < Sh::chunks; c++) {
+                    const uint64_t da = umma_desc_k_sw128(smem_addr(smem_q + c * Sh::q_chunk));
+                    const uint64_t db = umma_desc_k_sw128(smem_addr(smem_k + s * Sh::kv_bytes + c * Sh::kv_chunk));
 #pragma unroll
                     for (uint32_t k16 = 0; k16 < 4; k16++)
                         umma_bf16(d_tmem, da + 2 * k16, db + 2 * k16, idesc_qk, (c | k16) != 0);
@@ -188,22 +201,21 @@ attend_flash_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     ok = issue_qk(j + 1);
                     if (!ok) break;
                 }
-                ok = mbar_wait_or_abort(&p_full[s], ph, abort_flag) && mbar_wait_or_abort(&v_full[s], ph, abort_flag) &&
-                     mbar_wait_or_abort(&pv_empty[s], ph ^ 1, abort_flag);
+                ok = mbar_wait_or_abort(&p_full[s], ph, abort_flag) && mbar_wait_or_abort(&v_full[s], ph, abort_flag);
                 if (!ok) break;
                 tc_fence_after_sync();
-                const uint32_t p_tmem = tmem_base + s * 128;        // bf16 pairs: 16 keys = 8 columns
-                const uint32_t d_tmem = tmem_base + 256 + s * 128;
-                const uint32_t v_addr = smem_addr(smem_v + s * kTileBytes);
+                const uint32_t p_tmem = tmem_base + Sh::s_col + s * BK;  // bf16 pairs: 16 keys = 8 columns
+                const uint32_t o_tmem = tmem_base + Sh::o_col;
+                const uint32_t v_addr = smem_addr(smem_v + s * Sh::kv_bytes);
 #pragma unroll
-                for (uint32_t k16 = 0; k16 < 8; k16++) {
-                    // 16 keys = 16 rows of 128 bytes further down the V tile; the two 64-wide halves of
-                    // the head dimension are kChunkBytes apart, 8-row groups 1024 bytes apart.
-                    const uint64_t db = umma_desc_mn_sw128(v_addr + k16 * 2048, kChunkBytes, 1024);
-                    umma_bf16_ts(d_tmem, p_tmem + k16 * 8, db, idesc_pv, k16 != 0);
+                for (uint32_t k16 = 0; k16 < BK / 16; k16++) {
+                    // 16 keys = 16 rows of 128 bytes further down the V tile; the 64-wide slices of the head
+                    // width are kv_chunk bytes apart, 8-row groups 1024 bytes apart.
+                    const uint64_t db = umma_desc_mn_sw128(v_addr + k16 * 2048, Sh::kv_chunk, 1024);
+                    umma_bf16_ts(o_tmem, p_tmem + k16 * 8, db, idesc_pv, (j | k16) != 0);
                 }
                 umma_commit(&v_empty[s]);
-                umma_commit(&pv_full[s]);
+                umma_commit(&pv_done[s]);
             }
         }
     } else {
@@ -215,106 +227,116 @@ attend_flash_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         const uint32_t pos = past + t0 + row;
         const uint32_t from = pos > p.back ? pos - p.back : 0;
         const uint32_t to = min(k_len, sat_add(sat_add(pos, p.ahead), 1));
-        float o[kD];
-#pragma unroll
-        for (uint32_t i = 0; i < kD; i++) o[i] = 0.0f;
-        float m_run = -INFINITY, l_run = 0.0f;
+        const uint32_t o_tmem = tmem_base + lane_base + Sh::o_col;
+        float m_use = -INFINITY;  // the maximum the probabilities are taken against (may lag the true one)
+        float l_run = 0.0f;
         bool ok = true;
         for (uint32_t j = 0; j < nb && ok; j++) {
             const uint32_t s = j & 1, ph = (j >> 1) & 1;
             ok = mbar_wait_or_abort(&s_full[s], ph, abort_flag);
             if (!ok) break;
             tc_fence_after_sync();
-            const uint32_t s_tmem = tmem_base + lane_base + s * 128;
-            const uint32_t key0 = (jb0 + j) * kTile;
+            const uint32_t s_tmem = tmem_base + lane_base + Sh::s_col + s * BK;
+            const uint32_t key0 = (jb0 + j) * BK;
+            // Keys of this block the row sees: [c_from, c_to) in block columns.
+            const uint32_t c_from = from > key0 ? min(from - key0, BK) : 0;
+            const uint32_t c_to = to > key0 ? min(to - key0, BK) : 0;
             // Pass 1: the row's maximum over this block's visible keys.
             float m_blk = -INFINITY;
 #pragma unroll
-            for (uint32_t c0 = 0; c0 < kTile; c0 += 32) {
+            for (uint32_t c0 = 0; c0 < BK; c0 += 32) {
                 uint32_t r[32];
                 tmem_ld_32x32(s_tmem + c0, r);
                 tmem_ld_wait();
 #pragma unroll
                 for (uint32_t c = 0; c < 32; c++) {
-                    const uint32_t key = key0 + c0 + c;
-                    const float v = (key >= from && key < to) ? __uint_as_float(r[c]) : -INFINITY;
+                    const float v = (c0 + c >= c_from && c0 + c < c_to) ? __uint_as_float(r[c]) : -INFINITY;
                     m_blk = fmaxf(m_blk, v);
                 }
             }
-            const float m_new = fmaxf(m_run, m_blk * p.scale_log2);
-            const float m_use = m_new == -INFINITY ? 0.0f : m_new;
-            const float alpha = exp2f(m_run - m_use);  // 0 when nothing was seen before
+            const float m_new = fmaxf(m_use, m_blk * p.scale_log2);
+            // Rescale O and the running sum only when the maximum ran ahead by more than kRescaleStep:
+            // probabilities stay below 2^kRescaleStep, and after the first blocks this is rare.
+            float alpha = 1.0f;
+            bool need = false;
+            if (m_new > m_use + kRescaleStep || m_use == -INFINITY) {
+                need = l_run > 0.0f;
+                alpha = need ? exp2f(m_use - m_new) : 1.0f;
+                m_use = m_new;
+            }
+            if (__any_sync(0xFFFFFFFFu, need)) {
+                // O is complete up to the previous block once its MMAs are done.
+                const uint32_t sp = (j - 1) & 1, php = ((j - 1) >> 1) & 1;
+                ok = mbar_wait_or_abort(&pv_done[sp], php, abort_flag);
+                if (!ok) break;
+                tc_fence_after_sync();
+#pragma unroll
+                for (uint32_t c0 = 0; c0 < D; c0 += 32) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(o_tmem + c0, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (uint32_t c = 0; c < 32; c++) r[c] = __float_as_uint(__uint_as_float(r[c]) * alpha);
+                    tmem_st_32x32(o_tmem + c0, r);
+                }
+                l_run *= alpha;
+            }
+            const float m_sub = m_use == -INFINITY ? 0.0f : m_use;
             // Pass 2: probabilities, written back as bf16 pairs behind the read position.
             float l_blk = 0.0f;
 #pragma unroll
-            for (uint32_t c0 = 0; c0 < kTile; c0 += 32) {
+            for (uint32_t c0 = 0; c0 < BK; c0 += 32) {
                 uint32_t r[32];
                 tmem_ld_32x32(s_tmem + c0, r);
                 tmem_ld_wait();
                 uint32_t packed[16];
 #pragma unroll
                 for (uint32_t c = 0; c < 32; c += 2) {
-                    const uint32_t key = key0 + c0 + c;
-                    float p0 = (key >= from && key < to) ? exp2f(__uint_as_float(r[c]) * p.scale_log2 - m_use) : 0.0f;
-                    float p1 = (key + 1 >= from && key + 1 < to) ? exp2f(__uint_as_float(r[c + 1]) * p.scale_log2 - m_use)
-                                                                  : 0.0f;
+                    const uint32_t cc = c0 + c;
+                    const float p0 = (cc >= c_from && cc < c_to) ? exp2f(__uint_as_float(r[c]) * p.scale_log2 - m_sub) : 0.0f;
+                    const float p1 = (cc + 1 >= c_from && cc + 1 < c_to)
+                                         ? exp2f(__uint_as_float(r[c + 1]) * p.scale_log2 - m_sub)
+                                         : 0.0f;
                     l_blk += p0 + p1;
                     packed[c >> 1] = pack_bf16(p0, p1);
                 }
                 tmem_st_32x16(s_tmem + (c0 >> 1), packed);
             }
+            l_run += l_blk;
             tmem_st_wait();
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&p_full[s]);
-            // Fold in the previous block's P V (relative to the previous maximum), then rescale.
-            if (j > 0) {
-                const uint32_t sp = (j - 1) & 1, php = ((j - 1) >> 1) & 1;
-                ok = mbar_wait_or_abort(&pv_full[sp], php, abort_flag);
-                if (!ok) break;
-                tc_fence_after_sync();
-                const uint32_t pv_tmem = tmem_base + lane_base + 256 + sp * 128;
-#pragma unroll
-                for (uint32_t c0 = 0; c0 < kD; c0 += 32) {
-                    uint32_t r[32];
-                    tmem_ld_32x32(pv_tmem + c0, r);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (uint32_t c = 0; c < 32; c++) o[c0 + c] += __uint_as_float(r[c]);
-                }
-                tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&pv_empty[sp]);
-            }
-#pragma unroll
-            for (uint32_t i = 0; i < kD; i++) o[i] *= alpha;
-            l_run = l_run * alpha + l_blk;
-            m_run = m_new;
         }
         if (ok && nb > 0) {
             const uint32_t sp = (nb - 1) & 1, php = ((nb - 1) >> 1) & 1;
-            ok = mbar_wait_or_abort(&pv_full[sp], php, abort_flag);
-            if (ok) {
-                tc_fence_after_sync();
-                const uint32_t pv_tmem = tmem_base + lane_base + 256 + sp * 128;
-#pragma unroll
-                for (uint32_t c0 = 0; c0 < kD; c0 += 32) {
-                    uint32_t r[32];
-                    tmem_ld_32x32(pv_tmem + c0, r);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (uint32_t c = 0; c < 32; c++) o[c0 + c] += __uint_as_float(r[c]);
-                }
-            }
+            ok = mbar_wait_or_abort(&pv_done[sp], php, abort_flag);
+            if (ok) tc_fence_after_sync();
         }
-        if (ok && row_ok) {
+        if (ok) {
             const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-            uint16_t *dst = p.out + ((size_t)(q_begin + t0 + row) * p.heads + head) * kD;
+            uint16_t *dst = p.out + ((size_t)(q_begin + t0 + row) * p.heads + head) * D;
 #pragma unroll
-            for (uint32_t i = 0; i < kD; i += 8) {
-                uint4 pk = make_uint4(pack_bf16(o[i] * inv, o[i + 1] * inv), pack_bf16(o[i + 2] * inv, o[i + 3] * inv),
-                                      pack_bf16(o[i + 4] * inv, o[i + 5] * inv), pack_bf16(o[i + 6] * inv, o[i + 7] * inv));
-                *reinterpret_cast<uint4 *>(dst + i) = pk;
+            for (uint32_t c0 = 0; c0 < D; c0 += 32) {
+                uint32_t r[32];
+                if (nb > 0) {
+                    tmem_ld_32x32(o_tmem + c0, r);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (uint32_t c = 0; c < 32; c++) r[c] = 0;
+                }
+                if (row_ok) {
+#pragma unroll
+                    for (uint32_t i = 0; i < 32; i += 8) {
+                        float f[8];
+#pragma unroll
+                        for (uint32_t e = 0; e < 8; e++) f[e] = __uint_as_float(r[i + e]) * inv;
+                        *reinterpret_cast<uint4 *>(dst + c0 + i) =
+                            make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]),
+                                       pack_bf16(f[6], f[7]));
+                    }
+                }
             }
         }
     }
@@ -339,19 +361,36 @@ int flash_take_status() {
     return v;
 }
 
-bool flash_supports(uint32_t width) { return width == kD; }
+bool flash_supports(uint32_t width) { return width == 128 || width == 256; }
 
-// q [total_q, heads, 128], k/v [total_k, kv_heads, 128], out like q (rows packed sequence after sequence).
+template <uint32_t D>
+static int launch_flash(const void *q, const void *k, const void *v, const FlashParams &p, uint32_t total_q,
+                        uint32_t total_k, cudaStream_t stream) {
+    using Sh = FlashShape<D>;
+    CUtensorMap map_q, map_k, map_v;
+    int rc = make_tensor_map_2d(&map_q, q, total_q, (uint64_t)p.heads * D, (uint64_t)p.heads * D, kTile, 64);
+    if (rc != TS_OK) return rc;
+    rc = make_tensor_map_2d(&map_k, k, total_k, (uint64_t)p.kv_heads * D, (uint64_t)p.kv_heads * D, Sh::BK, 64);
+    if (rc != TS_OK) return rc;
+    rc = make_tensor_map_2d(&map_v, v, total_k, (uint64_t)p.kv_heads * D, (uint64_t)p.kv_heads * D, Sh::BK, 64);
+    if (rc != TS_OK) return rc;
+    static bool configured = false;
+    if (!configured) {
+        TS_CUDA(cudaFuncSetAttribute(attend_flash_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Sh::total));
+        configured = true;
+    }
+    cudaError_t e = launch(attend_flash_kernel<D>, dim3(p.q_tiles, p.heads, p.seqs), dim3(kThreads), Sh::total, stream,
+                           pdl_enabled(), map_q, map_k, map_v, p);
+    if (e != cudaSuccess)
+        return fail(TS_ERR_CUDA, "launch of attend_flash failed: %s (%d) %s", cudaGetErrorName(e), (int)e,
+                    cudaGetErrorString(e));
+    return TS_OK;
+}
+
+// q [total_q, heads, width], k/v [total_k, kv_heads, width], out like q (rows packed sequence after sequence).
 int attend_flash(const void *q, const void *k, const void *v, void *out, const uint32_t *cu_seqlens, uint32_t seqs,
                  uint32_t queries, uint32_t keys, uint32_t total_q, uint32_t total_k, uint32_t heads, uint32_t kv_heads,
-                 uint32_t back, uint32_t ahead, float scale, cudaStream_t stream) {
-    CUtensorMap map_q, map_k, map_v;
-    int rc = make_tensor_map_2d(&map_q, q, total_q, (uint64_t)heads * kD, (uint64_t)heads * kD, kTile, 64);
-    if (rc != TS_OK) return rc;
-    rc = make_tensor_map_2d(&map_k, k, total_k, (uint64_t)kv_heads * kD, (uint64_t)kv_heads * kD, kTile, 64);
-    if (rc != TS_OK) return rc;
-    rc = make_tensor_map_2d(&map_v, v, total_k, (uint64_t)kv_heads * kD, (uint64_t)kv_heads * kD, kTile, 64);
-    if (rc != TS_OK) return rc;
+                 uint32_t width, uint32_t back, uint32_t ahead, float scale, cudaStream_t stream) {
     FlashParams p = {};
     p.out = (uint16_t *)out;
     p.cu_seqlens = cu_seqlens;
@@ -367,17 +406,8 @@ int attend_flash(const void *q, const void *k, const void *v, void *out, const u
     int *status = nullptr;
     TS_CUDA(cudaGetSymbolAddress((void **)&status, g_flash_status));
     p.status = status;
-    static bool configured = false;
-    if (!configured) {
-        TS_CUDA(cudaFuncSetAttribute(attend_flash_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FlashSmem::total));
-        configured = true;
-    }
-    cudaError_t e = launch(attend_flash_kernel, dim3(p.q_tiles, heads, seqs), dim3(kThreads), FlashSmem::total, stream,
-                           pdl_enabled(), map_q, map_k, map_v, p);
-    if (e != cudaSuccess)
-        return fail(TS_ERR_CUDA, "launch of attend_flash failed: %s (%d) %s", cudaGetErrorName(e), (int)e,
-                    cudaGetErrorString(e));
-    return TS_OK;
+    if (width == 128) return launch_flash<128>(q, k, v, p, total_q, total_k, stream);
+    return launch_flash<256>(q, k, v, p, total_q, total_k, stream);
 }
 
 }  // namespace ts

@@ -316,6 +316,28 @@ __global__ void iota_rows_kernel(uint32_t *slots, uint32_t *positions, uint32_t 
     pdl_launch_dependents();
 }
 
+// Mean over each packed sequence's rows, then unit length: the embedding head.  The mean sums
+// x * (1 / count) in row order (engine/ir/interp/src/cpu.rs:449-473); the unit scale divides by
+// max(sqrt(sum of squares), 1e-12) (frontend/tasks/src/embed.rs:47-52).  One block per sequence.
+__global__ void __launch_bounds__(256) mean_pool_kernel(const float *x, const uint32_t *cu_seqlens, float *out,
+                                                        uint32_t width, int normalize) {
+    __shared__ float scratch[8];
+    pdl_wait();
+    const uint32_t a = cu_seqlens[blockIdx.x], b = cu_seqlens[blockIdx.x + 1];
+    const float w = b > a ? 1.0f / (float)(b - a) : 0.0f;
+    float ss = 0.0f;
+    for (uint32_t j = threadIdx.x; j < width; j += blockDim.x) {
+        float acc = 0.0f;
+        for (uint32_t t = a; t < b; t++) acc = __fadd_rn(acc, __fmul_rn(x[(size_t)t * width + j], w));
+        out[(size_t)blockIdx.x * width + j] = acc;
+        ss = fmaf(acc, acc, ss);
+    }
+    if (!normalize) return;
+    ss = block_sum(ss, scratch);
+    const float norm = fmaxf(sqrtf(ss), 1e-12f);
+    for (uint32_t j = threadIdx.x; j < width; j += blockDim.x) out[(size_t)blockIdx.x * width + j] /= norm;
+}
+
 // Holds the stream until the host sets *flag, so that launches queued behind it run back to back
 // and per-kernel event intervals exclude host launch gaps.  One thread; gives up after `spins` reads
 // (engine/gpu/gpukit/src/gate.cu does the same with 2^21).
@@ -335,6 +357,15 @@ int iota_rows(uint32_t *slots, uint32_t *positions, uint32_t seqs, uint32_t quer
     cudaError_t e = launch(iota_rows_kernel, dim3(ceil_div(total, 256)), dim3(256), 0, stream, pdl_enabled(), slots,
                            positions, total, queries, past);
     if (e != cudaSuccess) return fail(TS_ERR_CUDA, "launch of iota_rows failed: %s", cudaGetErrorString(e));
+    return TS_OK;
+}
+
+int mean_pool(const float *x, const uint32_t *cu_seqlens, float *out, uint32_t seqs, uint32_t width, int normalize,
+              cudaStream_t stream) {
+    if (seqs == 0) return TS_OK;
+    cudaError_t e = launch(mean_pool_kernel, dim3(seqs), dim3(256), 0, stream, pdl_enabled(), x, cu_seqlens, out, width,
+                           normalize);
+    if (e != cudaSuccess) return fail(TS_ERR_CUDA, "launch of mean_pool failed: %s", cudaGetErrorString(e));
     return TS_OK;
 }
 

@@ -31,12 +31,14 @@ bool flash_supports(uint32_t width);
 int flash_take_status();
 int attend_flash(const void *q, const void *k, const void *v, void *out, const uint32_t *cu_seqlens, uint32_t seqs,
                  uint32_t queries, uint32_t keys, uint32_t total_q, uint32_t total_k, uint32_t heads, uint32_t kv_heads,
-                 uint32_t back, uint32_t ahead, float scale, cudaStream_t stream);
+                 uint32_t width, uint32_t back, uint32_t ahead, float scale, cudaStream_t stream);
 // Fills slots[r] = r / queries, positions[r] = past + r % queries for the rows fallback of whole attention.
 int iota_rows(uint32_t *slots, uint32_t *positions, uint32_t seqs, uint32_t queries, uint32_t past, cudaStream_t stream);
 int rms_norm(const void *x, int x_dtype, const float *w, void *out, int out_dtype, uint32_t rows, uint32_t width,
              float eps, const uint32_t *row_ids, cudaStream_t stream);
 int gate(const volatile uint32_t *flag, cudaStream_t stream);
+int mean_pool(const float *x, const uint32_t *cu_seqlens, float *out, uint32_t seqs, uint32_t width, int normalize,
+              cudaStream_t stream);
 int advance_rows(const uint32_t *ids, uint32_t *tokens, uint32_t *positions, uint32_t rows, cudaStream_t stream);
 int gather_rows(const void *table, const uint32_t *ids, void *out, int out_dtype, uint32_t rows,
                 uint32_t table_rows, uint32_t width, uint32_t first, cudaStream_t stream);

@@ -1,0 +1,77 @@
+"""A bidirectional text encoder of the EmbeddingGemma-300M shape on the library's kernels: packed ragged
+sequences in, one unit-length embedding per sequence out.
+
+Layer order follows the reference's decoder trunk (engine/models/src/decoder.rs:327-389) with the
+embedding model's differences (engine/models/src/eg2.rs): a bidirectional mask, a GeGLU feed-forward
+(tanh GELU), mean pooling over each text's rows and a unit scale (frontend/tasks/src/embed.rs:47-52,
+148-154).  Where the reference groups texts of equal length because it has no kernel for ragged keys
+(frontend/tasks/src/embed.rs:14-17), every text of a batch shares one launch here: rows are packed
+back to back and the attention kernel takes the sequence bounds.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from . import ops
+
+EMBEDDING_300M = dict(layers=24, hidden=768, heads=3, kv_heads=1, head_dim=256, ffn=1152, vocab=262144,
+                      eps=1e-6, theta=1e6)
+
+
+def encoder_weight_names(layers: int) -> list[str]:
+    names = ["embed"]
+    for i in range(layers):
+        names += [f"layers.{i}.{f}" for f in ("ln1", "q", "k", "v", "q_norm", "k_norm", "o", "ln2", "mlp.gate", "mlp.up",
+                                              "mlp.down")]
+    return names + ["norm"]
+
+
+class Encoder:
+    def __init__(self, cfg: dict, named_weights, device="cuda"):
+        self.cfg = dict(cfg)
+        L = cfg["layers"]
+        raw = dict(named_weights)
+        bf = lambda a: torch.from_numpy(np.ascontiguousarray(a).view(np.int16)).view(torch.bfloat16).to(device)
+        f32 = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(device)
+        self.embed = bf(raw["embed"])
+        self.norm = f32(raw["norm"])
+        self.layers = []
+        for i in range(L):
+            g = lambda f: raw[f"layers.{i}.{f}"]
+            self.layers.append(dict(
+                ln1=f32(g("ln1")), ln2=f32(g("ln2")), q_norm=f32(g("q_norm")), k_norm=f32(g("k_norm")),
+                wqkv=bf(np.concatenate([g("q"), g("k"), g("v")], axis=0)), wo=bf(g("o")),
+                wgu=bf(np.concatenate([g("mlp.gate"), g("mlp.up")], axis=0)), wdown=bf(g("mlp.down"))))
+        self.inv_freq = ops.rope_inv_freq(cfg["theta"], cfg["head_dim"], device)
+        self.device = device
+
+    def forward(self, tokens: torch.Tensor, cu_seqlens: torch.Tensor, max_len: int) -> torch.Tensor:
+        """tokens int32 [total] packed, cu_seqlens int32 [seqs + 1] -> float32 [seqs, hidden], unit rows."""
+        c = self.cfg
+        total, seqs = tokens.numel(), cu_seqlens.numel() - 1
+        heads, kvh, d, eps = c["heads"], c["kv_heads"], c["head_dim"], c["eps"]
+        lens = (cu_seqlens[1:] - cu_seqlens[:-1]).to(torch.int64)
+        slots = torch.repeat_interleave(torch.arange(seqs, device=self.device), lens).to(torch.int32)
+        positions = (torch.arange(total, device=self.device) - cu_seqlens[:-1].to(torch.int64)[slots.long()]).to(torch.int32)
+        # Kept layout with one-row pages: table[s * max_len + t] = row of token t of text s in the packed buffer.
+        table = torch.zeros(seqs * max_len, dtype=torch.int32, device=self.device)
+        table[slots.long() * max_len + positions.long()] = torch.arange(total, dtype=torch.int32, device=self.device)
+        kept = ops.Kept("paged", max_len, table, total, page=1)
+        x = ops.gather(self.embed, tokens, out_dtype=torch.float32)
+        q = torch.empty((total, heads, d), dtype=torch.bfloat16, device=self.device)
+        k = torch.empty((total, kvh, d), dtype=torch.bfloat16, device=self.device)
+        v = torch.empty_like(k)
+        scale = float(d) ** -0.5
+        for L in self.layers:
+            h = ops.rms_norm(x, L["ln1"], eps)
+            qkv = ops.linear(h, L["wqkv"])
+            ops.qk_norm_rope_append(qkv, L["q_norm"], L["k_norm"], self.inv_freq, slots, positions, q, k, v, kept,
+                                    heads, kvh, d, eps)
+            a = ops.attend(q, k, v, mask="bidirectional", scale=scale, cu_seqlens=cu_seqlens, max_len=max_len)
+            x = ops.linear(a.view(total, heads * d), L["wo"], x, epilogue="add", out_dtype=torch.float32, out=x)
+            h = ops.rms_norm(x, L["ln2"], eps)
+            act = ops.linear(h, L["wgu"], epilogue="geglu")
+            x = ops.linear(act, L["wdown"], x, epilogue="add", out_dtype=torch.float32, out=x)
+        hidden = ops.rms_norm(x, self.norm, eps, out_dtype=torch.float32)
+        return ops.mean_pool(hidden, cu_seqlens, normalize=True)

@@ -81,10 +81,11 @@ class Kept:
     scalar: int            # kept_stride | kept_slots | kept_pages
     table: torch.Tensor | None = None  # u32 (stored as int32) [slots * kept_pages]
     rows: int = 0
+    page: int | None = None  # rows per page when it is neither 64 ("paged") nor 16 ("paged16")
 
     def c(self) -> TsKept:
         t = self.table
-        return TsKept(KEPT_KIND[self.layout], KEPT_PAGE[self.layout], self.scalar,
+        return TsKept(KEPT_KIND[self.layout], self.page or KEPT_PAGE[self.layout], self.scalar,
                       t.data_ptr() if t is not None else None, t.numel() if t is not None else 0, self.rows)
 
 
@@ -236,4 +237,13 @@ def moe_mix(y_picks, gates, add=None):
     hidden = y_picks.shape[-1]
     out = torch.empty((rows, hidden), dtype=torch.float32, device=y_picks.device)
     check(lib.ts_moe_mix(_ptr(y_picks), _ptr(gates), _ptr(add), _ptr(out), rows, top, hidden, _stream()))
+    return out
+
+
+def mean_pool(x, cu_seqlens, normalize=True):
+    """Per-sequence mean of packed rows, then unit length: ts_mean_pool."""
+    seqs = cu_seqlens.numel() - 1
+    width = x.shape[-1]
+    out = torch.empty((seqs, width), dtype=torch.float32, device=x.device)
+    check(lib.ts_mean_pool(_ptr(x), _ptr(cu_seqlens), _ptr(out), seqs, width, int(normalize), _stream()))
     return out

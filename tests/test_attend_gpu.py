@@ -54,6 +54,39 @@ def test_head_shapes(heads, kv_heads, width, mask):
 
 
 @pytest.mark.parametrize("mask", ["causal", "bidirectional"])
+@pytest.mark.parametrize("mask", ["causal", "bidirectional"])
+def test_packed_sequences_width_256(mask):
+    # the embedding encoder's attention shape: 3 query heads over 1 kv head, 256 wide, ragged lengths
+    rng = np.random.default_rng(6)
+    lens = [32, 200, 65, 512, 64, 129]
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.uint32)
+    total, heads, kv_heads, width = int(cu[-1]), 3, 1, 256
+    q = normal_bf16(rng, (total, heads, width))
+    k = normal_bf16(rng, (total, kv_heads, width))
+    v = normal_bf16(rng, (total, kv_heads, width))
+    scale = float(1.0 / np.sqrt(width))
+    got = _run(q, k, v, mask, scale, cu_seqlens=dev_u32(cu), max_len=max(lens))
+    for s, n in enumerate(lens):
+        a, b = int(cu[s]), int(cu[s + 1])
+        want = O.attend(O.bf16_widen(q[a:b])[None], O.bf16_widen(k[a:b])[None], O.bf16_widen(v[a:b])[None], mask, scale)[0]
+        assert rel_error(got[a:b], want) <= TOL, (s, n)
+
+
+def test_large_score_range_rescales():
+    # scores that keep growing along the keys force the lagging maximum to be rescaled block after block
+    rng = np.random.default_rng(8)
+    n, heads, width = 700, 2, 128
+    q = normal_bf16(rng, (1, n, heads, width))
+    ramp = np.linspace(0.2, 6.0, n, dtype=np.float32)[None, :, None, None]
+    k = O.bf16_bits(O.bf16_widen(q[:, :, :1]) * ramp)  # key j aligned with query j, growing norm
+    v = normal_bf16(rng, (1, n, 1, width))
+    for mask in ("causal", "bidirectional"):
+        want = O.attend(O.bf16_widen(q), O.bf16_widen(k), O.bf16_widen(v), mask, 0.5)
+        got = _run(q, k, v, mask, 0.5)
+        assert rel_error(got, want) <= TOL
+
+
+@pytest.mark.parametrize("mask", ["causal", "bidirectional"])
 def test_packed_sequences(mask):
     # ragged lengths packed back to back, the embedding batch's shape (lengths 32..512)
     rng = np.random.default_rng(5)
