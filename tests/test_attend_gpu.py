@@ -54,7 +54,6 @@ def test_head_shapes(heads, kv_heads, width, mask):
 
 
 @pytest.mark.parametrize("mask", ["causal", "bidirectional"])
-@pytest.mark.parametrize("mask", ["causal", "bidirectional"])
 def test_packed_sequences_width_256(mask):
     # the embedding encoder's attention shape: 3 query heads over 1 kv head, 256 wide, ragged lengths
     rng = np.random.default_rng(6)
