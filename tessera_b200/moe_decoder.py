@@ -1,0 +1,86 @@
+"""A GLM-style mixture-of-experts decoder layer stack for decode steps over paged kept rows, on the
+library's kernels; experts local or expert-parallel.
+
+Per layer (engine/models/src/decoder.rs:327-389 with the `Moe` feed-forward of decoder.rs:58-84 and the
+shared expert of engine/models/src/mla.rs:466-467): rms_norm, fused q|k|v linear, per-head norm +
+rotation + append to the slot's pages, ragged attention over the kept rows, o linear + residual,
+rms_norm, router -> top-k -> softmax gates, shared expert + routed experts (dispatched to their owning
+rank when expert-parallel), residual.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import ops
+from .moe import ExpertParallel, MoeWeights, moe_forward
+
+GLM_MOE = dict(layers=8, hidden=4096, heads=32, kv_heads=8, head_dim=128, experts=128, top=8, ffn=1536,
+               shared_ffn=1536, eps=1e-6, theta=1e6)
+
+
+def _bf16_normal(shape, std, gen, device):
+    return (torch.randn(shape, generator=gen, device=device, dtype=torch.float32) * std).to(torch.bfloat16)
+
+
+class MoeDecoder:
+    def __init__(self, cfg: dict, slots: int, context: int, rank: int = 0, world: int = 1, seed: int = 0,
+                 group=None, device="cuda"):
+        self.cfg, self.device, self.world, self.rank = dict(cfg), device, world, rank
+        c = cfg
+        h, d = c["hidden"], c["head_dim"]
+        qw, kw = c["heads"] * d, c["kv_heads"] * d
+        per = c["experts"] // world
+        shared = torch.Generator(device=device).manual_seed(seed)          # replicated weights: same on every rank
+        local = torch.Generator(device=device).manual_seed(seed * 1000 + 17 + rank)
+        self.layers = []
+        for _ in range(c["layers"]):
+            L = dict(ln1=torch.ones(h, device=device), ln2=torch.ones(h, device=device),
+                     q_norm=torch.ones(d, device=device), k_norm=torch.ones(d, device=device),
+                     wqkv=_bf16_normal((qw + 2 * kw, h), 0.02, shared, device), wo=_bf16_normal((h, qw), 0.02, shared, device))
+            L["moe"] = MoeWeights(router=_bf16_normal((c["experts"], h), 0.02, shared, device),
+                                  w_in=_bf16_normal((per, 2 * c["ffn"], h), 0.02, local, device),
+                                  w_out=_bf16_normal((per, h, c["ffn"]), 0.02, local, device),
+                                  shared_in=_bf16_normal((2 * c["shared_ffn"], h), 0.02, shared, device),
+                                  shared_out=_bf16_normal((h, c["shared_ffn"]), 0.02, shared, device),
+                                  first=rank * per, experts_total=c["experts"])
+            self.layers.append(L)
+        self.page = 64
+        self.pages = -(-context // self.page)
+        self.slots, self.context = slots, context
+        rows = slots * self.pages * self.page
+        self.k_rows = [torch.zeros((rows, c["kv_heads"], d), dtype=torch.bfloat16, device=device) for _ in self.layers]
+        self.v_rows = [torch.zeros_like(k) for k in self.k_rows]
+        self.table = torch.arange(slots * self.pages, dtype=torch.int32, device=device)
+        self.inv_freq = ops.rope_inv_freq(c["theta"], d, device)
+        self.ep = ExpertParallel(group) if world > 1 else None
+
+    def set_table(self, table):
+        self.table.copy_(torch.as_tensor(table, dtype=torch.int32, device=self.device))
+
+    def fill_kept(self, seed: int = 1):
+        """Synthetic kept rows ~ N(0, 1): decode cost does not depend on their values."""
+        gen = torch.Generator(device=self.device).manual_seed(seed)
+        for k, v in zip(self.k_rows, self.v_rows):
+            k.copy_(torch.randn(k.shape, generator=gen, device=self.device).to(torch.bfloat16))
+            v.copy_(torch.randn(v.shape, generator=gen, device=self.device).to(torch.bfloat16))
+
+    def step(self, x: torch.Tensor, slots: torch.Tensor, positions: torch.Tensor, keys: int) -> torch.Tensor:
+        """x f32 [rows, hidden] (the residual rows), one row per slot -> the rows after every layer."""
+        c = self.cfg
+        rows, d, heads, kvh, eps = x.shape[0], c["head_dim"], c["heads"], c["kv_heads"], c["eps"]
+        kept = ops.Kept("paged", self.pages, self.table, self.k_rows[0].shape[0])
+        q = torch.empty((rows, heads, d), dtype=torch.bfloat16, device=self.device)
+        for i, L in enumerate(self.layers):
+            h = ops.rms_norm(x, L["ln1"], eps)
+            qkv = ops.linear(h, L["wqkv"])
+            ops.qk_norm_rope_append(qkv, L["q_norm"], L["k_norm"], self.inv_freq, slots, positions, q, self.k_rows[i],
+                                    self.v_rows[i], kept, heads, kvh, d, eps)
+            a = ops.attend_rows(q, self.k_rows[i], self.v_rows[i], slots, positions, kept, keys, scale=d ** -0.5)
+            x = ops.linear(a.view(rows, heads * d), L["wo"], x, epilogue="add", out_dtype=torch.float32, out=x)
+            h = ops.rms_norm(x, L["ln2"], eps)
+            if self.ep is None:
+                y, _, _ = moe_forward(h, L["moe"], c["top"])
+            else:
+                y, _, _ = self.ep.forward(h, L["moe"], c["top"])
+            x = x + y
+        return x
