@@ -363,6 +363,25 @@ def run_case(args):
             calls.append(lambda k=k, vv=vv, kept=kept, out=out: ops.attend_rows(
                 q, k, vv, slots, positions, kept, ctx, scale=d ** -0.5, out=out))
         algo = kernel_bytes("attend_rows", cfg, rows, rows * ctx)
+    elif args.case == "attend_flash":
+        # causal prefill attention of the isolated attention configuration, one sequence of --ctx tokens
+        n = args.ctx if args.ctx > 192 else 4096
+        copies = 2
+        for c in range(copies):
+            q, k, vv = bf(1, n, cfg["heads"], d), bf(1, n, cfg["kv_heads"], d), bf(1, n, cfg["kv_heads"], d)
+            out = torch.empty_like(q)
+            calls.append(lambda q=q, k=k, vv=vv, out=out: ops.attend(q, k, vv, mask="causal", scale=d ** -0.5, out=out))
+        algo = 4.0 * cfg["heads"] * d * n * (n + 1) / 2  # flops
+    elif args.case == "linear_prefill":
+        # prefill-sized linear: 2048 rows through the fused gate|up shape (n 6144, k 1024)
+        rows = args.rows if args.rows > 128 else 2048
+        n, k = 2 * f, h
+        x = bf(rows, k)
+        for c in range(4):
+            w = bf(n, k, std=0.02)
+            out = torch.empty((rows, n), dtype=torch.bfloat16, device="cuda")
+            calls.append(lambda w=w, out=out: ops.linear(x, w, out=out))
+        algo = 2.0 * rows * n * k  # flops
     else:
         shapes = {"linear_qkv": (qw + 2 * kw, h, "none", torch.bfloat16), "linear_o": (h, qw, "add", torch.float32),
                   "linear_gate_up": (2 * f, h, "swiglu", torch.bfloat16), "linear_down": (h, f, "add", torch.float32),
@@ -393,6 +412,15 @@ def run_case(args):
     torch.cuda.synchronize()
     us = e0.elapsed_time(e1) * 1e3 / args.steps
     peak, kind = peaks()
+    if args.case in ("attend_flash", "linear_prefill"):
+        tf_peak = 1694.8
+        path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+        if os.path.exists(path):
+            tf_peak = float(json.load(open(path))["bf16_tflops"])
+        print(json.dumps({"case": args.case, "us_per_launch": us, "algorithmic_flops": algo, "TFLOPs": algo / us / 1e6,
+                          "frac": algo / us / 1e6 / tf_peak, "peak_kind": kind + " (burst)", "launches": args.steps,
+                          "status": ops.device_status()}))
+        return
     print(json.dumps({"case": args.case, "rows": rows, "ctx": args.ctx if args.case == "attend_rows" else None,
                       "us_per_launch": us, "algorithmic_bytes": algo, "GBs": algo / us / 1e3,
                       "frac": algo / us / 1e3 / peak, "peak_kind": kind, "launches": args.steps, "copies": len(calls),

@@ -452,6 +452,11 @@ class CpuRulesDecoder:
         self.values = [np.zeros(shape, np.float32) for _ in range(L)]
         self._kp = (C.c_void_p * L)(*[a.ctypes.data for a in self.keys])
         self._vp = (C.c_void_p * L)(*[a.ctypes.data for a in self.values])
+        try:
+            cores = len(os.sched_getaffinity(0))
+        except AttributeError:
+            cores = os.cpu_count() or 1
+        rules().cr_set_threads(C.c_int(cores))  # torchrun exports OMP_NUM_THREADS=1; use every host core
         self.threads = int(rules().cr_threads())
 
     def step(self, tokens, slots, positions) -> np.ndarray:

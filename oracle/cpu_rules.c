@@ -35,6 +35,11 @@ static inline float widen(uint16_t b) {
 
 CR_API int cr_threads(void) { return omp_get_max_threads(); }
 
+/* Launchers such as torchrun export OMP_NUM_THREADS=1; the baseline is meant to use every host core. */
+CR_API void cr_set_threads(int n) {
+    if (n > 0) omp_set_num_threads(n);
+}
+
 /* rows x 32 sums over one k panel; packed is [depth][32]. */
 CLONES static void panel(const float *x, size_t x_stride, const float *packed, size_t depth, size_t rows,
                          float *sums /* [rows][32] */) {
