@@ -39,9 +39,12 @@ BATCH = 64
 PROMPT = 128
 FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used only when MEASURED_PEAKS.json is absent
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu captures
-# (profiles/*.md name the command); None until a capture of that kernel exists.
-NCU_TRAFFIC_BYTES = {}
+# (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic bytes of the captured launch, from the
+# committed ncu captures (profiles/decode_kernels_sections.md names the commands).  The captures ran on
+# small cases of the same kernels; traffic grows in proportion to the rows, keys and weights a launch
+# visits, so a launch's traffic is this ratio times its algorithmic bytes.  None: no capture.
+NCU_TRAFFIC_RATIO = {"attend_rows": 50.663 / 50.856, "linear_unembed": 340.64 / 350.19,
+                     "linear_qkv": 8.585 / 8.520}
 
 
 def parse_args():
@@ -292,7 +295,7 @@ def run_ours(args, rank, world, local_rank):
     algo = kernel_bytes(top, cfg, BATCH, int(BATCH * ctx_prof))
     achieved = algo / per_launch_s / 1e9
     roofline = {"kernel": top, "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "traffic": NCU_TRAFFIC_BYTES.get(top),
+                "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "traffic": (NCU_TRAFFIC_RATIO[top] * algo if top in NCU_TRAFFIC_RATIO else None),
                 "algorithmic_bytes_per_launch": algo, "avg_launch_us": per_launch_s * 1e6,
                 "step_share": shares[top], "kernel_shares": {k: round(v, 4) for k, v in sorted(shares.items())},
                 "per_kernel_gbs": {k: round(kernel_bytes(k, cfg, BATCH, int(BATCH * ctx_prof)) / (ms / n / 1e3) / 1e9, 1)

@@ -90,6 +90,23 @@ int make_tensor_map_2d(CUtensorMap *map, const void *base, uint64_t rows, uint64
     return TS_OK;
 }
 
+int make_tensor_map_2d_plain(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, uint64_t row_stride,
+                             uint32_t box_rows, uint32_t box_cols) {
+    EncodeTiledFn fn = encode_tiled();
+    if (!fn) return fail(TS_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {row_stride * 2};
+    cuuint32_t box[2] = {box_cols, box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(TS_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) for a plain %llu x %llu tensor, box %u x %u", (int)r,
+                    (unsigned long long)rows, (unsigned long long)cols, box_rows, box_cols);
+    return TS_OK;
+}
+
 int make_tensor_map_3d(CUtensorMap *map, const void *base, uint64_t outer, uint64_t rows, uint64_t cols,
                        uint64_t outer_stride, uint64_t row_stride, uint32_t box_rows, uint32_t box_cols) {
     EncodeTiledFn fn = encode_tiled();
@@ -133,7 +150,8 @@ int ts_set_pdl(int enabled) {
 
 int ts_device_status(void) {
     const int a = umma_take_status(), b = stream_take_status(), c = flash_take_status(), d = moe_take_status();
-    return a ? a : b ? b : c ? c : d;
+    const int e = rows_take_status();
+    return a ? a : b ? b : c ? c : d ? d : e;
 }
 
 size_t ts_linear_workspace_bytes(uint32_t m, uint32_t n, uint32_t k, int epilogue, int path) {
@@ -197,7 +215,7 @@ int ts_attend_rows_bf16(const void *q, const void *k, const void *v, void *out, 
     if (rc != TS_OK) return rc;
     if (rows == 0 || keys == 0) return TS_OK;
     return attend_rows(q, k, v, out, slots, positions, dev, contiguous, rows, keys, heads, kv_heads, width, back, scale,
-                       workspace, workspace_bytes, (cudaStream_t)stream);
+                       workspace, workspace_bytes, (cudaStream_t)stream, 0, nullptr, kept->rows);
 }
 
 size_t ts_attend_workspace_bytes(uint32_t seqs, uint32_t queries, uint32_t keys, uint32_t heads, uint32_t kv_heads,

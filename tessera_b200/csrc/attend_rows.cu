@@ -17,9 +17,18 @@
 // (engine/rules/attention/src/flash.rs:505-580); `scatter`
 // (engine/plan/lower/src/kernels/scatter.rs:11-83) and the per-head norm + rotation that precede
 // it in the decoder (engine/models/src/decoder.rs:354-389) are the append kernels below.
+//
+// Two kernels share the arithmetic.  `attend_rows_tma_kernel` (head width 128, layouts where 32
+// aligned positions are 32 consecutive kept rows) is persistent: a producer warp walks the block's
+// (row, kv head, chunk) items and streams 32-key K and V tiles into a shared-memory ring with TMA,
+// four consumer warps take the tiles in turn.  The copies of the next item are in flight while the
+// current one is being reduced; three blocks share an SM, so twelve tile pairs (192 KB) per SM can
+// be in flight, which is what keeps HBM busy (0.96 of the copy rate at 4096 keys per row).  `attend_rows_kernel` loads straight into registers and covers every other width and layout.
 #include <cmath>
 
 #include "ts_common.cuh"
+#include "ts_kernels.cuh"
+#include "ts_ptx.cuh"
 
 namespace ts {
 namespace {
@@ -253,6 +262,286 @@ __global__ void __launch_bounds__(kThreads) attend_rows_kernel(const RowsParams 
     }
 }
 
+// ---- TMA-fed variant ------------------------------------------------------------------------
+
+// One ring stage per consumer warp: block n of a thread block's sequence lands in stage n % 4 and is
+// reduced by consumer warp n % 4, so a stage's barrier is only ever waited on by one warp and its
+// phase parity cannot be mistaken for an older one.  Depth comes from co-resident blocks.
+constexpr int kTmaStages = 4;
+static_assert(kTmaStages == kWarps, "one ring stage per consumer warp");
+constexpr int kTmaTile = 32 * 128 * 2;  // 32 keys x 128 bf16
+constexpr int kTmaThreads = 32 + kThreads;  // producer warp + the four consumer warps
+
+template <int G>
+struct TmaShared {
+    static constexpr size_t ring = (size_t)kTmaStages * 2 * kTmaTile;
+    static constexpr size_t o = ring;                                   // float [kWarps][G][128]
+    static constexpr size_t ml = o + sizeof(float) * kWarps * G * 128;  // float [kWarps][G][2]
+    static constexpr size_t bars = ml + sizeof(float) * kWarps * G * 2; // full[kTmaStages], empty[kTmaStages]
+    static constexpr size_t flag = bars + sizeof(uint64_t) * 2 * kTmaStages;
+    static constexpr size_t bytes = flag + 16;
+};
+
+struct ItemRange {
+    uint32_t row, hg, chunk, slot, lo, hi, last;
+};
+
+__device__ __forceinline__ ItemRange item_range(const RowsParams &p, uint32_t item, uint32_t n_hg) {
+    ItemRange r;
+    r.chunk = item % p.chunks;
+    const uint32_t t = item / p.chunks;
+    r.hg = t % n_hg;
+    r.row = t / n_hg;
+    r.slot = p.slots[r.row];
+    const uint32_t pos = p.positions[r.row];
+    uint32_t reach = pos + p.ahead;
+    if (reach < pos || reach == 0xFFFFFFFFu) reach = 0xFFFFFFFEu;
+    r.last = min(reach + 1, p.keys);
+    if (p.lens) r.last = min(r.last, p.lens[r.slot]);
+    const uint32_t first = pos > p.back ? pos - p.back : 0;
+    r.lo = max(first, r.chunk * p.chunk);
+    r.hi = min(r.last, (r.chunk + 1) * p.chunk);
+    return r;
+}
+
+template <int G>
+__global__ void __launch_bounds__(kTmaThreads, G == 4 ? 2 : 3)
+attend_rows_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                       const RowsParams p, const uint32_t items, int *status) {
+    using namespace ptx;
+    using Sh = TmaShared<G>;
+    constexpr int WIDTH = 128, LPK = 16, KPI = 2, N = 16, NB = 8;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    float (*sm_o)[G][WIDTH] = reinterpret_cast<float (*)[G][WIDTH]>(smem + Sh::o);
+    float (*sm_ml)[G][2] = reinterpret_cast<float (*)[G][2]>(smem + Sh::ml);
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + Sh::bars);
+    uint64_t *empty = full + kTmaStages;
+    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(smem + Sh::flag);
+
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t n_hg = p.heads / G, group = p.heads / p.kv_heads;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kTmaStages; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        prefetch_tensormap(&map_k);
+        prefetch_tensormap(&map_v);
+    }
+    __syncthreads();
+    pdl_wait();  // q, the positions and the newest kept rows come from the upstream kernels
+    pdl_launch_dependents();
+
+    if (warp == 0) {
+        // ---- producer: one tile pair per 32-key block, in item order ----
+        bool ok = true;
+        uint32_t n = 0;
+        for (uint32_t item = blockIdx.x; item < items; item += gridDim.x) {
+            const ItemRange r = item_range(p, item, n_hg);
+            if (r.lo >= r.hi) continue;
+            const int32_t x = (int32_t)((r.hg * G / group) * WIDTH);
+            const uint32_t blk_lo = r.lo / 32, blk_hi = (r.hi + 31) / 32;
+            for (uint32_t b0 = blk_lo; b0 < blk_hi; b0 += 32) {
+                // the lanes look up the kept rows of up to 32 blocks side by side
+                const uint32_t mine = b0 + lane;
+                const uint32_t row0 = mine < blk_hi ? kept_row(p.kept, r.slot, mine * 32) : 0;
+                const uint32_t cnt = min(32u, blk_hi - b0);
+                for (uint32_t j = 0; j < cnt; j++, n++) {
+                    const uint32_t y = __shfl_sync(0xFFFFFFFFu, row0, j);
+                    if (lane == 0 && ok) {
+                        const uint32_t s = n % kTmaStages;
+                        ok = mbar_wait_or_abort(&empty[s], ((n / kTmaStages) & 1) ^ 1, abort_flag);
+                        if (ok) {
+                            uint8_t *dst = smem + (size_t)s * 2 * kTmaTile;
+                            mbar_expect_tx(&full[s], 2 * kTmaTile);
+                            tma_load_2d(dst, &map_k, &full[s], x, (int32_t)y);
+                            tma_load_2d(dst + kTmaTile, &map_v, &full[s], x, (int32_t)y);
+                        }
+                    }
+                }
+            }
+        }
+        // Every copy issued has been waited for by a consumer before that consumer leaves, or the
+        // block gave up: then wait (bounded) for the copies still in flight so none lands after exit.
+        if (lane == 0 && !ok) {
+            for (uint32_t back = 0; back < (uint32_t)kTmaStages && back < n; back++) {
+                const uint32_t j = n - 1 - back;
+                if (!mbar_wait(&full[j % kTmaStages], (j / kTmaStages) & 1)) break;
+            }
+        }
+    } else {
+        // ---- consumers ----
+        const uint32_t cw = warp - 1, ct = threadIdx.x - 32;
+        const uint32_t gidx = lane / LPK, piece = lane % LPK;
+        bool ok = true;
+        uint32_t n = 0;
+        for (uint32_t item = blockIdx.x; item < items; item += gridDim.x) {
+            const ItemRange r = item_range(p, item, n_hg);
+            const uint32_t head0 = r.hg * G;
+            const bool single = p.chunks == 1;
+            if (r.lo >= r.hi) {
+                if (!single && ct < G) {
+                    size_t at = (((size_t)r.row * p.heads + head0 + ct) * p.chunks + r.chunk) * 2;
+                    p.part_ml[at] = -INFINITY;
+                    p.part_ml[at + 1] = 0.0f;
+                }
+                if (single)
+                    for (uint32_t i = ct; i < G * WIDTH; i += kThreads)
+                        p.out[((size_t)r.row * p.heads + head0) * WIDTH + i] = 0;
+                continue;
+            }
+            float q[G][8];
+#pragma unroll
+            for (int g = 0; g < G; g++) {
+                uint4 v = *reinterpret_cast<const uint4 *>(p.q + ((size_t)r.row * p.heads + head0 + g) * WIDTH + piece * 8);
+                q[g][0] = bf16_lo(v.x); q[g][1] = bf16_hi(v.x); q[g][2] = bf16_lo(v.y); q[g][3] = bf16_hi(v.y);
+                q[g][4] = bf16_lo(v.z); q[g][5] = bf16_hi(v.z); q[g][6] = bf16_lo(v.w); q[g][7] = bf16_hi(v.w);
+            }
+            float m[G], l[G], o[G][8];
+#pragma unroll
+            for (int g = 0; g < G; g++) {
+                m[g] = -INFINITY;
+                l[g] = 0.0f;
+#pragma unroll
+                for (int e = 0; e < 8; e++) o[g][e] = 0.0f;
+            }
+            const uint32_t blk_lo = r.lo / 32, blk_hi = (r.hi + 31) / 32;
+            for (uint32_t blk = blk_lo; blk < blk_hi; blk++, n++) {
+                if ((n & (kWarps - 1)) != cw) continue;
+                const uint32_t s = n % kTmaStages;
+                if (ok) ok = mbar_wait_or_abort(&full[s], (n / kTmaStages) & 1, abort_flag);
+                if (ok) {
+                    const uint8_t *tile_k = smem + (size_t)s * 2 * kTmaTile;
+                    uint8_t *tile_v = smem + (size_t)s * 2 * kTmaTile + kTmaTile;
+                    const uint32_t base = blk * 32;
+                    const uint32_t own = base + piece * KPI + gidx;
+                    const bool own_ok = own >= r.lo && own < r.hi;
+                    if (base < r.lo || base + 32 > r.hi) {
+                        // An edge block: rows outside the range may hold anything (a page's unwritten
+                        // tail); zero their V so that a zero probability cannot meet a NaN.
+                        for (uint32_t j = 0; j < 32; j++) {
+                            const uint32_t key = base + j;
+                            if (key < r.lo || key >= r.hi)
+                                *reinterpret_cast<uint2 *>(tile_v + j * 256 + lane * 8) = make_uint2(0, 0);
+                        }
+                        fence_async_shared();  // these stores precede the next copy into this stage
+                        __syncwarp();
+                    }
+                    // ---- scores ----
+                    float sc[G][N];
+#pragma unroll
+                    for (int i0 = 0; i0 < N; i0 += NB) {
+                        uint4 kv[NB];
+#pragma unroll
+                        for (int i = 0; i < NB; i++)
+                            kv[i] = *reinterpret_cast<const uint4 *>(tile_k + ((i0 + i) * KPI + gidx) * 256 + piece * 16);
+#pragma unroll
+                        for (int i = 0; i < NB; i++) {
+                            float f[8] = {bf16_lo(kv[i].x), bf16_hi(kv[i].x), bf16_lo(kv[i].y), bf16_hi(kv[i].y),
+                                          bf16_lo(kv[i].z), bf16_hi(kv[i].z), bf16_lo(kv[i].w), bf16_hi(kv[i].w)};
+#pragma unroll
+                            for (int g = 0; g < G; g++) {
+                                float a = 0.0f;
+#pragma unroll
+                                for (int e = 0; e < 8; e++) a = fmaf(q[g][e], f[e], a);
+                                sc[g][i0 + i] = a;
+                            }
+                        }
+                    }
+                    float prob[G];
+#pragma unroll
+                    for (int g = 0; g < G; g++) {
+#pragma unroll
+                        for (int off = LPK / 2; off >= 1; off /= 2) {
+                            const bool upper = (lane & off) != 0;
+#pragma unroll
+                            for (int i = 0; i < off; i++) {
+                                float keep = upper ? sc[g][i + off] : sc[g][i];
+                                float send = upper ? sc[g][i] : sc[g][i + off];
+                                sc[g][i] = keep + __shfl_xor_sync(0xFFFFFFFFu, send, off);
+                            }
+                        }
+                        const float score = own_ok ? sc[g][0] * p.scale : -INFINITY;
+                        const float m_new = fmaxf(m[g], warp_max(score));
+                        const float alpha = __expf(m[g] - m_new);
+                        prob[g] = own_ok ? __expf(score - m_new) : 0.0f;
+                        l[g] = l[g] * alpha + prob[g];
+#pragma unroll
+                        for (int e = 0; e < 8; e++) o[g][e] *= alpha;
+                        m[g] = m_new;
+                    }
+                    // ---- values ----
+#pragma unroll
+                    for (int i0 = 0; i0 < N; i0 += NB) {
+                        uint4 vv[NB];
+#pragma unroll
+                        for (int i = 0; i < NB; i++)
+                            vv[i] = *reinterpret_cast<const uint4 *>(tile_v + ((i0 + i) * KPI + gidx) * 256 + piece * 16);
+#pragma unroll
+                        for (int i = 0; i < NB; i++) {
+                            float f[8] = {bf16_lo(vv[i].x), bf16_hi(vv[i].x), bf16_lo(vv[i].y), bf16_hi(vv[i].y),
+                                          bf16_lo(vv[i].z), bf16_hi(vv[i].z), bf16_lo(vv[i].w), bf16_hi(vv[i].w)};
+#pragma unroll
+                            for (int g = 0; g < G; g++) {
+                                float pr = __shfl_sync(0xFFFFFFFFu, prob[g], gidx * LPK + i0 + i);
+#pragma unroll
+                                for (int e = 0; e < 8; e++) o[g][e] = fmaf(pr, f[e], o[g][e]);
+                            }
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[s]);
+            }
+            // ---- fold the two lane groups of a warp, then the four warps ----
+#pragma unroll
+            for (int g = 0; g < G; g++) {
+                l[g] = warp_sum(l[g]);
+#pragma unroll
+                for (int e = 0; e < 8; e++) o[g][e] += __shfl_xor_sync(0xFFFFFFFFu, o[g][e], 16);
+                if (gidx == 0) {
+#pragma unroll
+                    for (int e = 0; e < 8; e++) sm_o[cw][g][piece * 8 + e] = o[g][e];
+                }
+                if (lane == 0) {
+                    sm_ml[cw][g][0] = m[g];
+                    sm_ml[cw][g][1] = l[g];
+                }
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory");
+            for (uint32_t i = ct; i < G * WIDTH; i += kThreads) {
+                const uint32_t g = i / WIDTH, d = i % WIDTH;
+                float mm = -INFINITY;
+#pragma unroll
+                for (int w = 0; w < kWarps; w++) mm = fmaxf(mm, sm_ml[w][g][0]);
+                float ll = 0.0f, oo = 0.0f;
+#pragma unroll
+                for (int w = 0; w < kWarps; w++) {
+                    float mw = sm_ml[w][g][0];
+                    float f = mw == -INFINITY ? 0.0f : __expf(mw - mm);
+                    ll += sm_ml[w][g][1] * f;
+                    oo += sm_o[w][g][d] * f;
+                }
+                if (single) {
+                    p.out[((size_t)r.row * p.heads + head0 + g) * WIDTH + d] = ll > 0.0f ? bf16_bits(oo / ll) : (uint16_t)0;
+                } else {
+                    size_t at = ((size_t)r.row * p.heads + head0 + g) * p.chunks + r.chunk;
+                    p.part_o[at * WIDTH + d] = oo;
+                    if (d == 0) {
+                        p.part_ml[at * 2] = mm;
+                        p.part_ml[at * 2 + 1] = ll;
+                    }
+                }
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory");
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag) atomicExch(status, TS_ERR_TIMEOUT);
+}
+
 // One block per (row, head): folds the chunks in ascending order.
 template <int WIDTH>
 __global__ void __launch_bounds__(WIDTH) attend_rows_merge_kernel(const RowsParams p) {
@@ -297,7 +586,36 @@ cudaError_t launch_rows(const RowsParams &p, dim3 grid, cudaStream_t stream) {
     return launch(attend_rows_kernel<WIDTH, G>, grid, dim3(kThreads), 0, stream, pdl_enabled(), p);
 }
 
+__device__ int g_rows_status = 0;
+
+template <int G>
+int launch_rows_tma(const CUtensorMap &map_k, const CUtensorMap &map_v, const RowsParams &p, uint32_t items,
+                    cudaStream_t stream) {
+    using Sh = TmaShared<G>;
+    static bool configured = false;
+    if (!configured) {
+        TS_CUDA(cudaFuncSetAttribute(attend_rows_tma_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Sh::bytes));
+        configured = true;
+    }
+    int *status = nullptr;
+    TS_CUDA(cudaGetSymbolAddress((void **)&status, g_rows_status));
+    const uint32_t grid = min(items, (uint32_t)sm_count() * (G == 4 ? 2 : 3));
+    cudaError_t e = launch(attend_rows_tma_kernel<G>, dim3(grid), dim3(kTmaThreads), Sh::bytes, stream, pdl_enabled(),
+                           map_k, map_v, p, items, status);
+    if (e != cudaSuccess)
+        return fail(TS_ERR_CUDA, "launch of attend_rows (tma) failed: %s (%d) %s", cudaGetErrorName(e), (int)e,
+                    cudaGetErrorString(e));
+    return TS_OK;
+}
+
 }  // namespace
+
+int rows_take_status() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_rows_status, sizeof(int)) != cudaSuccess) return TS_ERR_CUDA;
+    if (v != 0) cudaMemcpyToSymbol(g_rows_status, &zero, sizeof(int));
+    return v;
+}
 
 size_t attend_rows_workspace_bytes(uint32_t rows, uint32_t keys, uint32_t heads, uint32_t kv_heads, uint32_t width) {
     if (rows == 0 || heads == 0 || kv_heads == 0) return 0;
@@ -309,7 +627,7 @@ size_t attend_rows_workspace_bytes(uint32_t rows, uint32_t keys, uint32_t heads,
 int attend_rows(const void *q, const void *k, const void *v, void *out, const uint32_t *slots,
                 const uint32_t *positions, const KeptDev &kept, bool contiguous, uint32_t rows, uint32_t keys,
                 uint32_t heads, uint32_t kv_heads, uint32_t width, uint32_t back, float scale, void *workspace,
-                size_t workspace_bytes, cudaStream_t stream, uint32_t ahead, const uint32_t *lens) {
+                size_t workspace_bytes, cudaStream_t stream, uint32_t ahead, const uint32_t *lens, uint32_t kept_rows) {
     RowsPlan s = plan_rows(rows, keys, heads, kv_heads);
     size_t need = s.chunks > 1 ? (size_t)rows * heads * s.chunks * (width + 2) * sizeof(float) : 0;
     TS_REQUIRE(workspace_bytes >= need && (need == 0 || workspace != nullptr),
@@ -337,7 +655,24 @@ int attend_rows(const void *q, const void *k, const void *v, void *out, const ui
     p.contiguous = contiguous ? 1 : 0;
     dim3 grid(rows, heads / s.g, s.chunks);
     cudaError_t e = cudaErrorInvalidValue;
-    if (width == 128) {
+    // The TMA-fed kernel: width 128, 32 aligned positions = 32 consecutive kept rows, and a known
+    // row count to bound the tensor maps with.
+    const bool tma = width == 128 && contiguous && kept_rows > 0 &&
+                     (uint64_t)rows * (heads / s.g) * s.chunks < 0xFFFFFFFFull;
+    if (tma) {
+        CUtensorMap map_k, map_v;
+        const uint64_t cols = (uint64_t)kv_heads * width;
+        int rc = make_tensor_map_2d_plain(&map_k, k, kept_rows, cols, cols, 32, 128);
+        if (rc != TS_OK) return rc;
+        rc = make_tensor_map_2d_plain(&map_v, v, kept_rows, cols, cols, 32, 128);
+        if (rc != TS_OK) return rc;
+        const uint32_t items = rows * (heads / s.g) * s.chunks;
+        rc = s.g == 4   ? launch_rows_tma<4>(map_k, map_v, p, items, stream)
+             : s.g == 2 ? launch_rows_tma<2>(map_k, map_v, p, items, stream)
+                        : launch_rows_tma<1>(map_k, map_v, p, items, stream);
+        if (rc != TS_OK) return rc;
+        e = cudaSuccess;
+    } else if (width == 128) {
         e = s.g == 4 ? launch_rows<128, 4>(p, grid, stream)
             : s.g == 2 ? launch_rows<128, 2>(p, grid, stream)
                        : launch_rows<128, 1>(p, grid, stream);

@@ -154,7 +154,8 @@ int enqueue(ts_decoder *d, uint32_t rows, uint32_t keys, uint32_t n_out, bool fe
                                  d->slots, d->positions, d->q, L.k_rows, L.v_rows, kd, rows, c.heads, c.kv_heads, D,
                                  c.eps, s));
         STEP("attend_rows", attend_rows(d->q, L.k_rows, L.v_rows, d->attn, d->slots, d->positions, kd, contiguous, rows, keys, c.heads,
-                         c.kv_heads, D, 0xFFFFFFFFu, scale, d->workspace, d->workspace_bytes, s));
+                         c.kv_heads, D, 0xFFFFFFFFu, scale, d->workspace, d->workspace_bytes, s, 0, nullptr,
+                         d->kept_total_rows));
         if (attend_rows_workspace_bytes(rows, keys, c.heads, c.kv_heads, D) > 0) launches++;
         STEP("linear_o", linear(d->attn, L.wo, d->x, d->x, H, QW, TS_EPI_ADD, TS_F32));
         STEP("rms_norm", rms_norm(d->x, TS_F32, L.ln2, d->h, TS_BF16, rows, H, c.eps, nullptr, s));

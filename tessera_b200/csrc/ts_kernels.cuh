@@ -26,7 +26,9 @@ size_t attend_rows_workspace_bytes(uint32_t rows, uint32_t keys, uint32_t heads,
 int attend_rows(const void *q, const void *k, const void *v, void *out, const uint32_t *slots,
                 const uint32_t *positions, const KeptDev &kept, bool contiguous, uint32_t rows, uint32_t keys,
                 uint32_t heads, uint32_t kv_heads, uint32_t width, uint32_t back, float scale, void *workspace,
-                size_t workspace_bytes, cudaStream_t stream, uint32_t ahead = 0, const uint32_t *lens = nullptr);
+                size_t workspace_bytes, cudaStream_t stream, uint32_t ahead = 0, const uint32_t *lens = nullptr,
+                uint32_t kept_rows = 0);  // kept_rows: rows the K/V buffers hold; 0 = unknown
+int rows_take_status();
 bool flash_supports(uint32_t width);
 int flash_take_status();
 int attend_flash(const void *q, const void *k, const void *v, void *out, const uint32_t *cu_seqlens, uint32_t seqs,

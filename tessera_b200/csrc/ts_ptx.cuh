@@ -336,6 +336,10 @@ __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.
 int make_tensor_map_2d(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, uint64_t row_stride,
                        uint32_t box_rows, uint32_t box_cols);
 
+// Same without swizzle: rows of the tile lie back to back in shared memory (box_cols <= 256).
+int make_tensor_map_2d_plain(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, uint64_t row_stride,
+                             uint32_t box_rows, uint32_t box_cols);
+
 // 3-D: [outer, rows, cols] with element strides; tile 1 x box_rows x box_cols.
 int make_tensor_map_3d(CUtensorMap *map, const void *base, uint64_t outer, uint64_t rows, uint64_t cols,
                        uint64_t outer_stride, uint64_t row_stride, uint32_t box_rows, uint32_t box_cols);

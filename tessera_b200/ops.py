@@ -99,6 +99,8 @@ def attend_rows(q, k_rows, v_rows, slots, positions, kept: Kept, keys: int, *, s
     nbytes = lib.ts_attend_rows_workspace_bytes(rows, keys, heads, kv_heads, width)
     ws = workspace(nbytes, q.device)
     kc = kept.c()
+    if kc.rows == 0:
+        kc.rows = k_rows.numel() // (kv_heads * width)
     check(lib.ts_attend_rows_bf16(_ptr(q), _ptr(k_rows), _ptr(v_rows), _ptr(out), _ptr(slots), _ptr(positions),
                                   C.byref(kc), rows, keys, heads, kv_heads, width, back, scale, _ptr(ws), nbytes,
                                   _stream()))

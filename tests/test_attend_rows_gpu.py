@@ -108,6 +108,32 @@ def test_long_ragged_contexts_split_and_merge(page_layout):
     assert torch.equal(got, again)  # fixed merge order: same bits on a re-run
 
 
+@pytest.mark.parametrize("layout", ["dense", "paged"])
+def test_unwritten_rows_may_hold_anything(layout):
+    # Rows past a slot's last position (a page's tail, a dense slot's unused part) are never written;
+    # whatever bits they hold must not reach the output.
+    from tessera_b200 import ops
+    rng = np.random.default_rng(21)
+    slots, heads, kv_heads, width = 4, 8, 4, 128
+    lengths = [1, 33, 70, 190]
+    context = 256
+    kept, row_fn, total = _layout(layout, slots, context, rng)
+    kd, vd, kb, vb = _fill_store(rng, slots, lengths, kv_heads, width, row_fn, total)
+    written = np.zeros(total, bool)
+    for s in range(slots):
+        written[[row_fn(s, p) for p in range(lengths[s])]] = True
+    kb[~written] = 0x7FC0  # NaN
+    vb[~written] = 0x7F80  # +inf
+    row_slots, row_pos = list(range(slots)), [n - 1 for n in lengths]
+    q = normal_bf16(rng, (slots, heads, width))
+    want = O.attend_rows(O.bf16_widen(q), kd[:, :max(lengths)], vd[:, :max(lengths)], row_slots, row_pos, "causal", 0.09)
+    got = ops.attend_rows(from_bits(q), from_bits(kb), from_bits(vb), dev_u32(row_slots), dev_u32(row_pos), kept,
+                          context, scale=0.09)
+    torch.cuda.synchronize()
+    assert torch.isfinite(got.float()).all()
+    assert rel_error(widen(got), want) <= TOL
+
+
 def test_window_back():
     # Mask::Back(n): keys at most n back (engine/ir/graph/src/node.rs:162-187)
     from tessera_b200 import ops
