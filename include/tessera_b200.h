@@ -85,6 +85,30 @@ int ts_linear_bf16(const void *x, const void *w, const void *a0, void *out, uint
                    uint32_t k, int epilogue, float scale, int out_dtype, int path, void *workspace,
                    size_t workspace_bytes, void *stream);
 
+/* A decode-sized linear (m <= 128) with the RMS norms of the residual stream folded into its two
+ * ends.  The reference runs `lane_norm` as a launch of its own between the residual add and the next
+ * projection (engine/models/src/decoder.rs:327-389, engine/rules/kernels/src/lane_norm.rs:10-17); at
+ * batch 64 that launch is pure latency, so here
+ *   - a linear with the ADD epilogue and an f32 output can also leave, per output row, the sum of
+ *     squares over each 128-column tile in ss_out [m, ts_linear_sumsq_parts(...)], and
+ *   - the next linear can take its input as norm_x (f32 [m, k]) with the gain norm_w (f32 [k]) and those
+ *     partial sums: it forms x = bf16(norm_x * (norm_w / sqrt(sum / k + eps))) itself, the value
+ *     ts_rms_norm would have written.  Pass x = NULL then.
+ * Either half may be left out (NULL pointers). */
+typedef struct {
+    const float *norm_x, *norm_w, *norm_ss;
+    uint32_t norm_parts; /* partial sums per row in norm_ss, 1..32 */
+    float norm_eps;
+    float *ss_out;
+} ts_linear_fused;
+
+/* Partial sums per row a linear of this shape writes to ss_out; 0 when it cannot (then run ts_rms_norm). */
+uint32_t ts_linear_sumsq_parts(uint32_t m, uint32_t n, uint32_t k, int epilogue);
+
+int ts_linear_fused_bf16(const void *x, const void *w, const void *a0, void *out, uint32_t m, uint32_t n,
+                         uint32_t k, int epilogue, float scale, int out_dtype, const ts_linear_fused *fused,
+                         void *stream);
+
 /* ---------------------------------------------------------------------------
  * Kept rows (paged KV).  Layouts follow engine/plan/codegen/src/kept.rs:135-194:
  *   dense        row = slot * kept_scalar + position          (kept_scalar = kept_stride)

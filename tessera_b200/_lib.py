@@ -26,6 +26,11 @@ class TsKept(C.Structure):
     _fields_ = [("kind", i32), ("page", u32), ("kept_scalar", u32), ("table", vp), ("table_len", u32), ("rows", u32)]
 
 
+class TsLinearFused(C.Structure):
+    """ts_linear_fused: the RMS norm folded into a decode-sized linear's input and output."""
+    _fields_ = [("norm_x", vp), ("norm_w", vp), ("norm_ss", vp), ("norm_parts", u32), ("norm_eps", f32), ("ss_out", vp)]
+
+
 class TsArg(C.Structure):
     class _V(C.Union):
         _fields_ = [("ptr", vp), ("u32", u32), ("f32", f32)]
@@ -40,6 +45,8 @@ SIGNATURES = {
     "ts_device_status": (i32, []),
     "ts_linear_workspace_bytes": (sz, [u32, u32, u32, i32, i32]),
     "ts_linear_bf16": (i32, [vp, vp, vp, vp, u32, u32, u32, i32, f32, i32, i32, vp, sz, vp]),
+    "ts_linear_sumsq_parts": (u32, [u32, u32, u32, i32]),
+    "ts_linear_fused_bf16": (i32, [vp, vp, vp, vp, u32, u32, u32, i32, f32, i32, C.POINTER(TsLinearFused), vp]),
     "ts_attend_rows_workspace_bytes": (sz, [u32, u32, u32, u32, u32]),
     "ts_attend_rows_bf16": (i32, [vp, vp, vp, vp, vp, vp, C.POINTER(TsKept), u32, u32, u32, u32, u32, u32, f32, vp, sz, vp]),
     "ts_attend_workspace_bytes": (sz, [u32, u32, u32, u32, u32, u32]),

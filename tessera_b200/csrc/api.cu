@@ -163,6 +163,32 @@ size_t ts_linear_workspace_bytes(uint32_t m, uint32_t n, uint32_t k, int epilogu
     return a > b ? a : b;
 }
 
+uint32_t ts_linear_sumsq_parts(uint32_t m, uint32_t n, uint32_t k, int epilogue) {
+    return stream_sumsq_parts(m, n, k, epilogue);
+}
+
+int ts_linear_fused_bf16(const void *x, const void *w, const void *a0, void *out, uint32_t m, uint32_t n, uint32_t k,
+                         int epilogue, float scale, int out_dtype, const ts_linear_fused *fused, void *stream) {
+    TS_REQUIRE(w && out, "linear: w and out must not be NULL");
+    TS_REQUIRE(aligned16(w) && aligned16(out), "linear: w and out must be 16-byte aligned");
+    TS_REQUIRE(out_dtype == TS_BF16 || out_dtype == TS_F32, "linear: out_dtype %d is neither bf16 nor f32", out_dtype);
+    TS_REQUIRE(epilogue != TS_EPI_ADD || a0 != nullptr, "linear: the ADD epilogue needs a0");
+    StreamFused f;
+    if (fused) {
+        f.norm_x = fused->norm_x;
+        f.norm_w = fused->norm_w;
+        f.norm_ss = fused->norm_ss;
+        f.norm_parts = fused->norm_parts;
+        f.norm_eps = fused->norm_eps;
+        f.ss_out = fused->ss_out;
+    }
+    TS_REQUIRE(f.norm_x || (x && aligned16(x)), "linear: x is NULL (or unaligned) and no norm_x was given");
+    if (m == 0 || n == 0) return TS_OK;
+    TS_REQUIRE(stream_supports(m, n, k, epilogue), "linear (fused): m=%u n=%u k=%u epilogue=%d is not a decode-sized shape",
+               m, n, k, epilogue);
+    return linear_stream(x, w, a0, out, m, n, k, epilogue, scale, out_dtype, (cudaStream_t)stream, &f);
+}
+
 int ts_linear_bf16(const void *x, const void *w, const void *a0, void *out, uint32_t m, uint32_t n, uint32_t k,
                    int epilogue, float scale, int out_dtype, int path, void *workspace, size_t workspace_bytes,
                    void *stream) {

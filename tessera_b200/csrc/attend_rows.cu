@@ -337,7 +337,7 @@ attend_rows_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     if (warp == 0) {
         // ---- producer: one tile pair per 32-key block, in item order ----
         bool ok = true;
-        uint32_t n = 0;
+        uint32_t odd = 0, any = 0;  // per stage: parity of the copies issued so far, and whether there were any
         for (uint32_t item = blockIdx.x; item < items; item += gridDim.x) {
             const ItemRange r = item_range(p, item, n_hg);
             if (r.lo >= r.hi) continue;
@@ -348,12 +348,15 @@ attend_rows_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                 const uint32_t mine = b0 + lane;
                 const uint32_t row0 = mine < blk_hi ? kept_row(p.kept, r.slot, mine * 32) : 0;
                 const uint32_t cnt = min(32u, blk_hi - b0);
-                for (uint32_t j = 0; j < cnt; j++, n++) {
+                for (uint32_t j = 0; j < cnt; j++) {
                     const uint32_t y = __shfl_sync(0xFFFFFFFFu, row0, j);
+                    // block b of an item goes to stage (and consumer warp) b % 4, whatever came before
+                    const uint32_t s = (b0 - blk_lo + j) & (kTmaStages - 1);
                     if (lane == 0 && ok) {
-                        const uint32_t s = n % kTmaStages;
-                        ok = mbar_wait_or_abort(&empty[s], ((n / kTmaStages) & 1) ^ 1, abort_flag);
+                        ok = mbar_wait_or_abort(&empty[s], ((odd >> s) & 1) ^ 1, abort_flag);
                         if (ok) {
+                            odd ^= 1u << s;
+                            any |= 1u << s;
                             uint8_t *dst = smem + (size_t)s * 2 * kTmaTile;
                             mbar_expect_tx(&full[s], 2 * kTmaTile);
                             tma_load_2d(dst, &map_k, &full[s], x, (int32_t)y);
@@ -366,17 +369,16 @@ attend_rows_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         // Every copy issued has been waited for by a consumer before that consumer leaves, or the
         // block gave up: then wait (bounded) for the copies still in flight so none lands after exit.
         if (lane == 0 && !ok) {
-            for (uint32_t back = 0; back < (uint32_t)kTmaStages && back < n; back++) {
-                const uint32_t j = n - 1 - back;
-                if (!mbar_wait(&full[j % kTmaStages], (j / kTmaStages) & 1)) break;
-            }
+            for (uint32_t s = 0; s < (uint32_t)kTmaStages; s++)
+                if (((any >> s) & 1) && !mbar_wait(&full[s], ((odd >> s) & 1) ^ 1)) break;
         }
     } else {
         // ---- consumers ----
         const uint32_t cw = warp - 1, ct = threadIdx.x - 32;
         const uint32_t gidx = lane / LPK, piece = lane % LPK;
         bool ok = true;
-        uint32_t n = 0;
+        uint32_t used = 0;  // tiles this warp has taken from its stage
+        const uint32_t s = cw;
         for (uint32_t item = blockIdx.x; item < items; item += gridDim.x) {
             const ItemRange r = item_range(p, item, n_hg);
             const uint32_t head0 = r.hg * G;
@@ -408,10 +410,9 @@ attend_rows_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                 for (int e = 0; e < 8; e++) o[g][e] = 0.0f;
             }
             const uint32_t blk_lo = r.lo / 32, blk_hi = (r.hi + 31) / 32;
-            for (uint32_t blk = blk_lo; blk < blk_hi; blk++, n++) {
-                if ((n & (kWarps - 1)) != cw) continue;
-                const uint32_t s = n % kTmaStages;
-                if (ok) ok = mbar_wait_or_abort(&full[s], (n / kTmaStages) & 1, abort_flag);
+            for (uint32_t blk = blk_lo + cw; blk < blk_hi; blk += kWarps) {
+                if (ok) ok = mbar_wait_or_abort(&full[s], used & 1, abort_flag);
+                used++;
                 if (ok) {
                     const uint8_t *tile_k = smem + (size_t)s * 2 * kTmaTile;
                     uint8_t *tile_v = smem + (size_t)s * 2 * kTmaTile + kTmaTile;

@@ -33,6 +33,7 @@ struct ts_decoder {
     uint16_t *attn = nullptr;    // [max_rows, heads * head_dim]
     uint16_t *act = nullptr;     // [max_rows, ffn]
     uint16_t *h_out = nullptr;   // final normed rows of the wanted rows [max_rows, hidden]
+    float *sumsq = nullptr;      // per-tile sums of squares of the residual rows [max_rows, 32]
     float *logits = nullptr;     // [max_out, vocab]
     uint32_t max_out = 0;
     uint32_t *tokens = nullptr, *slots = nullptr, *positions = nullptr, *out_rows = nullptr, *ids = nullptr;
@@ -110,6 +111,30 @@ size_t linear_workspace(uint32_t m, uint32_t n, uint32_t k, int epi) {
     return 0;
 }
 
+// Partial sums per row when the layer norms can fold into the projections around them (every
+// projection of the layer takes the weight-streaming kernel and the two that feed the residual
+// split their k), else 0.
+uint32_t fold_parts(const ts_decoder *d, uint32_t rows) {
+    // Off unless TS_FOLD_NORMS=1.  Measured on the Qwen3-0.6B shape at batch 64 the folded step is no
+    // faster (the projections spend on building their input what the norm launches cost), and its sums
+    // of squares add up in another order, which is enough to move a greedy token where two logits
+    // nearly tie.  The default keeps the launch sequence whose tokens equal the CPU checker's.
+    static const bool on = [] {
+        const char *v = getenv("TS_FOLD_NORMS");
+        return v && v[0] == '1';
+    }();
+    if (!on) return 0;
+    const ts_decoder_config &c = d->c;
+    const uint32_t H = c.hidden, QW = c.heads * c.head_dim;
+    const uint32_t parts = stream_sumsq_parts(rows, H, QW, TS_EPI_ADD);
+    const bool ok = parts != 0 && parts <= 32 && stream_sumsq_parts(rows, H, c.ffn, TS_EPI_ADD) == parts &&
+                    pick_linear_path(rows, H, QW, TS_EPI_ADD, TS_LINEAR_AUTO) == TS_LINEAR_STREAM &&
+                    pick_linear_path(rows, H, c.ffn, TS_EPI_ADD, TS_LINEAR_AUTO) == TS_LINEAR_STREAM &&
+                    pick_linear_path(rows, d->qkv_n, H, TS_EPI_NONE, TS_LINEAR_AUTO) == TS_LINEAR_STREAM &&
+                    pick_linear_path(rows, 2 * c.ffn, H, TS_EPI_SWIGLU, TS_LINEAR_AUTO) == TS_LINEAR_STREAM;
+    return ok ? parts : 0;
+}
+
 // The step list for `rows` rows that see at most `keys` positions; logits for n_out rows.
 int enqueue(ts_decoder *d, uint32_t rows, uint32_t keys, uint32_t n_out, bool feedback, cudaStream_t s,
             uint32_t *count) {
@@ -143,13 +168,36 @@ int enqueue(ts_decoder *d, uint32_t rows, uint32_t keys, uint32_t n_out, bool fe
                       int out_dtype) -> int {
         return linear_any(d, xin, w, a0, out, rows, n, k, epi, out_dtype, s);
     };
+    // Decode-sized steps fold the layer norms into the projections on either side: the o and down
+    // projections leave per-tile sums of squares of the new residual rows, the q,k,v and gate/up
+    // projections normalise their input from them.  Layer 0's first norm still runs on its own (its
+    // input comes from the embedding gather).
+    const uint32_t ss_parts = fold_parts(d, rows);
+    const bool fold = ss_parts != 0;
+    auto folded = [&](const float *ln, const void *xin, const void *w, const void *a0, void *out, uint32_t n, uint32_t k,
+                      int epi, int out_dtype, bool leave_sums) -> int {
+        StreamFused f;
+        if (ln) {
+            f.norm_x = d->x;
+            f.norm_w = ln;
+            f.norm_ss = d->sumsq;
+            f.norm_parts = ss_parts;
+            f.norm_eps = c.eps;
+        }
+        if (leave_sums) f.ss_out = d->sumsq;
+        return linear_stream(xin, w, a0, out, rows, n, k, epi, 1.0f, out_dtype, s, &f);
+    };
     if ((rc = mark("")) != TS_OK) return rc;  // interval origin
     if (feedback) STEP("advance_rows", advance_rows(d->ids, d->tokens, d->positions, rows, s));
     STEP("gather", gather_rows(d->embed, d->tokens, d->x, TS_F32, rows, c.vocab, H, 0, s));
     for (uint32_t l = 0; l < c.layers; l++) {
         ts_decoder::Layer &L = d->layers[l];
-        STEP("rms_norm", rms_norm(d->x, TS_F32, L.ln1, d->h, TS_BF16, rows, H, c.eps, nullptr, s));
-        STEP("linear_qkv", linear(d->h, L.wqkv, nullptr, d->qkv, d->qkv_n, H, TS_EPI_NONE, TS_BF16));
+        if (fold && l > 0) {
+            STEP("linear_qkv", folded(L.ln1, nullptr, L.wqkv, nullptr, d->qkv, d->qkv_n, H, TS_EPI_NONE, TS_BF16, false));
+        } else {
+            STEP("rms_norm", rms_norm(d->x, TS_F32, L.ln1, d->h, TS_BF16, rows, H, c.eps, nullptr, s));
+            STEP("linear_qkv", linear(d->h, L.wqkv, nullptr, d->qkv, d->qkv_n, H, TS_EPI_NONE, TS_BF16));
+        }
         STEP("qk_norm_rope_append", qk_norm_rope_append(d->qkv, c.qk_norm ? L.q_norm : nullptr, c.qk_norm ? L.k_norm : nullptr, d->inv_freq,
                                  d->slots, d->positions, d->q, L.k_rows, L.v_rows, kd, rows, c.heads, c.kv_heads, D,
                                  c.eps, s));
@@ -157,10 +205,16 @@ int enqueue(ts_decoder *d, uint32_t rows, uint32_t keys, uint32_t n_out, bool fe
                          c.kv_heads, D, 0xFFFFFFFFu, scale, d->workspace, d->workspace_bytes, s, 0, nullptr,
                          d->kept_total_rows));
         if (attend_rows_workspace_bytes(rows, keys, c.heads, c.kv_heads, D) > 0) launches++;
-        STEP("linear_o", linear(d->attn, L.wo, d->x, d->x, H, QW, TS_EPI_ADD, TS_F32));
-        STEP("rms_norm", rms_norm(d->x, TS_F32, L.ln2, d->h, TS_BF16, rows, H, c.eps, nullptr, s));
-        STEP("linear_gate_up", linear(d->h, L.wgu, nullptr, d->act, 2 * c.ffn, H, TS_EPI_SWIGLU, TS_BF16));
-        STEP("linear_down", linear(d->act, L.wdown, d->x, d->x, H, c.ffn, TS_EPI_ADD, TS_F32));
+        if (fold) {
+            STEP("linear_o", folded(nullptr, d->attn, L.wo, d->x, d->x, H, QW, TS_EPI_ADD, TS_F32, true));
+            STEP("linear_gate_up", folded(L.ln2, nullptr, L.wgu, nullptr, d->act, 2 * c.ffn, H, TS_EPI_SWIGLU, TS_BF16, false));
+            STEP("linear_down", folded(nullptr, d->act, L.wdown, d->x, d->x, H, c.ffn, TS_EPI_ADD, TS_F32, l + 1 < c.layers));
+        } else {
+            STEP("linear_o", linear(d->attn, L.wo, d->x, d->x, H, QW, TS_EPI_ADD, TS_F32));
+            STEP("rms_norm", rms_norm(d->x, TS_F32, L.ln2, d->h, TS_BF16, rows, H, c.eps, nullptr, s));
+            STEP("linear_gate_up", linear(d->h, L.wgu, nullptr, d->act, 2 * c.ffn, H, TS_EPI_SWIGLU, TS_BF16));
+            STEP("linear_down", linear(d->act, L.wdown, d->x, d->x, H, c.ffn, TS_EPI_ADD, TS_F32));
+        }
     }
     // Only the wanted rows go through the final norm and the unembedding.
     STEP("rms_norm", rms_norm(d->x, TS_F32, d->norm, d->h_out, TS_BF16, n_out, H, c.eps, n_out == rows ? nullptr : d->out_rows, s));
@@ -265,6 +319,7 @@ int ts_decoder_create(const ts_decoder_config *config, ts_decoder **out) {
     A(dev_alloc(d, &d->attn, R * QW));
     A(dev_alloc(d, &d->act, R * c.ffn));
     A(dev_alloc(d, &d->h_out, R * H));
+    A(dev_alloc(d, &d->sumsq, R * 32));
     A(dev_alloc(d, &d->logits, (size_t)d->max_out * c.vocab));
     A(dev_alloc(d, &d->tokens, R));
     A(dev_alloc(d, &d->slots, R));
@@ -472,11 +527,12 @@ uint32_t ts_decoder_launches_per_step(ts_decoder *d, uint32_t rows, uint32_t key
     auto lin = [&](uint32_t m, uint32_t n, uint32_t k, int epi) -> uint32_t {
         return linear_workspace(m, n, k, epi) > 0 ? 2 : 1;
     };
-    uint32_t per_layer = 2 /*norms*/ + 1 /*append*/ + 1 /*attention*/ +
+    const bool fold = fold_parts(d, rows) != 0;
+    uint32_t per_layer = (fold ? 0 : 2) /*norms*/ + 1 /*append*/ + 1 /*attention*/ +
                          (attend_rows_workspace_bytes(rows, keys, c.heads, c.kv_heads, c.head_dim) > 0 ? 1 : 0) +
                          lin(rows, d->qkv_n, c.hidden, TS_EPI_NONE) + lin(rows, c.hidden, c.heads * c.head_dim, TS_EPI_ADD) +
                          lin(rows, 2 * c.ffn, c.hidden, TS_EPI_SWIGLU) + lin(rows, c.hidden, c.ffn, TS_EPI_ADD);
-    return 1 /*gather*/ + c.layers * per_layer + 1 /*final norm*/ + lin(rows, c.vocab, c.hidden, TS_EPI_NONE) + 2 /*top-1*/;
+    return 1 /*gather*/ + c.layers * per_layer + (fold ? 1 : 0) /*layer 0's first norm*/ + 1 /*final norm*/ + lin(rows, c.vocab, c.hidden, TS_EPI_NONE) + 2 /*top-1*/;
 }
 
 uint64_t ts_decoder_graph_replays(ts_decoder *d) { return d ? d->replays : 0; }

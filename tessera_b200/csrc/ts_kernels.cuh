@@ -18,8 +18,20 @@ int linear_umma(const void *x, const void *w, const void *a0, void *out, uint32_
                 cudaStream_t stream);
 bool stream_supports(uint32_t m, uint32_t n, uint32_t k, int epilogue);
 int stream_take_status();
+// Optional fusions of the decode step around a streamed linear.
+struct StreamFused {
+    // x = bf16(norm_x * inv_rms * norm_w): norm_x f32 [m, k], norm_w f32 [k], norm_ss f32 [m, norm_parts]
+    // partial sums of squares of norm_x's rows (any split that adds up to the whole row).
+    const float *norm_x = nullptr, *norm_w = nullptr, *norm_ss = nullptr;
+    uint32_t norm_parts = 0;
+    float norm_eps = 0.0f;
+    // f32 [m, stream_sumsq_parts(...)]: per 128-column tile, the sum of squares of the finished output rows.
+    float *ss_out = nullptr;
+};
+// Parts per row that a linear of this shape leaves in ss_out, or 0 when it cannot.
+uint32_t stream_sumsq_parts(uint32_t m, uint32_t n, uint32_t k, int epilogue);
 int linear_stream(const void *x, const void *w, const void *a0, void *out, uint32_t m, uint32_t n, uint32_t k,
-                  int epilogue, float scale, int out_dtype, cudaStream_t stream);
+                  int epilogue, float scale, int out_dtype, cudaStream_t stream, const StreamFused *fused = nullptr);
 // Picks the kernel family for a linear: TS_LINEAR_SKINNY, TS_LINEAR_STREAM, TS_LINEAR_UMMA, or -1.
 int pick_linear_path(uint32_t m, uint32_t n, uint32_t k, int epilogue, int path);
 size_t attend_rows_workspace_bytes(uint32_t rows, uint32_t keys, uint32_t heads, uint32_t kv_heads, uint32_t width);
