@@ -177,6 +177,16 @@ __device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, u
         : "memory");
 }
 
+// Hands registers from one warp group to another (all four warps of a group execute it).
+template <uint32_t N>
+__device__ __forceinline__ void setmaxnreg_inc() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <uint32_t N>
+__device__ __forceinline__ void setmaxnreg_dec() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+
 // ---- tcgen05 / TMEM ---------------------------------------------------------
 
 // Whole warp.  Writes the TMEM base address of `cols` columns (a power of two >= 32) to *dst.
