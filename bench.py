@@ -43,7 +43,7 @@ FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used only when ME
 # committed ncu captures (profiles/decode_kernels_sections.md names the commands).  The captures ran on
 # small cases of the same kernels; traffic grows in proportion to the rows, keys and weights a launch
 # visits, so a launch's traffic is this ratio times its algorithmic bytes.  None: no capture.
-NCU_TRAFFIC_RATIO = {"attend_rows": 50.663 / 50.856, "linear_unembed": 340.64 / 350.19,
+NCU_TRAFFIC_RATIO = {"attend_rows": 50.670 / 50.856, "linear_unembed": 340.64 / 350.19,
                      "linear_qkv": 8.585 / 8.520}
 
 

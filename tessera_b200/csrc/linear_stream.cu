@@ -127,7 +127,9 @@ __device__ __forceinline__ void store_out(void *out, int out_dtype, size_t at, f
     else reinterpret_cast<uint16_t *>(out)[at] = bf16_bits(v);
 }
 
-template <uint32_t BN>
+// FUSED compiles in the normalised-input build and the sums of squares; the plain instantiation carries
+// neither (they cost registers and a few percent of a decode step even when unused).
+template <uint32_t BN, bool FUSED>
 __global__ void __launch_bounds__(kThreads, 1)
 linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                      const StreamParams p) {
@@ -188,7 +190,7 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
             mbar_init(&acc_full[s], 1);
             mbar_init(&acc_empty[s], kEpiWarps);
         }
-        mbar_init(b_full, p.norm_x ? kEpiWarps : 1);
+        mbar_init(b_full, (FUSED && p.norm_x) ? kEpiWarps : 1);
         mbar_init(red_full, kEpiWarps);
         // S > 1: one local arrival announces the bytes and the senders' asynchronous stores complete
         // them; S == 1: plain stores, one arrival per warp.
@@ -215,7 +217,7 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
             bool ok = true;
             // x is what the upstream kernel wrote: wait for it, then fetch this block's k slice once.
             pdl_wait();
-            if (!p.norm_x) {
+            if (!(FUSED && p.norm_x)) {
                 mbar_expect_tx(b_full, kbs * kBBytes);
                 for (uint32_t j = 0; j < kbs; j++)
                     tma_load_2d(smem_b + j * kBBytes, &map_x, b_full, (int32_t)((kb_begin + j) * kBlockK), 0);
@@ -274,7 +276,7 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
         const uint32_t recv_base = smem_addr(recv);
         const uint32_t bar_local = smem_addr(recv_full);
         bool ok = true;
-        if (p.norm_x) {
+        if (FUSED && p.norm_x) {
             // Build this block's k slice of x in shared memory, normalised: what the TMA copy of a
             // ready-made bf16 x would have left there, 128-byte rows with the 16-byte pieces of row r
             // at piece ^ (r & 7).  Warp e takes batch rows [e BN/8, (e+1) BN/8); a half warp covers the
@@ -426,7 +428,7 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                             if (p.epilogue == TS_EPI_SCALE) r *= p.scale;
                             store_out(p.out, p.out_dtype, at, r);
                         }
-                        if (p.ss_out) {  // the host only asks for this when n is a multiple of 128: every lane is here
+                        if (FUSED && p.ss_out) {  // the host only asks for this when n is a multiple of 128: every lane is here
                             const float t = warp_sum(r * r);
                             if (lane == 0) red[q * 128 + cc + j] = t;
                         }
@@ -435,7 +437,7 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(recv_free);
-            if (p.ss_out) {
+            if (FUSED && p.ss_out) {
                 // The four lane quarters of a column meet in shared memory; one thread per batch column
                 // adds them in a fixed order.
                 __syncwarp();
@@ -503,10 +505,10 @@ bool plan_stream(uint32_t m, uint32_t n, uint32_t k, int epilogue, StreamPlan *o
 
 __device__ int g_stream_status = 0;
 
-template <uint32_t BN>
+template <uint32_t BN, bool FUSED>
 cudaError_t launch_stream(const CUtensorMap &mw, const CUtensorMap &mx, const StreamParams &p, const StreamPlan &s,
                           cudaStream_t stream) {
-    auto kernel = linear_stream_kernel<BN>;
+    auto kernel = linear_stream_kernel<BN, FUSED>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
@@ -618,11 +620,12 @@ int linear_stream(const void *x, const void *w, const void *a0, void *out, uint3
     TS_CUDA(cudaGetSymbolAddress((void **)&status, g_stream_status));
     p.status = status;
     cudaError_t e;
+    const bool any_fused = p.norm_x || p.ss_out;
     switch (s.bn) {
-    case 16: e = launch_stream<16>(map_w, map_x, p, s, stream); break;
-    case 32: e = launch_stream<32>(map_w, map_x, p, s, stream); break;
-    case 64: e = launch_stream<64>(map_w, map_x, p, s, stream); break;
-    default: e = launch_stream<128>(map_w, map_x, p, s, stream); break;
+    case 16: e = any_fused ? launch_stream<16, true>(map_w, map_x, p, s, stream) : launch_stream<16, false>(map_w, map_x, p, s, stream); break;
+    case 32: e = any_fused ? launch_stream<32, true>(map_w, map_x, p, s, stream) : launch_stream<32, false>(map_w, map_x, p, s, stream); break;
+    case 64: e = any_fused ? launch_stream<64, true>(map_w, map_x, p, s, stream) : launch_stream<64, false>(map_w, map_x, p, s, stream); break;
+    default: e = any_fused ? launch_stream<128, true>(map_w, map_x, p, s, stream) : launch_stream<128, false>(map_w, map_x, p, s, stream); break;
     }
     if (e != cudaSuccess)
         return fail(TS_ERR_CUDA, "launch of linear_stream failed: %s (%d) %s", cudaGetErrorName(e), (int)e,
