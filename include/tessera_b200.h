@@ -142,6 +142,19 @@ int ts_attend_rows_bf16(const void *q, const void *k, const void *v, void *out, 
                         uint32_t heads, uint32_t kv_heads, uint32_t width, uint32_t back, float scale,
                         void *workspace, size_t workspace_bytes, void *stream);
 
+/* A decode step's ts_qk_norm_rope_append_bf16 and causal ts_attend_rows_bf16 in one launch: the attention
+ * kernel norms and rotates the row's q heads and its new key itself, appends the key and value at
+ * kept_row(slot, position) and attends over positions [0, position].  Same arithmetic, same bits as the
+ * two launches.  Preconditions: no two rows of the call share a slot (a row must not read a key that
+ * another row of the same call appends: that is a prefill, use the two launches); head width 128; a dense
+ * layout or pages of >= 32 rows, with kept->rows set.  Workspace: ts_attend_rows_workspace_bytes.
+ *   qkv [rows, (heads + 2 kv_heads) * width] bf16 (q heads, k heads, v heads); k_rows, v_rows are written. */
+int ts_attend_rows_append_bf16(const void *qkv, const float *q_norm, const float *k_norm, const float *inv_freq,
+                               void *k_rows, void *v_rows, void *out, const uint32_t *slots,
+                               const uint32_t *positions, const ts_kept *kept, uint32_t rows, uint32_t keys,
+                               uint32_t heads, uint32_t kv_heads, uint32_t width, float eps, float scale,
+                               void *workspace, size_t workspace_bytes, void *stream);
+
 /* Writes rows of x at kept_row(slot, position).  Replaces `scatter`
  * (engine/plan/lower/src/kernels/scatter.rs:11-83).  x [rows, width] bf16, out [kept rows, width]. */
 int ts_scatter_bf16(const void *x, const uint32_t *slots, const uint32_t *positions, void *out,

@@ -49,6 +49,8 @@ SIGNATURES = {
     "ts_linear_fused_bf16": (i32, [vp, vp, vp, vp, u32, u32, u32, i32, f32, i32, C.POINTER(TsLinearFused), vp]),
     "ts_attend_rows_workspace_bytes": (sz, [u32, u32, u32, u32, u32]),
     "ts_attend_rows_bf16": (i32, [vp, vp, vp, vp, vp, vp, C.POINTER(TsKept), u32, u32, u32, u32, u32, u32, f32, vp, sz, vp]),
+    "ts_attend_rows_append_bf16": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, vp, C.POINTER(TsKept), u32, u32, u32, u32, u32, f32,
+                                         f32, vp, sz, vp]),
     "ts_attend_workspace_bytes": (sz, [u32, u32, u32, u32, u32, u32]),
     "ts_attend_bf16": (i32, [vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u32, u32, u32, f32, vp, sz, vp]),
     "ts_scatter_bf16": (i32, [vp, vp, vp, vp, C.POINTER(TsKept), u32, u32, vp]),

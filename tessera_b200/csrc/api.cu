@@ -244,6 +244,33 @@ int ts_attend_rows_bf16(const void *q, const void *k, const void *v, void *out, 
                        workspace, workspace_bytes, (cudaStream_t)stream, 0, nullptr, kept->rows);
 }
 
+int ts_attend_rows_append_bf16(const void *qkv, const float *q_norm, const float *k_norm, const float *inv_freq, void *k_rows,
+                               void *v_rows, void *out, const uint32_t *slots, const uint32_t *positions,
+                               const ts_kept *kept, uint32_t rows, uint32_t keys, uint32_t heads, uint32_t kv_heads,
+                               uint32_t width, float eps, float scale, void *workspace, size_t workspace_bytes,
+                               void *stream) {
+    TS_REQUIRE(qkv && inv_freq && k_rows && v_rows && out && slots && positions, "attend_rows_append: a buffer is NULL");
+    TS_REQUIRE(aligned16(qkv) && aligned16(k_rows) && aligned16(v_rows) && aligned16(out),
+               "attend_rows_append: buffers must be 16-byte aligned");
+    TS_REQUIRE(kv_heads > 0 && heads % kv_heads == 0, "attend_rows_append: %u heads do not split over %u kv heads", heads, kv_heads);
+    KeptDev dev;
+    bool contiguous;
+    int rc = check_kept(kept, &dev, &contiguous);
+    if (rc != TS_OK) return rc;
+    TS_REQUIRE(attend_rows_fused_supports(contiguous, width, kept->rows),
+               "attend_rows_append: needs head width 128 (got %u) and a dense or >= 32-row paged layout with kept->rows set",
+               width);
+    if (rows == 0 || keys == 0) return TS_OK;
+    RowsFused f;
+    f.qkv = qkv;
+    f.q_norm = q_norm;
+    f.k_norm = k_norm;
+    f.inv_freq = inv_freq;
+    f.eps = eps;
+    return attend_rows(nullptr, k_rows, v_rows, out, slots, positions, dev, contiguous, rows, keys, heads, kv_heads, width,
+                       0xFFFFFFFFu, scale, workspace, workspace_bytes, (cudaStream_t)stream, 0, nullptr, kept->rows, &f);
+}
+
 size_t ts_attend_workspace_bytes(uint32_t seqs, uint32_t queries, uint32_t keys, uint32_t heads, uint32_t kv_heads,
                                  uint32_t width) {
     if (flash_supports(width)) return 0;

@@ -26,6 +26,7 @@
 // be in flight, which is what keeps HBM busy (0.96 of the copy rate at 4096 keys per row).  `attend_rows_kernel` loads straight into registers and covers every other width and layout.
 #include <cmath>
 
+#include "head_prep.cuh"
 #include "ts_common.cuh"
 #include "ts_kernels.cuh"
 #include "ts_ptx.cuh"
@@ -48,6 +49,13 @@ struct RowsParams {
     float *part_o;   // [rows, heads, chunks, WIDTH]
     float *part_ml;  // [rows, heads, chunks, 2]
     uint32_t contiguous;  // a 32-aligned block of 32 positions is 32 consecutive kept rows
+    // Fused front (TMA-fed kernel only; qkv NULL = off): q, k, v come raw from the projection as
+    // qkv [rows, (heads + 2 kv_heads) * 128]; the kernel norms and rotates q and k itself, appends k and
+    // v at kept_row(slot, position) (k, v are then written, not only read) and attends.
+    const uint16_t *qkv;
+    const float *q_norm, *k_norm, *inv_freq;
+    uint16_t *k_out, *v_out;
+    float eps;
 };
 
 __device__ __forceinline__ uint4 ldg16(const uint16_t *p) {
@@ -279,11 +287,12 @@ struct TmaShared {
     static constexpr size_t ml = o + sizeof(float) * kWarps * G * 128;  // float [kWarps][G][2]
     static constexpr size_t bars = ml + sizeof(float) * kWarps * G * 2; // full[kTmaStages], empty[kTmaStages]
     static constexpr size_t flag = bars + sizeof(uint64_t) * 2 * kTmaStages;
-    static constexpr size_t bytes = flag + 16;
+    static constexpr size_t prep = flag + 16;                       // bf16 [G + 2][128]: prepared q heads, k, v
+    static constexpr size_t bytes = prep + (G + 2) * 256;
 };
 
 struct ItemRange {
-    uint32_t row, hg, chunk, slot, lo, hi, last;
+    uint32_t row, hg, chunk, slot, pos, lo, hi, last;
 };
 
 __device__ __forceinline__ ItemRange item_range(const RowsParams &p, uint32_t item, uint32_t n_hg) {
@@ -293,7 +302,7 @@ __device__ __forceinline__ ItemRange item_range(const RowsParams &p, uint32_t it
     r.hg = t % n_hg;
     r.row = t / n_hg;
     r.slot = p.slots[r.row];
-    const uint32_t pos = p.positions[r.row];
+    const uint32_t pos = r.pos = p.positions[r.row];
     uint32_t reach = pos + p.ahead;
     if (reach < pos || reach == 0xFFFFFFFFu) reach = 0xFFFFFFFEu;
     r.last = min(reach + 1, p.keys);
@@ -394,10 +403,41 @@ attend_rows_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                         p.out[((size_t)r.row * p.heads + head0) * WIDTH + i] = 0;
                 continue;
             }
+            const bool own_key_here = p.qkv && r.pos >= r.lo && r.pos < r.hi;  // this item holds the row's new key
+            if (p.qkv) {
+                // Prepare the G query heads and the row's new key and value: a warp per head, as the
+                // stand-alone append kernel does it (same code, same bits), into shared memory.
+                uint16_t *prep = reinterpret_cast<uint16_t *>(smem + Sh::prep);
+                const uint32_t per_row = p.heads + 2 * p.kv_heads, kvh = head0 / group;
+                for (uint32_t u = cw; u < (uint32_t)G + 2; u += kWarps) {
+                    const bool is_q = u < (uint32_t)G, is_v = u == (uint32_t)G + 1;
+                    if (!is_q && !own_key_here) continue;
+                    const uint32_t h = is_q ? head0 + u : (is_v ? p.heads + p.kv_heads + kvh : p.heads + kvh);
+                    const uint16_t *src = p.qkv + ((size_t)r.row * per_row + h) * WIDTH;
+                    uint16_t *dst = prep + u * WIDTH;
+                    if (is_v) {
+                        if (lane < 16) reinterpret_cast<uint4 *>(dst)[lane] = reinterpret_cast<const uint4 *>(src)[lane];
+                    } else {
+                        uint16_t lo[2], hi[2];
+                        norm_rope_head<WIDTH>(src, is_q ? p.q_norm : p.k_norm, p.inv_freq, r.pos, p.eps, lane, lo, hi);
+                        *reinterpret_cast<uint32_t *>(dst + lane * 2) = (uint32_t)lo[0] | ((uint32_t)lo[1] << 16);
+                        *reinterpret_cast<uint32_t *>(dst + WIDTH / 2 + lane * 2) = (uint32_t)hi[0] | ((uint32_t)hi[1] << 16);
+                    }
+                    __syncwarp();
+                    // The first query-head group of a kv head also stores the new row for later steps.
+                    if (!is_q && head0 % group == 0 && lane < 16) {
+                        const size_t at = ((size_t)kept_row(p.kept, r.slot, r.pos) * p.kv_heads + kvh) * WIDTH;
+                        reinterpret_cast<uint4 *>((is_v ? p.v_out : p.k_out) + at)[lane] = reinterpret_cast<const uint4 *>(dst)[lane];
+                    }
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory");
+            }
             float q[G][8];
 #pragma unroll
             for (int g = 0; g < G; g++) {
-                uint4 v = *reinterpret_cast<const uint4 *>(p.q + ((size_t)r.row * p.heads + head0 + g) * WIDTH + piece * 8);
+                uint4 v;
+                if (p.qkv) v = *reinterpret_cast<const uint4 *>(smem + Sh::prep + g * 256 + piece * 16);
+                else v = *reinterpret_cast<const uint4 *>(p.q + ((size_t)r.row * p.heads + head0 + g) * WIDTH + piece * 8);
                 q[g][0] = bf16_lo(v.x); q[g][1] = bf16_hi(v.x); q[g][2] = bf16_lo(v.y); q[g][3] = bf16_hi(v.y);
                 q[g][4] = bf16_lo(v.z); q[g][5] = bf16_hi(v.z); q[g][6] = bf16_lo(v.w); q[g][7] = bf16_hi(v.w);
             }
@@ -419,6 +459,15 @@ attend_rows_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                     const uint32_t base = blk * 32;
                     const uint32_t own = base + piece * KPI + gidx;
                     const bool own_ok = own >= r.lo && own < r.hi;
+                    if (own_key_here && r.pos - base < 32) {
+                        // The copy read this row before (or while) it was appended: take it from the
+                        // prepared values instead.
+                        const uint8_t *from = smem + Sh::prep + (G + (lane >> 4)) * 256 + (lane & 15) * 16;
+                        uint8_t *to = (lane < 16 ? const_cast<uint8_t *>(tile_k) : tile_v) + (r.pos - base) * 256 + (lane & 15) * 16;
+                        *reinterpret_cast<uint4 *>(to) = *reinterpret_cast<const uint4 *>(from);
+                        fence_async_shared();
+                        __syncwarp();
+                    }
                     if (base < r.lo || base + 32 > r.hi) {
                         // An edge block: rows outside the range may hold anything (a page's unwritten
                         // tail); zero their V so that a zero probability cannot meet a NaN.
@@ -611,6 +660,10 @@ int launch_rows_tma(const CUtensorMap &map_k, const CUtensorMap &map_v, const Ro
 
 }  // namespace
 
+bool attend_rows_fused_supports(bool contiguous, uint32_t width, uint32_t kept_rows) {
+    return width == 128 && contiguous && kept_rows > 0;
+}
+
 int rows_take_status() {
     int v = 0, zero = 0;
     if (cudaMemcpyFromSymbol(&v, g_rows_status, sizeof(int)) != cudaSuccess) return TS_ERR_CUDA;
@@ -628,7 +681,8 @@ size_t attend_rows_workspace_bytes(uint32_t rows, uint32_t keys, uint32_t heads,
 int attend_rows(const void *q, const void *k, const void *v, void *out, const uint32_t *slots,
                 const uint32_t *positions, const KeptDev &kept, bool contiguous, uint32_t rows, uint32_t keys,
                 uint32_t heads, uint32_t kv_heads, uint32_t width, uint32_t back, float scale, void *workspace,
-                size_t workspace_bytes, cudaStream_t stream, uint32_t ahead, const uint32_t *lens, uint32_t kept_rows) {
+                size_t workspace_bytes, cudaStream_t stream, uint32_t ahead, const uint32_t *lens, uint32_t kept_rows,
+                const RowsFused *fused) {
     RowsPlan s = plan_rows(rows, keys, heads, kv_heads);
     size_t need = s.chunks > 1 ? (size_t)rows * heads * s.chunks * (width + 2) * sizeof(float) : 0;
     TS_REQUIRE(workspace_bytes >= need && (need == 0 || workspace != nullptr),
@@ -660,6 +714,19 @@ int attend_rows(const void *q, const void *k, const void *v, void *out, const ui
     // row count to bound the tensor maps with.
     const bool tma = width == 128 && contiguous && kept_rows > 0 &&
                      (uint64_t)rows * (heads / s.g) * s.chunks < 0xFFFFFFFFull;
+    if (fused) {
+        TS_REQUIRE(tma && ahead == 0 && lens == nullptr && back == 0xFFFFFFFFu,
+                   "attend_rows (fused front): needs head width 128, a dense or >= 32-row paged layout with a known "
+                   "row count, and the causal mask");
+        TS_REQUIRE(fused->qkv && fused->inv_freq, "attend_rows (fused front): qkv or inv_freq is NULL");
+        p.qkv = (const uint16_t *)fused->qkv;
+        p.q_norm = fused->q_norm;
+        p.k_norm = fused->k_norm;
+        p.inv_freq = fused->inv_freq;
+        p.eps = fused->eps;
+        p.k_out = (uint16_t *)const_cast<void *>(k);
+        p.v_out = (uint16_t *)const_cast<void *>(v);
+    }
     if (tma) {
         CUtensorMap map_k, map_v;
         const uint64_t cols = (uint64_t)kv_heads * width;

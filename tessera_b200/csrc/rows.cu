@@ -3,6 +3,7 @@
 // take + softmax.  Each follows the reference kernel it replaces (cited per kernel).
 #include <cmath>
 
+#include "head_prep.cuh"
 #include "ts_common.cuh"
 
 namespace ts {
@@ -117,35 +118,13 @@ __global__ void __launch_bounds__(128) qk_norm_rope_append_kernel(
         return;
     }
     // lane owns pairs j = lane * PER + e: elements j and j + WIDTH/2
-    float a[PER], b[PER];
-    float ss = 0.0f;
+    uint16_t lo[PER], hi[PER];
+    norm_rope_head<WIDTH>(src, gain, inv_freq, pos, eps, lane, lo, hi);
 #pragma unroll
     for (int e = 0; e < PER; e++) {
         const uint32_t j = lane * PER + e;
-        a[e] = __uint_as_float((uint32_t)src[j] << 16);
-        b[e] = __uint_as_float((uint32_t)src[j + WIDTH / 2] << 16);
-        ss = fmaf(a[e], a[e], ss);
-        ss = fmaf(b[e], b[e], ss);
-    }
-    if (gain) {
-        ss = warp_sum(ss);
-        const float inv = 1.0f / sqrtf(ss / (float)WIDTH + eps);
-#pragma unroll
-        for (int e = 0; e < PER; e++) {
-            const uint32_t j = lane * PER + e;
-            a[e] = a[e] * (inv * gain[j]);
-            b[e] = b[e] * (inv * gain[j + WIDTH / 2]);
-        }
-    }
-#pragma unroll
-    for (int e = 0; e < PER; e++) {
-        const uint32_t j = lane * PER + e;
-        float sn, cs;
-        sincosf((float)pos * inv_freq[j], &sn, &cs);
-        const float ra = a[e] * cs - b[e] * sn;
-        const float rb = a[e] * sn + b[e] * cs;
-        dst[j] = bf16_bits(ra);
-        dst[j + WIDTH / 2] = bf16_bits(rb);
+        dst[j] = lo[e];
+        dst[j + WIDTH / 2] = hi[e];
     }
 }
 

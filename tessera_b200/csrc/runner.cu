@@ -34,6 +34,7 @@ struct ts_decoder {
     uint16_t *act = nullptr;     // [max_rows, ffn]
     uint16_t *h_out = nullptr;   // final normed rows of the wanted rows [max_rows, hidden]
     float *sumsq = nullptr;      // per-tile sums of squares of the residual rows [max_rows, 32]
+    bool last_distinct = false;  // the rows of the last launch sat in slots of their own
     float *logits = nullptr;     // [max_out, vocab]
     uint32_t max_out = 0;
     uint32_t *tokens = nullptr, *slots = nullptr, *positions = nullptr, *out_rows = nullptr, *ids = nullptr;
@@ -135,8 +136,20 @@ uint32_t fold_parts(const ts_decoder *d, uint32_t rows) {
     return ok ? parts : 0;
 }
 
+// Whether the attention launch also does the per-head norm, the rotation and the append: only when no
+// two rows of the launch share a slot (a row must not read a key that another row of the same launch
+// appends), at head width 128 over a layout the TMA-fed kernel takes.  TS_FUSE_APPEND=0 turns it off.
+bool append_in_attention(const ts_decoder *d, bool distinct) {
+    static const bool off = [] {
+        const char *v = getenv("TS_FUSE_APPEND");
+        return v && v[0] == '0';
+    }();
+    const bool contiguous = d->c.page == 0 || d->c.page >= 32;
+    return !off && distinct && attend_rows_fused_supports(contiguous, d->c.head_dim, d->kept_total_rows);
+}
+
 // The step list for `rows` rows that see at most `keys` positions; logits for n_out rows.
-int enqueue(ts_decoder *d, uint32_t rows, uint32_t keys, uint32_t n_out, bool feedback, cudaStream_t s,
+int enqueue(ts_decoder *d, uint32_t rows, uint32_t keys, uint32_t n_out, bool feedback, bool distinct, cudaStream_t s,
             uint32_t *count) {
     const ts_decoder_config &c = d->c;
     const uint32_t H = c.hidden, D = c.head_dim, QW = c.heads * D;
@@ -198,12 +211,25 @@ int enqueue(ts_decoder *d, uint32_t rows, uint32_t keys, uint32_t n_out, bool fe
             STEP("rms_norm", rms_norm(d->x, TS_F32, L.ln1, d->h, TS_BF16, rows, H, c.eps, nullptr, s));
             STEP("linear_qkv", linear(d->h, L.wqkv, nullptr, d->qkv, d->qkv_n, H, TS_EPI_NONE, TS_BF16));
         }
-        STEP("qk_norm_rope_append", qk_norm_rope_append(d->qkv, c.qk_norm ? L.q_norm : nullptr, c.qk_norm ? L.k_norm : nullptr, d->inv_freq,
-                                 d->slots, d->positions, d->q, L.k_rows, L.v_rows, kd, rows, c.heads, c.kv_heads, D,
-                                 c.eps, s));
-        STEP("attend_rows", attend_rows(d->q, L.k_rows, L.v_rows, d->attn, d->slots, d->positions, kd, contiguous, rows, keys, c.heads,
-                         c.kv_heads, D, 0xFFFFFFFFu, scale, d->workspace, d->workspace_bytes, s, 0, nullptr,
-                         d->kept_total_rows));
+        if (append_in_attention(d, distinct)) {
+            // One row per slot (a decode step): the attention kernel norms, rotates and appends itself.
+            RowsFused f;
+            f.qkv = d->qkv;
+            f.q_norm = c.qk_norm ? L.q_norm : nullptr;
+            f.k_norm = c.qk_norm ? L.k_norm : nullptr;
+            f.inv_freq = d->inv_freq;
+            f.eps = c.eps;
+            STEP("attend_rows", attend_rows(nullptr, L.k_rows, L.v_rows, d->attn, d->slots, d->positions, kd, contiguous, rows, keys,
+                             c.heads, c.kv_heads, D, 0xFFFFFFFFu, scale, d->workspace, d->workspace_bytes, s, 0, nullptr,
+                             d->kept_total_rows, &f));
+        } else {
+            STEP("qk_norm_rope_append", qk_norm_rope_append(d->qkv, c.qk_norm ? L.q_norm : nullptr, c.qk_norm ? L.k_norm : nullptr, d->inv_freq,
+                                     d->slots, d->positions, d->q, L.k_rows, L.v_rows, kd, rows, c.heads, c.kv_heads, D,
+                                     c.eps, s));
+            STEP("attend_rows", attend_rows(d->q, L.k_rows, L.v_rows, d->attn, d->slots, d->positions, kd, contiguous, rows, keys, c.heads,
+                             c.kv_heads, D, 0xFFFFFFFFu, scale, d->workspace, d->workspace_bytes, s, 0, nullptr,
+                             d->kept_total_rows));
+        }
         if (attend_rows_workspace_bytes(rows, keys, c.heads, c.kv_heads, D) > 0) launches++;
         if (fold) {
             STEP("linear_o", folded(nullptr, d->attn, L.wo, d->x, d->x, H, QW, TS_EPI_ADD, TS_F32, true));
@@ -227,16 +253,16 @@ int enqueue(ts_decoder *d, uint32_t rows, uint32_t keys, uint32_t n_out, bool fe
 }
 
 // Replays the captured graph for these sizes, capturing it on first sight.
-int submit(ts_decoder *d, uint32_t rows, uint32_t keys, uint32_t n_out, bool feedback, cudaStream_t s) {
+int submit(ts_decoder *d, uint32_t rows, uint32_t keys, uint32_t n_out, bool feedback, bool distinct, cudaStream_t s) {
     set_pdl(d->c.pdl != 0);
-    if (!d->c.graphs) return enqueue(d, rows, keys, n_out, feedback, s, nullptr);
-    const uint64_t key = ((uint64_t)rows << 40) | ((uint64_t)keys << 16) | ((uint64_t)(n_out & 0x7FFF) << 1) |
-                         (feedback ? 1 : 0);
+    if (!d->c.graphs) return enqueue(d, rows, keys, n_out, feedback, distinct, s, nullptr);
+    const uint64_t key = ((uint64_t)(distinct ? 1 : 0) << 63) | ((uint64_t)rows << 40) | ((uint64_t)keys << 16) |
+                         ((uint64_t)(n_out & 0x7FFF) << 1) | (feedback ? 1 : 0);
     auto it = d->graphs.find(key);
     if (it == d->graphs.end()) {
         cudaGraph_t graph = nullptr;
         TS_CUDA(cudaStreamBeginCapture(s, cudaStreamCaptureModeRelaxed));
-        int rc = enqueue(d, rows, keys, n_out, feedback, s, nullptr);
+        int rc = enqueue(d, rows, keys, n_out, feedback, distinct, s, nullptr);
         cudaError_t e = cudaStreamEndCapture(s, &graph);
         if (rc != TS_OK) {
             if (graph) cudaGraphDestroy(graph);
@@ -461,9 +487,19 @@ int ts_decoder_step(ts_decoder *d, const uint32_t *tokens, const uint32_t *slots
         memcpy(st + 3 * R, out_rows, n_out * 4);
         TS_CUDA(cudaMemcpyAsync(d->out_rows, st + 3 * R, n_out * 4, cudaMemcpyHostToDevice, s));
     }
+    // Do all rows sit in slots of their own (a decode step), or does a slot take several (a prefill)?
+    bool distinct = true;
+    {
+        std::vector<bool> seen(c.slots, false);
+        for (uint32_t r = 0; r < rows && distinct; r++) {
+            distinct = !seen[slots[r]];
+            seen[slots[r]] = true;
+        }
+    }
     const uint32_t keys = keys_bucket(d, furthest);
-    int rc = submit(d, rows, keys, n_out, false, s);
+    int rc = submit(d, rows, keys, n_out, false, distinct, s);
     if (rc != TS_OK) return rc;
+    d->last_distinct = distinct;
     d->last_rows = rows;
     d->last_out = n_out;
     d->last_keys = furthest;
@@ -487,7 +523,7 @@ int ts_decoder_run_resident(ts_decoder *d, uint32_t steps, void *stream) {
         const uint32_t furthest = d->last_keys + 1;
         TS_REQUIRE(furthest <= d->c.context, "decoder resident loop: position %u is past the context of %u",
                    furthest - 1, d->c.context);
-        int rc = submit(d, d->last_rows, keys_bucket(d, furthest), d->last_rows, true, s);
+        int rc = submit(d, d->last_rows, keys_bucket(d, furthest), d->last_rows, true, d->last_distinct, s);
         if (rc != TS_OK) return rc;
         d->last_keys = furthest;
         for (auto &p : d->host_positions) p++;
@@ -528,7 +564,8 @@ uint32_t ts_decoder_launches_per_step(ts_decoder *d, uint32_t rows, uint32_t key
         return linear_workspace(m, n, k, epi) > 0 ? 2 : 1;
     };
     const bool fold = fold_parts(d, rows) != 0;
-    uint32_t per_layer = (fold ? 0 : 2) /*norms*/ + 1 /*append*/ + 1 /*attention*/ +
+    uint32_t per_layer = (fold ? 0 : 2) /*norms*/ + (append_in_attention(d, d->last_distinct) ? 0 : 1) /*append*/ +
+                         1 /*attention*/ +
                          (attend_rows_workspace_bytes(rows, keys, c.heads, c.kv_heads, c.head_dim) > 0 ? 1 : 0) +
                          lin(rows, d->qkv_n, c.hidden, TS_EPI_NONE) + lin(rows, c.hidden, c.heads * c.head_dim, TS_EPI_ADD) +
                          lin(rows, 2 * c.ffn, c.hidden, TS_EPI_SWIGLU) + lin(rows, c.hidden, c.ffn, TS_EPI_ADD);
@@ -554,7 +591,7 @@ int ts_decoder_profile(ts_decoder *d, uint32_t steps, void *stream) {
         int rc = gate(d->gate_flag, s);
         if (rc != TS_OK) return rc;
         d->profiling = true;
-        rc = enqueue(d, d->last_rows, keys_bucket(d, furthest), d->last_rows, true, s, nullptr);
+        rc = enqueue(d, d->last_rows, keys_bucket(d, furthest), d->last_rows, true, d->last_distinct, s, nullptr);
         d->profiling = false;
         *d->gate_flag = 1;  // every launch of the step is queued: let them run back to back
         if (rc != TS_OK) return rc;

@@ -35,11 +35,22 @@ int linear_stream(const void *x, const void *w, const void *a0, void *out, uint3
 // Picks the kernel family for a linear: TS_LINEAR_SKINNY, TS_LINEAR_STREAM, TS_LINEAR_UMMA, or -1.
 int pick_linear_path(uint32_t m, uint32_t n, uint32_t k, int epilogue, int path);
 size_t attend_rows_workspace_bytes(uint32_t rows, uint32_t keys, uint32_t heads, uint32_t kv_heads, uint32_t width);
+// Fused front of the decode attention: q, k, v raw from the projection (qkv [rows, (heads + 2 kv_heads) * 128]
+// bf16); the kernel norms and rotates q and k, appends k and v at kept_row(slot, position) and attends.
+// Only where every row of the launch sits in a slot of its own (a decode step): a row must not read a
+// key another row of the same launch appends.
+struct RowsFused {
+    const void *qkv = nullptr;
+    const float *q_norm = nullptr, *k_norm = nullptr, *inv_freq = nullptr;
+    float eps = 0.0f;
+};
+bool attend_rows_fused_supports(bool contiguous, uint32_t width, uint32_t kept_rows);
 int attend_rows(const void *q, const void *k, const void *v, void *out, const uint32_t *slots,
                 const uint32_t *positions, const KeptDev &kept, bool contiguous, uint32_t rows, uint32_t keys,
                 uint32_t heads, uint32_t kv_heads, uint32_t width, uint32_t back, float scale, void *workspace,
                 size_t workspace_bytes, cudaStream_t stream, uint32_t ahead = 0, const uint32_t *lens = nullptr,
-                uint32_t kept_rows = 0);  // kept_rows: rows the K/V buffers hold; 0 = unknown
+                uint32_t kept_rows = 0,  // rows the K/V buffers hold; 0 = unknown
+                const RowsFused *fused = nullptr);
 int rows_take_status();
 bool flash_supports(uint32_t width);
 int flash_take_status();

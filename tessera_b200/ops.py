@@ -138,6 +138,25 @@ def attend_rows(q, k_rows, v_rows, slots, positions, kept: Kept, keys: int, *, s
     return out
 
 
+def attend_rows_append(qkv, q_norm, k_norm, inv_freq, k_rows, v_rows, slots, positions, kept: Kept, keys: int, heads: int,
+                       *, eps: float, scale: float, out=None):
+    """ts_attend_rows_append_bf16: per-head norm + rotation + append + causal attention in one launch.
+    Every row must sit in a slot of its own."""
+    rows = qkv.shape[0]
+    kv_heads, width = k_rows.shape[-2], k_rows.shape[-1]
+    if out is None:
+        out = torch.empty((rows, heads, width), dtype=torch.bfloat16, device=qkv.device)
+    nbytes = lib.ts_attend_rows_workspace_bytes(rows, keys, heads, kv_heads, width)
+    ws = workspace(nbytes, qkv.device)
+    kc = kept.c()
+    if kc.rows == 0:
+        kc.rows = k_rows.numel() // (kv_heads * width)
+    check(lib.ts_attend_rows_append_bf16(_ptr(qkv), _ptr(q_norm), _ptr(k_norm), _ptr(inv_freq), _ptr(k_rows), _ptr(v_rows),
+                                         _ptr(out), _ptr(slots), _ptr(positions), C.byref(kc), rows, keys, heads, kv_heads,
+                                         width, eps, scale, _ptr(ws), nbytes, _stream()))
+    return out
+
+
 FAR = 0xFFFFFFFF
 MASKS = {"causal": (FAR, 0), "bidirectional": (FAR, FAR)}
 

@@ -193,6 +193,53 @@ def test_norm_rope_append_then_attend_two_launches(layout):
         assert rel_error(widen(got), want) <= 2e-2  # q and k carry the rotation's rounding
 
 
+@pytest.mark.parametrize("layout,heads,kv_heads,context", [("dense", 16, 8, 200), ("paged", 16, 8, 200), ("paged", 8, 2, 700),
+                                                           ("paged", 4, 4, 1500)])
+def test_append_inside_attention_equals_the_two_launches(layout, heads, kv_heads, context):
+    # A decode step (every row in a slot of its own): one launch that norms, rotates, appends and attends
+    # must leave the same kept rows and the same outputs, bit for bit, as append followed by attention.
+    from tessera_b200 import ops
+    rng = np.random.default_rng(heads * 7 + context)
+    slots, width, eps, theta = 9, 128, 1e-6, 1e6
+    kept, row_fn, total = _layout(layout, slots, context, rng)
+    lengths = [int(v) for v in rng.integers(1, context, size=slots)]
+    lengths[0], lengths[1], lengths[2] = 1, 33, context   # first position, just past a tile, the last position
+    # the past of every slot (at least one row, so that the store's shape is fixed); the row at the last
+    # position is what the launches append
+    kd, vd, kb, vb = _fill_store(rng, slots, [max(n - 1, 1) for n in lengths], kv_heads, width, row_fn, total)
+    row_slots = list(rng.permutation(slots))[:7]
+    row_pos = [lengths[s] - 1 for s in row_slots]
+    rows = len(row_slots)
+    qkv = from_bits(normal_bf16(rng, (rows, (heads + 2 * kv_heads) * width)))
+    qn = torch.from_numpy(rng.standard_normal(width).astype(np.float32)).cuda()
+    kn = torch.from_numpy(rng.standard_normal(width).astype(np.float32)).cuda()
+    inv_freq = ops.rope_inv_freq(theta, width, "cuda")
+    ds, dp = dev_u32(row_slots), dev_u32(row_pos)
+
+    k1, v1 = from_bits(kb), from_bits(vb)
+    q_out = torch.empty((rows, heads, width), dtype=torch.bfloat16, device="cuda")
+    ops.qk_norm_rope_append(qkv, qn, kn, inv_freq, ds, dp, q_out, k1, v1, kept, heads, kv_heads, width, eps)
+    want = ops.attend_rows(q_out, k1, v1, ds, dp, kept, context, scale=0.11)
+
+    k2, v2 = from_bits(kb), from_bits(vb)
+    got = ops.attend_rows_append(qkv, qn, kn, inv_freq, k2, v2, ds, dp, kept, context, heads, eps=eps, scale=0.11)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    assert torch.equal(k1, k2) and torch.equal(v1, v2)
+    assert torch.equal(got, want)
+
+
+def test_append_inside_attention_refuses_other_layouts():
+    from tessera_b200 import TesseraError, ops
+    rng = np.random.default_rng(1)
+    kept, row_fn, total = _layout("paged16", 2, 64, rng)
+    z = torch.zeros((total, 2, 128), dtype=torch.bfloat16, device="cuda")
+    qkv = torch.zeros((2, 8 * 128), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(TesseraError):
+        ops.attend_rows_append(qkv, None, None, ops.rope_inv_freq(1e6, 128, "cuda"), z, z.clone(), dev_u32([0, 1]),
+                               dev_u32([3, 4]), kept, 64, 4, eps=1e-6, scale=0.1)
+
+
 def test_scatter_places_rows_bit_exactly():
     from tessera_b200 import ops
     rng = np.random.default_rng(2)
