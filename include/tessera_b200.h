@@ -88,18 +88,23 @@ int ts_linear_bf16(const void *x, const void *w, const void *a0, void *out, uint
 /* A decode-sized linear (m <= 128) with the RMS norms of the residual stream folded into its two
  * ends.  The reference runs `lane_norm` as a launch of its own between the residual add and the next
  * projection (engine/models/src/decoder.rs:327-389, engine/rules/kernels/src/lane_norm.rs:10-17); at
- * batch 64 that launch is pure latency, so here
- *   - a linear with the ADD epilogue and an f32 output can also leave, per output row, the sum of
- *     squares over each 128-column tile in ss_out [m, ts_linear_sumsq_parts(...)], and
- *   - the next linear can take its input as norm_x (f32 [m, k]) with the gain norm_w (f32 [k]) and those
- *     partial sums: it forms x = bf16(norm_x * (norm_w / sqrt(sum / k + eps))) itself, the value
- *     ts_rms_norm would have written.  Pass x = NULL then.
- * Either half may be left out (NULL pointers). */
+ * batch 64 that launch is pure latency.  Since rms_norm(row) * gain = (row * gain) / rms(row), the
+ * 1/rms factor commutes with the projection:
+ *   - out: a linear with the ADD epilogue and an f32 output can also leave xs_out = bf16(out * xs_gain),
+ *     the next projection's input, and per output row the sum of squares over each 128-column tile in
+ *     ss_out [m, ts_linear_sumsq_parts(...)];
+ *   - in: the next linear takes x = that xs and row_ss = those sums, and multiplies its output rows by
+ *     1 / sqrt(sum(row_ss[row, :]) / k + row_eps) before its epilogue.
+ * The product differs from the unfolded one by where the bf16 rounding of the normed row falls (before
+ * instead of after the 1/rms factor): same size of error, not the same bits.  Either half may be left
+ * out (NULL pointers). */
 typedef struct {
-    const float *norm_x, *norm_w, *norm_ss;
-    uint32_t norm_parts; /* partial sums per row in norm_ss, 1..32 */
-    float norm_eps;
+    const float *row_ss;
+    uint32_t row_parts; /* partial sums per row in row_ss, 1..32 */
+    float row_eps;
     float *ss_out;
+    void *xs_out;        /* bf16 [m, n] */
+    const float *xs_gain; /* f32 [n] */
 } ts_linear_fused;
 
 /* Partial sums per row a linear of this shape writes to ss_out; 0 when it cannot (then run ts_rms_norm). */

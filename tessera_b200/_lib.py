@@ -28,7 +28,7 @@ class TsKept(C.Structure):
 
 class TsLinearFused(C.Structure):
     """ts_linear_fused: the RMS norm folded into a decode-sized linear's input and output."""
-    _fields_ = [("norm_x", vp), ("norm_w", vp), ("norm_ss", vp), ("norm_parts", u32), ("norm_eps", f32), ("ss_out", vp)]
+    _fields_ = [("row_ss", vp), ("row_parts", u32), ("row_eps", f32), ("ss_out", vp), ("xs_out", vp), ("xs_gain", vp)]
 
 
 class TsArg(C.Structure):

@@ -175,14 +175,14 @@ int ts_linear_fused_bf16(const void *x, const void *w, const void *a0, void *out
     TS_REQUIRE(epilogue != TS_EPI_ADD || a0 != nullptr, "linear: the ADD epilogue needs a0");
     StreamFused f;
     if (fused) {
-        f.norm_x = fused->norm_x;
-        f.norm_w = fused->norm_w;
-        f.norm_ss = fused->norm_ss;
-        f.norm_parts = fused->norm_parts;
-        f.norm_eps = fused->norm_eps;
+        f.row_ss = fused->row_ss;
+        f.row_parts = fused->row_parts;
+        f.row_eps = fused->row_eps;
         f.ss_out = fused->ss_out;
+        f.xs_out = fused->xs_out;
+        f.xs_gain = fused->xs_gain;
     }
-    TS_REQUIRE(f.norm_x || (x && aligned16(x)), "linear: x is NULL (or unaligned) and no norm_x was given");
+    TS_REQUIRE(x && aligned16(x), "linear: x is NULL or not 16-byte aligned");
     if (m == 0 || n == 0) return TS_OK;
     TS_REQUIRE(stream_supports(m, n, k, epilogue), "linear (fused): m=%u n=%u k=%u epilogue=%d is not a decode-sized shape",
                m, n, k, epilogue);

@@ -54,13 +54,17 @@ struct StreamParams {
     const float *a0;
     void *out;
     int *status;
-    // Fused RMS norm of the input (all NULL / 0 when x is taken as it is): x = bf16(norm_x * inv_rms * norm_w),
-    // inv_rms from the per-row partial sums of squares the upstream linear left in norm_ss [m, norm_parts].
-    const float *norm_x, *norm_w, *norm_ss;
-    uint32_t norm_parts;
-    float norm_eps;
-    // ADD epilogue: also leave sum_n out[m, n]^2 over this tile's 128 columns in ss_out [m, tiles].
+    // Folded RMS norm (FUSED kernels; all NULL / 0 otherwise).
+    // In: x holds bf16(row * gain) without the 1/rms factor; row_ss [m, row_parts] holds partial sums of
+    // squares of the rows; every output row is multiplied by 1/sqrt(sum/k + row_eps) before the epilogue.
+    const float *row_ss;
+    uint32_t row_parts;
+    float row_eps;
+    // Out (f32 output, n % 128 == 0, split k): ss_out [m, tiles] = per-tile sums of squares of the finished
+    // rows; xs_out [m, n] = bf16(out * xs_gain[n]), the next linear's x.
     float *ss_out;
+    uint16_t *xs_out;
+    const float *xs_gain;
 };
 
 struct StreamSmem {
@@ -73,8 +77,9 @@ __host__ __device__ inline StreamSmem stream_smem(uint32_t bn, uint32_t stages, 
     l.b_off = stages * kABytes;
     l.recv_off = l.b_off + kb_max * bn * kBlockK * 2;
     l.bar_off = l.recv_off + (recv ? kRows * (bn + 32) * 4 : 0);  // rows padded by 4 floats per sender
-    // barriers (256), per-warp partial sums of squares (4 x 128 floats), slack for the 1024-byte alignment
-    l.total = l.bar_off + 256 + 2048 + 1024;
+    // barriers (256), per-warp partial sums of squares (4 x 128 floats) and 128 row factors, slack for the
+    // 1024-byte alignment
+    l.total = l.bar_off + 256 + 2560 + 1024;
     return l;
 }
 
@@ -127,7 +132,7 @@ __device__ __forceinline__ void store_out(void *out, int out_dtype, size_t at, f
     else reinterpret_cast<uint16_t *>(out)[at] = bf16_bits(v);
 }
 
-// FUSED compiles in the normalised-input build and the sums of squares; the plain instantiation carries
+// FUSED compiles in the folded norm (row factors in, sums of squares and the scaled copy out); the plain instantiation carries
 // neither (they cost registers and a few percent of a decode step even when unused).
 template <uint32_t BN, bool FUSED>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -151,9 +156,11 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
     uint64_t *recv_full = b_full + 1;
     uint64_t *recv_free = recv_full + 1;
     uint64_t *red_full = recv_free + 1;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(red_full + 1);
+    uint64_t *inv_full = red_full + 1;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(inv_full + 1);
     volatile uint32_t *abort_flag = tmem_slot + 1;
     float *red = reinterpret_cast<float *>(smem + L.bar_off + 256);  // [4][128]
+    float *inv_s = red + 512;                                       // [128] 1/rms of the batch rows
 
     const uint32_t S = p.splits;
     const uint32_t rank = blockIdx.y;  // == cluster rank: the cluster spans grid y
@@ -190,8 +197,9 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
             mbar_init(&acc_full[s], 1);
             mbar_init(&acc_empty[s], kEpiWarps);
         }
-        mbar_init(b_full, (FUSED && p.norm_x) ? kEpiWarps : 1);
+        mbar_init(b_full, 1);
         mbar_init(red_full, kEpiWarps);
+        mbar_init(inv_full, kEpiWarps);
         // S > 1: one local arrival announces the bytes and the senders' asynchronous stores complete
         // them; S == 1: plain stores, one arrival per warp.
         mbar_init(recv_full, S > 1 ? 1 : kEpiWarps);
@@ -217,11 +225,9 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
             bool ok = true;
             // x is what the upstream kernel wrote: wait for it, then fetch this block's k slice once.
             pdl_wait();
-            if (!(FUSED && p.norm_x)) {
-                mbar_expect_tx(b_full, kbs * kBBytes);
-                for (uint32_t j = 0; j < kbs; j++)
-                    tma_load_2d(smem_b + j * kBBytes, &map_x, b_full, (int32_t)((kb_begin + j) * kBlockK), 0);
-            }
+            mbar_expect_tx(b_full, kbs * kBBytes);
+            for (uint32_t j = 0; j < kbs; j++)
+                tma_load_2d(smem_b + j * kBBytes, &map_x, b_full, (int32_t)((kb_begin + j) * kBlockK), 0);
             uint32_t it = early;
             for (; it < total_its; it++) {
                 ok = wait_bounded(&empty[it % p.stages], ((it / p.stages) & 1) ^ 1, abort_flag);
@@ -276,59 +282,22 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
         const uint32_t recv_base = smem_addr(recv);
         const uint32_t bar_local = smem_addr(recv_full);
         bool ok = true;
-        if (FUSED && p.norm_x) {
-            // Build this block's k slice of x in shared memory, normalised: what the TMA copy of a
-            // ready-made bf16 x would have left there, 128-byte rows with the 16-byte pieces of row r
-            // at piece ^ (r & 7).  Warp e takes batch rows [e BN/8, (e+1) BN/8); a half warp covers the
-            // 64 k of one (row, k block).
+        if (FUSED && p.row_ss) {
+            // 1/rms of every batch row from the partial sums the upstream linear left; runs under the
+            // loads and the MMAs, the epilogue below multiplies by it.
             pdl_wait();
             constexpr uint32_t RPW = BN / kEpiWarps;
-            const uint32_t e = warp - 2, half = lane >> 4, l16 = lane & 15;
-            float inv[RPW];
+            const uint32_t e = warp - 2;
 #pragma unroll
             for (uint32_t i = 0; i < RPW; i++) {
                 const uint32_t r = e * RPW + i;
-                float ss = (r < p.m && lane < p.norm_parts) ? p.norm_ss[(size_t)r * p.norm_parts + lane] : 0.0f;
+                float ss = (r < p.m && lane < p.row_parts) ? p.row_ss[(size_t)r * p.row_parts + lane] : 0.0f;
                 ss = warp_sum(ss);
-                inv[i] = 1.0f / sqrtf(ss / (float)p.k + p.norm_eps);
+                if (lane == 0) inv_s[r] = 1.0f / sqrtf(ss / (float)p.k + p.row_eps);
             }
-            // Sixteen (row pair, k block) loads per lane go out before the first is used: the slice
-            // comes from L2 and the wait for it is what this stage costs.
-            constexpr uint32_t HPW = RPW / 2, KBU = 16 / HPW;
-            for (uint32_t kb0 = 0; kb0 < kbs; kb0 += KBU) {
-                float4 wv[KBU], xv[KBU][HPW];
-#pragma unroll
-                for (uint32_t u = 0; u < KBU; u++) {
-                    if (kb0 + u < kbs) {
-                        const uint32_t k0 = (kb_begin + kb0 + u) * kBlockK + l16 * 4;
-                        wv[u] = *reinterpret_cast<const float4 *>(p.norm_w + k0);
-#pragma unroll
-                        for (uint32_t h = 0; h < HPW; h++) {
-                            const uint32_t r = e * RPW + 2 * h + half;
-                            xv[u][h] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                            if (r < p.m) xv[u][h] = *reinterpret_cast<const float4 *>(p.norm_x + (size_t)r * p.k + k0);
-                        }
-                    }
-                }
-#pragma unroll
-                for (uint32_t u = 0; u < KBU; u++) {
-                    if (kb0 + u < kbs) {
-                        unsigned char *tile_b = smem_b + (kb0 + u) * kBBytes;
-#pragma unroll
-                        for (uint32_t h = 0; h < HPW; h++) {
-                            const uint32_t r = e * RPW + 2 * h + half;
-                            const float s_inv = half ? inv[2 * h + 1] : inv[2 * h];
-                            uint2 packed;
-                            packed.x = pack_bf16(xv[u][h].x * (s_inv * wv[u].x), xv[u][h].y * (s_inv * wv[u].y));
-                            packed.y = pack_bf16(xv[u][h].z * (s_inv * wv[u].z), xv[u][h].w * (s_inv * wv[u].w));
-                            *reinterpret_cast<uint2 *>(tile_b + r * 128 + (((l16 >> 1) ^ (r & 7)) << 4) + (l16 & 1) * 8) = packed;
-                        }
-                    }
-                }
-            }
-            fence_async_shared();  // the tensor core reads these through the async proxy
             __syncwarp();
-            if (lane == 0) mbar_arrive(b_full);
+            if (lane == 0) mbar_arrive(inv_full);
+            ok = wait_bounded(inv_full, 0, abort_flag);
         }
         for (uint32_t acc_it = 0; acc_it < my_tiles && ok; acc_it++) {
             const uint32_t tile = blockIdx.x + acc_it * gridDim.x;
@@ -354,6 +323,7 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                     for (uint32_t c = 0; c < CW; c++, at += p.n) {
                         if (col0 + c < p.m) {
                             float r = v[c];
+                            if (FUSED && p.row_ss) r *= inv_s[col0 + c];
                             if (p.epilogue == TS_EPI_ADD) r += p.a0[at];
                             if (p.epilogue == TS_EPI_SCALE) r *= p.scale;
                             store_out(p.out, p.out_dtype, at, r);
@@ -422,11 +392,13 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                     for (uint32_t j = 0; j < 4; j++, at += out_n) {
                         float r = 0.0f;
                         if (m0 + j < p.m) {
-                            r = r4[j];
-                            if (p.gated) r = (p.epilogue == TS_EPI_SWIGLU ? silu(r) : gelu_tanh(r)) * u4[j];
+                            const float f = (FUSED && p.row_ss) ? inv_s[m0 + j] : 1.0f;
+                            r = r4[j] * f;
+                            if (p.gated) r = (p.epilogue == TS_EPI_SWIGLU ? silu(r) : gelu_tanh(r)) * (u4[j] * f);
                             if (p.epilogue == TS_EPI_ADD) r += p.a0[at];
                             if (p.epilogue == TS_EPI_SCALE) r *= p.scale;
                             store_out(p.out, p.out_dtype, at, r);
+                            if (FUSED && p.xs_out) p.xs_out[at] = bf16_bits(r * p.xs_gain[n_idx]);
                         }
                         if (FUSED && p.ss_out) {  // the host only asks for this when n is a multiple of 128: every lane is here
                             const float t = warp_sum(r * r);
@@ -570,31 +542,27 @@ int linear_stream(const void *x, const void *w, const void *a0, void *out, uint3
     StreamPlan s;
     if (!plan_stream(m, n, k, epilogue, &s))
         return fail(TS_ERR_BAD_INPUT, "linear (stream): unsupported shape m=%u n=%u k=%u epilogue=%d", m, n, k, epilogue);
-    const bool normed = fused && fused->norm_x;
     CUtensorMap map_w, map_x;
     int rc = make_tensor_map_2d(&map_w, w, n, k, k, s.gated ? 64 : kRows, kBlockK);
     if (rc != TS_OK) return rc;
-    if (!normed) {
-        rc = make_tensor_map_2d(&map_x, x, m, k, k, s.bn, kBlockK);
-        if (rc != TS_OK) return rc;
-    } else {
-        map_x = map_w;  // unused by the kernel
-        TS_REQUIRE(fused->norm_w && fused->norm_ss && fused->norm_parts >= 1 && fused->norm_parts <= 32,
-                   "linear (stream): the fused norm needs its gain, the partial sums and 1..32 parts (got %u)",
-                   fused->norm_parts);
-        TS_REQUIRE(aligned16(fused->norm_x) && aligned16(fused->norm_w), "linear (stream): norm inputs must be 16-byte aligned");
-    }
-    if (fused && fused->ss_out)
+    rc = make_tensor_map_2d(&map_x, x, m, k, k, s.bn, kBlockK);
+    if (rc != TS_OK) return rc;
+    if (fused && fused->row_ss)
+        TS_REQUIRE(fused->row_parts >= 1 && fused->row_parts <= 32, "linear (stream): 1..32 partial sums per row, got %u",
+                   fused->row_parts);
+    if (fused && (fused->ss_out || fused->xs_out)) {
         TS_REQUIRE(stream_sumsq_parts(m, n, k, epilogue) != 0 && out_dtype == TS_F32,
                    "linear (stream): sums of squares need an f32 output, n %% 128 == 0 and a split k (m=%u n=%u k=%u)", m, n, k);
+        TS_REQUIRE(!fused->xs_out || fused->xs_gain, "linear (stream): xs_out needs xs_gain");
+    }
     StreamParams p = {};
     if (fused) {
-        p.norm_x = fused->norm_x;
-        p.norm_w = fused->norm_w;
-        p.norm_ss = fused->norm_ss;
-        p.norm_parts = fused->norm_parts;
-        p.norm_eps = fused->norm_eps;
+        p.row_ss = fused->row_ss;
+        p.row_parts = fused->row_parts;
+        p.row_eps = fused->row_eps;
         p.ss_out = fused->ss_out;
+        p.xs_out = (uint16_t *)fused->xs_out;
+        p.xs_gain = fused->xs_gain;
     }
     p.m = m;
     p.n = n;
@@ -620,7 +588,7 @@ int linear_stream(const void *x, const void *w, const void *a0, void *out, uint3
     TS_CUDA(cudaGetSymbolAddress((void **)&status, g_stream_status));
     p.status = status;
     cudaError_t e;
-    const bool any_fused = p.norm_x || p.ss_out;
+    const bool any_fused = p.row_ss || p.ss_out || p.xs_out;
     switch (s.bn) {
     case 16: e = any_fused ? launch_stream<16, true>(map_w, map_x, p, s, stream) : launch_stream<16, false>(map_w, map_x, p, s, stream); break;
     case 32: e = any_fused ? launch_stream<32, true>(map_w, map_x, p, s, stream) : launch_stream<32, false>(map_w, map_x, p, s, stream); break;

@@ -66,6 +66,28 @@ __global__ void __launch_bounds__(128) gather_kernel(const uint16_t *table, cons
     pdl_launch_dependents();
 }
 
+// gather for a decoder whose first layer norm is folded into the q,k,v projection: besides the f32
+// rows, leaves xs = bf16(row * gain) and the row's sum of squares in ss[row, 0] (ss[row, 1..parts) = 0).
+__global__ void __launch_bounds__(128) gather_scaled_kernel(const uint16_t *table, const uint32_t *ids, float *out,
+                                                            uint16_t *xs, const float *gain, float *ss, uint32_t parts,
+                                                            uint32_t table_rows, uint32_t width) {
+    __shared__ float scratch[4];
+    pdl_wait();
+    const uint32_t id = ids[blockIdx.x];
+    const bool inside = id < table_rows;
+    const uint16_t *src = table + (size_t)(inside ? id : 0) * width;
+    float sq = 0.0f;
+    for (uint32_t i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = inside ? __uint_as_float((uint32_t)src[i] << 16) : 0.0f;
+        out[(size_t)blockIdx.x * width + i] = v;
+        xs[(size_t)blockIdx.x * width + i] = bf16_bits(v * gain[i]);
+        sq = fmaf(v, v, sq);
+    }
+    sq = block_sum(sq, scratch);
+    pdl_launch_dependents();
+    if (threadIdx.x < parts) ss[(size_t)blockIdx.x * parts + threadIdx.x] = threadIdx.x == 0 ? sq : 0.0f;
+}
+
 // ---- scatter: engine/plan/lower/src/kernels/scatter.rs:11-27
 __global__ void __launch_bounds__(128) scatter_kernel(const uint16_t *x, const uint32_t *slots,
                                                       const uint32_t *positions, uint16_t *out, KeptDev kept,
@@ -396,6 +418,16 @@ int gather_rows(const void *table, const uint32_t *ids, void *out, int out_dtype
         e = launch(gather_kernel<uint16_t>, dim3(rows), dim3(128), 0, stream, pdl_enabled(), (const uint16_t *)table,
                    ids, (uint16_t *)out, table_rows, width, first);
     if (e != cudaSuccess) return fail(TS_ERR_CUDA, "launch of gather failed: %s", cudaGetErrorString(e));
+    return TS_OK;
+}
+
+int gather_scaled(const void *table, const uint32_t *ids, float *out, void *xs, const float *gain, float *ss,
+                  uint32_t parts, uint32_t rows, uint32_t table_rows, uint32_t width, cudaStream_t stream) {
+    if (rows == 0) return TS_OK;
+    TS_REQUIRE(parts >= 1 && parts <= 128, "gather (scaled): %u partial sums per row", parts);
+    cudaError_t e = launch(gather_scaled_kernel, dim3(rows), dim3(128), 0, stream, pdl_enabled(), (const uint16_t *)table, ids,
+                           out, (uint16_t *)xs, gain, ss, parts, table_rows, width);
+    if (e != cudaSuccess) return fail(TS_ERR_CUDA, "launch of gather (scaled) failed: %s", cudaGetErrorString(e));
     return TS_OK;
 }
 

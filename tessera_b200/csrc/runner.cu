@@ -116,15 +116,12 @@ size_t linear_workspace(uint32_t m, uint32_t n, uint32_t k, int epi) {
 // projection of the layer takes the weight-streaming kernel and the two that feed the residual
 // split their k), else 0.
 uint32_t fold_parts(const ts_decoder *d, uint32_t rows) {
-    // Off unless TS_FOLD_NORMS=1.  Measured on the Qwen3-0.6B shape at batch 64 the folded step is no
-    // faster (the projections spend on building their input what the norm launches cost), and its sums
-    // of squares add up in another order, which is enough to move a greedy token where two logits
-    // nearly tie.  The default keeps the launch sequence whose tokens equal the CPU checker's.
-    static const bool on = [] {
+    // TS_FOLD_NORMS=0 keeps every norm a launch of its own (for A/B timing).
+    static const bool off = [] {
         const char *v = getenv("TS_FOLD_NORMS");
-        return v && v[0] == '1';
+        return v && v[0] == '0';
     }();
-    if (!on) return 0;
+    if (off) return 0;
     const ts_decoder_config &c = d->c;
     const uint32_t H = c.hidden, QW = c.heads * c.head_dim;
     const uint32_t parts = stream_sumsq_parts(rows, H, QW, TS_EPI_ADD);
@@ -181,32 +178,40 @@ int enqueue(ts_decoder *d, uint32_t rows, uint32_t keys, uint32_t n_out, bool fe
                       int out_dtype) -> int {
         return linear_any(d, xin, w, a0, out, rows, n, k, epi, out_dtype, s);
     };
-    // Decode-sized steps fold the layer norms into the projections on either side: the o and down
-    // projections leave per-tile sums of squares of the new residual rows, the q,k,v and gate/up
-    // projections normalise their input from them.  Layer 0's first norm still runs on its own (its
-    // input comes from the embedding gather).
+    // Decode-sized steps fold the layer norms into the projections on either side: the embedding gather
+    // and the o and down projections leave bf16(row * gain) in d->h and the rows' sums of squares in
+    // d->sumsq; the q,k,v and gate/up projections multiply their output rows by 1/rms.  Only the final
+    // norm (over the wanted rows) stays a launch.
     const uint32_t ss_parts = fold_parts(d, rows);
     const bool fold = ss_parts != 0;
-    auto folded = [&](const float *ln, const void *xin, const void *w, const void *a0, void *out, uint32_t n, uint32_t k,
-                      int epi, int out_dtype, bool leave_sums) -> int {
+    // x_in: bf16(residual * gain) as the upstream step left it in d->h; next_gain: the gain of the norm
+    // that follows this linear's output (NULL: none follows inside the layer stack).
+    auto folded = [&](bool scaled_in, const void *xin, const void *w, const void *a0, void *out, uint32_t n, uint32_t k,
+                      int epi, int out_dtype, const float *next_gain) -> int {
         StreamFused f;
-        if (ln) {
-            f.norm_x = d->x;
-            f.norm_w = ln;
-            f.norm_ss = d->sumsq;
-            f.norm_parts = ss_parts;
-            f.norm_eps = c.eps;
+        if (scaled_in) {
+            f.row_ss = d->sumsq;
+            f.row_parts = ss_parts;
+            f.row_eps = c.eps;
         }
-        if (leave_sums) f.ss_out = d->sumsq;
+        if (next_gain) {
+            f.ss_out = d->sumsq;
+            f.xs_out = d->h;
+            f.xs_gain = next_gain;
+        }
         return linear_stream(xin, w, a0, out, rows, n, k, epi, 1.0f, out_dtype, s, &f);
     };
     if ((rc = mark("")) != TS_OK) return rc;  // interval origin
     if (feedback) STEP("advance_rows", advance_rows(d->ids, d->tokens, d->positions, rows, s));
-    STEP("gather", gather_rows(d->embed, d->tokens, d->x, TS_F32, rows, c.vocab, H, 0, s));
+    if (fold) {
+        STEP("gather", gather_scaled(d->embed, d->tokens, d->x, d->h, d->layers[0].ln1, d->sumsq, ss_parts, rows, c.vocab, H, s));
+    } else {
+        STEP("gather", gather_rows(d->embed, d->tokens, d->x, TS_F32, rows, c.vocab, H, 0, s));
+    }
     for (uint32_t l = 0; l < c.layers; l++) {
         ts_decoder::Layer &L = d->layers[l];
-        if (fold && l > 0) {
-            STEP("linear_qkv", folded(L.ln1, nullptr, L.wqkv, nullptr, d->qkv, d->qkv_n, H, TS_EPI_NONE, TS_BF16, false));
+        if (fold) {
+            STEP("linear_qkv", folded(true, d->h, L.wqkv, nullptr, d->qkv, d->qkv_n, H, TS_EPI_NONE, TS_BF16, nullptr));
         } else {
             STEP("rms_norm", rms_norm(d->x, TS_F32, L.ln1, d->h, TS_BF16, rows, H, c.eps, nullptr, s));
             STEP("linear_qkv", linear(d->h, L.wqkv, nullptr, d->qkv, d->qkv_n, H, TS_EPI_NONE, TS_BF16));
@@ -232,9 +237,10 @@ int enqueue(ts_decoder *d, uint32_t rows, uint32_t keys, uint32_t n_out, bool fe
         }
         if (attend_rows_workspace_bytes(rows, keys, c.heads, c.kv_heads, D) > 0) launches++;
         if (fold) {
-            STEP("linear_o", folded(nullptr, d->attn, L.wo, d->x, d->x, H, QW, TS_EPI_ADD, TS_F32, true));
-            STEP("linear_gate_up", folded(L.ln2, nullptr, L.wgu, nullptr, d->act, 2 * c.ffn, H, TS_EPI_SWIGLU, TS_BF16, false));
-            STEP("linear_down", folded(nullptr, d->act, L.wdown, d->x, d->x, H, c.ffn, TS_EPI_ADD, TS_F32, l + 1 < c.layers));
+            STEP("linear_o", folded(false, d->attn, L.wo, d->x, d->x, H, QW, TS_EPI_ADD, TS_F32, L.ln2));
+            STEP("linear_gate_up", folded(true, d->h, L.wgu, nullptr, d->act, 2 * c.ffn, H, TS_EPI_SWIGLU, TS_BF16, nullptr));
+            STEP("linear_down", folded(false, d->act, L.wdown, d->x, d->x, H, c.ffn, TS_EPI_ADD, TS_F32,
+                                       l + 1 < c.layers ? d->layers[l + 1].ln1 : nullptr));
         } else {
             STEP("linear_o", linear(d->attn, L.wo, d->x, d->x, H, QW, TS_EPI_ADD, TS_F32));
             STEP("rms_norm", rms_norm(d->x, TS_F32, L.ln2, d->h, TS_BF16, rows, H, c.eps, nullptr, s));
@@ -569,7 +575,7 @@ uint32_t ts_decoder_launches_per_step(ts_decoder *d, uint32_t rows, uint32_t key
                          (attend_rows_workspace_bytes(rows, keys, c.heads, c.kv_heads, c.head_dim) > 0 ? 1 : 0) +
                          lin(rows, d->qkv_n, c.hidden, TS_EPI_NONE) + lin(rows, c.hidden, c.heads * c.head_dim, TS_EPI_ADD) +
                          lin(rows, 2 * c.ffn, c.hidden, TS_EPI_SWIGLU) + lin(rows, c.hidden, c.ffn, TS_EPI_ADD);
-    return 1 /*gather*/ + c.layers * per_layer + (fold ? 1 : 0) /*layer 0's first norm*/ + 1 /*final norm*/ + lin(rows, c.vocab, c.hidden, TS_EPI_NONE) + 2 /*top-1*/;
+    return 1 /*gather*/ + c.layers * per_layer + 1 /*final norm*/ + lin(rows, c.vocab, c.hidden, TS_EPI_NONE) + 2 /*top-1*/;
 }
 
 uint64_t ts_decoder_graph_replays(ts_decoder *d) { return d ? d->replays : 0; }

@@ -18,15 +18,19 @@ int linear_umma(const void *x, const void *w, const void *a0, void *out, uint32_
                 cudaStream_t stream);
 bool stream_supports(uint32_t m, uint32_t n, uint32_t k, int epilogue);
 int stream_take_status();
-// Optional fusions of the decode step around a streamed linear.
+// The residual stream's RMS norms folded into the streamed linears on either side of them.
 struct StreamFused {
-    // x = bf16(norm_x * inv_rms * norm_w): norm_x f32 [m, k], norm_w f32 [k], norm_ss f32 [m, norm_parts]
-    // partial sums of squares of norm_x's rows (any split that adds up to the whole row).
-    const float *norm_x = nullptr, *norm_w = nullptr, *norm_ss = nullptr;
-    uint32_t norm_parts = 0;
-    float norm_eps = 0.0f;
-    // f32 [m, stream_sumsq_parts(...)]: per 128-column tile, the sum of squares of the finished output rows.
+    // In: x is bf16(row * gain) without the 1/rms factor, row_ss f32 [m, row_parts] are partial sums of squares
+    // of the rows (any split that adds up to the row); the product's rows are multiplied by
+    // 1/sqrt(sum/k + row_eps) before the epilogue.
+    const float *row_ss = nullptr;
+    uint32_t row_parts = 0;
+    float row_eps = 0.0f;
+    // Out: ss_out f32 [m, stream_sumsq_parts(...)] = per 128-column tile, the sum of squares of the finished
+    // output rows; xs_out bf16 [m, n] = out * xs_gain[n], the next linear's x.
     float *ss_out = nullptr;
+    void *xs_out = nullptr;
+    const float *xs_gain = nullptr;
 };
 // Parts per row that a linear of this shape leaves in ss_out, or 0 when it cannot.
 uint32_t stream_sumsq_parts(uint32_t m, uint32_t n, uint32_t k, int epilogue);
@@ -65,6 +69,9 @@ int gate(const volatile uint32_t *flag, cudaStream_t stream);
 int mean_pool(const float *x, const uint32_t *cu_seqlens, float *out, uint32_t seqs, uint32_t width, int normalize,
               cudaStream_t stream);
 int advance_rows(const uint32_t *ids, uint32_t *tokens, uint32_t *positions, uint32_t rows, cudaStream_t stream);
+// Embedding rows as f32 plus xs = bf16(row * gain) and the rows' sums of squares (ss [rows, parts], all in part 0).
+int gather_scaled(const void *table, const uint32_t *ids, float *out, void *xs, const float *gain, float *ss,
+                  uint32_t parts, uint32_t rows, uint32_t table_rows, uint32_t width, cudaStream_t stream);
 int gather_rows(const void *table, const uint32_t *ids, void *out, int out_dtype, uint32_t rows,
                 uint32_t table_rows, uint32_t width, uint32_t first, cudaStream_t stream);
 int scatter_rows(const void *x, const uint32_t *slots, const uint32_t *positions, void *out, const KeptDev &kept,

@@ -74,35 +74,34 @@ def linear(x, w, a0=None, *, epilogue="none", scale=1.0, out_dtype=torch.bfloat1
     return out
 
 
-def linear_fused(x, w, a0=None, *, epilogue="none", scale=1.0, out_dtype=torch.bfloat16, out=None, norm=None,
-                 want_sumsq=False):
-    """ts_linear_fused_bf16.  norm = (x_f32 [m, k], gain f32 [k], partial sums f32 [m, parts], eps) replaces x
-    by its RMS-normalised bf16 form inside the kernel; want_sumsq also returns the per-tile sums of squares
-    of the output rows, f32 [m, ts_linear_sumsq_parts]."""
+def linear_fused(x, w, a0=None, *, epilogue="none", scale=1.0, out_dtype=torch.bfloat16, out=None, rows=None,
+                 next_gain=None):
+    """ts_linear_fused_bf16.  rows = (partial sums of squares f32 [m, parts], eps): x is bf16(row * gain) and the
+    output rows get the 1/rms factor.  next_gain (f32 [n]): also returns xs = bf16(out * next_gain) and the
+    per-tile sums of squares of the output rows, f32 [m, ts_linear_sumsq_parts]: (out, xs, ss)."""
     from ._lib import TsLinearFused
-    m, k = (norm[0] if norm is not None else x).shape
+    m, k = x.shape
     n = w.shape[0]
     gated = epilogue in ("swiglu", "geglu")
     if out is None:
         out = torch.empty((m, n // 2 if gated else n), dtype=out_dtype, device=w.device)
     f = TsLinearFused()
-    keep = []
-    if norm is not None:
-        nx, nw, nss, eps = norm
-        assert nx.dtype == torch.float32 and nw.dtype == torch.float32 and nss.dtype == torch.float32
-        assert nx.is_contiguous() and nss.is_contiguous() and nss.shape[0] == m
-        f.norm_x, f.norm_w, f.norm_ss, f.norm_parts, f.norm_eps = nx.data_ptr(), nw.data_ptr(), nss.data_ptr(), nss.shape[1], eps
-        keep += [nx, nw, nss]
-    ss = None
-    if want_sumsq:
+    if rows is not None:
+        ss_in, eps = rows
+        assert ss_in.dtype == torch.float32 and ss_in.is_contiguous() and ss_in.shape[0] == m
+        f.row_ss, f.row_parts, f.row_eps = ss_in.data_ptr(), ss_in.shape[1], eps
+    xs = ss = None
+    if next_gain is not None:
         parts = lib.ts_linear_sumsq_parts(m, n, k, EPILOGUE[epilogue])
         if parts == 0:
             raise ValueError(f"no sums of squares from a linear of m={m} n={n} k={k}")
         ss = torch.empty((m, parts), dtype=torch.float32, device=w.device)
-        f.ss_out = ss.data_ptr()
+        xs = torch.empty((m, n), dtype=torch.bfloat16, device=w.device)
+        assert next_gain.dtype == torch.float32 and next_gain.numel() == n
+        f.ss_out, f.xs_out, f.xs_gain = ss.data_ptr(), xs.data_ptr(), next_gain.data_ptr()
     check(lib.ts_linear_fused_bf16(_ptr(x), _ptr(w), _ptr(a0), _ptr(out), m, n, k, EPILOGUE[epilogue], scale,
                                    _dtype_code(out.dtype), C.byref(f), _stream()))
-    return (out, ss) if want_sumsq else out
+    return (out, xs, ss) if next_gain is not None else out
 
 
 @dataclass

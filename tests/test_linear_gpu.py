@@ -163,9 +163,10 @@ def test_bad_arguments_are_refused():
 
 @pytest.mark.parametrize("m", [64, 37, 128, 9])
 def test_norms_folded_into_the_projections(m):
-    # The decode step's pair: a residual-adding projection that also leaves per-tile sums of squares,
-    # and a projection that normalises its input from them.  Checked against the checker's
-    # rms_norm -> bf16 -> matmul chain and against the library's own unfused launches.
+    # The decode step's pair: a residual-adding projection that also leaves bf16(out * gain) and per-tile
+    # sums of squares, and a projection that takes those and multiplies its rows by 1/rms.  Checked
+    # against the checker's rms_norm -> bf16 -> matmul chain (the folded product rounds the normed row
+    # before instead of after the 1/rms factor: same tolerance) and against the unfolded launches.
     from tessera_b200 import ops
     rng = np.random.default_rng(m)
     hidden, inner, wide, eps = 1024, 2048, 4096, 1e-6
@@ -176,19 +177,20 @@ def test_norms_folded_into_the_projections(m):
     w2 = normal_bf16(rng, (wide, hidden), 0.02)
     wgu = normal_bf16(rng, (2 * 3072, hidden), 0.02)
 
-    x0_d = torch.from_numpy(x0).cuda()
-    y, ss = ops.linear_fused(from_bits(a), from_bits(w1), x0_d, epilogue="add", out_dtype=torch.float32, want_sumsq=True)
+    x0_d, gain_d = torch.from_numpy(x0).cuda(), torch.from_numpy(gain).cuda()
+    y, xs, ss = ops.linear_fused(from_bits(a), from_bits(w1), x0_d, epilogue="add", out_dtype=torch.float32,
+                                 next_gain=gain_d)
     torch.cuda.synchronize()
     want_y = O.matmul(O.bf16_widen(a), w1) + x0
     assert rel_error(y.cpu().numpy(), want_y) <= F32_TOL
     assert ss.shape == (m, hidden // 128)
     tiles = (y.double() ** 2).reshape(m, hidden // 128, 128).sum(-1)
     assert torch.allclose(ss.double(), tiles, rtol=1e-5, atol=1e-6)
+    assert torch.equal(xs, (y * gain_d).to(torch.bfloat16))   # one rounding of an f32 product: bit-exact
 
-    gain_d = torch.from_numpy(gain).cuda()
     h = O.bf16_round(O.rms_norm(y.cpu().numpy(), gain, eps))
     for w, epi in ((w2, "none"), (wgu, "swiglu")):
-        got = ops.linear_fused(None, from_bits(w), epilogue=epi, norm=(y, gain_d, ss, eps))
+        got = ops.linear_fused(xs, from_bits(w), epilogue=epi, rows=(ss, eps))
         unfused = ops.linear(ops.rms_norm(y, gain_d, eps), from_bits(w), epilogue=epi, path="stream")
         torch.cuda.synchronize()
         assert ops.device_status() == 0
@@ -196,14 +198,11 @@ def test_norms_folded_into_the_projections(m):
         want = z if epi == "none" else (z[:, :3072] / (1.0 + np.exp(-z[:, :3072])) * z[:, 3072:]).astype(np.float32)
         assert rel_error(widen(got), want) <= BF16_TOL
         assert rel_error(widen(got), widen(unfused)) <= BF16_TOL
-        # the two differ only where a sum of squares added in another order moved a bf16 rounding
-        assert (got != unfused).float().mean().item() < 0.02
 
 
 def test_sums_of_squares_are_refused_where_k_is_not_split():
     from tessera_b200 import TesseraError, ops
-    rng = np.random.default_rng(3)
     x, w = _case(64, 20000, 1024, 5)   # one block per tile: no cluster reduce to hang the sums on
     with pytest.raises((TesseraError, ValueError)):
         ops.linear_fused(from_bits(x), from_bits(w), torch.zeros((64, 20000), device="cuda"), epilogue="add",
-                         out_dtype=torch.float32, want_sumsq=True)
+                         out_dtype=torch.float32, next_gain=torch.ones(20000, device="cuda"))
