@@ -25,6 +25,21 @@ def test_rms_norm_f32_to_bf16():
     assert rel_error(widen(plain), O.rms_norm(x, None, 1e-6)) <= 1e-5
 
 
+@pytest.mark.parametrize("width", [768, 1024, 2048])
+def test_rms_norm_many_rows(width):
+    # from 1024 rows on a warp takes a row (registers, one read); the last block is ragged
+    from tessera_b200 import ops
+    rng = np.random.default_rng(width)
+    rows = 1024 + 13
+    x = rng.standard_normal((rows, width), dtype=np.float32) * 2
+    w = rng.standard_normal(width, dtype=np.float32)
+    want = O.rms_norm(x, w, 1e-6)
+    xd, wd = torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda()
+    assert rel_error(widen(ops.rms_norm(xd, wd, 1e-6)), want) <= 1e-2
+    assert rel_error(widen(ops.rms_norm(xd, wd, 1e-6, out_dtype=torch.float32)), want) <= 1e-5
+    assert rel_error(widen(ops.rms_norm(xd, None, 1e-6, out_dtype=torch.float32)), O.rms_norm(x, None, 1e-6)) <= 1e-5
+
+
 def test_rms_known_answer():
     # engine/ir/interp/src/cpu_test.rs:131-149, through the device kernel
     from tessera_b200 import ops
