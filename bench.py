@@ -64,7 +64,7 @@ def parse_args():
                          "linear_o, linear_gate_up, linear_down, linear_unembed); used for ncu captures")
     ap.add_argument("--ctx", type=int, default=192, help="--case attend_rows: context length of every row")
     ap.add_argument("--rows", type=int, default=BATCH, help="--case: rows (batch) of the launch")
-    ap.add_argument("--path", default="auto", choices=["auto", "skinny", "umma", "stream"], help="--case linear_*: kernel family")
+    ap.add_argument("--path", default="auto", choices=["auto", "skinny", "umma", "stream", "pair"], help="--case linear_*: kernel family")
     return ap.parse_args()
 
 
@@ -383,7 +383,7 @@ def run_case(args):
         for c in range(4):
             w = bf(n, k, std=0.02)
             out = torch.empty((rows, n), dtype=torch.bfloat16, device="cuda")
-            calls.append(lambda w=w, out=out: ops.linear(x, w, out=out))
+            calls.append(lambda w=w, out=out: ops.linear(x, w, out=out, path=args.path))
         algo = 2.0 * rows * n * k  # flops
     else:
         shapes = {"linear_qkv": (qw + 2 * kw, h, "none", torch.bfloat16), "linear_o": (h, qw, "add", torch.float32),

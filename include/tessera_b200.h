@@ -74,8 +74,10 @@ typedef enum {
     TS_LINEAR_AUTO = 0,
     TS_LINEAR_SKINNY = 1, /* decode-sized m: vector loads + warp MMA, split-K */
     TS_LINEAR_UMMA = 2,   /* tiled tcgen05 / TMEM accumulators fed by TMA (prefill-sized m) */
-    TS_LINEAR_STREAM = 3  /* m <= 128: weight-streaming tcgen05, k split over a thread-block cluster and
+    TS_LINEAR_STREAM = 3, /* m <= 128: weight-streaming tcgen05, k split over a thread-block cluster and
                              reduced through distributed shared memory, epilogue fused */
+    TS_LINEAR_PAIR = 4    /* m >= 512: 256 x 256 tiles on pairs of SMs (tcgen05 cta_group::2), each block of
+                             the pair loading half of both operands */
 } ts_linear_path;
 
 /* Bytes of workspace ts_linear_bf16 needs for these sizes (0 when none). */

@@ -1,6 +1,7 @@
 // The C ABI: argument checks on the host, then a launch.  Nothing here synchronises or allocates.
 #include <cstdarg>
 #include <cstring>
+#include <cstdlib>
 #include <mutex>
 
 #include "ts_common.cuh"
@@ -122,12 +123,22 @@ int make_tensor_map_3d(CUtensorMap *map, const void *base, uint64_t outer, uint6
     return TS_OK;
 }
 
+// TS_LINEAR_PAIR=0 keeps AUTO on the one-SM tiled kernel (for A/B timing).
+static bool pair_auto() {
+    static const bool off = [] {
+        const char *v = getenv("TS_LINEAR_PAIR");
+        return v && v[0] == '0';
+    }();
+    return !off;
+}
+
 int pick_linear_path(uint32_t m, uint32_t n, uint32_t k, int epilogue, int path) {
-    if (path == TS_LINEAR_SKINNY || path == TS_LINEAR_UMMA || path == TS_LINEAR_STREAM) return path;
+    if (path == TS_LINEAR_SKINNY || path == TS_LINEAR_UMMA || path == TS_LINEAR_STREAM || path == TS_LINEAR_PAIR) return path;
     // m <= 16: the warp-MMA streamer; m <= 128: the weight-streaming tcgen05 kernel with its cluster
     // reduce; larger m: the tiled tcgen05 kernel.
     if (m <= 16 && skinny_supports(m, n, k, epilogue)) return TS_LINEAR_SKINNY;
     if (m <= 128 && stream_supports(m, n, k, epilogue)) return TS_LINEAR_STREAM;
+    if (pair_auto() && pair_supports(m, n, k, epilogue)) return TS_LINEAR_PAIR;
     if (umma_supports(m, n, k, epilogue)) return TS_LINEAR_UMMA;
     if (skinny_supports(m, n, k, epilogue)) return TS_LINEAR_SKINNY;
     return -1;
@@ -150,8 +161,8 @@ int ts_set_pdl(int enabled) {
 
 int ts_device_status(void) {
     const int a = umma_take_status(), b = stream_take_status(), c = flash_take_status(), d = moe_take_status();
-    const int e = rows_take_status();
-    return a ? a : b ? b : c ? c : d ? d : e;
+    const int e = rows_take_status(), f = pair_take_status();
+    return a ? a : b ? b : c ? c : d ? d : e ? e : f;
 }
 
 size_t ts_linear_workspace_bytes(uint32_t m, uint32_t n, uint32_t k, int epilogue, int path) {
@@ -211,6 +222,10 @@ int ts_linear_bf16(const void *x, const void *w, const void *a0, void *out, uint
     if (chosen == TS_LINEAR_STREAM) {
         TS_REQUIRE(stream_supports(m, n, k, epilogue), "linear (stream): needs m <= 128 (m=%u n=%u k=%u)", m, n, k);
         return linear_stream(x, w, a0, out, m, n, k, epilogue, scale, out_dtype, s);
+    }
+    if (chosen == TS_LINEAR_PAIR) {
+        TS_REQUIRE(pair_supports(m, n, k, epilogue), "linear (pair): needs m >= 512 and n >= 256 (m=%u n=%u k=%u)", m, n, k);
+        return linear_pair(x, w, a0, out, m, n, k, epilogue, scale, out_dtype, s);
     }
     return linear_umma(x, w, a0, out, m, n, k, epilogue, scale, out_dtype, workspace, workspace_bytes, s);
 }

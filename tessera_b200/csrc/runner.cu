@@ -100,6 +100,7 @@ int linear_any(ts_decoder *d, const void *x, const void *w, const void *a0, void
     if (path == TS_LINEAR_SKINNY)
         return linear_skinny(x, w, a0, out, m, n, k, epi, 1.0f, out_dtype, d->workspace, d->workspace_bytes, s);
     if (path == TS_LINEAR_STREAM) return linear_stream(x, w, a0, out, m, n, k, epi, 1.0f, out_dtype, s);
+    if (path == TS_LINEAR_PAIR) return linear_pair(x, w, a0, out, m, n, k, epi, 1.0f, out_dtype, s);
     if (path == TS_LINEAR_UMMA)
         return linear_umma(x, w, a0, out, m, n, k, epi, 1.0f, out_dtype, d->workspace, d->workspace_bytes, s);
     return fail(TS_ERR_BAD_INPUT, "decoder: no linear kernel takes m=%u n=%u k=%u", m, n, k);

@@ -177,6 +177,17 @@ __device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, u
         : "memory");
 }
 
+// The same copy issued by either block of a two-block MMA pair (cta_group::2): the data lands in the issuing
+// block's shared memory, the bytes are credited to `bar_cluster_addr`, a cluster address that normally names
+// the pair leader's barrier, so that the leader's MMA thread waits once for both halves.
+__device__ __forceinline__ void tma_load_2d_pair(void *dst, const CUtensorMap *map, uint32_t bar_cluster_addr, int32_t x,
+                                                 int32_t y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_addr(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+        : "memory");
+}
+
 // Hands registers from one warp group to another (all four warps of a group execute it).
 template <uint32_t N>
 __device__ __forceinline__ void setmaxnreg_inc() {
@@ -269,6 +280,48 @@ __device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, u
         "}" ::"r"(tmem_d),
         "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
         : "memory");
+}
+
+// ---- two-block MMA pairs (cta_group::2): the leader block's thread issues for both SMs ----------------
+// The same warp of both blocks allocates / frees; the address is the same in both.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t *dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(dst)), "r"(cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+
+// D[tmem of both blocks] (+)= A * B with M = 256: block r of the pair holds rows [128 r, 128 r + 128) of A
+// and rows [N/2 r, N/2 r + N/2) of B at the same shared-memory offsets, and receives its 128 rows of D.
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                               uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// One arrival on the barrier at this shared-memory offset in both blocks of the pair once all MMAs issued so
+// far by this thread (for the pair) have finished.  (A barrier signal, not a copy: nothing is multicast into
+// shared memory.)
+__device__ __forceinline__ void umma_commit_pair(uint64_t *bar) {
+    const uint16_t both = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+                     smem_addr(bar)),
+                 "h"(both)
+                 : "memory");
+}
+
+// Plain arrival on a barrier of another block of the cluster (a notification; no data rides on it).
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 
 // One thread.  `bar` gets one arrival when every MMA issued so far by this thread has finished.

@@ -206,3 +206,42 @@ def test_sums_of_squares_are_refused_where_k_is_not_split():
     with pytest.raises((TesseraError, ValueError)):
         ops.linear_fused(from_bits(x), from_bits(w), torch.zeros((64, 20000), device="cuda"), epilogue="add",
                          out_dtype=torch.float32, next_gain=torch.ones(20000, device="cuda"))
+
+
+PAIR = [(512, 512, 256), (1024, 640, 256), (700, 1024, 512), (1300, 2304, 768), (512, 256, 64)]
+
+
+@pytest.mark.parametrize("m,n,k", PAIR)
+def test_pair_matches_oracle(m, n, k):
+    # 256 x 256 tiles on pairs of SMs: ragged last row tile (m % 256), ragged last column tile (n % 256)
+    x, w = _case(m, n, k, seed=m * 3 + n + k)
+    want = O.matmul(O.bf16_widen(x), w)
+    got = widen(_run(x, w, "pair"))
+    assert rel_error(got, want) <= BF16_TOL
+    got32 = widen(_run(x, w, "pair", out_dtype=torch.float32))
+    assert rel_error(got32, want) <= F32_TOL
+
+
+def test_pair_epilogues():
+    m, n, k = 640, 768, 256
+    x, w = _case(m, n, k, seed=12)
+    base = O.matmul(O.bf16_widen(x), w)
+    rng = np.random.default_rng(13)
+    res = rng.standard_normal((m, n), dtype=np.float32)
+    got = widen(_run(x, w, "pair", a0=torch.from_numpy(res).cuda(), epilogue="add", out_dtype=torch.float32))
+    assert rel_error(got, base + res) <= F32_TOL
+    got = widen(_run(x, w, "pair", epilogue="scale", scale=0.25, out_dtype=torch.float32))
+    assert rel_error(got, base * np.float32(0.25)) <= F32_TOL
+    ffn = n // 2   # 384 = 3 gated tiles of 128
+    for act in ("swiglu", "geglu"):
+        want = O.act(base[:, :ffn], "silu" if act == "swiglu" else "gelu_tanh") * base[:, ffn:]
+        got = widen(_run(x, w, "pair", epilogue=act))
+        assert got.shape == (m, ffn) and rel_error(got, want) <= BF16_TOL
+
+
+def test_pair_equals_one_sm_tiles_bit_for_bit():
+    # same k order inside the tensor core: the two tilings give the same f32 sums
+    x, w = _case(1024, 1024, 512, seed=4)
+    a = _run(x, w, "pair", out_dtype=torch.float32)
+    b = _run(x, w, "umma", out_dtype=torch.float32)
+    assert torch.equal(a, b)
