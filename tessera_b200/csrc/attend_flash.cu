@@ -68,6 +68,12 @@ __device__ __forceinline__ uint32_t sat_add(uint32_t a, uint32_t b) {
     return s < a ? 0xFFFFFFFFu : s;
 }
 
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 template <uint32_t D>
 __global__ void __launch_bounds__(kThreads, 1)
 attend_flash_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -242,19 +248,28 @@ attend_flash_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             // Keys of this block the row sees: [c_from, c_to) in block columns.
             const uint32_t c_from = from > key0 ? min(from - key0, BK) : 0;
             const uint32_t c_to = to > key0 ? min(to - key0, BK) : 0;
-            // Pass 1: the row's maximum over this block's visible keys.
-            float m_blk = -INFINITY;
+            // The whole S row of the block in registers (one TMEM read); masked keys become -inf so that the
+            // exponentials below need no selects.  Eight independent running maxima.
+            uint32_t rr[BK / 32][32];
 #pragma unroll
-            for (uint32_t c0 = 0; c0 < BK; c0 += 32) {
-                uint32_t r[32];
-                tmem_ld_32x32(s_tmem + c0, r);
-                tmem_ld_wait();
+            for (uint32_t c = 0; c < BK / 32; c++) tmem_ld_32x32(s_tmem + c * 32, rr[c]);
+            tmem_ld_wait();
+            float mx[8];
 #pragma unroll
-                for (uint32_t c = 0; c < 32; c++) {
-                    const float v = (c0 + c >= c_from && c0 + c < c_to) ? __uint_as_float(r[c]) : -INFINITY;
-                    m_blk = fmaxf(m_blk, v);
+            for (uint32_t i = 0; i < 8; i++) mx[i] = -INFINITY;
+            if (c_from == 0 && c_to == BK) {
+#pragma unroll
+                for (uint32_t c = 0; c < BK; c++) mx[c & 7] = fmaxf(mx[c & 7], __uint_as_float(rr[c >> 5][c & 31]));
+            } else {
+#pragma unroll
+                for (uint32_t c = 0; c < BK; c++) {
+                    const float v = (c >= c_from && c < c_to) ? __uint_as_float(rr[c >> 5][c & 31]) : -INFINITY;
+                    rr[c >> 5][c & 31] = __float_as_uint(v);
+                    mx[c & 7] = fmaxf(mx[c & 7], v);
                 }
             }
+            const float m_blk = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])),
+                                      fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
             const float m_new = fmaxf(m_use, m_blk * p.scale_log2);
             // Rescale O and the running sum only when the maximum ran ahead by more than kRescaleStep:
             // probabilities stay below 2^kRescaleStep, and after the first blocks this is rare.
@@ -262,7 +277,7 @@ attend_flash_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             bool need = false;
             if (m_new > m_use + kRescaleStep || m_use == -INFINITY) {
                 need = l_run > 0.0f;
-                alpha = need ? exp2f(m_use - m_new) : 1.0f;
+                alpha = need ? ex2(m_use - m_new) : 1.0f;
                 m_use = m_new;
             }
             if (__any_sync(0xFFFFFFFFu, need)) {
@@ -282,27 +297,22 @@ attend_flash_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 }
                 l_run *= alpha;
             }
-            const float m_sub = m_use == -INFINITY ? 0.0f : m_use;
-            // Pass 2: probabilities, written back as bf16 pairs behind the read position.
-            float l_blk = 0.0f;
+            const float neg_m = m_use == -INFINITY ? 0.0f : -m_use;
+            float ls[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-            for (uint32_t c0 = 0; c0 < BK; c0 += 32) {
-                uint32_t r[32];
-                tmem_ld_32x32(s_tmem + c0, r);
-                tmem_ld_wait();
+            for (uint32_t c0 = 0; c0 < BK / 32; c0++) {
                 uint32_t packed[16];
 #pragma unroll
                 for (uint32_t c = 0; c < 32; c += 2) {
-                    const uint32_t cc = c0 + c;
-                    const float p0 = (cc >= c_from && cc < c_to) ? exp2f(__uint_as_float(r[c]) * p.scale_log2 - m_sub) : 0.0f;
-                    const float p1 = (cc + 1 >= c_from && cc + 1 < c_to)
-                                         ? exp2f(__uint_as_float(r[c + 1]) * p.scale_log2 - m_sub)
-                                         : 0.0f;
-                    l_blk += p0 + p1;
+                    const float p0 = ex2(fmaf(__uint_as_float(rr[c0][c]), p.scale_log2, neg_m));
+                    const float p1 = ex2(fmaf(__uint_as_float(rr[c0][c + 1]), p.scale_log2, neg_m));
+                    ls[(c >> 1) & 1] += p0;
+                    ls[2 + ((c >> 1) & 1)] += p1;
                     packed[c >> 1] = pack_bf16(p0, p1);
                 }
-                tmem_st_32x16(s_tmem + (c0 >> 1), packed);
+                tmem_st_32x16(s_tmem + c0 * 16, packed);
             }
+            const float l_blk = (ls[0] + ls[1]) + (ls[2] + ls[3]);
             l_run += l_blk;
             tmem_st_wait();
             tc_fence_before_sync();
@@ -375,12 +385,6 @@ struct Flash2Shape {
     static constexpr uint32_t bar_off = v_off + 2 * tile_bytes;
     static constexpr uint32_t total = bar_off + 256 + 1024;
 };
-
-__device__ __forceinline__ float ex2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
 
 constexpr uint32_t kThreads2 = 384;  // softmax A, softmax B, and a group of TMA + MMA + two idle warps
 

@@ -216,7 +216,12 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
-    if (S > 1) cluster_sync();  // every block's barriers exist before anyone arrives on them remotely
+    // Cluster barrier 1 (every block's barriers exist before anyone signals them remotely) is split: all
+    // arrive here, the epilogue warps wait just before their first remote store, long after.  Barrier 2
+    // (no block leaves while a peer may still write into it) likewise: a thread arrives once it will
+    // send nothing more, and waits at the very end.
+    if (S > 1) cluster_arrive();
+    bool waited1 = false, arrived2 = false;
     const uint32_t tmem_base = *tmem_slot;
     if (threadIdx.x == 0) STAMP(2);
 
@@ -339,6 +344,10 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                 if (!ok) break;
             }
             if (S > 1) {
+                if (!waited1) {
+                    cluster_wait();
+                    waited1 = true;
+                }
                 // This block will receive S x 128 rows x chunk columns of f32 for the tile.
                 if (warp == 2 && lane == 0) mbar_expect_tx(recv_full, S * kRows * chunk * 4);
                 // Send: columns [col0, col0 + CW) go to the blocks that own them as asynchronous
@@ -350,6 +359,10 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                     const uint32_t local = recv_base + ((rank * kRows + row) * rs + within) * 4;
                     st_async_f32x4(map_to_rank(local, dest), map_to_rank(bar_local, dest), v[c], v[c + 1], v[c + 2],
                                    v[c + 3]);
+                }
+                if (acc_it + 1 >= my_tiles && !arrived2) {  // nothing more goes to the peers from this thread
+                    cluster_arrive();
+                    arrived2 = true;
                 }
             } else {
                 // One block: the buffer only pairs gate rows with up rows.  Plain stores, then one
@@ -425,10 +438,14 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
         }
     }
 
+    if (S > 1) {
+        if (!waited1) cluster_wait();
+        if (!arrived2) cluster_arrive();
+    }
     tc_fence_before_sync();
     __syncthreads();
     if (threadIdx.x == 0) STAMP(10);
-    if (S > 1) cluster_sync();  // no block leaves while a peer may still write to it
+    if (S > 1) cluster_wait();  // no block leaves while a peer may still write to it
     if (threadIdx.x == 0 && *abort_flag) atomicExch(p.status, TS_ERR_TIMEOUT);
     if (warp == 1) {
         tc_fence_after_sync();

@@ -110,6 +110,11 @@ __device__ __forceinline__ void cluster_sync() {
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
+// The two halves of cluster_sync, for split-phase use: arrive early, wait where the other blocks' arrival
+// is actually needed.  Every thread of every block executes arrive, then wait, in strict alternation.
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
+
 // Address of this block's shared-memory location `saddr` in block `rank` of the cluster.
 __device__ __forceinline__ uint32_t map_to_rank(uint32_t saddr, uint32_t rank) {
     uint32_t r;
