@@ -25,6 +25,7 @@
 // current one is being reduced; three blocks share an SM, so twelve tile pairs (192 KB) per SM can
 // be in flight, which is what keeps HBM busy (0.96 of the copy rate at 4096 keys per row).  `attend_rows_kernel` loads straight into registers and covers every other width and layout.
 #include <cmath>
+#include <cstdlib>
 
 #include "head_prep.cuh"
 #include "ts_common.cuh"
@@ -592,6 +593,308 @@ attend_rows_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     if (threadIdx.x == 0 && *abort_flag) atomicExch(status, TS_ERR_TIMEOUT);
 }
 
+// ---- four query heads per kv head: the arithmetic on the tensor cores -------------------------
+//
+// With four heads sharing every key the scalar kernel above is bound by its FMA and shuffle count, not
+// by HBM.  This variant keeps its skeleton (persistent blocks, producer warp, one ring stage per consumer
+// warp, split-KV merge) and does the two products of a 32-key tile with warp MMAs (m16n8k16, bf16 in,
+// f32 out): S[16 x 32] = Q[16 x 128] K^T with the four heads in rows 0-3 of the 16-row operand (the rest
+// zero), then O[16 x 128] += P[16 x 32] V.  About 170 instructions per tile and warp instead of 1700.
+// K and V tiles arrive as two 64-column halves with the 128-byte swizzle so that ldmatrix reads them
+// without bank conflicts (K as is for the B operand of Q K^T, V transposed for the B operand of P V).
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+// d (+)= a * b; rows 8-15 of a are zero here, so their two accumulators (z0, z1) stay zero.
+__device__ __forceinline__ void mma_16816(float &d0, float &d1, float &z0, float &z1, uint32_t a0, uint32_t a2, uint32_t b0,
+                                          uint32_t b1) {
+    const uint32_t zero = 0;
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d0), "+f"(d1), "+f"(z0), "+f"(z1)
+                 : "r"(a0), "r"(zero), "r"(a2), "r"(zero), "r"(b0), "r"(b1));
+}
+// byte offset of 16-byte piece `chunk16` (of 16) of row `row` in a tile held as two swizzled 64-column halves
+__device__ __forceinline__ uint32_t swz(uint32_t row, uint32_t chunk16) {
+    return (chunk16 >> 3) * 4096 + row * 128 + (((chunk16 & 7) ^ (row & 7)) << 4);
+}
+
+__global__ void __launch_bounds__(kTmaThreads, 2)
+attend_rows_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                       const RowsParams p, const uint32_t items, int *status) {
+    using namespace ptx;
+    constexpr int G = 4, WIDTH = 128;
+    using Sh = TmaShared<G>;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    float (*sm_o)[G][WIDTH] = reinterpret_cast<float (*)[G][WIDTH]>(smem + Sh::o);
+    float (*sm_ml)[G][2] = reinterpret_cast<float (*)[G][2]>(smem + Sh::ml);
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + Sh::bars);
+    uint64_t *empty = full + kTmaStages;
+    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(smem + Sh::flag);
+
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t n_hg = p.heads / G, group = p.heads / p.kv_heads;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kTmaStages; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        prefetch_tensormap(&map_k);
+        prefetch_tensormap(&map_v);
+    }
+    __syncthreads();
+    pdl_wait();
+    pdl_launch_dependents();
+
+    if (warp == 0) {
+        // ---- producer: as in the scalar kernel, each tile as two 64-column halves ----
+        bool ok = true;
+        uint32_t odd = 0, any = 0;
+        for (uint32_t item = blockIdx.x; item < items; item += gridDim.x) {
+            const ItemRange r = item_range(p, item, n_hg);
+            if (r.lo >= r.hi) continue;
+            const int32_t x = (int32_t)((r.hg * G / group) * WIDTH);
+            const uint32_t blk_lo = r.lo / 32, blk_hi = (r.hi + 31) / 32;
+            for (uint32_t b0 = blk_lo; b0 < blk_hi; b0 += 32) {
+                const uint32_t mine = b0 + lane;
+                const uint32_t row0 = mine < blk_hi ? kept_row(p.kept, r.slot, mine * 32) : 0;
+                const uint32_t cnt = min(32u, blk_hi - b0);
+                for (uint32_t j = 0; j < cnt; j++) {
+                    const uint32_t y = __shfl_sync(0xFFFFFFFFu, row0, j);
+                    const uint32_t s = (b0 - blk_lo + j) & (kTmaStages - 1);
+                    if (lane == 0 && ok) {
+                        ok = mbar_wait_or_abort(&empty[s], ((odd >> s) & 1) ^ 1, abort_flag);
+                        if (ok) {
+                            odd ^= 1u << s;
+                            any |= 1u << s;
+                            uint8_t *dst = smem + (size_t)s * 2 * kTmaTile;
+                            mbar_expect_tx(&full[s], 2 * kTmaTile);
+                            tma_load_2d(dst, &map_k, &full[s], x, (int32_t)y);
+                            tma_load_2d(dst + 4096, &map_k, &full[s], x + 64, (int32_t)y);
+                            tma_load_2d(dst + kTmaTile, &map_v, &full[s], x, (int32_t)y);
+                            tma_load_2d(dst + kTmaTile + 4096, &map_v, &full[s], x + 64, (int32_t)y);
+                        }
+                    }
+                }
+            }
+        }
+        if (lane == 0 && !ok) {
+            for (uint32_t s = 0; s < (uint32_t)kTmaStages; s++)
+                if (((any >> s) & 1) && !mbar_wait(&full[s], ((odd >> s) & 1) ^ 1)) break;
+        }
+    } else {
+        // ---- consumers ----
+        const uint32_t cw = warp - 1, ct = threadIdx.x - 32;
+        const uint32_t hrow = lane >> 2, quad = lane & 3;  // fragment row (= head when < 4) and column pair
+        bool ok = true;
+        uint32_t used = 0;
+        const uint32_t s = cw;
+        for (uint32_t item = blockIdx.x; item < items; item += gridDim.x) {
+            const ItemRange r = item_range(p, item, n_hg);
+            const uint32_t head0 = r.hg * G;
+            const bool single = p.chunks == 1;
+            if (r.lo >= r.hi) {
+                if (!single && ct < G) {
+                    size_t at = (((size_t)r.row * p.heads + head0 + ct) * p.chunks + r.chunk) * 2;
+                    p.part_ml[at] = -INFINITY;
+                    p.part_ml[at + 1] = 0.0f;
+                }
+                if (single)
+                    for (uint32_t i = ct; i < G * WIDTH; i += kThreads)
+                        p.out[((size_t)r.row * p.heads + head0) * WIDTH + i] = 0;
+                continue;
+            }
+            const bool own_key_here = p.qkv && r.pos >= r.lo && r.pos < r.hi;
+            if (p.qkv) {
+                uint16_t *prep = reinterpret_cast<uint16_t *>(smem + Sh::prep);
+                const uint32_t per_row = p.heads + 2 * p.kv_heads, kvh = head0 / group;
+                for (uint32_t u = cw; u < (uint32_t)G + 2; u += kWarps) {
+                    const bool is_q = u < (uint32_t)G, is_v = u == (uint32_t)G + 1;
+                    if (!is_q && !own_key_here) continue;
+                    const uint32_t h = is_q ? head0 + u : (is_v ? p.heads + p.kv_heads + kvh : p.heads + kvh);
+                    const uint16_t *src = p.qkv + ((size_t)r.row * per_row + h) * WIDTH;
+                    uint16_t *dst = prep + u * WIDTH;
+                    if (is_v) {
+                        if (lane < 16) reinterpret_cast<uint4 *>(dst)[lane] = reinterpret_cast<const uint4 *>(src)[lane];
+                    } else {
+                        uint16_t lo[2], hi[2];
+                        norm_rope_head<WIDTH>(src, is_q ? p.q_norm : p.k_norm, p.inv_freq, r.pos, p.eps, lane, lo, hi);
+                        *reinterpret_cast<uint32_t *>(dst + lane * 2) = (uint32_t)lo[0] | ((uint32_t)lo[1] << 16);
+                        *reinterpret_cast<uint32_t *>(dst + WIDTH / 2 + lane * 2) = (uint32_t)hi[0] | ((uint32_t)hi[1] << 16);
+                    }
+                    __syncwarp();
+                    if (!is_q && head0 % group == 0 && lane < 16) {
+                        const size_t at = ((size_t)kept_row(p.kept, r.slot, r.pos) * p.kv_heads + kvh) * WIDTH;
+                        reinterpret_cast<uint4 *>((is_v ? p.v_out : p.k_out) + at)[lane] = reinterpret_cast<const uint4 *>(dst)[lane];
+                    }
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory");
+            }
+            // Q as the A operand: rows 0-3 are the four heads (lanes 0-15), rows 4-15 zero.  Per 16-wide
+            // k step: qa[t][0] = dims 16 t + 2 quad, +1; qa[t][1] = the same + 8.
+            uint32_t qa[8][2];
+#pragma unroll
+            for (int t = 0; t < 8; t++) {
+                qa[t][0] = qa[t][1] = 0;
+                if (hrow < (uint32_t)G) {
+                    const uint32_t d = 16 * t + 2 * quad;
+                    if (p.qkv) {
+                        const uint8_t *qs = smem + Sh::prep + hrow * 256;
+                        qa[t][0] = *reinterpret_cast<const uint32_t *>(qs + d * 2);
+                        qa[t][1] = *reinterpret_cast<const uint32_t *>(qs + (d + 8) * 2);
+                    } else {
+                        const uint16_t *qg = p.q + ((size_t)r.row * p.heads + head0 + hrow) * WIDTH;
+                        qa[t][0] = *reinterpret_cast<const uint32_t *>(qg + d);
+                        qa[t][1] = *reinterpret_cast<const uint32_t *>(qg + d + 8);
+                    }
+                }
+            }
+            float m_row = -INFINITY, l_row = 0.0f;  // of head `hrow` (rows 4-7: never read)
+            float oacc[16][2];                       // O[hrow][8 n + 2 quad, +1]
+            float z0 = 0.0f, z1 = 0.0f;              // rows 8-15 of every product: stay zero
+#pragma unroll
+            for (int n = 0; n < 16; n++) oacc[n][0] = oacc[n][1] = 0.0f;
+
+            const uint32_t blk_lo = r.lo / 32, blk_hi = (r.hi + 31) / 32;
+            for (uint32_t blk = blk_lo + cw; blk < blk_hi; blk += kWarps) {
+                if (ok) ok = mbar_wait_or_abort(&full[s], used & 1, abort_flag);
+                used++;
+                if (ok) {
+                    uint8_t *tile_k = smem + (size_t)s * 2 * kTmaTile;
+                    uint8_t *tile_v = tile_k + kTmaTile;
+                    const uint32_t base = blk * 32;
+                    if (own_key_here && r.pos - base < 32) {
+                        // the row's own key and value, from the prepared copies (the tile was read before or
+                        // while they were appended)
+                        const uint32_t c16 = lane & 15, row = r.pos - base;
+                        const uint8_t *from = smem + Sh::prep + (G + (lane >> 4)) * 256 + c16 * 16;
+                        uint8_t *to = (lane < 16 ? tile_k : tile_v) + swz(row, c16);
+                        *reinterpret_cast<uint4 *>(to) = *reinterpret_cast<const uint4 *>(from);
+                        fence_async_shared();
+                        __syncwarp();
+                    }
+                    if (base < r.lo || base + 32 > r.hi) {
+                        // rows outside the range may hold anything: zero their V (both halves)
+                        for (uint32_t j = 0; j < 32; j++) {
+                            const uint32_t key = base + j;
+                            if (key < r.lo || key >= r.hi)
+                                *reinterpret_cast<uint2 *>(tile_v + (lane >> 4) * 4096 + j * 128 + (lane & 15) * 8) = make_uint2(0, 0);
+                        }
+                        fence_async_shared();
+                        __syncwarp();
+                    }
+                    // ---- S = Q K^T: four 8-key column tiles ----
+                    const uint32_t k_addr = smem_addr(tile_k), v_addr = smem_addr(tile_v);
+                    const uint32_t mtx = lane >> 3, mrow = lane & 7;
+                    float sc[4][2];
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        sc[j][0] = sc[j][1] = 0.0f;
+#pragma unroll
+                        for (int p4 = 0; p4 < 4; p4++) {
+                            uint32_t b[4];
+                            ldsm_x4(k_addr + swz(8 * j + mrow, 4 * p4 + mtx), b);
+                            mma_16816(sc[j][0], sc[j][1], z0, z1, qa[2 * p4][0], qa[2 * p4][1], b[0], b[1]);
+                            mma_16816(sc[j][0], sc[j][1], z0, z1, qa[2 * p4 + 1][0], qa[2 * p4 + 1][1], b[2], b[3]);
+                        }
+                    }
+                    // ---- softmax over the tile's keys; this lane holds keys base + 8 j + 2 quad, +1 of head hrow ----
+                    float mx = -INFINITY;
+#pragma unroll
+                    for (int j = 0; j < 4; j++)
+#pragma unroll
+                        for (int e = 0; e < 2; e++) {
+                            const uint32_t key = base + 8 * j + 2 * quad + e;
+                            sc[j][e] = (key >= r.lo && key < r.hi) ? sc[j][e] * p.scale : -INFINITY;
+                            mx = fmaxf(mx, sc[j][e]);
+                        }
+                    mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
+                    mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
+                    const float m_new = fmaxf(m_row, mx);  // finite: the tile holds a visible key
+                    const float alpha = __expf(m_row - m_new);
+                    m_row = m_new;
+                    uint32_t pa[2][2];  // P as the A operand of the two 16-key steps
+                    float sum = 0.0f;
+#pragma unroll
+                    for (int u = 0; u < 2; u++)
+#pragma unroll
+                        for (int h = 0; h < 2; h++) {
+                            const float p0 = __expf(sc[2 * u + h][0] - m_new), p1 = __expf(sc[2 * u + h][1] - m_new);
+                            sum += p0 + p1;
+                            pa[u][h] = pack_bf16(p0, p1);
+                        }
+                    l_row = l_row * alpha + sum;
+#pragma unroll
+                    for (int n = 0; n < 16; n++) {
+                        oacc[n][0] *= alpha;
+                        oacc[n][1] *= alpha;
+                    }
+                    // ---- O += P V: two 16-key steps, sixteen 8-dim column tiles two at a time ----
+#pragma unroll
+                    for (int u = 0; u < 2; u++)
+#pragma unroll
+                        for (int n2 = 0; n2 < 8; n2++) {
+                            uint32_t b[4];
+                            ldsm_x4_trans(v_addr + swz(16 * u + (mtx & 1) * 8 + mrow, 2 * n2 + (mtx >> 1)), b);
+                            mma_16816(oacc[2 * n2][0], oacc[2 * n2][1], z0, z1, pa[u][0], pa[u][1], b[0], b[1]);
+                            mma_16816(oacc[2 * n2 + 1][0], oacc[2 * n2 + 1][1], z0, z1, pa[u][0], pa[u][1], b[2], b[3]);
+                        }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[s]);
+            }
+            // ---- this warp's partial to shared memory, then the four warps fold ----
+            l_row += __shfl_xor_sync(0xFFFFFFFFu, l_row, 1);
+            l_row += __shfl_xor_sync(0xFFFFFFFFu, l_row, 2);
+            if (hrow < (uint32_t)G) {
+#pragma unroll
+                for (int n = 0; n < 16; n++)
+                    *reinterpret_cast<float2 *>(&sm_o[cw][hrow][8 * n + 2 * quad]) = make_float2(oacc[n][0], oacc[n][1]);
+                if (quad == 0) {
+                    sm_ml[cw][hrow][0] = m_row;
+                    sm_ml[cw][hrow][1] = l_row;
+                }
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory");
+            for (uint32_t i = ct; i < G * WIDTH; i += kThreads) {
+                const uint32_t g = i / WIDTH, d = i % WIDTH;
+                float mm = -INFINITY;
+#pragma unroll
+                for (int w = 0; w < kWarps; w++) mm = fmaxf(mm, sm_ml[w][g][0]);
+                float ll = 0.0f, oo = 0.0f;
+#pragma unroll
+                for (int w = 0; w < kWarps; w++) {
+                    float mw = sm_ml[w][g][0];
+                    float f = mw == -INFINITY ? 0.0f : __expf(mw - mm);
+                    ll += sm_ml[w][g][1] * f;
+                    oo += sm_o[w][g][d] * f;
+                }
+                if (single) {
+                    p.out[((size_t)r.row * p.heads + head0 + g) * WIDTH + d] = ll > 0.0f ? bf16_bits(oo / ll) : (uint16_t)0;
+                } else {
+                    size_t at = ((size_t)r.row * p.heads + head0 + g) * p.chunks + r.chunk;
+                    p.part_o[at * WIDTH + d] = oo;
+                    if (d == 0) {
+                        p.part_ml[at * 2] = mm;
+                        p.part_ml[at * 2 + 1] = ll;
+                    }
+                }
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory");
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag) atomicExch(status, TS_ERR_TIMEOUT);
+}
+
 // One block per (row, head): folds the chunks in ascending order.
 template <int WIDTH>
 __global__ void __launch_bounds__(WIDTH) attend_rows_merge_kernel(const RowsParams p) {
@@ -638,6 +941,15 @@ cudaError_t launch_rows(const RowsParams &p, dim3 grid, cudaStream_t stream) {
 
 __device__ int g_rows_status = 0;
 
+// TS_ROWS_MMA=0 keeps groups of four on the scalar kernel (for A/B timing).
+bool rows_mma_enabled() {
+    static const bool off = [] {
+        const char *v = getenv("TS_ROWS_MMA");
+        return v && v[0] == '0';
+    }();
+    return !off;
+}
+
 template <int G>
 int launch_rows_tma(const CUtensorMap &map_k, const CUtensorMap &map_v, const RowsParams &p, uint32_t items,
                     cudaStream_t stream) {
@@ -654,6 +966,25 @@ int launch_rows_tma(const CUtensorMap &map_k, const CUtensorMap &map_v, const Ro
                            map_k, map_v, p, items, status);
     if (e != cudaSuccess)
         return fail(TS_ERR_CUDA, "launch of attend_rows (tma) failed: %s (%d) %s", cudaGetErrorName(e), (int)e,
+                    cudaGetErrorString(e));
+    return TS_OK;
+}
+
+int launch_rows_mma(const CUtensorMap &map_k, const CUtensorMap &map_v, const RowsParams &p, uint32_t items,
+                    cudaStream_t stream) {
+    using Sh = TmaShared<4>;
+    static bool configured = false;
+    if (!configured) {
+        TS_CUDA(cudaFuncSetAttribute(attend_rows_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Sh::bytes));
+        configured = true;
+    }
+    int *status = nullptr;
+    TS_CUDA(cudaGetSymbolAddress((void **)&status, g_rows_status));
+    const uint32_t grid = min(items, (uint32_t)sm_count() * 2);
+    cudaError_t e = launch(attend_rows_mma_kernel, dim3(grid), dim3(kTmaThreads), Sh::bytes, stream, pdl_enabled(), map_k,
+                           map_v, p, items, status);
+    if (e != cudaSuccess)
+        return fail(TS_ERR_CUDA, "launch of attend_rows (mma) failed: %s (%d) %s", cudaGetErrorName(e), (int)e,
                     cudaGetErrorString(e));
     return TS_OK;
 }
@@ -730,12 +1061,16 @@ int attend_rows(const void *q, const void *k, const void *v, void *out, const ui
     if (tma) {
         CUtensorMap map_k, map_v;
         const uint64_t cols = (uint64_t)kv_heads * width;
-        int rc = make_tensor_map_2d_plain(&map_k, k, kept_rows, cols, cols, 32, 128);
+        const bool tensor = s.g == 4 && rows_mma_enabled();  // four heads per key: the warp-MMA variant
+        int rc = tensor ? make_tensor_map_2d(&map_k, k, kept_rows, cols, cols, 32, 64)
+                        : make_tensor_map_2d_plain(&map_k, k, kept_rows, cols, cols, 32, 128);
         if (rc != TS_OK) return rc;
-        rc = make_tensor_map_2d_plain(&map_v, v, kept_rows, cols, cols, 32, 128);
+        rc = tensor ? make_tensor_map_2d(&map_v, v, kept_rows, cols, cols, 32, 64)
+                    : make_tensor_map_2d_plain(&map_v, v, kept_rows, cols, cols, 32, 128);
         if (rc != TS_OK) return rc;
         const uint32_t items = rows * (heads / s.g) * s.chunks;
-        rc = s.g == 4   ? launch_rows_tma<4>(map_k, map_v, p, items, stream)
+        rc = tensor     ? launch_rows_mma(map_k, map_v, p, items, stream)
+             : s.g == 4 ? launch_rows_tma<4>(map_k, map_v, p, items, stream)
              : s.g == 2 ? launch_rows_tma<2>(map_k, map_v, p, items, stream)
                         : launch_rows_tma<1>(map_k, map_v, p, items, stream);
         if (rc != TS_OK) return rc;

@@ -18,11 +18,29 @@ __device__ __forceinline__ void norm_rope_head(const uint16_t *src, const float 
     constexpr int PER = WIDTH / 64;
     float a[PER], b[PER];
     float ss = 0.0f;
+    // the lane's PER consecutive elements of each half in one load
+    uint16_t ra[PER], rb[PER];
+    if constexpr (PER == 4) {
+        const uint2 va = *reinterpret_cast<const uint2 *>(src + lane * 4);
+        const uint2 vb = *reinterpret_cast<const uint2 *>(src + WIDTH / 2 + lane * 4);
+        ra[0] = va.x & 0xFFFF; ra[1] = va.x >> 16; ra[2] = va.y & 0xFFFF; ra[3] = va.y >> 16;
+        rb[0] = vb.x & 0xFFFF; rb[1] = vb.x >> 16; rb[2] = vb.y & 0xFFFF; rb[3] = vb.y >> 16;
+    } else if constexpr (PER == 2) {
+        const uint32_t va = *reinterpret_cast<const uint32_t *>(src + lane * 2);
+        const uint32_t vb = *reinterpret_cast<const uint32_t *>(src + WIDTH / 2 + lane * 2);
+        ra[0] = va & 0xFFFF; ra[1] = va >> 16;
+        rb[0] = vb & 0xFFFF; rb[1] = vb >> 16;
+    } else {
+#pragma unroll
+        for (int e = 0; e < PER; e++) {
+            ra[e] = src[lane * PER + e];
+            rb[e] = src[lane * PER + e + WIDTH / 2];
+        }
+    }
 #pragma unroll
     for (int e = 0; e < PER; e++) {
-        const uint32_t j = lane * PER + e;
-        a[e] = __uint_as_float((uint32_t)src[j] << 16);
-        b[e] = __uint_as_float((uint32_t)src[j + WIDTH / 2] << 16);
+        a[e] = __uint_as_float((uint32_t)ra[e] << 16);
+        b[e] = __uint_as_float((uint32_t)rb[e] << 16);
         ss = fmaf(a[e], a[e], ss);
         ss = fmaf(b[e], b[e], ss);
     }

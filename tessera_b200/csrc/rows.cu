@@ -180,11 +180,21 @@ __global__ void __launch_bounds__(128) qk_norm_rope_append_kernel(
     // lane owns pairs j = lane * PER + e: elements j and j + WIDTH/2
     uint16_t lo[PER], hi[PER];
     norm_rope_head<WIDTH>(src, gain, inv_freq, pos, eps, lane, lo, hi);
+    if constexpr (PER == 4) {
+        *reinterpret_cast<uint2 *>(dst + lane * 4) =
+            make_uint2((uint32_t)lo[0] | ((uint32_t)lo[1] << 16), (uint32_t)lo[2] | ((uint32_t)lo[3] << 16));
+        *reinterpret_cast<uint2 *>(dst + WIDTH / 2 + lane * 4) =
+            make_uint2((uint32_t)hi[0] | ((uint32_t)hi[1] << 16), (uint32_t)hi[2] | ((uint32_t)hi[3] << 16));
+    } else if constexpr (PER == 2) {
+        *reinterpret_cast<uint32_t *>(dst + lane * 2) = (uint32_t)lo[0] | ((uint32_t)lo[1] << 16);
+        *reinterpret_cast<uint32_t *>(dst + WIDTH / 2 + lane * 2) = (uint32_t)hi[0] | ((uint32_t)hi[1] << 16);
+    } else {
 #pragma unroll
-    for (int e = 0; e < PER; e++) {
-        const uint32_t j = lane * PER + e;
-        dst[j] = lo[e];
-        dst[j + WIDTH / 2] = hi[e];
+        for (int e = 0; e < PER; e++) {
+            const uint32_t j = lane * PER + e;
+            dst[j] = lo[e];
+            dst[j + WIDTH / 2] = hi[e];
+        }
     }
 }
 

@@ -85,12 +85,13 @@ def test_rows_match_oracle(layout, order, heads, kv_heads, width):
     assert rel_error(widen(got), want) <= TOL
 
 
-@pytest.mark.parametrize("page_layout", ["paged", "paged16"])
-def test_long_ragged_contexts_split_and_merge(page_layout):
-    # the decode shape of the isolated attention config, scaled down: contexts 40..2100, GQA 16/8
+@pytest.mark.parametrize("page_layout,kv_heads", [("paged", 8), ("paged16", 8), ("paged", 4), ("dense", 4)])
+def test_long_ragged_contexts_split_and_merge(page_layout, kv_heads):
+    # the decode shape of the isolated attention config, scaled down: contexts 40..2100, GQA 16/8 (two heads
+    # per key: the scalar kernels) and 16/4 (four: the warp-MMA kernel)
     from tessera_b200 import ops
     rng = np.random.default_rng(4)
-    slots, heads, kv_heads, width = 5, 16, 8, 128
+    slots, heads, width = 5, 16, 128
     lengths = [40, 513, 1024, 2100, 777]
     context = max(lengths)
     kept, row_fn, total = _layout(page_layout, slots, context, rng)
@@ -108,13 +109,14 @@ def test_long_ragged_contexts_split_and_merge(page_layout):
     assert torch.equal(got, again)  # fixed merge order: same bits on a re-run
 
 
+@pytest.mark.parametrize("kv_heads", [4, 2])
 @pytest.mark.parametrize("layout", ["dense", "paged"])
-def test_unwritten_rows_may_hold_anything(layout):
+def test_unwritten_rows_may_hold_anything(layout, kv_heads):
     # Rows past a slot's last position (a page's tail, a dense slot's unused part) are never written;
     # whatever bits they hold must not reach the output.
     from tessera_b200 import ops
     rng = np.random.default_rng(21)
-    slots, heads, kv_heads, width = 4, 8, 4, 128
+    slots, heads, width = 4, 8, 128
     lengths = [1, 33, 70, 190]
     context = 256
     kept, row_fn, total = _layout(layout, slots, context, rng)
