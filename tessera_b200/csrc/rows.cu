@@ -146,7 +146,7 @@ template <int WIDTH>
 __global__ void __launch_bounds__(128) qk_norm_rope_append_kernel(
     const uint16_t *qkv, const float *q_norm, const float *k_norm, const float *inv_freq, const uint32_t *slots,
     const uint32_t *positions, uint16_t *q_out, uint16_t *k_rows, uint16_t *v_rows, KeptDev kept, uint32_t rows,
-    uint32_t heads, uint32_t kv_heads, float eps) {
+    uint32_t heads, uint32_t kv_heads, float eps, uint16_t *k_dense, uint16_t *v_dense) {
     constexpr int PER = WIDTH / 64;  // pairs per lane
     pdl_wait();
     const uint32_t lane = threadIdx.x & 31;
@@ -157,7 +157,7 @@ __global__ void __launch_bounds__(128) qk_norm_rope_append_kernel(
     const uint16_t *src = qkv + ((size_t)r * per_row + h) * WIDTH;
     const uint32_t pos = positions[r];
 
-    uint16_t *dst;
+    uint16_t *dst, *dst2 = nullptr;  // dst2: the optional packed copy [rows, kv_heads, WIDTH] of k and v
     const float *gain = nullptr;
     bool turn = true;
     if (h < heads) {
@@ -168,13 +168,18 @@ __global__ void __launch_bounds__(128) qk_norm_rope_append_kernel(
         const bool is_v = h >= heads + kv_heads;
         const size_t at = ((size_t)kept_row(kept, slots[r], pos) * kv_heads + kvh) * WIDTH;
         dst = (is_v ? v_rows : k_rows) + at;
+        uint16_t *dense = is_v ? v_dense : k_dense;
+        if (dense) dst2 = dense + ((size_t)r * kv_heads + kvh) * WIDTH;
         gain = is_v ? nullptr : k_norm;
         turn = !is_v;
     }
     if (!turn) {
         // values pass through
-        for (uint32_t i = lane; i < WIDTH / 8; i += 32)
-            reinterpret_cast<uint4 *>(dst)[i] = reinterpret_cast<const uint4 *>(src)[i];
+        for (uint32_t i = lane; i < WIDTH / 8; i += 32) {
+            const uint4 v = reinterpret_cast<const uint4 *>(src)[i];
+            reinterpret_cast<uint4 *>(dst)[i] = v;
+            if (dst2) reinterpret_cast<uint4 *>(dst2)[i] = v;
+        }
         return;
     }
     // lane owns pairs j = lane * PER + e: elements j and j + WIDTH/2
@@ -194,6 +199,14 @@ __global__ void __launch_bounds__(128) qk_norm_rope_append_kernel(
             const uint32_t j = lane * PER + e;
             dst[j] = lo[e];
             dst[j + WIDTH / 2] = hi[e];
+        }
+    }
+    if (dst2) {
+#pragma unroll
+        for (int e = 0; e < PER; e++) {
+            const uint32_t j = lane * PER + e;
+            dst2[j] = lo[e];
+            dst2[j + WIDTH / 2] = hi[e];
         }
     }
 }
@@ -504,7 +517,7 @@ int scatter_rows(const void *x, const uint32_t *slots, const uint32_t *positions
 int qk_norm_rope_append(const void *qkv, const float *q_norm, const float *k_norm, const float *inv_freq,
                         const uint32_t *slots, const uint32_t *positions, void *q_out, void *k_rows, void *v_rows,
                         const KeptDev &kept, uint32_t rows, uint32_t heads, uint32_t kv_heads, uint32_t width,
-                        float eps, cudaStream_t stream) {
+                        float eps, cudaStream_t stream, void *k_dense, void *v_dense) {
     if (rows == 0) return TS_OK;
     const uint32_t units = rows * (heads + 2 * kv_heads);
     dim3 grid(ceil_div(units, 4));
@@ -512,15 +525,15 @@ int qk_norm_rope_append(const void *qkv, const float *q_norm, const float *k_nor
     if (width == 128)
         e = launch(qk_norm_rope_append_kernel<128>, grid, dim3(128), 0, stream, pdl_enabled(), (const uint16_t *)qkv,
                    q_norm, k_norm, inv_freq, slots, positions, (uint16_t *)q_out, (uint16_t *)k_rows,
-                   (uint16_t *)v_rows, kept, rows, heads, kv_heads, eps);
+                   (uint16_t *)v_rows, kept, rows, heads, kv_heads, eps, (uint16_t *)k_dense, (uint16_t *)v_dense);
     else if (width == 256)
         e = launch(qk_norm_rope_append_kernel<256>, grid, dim3(128), 0, stream, pdl_enabled(), (const uint16_t *)qkv,
                    q_norm, k_norm, inv_freq, slots, positions, (uint16_t *)q_out, (uint16_t *)k_rows,
-                   (uint16_t *)v_rows, kept, rows, heads, kv_heads, eps);
+                   (uint16_t *)v_rows, kept, rows, heads, kv_heads, eps, (uint16_t *)k_dense, (uint16_t *)v_dense);
     else if (width == 64)
         e = launch(qk_norm_rope_append_kernel<64>, grid, dim3(128), 0, stream, pdl_enabled(), (const uint16_t *)qkv,
                    q_norm, k_norm, inv_freq, slots, positions, (uint16_t *)q_out, (uint16_t *)k_rows,
-                   (uint16_t *)v_rows, kept, rows, heads, kv_heads, eps);
+                   (uint16_t *)v_rows, kept, rows, heads, kv_heads, eps, (uint16_t *)k_dense, (uint16_t *)v_dense);
     else
         return fail(TS_ERR_BAD_INPUT, "qk_norm_rope_append: width %u is not 64, 128 or 256", width);
     if (e != cudaSuccess) return fail(TS_ERR_CUDA, "launch of qk_norm_rope_append failed: %s", cudaGetErrorString(e));

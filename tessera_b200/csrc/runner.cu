@@ -35,6 +35,9 @@ struct ts_decoder {
     uint16_t *h_out = nullptr;   // final normed rows of the wanted rows [max_rows, hidden]
     float *sumsq = nullptr;      // per-tile sums of squares of the residual rows [max_rows, 32]
     bool last_distinct = false;  // the rows of the last launch sat in slots of their own
+    uint16_t *k_dense = nullptr, *v_dense = nullptr;  // packed k, v of a fresh-prompt launch [max_rows, kv_heads, head_dim]
+    uint32_t *cu = nullptr;      // device: row offsets of the prompts of such a launch [slots + 1]
+    uint32_t fresh_seqs = 0, fresh_longest = 0;  // set by ts_decoder_step for the launch it is about to submit
     float *logits = nullptr;     // [max_out, vocab]
     uint32_t max_out = 0;
     uint32_t *tokens = nullptr, *slots = nullptr, *positions = nullptr, *out_rows = nullptr, *ids = nullptr;
@@ -134,6 +137,15 @@ uint32_t fold_parts(const ts_decoder *d, uint32_t rows) {
     return ok ? parts : 0;
 }
 
+// TS_FRESH_PROMPTS=0 sends whole prompts through the kept-row attention like any other launch (for A/B).
+bool fresh_prompts_enabled() {
+    static const bool off = [] {
+        const char *v = getenv("TS_FRESH_PROMPTS");
+        return v && v[0] == '0';
+    }();
+    return !off;
+}
+
 // Whether the attention launch also does the per-head norm, the rotation and the append: only when no
 // two rows of the launch share a slot (a row must not read a key that another row of the same launch
 // appends), at head width 128 over a layout the TMA-fed kernel takes.  TS_FUSE_APPEND=0 turns it off.
@@ -217,7 +229,15 @@ int enqueue(ts_decoder *d, uint32_t rows, uint32_t keys, uint32_t n_out, bool fe
             STEP("rms_norm", rms_norm(d->x, TS_F32, L.ln1, d->h, TS_BF16, rows, H, c.eps, nullptr, s));
             STEP("linear_qkv", linear(d->h, L.wqkv, nullptr, d->qkv, d->qkv_n, H, TS_EPI_NONE, TS_BF16));
         }
-        if (append_in_attention(d, distinct)) {
+        if (d->fresh_seqs > 0) {
+            // Whole prompts from position 0: every key a row may see was made in this launch, so attention runs
+            // over the packed q, k, v with the tensor-core kernel; the kept rows are still written for later steps.
+            STEP("qk_norm_rope_append", qk_norm_rope_append(d->qkv, c.qk_norm ? L.q_norm : nullptr, c.qk_norm ? L.k_norm : nullptr, d->inv_freq,
+                                     d->slots, d->positions, d->q, L.k_rows, L.v_rows, kd, rows, c.heads, c.kv_heads, D,
+                                     c.eps, s, d->k_dense, d->v_dense));
+            STEP("attend_flash", attend_flash(d->q, d->k_dense, d->v_dense, d->attn, d->cu, d->fresh_seqs, d->fresh_longest, rows, rows,
+                              rows, c.heads, c.kv_heads, D, 0xFFFFFFFFu, 0, scale, s));
+        } else if (append_in_attention(d, distinct)) {
             // One row per slot (a decode step): the attention kernel norms, rotates and appends itself.
             RowsFused f;
             f.qkv = d->qkv;
@@ -353,6 +373,9 @@ int ts_decoder_create(const ts_decoder_config *config, ts_decoder **out) {
     A(dev_alloc(d, &d->act, R * c.ffn));
     A(dev_alloc(d, &d->h_out, R * H));
     A(dev_alloc(d, &d->sumsq, R * 32));
+    A(dev_alloc(d, &d->k_dense, R * KW));
+    A(dev_alloc(d, &d->v_dense, R * KW));
+    A(dev_alloc(d, &d->cu, (size_t)c.slots + 1));
     A(dev_alloc(d, &d->logits, (size_t)d->max_out * c.vocab));
     A(dev_alloc(d, &d->tokens, R));
     A(dev_alloc(d, &d->slots, R));
@@ -503,8 +526,53 @@ int ts_decoder_step(ts_decoder *d, const uint32_t *tokens, const uint32_t *slots
             seen[slots[r]] = true;
         }
     }
+    // A launch of whole prompts: the rows of every slot are consecutive and hold positions 0, 1, 2, ... (a fresh
+    // sequence, nothing kept before).  Then attention needs no kept rows and takes the prefill kernel.
+    d->fresh_seqs = 0;
+    std::vector<uint32_t> cu;
+    if (!distinct && flash_supports(c.head_dim) && fresh_prompts_enabled()) {
+        bool fresh = true;
+        cu.push_back(0);
+        uint32_t longest = 0;
+        for (uint32_t r = 0; r < rows && fresh; r++) {
+            const bool starts = r == 0 || slots[r] != slots[r - 1];
+            if (starts) {
+                fresh = positions[r] == 0;
+                if (r > 0) {
+                    longest = std::max(longest, r - cu.back());
+                    cu.push_back(r);
+                }
+            } else {
+                fresh = positions[r] == positions[r - 1] + 1;
+            }
+        }
+        if (fresh) {
+            // no slot may come back after another one started
+            std::vector<bool> seen(c.slots, false);
+            for (size_t i = 0; i < cu.size() && fresh; i++) {
+                fresh = !seen[slots[cu[i]]];
+                seen[slots[cu[i]]] = true;
+            }
+        }
+        if (fresh) {
+            longest = std::max(longest, rows - cu.back());
+            cu.push_back(rows);
+            TS_CUDA(cudaMemcpyAsync(d->cu, cu.data(), cu.size() * 4, cudaMemcpyHostToDevice, s));
+            TS_CUDA(cudaStreamSynchronize(s));  // cu is a local: the copy must have read it before it goes away
+            d->fresh_seqs = (uint32_t)cu.size() - 1;
+            d->fresh_longest = longest;
+        }
+    }
     const uint32_t keys = keys_bucket(d, furthest);
-    int rc = submit(d, rows, keys, n_out, false, distinct, s);
+    int rc;
+    if (d->fresh_seqs > 0) {
+        // one-off shapes: not worth a captured graph
+        set_pdl(d->c.pdl != 0);
+        rc = enqueue(d, rows, keys, n_out, false, false, s, nullptr);
+        d->fresh_seqs = 0;
+    } else {
+        rc = submit(d, rows, keys, n_out, false, distinct, s);
+    }
     if (rc != TS_OK) return rc;
     d->last_distinct = distinct;
     d->last_rows = rows;

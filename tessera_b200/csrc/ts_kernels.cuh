@@ -82,10 +82,11 @@ int gather_rows(const void *table, const uint32_t *ids, void *out, int out_dtype
                 uint32_t table_rows, uint32_t width, uint32_t first, cudaStream_t stream);
 int scatter_rows(const void *x, const uint32_t *slots, const uint32_t *positions, void *out, const KeptDev &kept,
                  uint32_t rows, uint32_t width, cudaStream_t stream);
+// k_dense, v_dense (optional): packed copies [rows, kv_heads, width] of the prepared keys and values.
 int qk_norm_rope_append(const void *qkv, const float *q_norm, const float *k_norm, const float *inv_freq,
                         const uint32_t *slots, const uint32_t *positions, void *q_out, void *k_rows, void *v_rows,
                         const KeptDev &kept, uint32_t rows, uint32_t heads, uint32_t kv_heads, uint32_t width,
-                        float eps, cudaStream_t stream);
+                        float eps, cudaStream_t stream, void *k_dense = nullptr, void *v_dense = nullptr);
 size_t top_k_workspace_bytes(uint32_t rows, uint32_t width, uint32_t k);
 int top_k(const void *x, int x_dtype, uint32_t *ids, uint32_t rows, uint32_t width, uint32_t k, void *workspace,
           size_t workspace_bytes, cudaStream_t stream);
