@@ -625,23 +625,39 @@ __device__ __forceinline__ uint32_t swz(uint32_t row, uint32_t chunk16) {
     return (chunk16 >> 3) * 4096 + row * 128 + (((chunk16 & 7) ^ (row & 7)) << 4);
 }
 
-__global__ void __launch_bounds__(kTmaThreads, 2)
+// CW consumer warps (and ring stages) per block.  Three: 53 KB and 128 threads, so four blocks share an SM
+// and a decode batch of 64 rows x 8 kv heads (512 short items) is resident at once instead of queueing a
+// second item behind a third of the blocks.  Four (two blocks per SM, no register cap to speak of): long items.
+template <int G, int CW>
+struct MmaShared {
+    static constexpr size_t ring = (size_t)CW * 2 * kTmaTile;
+    static constexpr size_t o = ring;                               // float [CW][G][128]
+    static constexpr size_t ml = o + sizeof(float) * CW * G * 128;  // float [CW][G][2]
+    static constexpr size_t bars = ml + sizeof(float) * CW * G * 2; // full[CW], empty[CW]
+    static constexpr size_t flag = bars + sizeof(uint64_t) * 2 * CW;
+    static constexpr size_t prep = (flag + 16 + 15) / 16 * 16;      // bf16 [G + 2][128]
+    static constexpr size_t bytes = prep + (G + 2) * 256;
+};
+
+template <int G, int CW>
+__global__ void __launch_bounds__(32 + CW * 32, CW == 3 ? 4 : 2)
 attend_rows_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                        const RowsParams p, const uint32_t items, int *status) {
     using namespace ptx;
-    constexpr int G = 4, WIDTH = 128;
-    using Sh = TmaShared<G>;
+    constexpr int WIDTH = 128;
+    using Sh = MmaShared<G, CW>;
+    constexpr int kMmaWarps = CW, kMmaConsumers = CW * 32;
     extern __shared__ __align__(1024) uint8_t smem[];
     float (*sm_o)[G][WIDTH] = reinterpret_cast<float (*)[G][WIDTH]>(smem + Sh::o);
     float (*sm_ml)[G][2] = reinterpret_cast<float (*)[G][2]>(smem + Sh::ml);
     uint64_t *full = reinterpret_cast<uint64_t *>(smem + Sh::bars);
-    uint64_t *empty = full + kTmaStages;
+    uint64_t *empty = full + kMmaWarps;
     volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(smem + Sh::flag);
 
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t n_hg = p.heads / G, group = p.heads / p.kv_heads;
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kTmaStages; s++) {
+        for (int s = 0; s < kMmaWarps; s++) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
@@ -669,7 +685,7 @@ attend_rows_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                 const uint32_t cnt = min(32u, blk_hi - b0);
                 for (uint32_t j = 0; j < cnt; j++) {
                     const uint32_t y = __shfl_sync(0xFFFFFFFFu, row0, j);
-                    const uint32_t s = (b0 - blk_lo + j) & (kTmaStages - 1);
+                    const uint32_t s = (b0 - blk_lo + j) % kMmaWarps;
                     if (lane == 0 && ok) {
                         ok = mbar_wait_or_abort(&empty[s], ((odd >> s) & 1) ^ 1, abort_flag);
                         if (ok) {
@@ -687,7 +703,7 @@ attend_rows_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             }
         }
         if (lane == 0 && !ok) {
-            for (uint32_t s = 0; s < (uint32_t)kTmaStages; s++)
+            for (uint32_t s = 0; s < (uint32_t)kMmaWarps; s++)
                 if (((any >> s) & 1) && !mbar_wait(&full[s], ((odd >> s) & 1) ^ 1)) break;
         }
     } else {
@@ -708,7 +724,7 @@ attend_rows_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                     p.part_ml[at + 1] = 0.0f;
                 }
                 if (single)
-                    for (uint32_t i = ct; i < G * WIDTH; i += kThreads)
+                    for (uint32_t i = ct; i < G * WIDTH; i += kMmaConsumers)
                         p.out[((size_t)r.row * p.heads + head0) * WIDTH + i] = 0;
                 continue;
             }
@@ -716,7 +732,7 @@ attend_rows_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             if (p.qkv) {
                 uint16_t *prep = reinterpret_cast<uint16_t *>(smem + Sh::prep);
                 const uint32_t per_row = p.heads + 2 * p.kv_heads, kvh = head0 / group;
-                for (uint32_t u = cw; u < (uint32_t)G + 2; u += kWarps) {
+                for (uint32_t u = cw; u < (uint32_t)G + 2; u += kMmaWarps) {
                     const bool is_q = u < (uint32_t)G, is_v = u == (uint32_t)G + 1;
                     if (!is_q && !own_key_here) continue;
                     const uint32_t h = is_q ? head0 + u : (is_v ? p.heads + p.kv_heads + kvh : p.heads + kvh);
@@ -736,7 +752,7 @@ attend_rows_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                         reinterpret_cast<uint4 *>((is_v ? p.v_out : p.k_out) + at)[lane] = reinterpret_cast<const uint4 *>(dst)[lane];
                     }
                 }
-                asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory");
+                asm volatile("bar.sync 1, %0;" ::"n"(kMmaConsumers) : "memory");
             }
             // Q as the A operand: rows 0-3 are the four heads (lanes 0-15), rows 4-15 zero.  Per 16-wide
             // k step: qa[t][0] = dims 16 t + 2 quad, +1; qa[t][1] = the same + 8.
@@ -764,7 +780,7 @@ attend_rows_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             for (int n = 0; n < 16; n++) oacc[n][0] = oacc[n][1] = 0.0f;
 
             const uint32_t blk_lo = r.lo / 32, blk_hi = (r.hi + 31) / 32;
-            for (uint32_t blk = blk_lo + cw; blk < blk_hi; blk += kWarps) {
+            for (uint32_t blk = blk_lo + cw; blk < blk_hi; blk += kMmaWarps) {
                 if (ok) ok = mbar_wait_or_abort(&full[s], used & 1, abort_flag);
                 used++;
                 if (ok) {
@@ -863,15 +879,15 @@ attend_rows_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                     sm_ml[cw][hrow][1] = l_row;
                 }
             }
-            asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory");
-            for (uint32_t i = ct; i < G * WIDTH; i += kThreads) {
+            asm volatile("bar.sync 1, %0;" ::"n"(kMmaConsumers) : "memory");
+            for (uint32_t i = ct; i < G * WIDTH; i += kMmaConsumers) {
                 const uint32_t g = i / WIDTH, d = i % WIDTH;
                 float mm = -INFINITY;
 #pragma unroll
-                for (int w = 0; w < kWarps; w++) mm = fmaxf(mm, sm_ml[w][g][0]);
+                for (int w = 0; w < kMmaWarps; w++) mm = fmaxf(mm, sm_ml[w][g][0]);
                 float ll = 0.0f, oo = 0.0f;
 #pragma unroll
-                for (int w = 0; w < kWarps; w++) {
+                for (int w = 0; w < kMmaWarps; w++) {
                     float mw = sm_ml[w][g][0];
                     float f = mw == -INFINITY ? 0.0f : __expf(mw - mm);
                     ll += sm_ml[w][g][1] * f;
@@ -888,7 +904,7 @@ attend_rows_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                     }
                 }
             }
-            asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory");
+            asm volatile("bar.sync 1, %0;" ::"n"(kMmaConsumers) : "memory");
         }
     }
     __syncthreads();
@@ -941,7 +957,7 @@ cudaError_t launch_rows(const RowsParams &p, dim3 grid, cudaStream_t stream) {
 
 __device__ int g_rows_status = 0;
 
-// TS_ROWS_MMA=0 keeps groups of four on the scalar kernel (for A/B timing).
+// TS_ROWS_MMA=0 keeps the scalar TMA-fed kernel (for A/B timing).
 bool rows_mma_enabled() {
     static const bool off = [] {
         const char *v = getenv("TS_ROWS_MMA");
@@ -970,18 +986,19 @@ int launch_rows_tma(const CUtensorMap &map_k, const CUtensorMap &map_v, const Ro
     return TS_OK;
 }
 
+template <int G, int CW>
 int launch_rows_mma(const CUtensorMap &map_k, const CUtensorMap &map_v, const RowsParams &p, uint32_t items,
                     cudaStream_t stream) {
-    using Sh = TmaShared<4>;
+    using Sh = MmaShared<G, CW>;
     static bool configured = false;
     if (!configured) {
-        TS_CUDA(cudaFuncSetAttribute(attend_rows_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Sh::bytes));
+        TS_CUDA(cudaFuncSetAttribute(attend_rows_mma_kernel<G, CW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Sh::bytes));
         configured = true;
     }
     int *status = nullptr;
     TS_CUDA(cudaGetSymbolAddress((void **)&status, g_rows_status));
-    const uint32_t grid = min(items, (uint32_t)sm_count() * 2);
-    cudaError_t e = launch(attend_rows_mma_kernel, dim3(grid), dim3(kTmaThreads), Sh::bytes, stream, pdl_enabled(), map_k,
+    const uint32_t grid = min(items, (uint32_t)sm_count() * (CW == 3 ? 4 : 2));
+    cudaError_t e = launch(attend_rows_mma_kernel<G, CW>, dim3(grid), dim3(32 + CW * 32), Sh::bytes, stream, pdl_enabled(), map_k,
                            map_v, p, items, status);
     if (e != cudaSuccess)
         return fail(TS_ERR_CUDA, "launch of attend_rows (mma) failed: %s (%d) %s", cudaGetErrorName(e), (int)e,
@@ -1061,7 +1078,11 @@ int attend_rows(const void *q, const void *k, const void *v, void *out, const ui
     if (tma) {
         CUtensorMap map_k, map_v;
         const uint64_t cols = (uint64_t)kv_heads * width;
-        const bool tensor = s.g == 4 && rows_mma_enabled();  // four heads per key: the warp-MMA variant
+        // The warp-MMA variants: four heads per key always (the scalar kernel is instruction-bound there); one or
+        // two heads per key for short items (a chunk of at most 256 keys), where what counts is that every item
+        // of the launch is resident at once.  Long items of one or two heads stay on the scalar kernel, which
+        // keeps more tiles in flight per SM and reaches 0.98 of the copy rate.
+        const bool tensor = rows_mma_enabled() && (s.g == 4 || s.chunk <= 256);
         int rc = tensor ? make_tensor_map_2d(&map_k, k, kept_rows, cols, cols, 32, 64)
                         : make_tensor_map_2d_plain(&map_k, k, kept_rows, cols, cols, 32, 128);
         if (rc != TS_OK) return rc;
@@ -1069,7 +1090,9 @@ int attend_rows(const void *q, const void *k, const void *v, void *out, const ui
                     : make_tensor_map_2d_plain(&map_v, v, kept_rows, cols, cols, 32, 128);
         if (rc != TS_OK) return rc;
         const uint32_t items = rows * (heads / s.g) * s.chunks;
-        rc = tensor     ? launch_rows_mma(map_k, map_v, p, items, stream)
+        rc = tensor     ? (s.g == 4   ? launch_rows_mma<4, 4>(map_k, map_v, p, items, stream)
+                           : s.g == 2 ? launch_rows_mma<2, 3>(map_k, map_v, p, items, stream)
+                                      : launch_rows_mma<1, 3>(map_k, map_v, p, items, stream))
              : s.g == 4 ? launch_rows_tma<4>(map_k, map_v, p, items, stream)
              : s.g == 2 ? launch_rows_tma<2>(map_k, map_v, p, items, stream)
                         : launch_rows_tma<1>(map_k, map_v, p, items, stream);
