@@ -48,6 +48,7 @@ struct StreamParams {
     uint32_t kb_max;         // most k blocks any split holds (sizes the resident x slice)
     uint32_t gated;
     uint32_t use_recv;       // reduce / pair through the receive buffer (S > 1 or gated)
+    uint32_t use_bulk;       // S > 1: partials go out as one bulk copy per peer instead of 16-byte stores
     uint32_t chunk_shift;    // log2(BN / S): batch columns each block owns after the reduce
     int epilogue, out_dtype;
     float scale;
@@ -68,15 +69,19 @@ struct StreamParams {
 };
 
 struct StreamSmem {
-    uint32_t a_off, b_off, recv_off, bar_off, total;
+    uint32_t a_off, b_off, recv_off, send_off, bar_off, total;
 };
 
-__host__ __device__ inline StreamSmem stream_smem(uint32_t bn, uint32_t stages, uint32_t kb_max, bool recv) {
+// recv: the block reduces / pairs through a receive buffer; send: it also stages its outgoing partials in a
+// buffer of the same shape, for bulk copies into the peers' receive buffers.
+__host__ __device__ inline StreamSmem stream_smem(uint32_t bn, uint32_t stages, uint32_t kb_max, bool recv, bool send) {
     StreamSmem l;
     l.a_off = 0;
     l.b_off = stages * kABytes;
     l.recv_off = l.b_off + kb_max * bn * kBlockK * 2;
-    l.bar_off = l.recv_off + (recv ? kRows * (bn + 32) * 4 : 0);  // rows padded by 4 floats per sender
+    const uint32_t buf = kRows * (bn + 32) * 4;  // rows padded by 4 floats per sender
+    l.send_off = l.recv_off + (recv ? buf : 0);
+    l.bar_off = l.send_off + (send ? buf : 0);
     // barriers (256), per-warp partial sums of squares (4 x 128 floats) and 128 row factors, slack for the
     // 1024-byte alignment
     l.total = l.bar_off + 256 + 2560 + 1024;
@@ -144,10 +149,11 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const StreamSmem L = stream_smem(BN, p.stages, p.kb_max, p.use_recv != 0);
+    const StreamSmem L = stream_smem(BN, p.stages, p.kb_max, p.use_recv != 0, p.use_bulk != 0);
     unsigned char *smem_a = smem + L.a_off;
     unsigned char *smem_b = smem + L.b_off;
     float *recv = reinterpret_cast<float *>(smem + L.recv_off);  // [S][128][BN / S]
+    float *send = reinterpret_cast<float *>(smem + L.send_off);  // same shape, indexed by destination
     uint64_t *full = reinterpret_cast<uint64_t *>(smem + L.bar_off);  // [8]
     uint64_t *empty = full + 8;                                       // [8]
     uint64_t *acc_full = empty + 8;                                   // [2]
@@ -157,7 +163,8 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
     uint64_t *recv_free = recv_full + 1;
     uint64_t *red_full = recv_free + 1;
     uint64_t *inv_full = red_full + 1;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(inv_full + 1);
+    uint64_t *send_full = inv_full + 1;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(send_full + 1);
     volatile uint32_t *abort_flag = tmem_slot + 1;
     float *red = reinterpret_cast<float *>(smem + L.bar_off + 256);  // [4][128]
     float *inv_s = red + 512;                                       // [128] 1/rms of the batch rows
@@ -200,6 +207,7 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
         mbar_init(b_full, 1);
         mbar_init(red_full, kEpiWarps);
         mbar_init(inv_full, kEpiWarps);
+        mbar_init(send_full, kEpiWarps);
         // S > 1: one local arrival announces the bytes and the senders' asynchronous stores complete
         // them; S == 1: plain stores, one arrival per warp.
         mbar_init(recv_full, S > 1 ? 1 : kEpiWarps);
@@ -348,19 +356,47 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                     cluster_wait();
                     waited1 = true;
                 }
-                // This block will receive S x 128 rows x chunk columns of f32 for the tile.
-                if (warp == 2 && lane == 0) mbar_expect_tx(recv_full, S * kRows * chunk * 4);
-                // Send: columns [col0, col0 + CW) go to the blocks that own them as asynchronous
-                // 16-byte stores that credit the owner's barrier; the sender does not wait for them.
+                if (p.use_bulk) {
+                    // Stage the partial in this block's send buffer, laid out like a peer's receive buffer
+                    // (by destination, row, column), then one thread sends each destination its 128 x chunk
+                    // block as a single bulk copy that credits the destination's barrier.  Eight 16-byte
+                    // remote stores per thread took 2.3 us of a 7.7 us kernel; this takes a fraction.
 #pragma unroll
-                for (uint32_t c = 0; c < CW; c += 4) {
-                    const uint32_t col = col0 + c;
-                    const uint32_t dest = col >> shift, within = col & (chunk - 1);
-                    const uint32_t local = recv_base + ((rank * kRows + row) * rs + within) * 4;
-                    st_async_f32x4(map_to_rank(local, dest), map_to_rank(bar_local, dest), v[c], v[c + 1], v[c + 2],
-                                   v[c + 3]);
+                    for (uint32_t c = 0; c < CW; c += 4) {
+                        const uint32_t col = col0 + c;
+                        const uint32_t dest = col >> shift, within = col & (chunk - 1);
+                        *reinterpret_cast<float4 *>(send + (dest * kRows + row) * rs + within) =
+                            make_float4(v[c], v[c + 1], v[c + 2], v[c + 3]);
+                    }
+                    fence_async_shared();  // the copy engine reads what these threads wrote
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(send_full);
+                    if (warp == 2 && lane == 0) {
+                        const uint32_t block_bytes = kRows * rs * 4;
+                        mbar_expect_tx(recv_full, S * block_bytes);
+                        if (wait_bounded(send_full, acc_it & 1, abort_flag)) {
+                            for (uint32_t d = 0; d < S; d++)
+                                bulk_copy_to_peer(map_to_rank(recv_base + rank * block_bytes, d),
+                                                  smem_addr(send) + d * block_bytes, block_bytes, map_to_rank(bar_local, d));
+                        }
+                    }
+                } else {
+                    // This block will receive S x 128 rows x chunk columns of f32 for the tile.
+                    if (warp == 2 && lane == 0) mbar_expect_tx(recv_full, S * kRows * chunk * 4);
+                    // Send: columns [col0, col0 + CW) go to the blocks that own them as asynchronous
+                    // 16-byte stores that credit the owner's barrier; the sender does not wait for them.
+#pragma unroll
+                    for (uint32_t c = 0; c < CW; c += 4) {
+                        const uint32_t col = col0 + c;
+                        const uint32_t dest = col >> shift, within = col & (chunk - 1);
+                        const uint32_t local = recv_base + ((rank * kRows + row) * rs + within) * 4;
+                        st_async_f32x4(map_to_rank(local, dest), map_to_rank(bar_local, dest), v[c], v[c + 1], v[c + 2],
+                                       v[c + 3]);
+                    }
                 }
-                if (acc_it + 1 >= my_tiles && !arrived2) {  // nothing more goes to the peers from this thread
+                // (With bulk copies the source buffer is still being read: that thread arrives after its own
+                // receive, below, by when every peer has its data.)
+                if (acc_it + 1 >= my_tiles && !arrived2 && !p.use_bulk) {  // nothing more goes to the peers from this thread
                     cluster_arrive();
                     arrived2 = true;
                 }
@@ -376,6 +412,10 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
             if (warp == 2 && lane == 0) STAMP(7);
             ok = wait_bounded(recv_full, acc_it & 1, abort_flag);
             if (!ok) break;
+            if (S > 1 && p.use_bulk && acc_it + 1 >= my_tiles && !arrived2) {
+                cluster_arrive();
+                arrived2 = true;
+            }
             if (warp == 2 && lane == 0) STAMP(8);
 
             // Reduce the S partials of this block's columns in rank order, finish, store.  Thread
@@ -455,7 +495,7 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
 
 struct StreamPlan {
     uint32_t bn, splits, tiles, stages, kb_total, kb_max, blocks;
-    bool gated, use_recv;
+    bool gated, use_recv, use_bulk;
     StreamSmem layout;
 };
 
@@ -470,9 +510,9 @@ bool plan_stream(uint32_t m, uint32_t n, uint32_t k, int epilogue, StreamPlan *o
     s.kb_total = k / kBlockK;
     s.tiles = s.gated ? (n / 2) / 64 : ceil_div(n, kRows);
     const uint32_t sms = (uint32_t)sm_count();
-    auto layout = [&](uint32_t splits, uint32_t stages) {
+    auto layout = [&](uint32_t splits, uint32_t stages, bool send = false) {
         const uint32_t kb_max = ceil_div(s.kb_total, splits);
-        return stream_smem(s.bn, stages, kb_max, splits > 1 || s.gated);
+        return stream_smem(s.bn, stages, kb_max, splits > 1 || s.gated, send);
     };
     // The largest power-of-two split that still fits one wave; more if the resident x slice needs it.
     uint32_t splits = 1;
@@ -483,10 +523,14 @@ bool plan_stream(uint32_t m, uint32_t n, uint32_t k, int epilogue, StreamPlan *o
     s.splits = splits;
     s.kb_max = ceil_div(s.kb_total, splits);
     s.use_recv = splits > 1 || s.gated;
+    // Bulk copies for the cluster reduce need a send buffer as large as the receive buffer: taken when at
+    // least three weight stages (or all the block's k blocks) still fit beside it.
+    const uint32_t want = std::min<uint32_t>(3, s.kb_max);
+    s.use_bulk = splits > 1 && layout(splits, want, true).total <= kSmemBudget;
     uint32_t stages = 8;
-    while (stages > 2 && layout(splits, stages).total > kSmemBudget) stages--;
+    while (stages > 2 && layout(splits, stages, s.use_bulk).total > kSmemBudget) stages--;
     s.stages = stages;
-    s.layout = layout(splits, stages);
+    s.layout = layout(splits, stages, s.use_bulk);
     s.blocks = splits > 1 ? s.tiles : std::min(s.tiles, sms);
     *out = s;
     return true;
@@ -591,6 +635,7 @@ int linear_stream(const void *x, const void *w, const void *a0, void *out, uint3
     p.kb_max = s.kb_max;
     p.gated = s.gated;
     p.use_recv = s.use_recv;
+    p.use_bulk = s.use_bulk;
     {
         uint32_t chunk = s.bn / s.splits, sh = 0;
         while ((1u << sh) < chunk) sh++;

@@ -137,6 +137,18 @@ __device__ __forceinline__ void st_async_f32x4(uint32_t addr, uint32_t bar_addr,
                  : "memory");
 }
 
+// One thread.  Copies `bytes` (a multiple of 16; both addresses 16-byte aligned) from this block's shared
+// memory to shared memory of a block of the cluster (`dst_cluster_addr`, from map_to_rank) and credits the bytes
+// to the mbarrier `bar_cluster_addr` of that block.  The source must stay untouched until the destination's
+// barrier has completed.
+__device__ __forceinline__ void bulk_copy_to_peer(uint32_t dst_cluster_addr, uint32_t src_addr, uint32_t bytes,
+                                                  uint32_t bar_cluster_addr) {
+    asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     dst_cluster_addr),
+                 "r"(src_addr), "r"(bytes), "r"(bar_cluster_addr)
+                 : "memory");
+}
+
 // One arrival on an mbarrier that may live in another block of the cluster; orders this thread's
 // earlier distributed-shared-memory writes before it.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
