@@ -1,0 +1,97 @@
+"""The reference's kernels by name, with arguments in the reference's order.
+
+tessera's lowering rules end in `Launch { args, shape }` records whose `args` follow the kernel's
+parameter list (engine/plan/lower/src/rule.rs:241-261; the lists below cite each kernel).  A host that
+walks such records can hand them to `launch(name, args, ...)` here unchanged: buffers as device tensors,
+scalars as Python numbers, in the reference's order.  What the reference keeps outside the argument
+list (element types, the kept layout's trailing scalars, epilogue stages fused by the lowering) comes in
+as keywords.  Unknown names and wrong argument counts raise `KeyError` / `TypeError` before anything is
+launched, as `Error::Launch` does in the reference.
+
+    launch("lanes", [x, w, out, n, k])                      # engine/rules/linear/src/lanes.rs:21-32
+    launch("attend_rows", [q, k, v, out, slots, positions, rows, keys, heads, kv_heads, width, back],
+           kept=ops.Kept("paged", pages, table), scale=d ** -0.5)
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable
+
+
+@dataclass(frozen=True)
+class Rule:
+    name: str
+    params: tuple[str, ...]   # the reference kernel's parameters, in order
+    cites: str                # where the reference declares them
+    run: Callable             # (args by name, keywords) -> output tensor
+
+
+def _linear(a, kw):
+    from . import ops
+    x, w, out = a["x"], a["w"], a["out"]
+    n, k = int(a["n"]), int(a["k"])
+    if w.shape != (n, k) or x.shape[-1] != k:
+        raise TypeError(f"linear: w is {tuple(w.shape)}, x is {tuple(x.shape)}, the launch says n={n} k={k}")
+    return ops.linear(x.reshape(-1, k), w, kw.get("a0"), epilogue=kw.get("epilogue", "none"), scale=kw.get("scale", 1.0),
+                      out_dtype=out.dtype, path=kw.get("path", "auto"), out=out)
+
+
+def _attend_rows(a, kw):
+    from . import ops
+    q = a["q"]
+    rows, heads, kv_heads, width = int(a["rows"]), int(a["heads"]), int(a["kv_heads"]), int(a["width"])
+    if q.numel() != rows * heads * width:
+        raise TypeError(f"attend_rows: q holds {q.numel()} elements, the launch says {rows} x {heads} x {width}")
+    if "kept" not in kw or "scale" not in kw:
+        raise TypeError("attend_rows: the kept layout and the score scale come as keywords")
+    k_rows = a["k"].reshape(-1, kv_heads, width)
+    v_rows = a["v"].reshape(-1, kv_heads, width)
+    return ops.attend_rows(q.reshape(rows, heads, width), k_rows, v_rows, a["slots"], a["positions"], kw["kept"],
+                           int(a["keys"]), scale=float(kw["scale"]), back=int(a["back"]),
+                           out=a["out"].reshape(rows, heads, width))
+
+
+def _scatter(a, kw):
+    from . import ops
+    if "kept" not in kw:
+        raise TypeError("scatter: the kept layout comes as a keyword")
+    rows, width = int(a["rows"]), int(a["width"])
+    return ops.scatter(a["x"].reshape(rows, width), a["slots"], a["positions"], a["out"].reshape(-1, width), kw["kept"])
+
+
+def _top_k(a, kw):
+    from . import ops
+    rows, width, k = int(a["rows"]), int(a["width"]), int(a["k"])
+    ids = ops.top_k(a["x"].reshape(rows, width), k)
+    a["out"].reshape(rows, k).copy_(ids.reshape(rows, k))
+    return a["out"]
+
+
+def _lane_norm(a, kw):
+    from . import ops
+    rows, width = int(a["rows"]), int(a["width"])
+    return ops.rms_norm(a["x"].reshape(rows, width), a["w"], float(a["eps"]), out_dtype=a["out"].dtype,
+                        out=a["out"].reshape(rows, width))
+
+
+_LINEAR_PARAMS = ("x", "w", "out", "n", "k")
+RULES = {r.name: r for r in (
+    # The linear family shares one parameter list; m rides in the launch shape (lanes.rs:21-32, thin.rs, tiled.rs:295-304).
+    Rule("lanes", _LINEAR_PARAMS, "engine/rules/linear/src/lanes.rs:21-32", _linear),
+    Rule("thin", _LINEAR_PARAMS, "engine/rules/linear/src/thin.rs", _linear),
+    Rule("tiled", _LINEAR_PARAMS, "engine/rules/linear/src/tiled.rs:295-304", _linear),
+    Rule("attend_rows", ("q", "k", "v", "out", "slots", "positions", "rows", "keys", "heads", "kv_heads", "width", "back"),
+         "engine/rules/attention/src/attend.rs:126-139", _attend_rows),
+    Rule("scatter", ("x", "slots", "positions", "out", "rows", "width"), "engine/plan/lower/src/kernels/scatter.rs:12-19", _scatter),
+    Rule("top_k", ("x", "out", "rows", "width", "k"), "engine/rules/kernels/src/argmax.rs:39", _top_k),
+    Rule("lane_norm", ("x", "w", "out", "rows", "width", "eps"), "engine/rules/kernels/src/lane_norm.rs:10-17", _lane_norm),
+)}
+
+
+def launch(name: str, args, **keywords):
+    """Runs the kernel `name` on `args` (the reference's order).  Returns the tensor written."""
+    rule = RULES[name]
+    args = list(args)
+    if len(args) != len(rule.params):
+        raise TypeError(f"{name} takes {len(rule.params)} arguments ({', '.join(rule.params)}), got {len(args)}")
+    return rule.run(dict(zip(rule.params, args)), keywords)

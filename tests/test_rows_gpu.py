@@ -101,3 +101,42 @@ def test_take_softmax():
     want = O.softmax(O.take(x, ids))
     got = ops.take_softmax(torch.from_numpy(x).cuda(), dev_u32(ids))
     assert rel_error(widen(got), want) <= 1e-5
+
+
+def test_launch_by_name_with_the_reference_argument_order():
+    from tessera_b200 import ops, rules
+    rng = np.random.default_rng(8)
+    m, n, k = 24, 512, 256
+    x = from_bits(normal_bf16(rng, (m, k)))
+    w = from_bits(normal_bf16(rng, (n, k), 0.02))
+    out = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    rules.launch("lanes", [x, w, out, n, k])
+    assert torch.equal(out, ops.linear(x, w))
+    with pytest.raises(TypeError):
+        rules.launch("tiled", [x, w, out, n + 1, k])
+
+    xs = torch.randn(5, 300, device="cuda")
+    ids = torch.empty((5, 3), dtype=torch.int32, device="cuda")
+    rules.launch("top_k", [xs, ids, 5, 300, 3])
+    assert torch.equal(ids, ops.top_k(xs, 3))
+
+    g = torch.randn(300, device="cuda")
+    normed = torch.empty((5, 300), dtype=torch.float32, device="cuda")
+    rules.launch("lane_norm", [xs, g, normed, 5, 300, 1e-6])
+    assert torch.equal(normed, ops.rms_norm(xs, g, 1e-6, out_dtype=torch.float32))
+
+    # attend_rows over a dense layout, then scatter a new row into it by name
+    slots, context, heads, kv_heads, width = 3, 40, 4, 2, 128
+    kept = ops.Kept("dense", context, None, slots * context)
+    kr = from_bits(normal_bf16(rng, (slots * context, kv_heads * width)))
+    vr = from_bits(normal_bf16(rng, (slots * context, kv_heads * width)))
+    q = from_bits(normal_bf16(rng, (2, heads * width)))
+    sl, ps = dev_u32([2, 0]), dev_u32([17, 39])
+    o = torch.empty_like(q)
+    rules.launch("attend_rows", [q, kr, vr, o, sl, ps, 2, context, heads, kv_heads, width, 0xFFFFFFFF], kept=kept, scale=0.1)
+    want = ops.attend_rows(q.reshape(2, heads, width), kr.reshape(-1, kv_heads, width), vr.reshape(-1, kv_heads, width), sl, ps,
+                           kept, context, scale=0.1)
+    assert torch.equal(o.reshape(2, heads, width), want)
+    new = from_bits(normal_bf16(rng, (2, kv_heads * width)))
+    rules.launch("scatter", [new, sl, ps, kr, 2, kv_heads * width], kept=kept)
+    assert torch.equal(kr[2 * context + 17], new[0]) and torch.equal(kr[39], new[1])
