@@ -43,8 +43,11 @@ FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used only when ME
 # committed ncu captures (profiles/decode_kernels_sections.md names the commands).  The captures ran on
 # small cases of the same kernels; traffic grows in proportion to the rows, keys and weights a launch
 # visits, so a launch's traffic is this ratio times its algorithmic bytes.  None: no capture.
-NCU_TRAFFIC_RATIO = {"attend_rows": 50.670 / 50.856, "linear_unembed": 340.64 / 350.19,
-                     "linear_qkv": 8.585 / 8.520}
+NCU_TRAFFIC_RATIO = {"attend_rows": 50.816 / 50.856, "linear_unembed": 340.02 / 350.19,
+                     # one capture (the q,k,v shape) stands for the four streamed linears of a layer: same kernel,
+                     # traffic = the weights once + x; the output stays in L2
+                     "linear_qkv": 8.592 / 9.044, "linear_o": 8.592 / 9.044, "linear_gate_up": 8.592 / 9.044,
+                     "linear_down": 8.592 / 9.044}
 
 
 def parse_args():
