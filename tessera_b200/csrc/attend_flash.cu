@@ -74,10 +74,52 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
+// What a work item (a 128-query tile of one sequence and head) covers; every role derives it from the item's
+// index in the same way.
+struct FlashItem {
+    uint32_t head, kvh, q_begin, k_begin, k_len, past, t0, rows_here, jb0, nb;
+};
+
+template <uint32_t BK>
+__device__ __forceinline__ FlashItem flash_item(const FlashParams &p, uint32_t item) {
+    FlashItem it;
+    const uint32_t per = p.heads * p.seqs;
+    const uint32_t tile = p.q_tiles - 1 - item / per, rem = item % per;  // later tiles (more keys under a causal mask) first
+    const uint32_t seq = rem / p.heads;
+    it.head = rem % p.heads;
+    it.kvh = it.head / (p.heads / p.kv_heads);
+    uint32_t q_len;
+    if (p.cu_seqlens) {
+        it.q_begin = it.k_begin = p.cu_seqlens[seq];
+        q_len = it.k_len = p.cu_seqlens[seq + 1] - it.q_begin;
+    } else {
+        it.q_begin = seq * p.queries;
+        q_len = p.queries;
+        it.k_begin = seq * p.keys;
+        it.k_len = p.keys;
+    }
+    it.t0 = tile * kTile;
+    it.past = it.k_len > q_len ? it.k_len - q_len : 0;
+    it.rows_here = it.t0 < q_len ? min(kTile, q_len - it.t0) : 0;
+    it.jb0 = it.nb = 0;
+    if (it.rows_here) {
+        // Keys any query of the tile can see: [lo, hi).
+        const uint32_t pos_first = it.past + it.t0, pos_last = pos_first + it.rows_here - 1;
+        const uint32_t lo = pos_first > p.back ? pos_first - p.back : 0;
+        const uint32_t hi = min(it.k_len, sat_add(sat_add(pos_last, p.ahead), 1));
+        it.jb0 = lo / BK;
+        it.nb = hi > lo ? (hi + BK - 1) / BK - it.jb0 : 0;
+    }
+    return it;
+}
+
+// Blocks are persistent over items (item = blockIdx.x, + gridDim.x, ...): the block-level set-up (barriers,
+// TMEM) is paid once, which matters for batches of short sequences where an item is a handful of key blocks.
+// Barrier phases run on across items.
 template <uint32_t D>
 __global__ void __launch_bounds__(kThreads, 1)
 attend_flash_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                    const __grid_constant__ CUtensorMap map_v, const FlashParams p) {
+                    const __grid_constant__ CUtensorMap map_v, const FlashParams p, const uint32_t items) {
     using Sh = FlashShape<D>;
     constexpr uint32_t BK = Sh::BK;
     extern __shared__ unsigned char smem_raw[];
@@ -95,35 +137,13 @@ attend_flash_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     uint64_t *s_full = bars + 9;      // [2]
     uint64_t *p_full = bars + 11;     // [2]
     uint64_t *pv_done = bars + 13;    // [2]
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 15);
+    uint64_t *q_empty = bars + 15;    // [1]
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 16);
     volatile uint32_t *abort_flag = tmem_slot + 1;
-
-    // Heavier tiles (later queries see more keys under a causal mask) first.
-    const uint32_t tile = p.q_tiles - 1 - blockIdx.x, head = blockIdx.y, seq = blockIdx.z;
-    const uint32_t kvh = head / (p.heads / p.kv_heads);
-    uint32_t q_begin, q_len, k_begin, k_len;
-    if (p.cu_seqlens) {
-        q_begin = k_begin = p.cu_seqlens[seq];
-        q_len = k_len = p.cu_seqlens[seq + 1] - q_begin;
-    } else {
-        q_begin = seq * p.queries;
-        q_len = p.queries;
-        k_begin = seq * p.keys;
-        k_len = p.keys;
-    }
-    const uint32_t t0 = tile * kTile;
-    if (t0 >= q_len) return;  // whole block: nothing to do
-    const uint32_t past = k_len > q_len ? k_len - q_len : 0;
-    const uint32_t rows_here = min(kTile, q_len - t0);
-    // Keys any query of the tile can see: [lo, hi).
-    const uint32_t pos_first = past + t0, pos_last = past + t0 + rows_here - 1;
-    const uint32_t lo = pos_first > p.back ? pos_first - p.back : 0;
-    const uint32_t hi = min(k_len, sat_add(sat_add(pos_last, p.ahead), 1));
-    const uint32_t jb0 = lo / BK;
-    const uint32_t nb = hi > lo ? (hi + BK - 1) / BK - jb0 : 0;
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
+        mbar_init(q_empty, 1);
         for (int s = 0; s < 2; s++) {
             mbar_init(&k_full[s], 1);
             mbar_init(&v_full[s], 1);
@@ -148,44 +168,54 @@ attend_flash_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        if (lane == 0 && nb > 0) {
+        if (lane == 0) {
             pdl_wait();
-            mbar_expect_tx(q_full, Sh::q_bytes);
-            for (uint32_t c = 0; c < Sh::chunks; c++)
-                tma_load_2d(smem_q + c * Sh::q_chunk, &map_q, q_full, (int32_t)(head * D + c * 64),
-                            (int32_t)(q_begin + t0));
             bool ok = true;
-            for (uint32_t j = 0; j < nb && ok; j++) {
-                const uint32_t s = j & 1, ph = (j >> 1) & 1;
-                const int32_t krow = (int32_t)(k_begin + (jb0 + j) * BK);
-                ok = mbar_wait_or_abort(&k_empty[s], ph ^ 1, abort_flag);
+            uint32_t jr = 0, n_item = 0;  // key blocks and items (with keys) so far
+            for (uint32_t item = blockIdx.x; item < items && ok; item += gridDim.x) {
+                const FlashItem it = flash_item<BK>(p, item);
+                if (it.nb == 0) continue;
+                // Q of the previous item is free once its MMAs are done.
+                if (n_item > 0) ok = mbar_wait_or_abort(q_empty, (n_item - 1) & 1, abort_flag);
                 if (!ok) break;
-                mbar_expect_tx(&k_full[s], Sh::kv_bytes);
+                n_item++;
+                mbar_expect_tx(q_full, Sh::q_bytes);
                 for (uint32_t c = 0; c < Sh::chunks; c++)
-                    tma_load_2d(smem_k + s * Sh::kv_bytes + c * Sh::kv_chunk, &map_k, &k_full[s],
-                                (int32_t)(kvh * D + c * 64), krow);
-                ok = mbar_wait_or_abort(&v_empty[s], ph ^ 1, abort_flag);
-                if (!ok) break;
-                mbar_expect_tx(&v_full[s], Sh::kv_bytes);
-                for (uint32_t c = 0; c < Sh::chunks; c++)
-                    tma_load_2d(smem_v + s * Sh::kv_bytes + c * Sh::kv_chunk, &map_v, &v_full[s],
-                                (int32_t)(kvh * D + c * 64), krow);
+                    tma_load_2d(smem_q + c * Sh::q_chunk, &map_q, q_full, (int32_t)(it.head * D + c * 64),
+                                (int32_t)(it.q_begin + it.t0));
+                for (uint32_t j = 0; j < it.nb && ok; j++, jr++) {
+                    const uint32_t s = jr & 1, ph = (jr >> 1) & 1;
+                    const int32_t krow = (int32_t)(it.k_begin + (it.jb0 + j) * BK);
+                    ok = mbar_wait_or_abort(&k_empty[s], ph ^ 1, abort_flag);
+                    if (!ok) break;
+                    mbar_expect_tx(&k_full[s], Sh::kv_bytes);
+                    for (uint32_t c = 0; c < Sh::chunks; c++)
+                        tma_load_2d(smem_k + s * Sh::kv_bytes + c * Sh::kv_chunk, &map_k, &k_full[s],
+                                    (int32_t)(it.kvh * D + c * 64), krow);
+                    ok = mbar_wait_or_abort(&v_empty[s], ph ^ 1, abort_flag);
+                    if (!ok) break;
+                    mbar_expect_tx(&v_full[s], Sh::kv_bytes);
+                    for (uint32_t c = 0; c < Sh::chunks; c++)
+                        tma_load_2d(smem_v + s * Sh::kv_bytes + c * Sh::kv_chunk, &map_v, &v_full[s],
+                                    (int32_t)(it.kvh * D + c * 64), krow);
+                }
             }
             pdl_launch_dependents();
             // Copies in flight land before the MMAs that release their stages; wait for those releases.
-            for (uint32_t back = 0; back < 2 && back < nb && ok; back++) {
-                const uint32_t j = nb - 1 - back;
+            for (uint32_t back = 0; back < 2 && back < jr && ok; back++) {
+                const uint32_t j = jr - 1 - back;
                 ok = mbar_wait_or_abort(&k_empty[j & 1], (j >> 1) & 1, abort_flag) &&
                      mbar_wait_or_abort(&v_empty[j & 1], (j >> 1) & 1, abort_flag);
             }
         }
     } else if (warp == 1) {
-        if (lane == 0 && nb > 0) {
+        if (lane == 0) {
             const uint32_t idesc_qk = umma_idesc_bf16(kTile, BK, false, false);
             const uint32_t idesc_pv = umma_idesc_bf16(kTile, D, false, true);  // V is MN-major
-            bool ok = mbar_wait_or_abort(q_full, 0, abort_flag);
-            auto issue_qk = [&](uint32_t j) -> bool {
-                const uint32_t s = j & 1, ph = (j >> 1) & 1;
+            bool ok = true;
+            uint32_t jr = 0, n_item = 0;
+            auto issue_qk = [&](uint32_t r) -> bool {  // r: running index of the key block
+                const uint32_t s = r & 1, ph = (r >> 1) & 1;
                 if (!mbar_wait_or_abort(&k_full[s], ph, abort_flag)) return false;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + Sh::s_col + s * BK;
@@ -201,28 +231,35 @@ attend_flash_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 umma_commit(&s_full[s]);
                 return true;
             };
-            if (ok) ok = issue_qk(0);
-            for (uint32_t j = 0; j < nb && ok; j++) {
-                const uint32_t s = j & 1, ph = (j >> 1) & 1;
-                if (j + 1 < nb) {
-                    ok = issue_qk(j + 1);
+            for (uint32_t item = blockIdx.x; item < items && ok; item += gridDim.x) {
+                const FlashItem it = flash_item<BK>(p, item);
+                if (it.nb == 0) continue;
+                ok = mbar_wait_or_abort(q_full, n_item & 1, abort_flag);
+                n_item++;
+                if (ok) ok = issue_qk(jr);
+                for (uint32_t j = 0; j < it.nb && ok; j++, jr++) {
+                    const uint32_t s = jr & 1, ph = (jr >> 1) & 1;
+                    if (j + 1 < it.nb) {
+                        ok = issue_qk(jr + 1);
+                        if (!ok) break;
+                    }
+                    ok = mbar_wait_or_abort(&p_full[s], ph, abort_flag) && mbar_wait_or_abort(&v_full[s], ph, abort_flag);
                     if (!ok) break;
-                }
-                ok = mbar_wait_or_abort(&p_full[s], ph, abort_flag) && mbar_wait_or_abort(&v_full[s], ph, abort_flag);
-                if (!ok) break;
-                tc_fence_after_sync();
-                const uint32_t p_tmem = tmem_base + Sh::s_col + s * BK;  // bf16 pairs: 16 keys = 8 columns
-                const uint32_t o_tmem = tmem_base + Sh::o_col;
-                const uint32_t v_addr = smem_addr(smem_v + s * Sh::kv_bytes);
+                    tc_fence_after_sync();
+                    const uint32_t p_tmem = tmem_base + Sh::s_col + s * BK;  // bf16 pairs: 16 keys = 8 columns
+                    const uint32_t o_tmem = tmem_base + Sh::o_col;
+                    const uint32_t v_addr = smem_addr(smem_v + s * Sh::kv_bytes);
 #pragma unroll
-                for (uint32_t k16 = 0; k16 < BK / 16; k16++) {
-                    // 16 keys = 16 rows of 128 bytes further down the V tile; the 64-wide slices of the head
-                    // width are kv_chunk bytes apart, 8-row groups 1024 bytes apart.
-                    const uint64_t db = umma_desc_mn_sw128(v_addr + k16 * 2048, Sh::kv_chunk, 1024);
-                    umma_bf16_ts(o_tmem, p_tmem + k16 * 8, db, idesc_pv, (j | k16) != 0);
+                    for (uint32_t k16 = 0; k16 < BK / 16; k16++) {
+                        // 16 keys = 16 rows of 128 bytes further down the V tile; the 64-wide slices of the head
+                        // width are kv_chunk bytes apart, 8-row groups 1024 bytes apart.
+                        const uint64_t db = umma_desc_mn_sw128(v_addr + k16 * 2048, Sh::kv_chunk, 1024);
+                        umma_bf16_ts(o_tmem, p_tmem + k16 * 8, db, idesc_pv, (j | k16) != 0);
+                    }
+                    umma_commit(&v_empty[s]);
+                    umma_commit(&pv_done[s]);
                 }
-                umma_commit(&v_empty[s]);
-                umma_commit(&pv_done[s]);
+                if (ok) umma_commit(q_empty);
             }
         }
     } else {
@@ -230,16 +267,21 @@ attend_flash_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         const uint32_t q = warp & 3;
         const uint32_t row = q * 32 + lane;
         const uint32_t lane_base = (q * 32u) << 16;
-        const bool row_ok = row < rows_here;
-        const uint32_t pos = past + t0 + row;
+        const uint32_t o_tmem = tmem_base + lane_base + Sh::o_col;
+        bool ok = true;
+        uint32_t jr = 0;
+        for (uint32_t item = blockIdx.x; item < items && ok; item += gridDim.x) {
+        const FlashItem it = flash_item<BK>(p, item);
+        if (it.rows_here == 0) continue;
+        const uint32_t nb = it.nb, jb0 = it.jb0, k_len = it.k_len;
+        const bool row_ok = row < it.rows_here;
+        const uint32_t pos = it.past + it.t0 + row;
         const uint32_t from = pos > p.back ? pos - p.back : 0;
         const uint32_t to = min(k_len, sat_add(sat_add(pos, p.ahead), 1));
-        const uint32_t o_tmem = tmem_base + lane_base + Sh::o_col;
         float m_use = -INFINITY;  // the maximum the probabilities are taken against (may lag the true one)
         float l_run = 0.0f;
-        bool ok = true;
-        for (uint32_t j = 0; j < nb && ok; j++) {
-            const uint32_t s = j & 1, ph = (j >> 1) & 1;
+        for (uint32_t j = 0; j < nb && ok; j++, jr++) {
+            const uint32_t s = jr & 1, ph = (jr >> 1) & 1;
             ok = mbar_wait_or_abort(&s_full[s], ph, abort_flag);
             if (!ok) break;
             tc_fence_after_sync();
@@ -282,7 +324,7 @@ attend_flash_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             }
             if (__any_sync(0xFFFFFFFFu, need)) {
                 // O is complete up to the previous block once its MMAs are done.
-                const uint32_t sp = (j - 1) & 1, php = ((j - 1) >> 1) & 1;
+                const uint32_t sp = (jr - 1) & 1, php = ((jr - 1) >> 1) & 1;
                 ok = mbar_wait_or_abort(&pv_done[sp], php, abort_flag);
                 if (!ok) break;
                 tc_fence_after_sync();
@@ -320,13 +362,13 @@ attend_flash_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             if (lane == 0) mbar_arrive(&p_full[s]);
         }
         if (ok && nb > 0) {
-            const uint32_t sp = (nb - 1) & 1, php = ((nb - 1) >> 1) & 1;
+            const uint32_t sp = (jr - 1) & 1, php = ((jr - 1) >> 1) & 1;
             ok = mbar_wait_or_abort(&pv_done[sp], php, abort_flag);
             if (ok) tc_fence_after_sync();
         }
         if (ok) {
             const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-            uint16_t *dst = p.out + ((size_t)(q_begin + t0 + row) * p.heads + head) * D;
+            uint16_t *dst = p.out + ((size_t)(it.q_begin + it.t0 + row) * p.heads + it.head) * D;
 #pragma unroll
             for (uint32_t c0 = 0; c0 < D; c0 += 32) {
                 uint32_t r[32];
@@ -349,7 +391,9 @@ attend_flash_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     }
                 }
             }
+            tc_fence_before_sync();  // the reads of O above precede this thread's next arrival on p_full
         }
+        }  // items
     }
 
     tc_fence_before_sync();
@@ -802,8 +846,12 @@ static int launch_flash(const void *q, const void *k, const void *v, const Flash
         e = launch(attend_flash2_kernel, dim3((uint32_t)std::min<uint64_t>(items, (uint64_t)sm_count())), dim3(kThreads2),
                    Flash2Shape::total, stream, pdl_enabled(), map_q, map_k, map_v, p, (uint32_t)items);
     else
-        e = launch(attend_flash_kernel<D>, dim3(p.q_tiles, p.heads, p.seqs), dim3(kThreads), Sh::total, stream,
-                   pdl_enabled(), map_q, map_k, map_v, p);
+    {
+        const uint64_t tiles = (uint64_t)p.q_tiles * p.heads * p.seqs;
+        if (tiles >= 0x7FFFFFFFull) return fail(TS_ERR_BAD_INPUT, "attend: %llu query tiles are too many", (unsigned long long)tiles);
+        e = launch(attend_flash_kernel<D>, dim3((uint32_t)std::min<uint64_t>(tiles, (uint64_t)sm_count())), dim3(kThreads),
+                   Sh::total, stream, pdl_enabled(), map_q, map_k, map_v, p, (uint32_t)tiles);
+    }
     if (e != cudaSuccess)
         return fail(TS_ERR_CUDA, "launch of attend_flash failed: %s (%d) %s", cudaGetErrorName(e), (int)e,
                     cudaGetErrorString(e));
