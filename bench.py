@@ -10,8 +10,9 @@ stand-ins of the configuration's shapes, nothing is read from disk but MEASURED_
 
   value  tokens/s with every input resident in HBM: the device-resident decode loop (each row's next
          token is the id it just produced), K graph replays timed with CUDA events on the launch stream.
-  e2e    the same steps through ts_decoder_step with host buffers: tokens/slots/positions copied host to
-         device and the ids read back device to host inside the timed region, every step.
+  e2e    the same steps (the sequences restart from their prompts, so the positions and context lengths
+         are those of the resident loop) through ts_decoder_step with host buffers: tokens/slots/positions
+         copied host to device and the ids read back device to host inside the timed region, every step.
   roofline  the kernel with the largest share of a step, timed live with CUDA events per kernel
          (ts_decoder_profile) right after the timed region; algorithmic bytes / that duration.
   cpu_baseline  the reference's native CPU rules restated in C (oracle/cpu_rules.c), timed on this
@@ -249,6 +250,7 @@ def run_ours(args, rank, world, local_rank):
 
     sampler = ClockSampler(local_rank)
     first = dec.prefill(prompts)
+    dec.prepare(BATCH, stream)  # graphs of every context bucket exist before anything is timed
     pos = PROMPT
     cur = dec.step(first, slots, np.full(BATCH, pos, np.uint32), stream=stream)  # one row per slot on the device
     pos += 1
@@ -270,7 +272,12 @@ def run_ours(args, rank, world, local_rank):
     barrier()
     cur = dec.read_ids(BATCH, stream)
 
-    # ---- e2e: host buffers in and out every step ----
+    # ---- e2e: host buffers in and out every step, over the same positions as the resident loop ----
+    # (the sequences start again from their prompts, so that both loops see the same context lengths)
+    first = dec.prefill(prompts)
+    pos = PROMPT
+    cur = dec.step(first, slots, np.full(BATCH, pos, np.uint32), stream=stream)
+    pos += 1
     for i in range(W):
         cur = dec.step(cur, slots, np.full(BATCH, pos, np.uint32), stream=stream)
         pos += 1

@@ -77,6 +77,12 @@ int ts_decoder_read_logits(ts_decoder *dec, float *out, uint32_t n_out, void *st
 uint32_t ts_decoder_launches_per_step(ts_decoder *dec, uint32_t rows, uint32_t keys);
 uint64_t ts_decoder_graph_replays(ts_decoder *dec);
 
+/* Captures, without running them, the graphs of a decode step of `rows` rows (one per slot, one id out per row)
+ * for every context bucket up to the plan's context, with and without on-device feedback: a serving loop then
+ * never pays a capture in the middle of a generation.  The reference builds its plans before the first request
+ * in the same way (engine/engine/src/lib.rs:401-468).  No-op without graphs. */
+int ts_decoder_prepare(ts_decoder *dec, uint32_t rows, void *stream);
+
 /* Per-kernel device time, the reference's Run::profiling / take_profile (engine/plan/run/src/run.rs:
  * 165-177; stamps behind a gate kernel so host launch gaps are excluded, device.rs:144-200).
  * ts_decoder_profile runs `steps` further device-resident decode launches without graphs, with a CUDA

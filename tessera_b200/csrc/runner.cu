@@ -280,9 +280,10 @@ int enqueue(ts_decoder *d, uint32_t rows, uint32_t keys, uint32_t n_out, bool fe
 }
 
 // Replays the captured graph for these sizes, capturing it on first sight.
-int submit(ts_decoder *d, uint32_t rows, uint32_t keys, uint32_t n_out, bool feedback, bool distinct, cudaStream_t s) {
+int submit(ts_decoder *d, uint32_t rows, uint32_t keys, uint32_t n_out, bool feedback, bool distinct, cudaStream_t s,
+           bool capture_only = false) {
     set_pdl(d->c.pdl != 0);
-    if (!d->c.graphs) return enqueue(d, rows, keys, n_out, feedback, distinct, s, nullptr);
+    if (!d->c.graphs) return capture_only ? TS_OK : enqueue(d, rows, keys, n_out, feedback, distinct, s, nullptr);
     const uint64_t key = ((uint64_t)(distinct ? 1 : 0) << 63) | ((uint64_t)rows << 40) | ((uint64_t)keys << 16) |
                          ((uint64_t)(n_out & 0x7FFF) << 1) | (feedback ? 1 : 0);
     auto it = d->graphs.find(key);
@@ -302,6 +303,7 @@ int submit(ts_decoder *d, uint32_t rows, uint32_t keys, uint32_t n_out, bool fee
         if (e != cudaSuccess) return fail(TS_ERR_CUDA, "cudaGraphInstantiate failed: %s", cudaGetErrorString(e));
         it = d->graphs.emplace(key, exec).first;
     }
+    if (capture_only) return TS_OK;
     TS_CUDA(cudaGraphLaunch(it->second, s));
     d->replays++;
     return TS_OK;
@@ -648,6 +650,22 @@ uint32_t ts_decoder_launches_per_step(ts_decoder *d, uint32_t rows, uint32_t key
 }
 
 uint64_t ts_decoder_graph_replays(ts_decoder *d) { return d ? d->replays : 0; }
+
+int ts_decoder_prepare(ts_decoder *d, uint32_t rows, void *stream) {
+    TS_REQUIRE(d, "decoder: NULL");
+    TS_REQUIRE(rows >= 1 && rows <= d->c.max_rows && rows <= d->max_out, "decoder prepare: %u rows, the plan takes 1..%u",
+               rows, d->c.max_rows < d->max_out ? d->c.max_rows : d->max_out);
+    cudaStream_t s = stream_of(d, stream);
+    for (uint32_t keys = 128;; keys += 128) {
+        const uint32_t k = keys > d->c.context ? d->c.context : keys;
+        for (int feedback = 0; feedback < 2; feedback++) {
+            int rc = submit(d, rows, k, rows, feedback != 0, true, s, true);
+            if (rc != TS_OK) return rc;
+        }
+        if (k == d->c.context) break;
+    }
+    return TS_OK;
+}
 
 int ts_decoder_profile(ts_decoder *d, uint32_t steps, void *stream) {
     TS_REQUIRE(d, "decoder: NULL");

@@ -28,6 +28,7 @@ RUN_SIGNATURES = {
     "ts_decoder_read_logits": (i32, [vp, vp, u32, vp]),
     "ts_decoder_launches_per_step": (u32, [vp, u32, u32]),
     "ts_decoder_graph_replays": (C.c_uint64, [vp]),
+    "ts_decoder_prepare": (i32, [vp, u32, vp]),
     "ts_decoder_profile": (i32, [vp, u32, vp]),
     "ts_decoder_take_profile": (i32, [vp, C.c_char_p, sz]),
 }
@@ -106,6 +107,10 @@ class Decoder:
 
     def launches_per_step(self, rows: int, keys: int) -> int:
         return int(lib.ts_decoder_launches_per_step(self._h, rows, keys))
+
+    def prepare(self, rows: int, stream=None):
+        """Captures the decode-step graphs of `rows` rows for every context bucket ahead of time."""
+        check(lib.ts_decoder_prepare(self._h, rows, vp(stream or 0)))
 
     def graph_replays(self) -> int:
         return int(lib.ts_decoder_graph_replays(self._h))

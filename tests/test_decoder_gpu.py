@@ -95,6 +95,22 @@ def test_resident_loop_equals_host_loop(graphs, pdl):
     dec.close()
 
 
+def test_prepared_graphs_cover_every_context_bucket():
+    # ts_decoder_prepare captures all decode-step graphs up front; generation afterwards replays them and
+    # produces the same ids as a runner that captured lazily.
+    rng = np.random.default_rng(9)
+    cfg = SMALL
+    prompts = [rng.integers(0, cfg["vocab"], size=n).tolist() for n in (120, 100, 126)]
+    lazy = _device(cfg, 3, slots=3, context=320, max_rows=512, gains="near_one", page=64, graphs=True)
+    want = lazy.generate(prompts, 40)   # crosses the 128- and 256-key buckets
+    lazy.close()
+    dec = _device(cfg, 3, slots=3, context=320, max_rows=512, gains="near_one", page=64, graphs=True)
+    dec.prepare(3)
+    got = dec.generate(prompts, 40)
+    assert np.array_equal(got, want)
+    dec.close()
+
+
 def test_bad_rows_are_refused_before_any_launch():
     from tessera_b200 import TesseraError
     dec = _device(SMALL, 0, slots=2, context=32, max_rows=8, gains="ones", page=16)
