@@ -300,6 +300,49 @@ int ts_set_pdl(int enabled);
  * kind of record).  Synchronises the device. */
 int ts_device_status(void);
 
+/* ---------------------------------------------------------------------------
+ * Launch by the reference's kernel names.  `args` is the list the reference's runner builds for a planned
+ * launch, in the kernel's parameter order: read buffers, the output buffer, the page table if the kept layout
+ * has one, then the u32 / f32 scalars, the layout's own scalar last (engine/plan/lower/src/abi.rs:11-18, 148-153;
+ * engine/plan/lower/src/rule.rs:62-109).  Names (ts_kernel_info_at lists them with their signatures):
+ *   lanes_bf16, thin_bf16, tiled_bf16, parts_bf16      x, w, out, [m,] n, k  (m from shape->down when left out)
+ *   attend_rows_<layout>, flash_rows_<layout>           q, k, v, out, slots, positions, [table], queries, keys,
+ *                                                       heads, kv_heads, width, back, <kept scalar>
+ *   scatter_<layout>                                    x, slots, positions, out, [table], rows, width, <kept scalar>
+ *   top_k                                               x (f32), out (u32), rows, width, k
+ *   lane_norm (f32 out), lane_norm_bf16                 x (f32), w, out, rows, width, eps
+ *   flash_128, flash_256 (one sequence per launch)      q, k, v, out, queries, keys, past, heads, kv_heads, back, ahead
+ * <layout> = dense | interleaved | paged | paged16, as in the reference's `plan_attend_rows_<layout>`.  Queries
+ * arrive already scaled, as the reference scales them in a launch of its own.  The list is checked against the
+ * kernel's signature before anything is launched; a mismatch is TS_ERR_BAD_INPUT.  `shape` is advisory (the
+ * kernels size their own grids) except for the rows of a five-argument linear. */
+typedef enum { TS_ARG_PTR = 0, TS_ARG_U32 = 1, TS_ARG_F32 = 2 } ts_arg_kind;
+
+typedef struct {
+    int kind; /* ts_arg_kind */
+    union {
+        void *ptr;
+        uint32_t u32;
+        float f32;
+    } v;
+} ts_arg;
+
+typedef struct {
+    uint32_t across, down, threads; /* Shape::Grid of the reference (engine/plan/lower/src/abi.rs:119-123) */
+} ts_shape;
+
+typedef struct {
+    const char *name;
+    const char *signature; /* one letter per argument: p = device pointer, u = u32, f = f32 */
+    int order;             /* 0: same bits in any batch (Order::Fixed); 1: deterministic per configuration */
+} ts_kernel_info;
+
+int ts_kernel_count(void);
+int ts_kernel_info_at(int index, ts_kernel_info *out);
+size_t ts_launch_workspace_bytes(const char *kernel, const ts_arg *args, int nargs, const ts_shape *shape);
+int ts_launch(const char *kernel, const ts_arg *args, int nargs, const ts_shape *shape, void *workspace,
+              size_t workspace_bytes, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

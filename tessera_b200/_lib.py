@@ -37,9 +37,21 @@ class TsArg(C.Structure):
     _fields_ = [("kind", i32), ("v", _V)]
 
 
+class TsShape(C.Structure):
+    _fields_ = [("across", u32), ("down", u32), ("threads", u32)]
+
+
+class TsKernelInfo(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("signature", C.c_char_p), ("order", i32)]
+
+
 # name -> (restype, argtypes); every symbol include/tessera_b200.h declares.
 SIGNATURES = {
     "ts_last_error": (C.c_char_p, []),
+    "ts_kernel_count": (i32, []),
+    "ts_kernel_info_at": (i32, [i32, C.POINTER(TsKernelInfo)]),
+    "ts_launch_workspace_bytes": (sz, [C.c_char_p, C.POINTER(TsArg), i32, C.POINTER(TsShape)]),
+    "ts_launch": (i32, [C.c_char_p, C.POINTER(TsArg), i32, C.POINTER(TsShape), vp, sz, vp]),
     "ts_abi_version": (i32, []),
     "ts_set_pdl": (i32, [i32]),
     "ts_device_status": (i32, []),

@@ -88,6 +88,40 @@ RULES = {r.name: r for r in (
 )}
 
 
+def kernels() -> dict:
+    """The C entry point's table: {name: (signature, order)}; signature letters p = pointer, u = u32, f = f32."""
+    import ctypes as C
+    from ._lib import TsKernelInfo, check, lib
+    out = {}
+    for i in range(lib.ts_kernel_count()):
+        info = TsKernelInfo()
+        check(lib.ts_kernel_info_at(i, C.byref(info)))
+        out[info.name.decode()] = (info.signature.decode(), info.order)
+    return out
+
+
+def launch_c(name: str, args, down: int = 0):
+    """ts_launch: `args` in the reference's order, tensors for buffers, int / float for scalars.  The workspace
+    comes from this library's pool; `down` fills shape->down (the rows of a five-argument linear)."""
+    import ctypes as C
+    import torch
+    from . import ops
+    from ._lib import TsArg, TsShape, check, lib
+    arr = (TsArg * len(args))()
+    for i, a in enumerate(args):
+        if isinstance(a, torch.Tensor):
+            arr[i].kind, arr[i].v.ptr = 0, ops._ptr(a)
+        elif isinstance(a, float):
+            arr[i].kind, arr[i].v.f32 = 2, a
+        else:
+            arr[i].kind, arr[i].v.u32 = 1, int(a)
+    shape = TsShape(0, down, 0)
+    device = next(a.device for a in args if isinstance(a, torch.Tensor))
+    nbytes = lib.ts_launch_workspace_bytes(name.encode(), arr, len(args), C.byref(shape))
+    ws = ops.workspace(nbytes, device)
+    check(lib.ts_launch(name.encode(), arr, len(args), C.byref(shape), ops._ptr(ws), nbytes, ops._stream()))
+
+
 def launch(name: str, args, **keywords):
     """Runs the kernel `name` on `args` (the reference's order).  Returns the tensor written."""
     rule = RULES[name]

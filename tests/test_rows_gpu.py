@@ -140,3 +140,58 @@ def test_launch_by_name_with_the_reference_argument_order():
     new = from_bits(normal_bf16(rng, (2, kv_heads * width)))
     rules.launch("scatter", [new, sl, ps, kr, 2, kv_heads * width], kept=kept)
     assert torch.equal(kr[2 * context + 17], new[0]) and torch.equal(kr[39], new[1])
+
+
+def test_ts_launch_by_name():
+    # the C entry point: argument lists in the reference's order, checked against the kernel's signature
+    from tessera_b200 import TesseraError, ops, rules
+    rng = np.random.default_rng(18)
+    m, n, k = 24, 512, 256
+    x = from_bits(normal_bf16(rng, (m, k)))
+    w = from_bits(normal_bf16(rng, (n, k), 0.02))
+    out = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    rules.launch_c("tiled_bf16", [x, w, out, m, n, k])
+    assert torch.equal(out, ops.linear(x, w))
+    out.zero_()
+    rules.launch_c("lanes_bf16", [x, w, out, n, k], down=m)   # m from the launch shape, as in the reference
+    assert torch.equal(out, ops.linear(x, w))
+    with pytest.raises(TesseraError):
+        rules.launch_c("lanes_bf16", [x, w, out, n, k])       # no rows anywhere
+    with pytest.raises(TesseraError):
+        rules.launch_c("tiled_bf16", [x, w, n, k, out])       # buffers after scalars
+
+    xs = torch.randn(5, 300, device="cuda")
+    ids = torch.empty((5, 3), dtype=torch.int32, device="cuda")
+    rules.launch_c("top_k", [xs, ids, 5, 300, 3])
+    assert torch.equal(ids, ops.top_k(xs, 3))
+    g = torch.randn(300, device="cuda")
+    normed = torch.empty((5, 300), dtype=torch.float32, device="cuda")
+    rules.launch_c("lane_norm", [xs, g, normed, 5, 300, 1e-6])
+    assert torch.equal(normed, ops.rms_norm(xs, g, 1e-6, out_dtype=torch.float32))
+
+    # paged16 attention: the table after the last buffer, kept_pages as the last scalar
+    slots, context, heads, kv_heads, width = 3, 48, 4, 2, 128
+    pages = context // 16
+    table = dev_u32(rng.permutation(slots * pages))
+    kept = ops.Kept("paged16", pages, table, slots * pages * 16)
+    kr = from_bits(normal_bf16(rng, (slots * pages * 16, kv_heads, width)))
+    vr = from_bits(normal_bf16(rng, (slots * pages * 16, kv_heads, width)))
+    q = from_bits(normal_bf16(rng, (2, heads, width)))
+    sl, ps = dev_u32([2, 0]), dev_u32([17, 47])
+    o = torch.empty_like(q)
+    rules.launch_c("attend_rows_paged16", [q, kr, vr, o, sl, ps, table, 2, context, heads, kv_heads, width, 0xFFFFFFFF, pages])
+    assert torch.equal(o, ops.attend_rows(q, kr, vr, sl, ps, kept, context, scale=1.0))
+    new = from_bits(normal_bf16(rng, (2, kv_heads * width)))
+    rules.launch_c("scatter_paged16", [new, sl, ps, kr, table, 2, kv_heads * width, pages])
+    want = kr.clone()
+    ops.scatter(new, sl, ps, want.reshape(-1, kv_heads * width), kept)
+    assert torch.equal(kr, want)
+
+    # one whole sequence, causal: q, k, v, out, queries, keys, past, heads, kv_heads, back, ahead
+    seq = 200
+    fq = from_bits(normal_bf16(rng, (1, seq, heads, width)))
+    fk = from_bits(normal_bf16(rng, (1, seq, kv_heads, width)))
+    fv = from_bits(normal_bf16(rng, (1, seq, kv_heads, width)))
+    fo = torch.empty_like(fq)
+    rules.launch_c("flash_128", [fq, fk, fv, fo, seq, seq, 0, heads, kv_heads, 0xFFFFFFFF, 0])
+    assert torch.equal(fo, ops.attend(fq, fk, fv, mask="causal", scale=1.0))

@@ -20,3 +20,31 @@ def test_unknown_names_and_wrong_counts_are_refused():
         rules.launch("no_such_kernel", [])
     with pytest.raises(TypeError):
         rules.launch("top_k", [1, 2, 3])
+
+
+def test_c_table_lists_the_reference_kernel_names():
+    # ts_kernel_info_at: loads the library (no GPU needed) and reads the by-name table
+    from tessera_b200 import rules
+    table = rules.kernels()
+    for name in ("lanes_bf16", "thin_bf16", "tiled_bf16", "parts_bf16", "attend_rows_dense", "attend_rows_paged",
+                 "attend_rows_paged16", "flash_rows_paged", "scatter_dense", "scatter_paged16", "top_k", "lane_norm",
+                 "flash_128", "flash_256"):
+        assert name in table
+    # read buffers, output, [page table], then scalars; the layout's scalar last (rule.rs:62-109)
+    assert table["attend_rows_dense"][0] == "pppppp" + "u" * 7
+    assert table["attend_rows_paged"][0] == "ppppppp" + "u" * 7
+    assert table["scatter_paged"][0] == "ppppp" + "uuu"
+    assert table["lane_norm"][0] == "pppuuf"
+    assert table["top_k"] == ("ppuuu", 0) and table["scatter_dense"][1] == 0   # Order::Fixed
+    assert table["tiled_bf16"][1] == 1 and table["flash_128"][1] == 1          # Order::PerConfig
+
+
+def test_c_launch_refuses_bad_lists_without_a_gpu():
+    import ctypes as C
+    from tessera_b200._lib import TsArg, TsShape, lib
+    arr = (TsArg * 2)()
+    shape = TsShape(0, 0, 0)
+    assert lib.ts_launch(b"no_such_kernel", arr, 2, C.byref(shape), None, 0, None) == 3
+    assert b"no kernel is called" in lib.ts_last_error()
+    assert lib.ts_launch(b"top_k", arr, 2, C.byref(shape), None, 0, None) == 3     # wrong count and NULL pointers
+    assert b"ppuuu" in lib.ts_last_error()
