@@ -87,7 +87,7 @@ int ts_linear_bf16(const void *x, const void *w, const void *a0, void *out, uint
                    uint32_t k, int epilogue, float scale, int out_dtype, int path, void *workspace,
                    size_t workspace_bytes, void *stream);
 
-/* A decode-sized linear (m <= 128) with the RMS norms of the residual stream folded into its two
+/* A linear (decode-sized, m <= 128, or prefill-sized, m >= 512) with the RMS norms of the residual stream folded into its two
  * ends.  The reference runs `lane_norm` as a launch of its own between the residual add and the next
  * projection (engine/models/src/decoder.rs:327-389, engine/rules/kernels/src/lane_norm.rs:10-17); at
  * batch 64 that launch is pure latency.  Since rms_norm(row) * gain = (row * gain) / rms(row), the
@@ -108,6 +108,12 @@ typedef struct {
     void *xs_out;        /* bf16 [m, n] */
     const float *xs_gain; /* f32 [n] */
 } ts_linear_fused;
+
+/* Embedding rows for a model whose first norm is folded into the projection after it: out f32 [rows, width]
+ * as ts_gather_bf16 gives them, xs = bf16(row * gain) and ss [rows, parts] with the row's sum of squares in
+ * part 0 and zeros in the others (`parts` = what the consuming linear will be told). */
+int ts_gather_scaled_bf16(const void *table, const uint32_t *ids, float *out, void *xs, const float *gain, float *ss,
+                          uint32_t parts, uint32_t rows, uint32_t table_rows, uint32_t width, void *stream);
 
 /* Partial sums per row a linear of this shape writes to ss_out; 0 when it cannot (then run ts_rms_norm). */
 uint32_t ts_linear_sumsq_parts(uint32_t m, uint32_t n, uint32_t k, int epilogue);

@@ -57,6 +57,7 @@ SIGNATURES = {
     "ts_device_status": (i32, []),
     "ts_linear_workspace_bytes": (sz, [u32, u32, u32, i32, i32]),
     "ts_linear_bf16": (i32, [vp, vp, vp, vp, u32, u32, u32, i32, f32, i32, i32, vp, sz, vp]),
+    "ts_gather_scaled_bf16": (i32, [vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, vp]),
     "ts_linear_sumsq_parts": (u32, [u32, u32, u32, i32]),
     "ts_linear_fused_bf16": (i32, [vp, vp, vp, vp, u32, u32, u32, i32, f32, i32, C.POINTER(TsLinearFused), vp]),
     "ts_attend_rows_workspace_bytes": (sz, [u32, u32, u32, u32, u32]),

@@ -175,6 +175,7 @@ size_t ts_linear_workspace_bytes(uint32_t m, uint32_t n, uint32_t k, int epilogu
 }
 
 uint32_t ts_linear_sumsq_parts(uint32_t m, uint32_t n, uint32_t k, int epilogue) {
+    if (pick_linear_path(m, n, k, epilogue, TS_LINEAR_AUTO) == TS_LINEAR_PAIR) return pair_sumsq_parts(m, n, k, epilogue);
     return stream_sumsq_parts(m, n, k, epilogue);
 }
 
@@ -195,8 +196,10 @@ int ts_linear_fused_bf16(const void *x, const void *w, const void *a0, void *out
     }
     TS_REQUIRE(x && aligned16(x), "linear: x is NULL or not 16-byte aligned");
     if (m == 0 || n == 0) return TS_OK;
-    TS_REQUIRE(stream_supports(m, n, k, epilogue), "linear (fused): m=%u n=%u k=%u epilogue=%d is not a decode-sized shape",
-               m, n, k, epilogue);
+    if (pick_linear_path(m, n, k, epilogue, TS_LINEAR_AUTO) == TS_LINEAR_PAIR)
+        return linear_pair(x, w, a0, out, m, n, k, epilogue, scale, out_dtype, (cudaStream_t)stream, &f);
+    TS_REQUIRE(stream_supports(m, n, k, epilogue),
+               "linear (fused): m=%u n=%u k=%u epilogue=%d fits neither the decode-sized nor the paired kernel", m, n, k, epilogue);
     return linear_stream(x, w, a0, out, m, n, k, epilogue, scale, out_dtype, (cudaStream_t)stream, &f);
 }
 
@@ -374,6 +377,12 @@ int ts_gather_bf16(const void *table, const uint32_t *ids, void *out, int out_dt
     TS_REQUIRE(table && ids && out, "gather: a buffer is NULL");
     TS_REQUIRE(out_dtype == TS_BF16 || out_dtype == TS_F32, "gather: unknown dtype");
     return gather_rows(table, ids, out, out_dtype, rows, table_rows, width, first, (cudaStream_t)stream);
+}
+
+int ts_gather_scaled_bf16(const void *table, const uint32_t *ids, float *out, void *xs, const float *gain, float *ss,
+                          uint32_t parts, uint32_t rows, uint32_t table_rows, uint32_t width, void *stream) {
+    TS_REQUIRE(table && ids && out && xs && gain && ss, "gather (scaled): a buffer is NULL");
+    return gather_scaled(table, ids, out, xs, gain, ss, parts, rows, table_rows, width, (cudaStream_t)stream);
 }
 
 size_t ts_top_k_workspace_bytes(uint32_t rows, uint32_t width, uint32_t k) {

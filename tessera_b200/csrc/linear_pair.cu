@@ -48,6 +48,16 @@ struct PairParams {
     const float *a0;
     void *out;
     int *status;
+    // The residual stream's RMS norms folded into the linears on either side (NULL / 0: off), as in the
+    // streamed linear: in, x holds bf16(row * gain) and row_ss [m, row_parts] partial sums of squares of the rows,
+    // and the output rows get the factor 1/sqrt(sum/k + row_eps); out (f32 output), ss_out [m, tiles_j] takes the
+    // sum of squares of each finished row over the tile's columns and xs_out [m, n] = bf16(out * xs_gain[n]).
+    const float *row_ss;
+    uint32_t row_parts;
+    float row_eps;
+    float *ss_out;
+    uint16_t *xs_out;
+    const float *xs_gain;
 };
 
 __device__ __forceinline__ bool wait_bounded(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_flag) {
@@ -174,6 +184,13 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
             tc_fence_after_sync();
             const uint32_t gi = ti * kTileM + rank * kRowsPerBlock + row;
             const uint32_t taddr = tmem_base + ((q * 32u) << 16) + as * kTileN;
+            float inv = 1.0f;  // this thread's row: 1/rms from the partial sums the upstream linear left
+            if (p.row_ss && gi < p.m) {
+                float ss = 0.0f;
+                for (uint32_t i = 0; i < p.row_parts; i++) ss += p.row_ss[(size_t)gi * p.row_parts + i];
+                inv = 1.0f / sqrtf(ss / (float)p.k + p.row_eps);
+            }
+            float sq = 0.0f;   // sum of squares of the row's finished values over this tile's columns
             if (p.gated) {
                 // columns [0, 128) are gate rows of w (the leader's half of B), [128, 256) the matching up rows
                 for (uint32_t c0 = 0; c0 < 128; c0 += 16) {
@@ -187,7 +204,7 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                         float v[16];
 #pragma unroll
                         for (uint32_t c = 0; c < 16; c++) {
-                            const float gv = __uint_as_float(rg[c]), uv = __uint_as_float(ru[c]);
+                            const float gv = __uint_as_float(rg[c]) * inv, uv = __uint_as_float(ru[c]) * inv;
                             v[c] = (p.epilogue == TS_EPI_SWIGLU ? silu(gv) : gelu_tanh(gv)) * uv;
                         }
                         if (out_n % 8 == 0 && gj0 + 16 <= out_n && p.out_dtype == TS_BF16) {
@@ -224,7 +241,7 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                             float v[8];
 #pragma unroll
                             for (uint32_t e = 0; e < 8; e++) {
-                                v[e] = __uint_as_float(r[c + e]);
+                                v[e] = __uint_as_float(r[c + e]) * inv;
                                 if (p.epilogue == TS_EPI_ADD) v[e] += p.a0[at0 + c + e];
                                 if (p.epilogue == TS_EPI_SCALE) v[e] *= p.scale;
                             }
@@ -235,8 +252,8 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                         float *o = reinterpret_cast<float *>(p.out) + at0;
 #pragma unroll
                         for (uint32_t c = 0; c < 32; c += 4) {
-                            float4 v = make_float4(__uint_as_float(r[c]), __uint_as_float(r[c + 1]),
-                                                   __uint_as_float(r[c + 2]), __uint_as_float(r[c + 3]));
+                            float4 v = make_float4(__uint_as_float(r[c]) * inv, __uint_as_float(r[c + 1]) * inv,
+                                                   __uint_as_float(r[c + 2]) * inv, __uint_as_float(r[c + 3]) * inv);
                             if (p.epilogue == TS_EPI_ADD) {
                                 const float4 a = *reinterpret_cast<const float4 *>(p.a0 + at0 + c);
                                 v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
@@ -245,20 +262,31 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                                 v.x *= p.scale; v.y *= p.scale; v.z *= p.scale; v.w *= p.scale;
                             }
                             *reinterpret_cast<float4 *>(o + c) = v;
+                            if (p.ss_out) {  // the host asks for these only with n % 8 == 0 and an f32 output: this path
+                                sq = fmaf(v.x, v.x, sq); sq = fmaf(v.y, v.y, sq); sq = fmaf(v.z, v.z, sq); sq = fmaf(v.w, v.w, sq);
+                                const float4 g = *reinterpret_cast<const float4 *>(p.xs_gain + gj0 + c);
+                                *reinterpret_cast<uint2 *>(p.xs_out + at0 + c) =
+                                    make_uint2(pack_bf16(v.x * g.x, v.y * g.y), pack_bf16(v.z * g.z, v.w * g.w));
+                            }
                         }
                     } else {
 #pragma unroll
                         for (uint32_t c = 0; c < 32; c++)
                             if (gj0 + c < p.n) {
-                                float v = __uint_as_float(r[c]);
+                                float v = __uint_as_float(r[c]) * inv;
                                 if (p.epilogue == TS_EPI_ADD) v += p.a0[at0 + c];
                                 if (p.epilogue == TS_EPI_SCALE) v *= p.scale;
                                 if (p.out_dtype == TS_F32) reinterpret_cast<float *>(p.out)[at0 + c] = v;
                                 else reinterpret_cast<uint16_t *>(p.out)[at0 + c] = bf16_bits(v);
+                                if (p.ss_out) {
+                                    sq = fmaf(v, v, sq);
+                                    p.xs_out[at0 + c] = bf16_bits(v * p.xs_gain[gj0 + c]);
+                                }
                             }
                     }
                 }
             }
+            if (p.ss_out && gi < p.m) p.ss_out[(size_t)gi * p.tiles_j + tj] = sq;
             // Release the accumulator stage to the leader's MMA thread: one arrival per epilogue warp of
             // either block.
             tc_fence_before_sync();
@@ -320,8 +348,13 @@ bool pair_supports(uint32_t m, uint32_t n, uint32_t k, int epilogue) {
     return n >= 256;
 }
 
+uint32_t pair_sumsq_parts(uint32_t m, uint32_t n, uint32_t k, int epilogue) {
+    const bool gated = epilogue == TS_EPI_SWIGLU || epilogue == TS_EPI_GEGLU;
+    return (!gated && pair_supports(m, n, k, epilogue) && n % 8 == 0) ? ceil_div(n, kTileN) : 0;
+}
+
 int linear_pair(const void *x, const void *w, const void *a0, void *out, uint32_t m, uint32_t n, uint32_t k, int epilogue,
-                float scale, int out_dtype, cudaStream_t stream) {
+                float scale, int out_dtype, cudaStream_t stream, const StreamFused *fused) {
     if (!pair_supports(m, n, k, epilogue))
         return fail(TS_ERR_BAD_INPUT, "linear (pair): unsupported shape m=%u n=%u k=%u epilogue=%d", m, n, k, epilogue);
     const bool gated = epilogue == TS_EPI_SWIGLU || epilogue == TS_EPI_GEGLU;
@@ -343,6 +376,21 @@ int linear_pair(const void *x, const void *w, const void *a0, void *out, uint32_
     p.scale = scale;
     p.a0 = (const float *)a0;
     p.out = out;
+    if (fused) {
+        if (fused->row_ss)
+            TS_REQUIRE(fused->row_parts >= 1 && fused->row_parts <= 64, "linear (pair): 1..64 partial sums per row, got %u",
+                       fused->row_parts);
+        if (fused->ss_out || fused->xs_out)
+            TS_REQUIRE(fused->ss_out && fused->xs_out && fused->xs_gain && out_dtype == TS_F32 &&
+                           pair_sumsq_parts(m, n, k, epilogue) != 0,
+                       "linear (pair): sums of squares and the scaled copy come together, with an f32 output and n %% 8 == 0");
+        p.row_ss = fused->row_ss;
+        p.row_parts = fused->row_parts;
+        p.row_eps = fused->row_eps;
+        p.ss_out = fused->ss_out;
+        p.xs_out = (uint16_t *)fused->xs_out;
+        p.xs_gain = fused->xs_gain;
+    }
     int *status = nullptr;
     TS_CUDA(cudaGetSymbolAddress((void **)&status, g_pair_status));
     p.status = status;

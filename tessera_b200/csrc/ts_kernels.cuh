@@ -15,8 +15,10 @@ size_t umma_workspace_bytes(uint32_t m, uint32_t n, uint32_t k, int epilogue);
 int umma_take_status();
 // Two-SM pairs (tcgen05 cta_group::2) on 256 x 256 tiles: prefill-sized m.
 bool pair_supports(uint32_t m, uint32_t n, uint32_t k, int epilogue);
+struct StreamFused;
+uint32_t pair_sumsq_parts(uint32_t m, uint32_t n, uint32_t k, int epilogue);  // partial sums per row it leaves, or 0
 int linear_pair(const void *x, const void *w, const void *a0, void *out, uint32_t m, uint32_t n, uint32_t k, int epilogue,
-                float scale, int out_dtype, cudaStream_t stream);
+                float scale, int out_dtype, cudaStream_t stream, const StreamFused *fused = nullptr);
 int pair_take_status();
 uint32_t pair_slots();  // SM pairs that can run the paired kernel at once
 int linear_umma(const void *x, const void *w, const void *a0, void *out, uint32_t m, uint32_t n, uint32_t k,

@@ -10,10 +10,13 @@ back to back and the attention kernel takes the sequence bounds.
 """
 from __future__ import annotations
 
+import os
+
 import numpy as np
 import torch
 
 from . import ops
+from ._lib import EPILOGUE, lib
 
 EMBEDDING_300M = dict(layers=24, hidden=768, heads=3, kv_heads=1, head_dim=256, ffn=1152, vocab=262144,
                       eps=1e-6, theta=1e6)
@@ -58,20 +61,40 @@ class Encoder:
         table = torch.zeros(seqs * max_len, dtype=torch.int32, device=self.device)
         table[slots.long() * max_len + positions.long()] = torch.arange(total, dtype=torch.int32, device=self.device)
         kept = ops.Kept("paged", max_len, table, total, page=1)
-        x = ops.gather(self.embed, tokens, out_dtype=torch.float32)
         q = torch.empty((total, heads, d), dtype=torch.bfloat16, device=self.device)
         k = torch.empty((total, kvh, d), dtype=torch.bfloat16, device=self.device)
         v = torch.empty_like(k)
         scale = float(d) ** -0.5
-        for L in self.layers:
-            h = ops.rms_norm(x, L["ln1"], eps)
-            qkv = ops.linear(h, L["wqkv"])
+        hidden_w, inner_w = c["hidden"], heads * d
+        # The two norms of a layer can fold into the projections around them (TS_ENCODER_FOLD=1) when the
+        # residual-adding ones can leave the rows' sums of squares (ts_linear_sumsq_parts > 0).  Off by default:
+        # at 273 K rows the paired kernel's epilogue (a thread per row: 16-byte pieces of 32 different rows per
+        # store instruction) is what bounds these short-k projections, and the extra scaled copy it then writes
+        # costs more (157 ms per pass) than the norm launches it removes (140 ms).
+        parts = lib.ts_linear_sumsq_parts(total, hidden_w, inner_w, EPILOGUE["add"])
+        fold = (os.environ.get("TS_ENCODER_FOLD", "0") == "1" and parts > 0 and
+                lib.ts_linear_sumsq_parts(total, hidden_w, c["ffn"], EPILOGUE["add"]) == parts)
+        if fold:
+            x, xs, ss = ops.gather_scaled(self.embed, tokens, self.layers[0]["ln1"], parts)
+        else:
+            x = ops.gather(self.embed, tokens, out_dtype=torch.float32)
+        for i, L in enumerate(self.layers):
+            if fold:
+                qkv = ops.linear_fused(xs, L["wqkv"], rows=(ss, eps))
+            else:
+                qkv = ops.linear(ops.rms_norm(x, L["ln1"], eps), L["wqkv"])
             ops.qk_norm_rope_append(qkv, L["q_norm"], L["k_norm"], self.inv_freq, slots, positions, q, k, v, kept,
                                     heads, kvh, d, eps)
             a = ops.attend(q, k, v, mask="bidirectional", scale=scale, cu_seqlens=cu_seqlens, max_len=max_len)
-            x = ops.linear(a.view(total, heads * d), L["wo"], x, epilogue="add", out_dtype=torch.float32, out=x)
-            h = ops.rms_norm(x, L["ln2"], eps)
-            act = ops.linear(h, L["wgu"], epilogue="geglu")
-            x = ops.linear(act, L["wdown"], x, epilogue="add", out_dtype=torch.float32, out=x)
+            if fold:
+                x, xs, ss = ops.linear_fused(a.view(total, inner_w), L["wo"], x, epilogue="add", out_dtype=torch.float32, out=x,
+                                             next_gain=L["ln2"])
+                act = ops.linear_fused(xs, L["wgu"], epilogue="geglu", rows=(ss, eps))
+                nxt = self.layers[i + 1]["ln1"] if i + 1 < len(self.layers) else self.norm
+                x, xs, ss = ops.linear_fused(act, L["wdown"], x, epilogue="add", out_dtype=torch.float32, out=x, next_gain=nxt)
+            else:
+                x = ops.linear(a.view(total, inner_w), L["wo"], x, epilogue="add", out_dtype=torch.float32, out=x)
+                act = ops.linear(ops.rms_norm(x, L["ln2"], eps), L["wgu"], epilogue="geglu")
+                x = ops.linear(act, L["wdown"], x, epilogue="add", out_dtype=torch.float32, out=x)
         hidden = ops.rms_norm(x, self.norm, eps, out_dtype=torch.float32)
         return ops.mean_pool(hidden, cu_seqlens, normalize=True)

@@ -218,6 +218,18 @@ def rms_norm(x, w=None, eps=1e-6, out_dtype=torch.bfloat16, out=None):
     return out
 
 
+def gather_scaled(table, ids, gain, parts: int):
+    """ts_gather_scaled_bf16: (rows f32, bf16(rows * gain), sums of squares f32 [rows, parts])."""
+    rows = ids.numel()
+    table_rows, width = table.shape
+    out = torch.empty((rows, width), dtype=torch.float32, device=table.device)
+    xs = torch.empty((rows, width), dtype=torch.bfloat16, device=table.device)
+    ss = torch.empty((rows, parts), dtype=torch.float32, device=table.device)
+    check(lib.ts_gather_scaled_bf16(_ptr(table), _ptr(ids), _ptr(out), _ptr(xs), _ptr(gain), _ptr(ss), parts, rows, table_rows,
+                                    width, _stream()))
+    return out, xs, ss
+
+
 def gather(table, ids, out_dtype=torch.float32, first=0):
     rows = ids.numel()
     table_rows, width = table.shape

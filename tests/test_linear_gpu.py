@@ -245,3 +245,33 @@ def test_pair_equals_one_sm_tiles_bit_for_bit():
     a = _run(x, w, "pair", out_dtype=torch.float32)
     b = _run(x, w, "umma", out_dtype=torch.float32)
     assert torch.equal(a, b)
+
+
+def test_norms_folded_into_the_paired_projections():
+    # the prefill-sized pair: same contract as the decode-sized one, on the two-SM kernel
+    from tessera_b200 import ops
+    rng = np.random.default_rng(77)
+    m, hidden, inner, eps = 640, 768, 512, 1e-6
+    a = normal_bf16(rng, (m, inner), 1.0)
+    w1 = normal_bf16(rng, (hidden, inner), 0.02)
+    x0 = rng.standard_normal((m, hidden)).astype(np.float32)
+    gain = (1.0 + 0.1 * rng.standard_normal(hidden)).astype(np.float32)
+    w2 = normal_bf16(rng, (1280, hidden), 0.02)
+    wgu = normal_bf16(rng, (2 * 1152, hidden), 0.02)
+    x0_d, gain_d = torch.from_numpy(x0).cuda(), torch.from_numpy(gain).cuda()
+    y, xs, ss = ops.linear_fused(from_bits(a), from_bits(w1), x0_d, epilogue="add", out_dtype=torch.float32, next_gain=gain_d)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    want_y = O.matmul(O.bf16_widen(a), w1) + x0
+    assert rel_error(y.cpu().numpy(), want_y) <= F32_TOL
+    assert ss.shape == (m, hidden // 256)
+    tiles = (y.double() ** 2).reshape(m, hidden // 256, 256).sum(-1)
+    assert torch.allclose(ss.double(), tiles, rtol=1e-5, atol=1e-6)
+    assert torch.equal(xs, (y * gain_d).to(torch.bfloat16))
+    h = O.bf16_round(O.rms_norm(y.cpu().numpy(), gain, eps))
+    for w, epi in ((w2, "none"), (wgu, "geglu")):
+        got = ops.linear_fused(xs, from_bits(w), epilogue=epi, rows=(ss, eps))
+        torch.cuda.synchronize()
+        z = O.matmul(h, w)
+        want = z if epi == "none" else O.act(z[:, :1152], "gelu_tanh") * z[:, 1152:]
+        assert rel_error(widen(got), want) <= BF16_TOL
