@@ -187,6 +187,19 @@ int ts_qk_norm_rope_append_bf16(const void *qkv, const float *q_norm, const floa
                                 uint32_t rows, uint32_t heads, uint32_t kv_heads, uint32_t width,
                                 float eps, void *stream);
 
+/* The reference's two rotary launches on their own (engine/rules/kernels/src/rope.rs:10-60), for a host that replays
+ * its step list launch by launch.  `angles`: out[p, 2j] = cos(a), out[p, 2j + 1] = sin(a), a = positions[p] *
+ * theta^(-2j / width) for pair j < turned, else 0; out f32 [count, width], width even and at most 512; the powers
+ * are taken on the host in f32 (cpu.rs:31-34) and ride in the launch.  `rope` (adjacent = 0: pair j is (j, j +
+ * width/2); adjacent = 1, `rope_adjacent`: (2j, 2j + 1)) rotates x [positions, heads, width] in place, f32 as in
+ * the reference or bf16; products and sums are separate roundings, so f32 rows equal the CPU interpreter's bit
+ * for bit given the same angles. */
+int ts_rope_angles(const uint32_t *positions, float *out, uint32_t count, uint32_t width, float theta, uint32_t turned,
+                   void *stream);
+
+int ts_rope(void *x, ts_dtype dtype, const float *freqs, uint32_t positions, uint32_t heads, uint32_t width, int adjacent,
+            void *stream);
+
 /* out[j] = theta^(-2j / width) for j < width/2, in f32 on the host (engine/ir/interp/src/cpu.rs:31-34). */
 void ts_rope_inv_freq(float theta, uint32_t width, float *out);
 
@@ -282,6 +295,18 @@ int ts_moe_experts_bf16(const void *x, const uint32_t *ids, const void *w_in, co
 int ts_moe_bf16(const void *h, const uint32_t *ids, const float *gates, const float *add, const void *w_in,
                 const void *w_out, float *y, uint32_t rows, uint32_t top, uint32_t experts, uint32_t first,
                 uint32_t hidden, uint32_t ffn, void *workspace, size_t workspace_bytes, void *stream);
+
+/* One `picked` launch on its own, with the reference's argument list (engine/rules/linear/src/picked.rs:28-60):
+ *     out[i, col] = sum_j x[i / repeat, j] * w[(ids[i] - first) * stride + offset + col, j]      col < n, j < k
+ * and zeros where ids[i] falls outside [first, first + count).  x bf16 [rows / repeat, k]; w bf16, `count`
+ * matrices `stride` rows apart, of which this launch reads rows [offset, offset + n) (the gate or the up half of a
+ * fused table, say); ids u32 [rows]; out f32 [rows, n].  n a multiple of 128, k of 64.  Rows are grouped by matrix
+ * (stable counting sort, integer work) so that each matrix streams once per 32 rows that picked it. */
+size_t ts_picked_workspace_bytes(uint32_t rows, uint32_t n, uint32_t k, uint32_t count);
+
+int ts_picked_bf16(const void *x, const void *w, const uint32_t *ids, float *out, uint32_t rows, uint32_t n, uint32_t k,
+                   uint32_t count, uint32_t stride, uint32_t offset, uint32_t repeat, uint32_t first, void *workspace,
+                   size_t workspace_bytes, void *stream);
 
 /* The `mix` alone (engine/ir/interp/src/cpu.rs:449-473): out[r, :] = sum_p gates[r, p] * y_picks[r * top + p, :]
  * in pick order, plus add[r, :] when add is not NULL.  For expert-parallel runs, where the per-pick outputs

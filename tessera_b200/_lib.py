@@ -69,6 +69,8 @@ SIGNATURES = {
     "ts_scatter_bf16": (i32, [vp, vp, vp, vp, C.POINTER(TsKept), u32, u32, vp]),
     "ts_qk_norm_rope_append_bf16": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, vp, C.POINTER(TsKept), u32, u32, u32, u32, f32, vp]),
     "ts_rope_inv_freq": (None, [f32, u32, vp]),
+    "ts_rope_angles": (i32, [vp, vp, u32, u32, f32, u32, vp]),
+    "ts_rope": (i32, [vp, i32, vp, u32, u32, u32, i32, vp]),
     "ts_rms_norm": (i32, [vp, i32, vp, vp, i32, u32, u32, f32, vp]),
     "ts_gather_bf16": (i32, [vp, vp, vp, i32, u32, u32, u32, u32, vp]),
     "ts_top_k_workspace_bytes": (sz, [u32, u32, u32]),
@@ -77,6 +79,8 @@ SIGNATURES = {
     "ts_moe_workspace_bytes": (sz, [u32, u32, u32, u32]),
     "ts_moe_experts_bf16": (i32, [vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u32, vp, sz, vp]),
     "ts_moe_bf16": (i32, [vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u32, vp, sz, vp]),
+    "ts_picked_workspace_bytes": (sz, [u32, u32, u32, u32]),
+    "ts_picked_bf16": (i32, [vp, vp, vp, vp, u32, u32, u32, u32, u32, u32, u32, u32, vp, sz, vp]),
     "ts_moe_mix": (i32, [vp, vp, vp, vp, u32, u32, u32, vp]),
     "ts_moe_permutation": (i32, [vp, vp, vp, vp, vp, u32, u32, u32, vp]),
     "ts_mean_pool": (i32, [vp, vp, vp, u32, u32, i32, vp]),

@@ -348,6 +348,21 @@ void ts_rope_inv_freq(float theta, uint32_t width, float *out) {
     for (uint32_t j = 0; j < width / 2; j++) out[j] = powf(theta, -((float)(2 * j)) / (float)width);
 }
 
+int ts_rope_angles(const uint32_t *positions, float *out, uint32_t count, uint32_t width, float theta, uint32_t turned,
+                   void *stream) {
+    TS_REQUIRE(positions && out, "rope angles: a buffer is NULL");
+    TS_REQUIRE(((uintptr_t)out & 7) == 0, "rope angles: out must be 8-byte aligned");
+    return rope_angles(positions, out, count, width, theta, turned, (cudaStream_t)stream);
+}
+
+int ts_rope(void *x, ts_dtype dtype, const float *freqs, uint32_t positions, uint32_t heads, uint32_t width, int adjacent,
+            void *stream) {
+    TS_REQUIRE(x && freqs, "rope: a buffer is NULL");
+    TS_REQUIRE(dtype == TS_BF16 || dtype == TS_F32, "rope: dtype %d is neither bf16 nor f32", (int)dtype);
+    TS_REQUIRE(((uintptr_t)freqs & 7) == 0, "rope: freqs must be 8-byte aligned");
+    return rope(x, dtype, freqs, positions, heads, width, adjacent, (cudaStream_t)stream);
+}
+
 int ts_qk_norm_rope_append_bf16(const void *qkv, const float *q_norm, const float *k_norm, const float *inv_freq,
                                 const uint32_t *slots, const uint32_t *positions, void *q_out, void *k_rows,
                                 void *v_rows, const ts_kept *kept, uint32_t rows, uint32_t heads, uint32_t kv_heads,
@@ -453,6 +468,20 @@ int ts_moe_bf16(const void *h, const uint32_t *ids, const float *gates, const fl
     if (rows == 0) return TS_OK;
     return moe_experts(h, ids, gates, add, w_in, w_out, y, rows * top, top, top, 1, experts, first, hidden, ffn, workspace,
                        workspace_bytes, (cudaStream_t)stream);
+}
+
+size_t ts_picked_workspace_bytes(uint32_t rows, uint32_t n, uint32_t k, uint32_t count) {
+    return picked_workspace_bytes(rows, n, k, count);
+}
+
+int ts_picked_bf16(const void *x, const void *w, const uint32_t *ids, float *out, uint32_t rows, uint32_t n, uint32_t k,
+                   uint32_t count, uint32_t stride, uint32_t offset, uint32_t repeat, uint32_t first, void *workspace,
+                   size_t workspace_bytes, void *stream) {
+    TS_REQUIRE(x && w && ids && out, "picked: a buffer is NULL");
+    TS_REQUIRE(aligned16(x) && aligned16(w) && aligned16(out), "picked: buffers must be 16-byte aligned");
+    TS_REQUIRE(count >= 1 && count <= 4096, "picked: %u matrices is outside 1..4096", count);
+    return picked(x, w, ids, out, rows, n, k, count, stride, offset, repeat, first, workspace, workspace_bytes,
+                  (cudaStream_t)stream);
 }
 
 int ts_moe_mix(const float *y_picks, const float *gates, const float *add, float *out, uint32_t rows, uint32_t top,

@@ -96,6 +96,24 @@ int run_flash(const Args &a, int, const ts_shape *, int variant, void *ws, size_
                           (uint32_t)variant, a.u(9), a.u(10), 1.0f, ws, ws_bytes, stream);
 }
 
+// x, w, ids, out, rows, n, k, count, stride, offset, repeat, first (engine/rules/linear/src/picked.rs:28-41); x and w bf16
+int run_picked(const Args &a, int, const ts_shape *, int, void *ws, size_t ws_bytes, void *stream) {
+    return ts_picked_bf16(a.ptr(0), a.ptr(1), (const uint32_t *)a.ptr(2), (float *)const_cast<void *>(a.ptr(3)), a.u(4), a.u(5),
+                          a.u(6), a.u(7), a.u(8), a.u(9), a.u(10), a.u(11), ws, ws_bytes, stream);
+}
+size_t ws_picked(const Args &a, int, const ts_shape *, int) { return ts_picked_workspace_bytes(a.u(4), a.u(5), a.u(6), a.u(7)); }
+
+// positions, out, count, width, theta, turned (engine/rules/kernels/src/rope.rs:36-44)
+int run_angles(const Args &a, int, const ts_shape *, int, void *, size_t, void *stream) {
+    return ts_rope_angles((const uint32_t *)a.ptr(0), (float *)const_cast<void *>(a.ptr(1)), a.u(2), a.u(3), a.f(4), a.u(5), stream);
+}
+
+// x (in place), freqs, positions, heads, width (rope.rs:10-16); variant bit 0: adjacent pairs, bit 1: bf16 rows
+int run_rope(const Args &a, int, const ts_shape *, int variant, void *, size_t, void *stream) {
+    return ts_rope(const_cast<void *>(a.ptr(0)), (variant & 2) ? TS_BF16 : TS_F32, (const float *)a.ptr(1), a.u(2), a.u(3), a.u(4),
+                   variant & 1, stream);
+}
+
 struct Entry {
     const char *name;
     const char *signature;  // p = device pointer, u = u32, f = f32, in the reference's order
@@ -125,6 +143,12 @@ const Entry kTable[] = {
     {"top_k", "ppuuu", nullptr, 0, 0, run_top_k, ws_top_k},
     {"lane_norm", "pppuuf", nullptr, 1, 0, run_lane_norm, nullptr},
     {"lane_norm_bf16", "pppuuf", nullptr, 1, 1, run_lane_norm, nullptr},
+    {"picked_bf16", "ppppuuuuuuuu", nullptr, 1, 0, run_picked, ws_picked},
+    {"angles", "ppuufu", nullptr, 1, 0, run_angles, nullptr},
+    {"rope", "ppuuu", nullptr, 0, 0, run_rope, nullptr},
+    {"rope_adjacent", "ppuuu", nullptr, 0, 1, run_rope, nullptr},
+    {"rope_bf16", "ppuuu", nullptr, 0, 2, run_rope, nullptr},
+    {"rope_adjacent_bf16", "ppuuu", nullptr, 0, 3, run_rope, nullptr},
     {"flash_128", "ppppuuuuuuu", nullptr, 1, 128, run_flash, nullptr},
     {"flash_256", "ppppuuuuuuu", nullptr, 1, 256, run_flash, nullptr},
 };

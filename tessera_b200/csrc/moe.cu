@@ -104,6 +104,7 @@ __global__ void __launch_bounds__(128) moe_gather_kernel(const uint16_t *x, cons
 struct GroupedParams {
     const uint32_t *offsets, *btiles;  // [experts + 1]
     uint32_t experts, n, k;            // per expert: weight [n, k]
+    uint32_t w_stride;                 // weight rows from one expert to the next (n, or more inside a wider table)
     uint32_t tiles;                    // weight tiles per expert: n / 128, or (n / 2) / 64 when gated
     uint32_t gated;
     void *out;                         // gated: bf16 [picks, n / 2]; plain: f32 [picks, n]
@@ -191,7 +192,7 @@ moe_grouped_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             bool ok = true;
             for (uint32_t i = blockIdx.x; i < items && ok; i += gridDim.x) {
                 const Item item = decode_item(p, i);
-                const uint32_t wrow = item.expert * p.n;  // the expert's first weight row
+                const uint32_t wrow = item.expert * p.w_stride;  // the expert's first weight row
                 for (uint32_t kb = 0; kb < kbs; kb++, it++) {
                     const uint32_t s = it % kStages, ph = (it / kStages) & 1;
                     ok = mbar_wait_or_abort(&empty[s], ph ^ 1, abort_flag);
@@ -342,7 +343,7 @@ struct MoeWorkspace {
     size_t total;
 };
 
-MoeWorkspace carve(void *base, uint32_t picks, uint32_t experts, uint32_t hidden, uint32_t ffn) {
+MoeWorkspace carve(void *base, uint32_t picks, uint32_t experts, uint32_t hidden, uint32_t ffn, uint32_t y_cols = 0) {
     MoeWorkspace w;
     size_t at = 0;
     auto take = [&](size_t bytes) {
@@ -357,15 +358,16 @@ MoeWorkspace carve(void *base, uint32_t picks, uint32_t experts, uint32_t hidden
     // TMA boxes of kBN rows may read past the last pick: pad the row buffers by one tile.
     w.xp = (uint16_t *)take((size_t)(picks + kBN) * hidden * 2);
     w.act = (uint16_t *)take((size_t)(picks + kBN) * ffn * 2);
-    w.y = (float *)take((size_t)picks * hidden * 4);
+    w.y = (float *)take((size_t)picks * (y_cols ? y_cols : hidden) * 4);
     w.total = at;
     return w;
 }
 
 int launch_grouped(const void *w, const void *x, void *out, const MoeWorkspace &ws, uint32_t picks, uint32_t experts,
-                   uint32_t n, uint32_t k, bool gated, cudaStream_t stream) {
+                   uint32_t n, uint32_t k, bool gated, cudaStream_t stream, uint32_t w_stride = 0) {
     CUtensorMap map_w, map_x;
-    int rc = make_tensor_map_2d(&map_w, w, (uint64_t)experts * n, k, k, gated ? 64 : kRows, kBlockK);
+    if (w_stride == 0) w_stride = n;
+    int rc = make_tensor_map_2d(&map_w, w, (uint64_t)(experts - 1) * w_stride + n, k, k, gated ? 64 : kRows, kBlockK);
     if (rc != TS_OK) return rc;
     rc = make_tensor_map_2d(&map_x, x, (uint64_t)picks + kBN, k, k, kBN, kBlockK);
     if (rc != TS_OK) return rc;
@@ -375,6 +377,7 @@ int launch_grouped(const void *w, const void *x, void *out, const MoeWorkspace &
     p.experts = experts;
     p.n = n;
     p.k = k;
+    p.w_stride = w_stride;
     p.tiles = gated ? (n / 2) / 64 : n / kRows;
     p.gated = gated;
     p.out = out;
@@ -437,6 +440,39 @@ int moe_experts(const void *x, const uint32_t *ids, const float *gates, const fl
     const uint32_t out_rows = mix ? picks / top : picks;
     e = launch(moe_scatter_mix_kernel, dim3(out_rows), dim3(256), 0, stream, pdl_enabled(), (const float *)ws.y,
                (const uint32_t *)ws.place, gates, add, out, hidden, top, mix);
+    if (e != cudaSuccess) return fail(TS_ERR_CUDA, "launch of moe_scatter_mix failed: %s", cudaGetErrorString(e));
+    return TS_OK;
+}
+
+// The reference's `picked` launch on its own: out[i, :] = x[i / repeat, :] . w[(ids[i] - first) * stride + offset + col, :],
+// zeros where ids[i] falls outside [first, first + count).  Rows are grouped by matrix so that each matrix
+// streams once per 32 rows that picked it.
+size_t picked_workspace_bytes(uint32_t rows, uint32_t n, uint32_t k, uint32_t count) {
+    return carve(nullptr, rows, count, k, 0, n).total;
+}
+
+int picked(const void *x, const void *w, const uint32_t *ids, float *out, uint32_t rows, uint32_t n, uint32_t k,
+           uint32_t count, uint32_t stride, uint32_t offset, uint32_t repeat, uint32_t first, void *workspace,
+           size_t workspace_bytes, cudaStream_t stream) {
+    TS_REQUIRE(n % kRows == 0 && k % kBlockK == 0, "picked: n must be a multiple of %u and k of %u (got %u, %u)", kRows,
+               kBlockK, n, k);
+    TS_REQUIRE(count >= 1 && repeat >= 1 && stride >= offset + n, "picked: stride %u does not hold offset %u + n %u",
+               stride, offset, n);
+    if (rows == 0) return TS_OK;
+    const size_t need = picked_workspace_bytes(rows, n, k, count);
+    TS_REQUIRE(workspace && workspace_bytes >= need, "picked: workspace of %zu bytes is smaller than the %zu needed",
+               workspace_bytes, need);
+    MoeWorkspace ws = carve(workspace, rows, count, k, 0, n);  // no inner rows; y holds n columns
+    int rc = moe_permutation(ids, ws.order, ws.place, ws.offsets, ws.btiles, rows, count, first, stream);
+    if (rc != TS_OK) return rc;
+    cudaError_t e = launch(moe_gather_kernel, dim3(rows), dim3(128), 0, stream, pdl_enabled(), (const uint16_t *)x,
+                           (const uint32_t *)ws.order, (const uint32_t *)ws.offsets, ws.xp, count, k, repeat);
+    if (e != cudaSuccess) return fail(TS_ERR_CUDA, "launch of moe_gather failed: %s", cudaGetErrorString(e));
+    const uint16_t *w0 = (const uint16_t *)w + (size_t)offset * k;
+    rc = launch_grouped(w0, ws.xp, ws.y, ws, rows, count, n, k, false, stream, stride);
+    if (rc != TS_OK) return rc;
+    e = launch(moe_scatter_mix_kernel, dim3(rows), dim3(256), 0, stream, pdl_enabled(), (const float *)ws.y,
+               (const uint32_t *)ws.place, (const float *)nullptr, (const float *)nullptr, out, n, 1u, 0);
     if (e != cudaSuccess) return fail(TS_ERR_CUDA, "launch of moe_scatter_mix failed: %s", cudaGetErrorString(e));
     return TS_OK;
 }

@@ -408,6 +408,61 @@ __global__ void gate_kernel(const volatile uint32_t *flag, uint32_t spins) {
         if (*flag) return;
 }
 
+// The reference's two rotary launches (engine/rules/kernels/src/rope.rs:10-60).  `angles`: a thread per
+// (position, pair) writes cos and sin of position * theta^(-2 pair / width) side by side; pairs from `turned`
+// on keep angle zero.  The powers come from the host in f32 (the table ts_rope_inv_freq writes), as a kernel
+// argument: the same bits as a host that computes them, which powf on the device does not promise.
+struct TurnTable {
+    float turn[256];
+};
+
+__global__ void __launch_bounds__(256) rope_angles_kernel(const uint32_t *positions, float *out, uint32_t count,
+                                                          uint32_t width, uint32_t turned, const TurnTable table) {
+    pdl_wait();
+    const uint32_t pairs = width / 2, i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < count * pairs) {
+        const uint32_t at = i / pairs, pair = i % pairs;
+        float sn = 0.0f, cs = 1.0f;
+        if (pair < turned) sincosf((float)positions[at] * table.turn[pair], &sn, &cs);
+        reinterpret_cast<float2 *>(out)[(size_t)at * pairs + pair] = make_float2(cs, sn);
+    }
+    pdl_launch_dependents();
+}
+
+// `rope` / `rope_adjacent`: a thread per (position, head, pair) rotates its pair in place by the position's
+// (cos, sin); pairs lie side by side (adjacent) or one in each half of the head.
+template <typename T, bool ADJACENT>
+__global__ void __launch_bounds__(256) rope_kernel(T *x, const float *freqs, uint32_t positions, uint32_t heads,
+                                                   uint32_t width) {
+    pdl_wait();
+    const uint32_t pairs = width / 2;
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < (size_t)positions * heads * pairs) {
+        const uint32_t pair = (uint32_t)(i % pairs), s = (uint32_t)(i / pairs / heads);
+        T *row = x + (i / pairs) * width;
+        const float2 cs = reinterpret_cast<const float2 *>(freqs)[(size_t)s * pairs + pair];
+        const uint32_t a = ADJACENT ? 2 * pair : pair, b = ADJACENT ? a + 1 : pairs + pair;
+        float x0, x1;
+        if constexpr (sizeof(T) == 2) {
+            x0 = __uint_as_float((uint32_t)row[a] << 16);
+            x1 = __uint_as_float((uint32_t)row[b] << 16);
+        } else {
+            x0 = row[a];
+            x1 = row[b];
+        }
+        const float ra = __fsub_rn(__fmul_rn(x0, cs.x), __fmul_rn(x1, cs.y));
+        const float rb = __fadd_rn(__fmul_rn(x0, cs.y), __fmul_rn(x1, cs.x));
+        if constexpr (sizeof(T) == 2) {
+            row[a] = bf16_bits(ra);
+            row[b] = bf16_bits(rb);
+        } else {
+            row[a] = ra;
+            row[b] = rb;
+        }
+    }
+    pdl_launch_dependents();
+}
+
 constexpr uint32_t kPeakParts = 64;
 
 }  // namespace
@@ -435,6 +490,37 @@ int gate(const volatile uint32_t *flag, cudaStream_t stream) {
     gate_kernel<<<1, 1, 0, stream>>>(flag, 1u << 21);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(TS_ERR_CUDA, "launch of gate failed: %s", cudaGetErrorString(e));
+    return TS_OK;
+}
+
+int rope_angles(const uint32_t *positions, float *out, uint32_t count, uint32_t width, float theta, uint32_t turned,
+                cudaStream_t stream) {
+    TS_REQUIRE(width >= 2 && width % 2 == 0 && width <= 512, "rope angles: width %u is not an even number up to 512", width);
+    if (count == 0) return TS_OK;
+    TurnTable table;
+    for (uint32_t j = 0; j < width / 2; j++) table.turn[j] = powf(theta, -((float)(2 * j)) / (float)width);
+    const uint32_t threads = count * (width / 2);
+    cudaError_t e = launch(rope_angles_kernel, dim3(ceil_div(threads, 256)), dim3(256), 0, stream, pdl_enabled(), positions,
+                           out, count, width, turned, table);
+    if (e != cudaSuccess) return fail(TS_ERR_CUDA, "launch of rope angles failed: %s", cudaGetErrorString(e));
+    return TS_OK;
+}
+
+int rope(void *x, int dtype, const float *freqs, uint32_t positions, uint32_t heads, uint32_t width, int adjacent,
+         cudaStream_t stream) {
+    TS_REQUIRE(width >= 2 && width % 2 == 0, "rope: width %u is odd", width);
+    const size_t threads = (size_t)positions * heads * (width / 2);
+    if (threads == 0) return TS_OK;
+    const dim3 grid((unsigned)((threads + 255) / 256));
+    const bool pdl = pdl_enabled();
+    cudaError_t e;
+    if (dtype == TS_BF16)
+        e = adjacent ? launch(rope_kernel<uint16_t, true>, grid, dim3(256), 0, stream, pdl, (uint16_t *)x, freqs, positions, heads, width)
+                     : launch(rope_kernel<uint16_t, false>, grid, dim3(256), 0, stream, pdl, (uint16_t *)x, freqs, positions, heads, width);
+    else
+        e = adjacent ? launch(rope_kernel<float, true>, grid, dim3(256), 0, stream, pdl, (float *)x, freqs, positions, heads, width)
+                     : launch(rope_kernel<float, false>, grid, dim3(256), 0, stream, pdl, (float *)x, freqs, positions, heads, width);
+    if (e != cudaSuccess) return fail(TS_ERR_CUDA, "launch of rope failed: %s", cudaGetErrorString(e));
     return TS_OK;
 }
 

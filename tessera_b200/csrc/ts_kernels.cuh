@@ -106,6 +106,14 @@ int moe_experts(const void *x, const uint32_t *ids, const float *gates, const fl
                 uint32_t first, uint32_t hidden, uint32_t ffn, void *workspace, size_t workspace_bytes,
                 cudaStream_t stream);
 
+int rope_angles(const uint32_t *positions, float *out, uint32_t count, uint32_t width, float theta, uint32_t turned,
+                cudaStream_t stream);
+int rope(void *x, int dtype, const float *freqs, uint32_t positions, uint32_t heads, uint32_t width, int adjacent,
+         cudaStream_t stream);
+size_t picked_workspace_bytes(uint32_t rows, uint32_t n, uint32_t k, uint32_t count);
+int picked(const void *x, const void *w, const uint32_t *ids, float *out, uint32_t rows, uint32_t n, uint32_t k,
+           uint32_t count, uint32_t stride, uint32_t offset, uint32_t repeat, uint32_t first, void *workspace,
+           size_t workspace_bytes, cudaStream_t stream);
 int moe_mix(const float *y_picks, const float *gates, const float *add, float *out, uint32_t rows, uint32_t top,
             uint32_t width, cudaStream_t stream);
 

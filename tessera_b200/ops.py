@@ -198,6 +198,21 @@ def rope_inv_freq(theta: float, width: int, device) -> torch.Tensor:
     return torch.tensor(list(buf), dtype=torch.float32, device=device)
 
 
+def rope_angles(positions, width: int, theta: float, turned: int | None = None) -> torch.Tensor:
+    """[count, width] f32: (cos, sin) per pair, the reference's `angles` launch (engine/rules/kernels/src/rope.rs:36-60)."""
+    out = torch.empty((positions.numel(), width), dtype=torch.float32, device=positions.device)
+    check(lib.ts_rope_angles(_ptr(positions), _ptr(out), positions.numel(), width, theta,
+                             width // 2 if turned is None else turned, _stream()))
+    return out
+
+
+def rope(x, freqs, heads: int, width: int, adjacent: bool = False):
+    """Rotates x [positions, heads, width] (f32 or bf16) in place by `freqs` (rope.rs:10-34)."""
+    positions = x.numel() // (heads * width)
+    check(lib.ts_rope(_ptr(x), _dtype_code(x.dtype), _ptr(freqs), positions, heads, width, int(adjacent), _stream()))
+    return x
+
+
 def qk_norm_rope_append(qkv, q_norm, k_norm, inv_freq, slots, positions, q_out, k_rows, v_rows, kept: Kept, heads,
                         kv_heads, width, eps):
     rows = qkv.shape[0]
@@ -292,6 +307,23 @@ def moe(h, ids, gates, w_in, w_out, *, add=None, first: int = 0):
     check(lib.ts_moe_bf16(_ptr(h), _ptr(ids), _ptr(gates), _ptr(add), _ptr(w_in), _ptr(w_out), _ptr(y), rows, top,
                           experts, first, hidden, two_f // 2, _ptr(ws), nbytes, _stream()))
     return y
+
+
+def picked(x, w, ids, n: int, *, count: int | None = None, stride: int | None = None, offset: int = 0, repeat: int = 1,
+           first: int = 0):
+    """out[i] = x[i // repeat] . w[(ids[i] - first) * stride + offset + (0..n)]^T, zeros for ids outside
+    [first, first + count): ts_picked_bf16 (engine/rules/linear/src/picked.rs:28-60).  w bf16 [matrices, stride, k]
+    or any row-major table of `count * stride` rows."""
+    k = x.shape[-1]
+    rows = ids.numel()
+    stride = stride if stride is not None else (w.shape[-2] if w.dim() == 3 else n)
+    count = count if count is not None else w.numel() // (stride * k)
+    out = torch.empty((rows, n), dtype=torch.float32, device=x.device)
+    nbytes = lib.ts_picked_workspace_bytes(rows, n, k, count)
+    ws = workspace(nbytes, x.device)
+    check(lib.ts_picked_bf16(_ptr(x), _ptr(w), _ptr(ids), _ptr(out), rows, n, k, count, stride, offset, repeat, first,
+                             _ptr(ws), nbytes, _stream()))
+    return out
 
 
 def moe_mix(y_picks, gates, add=None):

@@ -74,12 +74,42 @@ def _lane_norm(a, kw):
                         out=a["out"].reshape(rows, width))
 
 
+def _picked(a, kw):
+    from . import ops
+    rows, n, k = int(a["rows"]), int(a["n"]), int(a["k"])
+    if a["ids"].numel() != rows or a["out"].numel() != rows * n:
+        raise TypeError(f"picked: {a['ids'].numel()} ids and {a['out'].numel()} outputs, the launch says {rows} rows of {n}")
+    got = ops.picked(a["x"].reshape(-1, k), a["w"], a["ids"], n, count=int(a["count"]), stride=int(a["stride"]),
+                     offset=int(a["offset"]), repeat=int(a["repeat"]), first=int(a["first"]))
+    a["out"].reshape(rows, n).copy_(got)
+    return a["out"]
+
+
+def _angles(a, kw):
+    from . import ops
+    count, width = int(a["count"]), int(a["width"])
+    a["out"].reshape(count, width).copy_(ops.rope_angles(a["positions"], width, float(a["theta"]), int(a["turned"])))
+    return a["out"]
+
+
+def _rope(adjacent):
+    def run(a, kw):
+        from . import ops
+        return ops.rope(a["x"], a["freqs"], int(a["heads"]), int(a["width"]), adjacent)
+    return run
+
+
 _LINEAR_PARAMS = ("x", "w", "out", "n", "k")
 RULES = {r.name: r for r in (
     # The linear family shares one parameter list; m rides in the launch shape (lanes.rs:21-32, thin.rs, tiled.rs:295-304).
     Rule("lanes", _LINEAR_PARAMS, "engine/rules/linear/src/lanes.rs:21-32", _linear),
     Rule("thin", _LINEAR_PARAMS, "engine/rules/linear/src/thin.rs", _linear),
     Rule("tiled", _LINEAR_PARAMS, "engine/rules/linear/src/tiled.rs:295-304", _linear),
+    Rule("picked", ("x", "w", "ids", "out", "rows", "n", "k", "count", "stride", "offset", "repeat", "first"),
+         "engine/rules/linear/src/picked.rs:28-41", _picked),
+    Rule("angles", ("positions", "out", "count", "width", "theta", "turned"), "engine/rules/kernels/src/rope.rs:36-44", _angles),
+    Rule("rope", ("x", "freqs", "positions", "heads", "width"), "engine/rules/kernels/src/rope.rs:10-16", _rope(False)),
+    Rule("rope_adjacent", ("x", "freqs", "positions", "heads", "width"), "engine/rules/kernels/src/rope.rs:10-16", _rope(True)),
     Rule("attend_rows", ("q", "k", "v", "out", "slots", "positions", "rows", "keys", "heads", "kv_heads", "width", "back"),
          "engine/rules/attention/src/attend.rs:126-139", _attend_rows),
     Rule("scatter", ("x", "slots", "positions", "out", "rows", "width"), "engine/plan/lower/src/kernels/scatter.rs:12-19", _scatter),

@@ -49,18 +49,33 @@ def _margin(logits_row):
     return float(top2[1] - top2[0])
 
 
-def greedy(cfg, seed, prompt, new, context, stop_below=None):
-    """Returns (tokens, margins); stops early (None, margins) once one of the first 32 margins is too small."""
+def probe_ids(vocab, count=32, seed=11):
+    """The vocabulary ids whose logits the fixture records at every step (a fixed, seeded sample)."""
+    return np.sort(np.random.default_rng(seed).choice(vocab, size=count, replace=False)).astype(np.int64)
+
+
+def greedy(cfg, seed, prompt, new, context, stop_below=None, probes=None):
+    """Returns (tokens, margins); stops early (None, margins) once one of the first 32 margins is too small.
+    With `probes` (a dict), also records per step the winning logit and the logits at `probe_ids`."""
     dec = O.Decoder(dict(cfg, context=context, slots=1), oracle_weights(cfg, seed))
     n = len(prompt)
+    at = probe_ids(cfg["vocab"])
+
+    def note(row):
+        if probes is not None:
+            probes.setdefault("top", []).append(round(float(row.max()), 5))
+            probes.setdefault("at", []).append([round(float(v), 5) for v in row[at]])
+
     ids, logits, _ = dec.step(prompt, [0] * n, list(range(n)), want_logits=True)
     out, margins = [int(ids[-1])], [_margin(logits[-1])]
+    note(logits[-1])
     for t in range(1, new):
         if stop_below is not None and t <= 32 and margins[-1] < stop_below:
             return None, margins
         ids, logits, _ = dec.step([out[-1]], [0], [n + t - 1], want_logits=True)
         out.append(int(ids[0]))
         margins.append(_margin(logits[0]))
+        note(logits[0])
     return out, margins
 
 
@@ -70,21 +85,24 @@ if __name__ == "__main__":
     seeds = [int(a) for a in sys.argv[1:]] or list(range(8))
     t0 = time.time()
     for seed in seeds:
-        tokens, margins = greedy(cfg, seed, prompt.tolist(), 64, 192, stop_below=MIN_MARGIN)
+        probes = {}
+        tokens, margins = greedy(cfg, seed, prompt.tolist(), 64, 192, stop_below=MIN_MARGIN, probes=probes)
         print(f"seed {seed}: {'kept' if tokens else 'near tie at step %d' % (len(margins) - 1)}, "
               f"smallest margin {min(margins[:32]):.4g}, {time.time() - t0:.0f}s", flush=True)
         if tokens:
-            kept = (seed, tokens, margins)
+            kept = (seed, tokens, margins, probes)
             if len(set(tokens[:32])) >= MIN_DISTINCT:
                 break
             print(f"  only {len(set(tokens[:32]))} distinct ids", flush=True)
     if "kept" not in dir():
         raise SystemExit("no seed kept its margins")
-    seed, tokens, margins = kept
+    seed, tokens, margins, probes = kept
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "qwen3_0p6b_greedy.json")
     with open(path, "w") as f:
         json.dump({"config": cfg, "seed": seed, "prompt_seed": 0, "prompt_len": 128, "new": 64,
                    "prompt_head": prompt[:8].tolist(), "tokens": tokens, "min_margin": MIN_MARGIN,
-                   "margins": [round(m, 5) for m in margins], "numpy": np.__version__,
+                   "margins": [round(m, 5) for m in margins],
+                   "probe_ids": probe_ids(cfg["vocab"]).tolist(), "top_logit": probes["top"], "probe_logits": probes["at"],
+                   "numpy": np.__version__,
                    "seconds": round(time.time() - t0, 1)}, f, indent=1)
     print(path, tokens[:8], f"{time.time() - t0:.0f}s")

@@ -139,3 +139,32 @@ def test_qwen3_0p6b_greedy_tokens_match_golden():
     assert got[:32] == gold["tokens"][:32]
     same = sum(1 for a, b in zip(got, gold["tokens"]) if a == b)
     print(f"{same} of {len(got)} greedy ids equal the checker's")
+
+
+def test_qwen3_0p6b_logits_follow_golden():
+    """The same run step by step, fed the checker's ids (teacher forcing, so that a flipped id cannot hide
+    behind a later one): at each of the first 32 steps the winning logit and the logits at the fixture's
+    seeded sample of vocabulary ids stay within 1e-2 of the largest logit magnitude of the checker's."""
+    path = os.path.join(os.path.dirname(__file__), "golden", "qwen3_0p6b_greedy.json")
+    gold = json.load(open(path))
+    if "probe_logits" not in gold:
+        pytest.skip("fixture without logit probes")
+    cfg = gold["config"]
+    prompt = synth.prompt_tokens(cfg["vocab"], gold["prompt_len"], seed=gold["prompt_seed"])
+    at = np.array(gold["probe_ids"])
+    dec = _device(cfg, gold["seed"], slots=1, context=192, max_rows=128, gains="ones", page=64)
+    n = len(prompt)
+    worst = 0.0
+    for t in range(32):
+        if t == 0:
+            ids = dec.step(prompt, np.zeros(n), np.arange(n), out_rows=[n - 1])
+        else:
+            ids = dec.step([gold["tokens"][t - 1]], [0], [n + t - 1])
+        row = dec.read_logits(1)[0]
+        want_at, want_top = np.array(gold["probe_logits"][t]), gold["top_logit"][t]
+        scale = max(abs(want_top), float(np.abs(want_at).max()))
+        worst = max(worst, float(np.abs(row[at] - want_at).max()) / scale, abs(float(row.max()) - want_top) / scale)
+        assert int(ids[0]) == gold["tokens"][t], t
+    dec.close()
+    print(f"largest logit error over 32 steps: {worst:.2e} of the largest logit")
+    assert worst <= 1e-2

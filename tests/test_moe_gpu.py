@@ -124,3 +124,39 @@ def test_uneven_routing_many_rows_on_one_expert():
                              round_inner=True)
     got = widen(ops.moe(from_bits(h), dev_u32(ids), torch.from_numpy(gates).cuda(), from_bits(w_in), from_bits(w_out)))
     assert rel_error(got, want) <= 1e-2
+
+
+@pytest.mark.parametrize("rows,repeat,count,first,n,k", [(64, 4, 8, 0, 256, 128), (300, 1, 16, 4, 128, 192), (7, 7, 3, 0, 384, 64)])
+def test_picked_alone_matches_oracle(rows, repeat, count, first, n, k):
+    """The reference's `picked` launch (picked.rs:28-60): each row against the matrix its id names, the gate or
+    the up half of a fused table through stride / offset, zeros for ids this rank does not hold."""
+    from tessera_b200 import ops, rules
+    rng = np.random.default_rng(rows + n)
+    x = normal_bf16(rng, (rows // repeat, k))
+    table = normal_bf16(rng, (count, 2 * n, k), 0.05)          # two halves per matrix, as gate | up
+    ids = rng.integers(0, count + 2 * first, size=rows).astype(np.uint32)
+    xd, td, idd = from_bits(x), from_bits(table), dev_u32(ids)
+    for offset in (0, n):
+        want = O.matmul_picked(O.bf16_widen(x), O.bf16_widen(table)[:, offset:offset + n], ids, first)
+        got = ops.picked(xd, td, idd, n, count=count, stride=2 * n, offset=offset, repeat=repeat, first=first)
+        torch.cuda.synchronize()
+        assert ops.device_status() == 0
+        held = (ids >= first) & (ids - first < count)
+        assert not widen(got)[~held].any()                    # exactly zero, not small
+        assert rel_error(widen(got), want) <= 1e-2 and _cos(widen(got), want) > 0.9999
+        by_name = torch.full((rows, n), 7.0, dtype=torch.float32, device="cuda")
+        rules.launch_c("picked_bf16", [xd, td, idd, by_name, rows, n, k, count, 2 * n, offset, repeat, first])
+        assert torch.equal(by_name, got)                       # same kernels, same order: same bits
+
+
+def test_picked_refuses_what_it_cannot_tile():
+    from tessera_b200 import ops
+    from tessera_b200._lib import TesseraError
+    x = torch.zeros((4, 64), dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros((2, 100, 64), dtype=torch.bfloat16, device="cuda")
+    ids = dev_u32([0, 1, 0, 1])
+    with pytest.raises(TesseraError):
+        ops.picked(x, w, ids, 100)                             # n is not a multiple of 128
+    w = torch.zeros((2, 128, 64), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(TesseraError):
+        ops.picked(x, w, ids, 128, stride=64)                  # matrices would overlap

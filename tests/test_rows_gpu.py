@@ -195,3 +195,41 @@ def test_ts_launch_by_name():
     fo = torch.empty_like(fq)
     rules.launch_c("flash_128", [fq, fk, fv, fo, seq, seq, 0, heads, kv_heads, 0xFFFFFFFF, 0])
     assert torch.equal(fo, ops.attend(fq, fk, fv, mask="causal", scale=1.0))
+
+
+@pytest.mark.parametrize("width,heads,adjacent,turned", [(128, 4, False, None), (64, 3, True, None), (256, 2, False, 40), (6, 1, True, 2)])
+def test_rope_launches_match_oracle(width, heads, adjacent, turned):
+    """The reference's `angles` and `rope` / `rope_adjacent` launches (rope.rs:10-60) against the CPU interpreter's
+    rope (cpu.rs:31-47).  The rotation itself is exact in f32 given the angles; the device's sine and cosine may
+    differ from the host's in the last bits, which the tolerance covers."""
+    from tessera_b200 import ops, rules
+    rng = np.random.default_rng(width + heads)
+    count, theta = 9, 10000.0
+    positions = rng.integers(0, 4096, size=count).astype(np.uint32)
+    x = rng.standard_normal((count, heads, width)).astype(np.float32)
+    want = O.rope(x, positions, theta, pairs="adjacent" if adjacent else "halves", turned=turned)
+    freqs = ops.rope_angles(dev_u32(positions), width, theta, turned)
+    pairs = width // 2
+    upto = pairs if turned is None else min(turned, pairs)
+    f = widen(freqs).reshape(count, pairs, 2)
+    # The checker's cosines and sines: what its rope makes of the pair (1, 0).
+    a = np.arange(pairs) * 2 if adjacent else np.arange(pairs)
+    b = a + 1 if adjacent else a + pairs
+    unit = np.zeros((count, 1, width), np.float32)
+    unit[:, :, a] = 1.0
+    turned_unit = O.rope(unit, positions, theta, pairs="adjacent" if adjacent else "halves", turned=turned)[:, 0]
+    assert np.abs(f[:, :, 0] - turned_unit[:, a]).max() <= 1e-6 and np.abs(f[:, :, 1] - turned_unit[:, b]).max() <= 1e-6
+    assert (f[:, upto:, 0] == 1.0).all() and (f[:, upto:, 1] == 0.0).all()    # pairs past `turned` keep angle zero
+    got = ops.rope(torch.from_numpy(x).cuda(), freqs, heads, width, adjacent)
+    assert np.abs(widen(got) - want).max() <= 1e-5 * max(1.0, np.abs(want).max())
+    # by name, and in bf16
+    xb = torch.from_numpy(x).cuda()
+    fr = torch.empty_like(freqs)
+    rules.launch_c("angles", [dev_u32(positions), fr, count, width, theta, pairs if turned is None else turned])
+    assert torch.equal(fr, freqs)
+    rules.launch_c("rope_adjacent" if adjacent else "rope", [xb, fr, count, heads, width])
+    assert torch.equal(xb, got)
+    xh = torch.from_numpy(x).cuda().to(torch.bfloat16)
+    want_h = O.rope(widen(xh), positions, theta, pairs="adjacent" if adjacent else "halves", turned=turned)
+    ops.rope(xh, freqs, heads, width, adjacent)
+    assert rel_error(widen(xh), want_h) <= 1e-2

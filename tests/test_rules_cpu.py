@@ -9,6 +9,10 @@ def test_table_lists_the_reference_parameters():
     assert rules.RULES["scatter"].params == ("x", "slots", "positions", "out", "rows", "width")   # scatter.rs:12-19
     assert rules.RULES["top_k"].params == ("x", "out", "rows", "width", "k")   # argmax.rs:39
     assert rules.RULES["lane_norm"].params == ("x", "w", "out", "rows", "width", "eps")   # lane_norm.rs:10-17
+    assert rules.RULES["picked"].params == ("x", "w", "ids", "out", "rows", "n", "k", "count", "stride", "offset", "repeat",
+                                            "first")   # picked.rs:28-41
+    assert rules.RULES["angles"].params == ("positions", "out", "count", "width", "theta", "turned")   # rope.rs:36-44
+    assert rules.RULES["rope"].params == rules.RULES["rope_adjacent"].params == ("x", "freqs", "positions", "heads", "width")
     for name in ("lanes", "thin", "tiled"):
         assert rules.RULES[name].params == ("x", "w", "out", "n", "k")
     assert all(r.cites.startswith("engine/") for r in rules.RULES.values())
@@ -28,13 +32,14 @@ def test_c_table_lists_the_reference_kernel_names():
     table = rules.kernels()
     for name in ("lanes_bf16", "thin_bf16", "tiled_bf16", "parts_bf16", "attend_rows_dense", "attend_rows_paged",
                  "attend_rows_paged16", "flash_rows_paged", "scatter_dense", "scatter_paged16", "top_k", "lane_norm",
-                 "flash_128", "flash_256"):
+                 "flash_128", "flash_256", "picked_bf16", "angles", "rope", "rope_adjacent", "rope_bf16"):
         assert name in table
     # read buffers, output, [page table], then scalars; the layout's scalar last (rule.rs:62-109)
     assert table["attend_rows_dense"][0] == "pppppp" + "u" * 7
     assert table["attend_rows_paged"][0] == "ppppppp" + "u" * 7
     assert table["scatter_paged"][0] == "ppppp" + "uuu"
     assert table["lane_norm"][0] == "pppuuf"
+    assert table["picked_bf16"] == ("pppp" + "u" * 8, 1) and table["angles"][0] == "ppuufu" and table["rope"] == ("ppuuu", 0)
     assert table["top_k"] == ("ppuuu", 0) and table["scatter_dense"][1] == 0   # Order::Fixed
     assert table["tiled_bf16"][1] == 1 and table["flash_128"][1] == 1          # Order::PerConfig
 
