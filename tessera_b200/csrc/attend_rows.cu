@@ -57,6 +57,11 @@ struct RowsParams {
     const float *q_norm, *k_norm, *inv_freq;
     uint16_t *k_out, *v_out;
     float eps;
+    // With the fused front: the producer warp starts fetching key and value tiles without waiting for the
+    // upstream launch.  Only for callers whose kept rows below the rows' own positions, slots, positions and
+    // page table were all written two or more launches earlier in the stream (a launch starts only after
+    // its predecessor has seen its own predecessor complete); the rows' own keys never come from memory.
+    uint32_t early_keys;
 };
 
 __device__ __forceinline__ uint4 ldg16(const uint16_t *p) {
@@ -341,8 +346,10 @@ attend_rows_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         prefetch_tensormap(&map_v);
     }
     __syncthreads();
-    pdl_wait();  // q, the positions and the newest kept rows come from the upstream kernels
-    pdl_launch_dependents();
+    if (!(p.early_keys && warp == 0)) {
+        pdl_wait();  // q, the positions and the newest kept rows come from the upstream kernels
+        pdl_launch_dependents();
+    }
 
     if (warp == 0) {
         // ---- producer: one tile pair per 32-key block, in item order ----
@@ -667,8 +674,10 @@ attend_rows_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         prefetch_tensormap(&map_v);
     }
     __syncthreads();
-    pdl_wait();
-    pdl_launch_dependents();
+    if (!(p.early_keys && warp == 0)) {
+        pdl_wait();
+        pdl_launch_dependents();
+    }
 
     if (warp == 0) {
         // ---- producer: as in the scalar kernel, each tile as two 64-column halves ----
@@ -1072,6 +1081,7 @@ int attend_rows(const void *q, const void *k, const void *v, void *out, const ui
         p.k_norm = fused->k_norm;
         p.inv_freq = fused->inv_freq;
         p.eps = fused->eps;
+        p.early_keys = fused->early_keys ? 1 : 0;
         p.k_out = (uint16_t *)const_cast<void *>(k);
         p.v_out = (uint16_t *)const_cast<void *>(v);
     }

@@ -138,6 +138,14 @@ uint32_t fold_parts(const ts_decoder *d, uint32_t rows) {
 }
 
 // TS_FRESH_PROMPTS=0 sends whole prompts through the kept-row attention like any other launch (for A/B).
+bool early_keys_enabled() {
+    static const bool on = [] {
+        const char *e = getenv("TS_EARLY_KEYS");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+
 bool fresh_prompts_enabled() {
     static const bool off = [] {
         const char *v = getenv("TS_FRESH_PROMPTS");
@@ -245,6 +253,9 @@ int enqueue(ts_decoder *d, uint32_t rows, uint32_t keys, uint32_t n_out, bool fe
             f.k_norm = c.qk_norm ? L.k_norm : nullptr;
             f.inv_freq = d->inv_freq;
             f.eps = c.eps;
+            // This layer's kept rows were last written a whole step ago, the slots and positions before the
+            // step's first launch, and the upstream launch is this layer's q,k,v projection.
+            f.early_keys = early_keys_enabled();
             STEP("attend_rows", attend_rows(nullptr, L.k_rows, L.v_rows, d->attn, d->slots, d->positions, kd, contiguous, rows, keys,
                              c.heads, c.kv_heads, D, 0xFFFFFFFFu, scale, d->workspace, d->workspace_bytes, s, 0, nullptr,
                              d->kept_total_rows, &f));

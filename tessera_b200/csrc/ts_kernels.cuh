@@ -55,6 +55,9 @@ struct RowsFused {
     const void *qkv = nullptr;
     const float *q_norm = nullptr, *k_norm = nullptr, *inv_freq = nullptr;
     float eps = 0.0f;
+    // The kept rows, slots, positions and page table this launch reads were written two or more launches
+    // ago: key and value tiles may be fetched before the upstream launch has completed.
+    bool early_keys = false;
 };
 bool attend_rows_fused_supports(bool contiguous, uint32_t width, uint32_t kept_rows);
 int attend_rows(const void *q, const void *k, const void *v, void *out, const uint32_t *slots,

@@ -7,10 +7,17 @@ expert (engine/models/src/mla.rs:466-467).
 Expert parallel: rank r of g holds experts [r E/g, (r+1) E/g) - the reference's axis-0 split with its
 `first` / `count` (engine/plan/lower/src/sites/matmul.rs:64, engine/rules/linear/src/picked.rs:49-53) -
 and its own share of the token rows.  Where the reference lets every rank compute zeros for foreign
-picks and all-reduces, this module moves the picks: counts all-to-all, rows to the owning rank
-(NCCL all_to_all over NVLink), grouped expert kernels there, per-pick outputs back, gate-weighted sum
-at the source in pick order.  The exchange logic is device-agnostic (tested on CPU ranks over gloo with
-injected compute); the compute callbacks default to the CUDA kernels of this library.
+picks and all-reduces, this module has two schemes.  `dispatch` moves the picks: counts all-to-all, rows
+to the owning rank (NCCL all_to_all over NVLink), grouped expert kernels there, per-pick outputs back,
+gate-weighted sum at the source in pick order; its exchange sizes pass through the host, so it suits large
+launches (prefill), where each rank's picks are far fewer than the rows of all ranks.  `replicate` is the
+reference's scheme with the all-reduce split in two: all-gather the token rows, every rank routes all of
+them (the same kernels on the same bits: the same ids everywhere) and runs the whole routed block against
+its own experts with foreign picks contributing zeros, then a reduce-scatter sums the ranks' partial rows
+and leaves each rank its own.  Nothing passes through the host, so a decode step with it can be captured in
+a CUDA graph; with top-k >= ranks it moves no more bytes than dispatch.  The exchange logic is
+device-agnostic (tested on CPU ranks over gloo with injected compute); the compute callbacks default to
+the CUDA kernels of this library.
 """
 from __future__ import annotations
 
@@ -52,6 +59,11 @@ def _cuda_shared(h, w: MoeWeights):
     return ops.linear(inner, w.shared_out, out_dtype=torch.float32)
 
 
+def _cuda_local(h_all, ids, gates, w: MoeWeights):
+    from . import ops
+    return ops.moe(h_all, ids, gates, w.w_in, w.w_out, first=w.first)
+
+
 def _cuda_mix(y_picks, gates, add):
     from . import ops
     return ops.moe_mix(y_picks, gates, add)
@@ -69,7 +81,7 @@ class ExpertParallel:
     the rank that holds the experts; `mix_fn(y_picks [rows * top, H], gates, add) -> [rows, H]` at the source."""
 
     def __init__(self, group=None, experts_fn: Callable | None = None, route_fn: Callable | None = None,
-                 shared_fn: Callable | None = None, mix_fn: Callable | None = None):
+                 shared_fn: Callable | None = None, mix_fn: Callable | None = None, local_fn: Callable | None = None):
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -77,6 +89,7 @@ class ExpertParallel:
         self.route_fn = route_fn or _cuda_route
         self.shared_fn = shared_fn or _cuda_shared
         self.mix_fn = mix_fn or _cuda_mix
+        self.local_fn = local_fn or _cuda_local   # (h_all, ids, gates, w) -> [rows of all ranks, H] f32, this rank's experts only
 
     def plan(self, ids: torch.Tensor, experts_total: int):
         """Which rank owns each pick, the stable order that groups picks by owner, and per-owner counts."""
@@ -86,7 +99,28 @@ class ExpertParallel:
         counts = torch.bincount(owner, minlength=self.world)
         return order, counts
 
-    def forward(self, h, w: MoeWeights, top: int):
+    def forward_replicated(self, h, w: MoeWeights, top: int):
+        """all-gather rows -> route everywhere -> local experts on all rows -> reduce-scatter.  No host reads."""
+        rows, hidden = h.shape
+        h_all = torch.empty((self.world * rows, hidden), dtype=h.dtype, device=h.device)
+        dist.all_gather_into_tensor(h_all, h.contiguous(), group=self.group)
+        ids, gates = self.route_fn(h_all, w, top)
+        part = self.local_fn(h_all, ids, gates, w)
+        if dist.get_backend(self.group) == "gloo":      # no reduce-scatter there: all-reduce and keep this rank's rows
+            dist.all_reduce(part, group=self.group)
+            y = part[self.rank * rows:(self.rank + 1) * rows].clone()
+        else:
+            y = torch.empty((rows, hidden), dtype=part.dtype, device=part.device)
+            dist.reduce_scatter_tensor(y, part, group=self.group)
+        add = self.shared_fn(h, w)
+        if add is not None:
+            y += add
+        mine = slice(self.rank * rows, (self.rank + 1) * rows)
+        return y, ids[mine], gates[mine]
+
+    def forward(self, h, w: MoeWeights, top: int, scheme: str = "dispatch"):
+        if scheme == "replicate":
+            return self.forward_replicated(h, w, top)
         rows, hidden = h.shape
         ids, gates = self.route_fn(h, w, top)
         order, send_counts = self.plan(ids, w.experts_total)

@@ -24,8 +24,10 @@ def _bf16_normal(shape, std, gen, device):
 
 class MoeDecoder:
     def __init__(self, cfg: dict, slots: int, context: int, rank: int = 0, world: int = 1, seed: int = 0,
-                 group=None, device="cuda"):
+                 group=None, device="cuda", scheme: str = "replicate"):
         self.cfg, self.device, self.world, self.rank = dict(cfg), device, world, rank
+        self.scheme = scheme          # how picks meet their experts across ranks: see tessera_b200/moe.py
+        self._graphs: dict = {}       # (rows, keys) -> (graph, output); static inputs in self._static
         c = cfg
         h, d = c["hidden"], c["head_dim"]
         qw, kw = c["heads"] * d, c["kv_heads"] * d
@@ -81,6 +83,38 @@ class MoeDecoder:
             if self.ep is None:
                 y, _, _ = moe_forward(h, L["moe"], c["top"])
             else:
-                y, _, _ = self.ep.forward(h, L["moe"], c["top"])
+                y, _, _ = self.ep.forward(h, L["moe"], c["top"], scheme=self.scheme)
             x = x + y
         return x
+
+    def step_graphed(self, x: torch.Tensor, slots: torch.Tensor, positions: torch.Tensor, keys: int) -> torch.Tensor:
+        """`step` replayed from a CUDA graph per (rows, keys): a decode step is some hundred short launches and, across
+        ranks, two collectives per layer; replaying them removes the host's share of a step that takes about a
+        millisecond of device time per rank.  Needs a scheme with no host reads (`replicate`, or one rank).  The
+        returned tensor is overwritten by the next call with the same (rows, keys)."""
+        if self.ep is not None and self.scheme != "replicate":
+            return self.step(x, slots, positions, keys)
+        rows = x.shape[0]
+        st = self.__dict__.setdefault("_static", {})
+        if rows not in st:
+            st[rows] = (torch.empty_like(x), torch.empty_like(slots), torch.empty_like(positions))
+        gx, gs, gp = st[rows]
+        gx.copy_(x)
+        gs.copy_(slots)
+        gp.copy_(positions)
+        entry = self._graphs.get((rows, keys))
+        if entry is None:
+            cur = torch.cuda.current_stream()
+            side = torch.cuda.Stream()
+            side.wait_stream(cur)
+            with torch.cuda.stream(side):      # the launches once outside a capture: scratch buffers, attributes, communicators
+                for _ in range(2):
+                    self.step(gx.clone(), gs, gp, keys)
+            cur.wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                out = self.step(gx.clone(), gs, gp, keys)
+            entry = self._graphs[(rows, keys)] = (graph, out)
+        entry[0].replay()
+        return entry[1]

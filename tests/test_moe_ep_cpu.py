@@ -48,10 +48,16 @@ def _worker(rank, world, port, out):
         y = O.mean(y_picks.numpy().reshape(gates.shape[0], gates.shape[1], -1), 1, weights=gates.numpy())
         return torch.from_numpy(y)
 
-    ep = ExpertParallel(experts_fn=experts, route_fn=route, shared_fn=lambda h, mw: None, mix_fn=mix)
+    def local(h_all, ids, gates, mw):
+        # the whole routed block against this rank's experts: foreign picks contribute zeros (picked.rs:49-59)
+        per_pick = experts(torch.from_numpy(np.repeat(h_all.numpy(), TOP, axis=0)), ids.reshape(-1), mw)
+        return mix(per_pick, gates, None)
+
+    ep = ExpertParallel(experts_fn=experts, route_fn=route, shared_fn=lambda h, mw: None, mix_fn=mix, local_fn=local)
     h = torch.from_numpy(w["h"][rank * ROWS:(rank + 1) * ROWS])
     y, ids, gates = ep.forward(h, mw, TOP)
-    out[rank] = (y.numpy(), ids.numpy())
+    y2, ids2, _ = ep.forward(h, mw, TOP, scheme="replicate")
+    out[rank] = (y.numpy(), ids.numpy(), y2.numpy(), ids2.numpy())
     dist.destroy_process_group()
 
 
@@ -67,3 +73,8 @@ def test_two_ranks_reproduce_the_single_rank_block():
     ids = np.concatenate([out[0][1], out[1][1]])
     assert np.array_equal(ids.astype(np.uint32), want_ids)
     assert np.allclose(got, want, rtol=1e-6, atol=1e-7)
+    # the replicate scheme (all-gather rows, local experts with zeros for foreign picks, sum over ranks)
+    got2 = np.concatenate([out[0][2], out[1][2]])
+    ids2 = np.concatenate([out[0][3], out[1][3]])
+    assert np.array_equal(ids2.astype(np.uint32), want_ids)
+    assert np.allclose(got2, want, rtol=1e-5, atol=1e-6)

@@ -160,3 +160,66 @@ def test_picked_refuses_what_it_cannot_tile():
     w = torch.zeros((2, 128, 64), dtype=torch.bfloat16, device="cuda")
     with pytest.raises(TesseraError):
         ops.picked(x, w, ids, 128, stride=64)                  # matrices would overlap
+
+
+SMALL_MOE = dict(layers=2, hidden=256, heads=4, kv_heads=2, head_dim=128, experts=8, top=2, ffn=128, shared_ffn=128,
+                 eps=1e-6, theta=1e4)
+
+
+def _moe_decoder_want(dec, x, slots, positions, keys):
+    """One decode step of the MoE layer stack from the checker's ops, rounding to bf16 where the device stores bf16."""
+    c = dec.cfg
+    d, heads, kvh, eps = c["head_dim"], c["heads"], c["kv_heads"], c["eps"]
+    rows = x.shape[0]
+    table = u32(dec.table)
+    x = x.copy()
+    for i, L in enumerate(dec.layers):
+        h = O.bf16_round(O.rms_norm(x, widen(L["ln1"]), eps))
+        qkv = O.bf16_round(O.matmul(h, widen(L["wqkv"])))
+        q = qkv[:, :heads * d].reshape(rows, heads, d)
+        k = qkv[:, heads * d:(heads + kvh) * d].reshape(rows, kvh, d)
+        v = qkv[:, (heads + kvh) * d:].reshape(rows, kvh, d)
+        q = O.bf16_round(O.rope(O.rms_norm(q.reshape(-1, d), widen(L["q_norm"]), eps).reshape(rows, heads, d), positions, c["theta"]))
+        k = O.bf16_round(O.rope(O.rms_norm(k.reshape(-1, d), widen(L["k_norm"]), eps).reshape(rows, kvh, d), positions, c["theta"]))
+        # the slots' kept rows as a dense store, with this step's rows appended
+        kr, vr = widen(dec.k_rows[i]), widen(dec.v_rows[i])      # read before the device step appends
+        dense_k = np.zeros((dec.slots, keys, kvh, d), np.float32)
+        dense_v = np.zeros_like(dense_k)
+        for s in range(dec.slots):
+            for p in range(keys):
+                at = int(table[s * dec.pages + p // 64]) * 64 + p % 64
+                dense_k[s, p], dense_v[s, p] = kr[at], vr[at]
+        for r in range(rows):
+            dense_k[slots[r], positions[r]], dense_v[slots[r], positions[r]] = k[r], v[r]
+        a = O.bf16_round(O.attend_rows(q, dense_k, dense_v, slots, positions, scale=d ** -0.5))
+        x = x + O.matmul(a.reshape(rows, heads * d), widen(L["wo"]))
+        h = O.bf16_round(O.rms_norm(x, widen(L["ln2"]), eps))
+        m = L["moe"]
+        y, _, _ = O.moe_block(h, widen(m.router), widen(m.w_in), widen(m.w_out), c["top"], round_inner=True)
+        w_sh = widen(m.shared_in)
+        y = y + O.swiglu(h, w_sh[:c["shared_ffn"]], w_sh[c["shared_ffn"]:], widen(m.shared_out), round_inner=True)
+        x = x + y
+    return x
+
+
+def test_moe_decoder_step_matches_oracle_and_its_graph_replay():
+    """The GLM-style layer stack (decoder.rs:327-389 with the Moe feed-forward, decoder.rs:58-84) on one GPU: a decode
+    step over paged kept rows against the checker's composition, and the same step replayed from a CUDA graph."""
+    from tessera_b200.moe_decoder import MoeDecoder
+    rng = np.random.default_rng(12)
+    rows, context, keys = 6, 192, 128
+    dec = MoeDecoder(SMALL_MOE, slots=rows, context=context, seed=3)
+    dec.fill_kept(seed=4)
+    dec.set_table(rng.permutation(rows * dec.pages))
+    slots = np.arange(rows, dtype=np.uint32)
+    positions = np.array([5, 63, 64, 100, 0, 127], np.uint32)
+    x = rng.standard_normal((rows, SMALL_MOE["hidden"])).astype(np.float32)
+    want = _moe_decoder_want(dec, x, slots, positions, keys)
+    xd, sd, pd = torch.from_numpy(x).cuda(), dev_u32(slots), dev_u32(positions)
+    got = dec.step(xd.clone(), sd, pd, keys)
+    torch.cuda.synchronize()
+    assert rel_error(widen(got), want) <= 1e-2 and _cos(widen(got), want) > 0.9999
+    again = dec.step_graphed(xd, sd, pd, keys)          # appends the same rows again: same bits
+    assert torch.equal(again, got)
+    moved = dec.step_graphed(xd * 0.5, sd, pd, keys)     # replays the graph on new inputs
+    assert torch.equal(moved, dec.step((xd * 0.5).clone(), sd, pd, keys))
