@@ -514,6 +514,7 @@ def run_moe(args, rank, world, local_rank):
     seconds = _timed(resident, K, W, world)
     e2e_seconds = _timed(through_host, K, W, world)
     sampler.stop()
+    dec.close()   # graphs with captured collectives must go before the communicator does
     if world > 1:
         dist.destroy_process_group()
     if rank != 0:

@@ -56,6 +56,14 @@ class MoeDecoder:
         self.inv_freq = ops.rope_inv_freq(c["theta"], d, device)
         self.ep = ExpertParallel(group) if world > 1 else None
 
+    def close(self):
+        """Drops the captured graphs.  Call before torch.distributed.destroy_process_group(): a live graph that holds
+        captured collectives keeps the communicator busy and the teardown waits on it forever."""
+        torch.cuda.synchronize()
+        self._graphs.clear()
+        self.__dict__.pop("_static", None)
+        torch.cuda.synchronize()
+
     def set_table(self, table):
         self.table.copy_(torch.as_tensor(table, dtype=torch.int32, device=self.device))
 
