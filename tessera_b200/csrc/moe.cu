@@ -314,8 +314,43 @@ moe_grouped_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 __global__ void __launch_bounds__(256) moe_scatter_mix_kernel(const float *y, const uint32_t *place, const float *gates,
                                                               const float *add, float *out, uint32_t width,
                                                               uint32_t top, int mix) {
+    __shared__ uint32_t s_at[32];
+    __shared__ float s_gate[32];
     pdl_wait();
     const uint32_t r = blockIdx.x;
+    const bool vec = (((uintptr_t)y | (uintptr_t)out | (uintptr_t)add) & 15) == 0 && width % 4 == 0;
+    if (mix && top <= 32 && vec) {
+        // The row's picks once into shared memory, then 16-byte columns: the same products and sums, in pick
+        // order, as the scalar loop below.
+        if (threadIdx.x < top) {
+            s_at[threadIdx.x] = place ? place[r * top + threadIdx.x] : r * top + threadIdx.x;
+            s_gate[threadIdx.x] = gates[r * top + threadIdx.x];
+        }
+        __syncthreads();
+        for (uint32_t j = threadIdx.x * 4; j < width; j += blockDim.x * 4) {
+            float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            for (uint32_t t = 0; t < top; t++) {
+                const uint32_t at = s_at[t];
+                const float g = s_gate[t];
+                const float4 v = at == kNone ? make_float4(0.0f, 0.0f, 0.0f, 0.0f)
+                                             : *reinterpret_cast<const float4 *>(y + (size_t)at * width + j);
+                acc.x = __fadd_rn(acc.x, __fmul_rn(v.x, g));
+                acc.y = __fadd_rn(acc.y, __fmul_rn(v.y, g));
+                acc.z = __fadd_rn(acc.z, __fmul_rn(v.z, g));
+                acc.w = __fadd_rn(acc.w, __fmul_rn(v.w, g));
+            }
+            if (add) {
+                const float4 a = *reinterpret_cast<const float4 *>(add + (size_t)r * width + j);
+                acc.x = __fadd_rn(acc.x, a.x);
+                acc.y = __fadd_rn(acc.y, a.y);
+                acc.z = __fadd_rn(acc.z, a.z);
+                acc.w = __fadd_rn(acc.w, a.w);
+            }
+            *reinterpret_cast<float4 *>(out + (size_t)r * width + j) = acc;
+        }
+        pdl_launch_dependents();
+        return;
+    }
     for (uint32_t j = threadIdx.x; j < width; j += blockDim.x) {
         if (!mix) {
             const uint32_t at = place[r];

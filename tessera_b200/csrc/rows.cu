@@ -31,6 +31,36 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const TIn *x, const float
     const size_t base = (size_t)(row_ids ? row_ids[blockIdx.x] : blockIdx.x) * width;
     const size_t obase = (size_t)blockIdx.x * width;
     float ss = 0.0f;
+    if (width <= 16 * blockDim.x) {
+        // The row fits in registers (16 per thread): one read, all loads in flight at once; the sum of squares
+        // runs in the same order as the loop below, so both forms give the same bits.
+        float held[16];
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+            const uint32_t i = threadIdx.x + j * blockDim.x;
+            held[j] = 0.0f;
+            if (i < width) {
+                if constexpr (sizeof(TIn) == 4) held[j] = x[base + i];
+                else held[j] = __uint_as_float((uint32_t)x[base + i] << 16);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 16; j++)
+            if (threadIdx.x + j * blockDim.x < width) ss = fmaf(held[j], held[j], ss);
+        ss = block_sum(ss, scratch);
+        pdl_launch_dependents();
+        const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+            const uint32_t i = threadIdx.x + j * blockDim.x;
+            if (i < width) {
+                const float r = w ? held[j] * (inv * w[i]) : held[j] * inv;
+                if constexpr (sizeof(TOut) == 4) out[obase + i] = r;
+                else out[obase + i] = bf16_bits(r);
+            }
+        }
+        return;
+    }
     for (uint32_t i = threadIdx.x; i < width; i += blockDim.x) {
         float v;
         if constexpr (sizeof(TIn) == 4) v = x[base + i];
@@ -279,6 +309,50 @@ __global__ void __launch_bounds__(256) top_k_kernel(const TIn *x, uint32_t *ids,
             break;
         }
         __syncthreads();
+    }
+    pdl_launch_dependents();
+}
+
+// Narrow rows (router scores: a few hundred entries): a warp per row with the row in registers, no block
+// barriers.  The order is total (value, then index), so the picks are the same as the block kernel's.
+template <typename TIn>
+__global__ void __launch_bounds__(128) top_k_warp_kernel(const TIn *x, uint32_t *ids, uint32_t rows, uint32_t width,
+                                                         uint32_t k) {
+    pdl_wait();
+    const uint32_t row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row < rows) {
+        const size_t base = (size_t)row * width;
+        const uint32_t none = width;
+        float held[32];
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+            const uint32_t i = lane + 32 * j;
+            held[j] = i < width ? load_score(x, base + i) : -INFINITY;
+        }
+        Cand prev = {INFINITY, 0};
+        for (uint32_t round = 0; round < k; round++) {
+            Cand best = {0.0f, none};
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+                const uint32_t i = lane + 32 * j;
+                const float v = held[j];
+                if (!(v > -INFINITY)) continue;  // -inf and NaN never rank
+                if (round > 0 && !ranks_before(prev.v, prev.i, v, i)) continue;  // already taken
+                best = best_of(best, Cand{v, i}, none);
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                Cand other = {__shfl_xor_sync(0xFFFFFFFFu, best.v, o), __shfl_xor_sync(0xFFFFFFFFu, best.i, o)};
+                best = best_of(best, other, none);
+            }
+            if (lane == 0) ids[(size_t)row * k + round] = best.i;
+            prev = best;
+            if (best.i == none) {
+                if (lane == 0)
+                    for (uint32_t r2 = round + 1; r2 < k; r2++) ids[(size_t)row * k + r2] = none;  // spare slots hold the width
+                break;
+            }
+        }
     }
     pdl_launch_dependents();
 }
@@ -652,6 +726,15 @@ int top_k(const void *x, int x_dtype, uint32_t *ids, uint32_t rows, uint32_t wid
         e = launch(argmax_kernel, dim3(rows), dim3(32), 0, stream, pdl, (const float *)pv, (const uint32_t *)pi, ids,
                    width, kPeakParts);
         if (e != cudaSuccess) return fail(TS_ERR_CUDA, "launch of argmax failed: %s", cudaGetErrorString(e));
+        return TS_OK;
+    }
+    if (width <= 1024) {
+        const dim3 grid(ceil_div(rows, 4));
+        if (x_dtype == TS_F32)
+            e = launch(top_k_warp_kernel<float>, grid, dim3(128), 0, stream, pdl, (const float *)x, ids, rows, width, k);
+        else
+            e = launch(top_k_warp_kernel<uint16_t>, grid, dim3(128), 0, stream, pdl, (const uint16_t *)x, ids, rows, width, k);
+        if (e != cudaSuccess) return fail(TS_ERR_CUDA, "launch of top_k failed: %s", cudaGetErrorString(e));
         return TS_OK;
     }
     if (x_dtype == TS_F32)
