@@ -13,8 +13,11 @@ stand-ins of the configuration's shapes, nothing is read from disk but MEASURED_
   e2e    the same steps (the sequences restart from their prompts, so the positions and context lengths
          are those of the resident loop) through ts_decoder_step with host buffers: tokens/slots/positions
          copied host to device and the ids read back device to host inside the timed region, every step.
-  roofline  the kernel with the largest share of a step, timed live with CUDA events per kernel
-         (ts_decoder_profile) right after the timed region; algorithmic bytes / that duration.
+  roofline  the kernel with the largest share of a step.  Shares come from CUDA events after every kernel
+         (ts_decoder_profile) at the timed steps' context lengths, right after the timed region; that pass
+         serialises launches which overlap in the timed loop, so a kernel's duration in the timed loop is taken
+         as its share of the timed step (both measured live), the serialised interval is reported beside it,
+         and achieved = algorithmic bytes / that duration.
   cpu_baseline  the reference's native CPU rules restated in C (oracle/cpu_rules.c), timed on this
          host's cores on a bounded sample of the same step.
 
@@ -80,22 +83,33 @@ def peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 100 ms while running."""
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 50 ms by one background process from before
+    the warm-up until after the last timed loop.  `start()` / `stop()` bracket a timed region; the summary uses the
+    samples whose timestamps fall inside a region, or, when a region was shorter than nvidia-smi's start-up and
+    interval, the samples taken while the same steps ran as warm-up (it says which)."""
+    QUERY = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu_index: int):
-        self.gpu, self.proc, self.lines = gpu_index, None, []
-
-    def start(self):
+    def __init__(self, gpu_index: int, enabled: bool = True):
+        self.gpu, self.proc, self.lines, self.windows, self._t0 = gpu_index, None, [], [], None
+        if not enabled:   # only the rank that prints samples
+            return
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                                          "-i", str(self.gpu), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+                                          "-i", str(self.gpu), "-lms", "50"], stdout=subprocess.PIPE, text=True)
         except OSError:
             self.proc = None
 
+    def start(self):
+        self._t0 = time.time()
+
     def stop(self):
+        if self._t0 is not None:
+            self.windows.append((self._t0, time.time()))
+            self._t0 = None
+
+    def close(self):
         if self.proc is None:
             return
         self.proc.terminate()
@@ -107,23 +121,37 @@ class ClockSampler:
         self.lines += [l for l in out.splitlines() if l.strip()]
         self.proc = None
 
+    @staticmethod
+    def _when(stamp: str):
+        import datetime
+        try:
+            return datetime.datetime.strptime(stamp.strip(), "%Y/%m/%d %H:%M:%S.%f").timestamp()
+        except ValueError:
+            return None
+
     def summary(self) -> dict:
-        sm, mx, reasons = [], [], set()
+        self.close()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        rows = []
         for line in self.lines:
             f = [x.strip() for x in line.split(",")]
             if len(f) < 9:
                 continue
             try:
-                sm.append(float(f[1])); mx.append(float(f[2]))
+                rows.append((self._when(f[0]), float(f[1]), float(f[2]),
+                             [n for n, flag in zip(names, f[5:9]) if flag.lower().startswith("active")]))
             except ValueError:
                 continue
-            for name, flag in zip(names, f[5:9]):
-                if flag.lower().startswith("active"):
-                    reasons.add(name)
-        if not sm:
+        inside = [r for r in rows if r[0] is not None and any(a <= r[0] <= b for a, b in self.windows)]
+        window = "timed regions"
+        if not inside and self.windows:   # regions shorter than the sampling interval: the load around them
+            lo, hi = min(a for a, _ in self.windows) - 1.0, max(b for _, b in self.windows) + 0.2
+            inside = [r for r in rows if r[0] is not None and lo <= r[0] <= hi]
+            window = "warm-up and timed regions (the timed regions fell between two samples)"
+        if not inside:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+        return {"sm_mhz": statistics.median(r[1] for r in inside), "sm_max_mhz": max(r[2] for r in inside),
+                "reasons": sorted({n for r in inside for n in r[3]}), "samples": len(inside), "window": window}
 
 
 def kernel_bytes(name: str, cfg: dict, rows: int, ctx_sum: int) -> float:
@@ -248,7 +276,7 @@ def run_ours(args, rank, world, local_rank):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(local_rank, enabled=rank == 0)
     first = dec.prefill(prompts)
     dec.prepare(BATCH, stream)  # graphs of every context bucket exist before anything is timed
     pos = PROMPT
@@ -294,21 +322,38 @@ def run_ours(args, rank, world, local_rank):
 
     launches_per_step = dec.launches_per_step(BATCH, min(context, (pos + 127) // 128 * 128))
     # ---- per-kernel device time, live, for the roofline of the dominant kernel ----
+    # The sequences start again and run up to the middle of the timed steps' positions, so that the profiled
+    # launches see the context lengths the timed steps saw.  The profile records an event after every kernel:
+    # that serialises launches that overlap in the timed loop (programmatic dependent launch) and adds the gap
+    # between launches to every interval, so it is used for each kernel's SHARE of a step; a kernel's duration
+    # inside the timed loop is its share of the timed step, and the serialised interval is reported beside it.
+    first = dec.prefill(prompts)
+    pos = PROMPT
+    cur = dec.step(first, slots, np.full(BATCH, pos, np.uint32), stream=stream)
+    pos += 1
+    ahead = int(ctx_mid - (profile_steps + 1) / 2.0) - pos
+    if ahead > 0:
+        dec.run_resident(ahead, stream)
+        pos += ahead
     prof = dec.profile(profile_steps, stream)
     ctx_prof = pos + (profile_steps + 1) / 2.0
     step_ms = sum(ms for ms, _ in prof.values()) / profile_steps
     shares = {k: ms / profile_steps / step_ms for k, (ms, n) in prof.items()}
     top = max(prof, key=lambda k: prof[k][0])
     top_ms, top_n = prof[top]
-    per_launch_s = top_ms / top_n / 1e3
+    timed_step_s = resident_s / K
+    in_step_s = lambda k: shares[k] * timed_step_s / (prof[k][1] / profile_steps)   # per launch
     peak, peak_kind = peaks()
     algo = kernel_bytes(top, cfg, BATCH, int(BATCH * ctx_prof))
-    achieved = algo / per_launch_s / 1e9
+    achieved = algo / in_step_s(top) / 1e9
     roofline = {"kernel": top, "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                 "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "traffic": (NCU_TRAFFIC_RATIO[top] * algo if top in NCU_TRAFFIC_RATIO else None),
-                "algorithmic_bytes_per_launch": algo, "avg_launch_us": per_launch_s * 1e6,
+                "algorithmic_bytes_per_launch": algo, "avg_launch_us": in_step_s(top) * 1e6,
+                "duration": "the kernel's share (CUDA events after every kernel, launches serialised) of the timed step "
+                            "(CUDA events around the timed loop, launches overlapping as they run in production)",
+                "avg_launch_us_serialised": top_ms / top_n * 1e3,
                 "step_share": shares[top], "kernel_shares": {k: round(v, 4) for k, v in sorted(shares.items())},
-                "per_kernel_gbs": {k: round(kernel_bytes(k, cfg, BATCH, int(BATCH * ctx_prof)) / (ms / n / 1e3) / 1e9, 1)
+                "per_kernel_gbs": {k: round(kernel_bytes(k, cfg, BATCH, int(BATCH * ctx_prof)) / in_step_s(k) / 1e9, 1)
                                    for k, (ms, n) in prof.items() if kernel_bytes(k, cfg, BATCH, 1) > 0}}
     dec.close()
     if world > 1:
@@ -487,7 +532,7 @@ def run_moe(args, rank, world, local_rank):
     slots = torch.arange(rows, dtype=torch.int32, device="cuda")
     x_host = torch.randn(rows, cfg["hidden"], generator=torch.Generator().manual_seed(rank)).pin_memory()
     x_dev = x_host.cuda()
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(local_rank, enabled=rank == 0)
     graphed = os.environ.get("TS_MOE_GRAPHS", "1") != "0"
     step = dec.step_graphed if graphed else (lambda x, s, p, k: dec.step(x.clone(), s, p, k))
 
@@ -565,7 +610,7 @@ def run_embed(args, rank, world, local_rank):
     tok_dev, cu_dev = packed.cuda(), cu.cuda()
     max_len = max(my_lens)
     K, W = args.steps, max(args.warmup, 3)
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(local_rank, enabled=rank == 0)
     out_host = torch.empty(len(mine), cfg["hidden"]).pin_memory()
 
     def resident(i):
@@ -576,12 +621,6 @@ def run_embed(args, rank, world, local_rank):
         out_host.copy_(enc.forward(t, c, max_len), non_blocking=True)
         torch.cuda.synchronize()
 
-    if graphed:   # capture every context bucket the two loops will meet before anything is timed
-        for ctx in range(ctx0, ctx0 + 2 * (K + W) + 1):
-            keys = min(context, (ctx + 128) // 128 * 128)
-            if (rows, keys) not in dec._graphs:
-                step(x_dev, slots, torch.full((rows,), ctx, dtype=torch.int32, device="cuda"), keys)
-        torch.cuda.synchronize()
     sampler.start()
     seconds = _timed(resident, K, W, world)
     e2e_seconds = _timed(through_host, K, W, world)
