@@ -15,9 +15,10 @@ stand-ins of the configuration's shapes, nothing is read from disk but MEASURED_
          copied host to device and the ids read back device to host inside the timed region, every step.
   roofline  the kernel with the largest share of a step.  Shares come from CUDA events after every kernel
          (ts_decoder_profile) at the timed steps' context lengths, right after the timed region; that pass
-         serialises launches which overlap in the timed loop, so a kernel's duration in the timed loop is taken
-         as its share of the timed step (both measured live), the serialised interval is reported beside it,
-         and achieved = algorithmic bytes / that duration.
+         serialises launches which overlap in the timed loop and adds a launch gap to every interval, so a
+         kernel's duration in the timed loop is taken as its serialised interval less the average gap
+         ((serialised step - timed step) / launches per step, all measured live); the serialised interval is
+         reported beside it, and achieved = algorithmic bytes / that duration.
   cpu_baseline  the reference's native CPU rules restated in C (oracle/cpu_rules.c), timed on this
          host's cores on a bounded sample of the same step.
 
@@ -66,6 +67,9 @@ def parse_args():
                     help="decode: the headline Qwen3-0.6B-shaped decode (default); moe: GLM-style MoE decode, batch 256 at "
                          "context 2048, expert-parallel over the ranks; embed: 1024 ragged texts through the "
                          "EmbeddingGemma-300M-shaped encoder, data-parallel over the ranks")
+    ap.add_argument("--one-rank-of", type=int, default=0,
+                    help="with --workload moe on one GPU: run rank 0's share of an N-rank expert-parallel step with local "
+                         "copies in place of the collectives (for ncu, which cannot wrap a multi-rank command)")
     ap.add_argument("--case", default=None,
                     help="time one kernel of the step list alone at the benchmark's shapes (attend_rows, linear_qkv, "
                          "linear_o, linear_gate_up, linear_down, linear_unembed); used for ncu captures")
@@ -325,8 +329,9 @@ def run_ours(args, rank, world, local_rank):
     # The sequences start again and run up to the middle of the timed steps' positions, so that the profiled
     # launches see the context lengths the timed steps saw.  The profile records an event after every kernel:
     # that serialises launches that overlap in the timed loop (programmatic dependent launch) and adds the gap
-    # between launches to every interval, so it is used for each kernel's SHARE of a step; a kernel's duration
-    # inside the timed loop is its share of the timed step, and the serialised interval is reported beside it.
+    # between launches to every interval.  The serialised step is longer than the timed step by that gap times the
+    # launches of a step: a kernel's duration inside the timed loop is taken as its serialised interval less the
+    # average gap, and the serialised interval is reported beside it.
     first = dec.prefill(prompts)
     pos = PROMPT
     cur = dec.step(first, slots, np.full(BATCH, pos, np.uint32), stream=stream)
@@ -342,15 +347,21 @@ def run_ours(args, rank, world, local_rank):
     top = max(prof, key=lambda k: prof[k][0])
     top_ms, top_n = prof[top]
     timed_step_s = resident_s / K
-    in_step_s = lambda k: shares[k] * timed_step_s / (prof[k][1] / profile_steps)   # per launch
+    launches = sum(n for _, n in prof.values()) / profile_steps
+    gap_s = max(0.0, step_ms / 1e3 - timed_step_s) / launches   # what serialising adds to every launch, on average
+
+    def in_step_s(k):   # per launch: the serialised interval less the average gap
+        serial = prof[k][0] / prof[k][1] / 1e3
+        return max(serial - gap_s, 0.3 * serial)
     peak, peak_kind = peaks()
     algo = kernel_bytes(top, cfg, BATCH, int(BATCH * ctx_prof))
     achieved = algo / in_step_s(top) / 1e9
     roofline = {"kernel": top, "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                 "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "traffic": (NCU_TRAFFIC_RATIO[top] * algo if top in NCU_TRAFFIC_RATIO else None),
                 "algorithmic_bytes_per_launch": algo, "avg_launch_us": in_step_s(top) * 1e6,
-                "duration": "the kernel's share (CUDA events after every kernel, launches serialised) of the timed step "
-                            "(CUDA events around the timed loop, launches overlapping as they run in production)",
+                "duration": "interval between CUDA events recorded after every kernel (launches serialised), less the "
+                            "average gap serialising adds per launch = (serialised step - timed step) / launches per step",
+                "serialising_gap_us": gap_s * 1e6,
                 "avg_launch_us_serialised": top_ms / top_n * 1e3,
                 "step_share": shares[top], "kernel_shares": {k: round(v, 4) for k, v in sorted(shares.items())},
                 "per_kernel_gbs": {k: round(kernel_bytes(k, cfg, BATCH, int(BATCH * ctx_prof)) / in_step_s(k) / 1e9, 1)
@@ -520,13 +531,17 @@ def run_moe(args, rank, world, local_rank):
     import torch
     import torch.distributed as dist
     from tessera_b200.moe_decoder import GLM_MOE, MoeDecoder
-    _dist_setup(local_rank, world)
+    alone = args.one_rank_of > 1    # one rank's kernels on one GPU, collectives replaced by local copies
+    if alone:
+        world = args.one_rank_of
+    else:
+        _dist_setup(local_rank, world)
     cfg = GLM_MOE
     batch, ctx0 = 256, 2048
     rows = batch // world
     K, W = args.steps, max(args.warmup, 3)
     context = ctx0 + 2 * (K + W) + 64
-    dec = MoeDecoder(cfg, slots=rows, context=context, rank=rank, world=world, seed=0)
+    dec = MoeDecoder(cfg, slots=rows, context=context, rank=rank, world=world, seed=0, alone=alone)
     dec.fill_kept(seed=1 + rank)
     dec.set_table(np.random.default_rng(7 + rank).permutation(rows * dec.pages))
     slots = torch.arange(rows, dtype=torch.int32, device="cuda")
@@ -556,11 +571,11 @@ def run_moe(args, rank, world, local_rank):
                 step(x_dev, slots, torch.full((rows,), ctx, dtype=torch.int32, device="cuda"), keys)
         torch.cuda.synchronize()
     sampler.start()
-    seconds = _timed(resident, K, W, world)
-    e2e_seconds = _timed(through_host, K, W, world)
+    seconds = _timed(resident, K, W, 1 if alone else world)
+    e2e_seconds = _timed(through_host, K, W, 1 if alone else world)
     sampler.stop()
     dec.close()   # graphs with captured collectives must go before the communicator does
-    if world > 1:
+    if world > 1 and not alone:
         dist.destroy_process_group()
     if rank != 0:
         return
@@ -573,14 +588,17 @@ def run_moe(args, rank, world, local_rank):
     kv_bytes = cfg["layers"] * rows * ctx0 * cfg["kv_heads"] * cfg["head_dim"] * 4.0
     step_bytes = expert_bytes + dense_bytes + kv_bytes
     print(json.dumps({
-        "metric": "moe_decode_tokens_per_s", "value": batch * K / seconds, "unit": "tokens/s", "n_gpus": world, "steps": K,
+        "metric": "moe_decode_tokens_per_s" + ("_one_rank_alone" if alone else ""), "value": batch * K / seconds,
+        "unit": "tokens/s", "n_gpus": 1 if alone else world, "steps": K,
         "warmup": W, "ms_per_step": seconds / K * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (seeded weights, kept rows filled with N(0,1), residual rows N(0,1))",
         "config": {"workload": "GLM-style MoE decoder: 8 layers, hidden 4096, 32q/8kv heads x 128, 128 experts top-8 "
                                "softmax + 1 shared expert, ffn 1536; decode batch 256 at context 2048, paged kept rows",
                    "parallelism": f"ep{world}: {per} experts and {rows} token rows per GPU; rows all-gathered, every rank runs its "
                                   "experts on all rows, outputs reduce-scattered (the reference's zero-fill scheme, no host "
-                                  "reads)" + ("; step replayed from a CUDA graph" if graphed else ""),
+                                  "reads)" + ("; step replayed from a CUDA graph" if graphed else "")
+                                  + ("; ONE rank's kernels alone on one GPU, collectives replaced by local copies: a "
+                                     "profiling aid, not a throughput" if alone else ""),
                    "l2": "expert weights per step exceed the 126 MB L2"},
         "e2e": {"value": batch * K / e2e_seconds, "unit": "tokens/s", "h2d_bytes_per_step": rows * cfg["hidden"] * 4,
                 "d2h_bytes_per_step": rows * cfg["hidden"] * 4, "ms_per_step": e2e_seconds / K * 1e3},

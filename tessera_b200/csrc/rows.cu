@@ -315,7 +315,7 @@ __global__ void __launch_bounds__(256) top_k_kernel(const TIn *x, uint32_t *ids,
 
 // Narrow rows (router scores: a few hundred entries): a warp per row with the row in registers, no block
 // barriers.  The order is total (value, then index), so the picks are the same as the block kernel's.
-template <typename TIn>
+template <typename TIn, int PER>  // PER entries per lane: width <= 32 * PER
 __global__ void __launch_bounds__(128) top_k_warp_kernel(const TIn *x, uint32_t *ids, uint32_t rows, uint32_t width,
                                                          uint32_t k) {
     pdl_wait();
@@ -323,9 +323,9 @@ __global__ void __launch_bounds__(128) top_k_warp_kernel(const TIn *x, uint32_t 
     if (row < rows) {
         const size_t base = (size_t)row * width;
         const uint32_t none = width;
-        float held[32];
+        float held[PER];
 #pragma unroll
-        for (int j = 0; j < 32; j++) {
+        for (int j = 0; j < PER; j++) {
             const uint32_t i = lane + 32 * j;
             held[j] = i < width ? load_score(x, base + i) : -INFINITY;
         }
@@ -333,7 +333,7 @@ __global__ void __launch_bounds__(128) top_k_warp_kernel(const TIn *x, uint32_t 
         for (uint32_t round = 0; round < k; round++) {
             Cand best = {0.0f, none};
 #pragma unroll
-            for (int j = 0; j < 32; j++) {
+            for (int j = 0; j < PER; j++) {
                 const uint32_t i = lane + 32 * j;
                 const float v = held[j];
                 if (!(v > -INFINITY)) continue;  // -inf and NaN never rank
@@ -730,10 +730,12 @@ int top_k(const void *x, int x_dtype, uint32_t *ids, uint32_t rows, uint32_t wid
     }
     if (width <= 1024) {
         const dim3 grid(ceil_div(rows, 4));
+#define TS_TOPK_WARP(T, PER) launch(top_k_warp_kernel<T, PER>, grid, dim3(128), 0, stream, pdl, (const T *)x, ids, rows, width, k)
         if (x_dtype == TS_F32)
-            e = launch(top_k_warp_kernel<float>, grid, dim3(128), 0, stream, pdl, (const float *)x, ids, rows, width, k);
+            e = width <= 128 ? TS_TOPK_WARP(float, 4) : width <= 256 ? TS_TOPK_WARP(float, 8) : TS_TOPK_WARP(float, 32);
         else
-            e = launch(top_k_warp_kernel<uint16_t>, grid, dim3(128), 0, stream, pdl, (const uint16_t *)x, ids, rows, width, k);
+            e = width <= 128 ? TS_TOPK_WARP(uint16_t, 4) : width <= 256 ? TS_TOPK_WARP(uint16_t, 8) : TS_TOPK_WARP(uint16_t, 32);
+#undef TS_TOPK_WARP
         if (e != cudaSuccess) return fail(TS_ERR_CUDA, "launch of top_k failed: %s", cudaGetErrorString(e));
         return TS_OK;
     }

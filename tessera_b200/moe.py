@@ -142,3 +142,27 @@ class ExpertParallel:
         y_picks = torch.empty_like(y_back)
         y_picks[order] = y_back                           # back to pick order
         return self.mix_fn(y_picks, gates, self.shared_fn(h, w)), ids, gates
+
+
+class OneRankOfMany(ExpertParallel):
+    """One rank's share of an expert-parallel step with no peers: the all-gather is `world` copies of this rank's
+    rows and the reduce-scatter keeps this rank's slice of its own partial sums.  The kernels, their shapes and
+    their order are those of rank `rank` of `world` (the values are not): for timing and profiling one rank's
+    launches on one GPU, where a profiler cannot wrap a multi-rank command."""
+
+    def __init__(self, world: int, rank: int = 0):
+        self.group, self.world, self.rank = None, world, rank
+        self.experts_fn, self.route_fn, self.shared_fn = _cuda_experts, _cuda_route, _cuda_shared
+        self.mix_fn, self.local_fn = _cuda_mix, _cuda_local
+
+    def forward(self, h, w: MoeWeights, top: int, scheme: str = "replicate"):
+        rows = h.shape[0]
+        h_all = h.repeat(self.world, 1)
+        ids, gates = self.route_fn(h_all, w, top)
+        part = self.local_fn(h_all, ids, gates, w)
+        mine = slice(self.rank * rows, (self.rank + 1) * rows)
+        y = part[mine].clone()
+        add = self.shared_fn(h, w)
+        if add is not None:
+            y += add
+        return y, ids[mine], gates[mine]

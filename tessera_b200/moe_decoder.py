@@ -12,7 +12,7 @@ from __future__ import annotations
 import torch
 
 from . import ops
-from .moe import ExpertParallel, MoeWeights, moe_forward
+from .moe import ExpertParallel, MoeWeights, OneRankOfMany, moe_forward
 
 GLM_MOE = dict(layers=8, hidden=4096, heads=32, kv_heads=8, head_dim=128, experts=128, top=8, ffn=1536,
                shared_ffn=1536, eps=1e-6, theta=1e6)
@@ -24,7 +24,7 @@ def _bf16_normal(shape, std, gen, device):
 
 class MoeDecoder:
     def __init__(self, cfg: dict, slots: int, context: int, rank: int = 0, world: int = 1, seed: int = 0,
-                 group=None, device="cuda", scheme: str = "replicate"):
+                 group=None, device="cuda", scheme: str = "replicate", alone: bool = False):
         self.cfg, self.device, self.world, self.rank = dict(cfg), device, world, rank
         self.scheme = scheme          # how picks meet their experts across ranks: see tessera_b200/moe.py
         self._graphs: dict = {}       # (rows, keys) -> (graph, output); static inputs in self._static
@@ -54,7 +54,8 @@ class MoeDecoder:
         self.v_rows = [torch.zeros_like(k) for k in self.k_rows]
         self.table = torch.arange(slots * self.pages, dtype=torch.int32, device=device)
         self.inv_freq = ops.rope_inv_freq(c["theta"], d, device)
-        self.ep = ExpertParallel(group) if world > 1 else None
+        # alone: this rank's kernels with stand-ins for the collectives (see moe.OneRankOfMany)
+        self.ep = (OneRankOfMany(world, rank) if alone else ExpertParallel(group)) if world > 1 else None
 
     def close(self):
         """Drops the captured graphs.  Call before torch.distributed.destroy_process_group(): a live graph that holds
