@@ -439,9 +439,16 @@ bool plan_umma(uint32_t m, uint32_t n, uint32_t k, int epilogue, UmmaPlan *out) 
         s.tiles_i = ceil_div(m, kBlockA);
         s.tiles_j = gated ? (n / 2) / (s.bn / 2) : ceil_div(n, s.bn);
         s.b_resident = false;
-        s.splits = 1;
-        s.kb_per_split = kb;
-        s.to_partial = false;
+        // A handful of output tiles (a router: a few hundred rows against a hundred experts) would run their
+        // whole k loop on as many SMs: split k over blocks until about half the machine is busy, at least four
+        // k blocks a slice; the slices meet in the reduce kernel, in ascending order.
+        uint32_t splits = 1;
+        if (!gated)
+            while (kb % (splits * 2) == 0 && kb / (splits * 2) >= 4 && s.tiles_i * s.tiles_j * splits * 2 <= sms / 2)
+                splits *= 2;
+        s.splits = splits;
+        s.kb_per_split = kb / splits;
+        s.to_partial = splits > 1;
         uint32_t stages = 8;
         while (stages > 2 && smem_layout(s.bn, stages, stages).total > kSmemBudget) stages--;
         s.stages = stages;

@@ -399,10 +399,10 @@ int ts_decoder_create(const ts_decoder_config *config, ts_decoder **out) {
     A(dev_alloc(d, &d->inv_freq, c.head_dim / 2));
     // One workspace for every step: the largest any of them asks for at max_rows.
     size_t ws = 0;
-    for (uint32_t rows : {1u, 8u, 16u, 32u, 64u, 128u, c.max_rows, d->max_out}) {
+    std::vector<uint32_t> row_counts = {1u, 8u, 16u, 32u, 64u, 128u, c.max_rows, d->max_out};
+    for (uint32_t rows = 129; rows < 512 && rows <= c.max_rows; rows++) row_counts.push_back(rows);  // tiled kernel, k split by tile count
+    for (uint32_t rows : row_counts) {
         if (rows > c.max_rows) continue;
-        const bool g = true;
-        (void)g;
         auto need = [&](uint32_t n, uint32_t k, int epi) { return linear_workspace(rows, n, k, epi); };
         ws = max_size(ws, need(d->qkv_n, c.hidden, TS_EPI_NONE));
         ws = max_size(ws, need(c.hidden, c.heads * c.head_dim, TS_EPI_ADD));

@@ -36,7 +36,8 @@ def _run(x_bits, w_bits, path, **kw):
 SKINNY = [(1, 2048, 1024), (5, 1024, 1024), (16, 1024, 2048), (33, 6144, 1024), (64, 1024, 3072),
           (64, 2048, 1024), (7, 1000, 512), (64, 72, 256)]
 UMMA = [(1, 2048, 1024), (16, 1024, 2048), (64, 1024, 3072), (64, 6144, 1024), (100, 2048, 1024),
-        (128, 1024, 1024), (200, 512, 1024), (384, 1024, 512), (1024, 640, 256), (129, 200, 64)]
+        (128, 1024, 1024), (200, 512, 1024), (384, 1024, 512), (1024, 640, 256), (129, 200, 64),
+        (256, 128, 4096), (300, 100, 2048)]   # a router's shape: two tiles, k split sixteen ways over blocks
 
 
 STREAM = [(1, 2048, 1024), (16, 1024, 2048), (64, 1024, 3072), (64, 6144, 1024), (100, 2048, 1024),
@@ -97,6 +98,18 @@ def test_residual_add_epilogue(path, m):
     want = O.matmul(O.bf16_widen(x), w) + res
     got = widen(_run(x, w, path, a0=torch.from_numpy(res).cuda(), epilogue="add", out_dtype=torch.float32))
     assert rel_error(got, want) <= F32_TOL
+
+
+def test_few_tiles_split_k_with_residual():
+    # m > 128 with a handful of output tiles: k slices meet in the reduce kernel, which adds the residual
+    m, n, k = 256, 128, 2048
+    x, w = _case(m, n, k, seed=77)
+    res = np.random.default_rng(78).standard_normal((m, n), dtype=np.float32)
+    want = O.matmul(O.bf16_widen(x), w) + res
+    got = widen(_run(x, w, "umma", a0=torch.from_numpy(res).cuda(), epilogue="add", out_dtype=torch.float32))
+    assert rel_error(got, want) <= F32_TOL
+    again = widen(_run(x, w, "umma", a0=torch.from_numpy(res).cuda(), epilogue="add", out_dtype=torch.float32))
+    assert np.array_equal(got, again)     # slices add in a fixed order
 
 
 @pytest.mark.parametrize("path,m", [("skinny", 4), ("skinny", 64), ("umma", 64), ("umma", 256), ("stream", 4),
@@ -240,8 +253,9 @@ def test_pair_epilogues():
 
 
 def test_pair_equals_one_sm_tiles_bit_for_bit():
-    # same k order inside the tensor core: the two tilings give the same f32 sums
-    x, w = _case(1024, 1024, 512, seed=4)
+    # same k order inside the tensor core: the two tilings give the same f32 sums (64 one-SM tiles: enough
+    # of them that the one-SM kernel keeps its k loop whole)
+    x, w = _case(1024, 2048, 512, seed=4)
     a = _run(x, w, "pair", out_dtype=torch.float32)
     b = _run(x, w, "umma", out_dtype=torch.float32)
     assert torch.equal(a, b)
