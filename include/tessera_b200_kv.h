@@ -81,6 +81,47 @@ int ts_kv_fill_table(const ts_kv_pool *pool, ts_kv_run run, uint32_t *table, uin
 int ts_kv_copy_pages(void *kept_rows, const ts_kv_copy *copies, uint32_t n_copies, uint32_t page_rows,
                      size_t row_bytes, void *stream);
 
+/* ---------------------------------------------------------------------------
+ * Prefix reuse: which rows of a prompt the kept rows of an earlier run spare.
+ * Restates engine/ir/kv/src/reuse.rs:1-37 (`begin`) and engine/ir/kv/src/prefix.rs:1-55 (`Prefixes`).
+ * ------------------------------------------------------------------------- */
+
+/* reuse.rs:3-14: why a prompt skips the rows it does. */
+typedef enum {
+    TS_KV_WHY_FIRST = 0,   /* there is no history */
+    TS_KV_WHY_NO_LCP = 1,  /* no common row is both valid and within the limit */
+    TS_KV_WHY_GRID = 2,    /* the common rows end below one grid step */
+    TS_KV_WHY_HIT = 3
+} ts_kv_why;
+
+/* reuse.rs:16-22. */
+typedef struct {
+    uint64_t skip, lcp;
+    int why;
+} ts_kv_begin;
+
+/* reuse.rs:24-37: lcp = the common prefix of history and prompt; rows = min(lcp, valid, limit); skip = rows
+ * rounded down to a whole number of `grid` steps (grid 0 counts as 1). */
+void ts_kv_begin_rows(const uint32_t *history, uint64_t history_len, uint64_t valid, const uint32_t *prompt,
+                      uint64_t prompt_len, uint64_t limit, uint64_t grid, ts_kv_begin *out);
+
+/* prefix.rs:11-55: the tokens behind retained runs, oldest first. */
+typedef struct ts_kv_prefixes ts_kv_prefixes;
+ts_kv_prefixes *ts_kv_prefixes_new(uint64_t grid);
+void ts_kv_prefixes_free(ts_kv_prefixes *prefixes);
+
+/* Records the tokens behind a retained run's `valid` rows (the tokens are copied). */
+int ts_kv_prefixes_keep(ts_kv_prefixes *prefixes, ts_kv_run run, const uint32_t *history, uint64_t history_len,
+                        uint64_t valid);
+
+/* The newest run of `tag` with the longest skip for `prompt`: first drops entries whose run the pool no longer
+ * knows, then *found = 1 with the run and its skip, or *found = 0 when no entry spares a row. */
+int ts_kv_prefixes_find(ts_kv_prefixes *prefixes, const ts_kv_pool *pool, uint64_t tag, const uint32_t *prompt,
+                        uint64_t prompt_len, uint64_t limit, ts_kv_run *run, uint64_t *skip, int *found);
+
+/* Entries held (after the last find's clean-up). */
+uint64_t ts_kv_prefixes_len(const ts_kv_prefixes *prefixes);
+
 #ifdef __cplusplus
 }
 #endif

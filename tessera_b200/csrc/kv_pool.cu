@@ -385,5 +385,77 @@ int ts_kv_copy_pages(void *kept_rows, const ts_kv_copy *copies, uint32_t n_copie
     return TS_KV_OK;
 }
 
+// ---- prefix reuse (engine/ir/kv/src/reuse.rs, prefix.rs): host arithmetic on token ids ----
+void ts_kv_begin_rows(const uint32_t *history, uint64_t history_len, uint64_t valid, const uint32_t *prompt,
+                      uint64_t prompt_len, uint64_t limit, uint64_t grid, ts_kv_begin *out) {
+    if (!out) return;
+    uint64_t lcp = 0;
+    const uint64_t both = history_len < prompt_len ? history_len : prompt_len;
+    while (lcp < both && history[lcp] == prompt[lcp]) lcp++;
+    uint64_t rows = lcp < valid ? lcp : valid;
+    if (limit < rows) rows = limit;
+    const uint64_t step = grid > 0 ? grid : 1;
+    out->skip = rows / step * step;
+    out->lcp = lcp;
+    out->why = history_len == 0 ? TS_KV_WHY_FIRST : rows == 0 ? TS_KV_WHY_NO_LCP : out->skip == 0 ? TS_KV_WHY_GRID : TS_KV_WHY_HIT;
+}
+
+struct ts_kv_prefixes {
+    struct Entry {
+        ts_kv_run run;
+        std::vector<uint32_t> history;
+        uint64_t valid;
+    };
+    uint64_t grid;
+    std::vector<Entry> kept;  // oldest first
+};
+
+ts_kv_prefixes *ts_kv_prefixes_new(uint64_t grid) {
+    ts_kv_prefixes *p = new (std::nothrow) ts_kv_prefixes();
+    if (p) p->grid = grid;
+    return p;
+}
+
+void ts_kv_prefixes_free(ts_kv_prefixes *prefixes) { delete prefixes; }
+
+int ts_kv_prefixes_keep(ts_kv_prefixes *prefixes, ts_kv_run run, const uint32_t *history, uint64_t history_len,
+                        uint64_t valid) {
+    if (!prefixes || (history_len > 0 && !history)) return TS_KV_BAD_ARGUMENT;
+    ts_kv_prefixes::Entry e;
+    e.run = run;
+    e.history.assign(history, history + history_len);
+    e.valid = valid;
+    prefixes->kept.push_back(std::move(e));
+    return TS_KV_OK;
+}
+
+int ts_kv_prefixes_find(ts_kv_prefixes *prefixes, const ts_kv_pool *pool, uint64_t tag, const uint32_t *prompt,
+                        uint64_t prompt_len, uint64_t limit, ts_kv_run *run, uint64_t *skip, int *found) {
+    if (!prefixes || !pool || !run || !skip || !found || (prompt_len > 0 && !prompt)) return TS_KV_BAD_ARGUMENT;
+    // entries whose run is gone (released, reclaimed or adopted) leave first: prefix.rs:42
+    std::vector<ts_kv_prefixes::Entry> alive;
+    for (auto &e : prefixes->kept) {
+        uint64_t rows;
+        if (ts_kv_rows(pool, e.run, &rows) == TS_KV_OK) alive.push_back(std::move(e));
+    }
+    prefixes->kept.swap(alive);
+    *found = 0;
+    *skip = 0;
+    for (const auto &e : prefixes->kept) {
+        uint64_t its;
+        if (ts_kv_tag(pool, e.run, &its) != TS_KV_OK || its != tag) continue;
+        ts_kv_begin b;
+        ts_kv_begin_rows(e.history.data(), e.history.size(), e.valid, prompt, prompt_len, limit, prefixes->grid, &b);
+        if (b.skip > 0 && (!*found || b.skip >= *skip)) {  // a later entry wins a tie: the newest run
+            *found = 1;
+            *skip = b.skip;
+            *run = e.run;
+        }
+    }
+    return TS_KV_OK;
+}
+
+uint64_t ts_kv_prefixes_len(const ts_kv_prefixes *prefixes) { return prefixes ? prefixes->kept.size() : 0; }
+
 }  // extern "C"
 #pragma GCC visibility pop

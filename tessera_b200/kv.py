@@ -31,6 +31,10 @@ class Stats(C.Structure):
     _fields_ = [(n, u64) for n in ("size", "active", "worst", "live_runs", "kept_runs")]
 
 
+class _Begin(C.Structure):
+    _fields_ = [("skip", u64), ("lcp", u64), ("why", i32)]
+
+
 KV_SIGNATURES = {
     "ts_kv_pool_new": (vp, [u32, u32]),
     "ts_kv_pool_free": (None, [vp]),
@@ -52,6 +56,12 @@ KV_SIGNATURES = {
     "ts_kv_consistent": (i32, [vp]),
     "ts_kv_fill_table": (i32, [vp, Run, vp, u32, u32]),
     "ts_kv_copy_pages": (i32, [vp, C.POINTER(PageCopy), u32, u32, C.c_size_t, vp]),
+    "ts_kv_begin_rows": (None, [vp, u64, u64, vp, u64, u64, u64, C.POINTER(_Begin)]),
+    "ts_kv_prefixes_new": (vp, [u64]),
+    "ts_kv_prefixes_free": (None, [vp]),
+    "ts_kv_prefixes_keep": (i32, [vp, Run, vp, u64, u64]),
+    "ts_kv_prefixes_find": (i32, [vp, vp, u64, vp, u64, u64, C.POINTER(Run), C.POINTER(u64), C.POINTER(i32)]),
+    "ts_kv_prefixes_len": (u64, [vp]),
 }
 for _name, (_res, _args) in KV_SIGNATURES.items():
     _fn = getattr(lib, _name)
@@ -143,3 +153,49 @@ class Pool:
     def fill_table(self, run: Run, table: np.ndarray, slot: int, kept_pages: int):
         assert table.dtype == np.uint32 and table.flags.c_contiguous
         self._check(lib.ts_kv_fill_table(self._h, run, table.ctypes.data_as(vp), slot, kept_pages))
+
+
+WHY = ("First", "NoLcp", "Grid", "Hit")   # engine/ir/kv/src/reuse.rs:3-14
+
+
+def _ids(tokens) -> np.ndarray:
+    return np.ascontiguousarray(tokens, dtype=np.uint32)
+
+
+def begin(history, valid: int, prompt, limit: int, grid: int) -> tuple:
+    """(skip, lcp, why): the rows of `prompt` that `valid` kept rows spare (engine/ir/kv/src/reuse.rs:24-37)."""
+    h, p = _ids(history), _ids(prompt)
+    out = _Begin()
+    lib.ts_kv_begin_rows(h.ctypes.data_as(vp), h.size, valid, p.ctypes.data_as(vp), p.size, limit, grid, C.byref(out))
+    return int(out.skip), int(out.lcp), WHY[out.why]
+
+
+class Prefixes:
+    """The tokens of retained runs, oldest first (engine/ir/kv/src/prefix.rs:11-55)."""
+
+    def __init__(self, grid: int):
+        self._h = lib.ts_kv_prefixes_new(grid)
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            lib.ts_kv_prefixes_free(self._h)
+            self._h = None
+
+    def __len__(self):
+        return int(lib.ts_kv_prefixes_len(self._h))
+
+    def keep(self, run: Run, history, valid: int):
+        h = _ids(history)
+        code = lib.ts_kv_prefixes_keep(self._h, run, h.ctypes.data_as(vp), h.size, valid)
+        if code:
+            raise PoolError(code, 0)
+
+    def find(self, pool: "Pool", tag: int, prompt, limit: int):
+        """(run, skip) of the newest run with the longest skip, or None."""
+        p = _ids(prompt)
+        run, skip, found = Run(), u64(0), i32(0)
+        code = lib.ts_kv_prefixes_find(self._h, pool._h, tag, p.ctypes.data_as(vp), p.size, limit, C.byref(run),
+                                       C.byref(skip), C.byref(found))
+        if code:
+            raise PoolError(code, 0)
+        return (run, int(skip.value)) if found.value else None

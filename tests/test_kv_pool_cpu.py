@@ -117,3 +117,47 @@ def test_lowest_free_page_first_and_table_fill():
     table = np.full(2 * 4, 99, np.uint32)
     pool.fill_table(c, table, 1, 4)
     assert table.tolist() == [99, 99, 99, 99, 0, 1, 3, 99]
+
+
+def test_skips_follow_rule():
+    # engine/ir/kv/src/reuse_test.rs:3-14, case for case
+    from tessera_b200.kv import begin
+    cases = [
+        (1031, 1030, 191, 2191, 64, 128, "Hit"),
+        (1031, 1030, 63, 1999, 64, 0, "Grid"),
+        (100, 0, 100, 99, 0, 0, "NoLcp"),
+    ]
+    for h, valid, lcp, limit, grid, skip, why in cases:
+        assert begin([1] * h, valid, [1] * lcp, limit, grid) == (skip, lcp, why)
+    assert begin([], 5, [1, 2, 3], 10, 1) == (0, 0, "First")          # no history
+    assert begin([1, 2, 9], 3, [1, 2, 3, 4], 10, 1) == (2, 2, "Hit")   # the common rows stop at the first difference
+    assert begin([1, 2, 3], 3, [1, 2, 3], 2, 1) == (2, 3, "Hit")       # the limit caps the skip, not the lcp
+
+
+def test_prefixes_find_newest_longest():
+    # engine/ir/kv/src/prefix.rs:34-55: runs of another tag and runs the pool no longer knows never match; the
+    # longest skip wins and a later entry wins a tie
+    from tessera_b200.kv import Prefixes
+    pool = Pool(16, 4)
+    kept = Prefixes(grid=4)
+    prompt = list(range(100, 120))
+    assert kept.find(pool, T, prompt, 64) is None
+    runs = []
+    for tag, history in ((T, prompt[:6] + [7, 7]), (T, prompt[:9]), (1, prompt[:16]), (T, prompt[:10])):
+        r = pool.reserve(tag, len(history), len(history))
+        pool.retain(r)
+        kept.keep(r, history, len(history))
+        runs.append(r)
+    assert len(kept) == 4
+    run, skip = kept.find(pool, T, prompt, 64)
+    assert (run, skip) == (runs[3], 8)           # 9 and 10 common rows both skip 8: the newer run
+    assert kept.find(pool, 1, prompt, 64) == (runs[2], 16)
+    assert kept.find(pool, T, prompt, 7) == (runs[3], 4)   # the limit applies before the grid
+    assert kept.find(pool, T, [5, 5, 5], 64) is None
+    pool.release(runs[3])
+    run, skip = kept.find(pool, T, prompt, 64)
+    assert (run, skip) == (runs[1], 8) and len(kept) == 3  # the released run's entry left
+    # a run adopted by a new request is no longer the retained run either
+    pool.adopt(runs[1], 8, 12)
+    assert kept.find(pool, T, prompt, 64) == (runs[0], 4) and len(kept) == 2
+    assert pool.consistent()
