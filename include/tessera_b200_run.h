@@ -20,6 +20,7 @@
 #include <stdint.h>
 
 #include "tessera_b200.h"
+#include "tessera_b200_kv.h"
 
 #ifdef __cplusplus
 extern "C" {
@@ -52,6 +53,11 @@ int ts_decoder_load(ts_decoder *dec, const char *name, const void *host_data, si
 
 /* Replaces the page table (slots * ceil(context / page) entries; every entry < that count). */
 int ts_decoder_set_table(ts_decoder *dec, const uint32_t *host_table, uint32_t entries);
+
+/* Applies the page copies a pool planned (ts_kv_grow: a write into a shared partial page first copies it,
+ * engine/ir/kv/src/pool.rs:193-222) to the kept K and V rows of every layer, on `stream`, before the launch
+ * that writes.  Pages are the table's units: copy {from, to, rows} moves the first `rows` rows of page `from`. */
+int ts_decoder_copy_pages(ts_decoder *dec, const ts_kv_copy *copies, uint32_t n_copies, void *stream);
 
 /* One launch: feeds `rows` (token, slot, position) triples from host memory, runs the step list and
  * returns the greedy token of each row listed in `out_rows` (n_out indices into the launch's rows;

@@ -500,6 +500,25 @@ int ts_decoder_set_table(ts_decoder *d, const uint32_t *host_table, uint32_t ent
     return TS_OK;
 }
 
+int ts_decoder_copy_pages(ts_decoder *d, const ts_kv_copy *copies, uint32_t n_copies, void *stream) {
+    TS_REQUIRE(d && (copies || n_copies == 0), "decoder page copies: NULL argument");
+    TS_REQUIRE(d->c.page != 0, "decoder page copies: the kept rows are dense, there are no pages");
+    const uint32_t pages = d->c.slots * d->kept_pages;
+    for (uint32_t i = 0; i < n_copies; i++)
+        TS_REQUIRE(copies[i].from < pages && copies[i].to < pages && copies[i].rows <= d->c.page,
+                   "decoder page copies: copy %u (%u -> %u, %u rows) is outside %u pages of %u rows", i, copies[i].from,
+                   copies[i].to, copies[i].rows, pages, d->c.page);
+    const size_t row_bytes = (size_t)d->c.kv_heads * d->c.head_dim * 2;
+    cudaStream_t s = stream_of(d, stream);
+    for (auto &L : d->layers) {
+        int rc = ts_kv_copy_pages(L.k_rows, copies, n_copies, d->c.page, row_bytes, s);
+        if (rc != TS_OK) return rc;
+        rc = ts_kv_copy_pages(L.v_rows, copies, n_copies, d->c.page, row_bytes, s);
+        if (rc != TS_OK) return rc;
+    }
+    return TS_OK;
+}
+
 int ts_decoder_step(ts_decoder *d, const uint32_t *tokens, const uint32_t *slots, const uint32_t *positions,
                     uint32_t rows, const uint32_t *out_rows, uint32_t n_out, uint32_t *out_ids, void *stream) {
     TS_REQUIRE(d && tokens && slots && positions, "decoder step: NULL argument");

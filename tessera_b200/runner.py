@@ -21,6 +21,7 @@ RUN_SIGNATURES = {
     "ts_decoder_destroy": (None, [vp]),
     "ts_decoder_load": (i32, [vp, C.c_char_p, vp, sz]),
     "ts_decoder_set_table": (i32, [vp, vp, u32]),
+    "ts_decoder_copy_pages": (i32, [vp, vp, u32, vp]),
     "ts_decoder_step": (i32, [vp, vp, vp, vp, u32, vp, u32, vp, vp]),
     "ts_decoder_run_resident": (i32, [vp, u32, vp]),
     "ts_decoder_read_ids": (i32, [vp, vp, u32, vp]),
@@ -74,6 +75,13 @@ class Decoder:
     def set_table(self, table):
         t = _u(table)
         check(lib.ts_decoder_set_table(self._h, t.ctypes.data_as(vp), t.size))
+
+    def copy_pages(self, copies, stream=None):
+        """Applies a pool's planned page copies [(from, to, rows), ...] (kv.Pool.grow) to every layer's kept rows."""
+        if not copies:
+            return
+        flat = np.ascontiguousarray(copies, dtype=np.uint32).reshape(-1, 3)
+        check(lib.ts_decoder_copy_pages(self._h, flat.ctypes.data_as(vp), flat.shape[0], vp(stream or 0)))
 
     def step(self, tokens, slots, positions, out_rows=None, stream=None) -> np.ndarray:
         tokens, slots, positions = _u(tokens), _u(slots), _u(positions)

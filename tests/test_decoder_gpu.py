@@ -168,3 +168,60 @@ def test_qwen3_0p6b_logits_follow_golden():
     dec.close()
     print(f"largest logit error over 32 steps: {worst:.2e} of the largest logit")
     assert worst <= 1e-2
+
+
+def test_prefix_reuse_through_the_page_pool():
+    """A second prompt that shares its beginning with a retained run (engine/ir/kv/src/prefix.rs, reuse.rs): its slot
+    borrows the run's pages through the table, the shared partial page is copied before the first write
+    (pool.rs:193-222), only the rows past the skip are fed, and the tokens equal those of feeding the whole prompt."""
+    from tessera_b200.kv import Pool, Prefixes
+    cfg, page, context, tag = SMALL, 16, 64, 0
+    kept_pages = context // page
+    rng = np.random.default_rng(21)
+    first = rng.integers(0, cfg["vocab"], size=40).tolist()
+    second = first[:38] + rng.integers(0, cfg["vocab"], size=9).tolist()
+    new = 6
+
+    dec = _device(cfg, 5, slots=2, context=context, max_rows=64, gains="near_one", page=page)
+    pool, kept = Pool(2 * kept_pages, page), Prefixes(grid=4)
+    table = np.zeros(2 * kept_pages, np.uint32)
+
+    def feed(run, slot, tokens, start):
+        """Rows `start`.. of a sequence into `slot`, then `new` greedy tokens; returns them and the rows written."""
+        dec.copy_pages(pool.grow(run, start + len(tokens)))
+        pool.fill_table(run, table, slot, kept_pages)
+        dec.set_table(table)
+        n = len(tokens)
+        cur = dec.step(tokens, [slot] * n, list(range(start, start + n)), out_rows=[n - 1])
+        out, at = [int(cur[0])], start + n
+        for _ in range(1, new):
+            dec.copy_pages(pool.grow(run, at + 1))
+            pool.fill_table(run, table, slot, kept_pages)
+            dec.set_table(table)
+            cur = dec.step(cur, [slot], [at])
+            out.append(int(cur[0]))
+            at += 1
+        return out, at
+
+    a = pool.reserve(tag, 0, context)
+    said, rows = feed(a, 0, first, 0)
+    pool.retain(a)
+    kept.keep(a, first + said[:-1], rows)     # the tokens behind the run's rows (the last token was never fed)
+
+    run, skip = kept.find(pool, tag, second, len(second) - 1)
+    assert run == a and skip == 36           # 38 common rows, whole steps of 4
+    b = pool.fork(a, skip, context)
+    shared = pool.pages(b)
+    assert shared == pool.pages(a)[:3]        # two whole pages and a partial one, borrowed
+    got, _ = feed(b, 1, second[skip:], skip)
+    assert pool.pages(b)[:2] == shared[:2] and pool.pages(b)[2] != shared[2]   # the partial page was copied first
+    hidden = O.bf16_widen(dec.read_hidden(1))
+    dec.close()
+    assert pool.consistent()
+
+    fresh = _device(cfg, 5, slots=1, context=context, max_rows=64, gains="near_one", page=page)
+    want = fresh.generate([second], new)[0].tolist()
+    want_hidden = O.bf16_widen(fresh.read_hidden(1))
+    fresh.close()
+    assert rel_error(hidden, want_hidden) <= 1e-2
+    assert got == want
