@@ -84,9 +84,10 @@ class MoeDecoder:
         for i, L in enumerate(self.layers):
             h = ops.rms_norm(x, L["ln1"], eps)
             qkv = ops.linear(h, L["wqkv"])
-            ops.qk_norm_rope_append(qkv, L["q_norm"], L["k_norm"], self.inv_freq, slots, positions, q, self.k_rows[i],
-                                    self.v_rows[i], kept, heads, kvh, d, eps)
-            a = ops.attend_rows(q, self.k_rows[i], self.v_rows[i], slots, positions, kept, keys, scale=d ** -0.5)
+            # one row per slot: per-head norm, rotation, append and attention in one launch (the same bits as
+            # ops.qk_norm_rope_append followed by ops.attend_rows)
+            a = ops.attend_rows_append(qkv, L["q_norm"], L["k_norm"], self.inv_freq, self.k_rows[i], self.v_rows[i], slots,
+                                       positions, kept, keys, heads, eps=eps, scale=d ** -0.5, out=q)
             x = ops.linear(a.view(rows, heads * d), L["wo"], x, epilogue="add", out_dtype=torch.float32, out=x)
             h = ops.rms_norm(x, L["ln2"], eps)
             if self.ep is None:
