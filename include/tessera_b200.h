@@ -58,7 +58,7 @@ typedef enum { TS_BF16 = 0, TS_F32 = 1 } ts_dtype;
  *   x   [m, k] bf16 row-major          w   [n, k] bf16 row-major ("[Out, In]")
  *   a0  epilogue operand or NULL       out [m, n] (or [m, n/2] for SWIGLU)
  *
- * k must be a multiple of 64 and x, w, out 16-byte aligned.
+ * x, w, out 16-byte aligned; the tensor-core kernels take k in multiples of 64, any other k runs on the plain kernel.
  * ------------------------------------------------------------------------- */
 typedef enum {
     TS_EPI_NONE = 0,
@@ -76,8 +76,11 @@ typedef enum {
     TS_LINEAR_UMMA = 2,   /* tiled tcgen05 / TMEM accumulators fed by TMA (prefill-sized m) */
     TS_LINEAR_STREAM = 3, /* m <= 128: weight-streaming tcgen05, k split over a thread-block cluster and
                              reduced through distributed shared memory, epilogue fused */
-    TS_LINEAR_PAIR = 4    /* m >= 512: 256 x 256 tiles on pairs of SMs (tcgen05 cta_group::2), each block of
+    TS_LINEAR_PAIR = 4,   /* m >= 512: 256 x 256 tiles on pairs of SMs (tcgen05 cta_group::2), each block of
                              the pair loading half of both operands */
+    TS_LINEAR_PLAIN = 5   /* any m, n, k: a warp per output element; what AUTO falls back to when k is not a
+                             multiple of 64 (the reference's tiled rule takes every size,
+                             engine/rules/linear/tests/tiled_test.rs:61-67) */
 } ts_linear_path;
 
 /* Bytes of workspace ts_linear_bf16 needs for these sizes (0 when none). */

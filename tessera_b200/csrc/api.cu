@@ -133,7 +133,9 @@ static bool pair_auto() {
 }
 
 int pick_linear_path(uint32_t m, uint32_t n, uint32_t k, int epilogue, int path) {
-    if (path == TS_LINEAR_SKINNY || path == TS_LINEAR_UMMA || path == TS_LINEAR_STREAM || path == TS_LINEAR_PAIR) return path;
+    if (path == TS_LINEAR_SKINNY || path == TS_LINEAR_UMMA || path == TS_LINEAR_STREAM || path == TS_LINEAR_PAIR ||
+        path == TS_LINEAR_PLAIN)
+        return path;
     // m <= 16: the warp-MMA streamer; m <= 128: the weight-streaming tcgen05 kernel with its cluster
     // reduce; larger m: the tiled tcgen05 kernel.
     if (m <= 16 && skinny_supports(m, n, k, epilogue)) return TS_LINEAR_SKINNY;
@@ -141,6 +143,7 @@ int pick_linear_path(uint32_t m, uint32_t n, uint32_t k, int epilogue, int path)
     if (pair_auto() && pair_supports(m, n, k, epilogue)) return TS_LINEAR_PAIR;
     if (umma_supports(m, n, k, epilogue)) return TS_LINEAR_UMMA;
     if (skinny_supports(m, n, k, epilogue)) return TS_LINEAR_SKINNY;
+    if (plain_supports(m, n, k, epilogue)) return TS_LINEAR_PLAIN;  // k off the 64 grid and the like
     return -1;
 }
 
@@ -212,7 +215,8 @@ int ts_linear_bf16(const void *x, const void *w, const void *a0, void *out, uint
     TS_REQUIRE(out_dtype == TS_BF16 || out_dtype == TS_F32, "linear: out dtype %d is unknown", out_dtype);
     TS_REQUIRE(epilogue != TS_EPI_ADD || a0 != nullptr, "linear: the add epilogue needs its operand");
     TS_REQUIRE(a0 == nullptr || aligned16(a0), "linear: the epilogue operand must be 16-byte aligned");
-    TS_REQUIRE(k % 64 == 0 && k > 0, "linear: k = %u is not a positive multiple of 64", k);
+    TS_REQUIRE(k > 0, "linear: k is zero");
+    TS_REQUIRE(path >= TS_LINEAR_AUTO && path <= TS_LINEAR_PLAIN, "linear: path %d is unknown", path);
     if (m == 0 || n == 0) return TS_OK;
     const int chosen = pick_linear_path(m, n, k, epilogue, path);
     TS_REQUIRE(chosen > 0, "linear: no kernel takes m=%u n=%u k=%u epilogue=%d", m, n, k, epilogue);
@@ -230,6 +234,11 @@ int ts_linear_bf16(const void *x, const void *w, const void *a0, void *out, uint
         TS_REQUIRE(pair_supports(m, n, k, epilogue), "linear (pair): needs m >= 512 and n >= 256 (m=%u n=%u k=%u)", m, n, k);
         return linear_pair(x, w, a0, out, m, n, k, epilogue, scale, out_dtype, s);
     }
+    if (chosen == TS_LINEAR_PLAIN) {
+        TS_REQUIRE(plain_supports(m, n, k, epilogue), "linear (plain): a gated epilogue needs an even n (n=%u)", n);
+        return linear_plain(x, w, a0, out, m, n, k, epilogue, scale, out_dtype, s);
+    }
+    TS_REQUIRE(umma_supports(m, n, k, epilogue), "linear (umma): needs k in multiples of 64 (m=%u n=%u k=%u)", m, n, k);
     return linear_umma(x, w, a0, out, m, n, k, epilogue, scale, out_dtype, workspace, workspace_bytes, s);
 }
 

@@ -113,6 +113,9 @@ int rope_angles(const uint32_t *positions, float *out, uint32_t count, uint32_t 
                 cudaStream_t stream);
 int rope(void *x, int dtype, const float *freqs, uint32_t positions, uint32_t heads, uint32_t width, int adjacent,
          cudaStream_t stream);
+bool plain_supports(uint32_t m, uint32_t n, uint32_t k, int epilogue);
+int linear_plain(const void *x, const void *w, const void *a0, void *out, uint32_t m, uint32_t n, uint32_t k,
+                 int epilogue, float scale, int out_dtype, cudaStream_t stream);
 size_t picked_workspace_bytes(uint32_t rows, uint32_t n, uint32_t k, uint32_t count);
 int picked(const void *x, const void *w, const uint32_t *ids, float *out, uint32_t rows, uint32_t n, uint32_t k,
            uint32_t count, uint32_t stride, uint32_t offset, uint32_t repeat, uint32_t first, void *workspace,

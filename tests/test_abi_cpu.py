@@ -43,8 +43,12 @@ def test_bad_arguments_are_refused_on_the_host():
     buf = (C.c_char * 256)()
     p = C.cast(buf, C.c_void_p).value
     p = (p + 15) // 16 * 16
-    rc = lib.ts_linear_bf16(p, p, None, p, 1, 1, 100, 0, 1.0, 0, 0, None, 0, None)
-    assert rc == _lib.TS_ERR_BAD_INPUT and b"multiple of 64" in lib.ts_last_error()
+    rc = lib.ts_linear_bf16(p, p, None, p, 1, 1, 100, 0, 1.0, 0, 2, None, 0, None)   # path 2: the tiled tensor-core kernel
+    assert rc == _lib.TS_ERR_BAD_INPUT and b"multiples of 64" in lib.ts_last_error()
+    rc = lib.ts_linear_bf16(p, p, None, p, 1, 1, 100, 0, 1.0, 0, 9, None, 0, None)
+    assert rc == _lib.TS_ERR_BAD_INPUT and b"path 9" in lib.ts_last_error()
+    rc = lib.ts_linear_bf16(p, p, None, p, 1, 1, 0, 0, 1.0, 0, 0, None, 0, None)
+    assert rc == _lib.TS_ERR_BAD_INPUT and b"k is zero" in lib.ts_last_error()
     rc = lib.ts_linear_bf16(p + 2, p, None, p, 1, 1, 64, 0, 1.0, 0, 0, None, 0, None)
     assert rc == _lib.TS_ERR_BAD_INPUT and b"aligned" in lib.ts_last_error()
     kept = _lib.TsKept(2, 48, 4, None, 0, 0)  # page 48 is not a power of two

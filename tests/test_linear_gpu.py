@@ -167,11 +167,49 @@ def test_bad_arguments_are_refused():
     from tessera_b200 import TesseraError, ops
     x = torch.zeros((4, 100), dtype=torch.bfloat16, device="cuda")
     w = torch.zeros((8, 100), dtype=torch.bfloat16, device="cuda")
-    with pytest.raises(TesseraError) as e:
-        ops.linear(x, w)
-    assert e.value.code == 3  # TS_ERR_BAD_INPUT: k is not a multiple of 64
+    for path in ("skinny", "umma", "stream", "pair"):
+        with pytest.raises(TesseraError) as e:
+            ops.linear(x, w, path=path)
+        assert e.value.code == 3  # TS_ERR_BAD_INPUT: the tensor-core kernels take k in multiples of 64
+    assert ops.linear(x, w).shape == (4, 8)   # left to itself the library takes the plain kernel
     with pytest.raises(TesseraError):
         ops.linear(x.cpu(), w.cpu())
+    with pytest.raises(TesseraError):
+        ops.linear(x[:, :99].contiguous(), w[:7, :99].contiguous(), epilogue="swiglu")   # a gated epilogue with odd n
+
+
+def test_every_size_of_the_reference_tiled_cases():
+    # engine/rules/linear/tests/tiled_test.rs:57-67: Noise(29); sizes off the block, on it, beyond it, over bands;
+    # x drawn first, then w; the reference sees the weights in the stored (bf16) form.  Activations are bf16 here.
+    from tessera_b200 import ops
+    draws = O.Noise(29)
+    for m, n, k in [(1, 3, 4), (37, 50, 72), (64, 64, 64), (600, 40, 512), (256, 512, 1024)]:
+        x = O.bf16_bits(draws.draw(m, k))
+        w = O.bf16_bits(draws.draw(n, k))
+        want = O.matmul(O.bf16_widen(x), w)
+        got = ops.linear(from_bits(x), from_bits(w), out_dtype=torch.float32)
+        torch.cuda.synchronize()
+        assert ops.device_status() == 0
+        assert rel_error(widen(got), want) <= F32_TOL, (m, n, k)
+        plain = ops.linear(from_bits(x), from_bits(w), out_dtype=torch.float32, path="plain")
+        assert rel_error(widen(plain), want) <= F32_TOL, (m, n, k)
+        assert rel_error(widen(ops.linear(from_bits(x), from_bits(w))), want) <= BF16_TOL, (m, n, k)
+
+
+@pytest.mark.parametrize("act", ["swiglu", "geglu"])
+def test_plain_kernel_epilogues(act):
+    from tessera_b200 import ops
+    m, ffn, k = 5, 9, 40                     # nothing here sits on a tile or a 16-byte row
+    x, w = _case(m, 2 * ffn, k, seed=61)
+    xs = O.bf16_widen(x)
+    want = O.act(O.matmul(xs, w[:ffn]), "silu" if act == "swiglu" else "gelu_tanh") * O.matmul(xs, w[ffn:])
+    got = ops.linear(from_bits(x), from_bits(w), epilogue=act, out_dtype=torch.float32)
+    assert got.shape == (m, ffn) and rel_error(widen(got), want) <= 1e-3   # tanh / exp of the device's libm
+    res = np.random.default_rng(62).standard_normal((m, 2 * ffn), dtype=np.float32)
+    added = ops.linear(from_bits(x), from_bits(w), torch.from_numpy(res).cuda(), epilogue="add", out_dtype=torch.float32)
+    assert rel_error(widen(added), O.matmul(xs, w) + res) <= F32_TOL
+    scaled = ops.linear(from_bits(x), from_bits(w), epilogue="scale", scale=0.25, out_dtype=torch.float32)
+    assert rel_error(widen(scaled), O.matmul(xs, w) * np.float32(0.25)) <= F32_TOL
 
 
 @pytest.mark.parametrize("m", [64, 37, 128, 9])
