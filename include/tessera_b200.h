@@ -149,7 +149,7 @@ typedef struct {
  * (engine/rules/attention/src/attend.rs:124-167, arguments 182-201) and `flash_rows`
  * (engine/rules/attention/src/flash.rs:505-580).  The score scale, a separate `map` launch in
  * the reference (engine/rules/attention/src/lib.rs:22-31), is an argument here.
- *   q [rows, heads, width] bf16; out [rows, heads, width] bf16; width must be 128 or 256. */
+ *   q [rows, heads, width] bf16; out [rows, heads, width] bf16; width 16, 32, 64, 128 or 256 (the TMA-fed kernels take 128). */
 size_t ts_attend_rows_workspace_bytes(uint32_t rows, uint32_t keys, uint32_t heads, uint32_t kv_heads,
                                       uint32_t width);
 

@@ -260,7 +260,8 @@ int ts_attend_rows_bf16(const void *q, const void *k, const void *v, void *out, 
                         void *workspace, size_t workspace_bytes, void *stream) {
     TS_REQUIRE(q && k && v && out && slots && positions, "attend_rows: a buffer is NULL");
     TS_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out), "attend_rows: buffers must be 16-byte aligned");
-    TS_REQUIRE(width == 64 || width == 128 || width == 256, "attend_rows: width %u is not 64, 128 or 256", width);
+    TS_REQUIRE(width == 16 || width == 32 || width == 64 || width == 128 || width == 256,
+               "attend_rows: width %u is not 16, 32, 64, 128 or 256", width);
     TS_REQUIRE(kv_heads > 0 && heads % kv_heads == 0, "attend_rows: %u heads do not split over %u kv heads", heads, kv_heads);
     KeptDev dev;
     bool contiguous;
@@ -326,7 +327,7 @@ int ts_attend_bf16(const void *q, const void *k, const void *v, void *out, const
                             cu_seqlens ? keys : seqs * keys, heads, kv_heads, width, back, ahead, scale, s);
     }
     TS_REQUIRE(!cu_seqlens, "attend: packed sequences need width 128 or 256 (got %u)", width);
-    TS_REQUIRE(width == 64, "attend: width %u is not 64, 128 or 256", width);
+    TS_REQUIRE(width == 16 || width == 32 || width == 64, "attend: width %u is not 16, 32, 64, 128 or 256", width);
     const size_t rows = (size_t)seqs * queries;
     const size_t need = ts_attend_workspace_bytes(seqs, queries, keys, heads, kv_heads, width);
     TS_REQUIRE(workspace && workspace_bytes >= need, "attend: workspace of %zu bytes is smaller than the %zu needed",

@@ -1120,6 +1120,16 @@ int attend_rows(const void *q, const void *k, const void *v, void *out, const ui
         e = s.g == 4 ? launch_rows<64, 4>(p, grid, stream)
             : s.g == 2 ? launch_rows<64, 2>(p, grid, stream)
                        : launch_rows<64, 1>(p, grid, stream);
+    } else if (width == 32) {   // narrow heads: the reference's own attention cases run 16 wide
+        e = s.g == 4 ? launch_rows<32, 4>(p, grid, stream)
+            : s.g == 2 ? launch_rows<32, 2>(p, grid, stream)
+                       : launch_rows<32, 1>(p, grid, stream);
+    } else if (width == 16) {
+        e = s.g == 4 ? launch_rows<16, 4>(p, grid, stream)
+            : s.g == 2 ? launch_rows<16, 2>(p, grid, stream)
+                       : launch_rows<16, 1>(p, grid, stream);
+    } else {
+        return fail(TS_ERR_BAD_INPUT, "attend_rows: width %u is not 16, 32, 64, 128 or 256", width);
     }
     if (e != cudaSuccess)
         return fail(TS_ERR_CUDA, "launch of attend_rows failed: %s (%d) %s", cudaGetErrorName(e), (int)e,
@@ -1127,7 +1137,9 @@ int attend_rows(const void *q, const void *k, const void *v, void *out, const ui
     if (s.chunks > 1) {
         if (width == 128) e = launch(attend_rows_merge_kernel<128>, dim3(rows, heads), dim3(128), 0, stream, pdl_enabled(), p);
         else if (width == 256) e = launch(attend_rows_merge_kernel<256>, dim3(rows, heads), dim3(256), 0, stream, pdl_enabled(), p);
-        else e = launch(attend_rows_merge_kernel<64>, dim3(rows, heads), dim3(64), 0, stream, pdl_enabled(), p);
+        else if (width == 64) e = launch(attend_rows_merge_kernel<64>, dim3(rows, heads), dim3(64), 0, stream, pdl_enabled(), p);
+        else if (width == 32) e = launch(attend_rows_merge_kernel<32>, dim3(rows, heads), dim3(32), 0, stream, pdl_enabled(), p);
+        else e = launch(attend_rows_merge_kernel<16>, dim3(rows, heads), dim3(16), 0, stream, pdl_enabled(), p);
         if (e != cudaSuccess)
             return fail(TS_ERR_CUDA, "launch of attend_rows_merge failed: %s (%d) %s", cudaGetErrorName(e), (int)e,
                         cudaGetErrorString(e));

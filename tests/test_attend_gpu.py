@@ -129,3 +129,51 @@ def test_prefill_shape_spot_check():
     assert rel_error(got[0, rows], want) <= TOL
     again = _run(q, k, v, "causal", scale)
     assert np.array_equal(got, again)  # same bits on a re-run
+
+
+def test_reference_case_grid_with_its_noise():
+    """engine/rules/attention/tests/attention_test.rs:43-102, `flash_matches_cpu`: Noise(41); rows off, on and past
+    the block, with older keys; five masks; heads x width (2, 16), (4, 64), (2, 128); q, k, v drawn in that order.
+    Inputs are rounded to bf16 here (the reference feeds f32) and the checker sees the rounded values."""
+    draws = O.Noise(41)
+    cases = [(1, 1, 1), (1, 1, 38), (2, 7, 7), (1, 33, 33), (2, 70, 93), (1, 128, 128)]
+    masks = ["causal", "bidirectional", ("within", 5), ("within", 40), ("back", 5)]
+    worst = 0.0
+    for mask in masks:
+        for heads, width in [(2, 16), (4, 64), (2, 128)]:
+            for seqs, rows, keys in cases:
+                q = O.bf16_bits(draws.draw(seqs, rows, heads, width))
+                k = O.bf16_bits(draws.draw(seqs, keys, heads, width))
+                v = O.bf16_bits(draws.draw(seqs, keys, heads, width))
+                want = O.attend(O.bf16_widen(q), O.bf16_widen(k), O.bf16_widen(v), mask, 1.0)
+                got = _run(q, k, v, mask, 1.0)
+                off = rel_error(got, want)
+                worst = max(worst, off)
+                assert off <= TOL, (mask, heads, width, seqs, rows, keys, off)
+    print(f"worst relative error over the grid: {worst:.2e}")
+
+
+@pytest.mark.parametrize("width", [16, 32])
+def test_narrow_heads_over_kept_rows(width):
+    # ragged rows over paged kept rows at the narrow widths the reference's cases use
+    from tessera_b200 import ops
+    rng = np.random.default_rng(width)
+    slots, context, heads, kv_heads, page = 3, 96, 4, 2, 16
+    pages = context // page
+    table = rng.permutation(slots * pages).astype(np.uint32)
+    kd = normal_bf16(rng, (slots, context, kv_heads, width))
+    vd = normal_bf16(rng, (slots, context, kv_heads, width))
+    kr = np.zeros((slots * pages * page, kv_heads, width), np.uint16)
+    vr = np.zeros_like(kr)
+    for s in range(slots):
+        for p in range(context):
+            at = int(table[s * pages + p // page]) * page + p % page
+            kr[at], vr[at] = kd[s, p], vd[s, p]
+    row_slots, row_pos = [2, 0, 1, 2], [95, 0, 40, 17]
+    q = normal_bf16(rng, (4, heads, width))
+    want = O.attend_rows(O.bf16_widen(q), O.bf16_widen(kd), O.bf16_widen(vd), row_slots, row_pos, "causal", 0.25)
+    kept = ops.Kept("paged16", pages, dev_u32(table), slots * pages * page)
+    got = ops.attend_rows(from_bits(q), from_bits(kr), from_bits(vr), dev_u32(row_slots), dev_u32(row_pos), kept, context,
+                          scale=0.25)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0 and rel_error(widen(got), want) <= TOL
