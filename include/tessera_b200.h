@@ -303,8 +303,9 @@ int ts_moe_bf16(const void *h, const uint32_t *ids, const float *gates, const fl
  *     out[i, col] = sum_j x[i / repeat, j] * w[(ids[i] - first) * stride + offset + col, j]      col < n, j < k
  * and zeros where ids[i] falls outside [first, first + count).  x bf16 [rows / repeat, k]; w bf16, `count`
  * matrices `stride` rows apart, of which this launch reads rows [offset, offset + n) (the gate or the up half of a
- * fused table, say); ids u32 [rows]; out f32 [rows, n].  n a multiple of 128, k of 64.  Rows are grouped by matrix
- * (stable counting sort, integer work) so that each matrix streams once per 32 rows that picked it. */
+ * fused table, say); ids u32 [rows]; out f32 [rows, n].  With n a multiple of 128 and k of 64, rows are grouped by matrix
+ * (stable counting sort, integer work) so that each matrix streams once per 32 rows that picked it; any other
+ * size runs a warp per output element (the reference's own case is 4 matrices of 64 x 32). */
 size_t ts_picked_workspace_bytes(uint32_t rows, uint32_t n, uint32_t k, uint32_t count);
 
 int ts_picked_bf16(const void *x, const void *w, const uint32_t *ids, float *out, uint32_t rows, uint32_t n, uint32_t k,

@@ -479,21 +479,56 @@ int moe_experts(const void *x, const uint32_t *ids, const float *gates, const fl
     return TS_OK;
 }
 
+// `picked` for sizes the grouped kernel's tiles do not take (n off the 128 grid, k off the 64 grid: the reference's
+// own case runs 4 matrices of 64 x 32, engine/rules/linear/tests/lanes_test.rs:112-149).  A warp per output
+// element, lanes stride k in ascending order, a fixed butterfly: the same bits on every run and in any batch.
+__global__ void __launch_bounds__(256) picked_plain_kernel(const uint16_t *x, const uint16_t *w, const uint32_t *ids,
+                                                           float *out, uint32_t rows, uint32_t n, uint32_t k,
+                                                           uint32_t count, uint32_t stride, uint32_t offset,
+                                                           uint32_t repeat, uint32_t first) {
+    pdl_wait();
+    const uint32_t lane = threadIdx.x & 31;
+    const size_t total = (size_t)rows * n, warps = (size_t)gridDim.x * (blockDim.x >> 5);
+    for (size_t i = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); i < total; i += warps) {
+        const uint32_t row = (uint32_t)(i / n), col = (uint32_t)(i % n);
+        const uint32_t id = ids[row];
+        float sum = 0.0f;
+        if (id >= first && id - first < count) {   // this rank's matrices start at `first`
+            const uint16_t *xr = x + (size_t)(row / repeat) * k;
+            const uint16_t *wr = w + ((size_t)(id - first) * stride + offset + col) * k;
+            for (uint32_t j = lane; j < k; j += 32)
+                sum = fmaf(__uint_as_float((uint32_t)xr[j] << 16), __uint_as_float((uint32_t)wr[j] << 16), sum);
+            sum = warp_sum(sum);
+        }
+        if (lane == 0) out[i] = sum;
+    }
+    pdl_launch_dependents();
+}
+
 // The reference's `picked` launch on its own: out[i, :] = x[i / repeat, :] . w[(ids[i] - first) * stride + offset + col, :],
 // zeros where ids[i] falls outside [first, first + count).  Rows are grouped by matrix so that each matrix
 // streams once per 32 rows that picked it.
 size_t picked_workspace_bytes(uint32_t rows, uint32_t n, uint32_t k, uint32_t count) {
+    if (n % kRows != 0 || k % kBlockK != 0) return 0;  // the plain kernel needs none
     return carve(nullptr, rows, count, k, 0, n).total;
 }
 
 int picked(const void *x, const void *w, const uint32_t *ids, float *out, uint32_t rows, uint32_t n, uint32_t k,
            uint32_t count, uint32_t stride, uint32_t offset, uint32_t repeat, uint32_t first, void *workspace,
            size_t workspace_bytes, cudaStream_t stream) {
-    TS_REQUIRE(n % kRows == 0 && k % kBlockK == 0, "picked: n must be a multiple of %u and k of %u (got %u, %u)", kRows,
-               kBlockK, n, k);
     TS_REQUIRE(count >= 1 && repeat >= 1 && stride >= offset + n, "picked: stride %u does not hold offset %u + n %u",
                stride, offset, n);
-    if (rows == 0) return TS_OK;
+    if (rows == 0 || n == 0) return TS_OK;
+    if (n % kRows != 0 || k % kBlockK != 0) {
+        TS_REQUIRE(k > 0, "picked: k is zero");
+        const size_t total = (size_t)rows * n;
+        const uint32_t blocks = (uint32_t)std::min<size_t>((total + 7) / 8, (size_t)sm_count() * 16);
+        cudaError_t pe = launch(picked_plain_kernel, dim3(blocks ? blocks : 1), dim3(256), 0, stream, pdl_enabled(),
+                                (const uint16_t *)x, (const uint16_t *)w, ids, out, rows, n, k, count, stride, offset, repeat,
+                                first);
+        if (pe != cudaSuccess) return fail(TS_ERR_CUDA, "launch of picked (plain) failed: %s", cudaGetErrorString(pe));
+        return TS_OK;
+    }
     const size_t need = picked_workspace_bytes(rows, n, k, count);
     TS_REQUIRE(workspace && workspace_bytes >= need, "picked: workspace of %zu bytes is smaller than the %zu needed",
                workspace_bytes, need);

@@ -149,14 +149,28 @@ def test_picked_alone_matches_oracle(rows, repeat, count, first, n, k):
         assert torch.equal(by_name, got)                       # same kernels, same order: same bits
 
 
-def test_picked_refuses_what_it_cannot_tile():
+@pytest.mark.parametrize("count,n,k,rows,repeat", [(4, 32, 64, 10, 2), (4, 64, 32, 10, 2), (3, 7, 52, 5, 1), (2, 128, 40, 9, 3)])
+def test_picked_takes_every_size(count, n, k, rows, repeat):
+    # engine/rules/linear/tests/lanes_test.rs:112-149: two of four experts per row from one stacked set of 64 x 32;
+    # sizes off the tiles run the plain kernel (1e-3 relative and cos > 0.9999 is the reference's bar)
+    from tessera_b200 import ops
+    draws = O.Noise(11)
+    table = O.bf16_bits(draws.draw(count, n, k))
+    x = O.bf16_bits(draws.draw(-(-rows // repeat), k))
+    ids = (np.arange(rows) * 7 % (count + 1)).astype(np.uint32)     # one id past the table: zeros
+    each = np.repeat(O.bf16_widen(x), repeat, axis=0)[:rows]       # row i reads x[i // repeat]
+    want = O.matmul_picked(each, O.bf16_widen(table), ids, 0)
+    got = ops.picked(from_bits(x), from_bits(table), dev_u32(ids), n, count=count, stride=n, repeat=repeat)
+    torch.cuda.synchronize()
+    assert not widen(got)[ids >= count].any()
+    assert rel_error(widen(got), want) <= 1e-3 and _cos(widen(got), want) > 0.9999
+
+
+def test_picked_refuses_overlapping_matrices():
     from tessera_b200 import ops
     from tessera_b200._lib import TesseraError
     x = torch.zeros((4, 64), dtype=torch.bfloat16, device="cuda")
-    w = torch.zeros((2, 100, 64), dtype=torch.bfloat16, device="cuda")
     ids = dev_u32([0, 1, 0, 1])
-    with pytest.raises(TesseraError):
-        ops.picked(x, w, ids, 100)                             # n is not a multiple of 128
     w = torch.zeros((2, 128, 64), dtype=torch.bfloat16, device="cuda")
     with pytest.raises(TesseraError):
         ops.picked(x, w, ids, 128, stride=64)                  # matrices would overlap

@@ -72,7 +72,8 @@ def test_top_k_ties_known_answer():
     assert got == [1, 2, 0, 1, 4, 4, 3, 0, 1]
 
 
-@pytest.mark.parametrize("rows,width,k", [(256, 128, 8), (64, 128, 1), (5, 1000, 32), (3, 7, 4)])
+@pytest.mark.parametrize("rows,width,k", [(256, 128, 8), (64, 128, 1), (5, 1000, 32), (3, 7, 4), (6, 600, 1), (6, 32, 1),
+                                          (4, 3000, 5), (3, 20000, 3), (7, 200, 8), (2, 1024, 2)])
 def test_top_k_is_bit_exact(rows, width, k):
     from tessera_b200 import ops
     x = O.Noise(rows + width).draw(rows, width)
@@ -80,6 +81,22 @@ def test_top_k_is_bit_exact(rows, width, k):
     x[rows - 1, :] = 0.25      # a whole row of ties
     want = O.top_k(x, k)
     got = u32(ops.top_k(torch.from_numpy(x).cuda(), k))
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("width", [16, 128, 700, 5000])
+def test_top_k_spare_slots_hold_the_width(width):
+    # engine/ir/interp/src/run.rs:577-591: -inf and NaN never rank; slots past the rankable entries hold the width
+    from tessera_b200 import ops
+    x = np.full((3, width), -np.inf, np.float32)
+    x[0, [3, width - 1]] = [1.0, 2.0]          # two rankable entries, k = 4
+    x[1, 5] = np.nan                           # nothing ranks
+    x[2, :] = np.nan
+    x[2, [0, 1, 2, 7, 9]] = [0.5, 0.5, -1.0, 0.5, 3.0]
+    want = O.top_k(x, 4)
+    assert want[0].tolist() == [width - 1, 3, width, width] and want[1].tolist() == [width] * 4
+    assert want[2].tolist() == [9, 0, 1, 7]
+    got = u32(ops.top_k(torch.from_numpy(x).cuda(), 4))
     assert np.array_equal(got, want)
 
 
