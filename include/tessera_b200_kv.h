@@ -38,7 +38,10 @@ typedef enum {
     TS_KV_LIVE = 4,
     TS_KV_RETAINED = 5,
     TS_KV_UNKNOWN = 6,
-    TS_KV_BAD_ARGUMENT = 7
+    TS_KV_BAD_ARGUMENT = 7,
+    /* the engine's own two (engine/engine/src/lib.rs:101-102, 111-112) */
+    TS_KV_ROW_PLACE = 8,   /* the slot holds no live run */
+    TS_KV_SHARED_PAGE = 9  /* a slot's next row is in another run's page */
 } ts_kv_status;
 
 /* pool.rs:56-68. */
@@ -121,6 +124,42 @@ int ts_kv_prefixes_find(ts_kv_prefixes *prefixes, const ts_kv_pool *pool, uint64
 
 /* Entries held (after the last find's clean-up). */
 uint64_t ts_kv_prefixes_len(const ts_kv_prefixes *prefixes);
+
+/* ---------------------------------------------------------------------------
+ * Slots over the pool: which slot a prompt gets and how many of its rows the kept rows spare.
+ * Restates the engine's `Kept` (engine/engine/src/kept.rs:27-159), the caller of the pool and the prefix index.
+ * Dense: each slot is one page of `context` rows, a hit adopts the retained run (and with it the slot).
+ * Paged: slots share whole pages of `page` rows, a hit forks the retained run's pages into a free slot; skips come
+ * in whole pages, so no row ever moves.
+ * ------------------------------------------------------------------------- */
+typedef struct ts_kept_slots ts_kept_slots;
+
+typedef struct {
+    ts_kv_stats pool;
+    uint64_t hits, misses;
+} ts_kept_totals;
+
+ts_kept_slots *ts_kept_slots_dense(uint32_t slots, uint32_t context);                               /* kept.rs:43-55 */
+ts_kept_slots *ts_kept_slots_paged(uint32_t slots, uint32_t context, uint32_t pages, uint32_t page); /* kept.rs:57-67 */
+void ts_kept_slots_free(ts_kept_slots *kept);
+
+/* kept.rs:69-106: a slot for `prompt` and the rows it may skip (at most `limit`).  *admitted = 0 when no slot or no
+ * room is free (nothing changes then). */
+int ts_kept_slots_admit(ts_kept_slots *kept, const uint32_t *prompt, uint64_t prompt_len, uint64_t limit, uint32_t *slot,
+                        uint64_t *skip, int *admitted);
+
+/* kept.rs:133-148: paged: grows the slot's run to `rows` rows; when its lane lacks pages, writes the run's pages
+ * (at most `capacity`) and their count, else *count = 0.  Dense: *count = 0.  TS_KV_ROW_PLACE for a slot with no
+ * run, TS_KV_SHARED_PAGE when the growth would have to copy a shared page, the pool's errors otherwise. */
+int ts_kept_slots_grow(ts_kept_slots *kept, uint32_t slot, uint64_t rows, uint32_t *pages, uint32_t capacity,
+                       uint32_t *count);
+
+/* kept.rs:150-159: keeps the slot's rows under their tokens (the run is retained and indexed), or releases them when
+ * there are none or the pool refuses; the slot is free again. */
+int ts_kept_slots_finish(ts_kept_slots *kept, uint32_t slot, const uint32_t *history, uint64_t history_len);
+
+void ts_kept_slots_totals(const ts_kept_slots *kept, ts_kept_totals *out);                          /* kept.rs:125-131 */
+const ts_kv_pool *ts_kept_slots_pool(const ts_kept_slots *kept);
 
 #ifdef __cplusplus
 }

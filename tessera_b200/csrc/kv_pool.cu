@@ -457,5 +457,140 @@ int ts_kv_prefixes_find(ts_kv_prefixes *prefixes, const ts_kv_pool *pool, uint64
 
 uint64_t ts_kv_prefixes_len(const ts_kv_prefixes *prefixes) { return prefixes ? prefixes->kept.size() : 0; }
 
+// ---- slots over the pool (engine/engine/src/kept.rs:27-159) ----
+struct ts_kept_slots {
+    ts_kv_pool *pool = nullptr;
+    ts_kv_prefixes *index = nullptr;
+    uint64_t context = 0;
+    std::vector<std::optional<ts_kv_run>> runs;  // each slot's live run
+    bool paged = false;
+    std::vector<uint32_t> free_slots;            // paged: the free slots, the next one last
+    std::vector<size_t> laned;                   // paged: the pages each slot's lane names
+    uint64_t hits = 0, misses = 0;
+    ~ts_kept_slots() {
+        ts_kv_prefixes_free(index);
+        ts_kv_pool_free(pool);
+    }
+};
+
+static const uint64_t kKeptTag = 0;  // kept.rs:6
+
+ts_kept_slots *ts_kept_slots_dense(uint32_t slots, uint32_t context) {
+    if (slots == 0 || context == 0) return nullptr;
+    ts_kept_slots *k = new (std::nothrow) ts_kept_slots();
+    if (!k) return nullptr;
+    k->pool = ts_kv_pool_new(slots, context);
+    k->index = ts_kv_prefixes_new(0);
+    k->context = context;
+    k->runs.assign(slots, std::nullopt);
+    if (!k->pool || !k->index) {
+        delete k;
+        return nullptr;
+    }
+    return k;
+}
+
+ts_kept_slots *ts_kept_slots_paged(uint32_t slots, uint32_t context, uint32_t pages, uint32_t page) {
+    if (slots == 0 || context == 0 || pages == 0 || page == 0) return nullptr;
+    ts_kept_slots *k = new (std::nothrow) ts_kept_slots();
+    if (!k) return nullptr;
+    k->pool = ts_kv_pool_new(pages, page);
+    k->index = ts_kv_prefixes_new(page);
+    k->context = context;
+    k->runs.assign(slots, std::nullopt);
+    k->paged = true;
+    for (uint32_t s = slots; s-- > 0;) k->free_slots.push_back(s);  // (0..slots).rev(): slot 0 goes first
+    k->laned.assign(slots, 0);
+    if (!k->pool || !k->index) {
+        delete k;
+        return nullptr;
+    }
+    return k;
+}
+
+void ts_kept_slots_free(ts_kept_slots *kept) { delete kept; }
+
+int ts_kept_slots_admit(ts_kept_slots *k, const uint32_t *prompt, uint64_t prompt_len, uint64_t limit, uint32_t *slot,
+                        uint64_t *skip, int *admitted) {
+    if (!k || !slot || !skip || !admitted || (prompt_len > 0 && !prompt)) return TS_KV_BAD_ARGUMENT;
+    *admitted = 0;
+    *skip = 0;
+    ts_kv_run hit_run = {};
+    uint64_t hit_skip = 0;
+    int found = 0;
+    int rc = ts_kv_prefixes_find(k->index, k->pool, kKeptTag, prompt, prompt_len, limit, &hit_run, &hit_skip, &found);
+    if (rc != TS_KV_OK) return rc;
+    const uint64_t worst = k->context;
+    ts_kv_run run = {};
+    uint64_t got = 0;
+    if (!k->paged) {
+        bool have = found && ts_kv_adopt(k->pool, hit_run, hit_skip, worst, &run) == TS_KV_OK;
+        if (have) got = hit_skip;
+        else if (ts_kv_reserve(k->pool, kKeptTag, 1, worst, &run) != TS_KV_OK) return TS_KV_OK;  // no room: not admitted
+        uint32_t page = 0, count = 0;
+        if (ts_kv_pages(k->pool, run, &page, 1, &count) != TS_KV_OK || count == 0) return TS_KV_OK;
+        *slot = page;  // dense: the slot is the run's one page
+        k->runs[page] = run;
+    } else {
+        if (k->free_slots.empty()) return TS_KV_OK;
+        const uint32_t s = k->free_slots.back();
+        bool have = found && ts_kv_fork(k->pool, hit_run, hit_skip, worst, &run) == TS_KV_OK;
+        if (have) got = hit_skip;
+        else if (ts_kv_reserve(k->pool, kKeptTag, 0, worst, &run) != TS_KV_OK) return TS_KV_OK;
+        k->free_slots.pop_back();
+        k->runs[s] = run;
+        k->laned[s] = 0;
+        *slot = s;
+    }
+    *skip = got;
+    *admitted = 1;
+    (got == 0 ? k->misses : k->hits)++;
+    return TS_KV_OK;
+}
+
+int ts_kept_slots_grow(ts_kept_slots *k, uint32_t slot, uint64_t rows, uint32_t *pages, uint32_t capacity,
+                       uint32_t *count) {
+    if (!k || !count || slot >= k->runs.size()) return TS_KV_BAD_ARGUMENT;
+    *count = 0;
+    if (!k->paged) return TS_KV_OK;
+    if (!k->runs[slot]) return TS_KV_ROW_PLACE;
+    const ts_kv_run run = *k->runs[slot];
+    ts_kv_copy copies[2];
+    uint32_t n = 0;
+    int rc = ts_kv_grow(k->pool, run, rows, copies, 2, &n);
+    if (rc != TS_KV_OK) return rc;
+    if (n != 0) return TS_KV_SHARED_PAGE;  // runs share only whole pages, so no row moves
+    uint32_t have = 0;
+    rc = ts_kv_pages(k->pool, run, pages, pages ? capacity : 0, &have);
+    if (rc != TS_KV_OK) return rc;
+    const bool more = have != k->laned[slot];
+    k->laned[slot] = have;
+    *count = more ? have : 0;
+    return TS_KV_OK;
+}
+
+int ts_kept_slots_finish(ts_kept_slots *k, uint32_t slot, const uint32_t *history, uint64_t history_len) {
+    if (!k || slot >= k->runs.size() || (history_len > 0 && !history)) return TS_KV_BAD_ARGUMENT;
+    if (!k->runs[slot]) return TS_KV_OK;
+    const ts_kv_run run = *k->runs[slot];
+    k->runs[slot].reset();
+    if (k->paged) k->free_slots.push_back(slot);
+    ts_kv_copy copies[2];
+    uint32_t n = 0;
+    const bool grown = history_len > 0 && ts_kv_grow(k->pool, run, history_len, copies, 2, &n) == TS_KV_OK;
+    if (grown && ts_kv_retain(k->pool, run) == TS_KV_OK) ts_kv_prefixes_keep(k->index, run, history, history_len, history_len);
+    else ts_kv_release(k->pool, run);
+    return TS_KV_OK;
+}
+
+void ts_kept_slots_totals(const ts_kept_slots *k, ts_kept_totals *out) {
+    if (!k || !out) return;
+    ts_kv_get_stats(k->pool, &out->pool);
+    out->hits = k->hits;
+    out->misses = k->misses;
+}
+
+const ts_kv_pool *ts_kept_slots_pool(const ts_kept_slots *k) { return k ? k->pool : nullptr; }
+
 }  // extern "C"
 #pragma GCC visibility pop

@@ -31,6 +31,11 @@ class Stats(C.Structure):
     _fields_ = [(n, u64) for n in ("size", "active", "worst", "live_runs", "kept_runs")]
 
 
+class Totals(C.Structure):
+    """engine/engine/src/kept.rs:14-25."""
+    _fields_ = [("pool", Stats), ("hits", u64), ("misses", u64)]
+
+
 class _Begin(C.Structure):
     _fields_ = [("skip", u64), ("lcp", u64), ("why", i32)]
 
@@ -62,12 +67,21 @@ KV_SIGNATURES = {
     "ts_kv_prefixes_keep": (i32, [vp, Run, vp, u64, u64]),
     "ts_kv_prefixes_find": (i32, [vp, vp, u64, vp, u64, u64, C.POINTER(Run), C.POINTER(u64), C.POINTER(i32)]),
     "ts_kv_prefixes_len": (u64, [vp]),
+    "ts_kept_slots_dense": (vp, [u32, u32]),
+    "ts_kept_slots_paged": (vp, [u32, u32, u32, u32]),
+    "ts_kept_slots_free": (None, [vp]),
+    "ts_kept_slots_admit": (i32, [vp, vp, u64, u64, C.POINTER(u32), C.POINTER(u64), C.POINTER(i32)]),
+    "ts_kept_slots_grow": (i32, [vp, u32, u64, vp, u32, C.POINTER(u32)]),
+    "ts_kept_slots_finish": (i32, [vp, u32, vp, u64]),
+    "ts_kept_slots_totals": (None, [vp, vp]),
+    "ts_kept_slots_pool": (vp, [vp]),
 }
 for _name, (_res, _args) in KV_SIGNATURES.items():
     _fn = getattr(lib, _name)
     _fn.restype, _fn.argtypes = _res, _args
 
-ERRORS = {1: "NoRoom", 2: "PastWorst", 3: "PastSource", 4: "Live", 5: "Retained", 6: "Unknown", 7: "BadArgument"}
+ERRORS = {1: "NoRoom", 2: "PastWorst", 3: "PastSource", 4: "Live", 5: "Retained", 6: "Unknown", 7: "BadArgument",
+          8: "RowPlace", 9: "SharedPage"}
 
 
 class PoolError(Exception):
@@ -199,3 +213,49 @@ class Prefixes:
         if code:
             raise PoolError(code, 0)
         return (run, int(skip.value)) if found.value else None
+
+
+class KeptSlots:
+    """Which slot a prompt gets and how many of its rows the kept rows spare: the engine's `Kept`
+    (engine/engine/src/kept.rs:27-159) over the pool and the prefix index."""
+
+    def __init__(self, slots: int, context: int, pages: int | None = None, page: int | None = None):
+        """Dense (each slot one page of `context` rows) unless `pages` and `page` are given (slots share whole pages)."""
+        self.paged = pages is not None
+        self._h = lib.ts_kept_slots_paged(slots, context, pages, page) if self.paged else lib.ts_kept_slots_dense(slots, context)
+        if not self._h:
+            raise ValueError("slots, context, pages and page must be positive")
+        self.capacity = -(-context // page) if self.paged else 1
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            lib.ts_kept_slots_free(self._h)
+            self._h = None
+
+    def admit(self, prompt, limit: int):
+        """(slot, skip), or None while no slot or room is free (kept.rs:69-106)."""
+        p = _ids(prompt)
+        slot, skip, ok = u32(0), u64(0), i32(0)
+        code = lib.ts_kept_slots_admit(self._h, p.ctypes.data_as(vp), p.size, limit, C.byref(slot), C.byref(skip), C.byref(ok))
+        if code:
+            raise PoolError(code, 0)
+        return (int(slot.value), int(skip.value)) if ok.value else None
+
+    def grow(self, slot: int, rows: int):
+        """Paged: the slot's pages if its lane lacks some, else None (kept.rs:133-148)."""
+        pages, n = (u32 * self.capacity)(), u32(0)
+        code = lib.ts_kept_slots_grow(self._h, slot, rows, pages, self.capacity, C.byref(n))
+        if code:
+            raise PoolError(code, int(lib.ts_kv_last_detail(lib.ts_kept_slots_pool(self._h))))
+        return list(pages[: n.value]) if n.value else None
+
+    def finish(self, slot: int, history):
+        h = _ids(history)
+        code = lib.ts_kept_slots_finish(self._h, slot, h.ctypes.data_as(vp), h.size)
+        if code:
+            raise PoolError(code, 0)
+
+    def totals(self) -> Totals:
+        t = Totals()
+        lib.ts_kept_slots_totals(self._h, C.byref(t))
+        return t

@@ -161,3 +161,62 @@ def test_prefixes_find_newest_longest():
     pool.adopt(runs[1], 8, 12)
     assert kept.find(pool, T, prompt, 64) == (runs[0], 4) and len(kept) == 2
     assert pool.consistent()
+
+
+def test_kept_rows_resume():
+    # engine/engine/tests/engine_test.rs:331-360 at the level of the slots: two dense slots of 16 rows, three tokens
+    # made per request, one row fed per step.  A request feeds its prompt past the skip and all but the last token it
+    # makes; those fed tokens are its history.
+    from tessera_b200.kv import KeptSlots
+    kept = KeptSlots(slots=2, context=16)
+
+    def ask(prompt, made):
+        slot, skip = kept.admit(prompt, len(prompt) - 1)
+        history = list(prompt) + made[:-1]
+        assert kept.grow(slot, len(history)) is None          # dense: no lanes
+        kept.finish(slot, history)
+        return skip, len(history) - skip                       # rows spared, rows fed (= steps at one row a step)
+
+    first = [20, 21, 22]
+    longer = [3, 9, 4] + first
+    assert ask([3, 9, 4], first) == (0, 5)
+    assert ask(longer, [23, 24, 25]) == (5, 3)                 # everything but the last prompt row is kept
+    assert ask([3, 9, 7, 1], [26, 27, 28]) == (2, 4)           # the common rows of the one retained run
+    slot, skip = kept.admit(longer, len(longer) - 1)           # still in flight below
+    assert skip == 2                                           # Event::Kept(2): the adopting run was cut to two rows
+    t = kept.totals()
+    assert (t.hits, t.misses) == (3, 1)
+    assert (t.pool.size, t.pool.active) == (32, 16)
+
+
+def test_paged_slots_share():
+    # engine/engine/tests/engine_test.rs:362-385: 16-row pages, two slots of 64 rows; both later prompts start at the
+    # kept answer's first page and take a page of their own for the rest
+    from tessera_b200.kv import KeptSlots
+    kept = KeptSlots(slots=2, context=64, pages=8, page=16)
+    base = [(i * 7 + 3) % 32 for i in range(20)]
+    slot, skip = kept.admit(base, len(base) - 1)
+    assert (slot, skip) == (0, 0)
+    lanes = []
+    for rows in range(1, 23):                                  # 20 prompt rows and two fed answers: 22 steps
+        got = kept.grow(slot, rows)
+        if got is not None:
+            lanes.append((rows, got))
+    assert [r for r, _ in lanes] == [1, 17] and lanes[1][1][0] == lanes[0][1][0]   # a page at row 1, another at row 17
+    first_page = lanes[0][1][0]
+    kept.finish(slot, base + [40, 41])
+    a, b = base[:18] + [1, 2], base[:17] + [5]
+    (sa, ka), (sb, kb) = kept.admit(a, len(a) - 1), kept.admit(b, len(b) - 1)
+    assert (ka, kb) == (16, 16) and {sa, sb} == {0, 1}
+    assert kept.admit([1, 2, 3], 2) is None                    # no slot left
+    pa, pb = kept.grow(sa, 17), kept.grow(sb, 17)
+    assert pa[0] == pb[0] == first_page and pa[1] != pb[1]     # the shared page, then one each
+    fed = (len(a) + 2 - ka) + (len(b) + 2 - kb)
+    assert fed == 10                                           # the reference's step count for the second round
+    kept.finish(sa, a + [50, 51])
+    kept.finish(sb, b + [60, 61])
+    t = kept.totals()
+    assert (t.hits, t.misses) == (2, 1) and t.pool.live_runs == 0 and t.pool.kept_runs == 3
+    with pytest.raises(PoolError) as e:
+        kept.grow(0, 5)                                        # a finished slot has no run
+    assert e.value.kind == "RowPlace"
