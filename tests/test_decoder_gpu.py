@@ -225,3 +225,29 @@ def test_prefix_reuse_through_the_page_pool():
     fresh.close()
     assert rel_error(hidden, want_hidden) <= 1e-2
     assert got == want
+
+
+@pytest.mark.parametrize("page", [16, 0])
+def test_sessions_continue_kept_rows(page):
+    """tessera_b200/sessions.py on the device: answers that continue rows an earlier answer left (paged: borrowed
+    whole pages; dense: the adopted slot) equal the answers of feeding every prompt whole (the reference's
+    kept_rows_resume and paged_slots_share, engine/engine/tests/engine_test.rs:331-385)."""
+    from tessera_b200.sessions import Sessions
+    cfg, context, new = SMALL, 64, 3
+    rng = np.random.default_rng(31)
+    base = rng.integers(0, cfg["vocab"], size=24).tolist()
+    prompts = [base, base[:20] + [1, 2], base[:17] + [5], rng.integers(0, cfg["vocab"], size=6).tolist()]
+    want = []
+    for p in prompts:
+        fresh = _device(cfg, 9, slots=1, context=context, max_rows=32, gains="near_one", page=page)
+        want.append(fresh.generate([p], new)[0].tolist())
+        fresh.close()
+    dec = _device(cfg, 9, slots=2, context=context, max_rows=32, gains="near_one", page=page)
+    s = Sessions(dec)
+    got = s.generate(prompts[:1], new) + s.generate(prompts[1:], new)   # the later three find the first one's rows
+    dec.close()
+    assert got == want
+    t = s.totals()
+    # paged: both later prompts fork the first answer's page; dense: the first of them adopts its slot, the other
+    # finds nothing retained
+    assert (t.hits, t.misses) == ((2, 2) if page else (1, 3))
