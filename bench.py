@@ -357,7 +357,8 @@ def run_ours(args, rank, world, local_rank):
     algo = kernel_bytes(top, cfg, BATCH, int(BATCH * ctx_prof))
     achieved = algo / in_step_s(top) / 1e9
     roofline = {"kernel": top, "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "traffic": (NCU_TRAFFIC_RATIO[top] * algo if top in NCU_TRAFFIC_RATIO else None),
+                "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "frac_of_nominal_8tbs": achieved / 8000.0,
+                "traffic": (NCU_TRAFFIC_RATIO[top] * algo if top in NCU_TRAFFIC_RATIO else None),
                 "algorithmic_bytes_per_launch": algo, "avg_launch_us": in_step_s(top) * 1e6,
                 "duration": "interval between CUDA events recorded after every kernel (launches serialised), less the "
                             "average gap serialising adds per launch = (serialised step - timed step) / launches per step",
