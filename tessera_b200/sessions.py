@@ -2,8 +2,9 @@
 
 The host loop around the decode step, as the reference's scheduler runs it (engine/engine/src/schedule.rs:227-345):
 a waiting prompt is admitted to a slot (`KeptSlots.admit`, engine/engine/src/kept.rs:69-106) and skips the rows an
-earlier answer left in the kept rows; every step feeds each active sequence its pending prompt rows (as many as the
-launch has room for) or the token it made last; before the launch each fed slot gets the pages its rows need
+earlier answer left in the kept rows; every step feeds the rows the `Fair` policy picks (every decoding sequence the
+token it made last, then the prompts a token each in turn within the step's row budget, schedule.rs:127-153);
+before the launch each fed slot gets the pages its rows need
 (`KeptSlots.grow`, the table as `Lanes.set`, engine/engine/src/lanes.rs:41-46); a finished sequence's rows stay under
 the tokens that were fed (`KeptSlots.finish`).  The decoder is anything with `step(tokens, slots, positions,
 out_rows)`, `set_table(table)` and `slots`, `context`, `max_rows`, `page`, `pages` (tessera_b200.runner.Decoder).
@@ -20,18 +21,48 @@ from .kv import KeptSlots
 
 @dataclass
 class _Seq:
+    """An answer in flight, in its slot (schedule.rs:17-31)."""
     index: int               # place in the caller's list
     slot: int
-    pending: deque           # prompt tokens not fed yet
+    pending: deque           # tokens to feed: the prompt past the skip, then each token made
     fed: int                 # rows of this sequence in the kept rows
     history: list            # the tokens behind those rows
     want: int
     made: list = field(default_factory=list)
 
+    def prefilling(self) -> bool:
+        return len(self.pending) > 1
+
+
+def fair(seqs: list, budget: int, most: int) -> dict:
+    """Rows per sequence for the next step: decodes first, then a prompt token each in turn while the step has
+    fewer than `budget` rows (`Fair`, schedule.rs:127-153).  `most` is the launch's own limit, which decodes count
+    against too."""
+    take = {id(s): 1 for s in seqs if s.pending and not s.prefilling()}
+    take = dict(list(take.items())[:most])
+    rows = len(take)
+    prompts = [s for s in seqs if s.prefilling()]
+    for s in prompts:
+        take[id(s)] = 0
+    while True:
+        more = False
+        for s in prompts:
+            if take[id(s)] < len(s.pending) and rows < min(budget, most):
+                take[id(s)] += 1
+                rows += 1
+                more = True
+        if not more:
+            return take
+
 
 class Sessions:
-    def __init__(self, decoder, reuse: bool = True):
+    def __init__(self, decoder, reuse: bool = True, budget: int | None = None):
+        """`budget`: the most rows one step feeds to prompts (the scheduler's budget, schedule.rs:166-167); the
+        decoder's `max_rows` by default."""
         self.dec, self.reuse = decoder, reuse
+        self.budget = decoder.max_rows if budget is None else budget
+        if self.budget < 1:
+            raise ValueError("a step feeds at least one row")
         d = decoder
         if d.page:
             self.kept = KeptSlots(d.slots, d.context, pages=d.slots * d.pages, page=d.page)
@@ -60,6 +91,8 @@ class Sessions:
 
     def generate(self, prompts: list, new: int) -> list:
         """`new` greedy tokens for each prompt; prompts wait while every slot is taken."""
+        if new < 1:
+            raise ValueError("an answer has at least one token")
         waiting = deque((i, [int(t) for t in p]) for i, p in enumerate(prompts))
         active: list = []
         out = [None] * len(prompts)
@@ -67,40 +100,37 @@ class Sessions:
             self._admit(waiting, active, new)
             if not active:
                 raise RuntimeError("nothing can be admitted: the pool has no room for one more sequence")
-            tokens, slots, positions, out_rows, owners = [], [], [], [], []
-            room = self.dec.max_rows
-            for seq in active:
-                if room == 0:
-                    break
-                if seq.pending:
-                    n = min(len(seq.pending), room)
-                    feed = [seq.pending.popleft() for _ in range(n)]
-                else:
-                    feed = [seq.made[-1]]
-                    n = 1
-                room -= n
-                tokens += feed
+            take = fair(active, self.budget, self.dec.max_rows)
+            tokens, slots, positions, ends, owners = [], [], [], [], []
+            for seq in active:                     # a sequence's rows side by side, in position order
+                n = take.get(id(seq), 0)
+                if n == 0:
+                    continue
+                tokens += [seq.pending[i] for i in range(n)]
                 slots += [seq.slot] * n
                 positions += list(range(seq.fed, seq.fed + n))
-                seq.history += feed
-                seq.fed += n
-                pages = self.kept.grow(seq.slot, seq.fed)
+                pages = self.kept.grow(seq.slot, seq.fed + n)          # Sched::page, schedule.rs:311-322
                 if pages is not None:
                     first = seq.slot * self.dec.pages
                     self.table[first:first + len(pages)] = pages
                     self.stale = True
-                if not seq.pending:               # the sequence's newest row makes its next token
-                    out_rows.append(len(tokens) - 1)
-                    owners.append(seq)
+                ends.append(len(tokens) - 1)
+                owners.append((seq, n))
             if self.stale:
                 self.dec.set_table(self.table)
                 self.stale = False
-            ids = self.dec.step(tokens, slots, positions, out_rows=out_rows or [len(tokens) - 1])
+            ids = self.dec.step(tokens, slots, positions, out_rows=ends)
             self.steps += 1
-            for seq, token in zip(owners, ids):
+            for (seq, n), token in zip(owners, ids):                   # Seq::advance, schedule.rs:52-76
+                seq.history += [seq.pending.popleft() for _ in range(n)]
+                seq.fed += n
+                if seq.pending:
+                    continue                                           # more of the prompt to feed: the id is not used
                 seq.made.append(int(token))
-                if len(seq.made) == seq.want:
+                if len(seq.made) >= seq.want:
                     out[seq.index] = seq.made
-                    self.kept.finish(seq.slot, seq.history)
+                    self.kept.finish(seq.slot, seq.history)            # Sched::retire
                     active.remove(seq)
+                else:
+                    seq.pending.append(int(token))
         return out

@@ -88,3 +88,45 @@ def test_prompts_that_cannot_fit_are_refused():
         s.generate([list(range(15))], 4)
     with pytest.raises(ValueError):
         s.generate([[]], 1)
+
+
+def test_step_counts_of_the_reference_cases():
+    # engine/engine/tests/engine_test.rs:331-385 with its budget of one prompt row a step: the steps each request
+    # takes are the rows it feeds (prompt past the skip, then all but the last token it makes)
+    dec = KeptTokens(slots=2, context=16, max_rows=16, page=0)
+    s = Sessions(dec, budget=1)
+
+    def asked(prompts):
+        before = s.steps
+        return s.generate(prompts, 3), s.steps - before
+
+    first, steps = asked([[3, 9, 4]])
+    assert steps == 5
+    longer = [3, 9, 4] + first[0]
+    assert asked([longer])[1] == 3 and asked([[3, 9, 7, 1]])[1] == 4
+    t = s.totals()
+    assert (t.hits, t.misses) == (2, 1)
+
+    paged = Sessions(KeptTokens(slots=2, context=64, max_rows=64, page=16), budget=1)
+    base = [(i * 7 + 3) % 32 for i in range(20)]
+    before = paged.steps
+    paged.generate([base], 3)
+    assert paged.steps - before == 22
+    before = paged.steps
+    got = paged.generate([base[:18] + [1, 2], base[:17] + [5]], 3)
+    assert paged.steps - before == 10          # both start at the kept answer's first page; their rows share steps
+    assert got == [alone(base[:18] + [1, 2], 3), alone(base[:17] + [5], 3)]
+
+
+def test_fair_feeds_decodes_first_then_prompts_in_turn():
+    from collections import deque
+    from tessera_b200.sessions import _Seq, fair
+    a = _Seq(0, 0, deque([7]), 9, [], 3)                 # decoding
+    b = _Seq(1, 1, deque(range(10)), 0, [], 3)           # ten prompt rows
+    c = _Seq(2, 2, deque(range(3)), 0, [], 3)            # three
+    take = fair([b, a, c], budget=6, most=64)
+    assert (take[id(a)], take[id(b)], take[id(c)]) == (1, 3, 2)     # 1 decode, then b c b c b: six rows
+    take = fair([b, a, c], budget=64, most=64)
+    assert (take[id(a)], take[id(b)], take[id(c)]) == (1, 10, 3)
+    take = fair([b, a, c], budget=64, most=4)                        # the launch itself holds four rows
+    assert sum(take.values()) == 4 and take[id(a)] == 1
