@@ -259,3 +259,7 @@ class KeptSlots:
         t = Totals()
         lib.ts_kept_slots_totals(self._h, C.byref(t))
         return t
+
+    def consistent(self) -> bool:
+        """The pool's self-check (page counts, owners and promises add up)."""
+        return bool(lib.ts_kv_consistent(lib.ts_kept_slots_pool(self._h)))

@@ -130,3 +130,33 @@ def test_fair_feeds_decodes_first_then_prompts_in_turn():
     assert (take[id(a)], take[id(b)], take[id(c)]) == (1, 10, 3)
     take = fair([b, a, c], budget=64, most=4)                        # the launch itself holds four rows
     assert sum(take.values()) == 4 and take[id(a)] == 1
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_rounds_of_related_prompts(seed):
+    # prompts cut from a few stems at random lengths, in random-sized rounds, random page and budget: whatever
+    # was kept, borrowed, adopted or reclaimed on the way, every answer equals the one of a decoder used once
+    rng = np.random.default_rng(100 + seed)
+    page = int(rng.choice([0, 16, 64]))
+    slots, context = int(rng.integers(1, 4)), 128
+    dec = KeptTokens(slots, context, max_rows=int(rng.choice([8, 32, 128])), page=page)
+    s = Sessions(dec, budget=int(rng.choice([1, 5, 128])))
+    stems = [rng.integers(0, 900, size=100).tolist() for _ in range(3)]
+    asked = 0
+    for _ in range(8):
+        prompts = []
+        for _ in range(int(rng.integers(1, 5))):
+            stem = stems[int(rng.integers(0, 3))]
+            cut = int(rng.integers(1, 100))
+            tail = rng.integers(0, 900, size=int(rng.integers(0, 6))).tolist()
+            prompts.append(stem[:cut] + tail)
+        new = int(rng.integers(1, 5))
+        assert s.generate(prompts, new) == [alone_in(context, p, new) for p in prompts]
+        assert s.kept.consistent()
+        asked += len(prompts)
+    t = s.totals()
+    assert t.hits + t.misses == asked and t.pool.live_runs == 0
+
+
+def alone_in(context, prompt, new):
+    return Sessions(KeptTokens(1, context, context, 0), reuse=False).generate([prompt], new)[0]
