@@ -97,6 +97,46 @@ int ts_decoder_prepare(ts_decoder *dec, uint32_t rows, void *stream);
 int ts_decoder_profile(ts_decoder *dec, uint32_t steps, void *stream);
 int ts_decoder_take_profile(ts_decoder *dec, char *out, size_t capacity);
 
+/* The configuration the decoder was created with. */
+int ts_decoder_get_config(const ts_decoder *dec, ts_decoder_config *out);
+
+/* ---------------------------------------------------------------------------
+ * The request loop over a decoder whose kept rows outlive the request that wrote them: the reference's
+ * scheduler (engine/engine/src/schedule.rs:122-153, 227-345, 383-416) with its `Fair` policy, over
+ * ts_kept_slots_*.  A waiting prompt is admitted to a slot and skips the rows an earlier answer left; every step
+ * feeds each decoding sequence the token it made last, then the prompts a token each in turn while the step has
+ * fewer than `budget` rows; before the launch each fed slot gets the pages its rows need; a finished sequence's
+ * rows stay under the tokens that were fed.  The loop drives anything that steps rows: a ts_decoder, or a host's own
+ * stepper (tests drive it with a stand-in that needs no GPU).
+ * ------------------------------------------------------------------------- */
+typedef struct {
+    void *self;
+    uint32_t slots, context, max_rows;
+    uint32_t page;            /* rows per page, 0 = dense kept rows */
+    /* rows in, the greedy id of each row listed in out_rows out; 0 = ok */
+    int (*step)(void *self, const uint32_t *tokens, const uint32_t *slots, const uint32_t *positions, uint32_t rows,
+                const uint32_t *out_rows, uint32_t n_out, uint32_t *out_ids);
+    /* paged only: the whole table, slots * ceil(context / page) entries */
+    int (*set_table)(void *self, const uint32_t *table, uint32_t entries);
+} ts_stepper;
+
+typedef struct ts_sessions ts_sessions;
+
+/* reuse = 0: prompts never skip rows (the kept rows are still retained and reclaimed).  budget = 0: max_rows. */
+ts_sessions *ts_sessions_new(const ts_stepper *stepper, int reuse, uint32_t budget);
+ts_sessions *ts_sessions_on_decoder(ts_decoder *dec, int reuse, uint32_t budget);
+void ts_sessions_free(ts_sessions *sessions);
+
+/* `new_tokens` greedy tokens for each of `n_prompts` prompts (tokens packed, prompt i = tokens[offsets[i] ..
+ * offsets[i + 1])); prompts wait while every slot is taken.  out [n_prompts, new_tokens].  TS_ERR_BAD_INPUT for an
+ * empty prompt or one that does not fit the context with its answer; a failing step's status otherwise. */
+int ts_sessions_generate(ts_sessions *sessions, const uint32_t *tokens, const uint64_t *offsets, uint32_t n_prompts,
+                         uint32_t new_tokens, uint32_t *out);
+
+uint64_t ts_sessions_steps(const ts_sessions *sessions);
+void ts_sessions_totals(const ts_sessions *sessions, ts_kept_totals *out);
+int ts_sessions_consistent(const ts_sessions *sessions);
+
 #ifdef __cplusplus
 }
 #endif

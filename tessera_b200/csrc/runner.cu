@@ -681,6 +681,12 @@ uint32_t ts_decoder_launches_per_step(ts_decoder *d, uint32_t rows, uint32_t key
 
 uint64_t ts_decoder_graph_replays(ts_decoder *d) { return d ? d->replays : 0; }
 
+int ts_decoder_get_config(const ts_decoder *d, ts_decoder_config *out) {
+    TS_REQUIRE(d && out, "decoder config: NULL argument");
+    *out = d->c;
+    return TS_OK;
+}
+
 int ts_decoder_prepare(ts_decoder *d, uint32_t rows, void *stream) {
     TS_REQUIRE(d, "decoder: NULL");
     TS_REQUIRE(rows >= 1 && rows <= d->c.max_rows && rows <= d->max_out, "decoder prepare: %u rows, the plan takes 1..%u",

@@ -32,6 +32,15 @@ RUN_SIGNATURES = {
     "ts_decoder_prepare": (i32, [vp, u32, vp]),
     "ts_decoder_profile": (i32, [vp, u32, vp]),
     "ts_decoder_take_profile": (i32, [vp, C.c_char_p, sz]),
+    "ts_decoder_get_config": (i32, [vp, C.POINTER(DecoderConfig)]),
+    # the request loop (tessera_b200/sessions.py binds the stepper's callback types)
+    "ts_sessions_new": (vp, [vp, i32, u32]),
+    "ts_sessions_on_decoder": (vp, [vp, i32, u32]),
+    "ts_sessions_free": (None, [vp]),
+    "ts_sessions_generate": (i32, [vp, vp, vp, u32, u32, vp]),
+    "ts_sessions_steps": (C.c_uint64, [vp]),
+    "ts_sessions_totals": (None, [vp, vp]),
+    "ts_sessions_consistent": (i32, [vp]),
 }
 for _name, (_res, _args) in RUN_SIGNATURES.items():
     _fn = getattr(lib, _name)

@@ -227,12 +227,13 @@ def test_prefix_reuse_through_the_page_pool():
     assert got == want
 
 
+@pytest.mark.parametrize("native", [False, True])
 @pytest.mark.parametrize("page", [16, 0])
-def test_sessions_continue_kept_rows(page):
+def test_sessions_continue_kept_rows(page, native):
     """tessera_b200/sessions.py on the device: answers that continue rows an earlier answer left (paged: borrowed
     whole pages; dense: the adopted slot) equal the answers of feeding every prompt whole (the reference's
     kept_rows_resume and paged_slots_share, engine/engine/tests/engine_test.rs:331-385)."""
-    from tessera_b200.sessions import Sessions
+    from tessera_b200.sessions import NativeSessions, Sessions
     cfg, context, new = SMALL, 64, 3
     rng = np.random.default_rng(31)
     base = rng.integers(0, cfg["vocab"], size=24).tolist()
@@ -243,11 +244,12 @@ def test_sessions_continue_kept_rows(page):
         want.append(fresh.generate([p], new)[0].tolist())
         fresh.close()
     dec = _device(cfg, 9, slots=2, context=context, max_rows=32, gains="near_one", page=page)
-    s = Sessions(dec)
+    s = (NativeSessions if native else Sessions)(dec)   # the loop in the library (ts_sessions_*), or in Python
     got = s.generate(prompts[:1], new) + s.generate(prompts[1:], new)   # the later three find the first one's rows
+    t = s.totals()
+    del s
     dec.close()
     assert got == want
-    t = s.totals()
     # paged: both later prompts fork the first answer's page; dense: the first of them adopts its slot, the other
     # finds nothing retained
     assert (t.hits, t.misses) == ((2, 2) if page else (1, 3))

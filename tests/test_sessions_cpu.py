@@ -160,3 +160,43 @@ def test_random_rounds_of_related_prompts(seed):
 
 def alone_in(context, prompt, new):
     return Sessions(KeptTokens(1, context, context, 0), reuse=False).generate([prompt], new)[0]
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_the_library_loop_equals_the_python_loop(seed):
+    # ts_sessions_* (csrc/sessions.cu) driven through callbacks by the stand-in decoder: the same answers, the same
+    # launches row for row, the same steps and totals as tessera_b200.sessions.Sessions
+    from tessera_b200.sessions import NativeSessions
+    rng = np.random.default_rng(200 + seed)
+    page = int(rng.choice([0, 16, 64]))
+    slots, context, rows = int(rng.integers(1, 4)), 128, int(rng.choice([8, 32, 128]))
+    budget = int(rng.choice([1, 5, 128]))
+    a, b = KeptTokens(slots, context, rows, page), KeptTokens(slots, context, rows, page)
+    py, lib = Sessions(a, budget=budget), NativeSessions(b, budget=budget)
+    stems = [rng.integers(0, 900, size=100).tolist() for _ in range(3)]
+    for _ in range(6):
+        prompts = [stems[int(rng.integers(0, 3))][: int(rng.integers(1, 100))] + rng.integers(0, 900, size=int(rng.integers(0, 6))).tolist()
+                   for _ in range(int(rng.integers(1, 5)))]
+        new = int(rng.integers(1, 5))
+        assert lib.generate(prompts, new) == py.generate(prompts, new)
+        assert lib.consistent()
+    assert a.launches == b.launches and lib.steps == py.steps
+    tp, tl = py.totals(), lib.totals()
+    assert (tp.hits, tp.misses, tp.pool.kept_runs) == (tl.hits, tl.misses, tl.pool.kept_runs)
+
+
+def test_the_library_loop_refuses_and_reports():
+    from tessera_b200 import TesseraError
+    from tessera_b200.sessions import NativeSessions
+    s = NativeSessions(KeptTokens(1, 16, 16, 0))
+    with pytest.raises(TesseraError):
+        s.generate([list(range(15))], 4)           # does not fit the context with its answer
+    with pytest.raises(TesseraError):
+        s.generate([[]], 1)
+
+    class Broken(KeptTokens):
+        def step(self, *a, **k):
+            raise RuntimeError("the device fell over")
+
+    with pytest.raises(RuntimeError, match="fell over"):
+        NativeSessions(Broken(1, 16, 16, 0)).generate([[1, 2, 3]], 2)
