@@ -335,6 +335,13 @@ int ts_set_pdl(int enabled);
  * kind of record).  Synchronises the device. */
 int ts_device_status(void);
 
+/* Runs a one-block kernel whose only act is a bounded wait on a barrier nothing arrives at, with `wait_ns`
+ * as the bound, and waits for it.  The wait gives up, and the next ts_device_status() reads TS_ERR_TIMEOUT: the
+ * give-up path every waiting kernel of this library shares (bounded poll -> flag -> status word), made
+ * observable without a fault or a hang.  The reference tests its bounded spins the same way, against a
+ * flag nothing sets (engine/rules/device/include/tessera/status.h:9-39). */
+int ts_wait_runs_out(uint64_t wait_ns, void *stream);
+
 /* ---------------------------------------------------------------------------
  * Launch by the reference's kernel names.  `args` is the list the reference's runner builds for a planned
  * launch, in the kernel's parameter order: read buffers, the output buffer, the page table if the kept layout

@@ -97,6 +97,13 @@ int ts_decoder_prepare(ts_decoder *dec, uint32_t rows, void *stream);
 int ts_decoder_profile(ts_decoder *dec, uint32_t steps, void *stream);
 int ts_decoder_take_profile(ts_decoder *dec, char *out, size_t capacity);
 
+/* Decode steps of at most 64 rows, one row per slot, at head width 128 run their gather and whole layer stack as
+ * one persistent kernel (every SM resident, phases separated by a bounded device-wide barrier, weights streamed
+ * across the phases); `on` = 0 keeps one launch per product instead (the reference's plan of launches,
+ * engine/models/src/decoder.rs:281-389, one kernel per step of it).  Returns 1 when the persistent kernel exists
+ * for this decoder's shapes, 0 when it does not.  Captured graphs of the other form are dropped. */
+int ts_decoder_use_step_kernel(ts_decoder *dec, int on);
+
 /* The configuration the decoder was created with. */
 int ts_decoder_get_config(const ts_decoder *dec, ts_decoder_config *out);
 

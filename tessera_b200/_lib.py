@@ -55,6 +55,7 @@ SIGNATURES = {
     "ts_abi_version": (i32, []),
     "ts_set_pdl": (i32, [i32]),
     "ts_device_status": (i32, []),
+    "ts_wait_runs_out": (i32, [C.c_uint64, vp]),
     "ts_linear_workspace_bytes": (sz, [u32, u32, u32, i32, i32]),
     "ts_linear_bf16": (i32, [vp, vp, vp, vp, u32, u32, u32, i32, f32, i32, i32, vp, sz, vp]),
     "ts_gather_scaled_bf16": (i32, [vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, vp]),

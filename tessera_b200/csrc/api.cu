@@ -21,20 +21,25 @@ int fail(int code, const char *fmt, ...) {
     return code;
 }
 
-int sm_count() {
-    static int cached = 0;
-    if (cached == 0) {
-        int dev = 0, n = 0;
-        if (cudaGetDevice(&dev) == cudaSuccess &&
-            cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
-            cached = n;
-        else
-            return 148;  // B200; only reached without a device, where nothing launches anyway
-    }
-    return cached;
+int current_device() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) return 0;
+    return dev;
 }
 
-static bool g_pdl = false;
+int sm_count() {
+    static std::atomic<int> cached[256] = {};
+    const int dev = current_device() & 255;
+    int n = cached[dev].load(std::memory_order_relaxed);
+    if (n == 0) {
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+            return 148;  // B200; only reached without a device, where nothing launches anyway
+        cached[dev].store(n, std::memory_order_relaxed);
+    }
+    return n;
+}
+
+static thread_local bool g_pdl = false;  // per host thread: a runner on another thread keeps its own setting
 bool pdl_enabled() { return g_pdl; }
 void set_pdl(bool enabled) { g_pdl = enabled; }
 
@@ -164,8 +169,13 @@ int ts_set_pdl(int enabled) {
 
 int ts_device_status(void) {
     const int a = umma_take_status(), b = stream_take_status(), c = flash_take_status(), d = moe_take_status();
-    const int e = rows_take_status(), f = pair_take_status();
-    return a ? a : b ? b : c ? c : d ? d : e ? e : f;
+    const int e = rows_take_status(), f = pair_take_status(), g = step_take_status();
+    return a ? a : b ? b : c ? c : d ? d : e ? e : f ? f : g;
+}
+
+int ts_wait_runs_out(uint64_t wait_ns, void *stream) {
+    TS_REQUIRE(wait_ns > 0 && wait_ns <= 1000000000ull, "wait_runs_out: the bound must be within (0, 1 s]");
+    return wait_runs_out(wait_ns, (cudaStream_t)stream);
 }
 
 size_t ts_linear_workspace_bytes(uint32_t m, uint32_t n, uint32_t k, int epilogue, int path) {

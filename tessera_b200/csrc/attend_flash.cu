@@ -834,11 +834,11 @@ static int launch_flash(const void *q, const void *k, const void *v, const Flash
     if (rc != TS_OK) return rc;
     rc = make_tensor_map_2d(&map_v, v, total_k, (uint64_t)p.kv_heads * D, (uint64_t)p.kv_heads * D, Sh::BK, 64);
     if (rc != TS_OK) return rc;
-    static bool configured = false;
-    if (!configured) {
+    static OncePerDevice configured;
+    if (configured.needs()) {
         TS_CUDA(cudaFuncSetAttribute(attend_flash_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Sh::total));
         TS_CUDA(cudaFuncSetAttribute(attend_flash2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Flash2Shape::total));
-        configured = true;
+        configured.done();
     }
     cudaError_t e;
     const uint64_t items = (uint64_t)((p.q_tiles + 1) / 2) * p.heads * p.seqs;

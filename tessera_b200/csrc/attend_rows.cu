@@ -979,10 +979,10 @@ template <int G>
 int launch_rows_tma(const CUtensorMap &map_k, const CUtensorMap &map_v, const RowsParams &p, uint32_t items,
                     cudaStream_t stream) {
     using Sh = TmaShared<G>;
-    static bool configured = false;
-    if (!configured) {
+    static OncePerDevice configured;
+    if (configured.needs()) {
         TS_CUDA(cudaFuncSetAttribute(attend_rows_tma_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Sh::bytes));
-        configured = true;
+        configured.done();
     }
     int *status = nullptr;
     TS_CUDA(cudaGetSymbolAddress((void **)&status, g_rows_status));
@@ -999,10 +999,10 @@ template <int G, int CW>
 int launch_rows_mma(const CUtensorMap &map_k, const CUtensorMap &map_v, const RowsParams &p, uint32_t items,
                     cudaStream_t stream) {
     using Sh = MmaShared<G, CW>;
-    static bool configured = false;
-    if (!configured) {
+    static OncePerDevice configured;
+    if (configured.needs()) {
         TS_CUDA(cudaFuncSetAttribute(attend_rows_mma_kernel<G, CW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Sh::bytes));
-        configured = true;
+        configured.done();
     }
     int *status = nullptr;
     TS_CUDA(cudaGetSymbolAddress((void **)&status, g_rows_status));

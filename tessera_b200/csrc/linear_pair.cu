@@ -319,8 +319,9 @@ int pair_take_status() {
 // Pairs of SMs that can hold a cluster of two of these blocks at the same time (not every SM has a partner
 // on a part with disabled SMs); persistent pairs beyond that number would only queue behind the others.
 uint32_t pair_slots() {
-    static uint32_t cached = 0;
-    if (cached) return cached;
+    static std::atomic<uint32_t> per_device[256] = {};
+    std::atomic<uint32_t> &cached = per_device[current_device() & 255];
+    if (const uint32_t have = cached.load(std::memory_order_relaxed)) return have;
     cudaFuncSetAttribute(linear_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((uint32_t)sm_count() / 2 * 2);
@@ -336,8 +337,8 @@ uint32_t pair_slots() {
     int clusters = 0;
     if (cudaOccupancyMaxActiveClusters(&clusters, linear_pair_kernel, &cfg) != cudaSuccess || clusters <= 0)
         clusters = sm_count() / 2;
-    cached = (uint32_t)clusters;
-    return cached;
+    cached.store((uint32_t)clusters, std::memory_order_relaxed);
+    return (uint32_t)clusters;
 }
 
 // Worth it from a few hundred rows on: below that the 256-row tile wastes more than the pairing saves.
@@ -394,10 +395,10 @@ int linear_pair(const void *x, const void *w, const void *a0, void *out, uint32_
     int *status = nullptr;
     TS_CUDA(cudaGetSymbolAddress((void **)&status, g_pair_status));
     p.status = status;
-    static bool configured = false;
-    if (!configured) {
+    static OncePerDevice configured;
+    if (configured.needs()) {
         TS_CUDA(cudaFuncSetAttribute(linear_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal));
-        configured = true;
+        configured.done();
     }
     const uint32_t tiles = p.tiles_i * p.tiles_j;
     const uint32_t pairs = std::min<uint32_t>(tiles, pair_slots());

@@ -287,11 +287,11 @@ bool skinny_supports(uint32_t m, uint32_t n, uint32_t k, int epilogue) {
 template <int NT, int DEPTH>
 static cudaError_t launch_skinny(const SkinnyParams &p, const SkinnyPlan &s, cudaStream_t stream) {
     auto kernel = linear_skinny_kernel<NT, DEPTH>;
-    static bool configured = false;
-    if (!configured) {
+    static OncePerDevice configured;
+    if (configured.needs()) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) return e;
-        configured = true;
+        configured.done();
     }
     return launch(kernel, dim3(s.blocks, s.splits), dim3(kThreads), s.smem, stream, pdl_enabled(), p);
 }

@@ -543,11 +543,11 @@ template <uint32_t BN, bool FUSED>
 cudaError_t launch_stream(const CUtensorMap &mw, const CUtensorMap &mx, const StreamParams &p, const StreamPlan &s,
                           cudaStream_t stream) {
     auto kernel = linear_stream_kernel<BN, FUSED>;
-    static bool configured = false;
-    if (!configured) {
+    static OncePerDevice configured;
+    if (configured.needs()) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
         if (e != cudaSuccess) return e;
-        configured = true;
+        configured.done();
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(s.blocks, s.splits);

@@ -465,11 +465,11 @@ template <uint32_t BN>
 cudaError_t launch_umma(const CUtensorMap &ma, const CUtensorMap &mb, const UmmaParams &p, const UmmaPlan &s,
                         cudaStream_t stream) {
     auto kernel = linear_umma_kernel<BN>;
-    static bool configured = false;
-    if (!configured) {
+    static OncePerDevice configured;
+    if (configured.needs()) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
         if (e != cudaSuccess) return e;
-        configured = true;
+        configured.done();
     }
     return launch(kernel, dim3(s.blocks, s.splits), dim3(kThreads), s.layout.total, stream, pdl_enabled(), ma,
                   mb, p);

@@ -419,10 +419,10 @@ int launch_grouped(const void *w, const void *x, void *out, const MoeWorkspace &
     int *status = nullptr;
     TS_CUDA(cudaGetSymbolAddress((void **)&status, g_moe_status));
     p.status = status;
-    static bool configured = false;
-    if (!configured) {
+    static OncePerDevice configured;
+    if (configured.needs()) {
         TS_CUDA(cudaFuncSetAttribute(moe_grouped_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GroupedSmem::total));
-        configured = true;
+        configured.done();
     }
     cudaError_t e = launch(moe_grouped_kernel, dim3(sm_count()), dim3(kThreads), GroupedSmem::total, stream,
                            pdl_enabled(), map_w, map_x, p);

@@ -759,18 +759,18 @@ static __device__ __align__(256) unsigned char g_top1_scratch[kStaticTopRows * k
 
 // In host code `g_top1_scratch` is only a stand-in for the symbol, not a device address: the real
 // address is looked up once per device, with that device current, and cached.
-static void *g_top1_scratch_addr[64] = {};
+static std::atomic<void *> g_top1_scratch_addr[64] = {};  // atomic: two host threads may make their first call at once
 
 static int top1_scratch(void **out) {
     int dev = -1;
     TS_CUDA(cudaGetDevice(&dev));
     TS_REQUIRE(dev >= 0 && dev < 64, "top_1_static: device ordinal %d is outside 0..63", dev);
-    if (g_top1_scratch_addr[dev] == nullptr) {
-        void *p = nullptr;
+    void *p = g_top1_scratch_addr[dev].load(std::memory_order_acquire);
+    if (p == nullptr) {
         TS_CUDA(cudaGetSymbolAddress(&p, g_top1_scratch));
-        g_top1_scratch_addr[dev] = p;
+        g_top1_scratch_addr[dev].store(p, std::memory_order_release);
     }
-    *out = g_top1_scratch_addr[dev];
+    *out = p;
     return TS_OK;
 }
 

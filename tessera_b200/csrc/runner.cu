@@ -59,6 +59,9 @@ struct ts_decoder {
     size_t events_used = 0;
     std::vector<const char *> event_names;
     std::map<std::string, std::pair<double, uint64_t>> profile;  // name -> (ms, intervals)
+    StepKernel *step = nullptr;  // the persistent layer-stack kernel, when the shapes allow it
+    bool use_step = false;       // off until ts_decoder_use_step_kernel(dec, 1): slower than the launches it replaces so far
+    uint32_t step_keys = 1024;   // decode steps that see more positions than this keep the per-product launches
     cudaStream_t own_stream = nullptr;  // used when the caller passes the NULL stream, which cannot capture
     volatile uint32_t *gate_flag = nullptr;  // pinned; the gate kernel holds the stream until it is set
 };
@@ -166,6 +169,13 @@ bool append_in_attention(const ts_decoder *d, bool distinct) {
     return !off && distinct && attend_rows_fused_supports(contiguous, d->c.head_dim, d->kept_total_rows);
 }
 
+// Whether this launch's gather and layers run as the one persistent kernel: a decode step (every row in a slot of
+// its own) of at most 64 rows within the context limit.
+bool takes_step_kernel(const ts_decoder *d, uint32_t rows, uint32_t keys, bool distinct) {
+    return d->step && d->use_step && distinct && d->fresh_seqs == 0 && rows <= step_kernel_max_rows() &&
+           keys <= d->step_keys;
+}
+
 // The step list for `rows` rows that see at most `keys` positions; logits for n_out rows.
 int enqueue(ts_decoder *d, uint32_t rows, uint32_t keys, uint32_t n_out, bool feedback, bool distinct, cudaStream_t s,
             uint32_t *count) {
@@ -224,12 +234,15 @@ int enqueue(ts_decoder *d, uint32_t rows, uint32_t keys, uint32_t n_out, bool fe
     };
     if ((rc = mark("")) != TS_OK) return rc;  // interval origin
     if (feedback) STEP("advance_rows", advance_rows(d->ids, d->tokens, d->positions, rows, s));
-    if (fold) {
+    const bool one_kernel = takes_step_kernel(d, rows, keys, distinct);
+    if (one_kernel) {
+        STEP("decode_layers", step_kernel_launch(d->step, rows, keys, kd, s));
+    } else if (fold) {
         STEP("gather", gather_scaled(d->embed, d->tokens, d->x, d->h, d->layers[0].ln1, d->sumsq, ss_parts, rows, c.vocab, H, s));
     } else {
         STEP("gather", gather_rows(d->embed, d->tokens, d->x, TS_F32, rows, c.vocab, H, 0, s));
     }
-    for (uint32_t l = 0; l < c.layers; l++) {
+    for (uint32_t l = 0; l < c.layers && !one_kernel; l++) {
         ts_decoder::Layer &L = d->layers[l];
         if (fold) {
             STEP("linear_qkv", folded(true, d->h, L.wqkv, nullptr, d->qkv, d->qkv_n, H, TS_EPI_NONE, TS_BF16, nullptr));
@@ -436,6 +449,21 @@ int ts_decoder_create(const ts_decoder_config *config, ts_decoder **out) {
         if (e == cudaSuccess) e = cudaMemcpy(d->table, t.data(), t.size() * 4, cudaMemcpyHostToDevice);
         if (e != cudaSuccess) rc = fail(TS_ERR_CUDA, "initial uploads failed: %s", cudaGetErrorString(e));
     }
+    if (rc == TS_OK) {
+        StepKernelShape shape = {c.layers, c.hidden, c.heads, c.kv_heads, c.head_dim, c.ffn, c.vocab, c.page,
+                                 d->kept_total_rows, c.max_rows, c.eps, c.qk_norm};
+        if (step_kernel_supports(shape)) {
+            std::vector<StepKernelLayer> layers(c.layers);
+            for (uint32_t l = 0; l < c.layers; l++) {
+                const ts_decoder::Layer &L = d->layers[l];
+                layers[l] = {L.wqkv, L.wo, L.wgu, L.wdown, L.ln1, L.ln2, L.q_norm, L.k_norm, L.k_rows, L.v_rows};
+            }
+            StepKernelBuffers buffers = {layers.data(), d->embed, d->x, d->h, d->attn, d->act,
+                                         d->tokens, d->slots, d->positions, d->inv_freq};
+            rc = step_kernel_create(shape, buffers, &d->step);
+            if (const char *v = getenv("TS_STEP_KERNEL_KEYS")) d->step_keys = (uint32_t)atoi(v);
+        }
+    }
     if (rc != TS_OK) {
         ts_decoder_destroy(d);
         return rc;
@@ -444,9 +472,22 @@ int ts_decoder_create(const ts_decoder_config *config, ts_decoder **out) {
     return TS_OK;
 }
 
+int ts_decoder_use_step_kernel(ts_decoder *d, int on) {
+    if (!d) return 0;
+    const bool want = on != 0;
+    if (want != d->use_step) {
+        // captured graphs hold the other form of the step
+        for (auto &g : d->graphs) cudaGraphExecDestroy(g.second);
+        d->graphs.clear();
+        d->use_step = want;
+    }
+    return d->step != nullptr ? 1 : 0;
+}
+
 void ts_decoder_destroy(ts_decoder *d) {
     if (!d) return;
     for (auto &g : d->graphs) cudaGraphExecDestroy(g.second);
+    step_kernel_destroy(d->step);
     for (void *p : d->owned) cudaFree(p);
     if (d->stage) cudaFreeHost(d->stage);
     if (d->gate_flag) cudaFreeHost((void *)d->gate_flag);
@@ -670,6 +711,8 @@ uint32_t ts_decoder_launches_per_step(ts_decoder *d, uint32_t rows, uint32_t key
     auto lin = [&](uint32_t m, uint32_t n, uint32_t k, int epi) -> uint32_t {
         return linear_workspace(m, n, k, epi) > 0 ? 2 : 1;
     };
+    if (takes_step_kernel(d, rows, keys, d->last_distinct))
+        return 1 /*gather and every layer*/ + 1 /*final norm*/ + lin(rows, c.vocab, c.hidden, TS_EPI_NONE) + 2 /*top-1*/;
     const bool fold = fold_parts(d, rows) != 0;
     uint32_t per_layer = (fold ? 0 : 2) /*norms*/ + (append_in_attention(d, d->last_distinct) ? 0 : 1) /*append*/ +
                          1 /*attention*/ +

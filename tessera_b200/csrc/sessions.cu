@@ -98,6 +98,14 @@ int ts_sessions_generate(ts_sessions *s, const uint32_t *tokens, const uint64_t 
     }
     uint32_t next = 0;  // the first prompt still waiting
     std::vector<Seq> active;
+    // Every failing exit gives the active sequences' slots and pages back (finish with no history releases
+    // instead of retaining), as the reference retires a sequence on every exit path (schedule.rs finish/retire):
+    // the next generate on these sessions then starts from a clean pool.
+    auto bail = [&](int rc) {
+        for (Seq &q : active) ts_kept_slots_finish(s->kept, q.slot, nullptr, 0);
+        active.clear();
+        return rc;
+    };
     std::vector<uint32_t> row_tokens, row_slots, row_positions, ends, ids, pages(s->pages_per_slot ? s->pages_per_slot : 1);
     std::vector<uint32_t> take;
     std::vector<size_t> owners;
@@ -111,7 +119,7 @@ int ts_sessions_generate(ts_sessions *s, const uint32_t *tokens, const uint64_t 
             int admitted = 0;
             // the last prompt row is always fed: its logits make the first token
             int rc = ts_kept_slots_admit(s->kept, prompt, len, s->reuse ? len - 1 : 0, &slot, &skip, &admitted);
-            if (rc != TS_KV_OK) return ts::fail(TS_ERR_PROTOCOL, "sessions: admission failed with pool status %d", rc);
+            if (rc != TS_KV_OK) return bail(ts::fail(TS_ERR_PROTOCOL, "sessions: admission failed with pool status %d", rc));
             if (!admitted) break;
             Seq q;
             q.index = next;
@@ -123,7 +131,7 @@ int ts_sessions_generate(ts_sessions *s, const uint32_t *tokens, const uint64_t 
             active.push_back(std::move(q));
             next++;
         }
-        if (active.empty()) return ts::fail(TS_ERR_PROTOCOL, "sessions: the pool has no room for one more sequence");
+        if (active.empty()) return bail(ts::fail(TS_ERR_PROTOCOL, "sessions: the pool has no room for one more sequence"));
 
         // ---- Fair: decodes first, then a prompt token each in turn within the budget (schedule.rs:127-153) ----
         take.assign(active.size(), 0);
@@ -161,8 +169,9 @@ int ts_sessions_generate(ts_sessions *s, const uint32_t *tokens, const uint64_t 
             }
             uint32_t count = 0;
             int rc = ts_kept_slots_grow(s->kept, q.slot, q.fed + n, pages.data(), (uint32_t)pages.size(), &count);
-            if (rc != TS_KV_OK) return ts::fail(TS_ERR_PROTOCOL, "sessions: slot %u cannot grow to %llu rows (pool status %d)", q.slot,
-                                                (unsigned long long)(q.fed + n), rc);
+            if (rc != TS_KV_OK)
+                return bail(ts::fail(TS_ERR_PROTOCOL, "sessions: slot %u cannot grow to %llu rows (pool status %d)", q.slot,
+                                     (unsigned long long)(q.fed + n), rc));
             if (count > 0) {
                 for (uint32_t j = 0; j < count; j++) s->table[(size_t)q.slot * s->pages_per_slot + j] = pages[j];
                 s->stale = true;
@@ -172,13 +181,13 @@ int ts_sessions_generate(ts_sessions *s, const uint32_t *tokens, const uint64_t 
         }
         if (s->stale) {
             int rc = st.set_table(st.self, s->table.data(), (uint32_t)s->table.size());
-            if (rc != TS_OK) return rc;
+            if (rc != TS_OK) return bail(rc);
             s->stale = false;
         }
         ids.assign(ends.size(), 0);
         int rc = st.step(st.self, row_tokens.data(), row_slots.data(), row_positions.data(), (uint32_t)row_tokens.size(),
                          ends.data(), (uint32_t)ends.size(), ids.data());
-        if (rc != TS_OK) return rc;
+        if (rc != TS_OK) return bail(rc);
         s->steps++;
 
         // ---- each answer takes its rows and its last id (Seq::advance, schedule.rs:52-76) ----

@@ -6,6 +6,8 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include <atomic>
+
 #include "tessera_b200.h"
 
 namespace ts {
@@ -39,8 +41,29 @@ inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 
 inline uint32_t ceil_div(uint32_t a, uint32_t b) { return (a + b - 1) / b; }
 inline size_t align_up(size_t a, size_t b) { return (a + b - 1) / b * b; }
 
-// SM count of the current device, cached.
+// SM count of the current device, cached per device ordinal.
 int sm_count();
+
+// Ordinal of the current device (0 when there is none).
+int current_device();
+
+// "Set up once" record for state CUDA keeps per device (a kernel's dynamic shared-memory limit, a symbol's
+// address): one bit per device ordinal, safe to use from several host threads.  needs() is true until done()
+// ran with that device current; two threads racing through the set-up both do it, which is harmless.
+class OncePerDevice {
+public:
+    bool needs() const {
+        const int d = current_device();
+        return ((mask_[(d >> 6) & 3].load(std::memory_order_acquire) >> (d & 63)) & 1u) == 0;
+    }
+    void done() {
+        const int d = current_device();
+        mask_[(d >> 6) & 3].fetch_or(1ull << (d & 63), std::memory_order_release);
+    }
+
+private:
+    std::atomic<uint64_t> mask_[4] = {};
+};
 
 // ---- device helpers -------------------------------------------------------
 

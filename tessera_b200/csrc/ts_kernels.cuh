@@ -123,6 +123,37 @@ int picked(const void *x, const void *w, const uint32_t *ids, float *out, uint32
 int moe_mix(const float *y_picks, const float *gates, const float *add, float *out, uint32_t rows, uint32_t top,
             uint32_t width, cudaStream_t stream);
 
+// The layer stack of a decode step (<= 64 rows, one per slot, head width 128) as one persistent kernel.
+struct StepKernel;
+struct StepKernelShape {
+    uint32_t layers, hidden, heads, kv_heads, head_dim, ffn, vocab, page, kept_rows, max_rows;
+    float eps;
+    int qk_norm;
+};
+struct StepKernelLayer {
+    const void *wqkv, *wo, *wgu, *wdown;
+    const float *ln1, *ln2, *q_norm, *k_norm;
+    void *k_rows, *v_rows;
+};
+struct StepKernelBuffers {
+    const StepKernelLayer *layers;
+    const void *embed;
+    float *x;                 // residual rows f32 [max_rows, hidden]
+    void *xs, *attn, *act;    // bf16 [max_rows, hidden | heads * 128 | ffn]
+    const uint32_t *tokens, *slots, *positions;
+    const float *inv_freq;
+};
+bool step_kernel_supports(const StepKernelShape &shape);
+uint32_t step_kernel_max_rows();
+int step_kernel_create(const StepKernelShape &shape, const StepKernelBuffers &buffers, StepKernel **out);
+void step_kernel_destroy(StepKernel *kernel);
+// Gather + every layer for `rows` rows (tokens, slots, positions on the device) whose positions are all below
+// `keys`; leaves the residual rows in x.
+int step_kernel_launch(StepKernel *kernel, uint32_t rows, uint32_t keys, const KeptDev &kept, cudaStream_t stream);
+int step_take_status();
+// Runs a one-block kernel whose bounded wait runs out after `wait_ns`: the status word then reads TS_ERR_TIMEOUT.
+int wait_runs_out(uint64_t wait_ns, cudaStream_t stream);
+
 // Sets the process-wide programmatic-dependent-launch switch.
 void set_pdl(bool enabled);
 

@@ -33,6 +33,7 @@ RUN_SIGNATURES = {
     "ts_decoder_profile": (i32, [vp, u32, vp]),
     "ts_decoder_take_profile": (i32, [vp, C.c_char_p, sz]),
     "ts_decoder_get_config": (i32, [vp, C.POINTER(DecoderConfig)]),
+    "ts_decoder_use_step_kernel": (i32, [vp, i32]),
     # the request loop (tessera_b200/sessions.py binds the stepper's callback types)
     "ts_sessions_new": (vp, [vp, i32, u32]),
     "ts_sessions_on_decoder": (vp, [vp, i32, u32]),
@@ -128,6 +129,11 @@ class Decoder:
     def prepare(self, rows: int, stream=None):
         """Captures the decode-step graphs of `rows` rows for every context bucket ahead of time."""
         check(lib.ts_decoder_prepare(self._h, rows, vp(stream or 0)))
+
+    def use_step_kernel(self, on: bool) -> bool:
+        """Chooses between the one persistent kernel per decode step and one launch per product; returns whether
+        the persistent kernel exists for this decoder's shapes."""
+        return bool(lib.ts_decoder_use_step_kernel(self._h, int(on)))
 
     def graph_replays(self) -> int:
         return int(lib.ts_decoder_graph_replays(self._h))

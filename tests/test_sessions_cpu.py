@@ -200,3 +200,29 @@ def test_the_library_loop_refuses_and_reports():
 
     with pytest.raises(RuntimeError, match="fell over"):
         NativeSessions(Broken(1, 16, 16, 0)).generate([[1, 2, 3]], 2)
+
+
+@pytest.mark.parametrize("page", [0, 16])
+def test_a_failed_step_gives_its_slots_back(page):
+    # A step that fails once must not strand the active sequences' slots and pages: the same sessions then answer
+    # the next request, with the answers of a decoder that never failed (the reference retires a sequence on every
+    # exit path: engine/engine/src/schedule.rs finish / retire).
+    from tessera_b200.sessions import NativeSessions
+
+    class FailsOnce(KeptTokens):
+        armed = True
+
+        def step(self, *a, **k):
+            if self.armed and len(self.launches) == 2:
+                self.armed = False
+                raise RuntimeError("one bad launch")
+            return super().step(*a, **k)
+
+    prompts = [[5, 6, 7, 8], [9, 10], [11, 12, 13]]
+    s = NativeSessions(FailsOnce(2, 64, 16, page), reuse=False)
+    with pytest.raises(RuntimeError, match="one bad launch"):
+        s.generate(prompts, 3)
+    assert s.consistent()
+    got = s.generate(prompts, 3)          # both slots are free again: three prompts over two slots
+    assert s.consistent()
+    assert got == [alone(p, 3) for p in prompts]

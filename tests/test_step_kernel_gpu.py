@@ -1,0 +1,156 @@
+"""The persistent decode-step kernel (csrc/decode_step.cu): one launch for the gather and every layer.
+
+It is checked three ways: against the CPU checker's decoder on the same seeded weights, against the per-product
+launches it replaces on the same decoder, and for its give-up path (a bounded wait that nothing satisfies must end
+as TS_ERR_TIMEOUT in the status word and leave the device usable).
+
+Tolerance.  The per-op bar is 1e-2 (bf16 outputs, f32 sums) and every op of the kernel is held to it through the
+tests of the same arithmetic (tests/test_linear_gpu.py, tests/test_attend_rows_gpu.py).  Here whole decode steps
+are compared: a few layers of bf16 rounding points stacked, on small random models whose largest logit is only
+2-3.  Measured on a B200 against the checker, logits error over the largest logit: 0.8e-2 to 1.3e-2 for this kernel
+and 0.7e-2 to 1.2e-2 for the per-product launches (the same rounding points, another summation order), so the
+end-to-end bar here is 2e-2; greedy ids must agree wherever the checker's top two logits differ by more than that.
+"""
+import numpy as np
+import pytest
+
+import oracle as O
+from tessera_b200 import synth
+from tests.test_decoder_gpu import _device
+from tests.util import rel_error
+
+pytestmark = pytest.mark.gpu
+
+E2E_TOL = 2e-2
+
+# head width 128 throughout (the kernel's attention); 1, 2 and 4 query heads per kv head
+G1 = dict(layers=2, hidden=512, heads=4, kv_heads=4, head_dim=128, ffn=768, vocab=3000, eps=1e-6, theta=1e4)
+G2 = dict(layers=3, hidden=1024, heads=16, kv_heads=8, head_dim=128, ffn=3072, vocab=5000, eps=1e-6, theta=1e6)
+G4 = dict(layers=2, hidden=256, heads=8, kv_heads=2, head_dim=128, ffn=512, vocab=2000, eps=1e-6, theta=1e5)
+
+
+def _oracle_run(cfg, seed, prompts, new, context, gains):
+    """The checker's greedy run with its logits: ids [n, new], logits [new][n, vocab], final hidden rows."""
+    from tests.golden.make_qwen3_tokens import oracle_weights
+    dec = O.Decoder(dict(cfg, context=context, slots=len(prompts)), oracle_weights(cfg, seed, gains))
+    toks = [t for p in prompts for t in p]
+    slts = [s for s, p in enumerate(prompts) for _ in p]
+    poss = [i for p in prompts for i in range(len(p))]
+    ids, logits, hidden = dec.step(toks, slts, poss, want_logits=True, want_hidden=True)
+    ends = np.cumsum([len(p) for p in prompts]) - 1
+    out = np.zeros((len(prompts), new), np.uint32)
+    out[:, 0] = ids[ends]
+    all_logits, hidden = [logits[ends]], hidden[ends]
+    pos = np.array([len(p) for p in prompts], np.uint32)
+    for t in range(1, new):
+        ids, logits, hidden = dec.step(out[:, t - 1], np.arange(len(prompts)), pos, want_logits=True, want_hidden=True)
+        out[:, t] = ids
+        all_logits.append(logits)
+        pos += 1
+    return out, all_logits, hidden
+
+
+@pytest.mark.parametrize("cfg,page,prompts", [(G1, 64, (3, 40, 1, 33)), (G2, 64, (5, 17, 1)), (G4, 0, (31, 2)),
+                                              (G2, 0, (64,))])
+def test_decode_steps_match_oracle(cfg, page, prompts):
+    """Fed the checker's own ids step by step (so that one flipped id cannot hide behind, or spoil, the later ones):
+    every step's logits within E2E_TOL of the largest logit, and the greedy id equal to the checker's wherever the
+    checker's top-1 beats its top-2 by more than twice that tolerance - below it a tie is decided by rounding."""
+    from tessera_b200 import ops
+    rng = np.random.default_rng(11)
+    texts = [rng.integers(0, cfg["vocab"], size=n).tolist() for n in prompts]
+    n, new = len(texts), 10
+    want, want_logits, want_hidden = _oracle_run(cfg, 5, texts, new, 128, "near_one")
+    dec = _device(cfg, 5, slots=n, context=128, max_rows=64, gains="near_one", page=page)
+    assert dec.use_step_kernel(True)
+    if page:
+        dec.set_table(synth.page_permutation(n * dec.pages, seed=2))
+    got = np.zeros_like(want)
+    got[:, 0] = dec.prefill(texts)
+    pos = np.array([len(t) for t in texts], np.uint32)
+    decided = 0
+    for t in range(1, new):
+        got[:, t] = dec.step(want[:, t - 1], np.arange(n), pos)     # one row per slot: the persistent kernel
+        pos += 1
+        logits = dec.read_logits(n)
+        scale = float(np.abs(want_logits[t]).max())
+        assert float(np.abs(logits - want_logits[t]).max()) <= E2E_TOL * scale, t
+        top2 = np.sort(want_logits[t], axis=1)[:, -2:]
+        clear = (top2[:, 1] - top2[:, 0]) > 2 * E2E_TOL * scale
+        decided += int(clear.sum())
+        assert np.array_equal(got[clear, t], want[clear, t]), t
+    hidden = O.bf16_widen(dec.read_hidden(n))
+    assert ops.device_status() == 0
+    dec.close()
+    assert decided >= (new - 1) * n // 2       # most steps were decided by more than rounding
+    assert rel_error(hidden, want_hidden) <= E2E_TOL
+
+
+@pytest.mark.parametrize("rows,page", [(64, 64), (37, 0)])
+def test_step_kernel_equals_per_product_launches(rows, page):
+    """A full batch of rows, both forms of the step fed the same ids (those the per-product launches produce):
+    logits within E2E_TOL of the largest logit at every step, ids equal wherever the top two logits are further
+    apart than twice that; then the device-resident loop (graph replays) runs on both."""
+    cfg = G2
+    rng = np.random.default_rng(3)
+    texts = [rng.integers(0, cfg["vocab"], size=int(n)).tolist() for n in rng.integers(1, 70, size=rows)]
+    runs, feed = {}, None
+    for on in (False, True):
+        dec = _device(cfg, 13, slots=rows, context=128, max_rows=128, gains="near_one", page=page)
+        assert dec.use_step_kernel(on)
+        if page:
+            dec.set_table(synth.page_permutation(rows * dec.pages, seed=6))
+        first = dec.prefill(texts, chunk=128)
+        pos = np.array([len(t) for t in texts], np.uint32)
+        ids, logits = [], []
+        cur = first
+        for t in range(5):
+            cur = dec.step(cur if feed is None else feed[t], np.arange(rows), pos)
+            pos += 1
+            ids.append(cur.copy())
+            logits.append(dec.read_logits(rows))
+        dec.run_resident(4)
+        last = dec.read_ids(rows)
+        runs[on] = (np.stack(ids), np.stack(logits), dec.launches_per_step(rows, 128), last)
+        if feed is None:
+            feed = [first] + ids
+        dec.close()
+    from tessera_b200 import ops
+    assert ops.device_status() == 0
+    a, b = runs[True], runs[False]
+    scale = float(np.abs(b[1]).max())
+    assert float(np.abs(a[1] - b[1]).max()) <= E2E_TOL * scale
+    top2 = np.sort(b[1], axis=2)[:, :, -2:]
+    clear = (top2[:, :, 1] - top2[:, :, 0]) > 2 * E2E_TOL * scale
+    assert clear.mean() > 0.5 and np.array_equal(a[0][clear], b[0][clear])
+    assert a[2] < 8 < b[2]   # one launch for the layers instead of four or five a layer
+    assert a[3].shape == b[3].shape and int(a[3].max()) < cfg["vocab"]
+
+
+def test_step_kernel_is_deterministic():
+    cfg = G2
+    rng = np.random.default_rng(4)
+    texts = [rng.integers(0, cfg["vocab"], size=9).tolist() for _ in range(16)]
+    outs = []
+    for _ in range(2):
+        dec = _device(cfg, 1, slots=16, context=64, max_rows=64, gains="near_one", page=64)
+        dec.generate(texts, 6)
+        outs.append(dec.read_logits(16))
+        dec.close()
+    assert np.array_equal(outs[0], outs[1])   # fixed summation order: the same bits
+
+
+def test_bounded_wait_gives_up_cleanly():
+    """A wait on a barrier nothing arrives at, bounded at 100 microseconds: the kernel returns, the status word
+    reads TS_ERR_TIMEOUT once, and the next ordinary launches succeed."""
+    import torch
+    from tessera_b200 import _lib, ops
+    assert ops.device_status() == 0
+    _lib.check(_lib.lib.ts_wait_runs_out(100_000, None))
+    assert ops.device_status() == _lib.TS_ERR_TIMEOUT
+    assert ops.device_status() == 0            # read and cleared
+    x = torch.ones((4, 64), dtype=torch.bfloat16, device="cuda")
+    w = torch.ones((128, 64), dtype=torch.bfloat16, device="cuda")
+    out = ops.linear(x, w)
+    torch.cuda.synchronize()
+    assert float(out.float().min()) == 64.0 and ops.device_status() == 0
