@@ -63,6 +63,9 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--pdl", type=int, default=1)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--step-kernel", type=int, default=1,
+                    help="decode: 1 = the gather and every layer as one persistent kernel per step (default), 0 = one launch "
+                         "per product (for A/B timing)")
     ap.add_argument("--workload", default="decode", choices=["decode", "moe", "embed"],
                     help="decode: the headline Qwen3-0.6B-shaped decode (default); moe: GLM-style MoE decode, batch 256 at "
                          "context 2048, expert-parallel over the ranks; embed: 1024 ragged texts through the "
@@ -264,6 +267,7 @@ def run_ours(args, rank, world, local_rank):
     dec = runner.Decoder(cfg, slots=BATCH, context=context, max_rows=2048, page=64, graphs=True, pdl=bool(args.pdl))
     named, cpu_w = cpu_weights(cfg, 0)
     dec.load_all(named)
+    dec.use_step_kernel(bool(args.step_kernel))
     dec.set_table(synth.page_permutation(BATCH * dec.pages, seed=4 + rank))
     side = torch.cuda.Stream()  # the legacy NULL stream cannot be captured into graphs
     torch.cuda.set_stream(side)

@@ -1,40 +1,43 @@
-// The layer stack of a decode step as ONE persistent kernel: every SM holds one block for the whole step.
+// The layer stack of a decode step as ONE persistent kernel: clusters of eight blocks, one block per SM, stay
+// resident for the whole step.
 //
-// A decode step at batch 64 is a chain of five dependent products per layer (q,k,v -> attention -> o ->
+// A decode step at batch 64 is a chain of five dependent stages per layer (q,k,v -> attention -> o ->
 // gate/up -> down), each worth 1-2 microseconds of HBM time.  As separate launches each link of the chain
-// pays a launch prologue (barrier set-up, TMEM allocation, tensor-map fetch), the first-byte latency of its
-// weights and a cluster reduce: 9-12 microseconds a link.  Here the links are phases of one kernel:
+// pays a launch prologue (barrier set-up, TMEM allocation, tensor-map fetch) and the first-byte latency of its
+// weights: 9-12 microseconds a link.  Here the links are phases of one kernel:
 //
 //   * a producer warp streams the block's weight tiles of ALL phases and layers, in schedule order, through a
-//     shared-memory ring by TMA.  Weights depend on nothing, so the stream never stops at a phase boundary:
-//     while a block waits at a barrier or attends, the tiles of its next products are already landing;
-//   * a control thread issues the tcgen05 MMAs of the block's (weight tile, k slice) units (weight rows on
-//     the TMEM lanes, the batch on the columns) and runs the device-wide barrier that separates phases:
-//     one release-add and an acquire-poll on a counter, bounded in time;
-//   * four worker warps drain the accumulators into f32 partial sums in global memory (they stay in L2) and
-//     do everything else: the embedding gather, decode attention (a warp per (row, kv head): per-head norm,
-//     rotation, append, warp-MMA flash attention over TMA-fed 32-key tiles) and the fixed-order reduction of
-//     the k-slice partials with the residual add, the next norm's scaled copy and sums of squares, or SwiGLU.
+//     shared-memory ring by TMA, a few tiles in flight at a time.  Weights depend on nothing, so the stream
+//     never stops at a phase boundary: while a block waits at a barrier or attends, the tiles of its next
+//     products are already landing;
+//   * a cluster owns whole 128-row weight tiles; its eight blocks split k.  A control thread issues the
+//     tcgen05 MMAs of the block's k slice (weight rows on the TMEM lanes, the batch on the columns) and runs
+//     the device-wide barrier that separates phases: one release-add and an acquire-poll on a counter;
+//   * four worker warps reduce the eight partial accumulators through distributed shared memory (block r of
+//     the cluster ends up with batch columns 8 r .. 8 r + 7, added in rank order) and apply the stage chain on
+//     the way out: 1/rms and bf16 for q,k,v; residual add, the next norm's scaled copy and sums of squares
+//     for o and down; SwiGLU for gate/up.  No partial sum touches global memory.  The same warps do the
+//     embedding gather and the decode attention (a warp per (row, kv head): per-head norm, rotation, append,
+//     warp-MMA flash attention over 32-key tiles it fetches for itself).
 //
 // Phases of layer l (a device-wide barrier after each):
-//   QKV   partials of xs . Wqkv^T                      (xs = bf16(residual * ln1 gain), 1/rms applied later)
-//   ATTN  q,k,v = bf16(sum of partials * 1/rms); norm, rotate, append k,v; attend  -> attn (bf16)
-//   O     partials of attn . Wo^T
-//   R1    x += sum of partials; xs = bf16(x * ln2 gain); sums of squares per 128 columns
-//   GU    partials of xs . [Wgate; Wup]^T
-//   R2    act = bf16(silu(g / rms) * (u / rms))
-//   DOWN  partials of act . Wdown^T
-//   R3    x += sum of partials; xs = bf16(x * next ln1 gain); sums of squares
-// Every sum runs in a fixed order (k blocks inside a slice in the MMA, slices in ascending order): a re-run
-// gives the same bits.  Every wait is bounded (two seconds); a block that gives up raises a device-wide flag,
+//   QKV   qkv = bf16((xs . Wqkv^T) / rms)              (xs = bf16(residual * ln1 gain))
+//   ATTN  per-head norm, rotation, append of k,v; attention over the kept rows -> attn (bf16)
+//   O     x += attn . Wo^T; xs = bf16(x * ln2 gain); sums of squares per 128 columns
+//   GU    act = bf16(silu(g / rms) * (u / rms)), [g; u] = xs . [Wgate; Wup]^T
+//   DOWN  x += act . Wdown^T; xs = bf16(x * next ln1 gain); sums of squares
+// Every sum runs in a fixed order (k blocks inside a slice in the MMA, slices in rank order): a re-run gives
+// the same bits.  Every wait is bounded (two seconds); a block that gives up raises a device-wide flag,
 // every role of every block leaves, waits for its own copies in flight, TMEM is freed and the host reads
 // TS_ERR_TIMEOUT from the status word (the reference bounds its device spins the same way:
-// engine/rules/device/include/tessera/status.h:9-39, grid.h:22-42).
+// engine/rules/device/include/tessera/status.h:9-39, grid.h:22-42).  The only unbounded primitive is the
+// hardware cluster barrier at entry and exit, which every path reaches.
 //
 // Stands in for the per-layer step list of engine/models/src/decoder.rs:281-389 at decode sizes (<= 64 rows,
 // one row per slot, head width 128), i.e. for the `lanes`/`thin` matmul rules
 // (engine/rules/linear/src/lanes.rs:20-65) and `attend_rows`/`flash_rows`
-// (engine/rules/attention/src/attend.rs:124-167, flash.rs:505-580) with their fused stage chains.
+// (engine/rules/attention/src/attend.rs:124-167, flash.rs:505-580) with their fused stage chains
+// (engine/plan/lower/src/sites/matmul.rs:148-176).
 #include <cstdlib>
 #include <vector>
 
@@ -48,44 +51,52 @@ namespace {
 
 using namespace ptx;
 
+constexpr uint32_t kCluster = 8;               // blocks of a cluster: the k slices of a weight tile
 constexpr uint32_t kRing = 5;                  // weight stages
-constexpr uint32_t kInFlight = 2;              // weight tiles the producer keeps in flight
+constexpr uint32_t kAhead = 10;                // weight tiles asked of L2 ahead of the ring (most of a layer for a block)
 constexpr uint32_t kTile = 128 * 64 * 2;       // one stage: 128 weight rows x 64 k
 constexpr uint32_t kXkb = 64 * 64 * 2;         // one k block of the batch operand: 64 rows x 64 k
+constexpr uint32_t kMaxKb = 8;                 // most k blocks a block's k slice may hold
 constexpr uint32_t kWorkers = 4;
 constexpr uint32_t kThreads = (2 + kWorkers) * 32;
 constexpr uint32_t kKvStages = 2;              // per worker warp
 constexpr uint32_t kKvStage = 2 * 32 * 128 * 2;  // a 32-key K tile and its V tile
-constexpr uint32_t kUnion = kWorkers * kKvStages * kKvStage;  // x slice (linear phases) / K,V tiles (attention)
-constexpr uint32_t kMaxKb = kUnion / kXkb;     // most k blocks a unit's x slice may hold
+constexpr uint32_t kBatch = 64;                // batch columns of the MMA
+constexpr uint32_t kOwn = kBatch / kCluster;   // batch columns a block owns after the cluster reduce
+constexpr uint32_t kXfer = 128 * kOwn * 4;     // bytes one block sends another per tile: 128 rows x 8 columns f32
 constexpr uint32_t kPrepHeads = 6;             // up to 4 query heads + k + v per item
-constexpr uint32_t kBatch = 64;                // batch columns of the MMA; row stride of the partial buffers
 constexpr uint32_t kAccStages = 2;
-constexpr uint32_t kWarpStage = kKvStages * kKvStage;  // a worker warp's share of the union region
 
+// The union region: x slice + receive + send buffers in the linear phases, the workers' K,V tile stages in the
+// attention phase.
 struct Smem {
     static constexpr uint32_t ring = 0;
     static constexpr uint32_t uni = ring + kRing * kTile;
-    static constexpr uint32_t prep = uni + kUnion;                       // bf16 [kWorkers][kPrepHeads][128]
-    static constexpr uint32_t bars = prep + kWorkers * kPrepHeads * 256;
-    static constexpr uint32_t n_bars = 2 * kRing + 1 + 2 * kAccStages + 2 + kWorkers * kKvStages;
+    static constexpr uint32_t x = uni;                                   // kMaxKb k blocks
+    static constexpr uint32_t recv = x + kMaxKb * kXkb;                  // [kCluster][128][kOwn] f32, by source rank
+    static constexpr uint32_t send = recv + kCluster * kXfer;            // same shape, by destination rank
+    static constexpr uint32_t uni_bytes = kMaxKb * kXkb + 2 * kCluster * kXfer;
+    static_assert(uni_bytes == kWorkers * kKvStages * kKvStage, "the two uses of the union region have the same size");
+    static constexpr uint32_t prep = uni + uni_bytes;                    // bf16 [kWorkers][kPrepHeads][128]
+    static constexpr uint32_t red = prep + kWorkers * kPrepHeads * 256;  // f32 [kWorkers][kOwn] + inv_s [kOwn]
+    static constexpr uint32_t bars = red + (kWorkers + 1) * kOwn * 4;
+    static constexpr uint32_t n_bars = 2 * kRing + 1 + 2 * kAccStages + 2 + kWorkers * kKvStages + 5;
     static constexpr uint32_t misc = bars + ((n_bars * 8 + 63) / 64) * 64;   // tmem slot, abort flag
     static constexpr uint32_t bytes = misc + 64 + 1024;                  // slack for the 1024-byte alignment
 };
 static_assert(Smem::bytes <= 227 * 1024, "shared memory budget");
 
 enum { LIN_QKV = 0, LIN_O = 1, LIN_GU = 2, LIN_DOWN = 3 };
+enum { EPI_QKV = 0, EPI_RESIDUAL = 1, EPI_GATED = 2 };
 
 struct LinPhase {
     uint32_t n;         // weight rows
     uint32_t kb_total;  // k / 64
     uint32_t tiles;     // 128-row tiles (gated: 64 gate rows + their 64 up rows)
-    uint32_t splits;    // k slices
-    uint32_t units;     // tiles * splits
-    uint32_t cum;       // units of the layer's earlier phases (deals units round robin over the blocks)
+    uint32_t cum;       // tiles of the layer's earlier phases (deals tiles round robin over the clusters)
     uint32_t gated;
     uint32_t x_map;     // which activation map feeds it
-    float *part;        // [splits][kBatch][n] f32
+    uint32_t epilogue;
 };
 
 struct LayerDev {
@@ -94,16 +105,19 @@ struct LayerDev {
 };
 
 struct StepParams {
-    CUtensorMap x_maps[3];     // xs, attn, act: in the parameter space, where a copy need not fetch its map from global memory
-    const CUtensorMap *maps;   // [4 L] weights, then [2 L] kept K and V
+    // Every tensor map rides in the kernel's parameters, where a copy need not fetch its map from global memory;
+    // one map covers all layers of a weight (the layers' copies lie back to back).
+    CUtensorMap x_maps[3];     // xs, attn, act
+    CUtensorMap w_maps[4];     // q|k|v, o, gate|up, down: [layers * n, k]
+    CUtensorMap kv_maps[2];    // kept K and V rows: [layers * kept_rows, kv_heads * 128]
+    uint32_t kept_rows;
     const LayerDev *layers;
     LinPhase lin[4];
-    uint32_t n_layers, blocks, rows, hidden, qw, ffn, heads, kv_heads, qkv_n, units_per_layer;
+    uint32_t n_layers, clusters, blocks, rows, hidden, qw, ffn, heads, kv_heads, qkv_n, tiles_per_layer;
     uint32_t ss_parts;         // hidden / 128
-    uint32_t vocab;
     uint32_t max_blk;          // 32-key blocks up to the furthest position of the launch
     float *x;                  // residual rows f32 [rows, hidden]
-    uint16_t *xs, *attn, *act;
+    uint16_t *xs, *attn, *act, *qkv;
     float *ss;                 // [rows, ss_parts]
     const uint16_t *embed;
     const uint32_t *tokens, *slots, *positions;
@@ -152,7 +166,9 @@ __device__ __forceinline__ void give_up(const Bounds &b) {
     atomicExch(b.abort_g, 1u);
 }
 
-__device__ __forceinline__ bool wait_bar(uint64_t *bar, uint32_t parity, const Bounds &b) {
+// (Not inlined, like the other rarely-run or once-a-phase pieces below: the kernel's code has to stay small enough
+// for the instruction cache, or every phase of every layer begins by fetching its instructions again.)
+__device__ __noinline__ bool wait_bar(uint64_t *bar, uint32_t parity, const Bounds &b) {
     uint64_t start = 0;
     for (uint32_t i = 0;; i++) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -169,7 +185,7 @@ __device__ __forceinline__ bool wait_bar(uint64_t *bar, uint32_t parity, const B
 
 // After an abort: a copy this thread issued may still be in flight; wait for it (bounded) so that nothing
 // lands in shared memory after the block has left.
-__device__ __forceinline__ void drain_bar(uint64_t *bar, uint32_t parity, uint64_t wait_ns) {
+__device__ __noinline__ void drain_bar(uint64_t *bar, uint32_t parity, uint64_t wait_ns) {
     const uint64_t start = now_ns();
     for (uint32_t i = 0;; i++) {
         if (mbar_try_wait(bar, parity)) return;
@@ -182,7 +198,7 @@ __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.pr
 // Device-wide barrier, one thread per block.  Everything this block wrote (observed by this thread through
 // the workers' arrivals) is released to the other blocks; what they wrote is acquired, for the async proxy
 // (TMA) too.
-__device__ __forceinline__ bool grid_sync(uint32_t *counter, uint32_t target, const Bounds &b) {
+__device__ __noinline__ bool grid_sync(uint32_t *counter, uint32_t target, const Bounds &b) {
     __threadfence();
     fence_proxy_async_all();
     asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(counter) : "memory");
@@ -212,42 +228,29 @@ __device__ __forceinline__ bool grid_sync(uint32_t *counter, uint32_t target, co
 
 // ---- small helpers -----------------------------------------------------------------------------------------
 
-// One thread.  Copies `bytes` (a multiple of 16, both addresses 16-byte aligned) from global to this block's shared
-// memory and credits them to `bar`.  The copy reads through L2, so it sees what other blocks released before the
-// barrier that preceded it.
-__device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_addr(dst)),
-                 "l"(src), "r"(bytes), "r"(smem_addr(bar))
+// Asks L2 for the box a later tma_load_2d with the same map and coordinates will copy.
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap *map, int32_t x, int32_t y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y)
                  : "memory");
 }
 
-// A worker warp's staging area (its share of the union region) and the barrier its copies complete on.
-struct Stage {
-    uint8_t *mem;       // kWarpStage bytes
-    uint64_t *bar;
-    uint32_t *parity;   // bit 0: parity of the barrier's next completion
-    uint32_t *pending;  // bit 0: copies in flight
-};
-
-__device__ __forceinline__ void k_slice(const LinPhase &P, uint32_t split, uint32_t &kb0, uint32_t &kb1) {
-    kb0 = (uint32_t)(((uint64_t)split * P.kb_total) / P.splits);
-    kb1 = (uint32_t)(((uint64_t)(split + 1) * P.kb_total) / P.splits);
+// The k blocks of rank `r`'s slice.
+__device__ __forceinline__ void k_slice(const LinPhase &P, uint32_t r, uint32_t &kb0, uint32_t &kb1) {
+    kb0 = (uint32_t)(((uint64_t)r * P.kb_total) / kCluster);
+    kb1 = (uint32_t)(((uint64_t)(r + 1) * P.kb_total) / kCluster);
 }
 
-// First unit of phase `ph` of layer `l` that block `cta` owns; the block's units are that one and every
-// `blocks`-th after it.  Units are dealt round robin over the blocks, carrying on across phases and layers.
-__device__ __forceinline__ uint32_t first_unit(const StepParams &p, uint32_t l, uint32_t ph, uint32_t cta) {
-    const uint32_t rot = (uint32_t)(((uint64_t)l * p.units_per_layer + p.lin[ph].cum) % p.blocks);
-    return (cta + p.blocks - rot) % p.blocks;
+// First tile of phase `ph` of layer `l` that cluster `cid` owns; its tiles are that one and every `clusters`-th
+// after it.  Tiles are dealt round robin over the clusters, carrying on across phases and layers, so that phases
+// with fewer tiles than clusters (o, down) land on different clusters.
+__device__ __forceinline__ uint32_t first_tile(const StepParams &p, uint32_t l, uint32_t ph, uint32_t cid) {
+    const uint32_t rot = (l * p.tiles_per_layer + p.lin[ph].cum) % p.clusters;  // a few thousand tiles at most: 32 bits do
+    return (cid + p.clusters - rot) % p.clusters;
 }
 
-// 1/rms of residual row `m` from the partial sums of squares the last reduction left (whole warp).
-__device__ __forceinline__ float row_inv_rms(const StepParams &p, uint32_t m, uint32_t lane) {
-    float ss = 0.0f;
-    for (uint32_t i = lane; i < p.ss_parts; i += 32) ss += __ldcg(p.ss + (size_t)m * p.ss_parts + i);
-    ss = warp_sum(ss);
-    return 1.0f / sqrtf(ss / (float)p.hidden + p.eps);
-}
+// Word offset of 4-column group `half` (0, 1) of row `row` in a [128][8] f32 exchange block; the groups of rows
+// 4-7 of every eight swap places, which keeps a quarter warp's 16-byte accesses on distinct banks.
+__device__ __forceinline__ uint32_t xfer_at(uint32_t row, uint32_t half) { return row * kOwn + ((half ^ ((row >> 2) & 1)) << 2); }
 
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
@@ -278,9 +281,9 @@ __device__ __forceinline__ uint32_t swz(uint32_t row, uint32_t c16) {
 // block per lane: issued while the q,k,v product runs, so that the attention phase's tile copies hit L2 instead of
 // paying HBM latency with two tiles in flight per warp.  The kept rows of earlier positions depend on nothing in
 // this step.
-__device__ __forceinline__ void prefetch_kept(const StepParams &p, const LayerDev &L, uint32_t wid, uint32_t lane) {
+__device__ __noinline__ void prefetch_kept(const StepParams &p, const LayerDev &L, uint32_t wid, uint32_t lane) {
     const uint32_t units = p.rows * p.max_blk * 2, row_elems = p.kv_heads * 128;
-    for (uint32_t u = wid * 32 + lane; u < units; u += kWorkers * p.blocks * 32) {
+    for (uint32_t u = wid + lane * kWorkers * p.blocks; u < units; u += kWorkers * p.blocks * 32) {  // a unit per warp before a second per warp
         const uint32_t t = u >> 1, blk = t % p.max_blk, row = t / p.max_blk;
         const uint32_t pos = p.positions[row];
         if (blk * 32 >= pos) continue;
@@ -291,7 +294,7 @@ __device__ __forceinline__ void prefetch_kept(const StepParams &p, const LayerDe
 }
 
 // Embedding rows: x = f32(row), xs = bf16(row * gain), sums of squares per 128 columns.
-__device__ __forceinline__ void gather_phase(const StepParams &p, const float *gain, uint32_t wid, uint32_t lane) {
+__device__ __noinline__ void gather_phase(const StepParams &p, const float *gain, uint32_t wid, uint32_t lane) {
     const uint32_t nch = p.ss_parts, units = p.rows * nch;
     for (uint32_t u = wid; u < units; u += kWorkers * p.blocks) {
         const uint32_t m = u / nch, col = (u % nch) * 128 + lane * 4;
@@ -308,103 +311,6 @@ __device__ __forceinline__ void gather_phase(const StepParams &p, const float *g
     }
 }
 
-// x += sum over the k slices (ascending) of a residual-feeding product; xs = bf16(x * gain) and the sums of
-// squares for the norm that follows (gain NULL: the last layer, nothing follows inside the kernel).  The slices'
-// 128-column rows are staged in shared memory by bulk copies, all in flight at once: one L2 round trip a unit.
-__device__ __forceinline__ bool residual_phase(const StepParams &p, const LinPhase &P, const float *gain, uint32_t wid,
-                                               uint32_t lane, const Stage &st, const Bounds &bd) {
-    const uint32_t nch = p.ss_parts, units = p.rows * nch, H = p.hidden, S = P.splits;
-    constexpr uint32_t kMost = kWarpStage / 512 - 1;  // slices a pass can stage beside the residual row
-    for (uint32_t u = wid; u < units; u += kWorkers * p.blocks) {
-        const uint32_t m = u / nch, col0 = (u % nch) * 128;
-        float *xo = p.x + (size_t)m * H + col0;
-        float4 a = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        for (uint32_t s0 = 0; s0 < S; s0 += kMost) {
-            const uint32_t n = min(kMost, S - s0), copies = n + (s0 == 0 ? 1 : 0);
-            if (lane == 0) {
-                mbar_expect_tx(st.bar, copies * 512);
-                *st.pending |= 1u;
-            }
-            __syncwarp();
-            for (uint32_t c = lane; c < copies; c += 32) {
-                const float *src = c < n ? P.part + ((size_t)(s0 + c) * kBatch + m) * H + col0 : xo;
-                bulk_load(st.mem + c * 512, src, 512, st.bar);
-            }
-            if (!wait_bar(st.bar, *st.parity & 1, bd)) return false;
-            *st.parity ^= 1u;
-            *st.pending &= ~1u;
-            if (s0 == 0) a = *reinterpret_cast<const float4 *>(st.mem + n * 512 + lane * 16);  // the residual row
-            for (uint32_t c = 0; c < n; c++) {
-                const float4 t = *reinterpret_cast<const float4 *>(st.mem + c * 512 + lane * 16);
-                a.x += t.x; a.y += t.y; a.z += t.z; a.w += t.w;
-            }
-            __syncwarp();  // every lane has read the stage before the next pass overwrites it
-        }
-        const uint32_t col = col0 + lane * 4;
-        *reinterpret_cast<float4 *>(xo + lane * 4) = a;
-        if (gain) {
-            const float4 g = __ldg(reinterpret_cast<const float4 *>(gain + col));
-            *reinterpret_cast<uint2 *>(p.xs + (size_t)m * H + col) =
-                make_uint2(pack_bf16(a.x * g.x, a.y * g.y), pack_bf16(a.z * g.z, a.w * g.w));
-            float ss = fmaf(a.x, a.x, fmaf(a.y, a.y, fmaf(a.z, a.z, a.w * a.w)));
-            ss = warp_sum(ss);
-            if (lane == 0) p.ss[(size_t)m * nch + u % nch] = ss;
-        }
-    }
-    return true;
-}
-
-// act = bf16(silu(g / rms) * (u / rms)), g and u the sums over the k slices of the gate and up halves; a unit is
-// 512 columns of one row (or the row's last columns), staged like the residual rows.
-__device__ __forceinline__ bool gated_phase(const StepParams &p, const LinPhase &P, uint32_t wid, uint32_t lane,
-                                            const Stage &st, const Bounds &bd) {
-    const uint32_t F = p.ffn, nch = (F + 511) / 512, units = p.rows * nch, N = P.n, S = P.splits;
-    for (uint32_t u = wid; u < units; u += kWorkers * p.blocks) {
-        const uint32_t m = u / nch, col0 = (u % nch) * 512;
-        const uint32_t width = min(512u, F - col0), row_bytes = width * 4;      // multiples of 256 columns
-        const uint32_t most = kWarpStage / (2 * row_bytes);
-        float4 g[4], up[4];
-#pragma unroll
-        for (uint32_t i = 0; i < 4; i++) g[i] = up[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        for (uint32_t s0 = 0; s0 < S; s0 += most) {
-            const uint32_t n = min(most, S - s0), copies = 2 * n;
-            if (lane == 0) {
-                mbar_expect_tx(st.bar, copies * row_bytes);
-                *st.pending |= 1u;
-            }
-            __syncwarp();
-            for (uint32_t c = lane; c < copies; c += 32) {   // copy 2 j: gate columns of slice s0 + j; 2 j + 1: up columns
-                const float *src = P.part + ((size_t)(s0 + (c >> 1)) * kBatch + m) * N + col0 + (c & 1) * F;
-                bulk_load(st.mem + c * row_bytes, src, row_bytes, st.bar);
-            }
-            if (!wait_bar(st.bar, *st.parity & 1, bd)) return false;
-            *st.parity ^= 1u;
-            *st.pending &= ~1u;
-            for (uint32_t c = 0; c < n; c++) {
-#pragma unroll
-                for (uint32_t i = 0; i < 4; i++)
-                    if (i * 128 < width) {
-                        const float4 a = *reinterpret_cast<const float4 *>(st.mem + (2 * c) * row_bytes + i * 512 + lane * 16);
-                        const float4 b = *reinterpret_cast<const float4 *>(st.mem + (2 * c + 1) * row_bytes + i * 512 + lane * 16);
-                        g[i].x += a.x; g[i].y += a.y; g[i].z += a.z; g[i].w += a.w;
-                        up[i].x += b.x; up[i].y += b.y; up[i].z += b.z; up[i].w += b.w;
-                    }
-            }
-            __syncwarp();
-        }
-        const float inv = row_inv_rms(p, m, lane);
-#pragma unroll
-        for (uint32_t i = 0; i < 4; i++)
-            if (i * 128 < width) {
-                const float r0 = silu(g[i].x * inv) * (up[i].x * inv), r1 = silu(g[i].y * inv) * (up[i].y * inv);
-                const float r2 = silu(g[i].z * inv) * (up[i].z * inv), r3 = silu(g[i].w * inv) * (up[i].w * inv);
-                *reinterpret_cast<uint2 *>(p.act + (size_t)m * F + col0 + i * 128 + lane * 4) =
-                    make_uint2(pack_bf16(r0, r1), pack_bf16(r2, r3));
-            }
-    }
-    return true;
-}
-
 // What an attention item needs that does not change from layer to layer: where the row sits, the rotation of its
 // position (lane l owns the pairs j = 2 l, 2 l + 1 of a head: elements j and j + 64) and the kept rows of the
 // slot's first 32 key blocks (lane b holds block b's).  A warp computes it once per step for its first item.
@@ -413,7 +319,7 @@ struct ItemCtx {
     float cs[2], sn[2];
 };
 
-__device__ __forceinline__ ItemCtx make_item(const StepParams &p, uint32_t item, uint32_t lane) {
+__device__ __noinline__ ItemCtx make_item(const StepParams &p, uint32_t item, uint32_t lane) {
     ItemCtx c;
     c.row = item / p.kv_heads;
     c.kvh = item % p.kv_heads;
@@ -428,7 +334,7 @@ __device__ __forceinline__ ItemCtx make_item(const StepParams &p, uint32_t item,
 // Per-head RMS norm (gains g: elements j and j + 64 of the lane's two pairs; none when `normed` is false) and the
 // half-pair rotation of one 128-wide head held as bf16 in shared memory, in place: the arithmetic of
 // norm_rope_head (head_prep.cuh) with the angles' sines and cosines computed once per step instead of per head.
-__device__ __forceinline__ void norm_rotate(uint16_t *h, const float (&g)[4], bool normed, const ItemCtx &c, float eps,
+__device__ __noinline__ void norm_rotate(uint16_t *h, const float (&g)[4], bool normed, const ItemCtx &c, float eps,
                                             uint32_t lane) {
     const uint32_t va = *reinterpret_cast<const uint32_t *>(h + lane * 2), vb = *reinterpret_cast<const uint32_t *>(h + 64 + lane * 2);
     float a[2] = {bf16_lo(va), bf16_hi(va)}, b[2] = {bf16_lo(vb), bf16_hi(vb)};
@@ -458,16 +364,16 @@ __device__ __forceinline__ void norm_rotate(uint16_t *h, const float (&g)[4], bo
     *reinterpret_cast<uint32_t *>(h + 64 + lane * 2) = (uint32_t)hi[0] | ((uint32_t)hi[1] << 16);
 }
 
-// One (row, kv head) of the decode attention on one warp: q,k,v from the projection's partials, per-head
-// norm and rotation (the stand-alone append kernel's code: same bits), append, then flash attention over the
-// slot's kept rows in 32-key tiles the warp fetches for itself by TMA, two tiles ahead.  The products run on
-// warp MMAs with the GRP query heads in rows 0..GRP-1 of the 16-row operand.
+// One (row, kv head) of the decode attention on one warp: q, k, v of the row from the projection (bf16), per-head
+// norm and rotation, append, then flash attention over the slot's kept rows in 32-key tiles the warp fetches for
+// itself by TMA, two tiles ahead.  The products run on warp MMAs with the GRP query heads in rows 0..GRP-1 of
+// the 16-row operand.
 template <int GRP>
 __device__ __forceinline__ bool attend_item(const StepParams &p, const LayerDev &L, const CUtensorMap *map_k,
                                             const CUtensorMap *map_v, const ItemCtx &c, const float (&qg)[4],
                                             const float (&kg)[4], bool normed, uint32_t lane, uint8_t *stages,
                                             uint16_t *prep, uint64_t *kv_full, uint32_t &kv_parity,
-                                            uint32_t &kv_pending, const Bounds &bd, uint32_t stamp_phase) {
+                                            uint32_t &kv_pending, const Bounds &bd, uint32_t y_base, uint32_t stamp_phase) {
     constexpr int WIDTH = 128;
     (void)stamp_phase;
     const uint32_t row = c.row, kvh = c.kvh, slot = c.slot, pos = c.pos;
@@ -477,7 +383,7 @@ __device__ __forceinline__ bool attend_item(const StepParams &p, const LayerDev 
     auto issue = [&](uint32_t blk) {  // whole warp
         const uint32_t s = blk % kKvStages;
         const uint32_t yl = __shfl_sync(0xFFFFFFFFu, c.y_lane, blk & 31);
-        const int32_t y = (int32_t)(blk < 32 ? yl : kept_row(p.kept, slot, blk * 32));
+        const int32_t y = (int32_t)(y_base + (blk < 32 ? yl : kept_row(p.kept, slot, blk * 32)));  // y_base: the layer's rows in the all-layers tensor
         if (lane == 0) {
             uint8_t *dst = stages + s * kKvStage;
             mbar_expect_tx(&kv_full[s], kKvStage);
@@ -488,57 +394,21 @@ __device__ __forceinline__ bool attend_item(const StepParams &p, const LayerDev 
         }
         kv_pending |= 1u << s;
     };
-    // the row's sums of squares: asked for before anything is waited on
-    float ss_part = 0.0f;
-    for (uint32_t i = lane; i < p.ss_parts; i += 32) ss_part += __ldcg(p.ss + (size_t)row * p.ss_parts + i);
-    if (lane == 0 && stamp_phase) STEP_STAMP(stamp_phase, 4);
-    // ---- q heads, k, v of this row: the projection's partial sums, staged in the second tile stage by bulk
-    // copies (all in flight at once), added in slice order, times 1/rms, as bf16 ----
-    bool ok = true;
-    {
-        const LinPhase &P = p.lin[LIN_QKV];
-        constexpr uint32_t kHeads = GRP + 2, kMost = 32 / kHeads < kKvStage / (kHeads * 512) ? 32 / kHeads : kKvStage / (kHeads * 512);
-        uint8_t *stage = stages + kKvStage;
-        uint64_t *bar = &kv_full[1];
-        float4 acc[kHeads];
+    // ---- q heads, k, v of this row: four values a lane and head, asked for before the key tiles ----
+    uint2 raw[GRP + 2];
 #pragma unroll
-        for (uint32_t u = 0; u < kHeads; u++) acc[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        for (uint32_t s0 = 0; s0 < P.splits; s0 += kMost) {
-            const uint32_t n = min(kMost, P.splits - s0), copies = kHeads * n;   // <= 32: a lane a copy
-            if (lane == 0) {
-                mbar_expect_tx(bar, copies * 512);
-                kv_pending |= 2u;
-            }
-            __syncwarp();
-            if (lane < copies) {
-                const uint32_t u = lane / n, j = lane % n;
-                const bool is_q = u < (uint32_t)GRP, is_v = u == (uint32_t)GRP + 1;
-                const uint32_t h = is_q ? head0 + u : (is_v ? p.heads + p.kv_heads + kvh : p.heads + kvh);
-                bulk_load(stage + lane * 512, P.part + ((size_t)(s0 + j) * kBatch + row) * P.n + h * WIDTH, 512, bar);
-            }
-            if (s0 == 0) issue(0);  // the first key tile follows the small copies into the copy queue
-            ok = wait_bar(bar, (kv_parity >> 1) & 1, bd);
-            if (!ok) return false;
-            kv_parity ^= 2u;
-            kv_pending &= ~2u;
-#pragma unroll
-            for (uint32_t u = 0; u < kHeads; u++)
-                for (uint32_t j = 0; j < n; j++) {
-                    const float4 t = *reinterpret_cast<const float4 *>(stage + (u * n + j) * 512 + lane * 16);
-                    acc[u].x += t.x; acc[u].y += t.y; acc[u].z += t.z; acc[u].w += t.w;
-                }
-            __syncwarp();
-        }
-        const float inv = 1.0f / sqrtf(warp_sum(ss_part) / (float)p.hidden + p.eps);
-#pragma unroll
-        for (uint32_t u = 0; u < kHeads; u++)
-            *reinterpret_cast<uint2 *>(prep + u * WIDTH + lane * 4) =
-                make_uint2(pack_bf16(acc[u].x * inv, acc[u].y * inv), pack_bf16(acc[u].z * inv, acc[u].w * inv));
+    for (uint32_t u = 0; u < (uint32_t)GRP + 2; u++) {
+        const bool is_q = u < (uint32_t)GRP, is_v = u == (uint32_t)GRP + 1;
+        const uint32_t h = is_q ? head0 + u : (is_v ? p.heads + p.kv_heads + kvh : p.heads + kvh);
+        raw[u] = __ldcg(reinterpret_cast<const uint2 *>(p.qkv + (size_t)row * p.qkv_n + h * WIDTH + lane * 4));
     }
-    if (lane == 0 && stamp_phase) STEP_STAMP(stamp_phase, 5);
-    if (n_blk > 1) issue(1);  // the staging area is a tile stage again
-    __syncwarp();
+    if (lane == 0 && stamp_phase) STEP_STAMP(stamp_phase, 4);
+    issue(0);
+    if (n_blk > 1) issue(1);
 #pragma unroll
+    for (uint32_t u = 0; u < (uint32_t)GRP + 2; u++) *reinterpret_cast<uint2 *>(prep + u * WIDTH + lane * 4) = raw[u];
+    __syncwarp();
+#pragma unroll 1
     for (uint32_t u = 0; u < (uint32_t)GRP + 1; u++) norm_rotate(prep + u * WIDTH, u < (uint32_t)GRP ? qg : kg, normed, c, p.eps, lane);
     __syncwarp();
     {   // the new kept row, for later steps: lanes 0-15 the key, 16-31 the value
@@ -546,7 +416,7 @@ __device__ __forceinline__ bool attend_item(const StepParams &p, const LayerDev 
         const uint16_t *from = prep + (GRP + (lane >> 4)) * WIDTH;
         reinterpret_cast<uint4 *>((lane < 16 ? L.k_rows : L.v_rows) + at)[lane & 15] = reinterpret_cast<const uint4 *>(from)[lane & 15];
     }
-    if (lane == 0 && stamp_phase) STEP_STAMP(stamp_phase, 6);
+    bool ok = true;
     const uint32_t hrow = lane >> 2, quad = lane & 3;
     uint32_t qa[8][2];
 #pragma unroll
@@ -670,14 +540,24 @@ __global__ void __launch_bounds__(kThreads, 1) decode_layers_kernel(const __grid
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, cta = blockIdx.x, G = p.blocks;
+    const uint32_t rank = cluster_ctarank(), cid = cta / kCluster;
     unsigned char *ring = smem + Smem::ring;
-    unsigned char *uni = smem + Smem::uni;
+    unsigned char *xbuf = smem + Smem::x;
+    float *recv = reinterpret_cast<float *>(smem + Smem::recv);
+    float *send = reinterpret_cast<float *>(smem + Smem::send);
+    float *red = reinterpret_cast<float *>(smem + Smem::red);  // [kWorkers][kOwn]
+    float *inv_s = red + kWorkers * kOwn;                      // [kOwn]: 1/rms of the batch rows this block owns
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + Smem::bars);
     uint64_t *ring_full = bars, *ring_empty = bars + kRing;
     uint64_t *x_full = ring_empty + kRing;
     uint64_t *acc_full = x_full + 1, *acc_empty = acc_full + kAccStages;
     uint64_t *workers_done = acc_empty + kAccStages, *phase_go = workers_done + 1;
     uint64_t *kv_full = phase_go + 1;  // [kWorkers][kKvStages]
+    uint64_t *send_full = kv_full + kWorkers * kKvStages;  // the four warps have staged their partials
+    uint64_t *recv_full = send_full + 1;                   // the eight blocks' partials of my columns have landed
+    uint64_t *peers_free = recv_full + 1;                  // every block of the cluster has read its receive buffer
+    uint64_t *red_full = peers_free + 1;                   // the four warps' sums of squares are in shared memory
+    uint64_t *inv_full = red_full + 1;                     // inv_s is written
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + Smem::misc);
     volatile uint32_t *abort_s = tmem_slot + 1;
     const Bounds bd = {abort_s, p.sync + 1, p.wait_ns};
@@ -695,6 +575,11 @@ __global__ void __launch_bounds__(kThreads, 1) decode_layers_kernel(const __grid
         mbar_init(workers_done, kWorkers);
         mbar_init(phase_go, 1);
         for (uint32_t s = 0; s < kWorkers * kKvStages; s++) mbar_init(&kv_full[s], 1);
+        mbar_init(send_full, kWorkers);
+        mbar_init(recv_full, 1);
+        mbar_init(peers_free, kCluster * kWorkers);
+        mbar_init(red_full, kWorkers);
+        mbar_init(inv_full, 1);
         *abort_s = 0;
         fence_barrier_init();
     }
@@ -702,43 +587,90 @@ __global__ void __launch_bounds__(kThreads, 1) decode_layers_kernel(const __grid
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
+    cluster_sync();  // every block's barriers exist before a peer signals them
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t L = p.n_layers;
+    const uint32_t L = p.n_layers, C = p.clusters;
 
     if (warp == 0) {
-        // ---- weight producer: the block's tiles of every phase and layer, in schedule order ----
+        // ---- weight producer: the block's k slice of its cluster's tiles, every phase and layer, in order.  A
+        // second cursor runs kAhead tiles in front and asks L2 for them, so that a stage freed at the end of a
+        // phase refills from L2 in about a microsecond instead of from HBM in three or four.
         if (lane == 0) {
-            uint32_t it = 0;
-            bool ok = true;
-            for (uint32_t l = 0; l < L && ok; l++) {
-                for (uint32_t ph = 0; ph < 4 && ok; ph++) {
-                    const LinPhase &P = p.lin[ph];
-                    const CUtensorMap *mw = p.maps + l * 4 + ph;
-                    for (uint32_t u = first_unit(p, l, ph, cta); u < P.units && ok; u += G) {
-                        const uint32_t tile = u / P.splits;
-                        uint32_t kb0, kb1;
-                        k_slice(P, u % P.splits, kb0, kb1);
-                        for (uint32_t kb = kb0; kb < kb1; kb++, it++) {
-                            const uint32_t s = it % kRing;
-                            ok = wait_bar(&ring_empty[s], ((it / kRing) & 1) ^ 1, bd);
-                            if (!ok) break;
-                            if (it >= kInFlight) {  // pace the stream: a burst of tiles would queue ahead of the small, urgent copies
-                                const uint32_t j = it - kInFlight;
-                                ok = wait_bar(&ring_full[j % kRing], (j / kRing) & 1, bd);
-                                if (!ok) break;
-                            }
-                            unsigned char *dst = ring + s * kTile;
-                            mbar_expect_tx(&ring_full[s], kTile);
-                            const int32_t kx = (int32_t)(kb * 64);
-                            if (P.gated) {
-                                tma_load_2d(dst, mw, &ring_full[s], kx, (int32_t)(tile * 64));
-                                tma_load_2d(dst + kTile / 2, mw, &ring_full[s], kx, (int32_t)(P.n / 2 + tile * 64));
-                            } else {
-                                tma_load_2d(dst, mw, &ring_full[s], kx, (int32_t)(tile * 128));
-                            }
-                        }
+            struct Cursor {
+                uint32_t l, ph, tile, kb, kb1;
+            };
+            auto settle = [&](Cursor &c) {  // moves to the next (layer, phase) that has a tile for this cluster
+                while (c.l < L) {
+                    const LinPhase &P = p.lin[c.ph];
+                    if (c.tile == 0xFFFFFFFFu) {
+                        c.tile = first_tile(p, c.l, c.ph, cid);
+                        uint32_t kb0;
+                        k_slice(P, rank, kb0, c.kb1);
+                        c.kb = kb0;
+                    }
+                    if (c.tile < P.tiles) return true;
+                    c.tile = 0xFFFFFFFFu;
+                    if (++c.ph == 4) {
+                        c.ph = 0;
+                        c.l++;
                     }
                 }
+                return false;
+            };
+            auto advance = [&](Cursor &c) {
+                const LinPhase &P = p.lin[c.ph];
+                if (++c.kb < c.kb1) return;
+                uint32_t kb0;
+                k_slice(P, rank, kb0, c.kb1);
+                c.kb = kb0;
+                c.tile += C;
+                if (c.tile >= P.tiles) {
+                    c.tile = 0xFFFFFFFFu;
+                    if (++c.ph == 4) {
+                        c.ph = 0;
+                        c.l++;
+                    }
+                }
+            };
+            auto coords = [&](const Cursor &c, int32_t &y0, int32_t &y1) {
+                const LinPhase &P = p.lin[c.ph];
+                const uint32_t base = c.l * P.n;  // the layer's rows in the all-layers tensor
+                y0 = (int32_t)(base + (P.gated ? c.tile * 64 : c.tile * 128));
+                y1 = (int32_t)(base + P.n / 2 + c.tile * 64);
+            };
+            Cursor cur = {0, 0, 0xFFFFFFFFu, 0, 0}, ahead = cur;
+            uint32_t it = 0, asked = 0;
+            bool ok = true;
+#pragma unroll 1
+            while (ok && settle(cur)) {
+                // keep the look-ahead cursor kAhead tiles in front
+#pragma unroll 1
+                while (asked < it + kAhead && settle(ahead)) {
+                    const CUtensorMap *ma = &p.w_maps[ahead.ph];
+                    int32_t y0, y1;
+                    coords(ahead, y0, y1);
+                    tma_prefetch_2d(ma, (int32_t)(ahead.kb * 64), y0);
+                    if (p.lin[ahead.ph].gated) tma_prefetch_2d(ma, (int32_t)(ahead.kb * 64), y1);
+                    advance(ahead);
+                    asked++;
+                }
+                const uint32_t s = it % kRing;
+                ok = wait_bar(&ring_empty[s], ((it / kRing) & 1) ^ 1, bd);
+                if (!ok) break;
+                const CUtensorMap *mw = &p.w_maps[cur.ph];
+                unsigned char *dst = ring + s * kTile;
+                int32_t y0, y1;
+                coords(cur, y0, y1);
+                mbar_expect_tx(&ring_full[s], kTile);
+                const int32_t kx = (int32_t)(cur.kb * 64);
+                if (p.lin[cur.ph].gated) {
+                    tma_load_2d(dst, mw, &ring_full[s], kx, y0);
+                    tma_load_2d(dst + kTile / 2, mw, &ring_full[s], kx, y1);
+                } else {
+                    tma_load_2d(dst, mw, &ring_full[s], kx, y0);
+                }
+                advance(cur);
+                it++;
             }
             if (!ok) {  // copies still in flight must land before the block leaves
                 for (uint32_t back = 0; back < kRing && back < it; back++) {
@@ -748,7 +680,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_layers_kernel(const __grid
             }
         }
     } else if (warp == 1) {
-        // ---- control: the MMAs of the block's units and the barrier between phases ----
+        // ---- control: the MMAs of the block's k slice and the barrier between phases ----
         if (lane == 0) {
             const uint32_t idesc = umma_idesc_bf16(128, kBatch);
             uint32_t it = 0, xi = 0, ai = 0, bar = 0;
@@ -763,62 +695,50 @@ __global__ void __launch_bounds__(kThreads, 1) decode_layers_kernel(const __grid
             };
             auto linear = [&](uint32_t l, uint32_t ph) {
                 const LinPhase &P = p.lin[ph];
-                const CUtensorMap *mx = &p.x_maps[P.x_map];
-                bool first = true;
-                for (uint32_t u = first_unit(p, l, ph, cta); u < P.units && ok; u += G) {
-                    uint32_t kb0, kb1;
-                    k_slice(P, u % P.splits, kb0, kb1);
-                    const uint32_t nkb = kb1 - kb0;
-                    if (!first) {  // the x slice is still being read by the previous unit's MMAs
-                        const uint32_t prev = ai - 1;
-                        ok = wait_bar(&acc_full[prev % kAccStages], (prev / kAccStages) & 1, bd);
-                        if (!ok) break;
-                    }
-                    first = false;
-                    mbar_expect_tx(x_full, nkb * kXkb);
-                    for (uint32_t j = 0; j < nkb; j++) tma_load_2d(uni + j * kXkb, mx, x_full, (int32_t)((kb0 + j) * 64), 0);
-                    x_pending = true;
+                uint32_t tile = first_tile(p, l, ph, cid);
+                if (tile >= P.tiles || !ok) return;
+                uint32_t kb0, kb1;
+                k_slice(P, rank, kb0, kb1);
+                const uint32_t nkb = kb1 - kb0;
+                // the block's k slice of the batch rows: the same for every tile of the phase
+                mbar_expect_tx(x_full, nkb * kXkb);
+                for (uint32_t j = 0; j < nkb; j++) tma_load_2d(xbuf + j * kXkb, &p.x_maps[P.x_map], x_full, (int32_t)((kb0 + j) * 64), 0);
+                x_pending = true;
+                ok = wait_bar(x_full, xi & 1, bd);
+                if (!ok) return;
+                x_pending = false;
+                xi++;
+                STEP_STAMP(bar, 4);
+                for (; tile < P.tiles; tile += C) {
                     const uint32_t as = ai % kAccStages;
                     ok = wait_bar(&acc_empty[as], ((ai / kAccStages) & 1) ^ 1, bd);
-                    if (!ok) break;
-                    ok = wait_bar(x_full, xi & 1, bd);
-                    if (!ok) break;
-                    x_pending = false;
-                    xi++;
-                    STEP_STAMP(bar, 4);
+                    if (!ok) return;
                     tc_fence_after_sync();
                     const uint32_t d_tmem = tmem_base + as * kBatch;
                     for (uint32_t kb = 0; kb < nkb; kb++, it++) {
                         const uint32_t s = it % kRing;
                         ok = wait_bar(&ring_full[s], (it / kRing) & 1, bd);
-                        if (!ok) break;
+                        if (!ok) return;
                         tc_fence_after_sync();
                         const uint64_t da = umma_desc_k_sw128(smem_addr(ring + s * kTile));
-                        const uint64_t db = umma_desc_k_sw128(smem_addr(uni + kb * kXkb));
+                        const uint64_t db = umma_desc_k_sw128(smem_addr(xbuf + kb * kXkb));
 #pragma unroll
                         for (uint32_t k16 = 0; k16 < 4; k16++) umma_bf16(d_tmem, da + 2 * k16, db + 2 * k16, idesc, (kb | k16) != 0);
                         umma_commit(&ring_empty[s]);
                     }
-                    if (!ok) break;
                     umma_commit(&acc_full[as]);
                     STEP_STAMP(bar, 5);
                     ai++;
                 }
             };
             sync_phase();  // the gather
-            for (uint32_t l = 0; l < L; l++) {
-                linear(l, LIN_QKV);
-                sync_phase();
-                sync_phase();  // attention
-                linear(l, LIN_O);
-                sync_phase();
-                sync_phase();  // residual
-                linear(l, LIN_GU);
-                sync_phase();
-                sync_phase();  // gate
-                linear(l, LIN_DOWN);
-                sync_phase();
-                if (l + 1 < L) sync_phase();  // residual; nothing follows the last one
+            // One copy of the phase code, walked by a loop that is not unrolled: the kernel's instructions must stay
+            // within the instruction cache, or every phase of every layer starts by fetching its code again.
+#pragma unroll 1
+            for (uint32_t step = 0; step < 5 * L; step++) {
+                const uint32_t l = step / 5, k5 = step % 5;  // q,k,v | attention | o | gate,up | down
+                if (k5 != 1) linear(l, k5 == 0 ? LIN_QKV : k5 - 1);
+                if (step + 1 < 5 * L) sync_phase();  // nothing follows the last one
             }
             if (x_pending) drain_bar(x_full, xi & 1, p.wait_ns);
         }
@@ -826,16 +746,17 @@ __global__ void __launch_bounds__(kThreads, 1) decode_layers_kernel(const __grid
         // ---- workers ----
         const uint32_t w = warp - 2, q = warp & 3;
         const uint32_t wid = w * G + cta;  // spreads consecutive units over the blocks first
-        uint32_t ai = 0, bar = 0;
+        const uint32_t row = q * 32 + lane;  // the tile row (TMEM lane) this thread owns
+        uint32_t ai = 0, bar = 0, unit = 0, n_inv = 0, n_red = 0;
         uint32_t kv_parity = 0, kv_pending = 0;  // bit s: parity of the next completion of stage s / a copy in flight
-        bool ok = true;
-        uint8_t *stages = uni + w * kKvStages * kKvStage;
+        bool ok = true, sent = false;
+        uint8_t *stages = smem + Smem::uni + w * kKvStages * kKvStage;
         uint16_t *prep = reinterpret_cast<uint16_t *>(smem + Smem::prep) + w * kPrepHeads * 128;
         uint64_t *my_kv_full = kv_full + w * kKvStages;
-        const Stage st = {stages, my_kv_full, &kv_parity, &kv_pending};  // the residual and gate phases stage through tile stage 0
+        const uint32_t recv_addr = smem_addr(recv), send_addr = smem_addr(send);
+        const uint32_t recv_full_addr = smem_addr(recv_full), peers_free_addr = smem_addr(peers_free);
         auto begin = [&]() {  // the barrier that ended the previous phase
             if (ok && bar > 0) ok = wait_bar(phase_go, (bar - 1) & 1, bd);
-            fence_proxy_async_all();  // this warp's bulk copies read what other blocks stored before the barrier
             if (w == 0 && lane == 0) STEP_STAMP(bar, 2);
         };
         auto done = [&]() {
@@ -845,10 +766,29 @@ __global__ void __launch_bounds__(kThreads, 1) decode_layers_kernel(const __grid
             if (lane == 0) mbar_arrive(workers_done);
             bar++;
         };
-        auto drain = [&](uint32_t l, uint32_t ph) {  // accumulators of the block's units -> partial sums
+        // The cluster's tiles of a linear phase: partial accumulators out of TMEM, exchanged through distributed
+        // shared memory, added in rank order, finished with the phase's stage chain and stored.
+        auto finish = [&](uint32_t l, uint32_t ph, const float *gain) {
             const LinPhase &P = p.lin[ph];
-            for (uint32_t u = first_unit(p, l, ph, cta); u < P.units && ok; u += G) {
-                const uint32_t tile = u / P.splits, split = u % P.splits;
+            uint32_t tile = first_tile(p, l, ph, cid);
+            if (tile >= P.tiles) return;
+            const uint32_t m0 = rank * kOwn;  // the batch rows this block owns
+            if (P.epilogue != EPI_RESIDUAL) {
+                // 1/rms of the owned batch rows, from the sums of squares the last residual-feeding phase left
+                if (w == 0 && ok) {
+                    const uint32_t i = lane >> 2, sub = lane & 3;
+                    float ss = 0.0f;
+                    for (uint32_t part = sub; part < p.ss_parts; part += 4) ss += __ldcg(p.ss + (size_t)(m0 + i) * p.ss_parts + part);
+                    ss += __shfl_xor_sync(0xFFFFFFFFu, ss, 1);
+                    ss += __shfl_xor_sync(0xFFFFFFFFu, ss, 2);
+                    if (sub == 0) inv_s[i] = 1.0f / sqrtf(ss / (float)p.hidden + p.eps);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(inv_full);
+                }
+                if (ok) ok = wait_bar(inv_full, n_inv & 1, bd);
+                n_inv++;
+            }
+            for (; tile < P.tiles && ok; tile += C, unit++) {
                 const uint32_t as = ai % kAccStages;
                 ok = wait_bar(&acc_full[as], (ai / kAccStages) & 1, bd);
                 if (!ok) break;
@@ -867,13 +807,101 @@ __global__ void __launch_bounds__(kThreads, 1) decode_layers_kernel(const __grid
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&acc_empty[as]);
-                if (w == 0 && lane == 0) STEP_STAMP(bar, 7);
-                const uint32_t r = q * 32 + lane;
-                const uint32_t n = P.gated ? (r < 64 ? tile * 64 + r : P.n / 2 + tile * 64 + (r - 64)) : tile * 128 + r;
-                float *dst = P.part + (size_t)split * kBatch * P.n + n;
+                // What the stage chain reads besides the sum, asked for now: it arrives under the exchange.
+                const bool upper = P.gated && row >= 64;  // an up row: its gate row's thread finishes the pair
+                const uint32_t n = P.gated ? tile * 64 + (row & 63) : tile * 128 + row;
+                float res[kOwn];
+                float g = 0.0f;
+                if (P.epilogue == EPI_RESIDUAL) {
 #pragma unroll
-                for (uint32_t c = 0; c < kBatch; c++)
-                    if (c < p.rows) dst[(size_t)c * P.n] = v[c];
+                    for (uint32_t i = 0; i < kOwn; i++) res[i] = m0 + i < p.rows ? __ldcg(p.x + (size_t)(m0 + i) * P.n + n) : 0.0f;
+                    if (gain) g = __ldg(gain + n);
+                }
+                // The previous tile's exchange must be over in every block of the cluster: its buffers are reused.
+                if (sent) {
+                    ok = wait_bar(peers_free, (unit - 1) & 1, bd);
+                    if (!ok) break;
+                }
+                // Stage the partial by destination block, then one thread sends each block its 128 x 8 share.
+#pragma unroll
+                for (uint32_t d = 0; d < kCluster; d++) {
+                    float *to = send + d * (kXfer / 4);
+                    *reinterpret_cast<float4 *>(to + xfer_at(row, 0)) = make_float4(v[8 * d], v[8 * d + 1], v[8 * d + 2], v[8 * d + 3]);
+                    *reinterpret_cast<float4 *>(to + xfer_at(row, 1)) = make_float4(v[8 * d + 4], v[8 * d + 5], v[8 * d + 6], v[8 * d + 7]);
+                }
+                fence_async_shared();  // the copy engine reads what these threads wrote
+                __syncwarp();
+                if (lane == 0) mbar_arrive(send_full);
+                if (w == 0 && lane == 0) {
+                    mbar_expect_tx(recv_full, kCluster * kXfer);
+                    if (wait_bar(send_full, unit & 1, bd)) {
+                        for (uint32_t d = 0; d < kCluster; d++)
+                            bulk_copy_to_peer(map_to_rank(recv_addr + rank * kXfer, d), send_addr + d * kXfer, kXfer,
+                                              map_to_rank(recv_full_addr, d));
+                    }
+                }
+                sent = true;
+                if (w == 0 && lane == 0) STEP_STAMP(bar, 7);
+                ok = wait_bar(recv_full, unit & 1, bd);
+                if (!ok) break;
+                // Add the eight partials of the owned columns in rank order.
+                float a[kOwn], b[kOwn];
+                auto sum_row = [&](uint32_t r, float (&out)[kOwn]) {
+                    const float4 lo = *reinterpret_cast<const float4 *>(recv + xfer_at(r, 0));
+                    const float4 hi = *reinterpret_cast<const float4 *>(recv + xfer_at(r, 1));
+                    out[0] = lo.x; out[1] = lo.y; out[2] = lo.z; out[3] = lo.w;
+                    out[4] = hi.x; out[5] = hi.y; out[6] = hi.z; out[7] = hi.w;
+#pragma unroll
+                    for (uint32_t s = 1; s < kCluster; s++) {
+                        const float4 l2 = *reinterpret_cast<const float4 *>(recv + s * (kXfer / 4) + xfer_at(r, 0));
+                        const float4 h2 = *reinterpret_cast<const float4 *>(recv + s * (kXfer / 4) + xfer_at(r, 1));
+                        out[0] += l2.x; out[1] += l2.y; out[2] += l2.z; out[3] += l2.w;
+                        out[4] += h2.x; out[5] += h2.y; out[6] += h2.z; out[7] += h2.w;
+                    }
+                };
+                sum_row(row, a);
+                if (P.gated && !upper) sum_row(row + 64, b);
+                // this block has read its receive buffer: tell every block of the cluster (itself included)
+                __syncwarp();
+                if (lane == 0) {
+                    for (uint32_t d = 0; d < kCluster; d++) mbar_arrive_remote(map_to_rank(peers_free_addr, d));
+                }
+                if (P.epilogue == EPI_QKV) {
+#pragma unroll
+                    for (uint32_t i = 0; i < kOwn; i++)
+                        if (m0 + i < p.rows) p.qkv[(size_t)(m0 + i) * P.n + n] = bf16_bits(a[i] * inv_s[i]);
+                } else if (P.epilogue == EPI_GATED) {
+                    if (!upper) {
+#pragma unroll
+                        for (uint32_t i = 0; i < kOwn; i++)
+                            if (m0 + i < p.rows) p.act[(size_t)(m0 + i) * (P.n / 2) + n] = bf16_bits(silu(a[i] * inv_s[i]) * (b[i] * inv_s[i]));
+                    }
+                } else {
+#pragma unroll
+                    for (uint32_t i = 0; i < kOwn; i++) {
+                        const float r = a[i] + res[i];
+                        const size_t at = (size_t)(m0 + i) * P.n + n;
+                        if (m0 + i < p.rows) {
+                            p.x[at] = r;
+                            if (gain) p.xs[at] = bf16_bits(r * g);
+                        }
+                        if (gain) {  // sums of squares of the finished rows over this tile's 128 columns
+                            const float t = warp_sum(r * r);
+                            if (lane == 0) red[w * kOwn + i] = t;
+                        }
+                    }
+                    if (gain) {
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(red_full);
+                        ok = wait_bar(red_full, n_red & 1, bd);
+                        n_red++;
+                        if (!ok) break;
+                        if (w == 0 && lane < kOwn && m0 + lane < p.rows)
+                            p.ss[(size_t)(m0 + lane) * p.ss_parts + tile] = ((red[lane] + red[kOwn + lane]) + red[2 * kOwn + lane]) + red[3 * kOwn + lane];
+                        __syncwarp();
+                        // (the next tile's partial sums are written only after the next exchange, which every warp joins)
+                    }
+                }
             }
         };
         const uint32_t items = p.rows * p.kv_heads;
@@ -883,49 +911,42 @@ __global__ void __launch_bounds__(kThreads, 1) decode_layers_kernel(const __grid
         // phase 0: the gather
         gather_phase(p, p.layers[0].ln1, wid, lane);
         done();
-        for (uint32_t l = 0; l < L; l++) {
+        bool normed = false;
+#pragma unroll 1
+        for (uint32_t step = 0; step < 5 * L; step++) {
+            const uint32_t l = step / 5, k5 = step % 5;  // q,k,v | attention | o | gate,up | down
             const LayerDev &Ly = p.layers[l];
             begin();
-            const bool normed = Ly.q_norm != nullptr;
-            if (ok && normed && wid < items) {  // the per-head gains of this layer, long before the attention phase wants them
+            if (k5 == 0) {
+                normed = Ly.q_norm != nullptr;
+                if (ok && normed && wid < items) {  // the per-head gains of this layer, long before the attention phase wants them
 #pragma unroll
-                for (int e = 0; e < 2; e++) {
-                    qg[e] = __ldg(Ly.q_norm + lane * 2 + e);
-                    qg[2 + e] = __ldg(Ly.q_norm + 64 + lane * 2 + e);
-                    kg[e] = __ldg(Ly.k_norm + lane * 2 + e);
-                    kg[2 + e] = __ldg(Ly.k_norm + 64 + lane * 2 + e);
+                    for (int e = 0; e < 2; e++) {
+                        qg[e] = __ldg(Ly.q_norm + lane * 2 + e);
+                        qg[2 + e] = __ldg(Ly.q_norm + 64 + lane * 2 + e);
+                        kg[e] = __ldg(Ly.k_norm + lane * 2 + e);
+                        kg[2 + e] = __ldg(Ly.k_norm + 64 + lane * 2 + e);
+                    }
                 }
+                if (ok) prefetch_kept(p, Ly, wid, lane);
             }
-            if (ok) prefetch_kept(p, Ly, wid, lane);
-            drain(l, LIN_QKV);
-            done();
-            begin();
-            if (ok) {
-                const CUtensorMap *mk = p.maps + 4 * L + 2 * l, *mv = mk + 1;
-                for (uint32_t item = wid; item < items && ok; item += kWorkers * G) {
-                    const ItemCtx c = item == wid ? first_item : make_item(p, item, lane);
-                    ok = attend_item<GRP>(p, Ly, mk, mv, c, qg, kg, normed, lane, stages, prep, my_kv_full, kv_parity, kv_pending, bd,
-                                          w == 0 ? bar : 0);
+            if (k5 == 1) {
+                if (w == 0 && lane == 0) STEP_STAMP(bar, 5);
+                if (ok) {
+                    const CUtensorMap *mk = &p.kv_maps[0], *mv = &p.kv_maps[1];
+#pragma unroll 1
+                    for (uint32_t item = wid; item < items && ok; item += kWorkers * G) {
+                        ItemCtx c = first_item;
+                        if (item != wid) c = make_item(p, item, lane);
+                        if (w == 0 && lane == 0) STEP_STAMP(bar, 6);
+                        ok = attend_item<GRP>(p, Ly, mk, mv, c, qg, kg, normed, lane, stages, prep, my_kv_full, kv_parity, kv_pending, bd,
+                                              l * p.kept_rows, w == 0 ? bar : 0);
+                    }
                 }
+            } else {
+                const float *gain = k5 == 2 ? Ly.ln2 : (k5 == 4 && l + 1 < L) ? p.layers[l + 1].ln1 : nullptr;
+                finish(l, k5 == 0 ? LIN_QKV : k5 - 1, gain);
             }
-            done();
-            begin();
-            drain(l, LIN_O);
-            done();
-            begin();
-            if (ok) ok = residual_phase(p, p.lin[LIN_O], Ly.ln2, wid, lane, st, bd);
-            done();
-            begin();
-            drain(l, LIN_GU);
-            done();
-            begin();
-            if (ok) ok = gated_phase(p, p.lin[LIN_GU], wid, lane, st, bd);
-            done();
-            begin();
-            drain(l, LIN_DOWN);
-            done();
-            begin();
-            if (ok) ok = residual_phase(p, p.lin[LIN_DOWN], l + 1 < L ? p.layers[l + 1].ln1 : nullptr, wid, lane, st, bd);
             done();
         }
         if (!ok && lane == 0) {
@@ -936,6 +957,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_layers_kernel(const __grid
 
     tc_fence_before_sync();
     __syncthreads();
+    cluster_sync();  // no block leaves while a peer may still write into it or signal it
     if (threadIdx.x == 0 && *abort_s) atomicExch(p.status, TS_ERR_TIMEOUT);
     if (warp == 1) {
         tc_fence_after_sync();
@@ -968,6 +990,36 @@ bool step_kernel_enabled() {
     return !off;
 }
 
+template <typename Kernel>
+cudaError_t cluster_config(Kernel kernel, uint32_t blocks, cudaStream_t stream, cudaLaunchConfig_t *cfg, cudaLaunchAttribute *attr) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Smem::bytes);
+    if (e != cudaSuccess) return e;
+    *cfg = {};
+    cfg->gridDim = dim3(blocks);
+    cfg->blockDim = dim3(kThreads);
+    cfg->dynamicSmemBytes = Smem::bytes;
+    cfg->stream = stream;
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = kCluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg->attrs = attr;
+    cfg->numAttrs = 1;
+    return cudaSuccess;
+}
+
+// Clusters of eight blocks of this kernel that the device holds at once.
+template <typename Kernel>
+int resident_clusters(Kernel kernel, uint32_t *out) {
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr[1];
+    TS_CUDA(cluster_config(kernel, (uint32_t)sm_count() / kCluster * kCluster, nullptr, &cfg, attr));
+    int n = 0;
+    TS_CUDA(cudaOccupancyMaxActiveClusters(&n, kernel, &cfg));
+    *out = n > 0 ? (uint32_t)n : 0;
+    return TS_OK;
+}
+
 }  // namespace
 
 #ifdef TS_DEBUG_STAMPS
@@ -988,38 +1040,31 @@ int step_take_status() {
 struct StepKernel {
     StepParams p = {};
     uint32_t group = 0;
-    void *maps = nullptr, *layers = nullptr, *sync = nullptr;
-    float *parts[4] = {nullptr, nullptr, nullptr, nullptr};
+    void *layers = nullptr, *sync = nullptr;
     std::vector<void *> owned;
 };
 
 bool step_kernel_supports(const StepKernelShape &s) {
     if (!step_kernel_enabled()) return false;
-    if (s.head_dim != 128 || s.heads % s.kv_heads != 0) return false;
+    if (s.head_dim != 128 || s.kv_heads == 0 || s.heads % s.kv_heads != 0) return false;
     const uint32_t group = s.heads / s.kv_heads;
     if (group != 1 && group != 2 && group != 4) return false;
-    if (s.hidden % 256 != 0 || s.ffn % 256 != 0 || (s.heads * s.head_dim) % 256 != 0 || s.hidden > 8192) return false;
+    const uint32_t qw = s.heads * 128;
+    // every product's k splits eight ways into slices of one to kMaxKb 64-wide blocks; tiles are whole
+    for (uint32_t k : {s.hidden, qw, s.ffn})
+        if (k % 64 != 0 || k / 64 < kCluster || ceil_div(k / 64, kCluster) > kMaxKb) return false;
+    if (s.hidden % 128 != 0 || s.ffn % 64 != 0 || s.hidden > 8192) return false;
     if (!(s.page == 0 || s.page >= 32)) return false;  // 32 aligned positions must be 32 consecutive kept rows
-    if (s.kept_rows == 0) return false;
-    return true;
+    return s.kept_rows > 0;
 }
 
-static void plan_linear(LinPhase *P, uint32_t n, uint32_t k, bool gated, uint32_t x_map, uint32_t blocks) {
+static void plan_linear(LinPhase *P, uint32_t n, uint32_t k, bool gated, uint32_t x_map, uint32_t epilogue) {
     P->n = n;
     P->kb_total = k / 64;
     P->gated = gated ? 1 : 0;
     P->tiles = gated ? (n / 2) / 64 : n / 128;
     P->x_map = x_map;
-    // As many k slices as keep one wave of units, at least what the x slice's shared memory asks for; then the
-    // fewest slices with the same longest slice (fewer partial sums to add up, same critical path).
-    uint32_t most = std::max<uint32_t>(1, blocks / P->tiles);
-    most = std::min<uint32_t>(std::min<uint32_t>(most, P->kb_total), 32);
-    const uint32_t least = ceil_div(P->kb_total, kMaxKb);
-    uint32_t s = std::max(most, least);
-    const uint32_t longest = ceil_div(P->kb_total, s);
-    while (s > least && s > 1 && ceil_div(P->kb_total, s - 1) == longest) s--;
-    P->splits = s;
-    P->units = P->tiles * s;
+    P->epilogue = epilogue;
 }
 
 int step_kernel_create(const StepKernelShape &s, const StepKernelBuffers &b, StepKernel **out) {
@@ -1031,7 +1076,15 @@ int step_kernel_create(const StepKernelShape &s, const StepKernelBuffers &b, Ste
     StepParams &p = k->p;
     const uint32_t H = s.hidden, QW = s.heads * 128, KW = s.kv_heads * 128, F = s.ffn, L = s.layers;
     k->group = s.heads / s.kv_heads;
-    p.blocks = (uint32_t)sm_count();
+    int rc;
+    uint32_t clusters = 0;
+    rc = k->group == 1 ? resident_clusters(decode_layers_kernel<1>, &clusters)
+         : k->group == 2 ? resident_clusters(decode_layers_kernel<2>, &clusters)
+                         : resident_clusters(decode_layers_kernel<4>, &clusters);
+    if (rc != TS_OK) return bail(rc);
+    if (clusters == 0) return bail(fail(TS_ERR_CUDA, "step kernel: no cluster of %u blocks fits this device", kCluster));
+    p.clusters = clusters;
+    p.blocks = clusters * kCluster;
     p.n_layers = L;
     p.hidden = H;
     p.qw = QW;
@@ -1040,58 +1093,59 @@ int step_kernel_create(const StepKernelShape &s, const StepKernelBuffers &b, Ste
     p.kv_heads = s.kv_heads;
     p.qkv_n = QW + 2 * KW;
     p.ss_parts = H / 128;
-    p.vocab = s.vocab;
-    plan_linear(&p.lin[LIN_QKV], p.qkv_n, H, false, 0, p.blocks);
-    plan_linear(&p.lin[LIN_O], H, QW, false, 1, p.blocks);
-    plan_linear(&p.lin[LIN_GU], 2 * F, H, true, 0, p.blocks);
-    plan_linear(&p.lin[LIN_DOWN], H, F, false, 2, p.blocks);
+    plan_linear(&p.lin[LIN_QKV], p.qkv_n, H, false, 0, EPI_QKV);
+    plan_linear(&p.lin[LIN_O], H, QW, false, 1, EPI_RESIDUAL);
+    plan_linear(&p.lin[LIN_GU], 2 * F, H, true, 0, EPI_GATED);
+    plan_linear(&p.lin[LIN_DOWN], H, F, false, 2, EPI_RESIDUAL);
     uint32_t cum = 0;
     for (int i = 0; i < 4; i++) {
         p.lin[i].cum = cum;
-        cum += p.lin[i].units;
+        cum += p.lin[i].tiles;
     }
-    p.units_per_layer = cum;
+    p.tiles_per_layer = cum;
     auto dev = [&](void **ptr, size_t bytes) -> int {
         TS_CUDA(cudaMalloc(ptr, bytes));
         k->owned.push_back(*ptr);
         TS_CUDA(cudaMemset(*ptr, 0, bytes));
         return TS_OK;
     };
-    int rc;
-    for (int i = 0; i < 4; i++) {
-        if ((rc = dev((void **)&k->parts[i], (size_t)p.lin[i].splits * kBatch * p.lin[i].n * sizeof(float))) != TS_OK) return bail(rc);
-        p.lin[i].part = k->parts[i];
-    }
     if ((rc = dev(&k->sync, 256)) != TS_OK) return bail(rc);
     p.sync = (uint32_t *)k->sync;
-    // tensor maps: weights of every layer, the three activations, kept K and V of every layer
-    std::vector<CUtensorMap> maps(6 * (size_t)L);
+    // One tensor map per weight over all layers (the layers' copies must lie back to back, which the runner's slabs
+    // guarantee), one each for the kept K and V rows, three for the activations.
     std::vector<LayerDev> layers(L);
     for (uint32_t l = 0; l < L; l++) {
-        const StepKernelLayer &Y = b.layers[l];
-        if ((rc = make_tensor_map_2d(&maps[l * 4 + LIN_QKV], Y.wqkv, p.qkv_n, H, H, 128, 64)) != TS_OK) return bail(rc);
-        if ((rc = make_tensor_map_2d(&maps[l * 4 + LIN_O], Y.wo, H, QW, QW, 128, 64)) != TS_OK) return bail(rc);
-        if ((rc = make_tensor_map_2d(&maps[l * 4 + LIN_GU], Y.wgu, 2 * F, H, H, 64, 64)) != TS_OK) return bail(rc);
-        if ((rc = make_tensor_map_2d(&maps[l * 4 + LIN_DOWN], Y.wdown, H, F, F, 128, 64)) != TS_OK) return bail(rc);
-        if ((rc = make_tensor_map_2d(&maps[4 * L + 2 * l], Y.k_rows, s.kept_rows, KW, KW, 32, 64)) != TS_OK) return bail(rc);
-        if ((rc = make_tensor_map_2d(&maps[4 * L + 2 * l + 1], Y.v_rows, s.kept_rows, KW, KW, 32, 64)) != TS_OK) return bail(rc);
+        const StepKernelLayer &Y = b.layers[l], &Z = b.layers[0];
+        const bool packed = (const uint16_t *)Y.wqkv == (const uint16_t *)Z.wqkv + (size_t)l * p.qkv_n * H &&
+                            (const uint16_t *)Y.wo == (const uint16_t *)Z.wo + (size_t)l * H * QW &&
+                            (const uint16_t *)Y.wgu == (const uint16_t *)Z.wgu + (size_t)l * 2 * F * H &&
+                            (const uint16_t *)Y.wdown == (const uint16_t *)Z.wdown + (size_t)l * H * F &&
+                            (const uint16_t *)Y.k_rows == (const uint16_t *)Z.k_rows + (size_t)l * s.kept_rows * KW &&
+                            (const uint16_t *)Y.v_rows == (const uint16_t *)Z.v_rows + (size_t)l * s.kept_rows * KW;
+        if (!packed) return bail(fail(TS_ERR_BAD_INPUT, "step kernel: layer %u's weights do not follow layer 0's back to back", l));
         layers[l] = {Y.ln1, Y.ln2, s.qk_norm ? Y.q_norm : nullptr, s.qk_norm ? Y.k_norm : nullptr, (uint16_t *)Y.k_rows,
                      (uint16_t *)Y.v_rows};
     }
+    const StepKernelLayer &Z = b.layers[0];
+    if ((rc = make_tensor_map_2d(&p.w_maps[LIN_QKV], Z.wqkv, (uint64_t)L * p.qkv_n, H, H, 128, 64)) != TS_OK) return bail(rc);
+    if ((rc = make_tensor_map_2d(&p.w_maps[LIN_O], Z.wo, (uint64_t)L * H, QW, QW, 128, 64)) != TS_OK) return bail(rc);
+    if ((rc = make_tensor_map_2d(&p.w_maps[LIN_GU], Z.wgu, (uint64_t)L * 2 * F, H, H, 64, 64)) != TS_OK) return bail(rc);
+    if ((rc = make_tensor_map_2d(&p.w_maps[LIN_DOWN], Z.wdown, (uint64_t)L * H, F, F, 128, 64)) != TS_OK) return bail(rc);
+    if ((rc = make_tensor_map_2d(&p.kv_maps[0], Z.k_rows, (uint64_t)L * s.kept_rows, KW, KW, 32, 64)) != TS_OK) return bail(rc);
+    if ((rc = make_tensor_map_2d(&p.kv_maps[1], Z.v_rows, (uint64_t)L * s.kept_rows, KW, KW, 32, 64)) != TS_OK) return bail(rc);
+    p.kept_rows = s.kept_rows;
     if ((rc = make_tensor_map_2d(&p.x_maps[0], b.xs, s.max_rows, H, H, kBatch, 64)) != TS_OK) return bail(rc);
     if ((rc = make_tensor_map_2d(&p.x_maps[1], b.attn, s.max_rows, QW, QW, kBatch, 64)) != TS_OK) return bail(rc);
     if ((rc = make_tensor_map_2d(&p.x_maps[2], b.act, s.max_rows, F, F, kBatch, 64)) != TS_OK) return bail(rc);
-    if ((rc = dev(&k->maps, maps.size() * sizeof(CUtensorMap))) != TS_OK) return bail(rc);
     if ((rc = dev(&k->layers, layers.size() * sizeof(LayerDev))) != TS_OK) return bail(rc);
-    cudaError_t e = cudaMemcpy(k->maps, maps.data(), maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice);
-    if (e == cudaSuccess) e = cudaMemcpy(k->layers, layers.data(), layers.size() * sizeof(LayerDev), cudaMemcpyHostToDevice);
+    cudaError_t e = cudaMemcpy(k->layers, layers.data(), layers.size() * sizeof(LayerDev), cudaMemcpyHostToDevice);
     if (e != cudaSuccess) return bail(fail(TS_ERR_CUDA, "step kernel: uploads failed: %s", cudaGetErrorString(e)));
-    p.maps = (const CUtensorMap *)k->maps;
     p.layers = (const LayerDev *)k->layers;
     p.x = b.x;
     p.xs = (uint16_t *)b.xs;
     p.attn = (uint16_t *)b.attn;
     p.act = (uint16_t *)b.act;
+    p.qkv = (uint16_t *)b.qkv;
     float *ss = nullptr;
     if ((rc = dev((void **)&ss, (size_t)kBatch * p.ss_parts * sizeof(float))) != TS_OK) return bail(rc);
     p.ss = ss;
@@ -1126,16 +1180,10 @@ int step_kernel_launch(StepKernel *k, uint32_t rows, uint32_t keys, const KeptDe
     p.kept = kept;
     p.max_blk = ceil_div(keys ? keys : 1, 32);
     auto go = [&](auto kernel) -> int {
-        TS_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Smem::bytes));
-        int per_sm = 0;
-        TS_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, (int)kThreads, Smem::bytes));
-        TS_REQUIRE(per_sm >= 1, "step kernel: a block does not fit an SM");
+        cudaLaunchConfig_t cfg;
+        cudaLaunchAttribute attr[1];
+        TS_CUDA(cluster_config(kernel, p.blocks, stream, &cfg, attr));
         TS_CUDA(cudaMemsetAsync(p.sync, 0, 8, stream));
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(p.blocks);
-        cfg.blockDim = dim3(kThreads);
-        cfg.dynamicSmemBytes = Smem::bytes;
-        cfg.stream = stream;
         cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, p);
         if (e != cudaSuccess)
             return fail(TS_ERR_CUDA, "launch of decode_layers failed: %s (%d) %s", cudaGetErrorName(e), (int)e, cudaGetErrorString(e));

@@ -377,18 +377,31 @@ int ts_decoder_create(const ts_decoder_config *config, ts_decoder **out) {
     A(dev_alloc(d, &d->embed, (size_t)c.vocab * H));
     A(dev_alloc(d, &d->norm, H));
     d->layers.resize(c.layers);
-    for (uint32_t l = 0; l < c.layers && rc == TS_OK; l++) {
-        ts_decoder::Layer &L = d->layers[l];
-        A(dev_alloc(d, &L.wqkv, (size_t)d->qkv_n * H));
-        A(dev_alloc(d, &L.wo, H * QW));
-        A(dev_alloc(d, &L.wgu, (size_t)2 * c.ffn * H));
-        A(dev_alloc(d, &L.wdown, H * c.ffn));
-        A(dev_alloc(d, &L.ln1, H));
-        A(dev_alloc(d, &L.ln2, H));
-        A(dev_alloc(d, &L.q_norm, c.head_dim));
-        A(dev_alloc(d, &L.k_norm, c.head_dim));
-        A(dev_alloc(d, &L.k_rows, (size_t)d->kept_total_rows * KW));
-        A(dev_alloc(d, &L.v_rows, (size_t)d->kept_total_rows * KW));
+    {
+        // Every layer's copy of a weight (and of the kept K and V rows) sits in one slab, layer after layer: one
+        // tensor map then covers all layers of that weight, which the persistent decode kernel relies on.
+        const size_t n_qkv = (size_t)d->qkv_n * H, n_o = H * QW, n_gu = (size_t)2 * c.ffn * H, n_down = H * c.ffn;
+        const size_t n_kept = (size_t)d->kept_total_rows * KW;
+        uint16_t *wqkv = nullptr, *wo = nullptr, *wgu = nullptr, *wdown = nullptr, *k_rows = nullptr, *v_rows = nullptr;
+        A(dev_alloc(d, &wqkv, c.layers * n_qkv));
+        A(dev_alloc(d, &wo, c.layers * n_o));
+        A(dev_alloc(d, &wgu, c.layers * n_gu));
+        A(dev_alloc(d, &wdown, c.layers * n_down));
+        A(dev_alloc(d, &k_rows, c.layers * n_kept));
+        A(dev_alloc(d, &v_rows, c.layers * n_kept));
+        for (uint32_t l = 0; l < c.layers && rc == TS_OK; l++) {
+            ts_decoder::Layer &L = d->layers[l];
+            L.wqkv = wqkv + l * n_qkv;
+            L.wo = wo + l * n_o;
+            L.wgu = wgu + l * n_gu;
+            L.wdown = wdown + l * n_down;
+            L.k_rows = k_rows + l * n_kept;
+            L.v_rows = v_rows + l * n_kept;
+            A(dev_alloc(d, &L.ln1, H));
+            A(dev_alloc(d, &L.ln2, H));
+            A(dev_alloc(d, &L.q_norm, c.head_dim));
+            A(dev_alloc(d, &L.k_norm, c.head_dim));
+        }
     }
     const size_t R = c.max_rows;
     A(dev_alloc(d, &d->x, R * H));
@@ -458,7 +471,7 @@ int ts_decoder_create(const ts_decoder_config *config, ts_decoder **out) {
                 const ts_decoder::Layer &L = d->layers[l];
                 layers[l] = {L.wqkv, L.wo, L.wgu, L.wdown, L.ln1, L.ln2, L.q_norm, L.k_norm, L.k_rows, L.v_rows};
             }
-            StepKernelBuffers buffers = {layers.data(), d->embed, d->x, d->h, d->attn, d->act,
+            StepKernelBuffers buffers = {layers.data(), d->embed, d->x, d->h, d->attn, d->act, d->qkv,
                                          d->tokens, d->slots, d->positions, d->inv_freq};
             rc = step_kernel_create(shape, buffers, &d->step);
             if (const char *v = getenv("TS_STEP_KERNEL_KEYS")) d->step_keys = (uint32_t)atoi(v);

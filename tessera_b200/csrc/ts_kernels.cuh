@@ -140,6 +140,7 @@ struct StepKernelBuffers {
     const void *embed;
     float *x;                 // residual rows f32 [max_rows, hidden]
     void *xs, *attn, *act;    // bf16 [max_rows, hidden | heads * 128 | ffn]
+    void *qkv;                // bf16 [max_rows, (heads + 2 kv_heads) * 128]
     const uint32_t *tokens, *slots, *positions;
     const float *inv_freq;
 };

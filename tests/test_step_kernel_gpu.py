@@ -26,7 +26,7 @@ E2E_TOL = 2e-2
 # head width 128 throughout (the kernel's attention); 1, 2 and 4 query heads per kv head
 G1 = dict(layers=2, hidden=512, heads=4, kv_heads=4, head_dim=128, ffn=768, vocab=3000, eps=1e-6, theta=1e4)
 G2 = dict(layers=3, hidden=1024, heads=16, kv_heads=8, head_dim=128, ffn=3072, vocab=5000, eps=1e-6, theta=1e6)
-G4 = dict(layers=2, hidden=256, heads=8, kv_heads=2, head_dim=128, ffn=512, vocab=2000, eps=1e-6, theta=1e5)
+G4 = dict(layers=2, hidden=512, heads=8, kv_heads=2, head_dim=128, ffn=512, vocab=2000, eps=1e-6, theta=1e5)
 
 
 def _oracle_run(cfg, seed, prompts, new, context, gains):
