@@ -63,9 +63,9 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--pdl", type=int, default=1)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--step-kernel", type=int, default=1,
-                    help="decode: 1 = the gather and every layer as one persistent kernel per step (default), 0 = one launch "
-                         "per product (for A/B timing)")
+    ap.add_argument("--step-kernel", type=int, default=0,
+                    help="decode: 1 = the gather and every layer as one persistent kernel per step, 0 = one launch per "
+                         "product (default: the faster of the two today)")
     ap.add_argument("--workload", default="decode", choices=["decode", "moe", "embed"],
                     help="decode: the headline Qwen3-0.6B-shaped decode (default); moe: GLM-style MoE decode, batch 256 at "
                          "context 2048, expert-parallel over the ranks; embed: 1024 ragged texts through the "

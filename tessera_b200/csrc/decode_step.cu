@@ -168,7 +168,8 @@ __device__ __forceinline__ void give_up(const Bounds &b) {
 
 // (Not inlined, like the other rarely-run or once-a-phase pieces below: the kernel's code has to stay small enough
 // for the instruction cache, or every phase of every layer begins by fetching its instructions again.)
-__device__ __noinline__ bool wait_bar(uint64_t *bar, uint32_t parity, const Bounds &b) {
+__device__ __noinline__ bool wait_bar_impl(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_s, uint32_t *abort_g, uint64_t wait_ns) {
+    const Bounds b = {abort_s, abort_g, wait_ns};
     uint64_t start = 0;
     for (uint32_t i = 0;; i++) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -193,12 +194,20 @@ __device__ __noinline__ void drain_bar(uint64_t *bar, uint32_t parity, uint64_t 
     }
 }
 
+// Arguments of the out-of-line pieces travel as scalars: a struct or array handed to a real call by reference
+// lives on the thread's stack, and with nearly all of the SM's L1 given to shared memory a stack access is an L2
+// round trip.
+__device__ __forceinline__ bool wait_bar(uint64_t *bar, uint32_t parity, const Bounds &b) {
+    return wait_bar_impl(bar, parity, b.abort_s, b.abort_g, b.wait_ns);
+}
+
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
 // Device-wide barrier, one thread per block.  Everything this block wrote (observed by this thread through
 // the workers' arrivals) is released to the other blocks; what they wrote is acquired, for the async proxy
 // (TMA) too.
-__device__ __noinline__ bool grid_sync(uint32_t *counter, uint32_t target, const Bounds &b) {
+__device__ __noinline__ bool grid_sync_impl(uint32_t *counter, uint32_t target, volatile uint32_t *abort_s, uint32_t *abort_g, uint64_t wait_ns) {
+    const Bounds b = {abort_s, abort_g, wait_ns};
     __threadfence();
     fence_proxy_async_all();
     asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(counter) : "memory");
@@ -224,6 +233,10 @@ __device__ __noinline__ bool grid_sync(uint32_t *counter, uint32_t target, const
     }
     fence_proxy_async_all();
     return true;
+}
+
+__device__ __forceinline__ bool grid_sync(uint32_t *counter, uint32_t target, const Bounds &b) {
+    return grid_sync_impl(counter, target, b.abort_s, b.abort_g, b.wait_ns);
 }
 
 // ---- small helpers -----------------------------------------------------------------------------------------
@@ -319,7 +332,7 @@ struct ItemCtx {
     float cs[2], sn[2];
 };
 
-__device__ __noinline__ ItemCtx make_item(const StepParams &p, uint32_t item, uint32_t lane) {
+__device__ __forceinline__ ItemCtx make_item(const StepParams &p, uint32_t item, uint32_t lane) {
     ItemCtx c;
     c.row = item / p.kv_heads;
     c.kvh = item % p.kv_heads;
@@ -334,7 +347,7 @@ __device__ __noinline__ ItemCtx make_item(const StepParams &p, uint32_t item, ui
 // Per-head RMS norm (gains g: elements j and j + 64 of the lane's two pairs; none when `normed` is false) and the
 // half-pair rotation of one 128-wide head held as bf16 in shared memory, in place: the arithmetic of
 // norm_rope_head (head_prep.cuh) with the angles' sines and cosines computed once per step instead of per head.
-__device__ __noinline__ void norm_rotate(uint16_t *h, const float (&g)[4], bool normed, const ItemCtx &c, float eps,
+__device__ __forceinline__ void norm_rotate(uint16_t *h, const float (&g)[4], bool normed, const ItemCtx &c, float eps,
                                             uint32_t lane) {
     const uint32_t va = *reinterpret_cast<const uint32_t *>(h + lane * 2), vb = *reinterpret_cast<const uint32_t *>(h + 64 + lane * 2);
     float a[2] = {bf16_lo(va), bf16_hi(va)}, b[2] = {bf16_lo(vb), bf16_hi(vb)};
@@ -907,6 +920,12 @@ __global__ void __launch_bounds__(kThreads, 1) decode_layers_kernel(const __grid
         const uint32_t items = p.rows * p.kv_heads;
         ItemCtx first_item = {};
         if (wid < items) first_item = make_item(p, wid, lane);
+        {
+            // Pin the values here: without this the compiler is free to recompute them where they are first used,
+            // which is inside every layer's attention phase (two dependent loads, a table look-up and two sincosf).
+            asm volatile("" : "+r"(first_item.row), "+r"(first_item.kvh), "+r"(first_item.slot), "+r"(first_item.pos), "+r"(first_item.y_lane));
+            asm volatile("" : "+f"(first_item.cs[0]), "+f"(first_item.cs[1]), "+f"(first_item.sn[0]), "+f"(first_item.sn[1]));
+        }
         float qg[4] = {1.0f, 1.0f, 1.0f, 1.0f}, kg[4] = {1.0f, 1.0f, 1.0f, 1.0f};
         // phase 0: the gather
         gather_phase(p, p.layers[0].ln1, wid, lane);
@@ -931,14 +950,12 @@ __global__ void __launch_bounds__(kThreads, 1) decode_layers_kernel(const __grid
                 if (ok) prefetch_kept(p, Ly, wid, lane);
             }
             if (k5 == 1) {
-                if (w == 0 && lane == 0) STEP_STAMP(bar, 5);
                 if (ok) {
                     const CUtensorMap *mk = &p.kv_maps[0], *mv = &p.kv_maps[1];
 #pragma unroll 1
                     for (uint32_t item = wid; item < items && ok; item += kWorkers * G) {
                         ItemCtx c = first_item;
                         if (item != wid) c = make_item(p, item, lane);
-                        if (w == 0 && lane == 0) STEP_STAMP(bar, 6);
                         ok = attend_item<GRP>(p, Ly, mk, mv, c, qg, kg, normed, lane, stages, prep, my_kv_full, kv_parity, kv_pending, bd,
                                               l * p.kept_rows, w == 0 ? bar : 0);
                     }
