@@ -13,12 +13,19 @@ stand-ins of the configuration's shapes, nothing is read from disk but MEASURED_
   e2e    the same steps (the sequences restart from their prompts, so the positions and context lengths
          are those of the resident loop) through ts_decoder_step with host buffers: tokens/slots/positions
          copied host to device and the ids read back device to host inside the timed region, every step.
-  roofline  the kernel with the largest share of a step.  Shares come from CUDA events after every kernel
-         (ts_decoder_profile) at the timed steps' context lengths, right after the timed region; that pass
-         serialises launches which overlap in the timed loop and adds a launch gap to every interval, so a
-         kernel's duration in the timed loop is taken as its serialised interval less the average gap
-         ((serialised step - timed step) / launches per step, all measured live); the serialised interval is
-         reported beside it, and achieved = algorithmic bytes / that duration.
+  roofline  the kernel with the largest share of a step.  Shares and durations come from CUDA events recorded
+         after every kernel (ts_decoder_profile) at the timed steps' context lengths, right after the timed
+         region: achieved = algorithmic bytes / that measured interval.  The pass serialises launches which overlap
+         in the timed loop (programmatic dependent launch), so the interval holds the launch gap too and the
+         fraction is a lower bound; `in_step_estimate` gives the interval less the average gap
+         ((serialised step - timed step) / launches per step) beside it, marked as an estimate.
+  workloads  after the headline: the GLM-style MoE decode (expert-parallel over the ranks, with a check of the
+         exchange against the all-local block) and the embedding encoder (texts dealt to the ranks), a few steps
+         each, nested in the same line; --no-extras skips them.
+
+    python bench.py --workload sweep     one line per case of the isolated linear sweep (6 shapes x 6 row counts)
+    python bench.py --workload attn      the isolated attention cases: causal prefill 4 x 4096, paged decode of 64
+                                         ragged sequences (512..8192 positions) at 64- and 16-row pages
   cpu_baseline  the reference's native CPU rules restated in C (oracle/cpu_rules.c), timed on this
          host's cores on a bounded sample of the same step.
 
@@ -44,10 +51,9 @@ BATCH = 64
 PROMPT = 128
 FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used only when MEASURED_PEAKS.json is absent
 
-# (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic bytes of the captured launch, from the
-# committed ncu captures (profiles/decode_kernels_sections.md names the commands).  The captures ran on
-# small cases of the same kernels; traffic grows in proportion to the rows, keys and weights a launch
-# visits, so a launch's traffic is this ratio times its algorithmic bytes.  None: no capture.
+# (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic bytes of the captured launch, from ncu captures of
+# small cases of the same kernels (bench.py --case <kernel>); traffic grows in proportion to the rows, keys and
+# weights a launch visits, so a launch's traffic is this ratio times its algorithmic bytes.  Absent: no capture.
 NCU_TRAFFIC_RATIO = {"attend_rows": 50.816 / 50.856, "linear_unembed": 340.02 / 350.19,
                      # one capture (the q,k,v shape) stands for the four streamed linears of a layer: same kernel,
                      # traffic = the weights once + x; the output stays in L2
@@ -66,7 +72,8 @@ def parse_args():
     ap.add_argument("--step-kernel", type=int, default=0,
                     help="decode: 1 = the gather and every layer as one persistent kernel per step, 0 = one launch per "
                          "product (default: the faster of the two today)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "moe", "embed"],
+    ap.add_argument("--no-extras", action="store_true", help="decode: skip the MoE and embedding workloads nested after the headline")
+    ap.add_argument("--workload", default="decode", choices=["decode", "moe", "embed", "sweep", "attn"],
                     help="decode: the headline Qwen3-0.6B-shaped decode (default); moe: GLM-style MoE decode, batch 256 at "
                          "context 2048, expert-parallel over the ranks; embed: 1024 ragged texts through the "
                          "EmbeddingGemma-300M-shaped encoder, data-parallel over the ranks")
@@ -78,7 +85,9 @@ def parse_args():
                          "linear_o, linear_gate_up, linear_down, linear_unembed); used for ncu captures")
     ap.add_argument("--ctx", type=int, default=192, help="--case attend_rows: context length of every row")
     ap.add_argument("--rows", type=int, default=BATCH, help="--case: rows (batch) of the launch")
-    ap.add_argument("--path", default="auto", choices=["auto", "skinny", "umma", "stream", "pair"], help="--case linear_*: kernel family")
+    ap.add_argument("--path", default="auto", choices=["auto", "skinny", "umma", "stream", "pair"],
+                    help="--case linear_* and --workload sweep: kernel family")
+    ap.add_argument("--only-rows", type=int, default=0, help="--workload sweep: only this row count")
     return ap.parse_args()
 
 
@@ -257,8 +266,6 @@ def run_ours(args, rank, world, local_rank):
     from tessera_b200 import runner, synth
 
     torch.cuda.set_device(local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     cfg = synth.QWEN3_0_6B
     K, W = args.steps, args.warmup
     profile_steps = 3
@@ -357,28 +364,33 @@ def run_ours(args, rank, world, local_rank):
     launches = sum(n for _, n in prof.values()) / profile_steps
     gap_s = max(0.0, step_ms / 1e3 - timed_step_s) / launches   # what serialising adds to every launch, on average
 
-    def in_step_s(k):   # per launch: the serialised interval less the average gap
-        serial = prof[k][0] / prof[k][1] / 1e3
-        return max(serial - gap_s, 1e-9)
+    def serial_s(k):    # per launch, as measured: the interval between the events either side of the kernel
+        return prof[k][0] / prof[k][1] / 1e3
+
+    def in_step_s(k):   # an estimate of the same launch inside the timed loop: less the average serialising gap
+        return max(serial_s(k) - gap_s, 1e-9)
     peak, peak_kind = peaks()
     algo = kernel_bytes(top, cfg, BATCH, int(BATCH * ctx_prof))
-    achieved = algo / in_step_s(top) / 1e9
+    achieved = algo / serial_s(top) / 1e9
+    ratio = NCU_TRAFFIC_RATIO.get(top)
     roofline = {"kernel": top, "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                 "frac": achieved / peak, "peak_kind": f"of {peak_kind}", "frac_of_nominal_8tbs": achieved / 8000.0,
-                "traffic": (NCU_TRAFFIC_RATIO[top] * algo if top in NCU_TRAFFIC_RATIO else None),
-                "algorithmic_bytes_per_launch": algo, "avg_launch_us": in_step_s(top) * 1e6,
-                "duration": "interval between CUDA events recorded after every kernel (launches serialised), less the "
-                            "average gap serialising adds per launch = (serialised step - timed step) / launches per step",
-                "serialising_gap_us": gap_s * 1e6,
-                "avg_launch_us_serialised": top_ms / top_n * 1e3,
+                "traffic": (ratio * algo if ratio else None),
+                "traffic_source": ("dram bytes / algorithmic bytes of the committed ncu capture of this kernel, times this "
+                                   "launch's algorithmic bytes" if ratio else None),
+                "algorithmic_bytes_per_launch": algo, "avg_launch_us": serial_s(top) * 1e6,
+                "duration": "measured: interval between CUDA events recorded after every kernel of the step (launches "
+                            "serialised, so it includes the gap between two launches: a lower bound on the fraction)",
+                "in_step_estimate": {"avg_launch_us": in_step_s(top) * 1e6, "frac": algo / in_step_s(top) / 1e9 / peak,
+                                     "serialising_gap_us": gap_s * 1e6,
+                                     "how": "interval less (serialised step - timed step) / launches per step"},
                 "step_share": shares[top], "kernel_shares": {k: round(v, 4) for k, v in sorted(shares.items())},
-                "per_kernel_gbs": {k: round(kernel_bytes(k, cfg, BATCH, int(BATCH * ctx_prof)) / in_step_s(k) / 1e9, 1)
+                "per_kernel_gbs": {k: round(kernel_bytes(k, cfg, BATCH, int(BATCH * ctx_prof)) / serial_s(k) / 1e9, 1)
                                    for k, (ms, n) in prof.items() if kernel_bytes(k, cfg, BATCH, 1) > 0}}
     dec.close()
-    if world > 1:
-        dist.destroy_process_group()
+    torch.cuda.set_stream(torch.cuda.default_stream())
     if rank != 0:
-        return
+        return None
 
     value = world * BATCH * K / resident_s
     step_bytes = sum(kernel_bytes(k, cfg, BATCH, int(BATCH * ctx_mid)) for k in ("decode_layers", "linear_unembed"))
@@ -407,7 +419,7 @@ def run_ours(args, rank, world, local_rank):
                                              f"kept rows before them zero-filled), {best:.2f} s per step"}
         except Exception as e:  # the baseline is a report, never a reason to lose the GPU numbers
             out["cpu_baseline"] = {"value": None, "unit": "tokens/s", "cores": 0, "kind": "port", "sample": f"failed: {e}"}
-    print(json.dumps(out))
+    return out
 
 
 def run_case(args):
@@ -503,12 +515,128 @@ def run_case(args):
                       "status": ops.device_status()}))
 
 
+def _tensor_peaks():
+    """(burst, sustained) bf16 TFLOP/s of MEASURED_PEAKS.json, else the pool's earlier measurement."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return float(d["bf16_tflops"]), float(d["bf16_tflops_sustained"]), "measured"
+    return 1590.0, 1400.0, "fallback"
+
+
+def _graph_us(calls, steps, warmup=3):
+    """`steps` launches replayed from one CUDA graph, the calls taken in turn (their buffers together exceed the
+    L2), timed with CUDA events on the launch stream; microseconds per launch."""
+    import torch
+    side = torch.cuda.current_stream()
+    for i in range(max(3, warmup)):
+        calls[i % len(calls)]()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        for i in range(steps):
+            calls[i % len(calls)]()
+    graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    del graph
+    return e0.elapsed_time(e1) * 1e3 / steps
+
+
+SWEEP_SHAPES = [("q_proj", 2048, 1024), ("kv_proj", 1024, 1024), ("o_proj", 1024, 2048), ("gate_up", 6144, 1024),
+                ("down", 1024, 3072), ("lm_head", 151936, 1024)]
+SWEEP_ROWS = [1, 16, 64, 128, 2048, 8192]
+
+
+def run_sweep(args):
+    """The isolated linear sweep: every (N, K) of the Qwen3-0.6B shape at every M, the kernel path "auto" picks,
+    one JSON line a case.  Decode-sized M (<= 128) is weight-bound: GB/s of the algorithmic bytes against the
+    measured copy rate; prefill-sized M is tensor-bound: TFLOP/s against the measured cuBLAS burst."""
+    import torch
+    from tessera_b200 import ops
+    torch.manual_seed(0)
+    side = torch.cuda.Stream()
+    torch.cuda.set_stream(side)
+    ops.set_pdl(bool(args.pdl))
+    hbm, hbm_kind = peaks()
+    burst, _, tf_kind = _tensor_peaks()
+    bf = lambda *shape, std=1.0: (torch.randn(*shape, device="cuda") * std).to(torch.bfloat16)
+    for name, n, k in SWEEP_SHAPES:
+        copies = min(48, max(2, int(400e6 // (n * k * 2)) + 1))   # rotated so that a launch never finds its weights in L2
+        ws = [bf(n, k, std=0.02) for _ in range(copies)]
+        for m in ([args.only_rows] if args.only_rows else SWEEP_ROWS):
+            x = bf(m, k)
+            outs = [torch.empty((m, n), dtype=torch.bfloat16, device="cuda") for _ in range(min(copies, 4))]
+            calls = [(lambda w=w, o=outs[i % len(outs)]: ops.linear(x, w, out=o, path=args.path)) for i, w in enumerate(ws)]
+            steps = max(8, min(200, int(2e9 // (2.0 * m * n * k + 1e7))))
+            us = _graph_us(calls, steps)
+            byts, flops = 2.0 * n * k + 2.0 * m * k + 2.0 * m * n, 2.0 * m * n * k
+            bound = "hbm" if m <= 128 else "tensor"
+            line = {"workload": "linear sweep", "case": name, "m": m, "n": n, "k": k, "us_per_launch": round(us, 3),
+                    "GBs": round(byts / us / 1e3, 1), "TFLOPs": round(flops / us / 1e6, 2), "bound": bound,
+                    "frac": round((byts / us / 1e3 / hbm) if bound == "hbm" else (flops / us / 1e6 / burst), 4),
+                    "peak_kind": f"of {hbm_kind} copy rate" if bound == "hbm" else f"of {tf_kind} cuBLAS bf16 burst",
+                    "path": args.path, "launches": steps, "weight_copies": copies, "status": ops.device_status()}
+            print(json.dumps(line), flush=True)
+        del ws
+
+
+def run_attn(args):
+    """The isolated attention cases: (a) causal prefill, 4 sequences x 4096 tokens, 16 query / 8 kv heads x 128;
+    (b) paged decode, 64 sequences with context lengths uniform in [512, 8192] (seed 4) behind a seeded random page
+    table, at 64- and 16-row pages.  One JSON line a case."""
+    import torch
+    from tessera_b200 import ops, synth
+    torch.manual_seed(0)
+    side = torch.cuda.Stream()
+    torch.cuda.set_stream(side)
+    ops.set_pdl(bool(args.pdl))
+    hbm, hbm_kind = peaks()
+    burst, _, tf_kind = _tensor_peaks()
+    heads, kv_heads, d = 16, 8, 128
+    bf = lambda *shape: torch.randn(*shape, device="cuda").to(torch.bfloat16)
+    seqs, n = 4, 4096
+    calls = []
+    for c in range(2):
+        q, k, v = bf(seqs, n, heads, d), bf(seqs, n, kv_heads, d), bf(seqs, n, kv_heads, d)
+        out = torch.empty_like(q)
+        calls.append(lambda q=q, k=k, v=v, out=out: ops.attend(q, k, v, mask="causal", scale=d ** -0.5, out=out))
+    us = _graph_us(calls, 20)
+    flops = 4.0 * seqs * heads * d * n * (n + 1) / 2
+    print(json.dumps({"workload": "attention", "case": "causal prefill 4 x 4096, 16q/8kv x 128", "us_per_launch": round(us, 2),
+                      "TFLOPs": round(flops / us / 1e6, 1), "bound": "tensor", "frac": round(flops / us / 1e6 / burst, 4),
+                      "peak_kind": f"of {tf_kind} cuBLAS bf16 burst", "launches": 20, "status": ops.device_status()}), flush=True)
+    del calls
+    slots, context = 64, 8192
+    lengths = np.random.default_rng(4).integers(512, 8193, size=slots)
+    q = bf(slots, heads, d)
+    row_slots = torch.arange(slots, dtype=torch.int32, device="cuda")
+    positions = torch.from_numpy((lengths - 1).astype(np.int32)).cuda()
+    for page in (64, 16):
+        pages = context // page
+        total = slots * pages * page
+        table = torch.from_numpy(synth.page_permutation(slots * pages, seed=4).view(np.int32)).cuda()
+        kept = ops.Kept("paged" if page == 64 else "paged16", pages, table, total)
+        k, v = bf(total, kv_heads, d), bf(total, kv_heads, d)   # 1 GB each: far beyond the L2
+        out = torch.empty_like(q)
+        call = lambda: ops.attend_rows(q, k, v, row_slots, positions, kept, context, scale=d ** -0.5, out=out)
+        us = _graph_us([call], 20)
+        byts = float(lengths.sum()) * kv_heads * d * 2 * 2 + slots * heads * d * 2 * 2
+        print(json.dumps({"workload": "attention", "case": f"paged decode, 64 sequences of 512..8192 positions, {page}-row pages",
+                          "us_per_launch": round(us, 2), "GBs": round(byts / us / 1e3, 1), "bound": "hbm",
+                          "frac": round(byts / us / 1e3 / hbm, 4), "peak_kind": f"of {hbm_kind} copy rate",
+                          "positions_total": int(lengths.sum()), "launches": 20, "status": ops.device_status()}), flush=True)
+        del k, v
+
+
 def _dist_setup(local_rank, world):
     import torch
     import torch.distributed as dist
     torch.cuda.set_device(local_rank)
-    if world > 1 and not dist.is_initialized():
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
 
 def _timed(fn, steps, warmup, world):
@@ -582,10 +710,9 @@ def run_moe(args, rank, world, local_rank):
     e2e_seconds = _timed(through_host, K, W, 1 if alone else world)
     sampler.stop()
     dec.close()   # graphs with captured collectives must go before the communicator does
-    if world > 1 and not alone:
-        dist.destroy_process_group()
+    check = None if alone else ep_check(rank, world)
     if rank != 0:
-        return
+        return None
     peak, kind = peaks()
     per = cfg["experts"] // world
     expert_bytes = cfg["layers"] * per * 3 * cfg["hidden"] * cfg["ffn"] * 2.0
@@ -594,7 +721,7 @@ def run_moe(args, rank, world, local_rank):
                                    3 * cfg["hidden"] * cfg["shared_ffn"]) * 2.0
     kv_bytes = cfg["layers"] * rows * ctx0 * cfg["kv_heads"] * cfg["head_dim"] * 4.0
     step_bytes = expert_bytes + dense_bytes + kv_bytes
-    print(json.dumps({
+    return ({
         "metric": "moe_decode_tokens_per_s" + ("_one_rank_alone" if alone else ""), "value": batch * K / seconds,
         "unit": "tokens/s", "n_gpus": 1 if alone else world, "steps": K,
         "warmup": W, "ms_per_step": seconds / K * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
@@ -612,7 +739,41 @@ def run_moe(args, rank, world, local_rank):
         "roofline": {"kernel": "whole step (expert, dense and kept-row bytes of one rank)", "bound": "hbm",
                      "achieved": step_bytes / (seconds / K) / 1e9, "peak": peak, "unit": "GB/s",
                      "frac": step_bytes / (seconds / K) / 1e9 / peak, "peak_kind": f"of {kind}", "traffic": None},
-        "clocks": sampler.summary()}))
+        "ep_check": check, "clocks": sampler.summary()})
+
+
+def ep_check(rank, world):
+    """The expert-parallel exchange with this library's kernels on every rank, against the same block with every
+    expert local: a small routed block (32 experts top-4, hidden 512, ffn 256, 16 rows a rank) with the same seeded
+    weights on every rank; each rank takes its experts' slice, runs both schemes of tessera_b200.moe, and compares
+    its own rows with the all-local result.  Ids must be equal bit for bit; outputs are sums in another order."""
+    import torch
+    import torch.distributed as dist
+    from tessera_b200 import moe
+    E, H, F, top, rows = 32, 512, 256, 4, 16
+    g = torch.Generator().manual_seed(77)
+    bf = lambda *shape, std: (torch.randn(*shape, generator=g) * std).to(torch.bfloat16).cuda()
+    router, w_in, w_out = bf(E, H, std=0.05), bf(E, 2 * F, H, std=0.05), bf(E, H, F, std=0.05)
+    h_all = bf(world * rows, H, std=1.0)
+    h = h_all[rank * rows:(rank + 1) * rows].contiguous()
+    full = moe.MoeWeights(router, w_in, w_out, first=0, experts_total=E)
+    want, want_ids, _ = moe.moe_forward(h, full, top)
+    if world == 1:
+        return {"ranks": 1, "ids_equal": True, "max_rel_err": 0.0, "schemes": [], "note": "one rank: every expert is local"}
+    per = E // world
+    mine = moe.MoeWeights(router, w_in[rank * per:(rank + 1) * per].contiguous(), w_out[rank * per:(rank + 1) * per].contiguous(),
+                          first=rank * per, experts_total=E)
+    ep = moe.ExpertParallel()
+    worst, same = 0.0, True
+    for scheme in ("replicate", "dispatch"):
+        y, ids, _ = ep.forward(h, mine, top, scheme=scheme)
+        torch.cuda.synchronize()
+        same = same and bool(torch.equal(ids, want_ids))
+        worst = max(worst, float((y - want).abs().max() / want.abs().max()))
+    t = torch.tensor([worst, 0.0 if same else 1.0], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return {"ranks": world, "ids_equal": bool(t[1].item() == 0.0), "max_rel_err": float(t[0].item()),
+            "schemes": ["replicate", "dispatch"], "case": f"{E} experts top-{top}, hidden {H}, ffn {F}, {rows} rows a rank"}
 
 
 def run_embed(args, rank, world, local_rank):
@@ -650,15 +811,14 @@ def run_embed(args, rank, world, local_rank):
     seconds = _timed(resident, K, W, world)
     e2e_seconds = _timed(through_host, K, W, world)
     sampler.stop()
-    if world > 1:
-        dist.destroy_process_group()
+    del enc
     if rank != 0:
-        return
+        return None
     total_tokens = int(lens.sum())
     params = cfg["layers"] * ((cfg["heads"] + 2 * cfg["kv_heads"]) * cfg["head_dim"] * cfg["hidden"] +
                               cfg["hidden"] * cfg["heads"] * cfg["head_dim"] + 3 * cfg["hidden"] * cfg["ffn"])
     flops = 2.0 * params * total_tokens + 4.0 * cfg["layers"] * cfg["heads"] * cfg["head_dim"] * float((lens.astype(np.float64) ** 2).sum())
-    print(json.dumps({
+    return ({
         "metric": "embedding_seqs_per_s", "value": texts * K / seconds, "unit": "sequences/s", "n_gpus": world, "steps": K,
         "warmup": W, "ms_per_step": seconds / K * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (seeded weights, uniform token ids, lengths uniform in [32, 512])",
@@ -670,19 +830,19 @@ def run_embed(args, rank, world, local_rank):
         "roofline": {"kernel": "whole pass (linear and attention flops)", "bound": "tensor",
                      "achieved": flops / (seconds / K) / 1e12 / world, "peak": 1418.9, "unit": "TFLOP/s",
                      "frac": flops / (seconds / K) / 1e12 / world / 1418.9, "peak_kind": "of measured (sustained)", "traffic": None},
-        "clocks": sampler.summary()}))
+        "clocks": sampler.summary()})
 
 
 def main():
     args = parse_args()
-    if args.workload != "decode" and args.impl != "reference" and not args.case:
-        rank = int(os.environ.get("RANK", "0"))
-        world = int(os.environ.get("WORLD_SIZE", "1"))
-        local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-        (run_moe if args.workload == "moe" else run_embed)(args, rank, world, local_rank)
-        return
     if args.case:
         run_case(args)
+        return
+    if args.workload == "sweep":
+        run_sweep(args)
+        return
+    if args.workload == "attn":
+        run_attn(args)
         return
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -690,7 +850,31 @@ def main():
     if args.impl == "reference":
         run_reference(args, rank)
         return
-    run_ours(args, rank, world, local_rank)
+    import torch
+    import torch.distributed as dist
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        if args.workload == "decode":
+            out = run_ours(args, rank, world, local_rank)
+            if not args.no_extras:
+                # The other two sharded workloads, a few steps each, nested under the headline line.
+                extra = argparse.Namespace(**vars(args))
+                extra.one_rank_of = 0
+                extra.steps, extra.warmup = min(args.steps, 8), 3
+                moe_line = run_moe(extra, rank, world, local_rank)
+                extra.steps = min(args.steps, 3)
+                embed_line = run_embed(extra, rank, world, local_rank)
+                if out is not None:
+                    out["workloads"] = {"moe": moe_line, "embed": embed_line}
+        else:
+            out = (run_moe if args.workload == "moe" else run_embed)(args, rank, world, local_rank)
+        if out is not None:
+            print(json.dumps(out))
+    finally:
+        if world > 1 and dist.is_initialized():
+            dist.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -78,9 +78,15 @@ typedef enum {
                              reduced through distributed shared memory, epilogue fused */
     TS_LINEAR_PAIR = 4,   /* m >= 512: 256 x 256 tiles on pairs of SMs (tcgen05 cta_group::2), each block of
                              the pair loading half of both operands */
-    TS_LINEAR_PLAIN = 5   /* any m, n, k: a warp per output element; what AUTO falls back to when k is not a
+    TS_LINEAR_PLAIN = 5,  /* any m, n, k: a warp per output element; what AUTO falls back to when k is not a
                              multiple of 64 (the reference's tiled rule takes every size,
                              engine/rules/linear/tests/tiled_test.rs:61-67) */
+    TS_LINEAR_ORDERED = 6 /* any m, n, k, no gated epilogue: every output summed over k in ascending order, one
+                             multiply and one add at a time, the order of the reference's interpreter
+                             (engine/ir/interp/src/cpu.rs, sequential f32 sums; numerics `Order::Fixed`,
+                             engine/ir/graph/src/numerics.rs:26-35), so f32 outputs carry the interpreter's bits.
+                             For outputs whose ranking matters: a MoE router's scores feed top-k, and an index
+                             must not flip on a near tie.  Never picked by AUTO. */
 } ts_linear_path;
 
 /* Bytes of workspace ts_linear_bf16 needs for these sizes (0 when none). */
@@ -334,6 +340,18 @@ int ts_set_pdl(int enabled);
  * inside a tcgen05 kernel gave up (engine/rules/device/include/tessera/status.h:9-39 keeps the same
  * kind of record).  Synchronises the device. */
 int ts_device_status(void);
+
+/* The B200 entry of the reference's platform table plus what the current device reports, as JSON text:
+ *   {"row": <the table row: matches "cuda sm_100", tile = bf16_tile = [128, 256, 16] (tcgen05.mma, M x N x K with
+ *            N up to 256), pdl, check ["sm_100a"], and under "b200" what the reference's `Needs` has no field for
+ *            yet: the paired-SM tile, TMEM columns, cluster size, shared memory per block, the library and ABI>,
+ *    "asked": <backend, arch, name, driver, units, memory, bandwidth, limits as the reference's `Asked`
+ *              (engine/gpu/platform/src/platform.rs:72-84), "fits": whether this library's kernels run there;
+ *              null without a device>}
+ * The row is the content of tessera_b200/platforms/cuda-b200.json, which refines
+ * engine/gpu/platform/platforms/cuda-blackwell.json:1-21 (that row still names the mma.sync tiles) the way
+ * engine/gpu/platform/src/platform.rs:11-29 `Row` is read.  Needs no device. */
+int ts_platform_info(char *out, size_t capacity);
 
 /* Runs a one-block kernel whose only act is a bounded wait on a barrier nothing arrives at, with `wait_ns`
  * as the bound, and waits for it.  The wait gives up, and the next ts_device_status() reads TS_ERR_TIMEOUT: the

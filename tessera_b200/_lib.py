@@ -14,7 +14,7 @@ LIB_PATH = os.path.join(HERE, "lib", "libtessera_b200.so")
 TS_OK, TS_ERR_ABI, TS_ERR_PEER, TS_ERR_BAD_INPUT, TS_ERR_TIMEOUT, TS_ERR_PROTOCOL, TS_ERR_CUDA = range(7)
 TS_BF16, TS_F32 = 0, 1
 EPILOGUE = {"none": 0, "add": 1, "swiglu": 2, "scale": 3, "geglu": 4}
-LINEAR_PATH = {"auto": 0, "skinny": 1, "umma": 2, "stream": 3, "pair": 4, "plain": 5}
+LINEAR_PATH = {"auto": 0, "skinny": 1, "umma": 2, "stream": 3, "pair": 4, "plain": 5, "ordered": 6}
 KEPT_KIND = {"dense": 0, "interleaved": 1, "paged": 2, "paged16": 2}
 KEPT_PAGE = {"dense": 1, "interleaved": 1, "paged": 64, "paged16": 16}
 
@@ -56,6 +56,7 @@ SIGNATURES = {
     "ts_set_pdl": (i32, [i32]),
     "ts_device_status": (i32, []),
     "ts_wait_runs_out": (i32, [C.c_uint64, vp]),
+    "ts_platform_info": (i32, [C.c_char_p, sz]),
     "ts_linear_workspace_bytes": (sz, [u32, u32, u32, i32, i32]),
     "ts_linear_bf16": (i32, [vp, vp, vp, vp, u32, u32, u32, i32, f32, i32, i32, vp, sz, vp]),
     "ts_gather_scaled_bf16": (i32, [vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, vp]),

@@ -139,7 +139,7 @@ static bool pair_auto() {
 
 int pick_linear_path(uint32_t m, uint32_t n, uint32_t k, int epilogue, int path) {
     if (path == TS_LINEAR_SKINNY || path == TS_LINEAR_UMMA || path == TS_LINEAR_STREAM || path == TS_LINEAR_PAIR ||
-        path == TS_LINEAR_PLAIN)
+        path == TS_LINEAR_PLAIN || path == TS_LINEAR_ORDERED)
         return path;
     // m <= 16: the warp-MMA streamer; m <= 128: the weight-streaming tcgen05 kernel with its cluster
     // reduce; larger m: the tiled tcgen05 kernel.
@@ -226,7 +226,7 @@ int ts_linear_bf16(const void *x, const void *w, const void *a0, void *out, uint
     TS_REQUIRE(epilogue != TS_EPI_ADD || a0 != nullptr, "linear: the add epilogue needs its operand");
     TS_REQUIRE(a0 == nullptr || aligned16(a0), "linear: the epilogue operand must be 16-byte aligned");
     TS_REQUIRE(k > 0, "linear: k is zero");
-    TS_REQUIRE(path >= TS_LINEAR_AUTO && path <= TS_LINEAR_PLAIN, "linear: path %d is unknown", path);
+    TS_REQUIRE(path >= TS_LINEAR_AUTO && path <= TS_LINEAR_ORDERED, "linear: path %d is unknown", path);
     if (m == 0 || n == 0) return TS_OK;
     const int chosen = pick_linear_path(m, n, k, epilogue, path);
     TS_REQUIRE(chosen > 0, "linear: no kernel takes m=%u n=%u k=%u epilogue=%d", m, n, k, epilogue);
@@ -243,6 +243,10 @@ int ts_linear_bf16(const void *x, const void *w, const void *a0, void *out, uint
     if (chosen == TS_LINEAR_PAIR) {
         TS_REQUIRE(pair_supports(m, n, k, epilogue), "linear (pair): needs m >= 512 and n >= 256 (m=%u n=%u k=%u)", m, n, k);
         return linear_pair(x, w, a0, out, m, n, k, epilogue, scale, out_dtype, s);
+    }
+    if (chosen == TS_LINEAR_ORDERED) {
+        TS_REQUIRE(ordered_supports(m, n, k, epilogue), "linear (ordered): gated epilogues are not offered in the fixed order");
+        return linear_ordered(x, w, a0, out, m, n, k, epilogue, scale, out_dtype, s);
     }
     if (chosen == TS_LINEAR_PLAIN) {
         TS_REQUIRE(plain_supports(m, n, k, epilogue), "linear (plain): a gated epilogue needs an even n (n=%u)", n);

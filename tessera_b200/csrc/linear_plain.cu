@@ -53,7 +53,117 @@ __global__ void __launch_bounds__(256) linear_plain_kernel(const PlainParams p) 
     pdl_launch_dependents();
 }
 
+// The same product with every output summed over k in ascending order, one multiply and one add at a time
+// (no fused multiply-add, no tree): the order of the reference's interpreter (engine/ir/interp/src/cpu.rs
+// matmul, sequential f32 sums), so the f32 outputs carry its bits.  For the few outputs whose *ranking* matters:
+// a MoE router's scores feed top-k, and an index must not flip on a near tie because the sums met in another
+// order.  A block owns 8 rows x 32 columns and walks k in chunks staged in shared memory (coalesced loads); a
+// thread owns one output.
+constexpr uint32_t kOrdRows = 8, kOrdCols = 32, kOrdChunk = 128, kOrdThreads = kOrdRows * kOrdCols;
+
+__device__ __forceinline__ void widen8(const uint4 &v, float *to) {
+    to[0] = bf16_lo(v.x); to[1] = bf16_hi(v.x); to[2] = bf16_lo(v.y); to[3] = bf16_hi(v.y);
+    to[4] = bf16_lo(v.z); to[5] = bf16_hi(v.z); to[6] = bf16_lo(v.w); to[7] = bf16_hi(v.w);
+}
+
+// VEC: k is a multiple of 8 and both operands start on 16-byte boundaries, so a chunk arrives as 16-byte loads,
+// asked for one chunk ahead of the sums that use it; otherwise element by element.
+template <bool VEC>
+__global__ void __launch_bounds__(kOrdThreads) linear_ordered_kernel(const PlainParams p) {
+    __shared__ float xs[kOrdRows][kOrdChunk];
+    __shared__ float ws[kOrdCols][kOrdChunk + 1];
+    pdl_wait();
+    const uint32_t tid = threadIdx.x, tx = tid % kOrdCols, ty = tid / kOrdCols;
+    const uint32_t row0 = blockIdx.y * kOrdRows, col0 = blockIdx.x * kOrdCols;
+    float sum = 0.0f;
+    if constexpr (VEC) {
+        // piece i of a chunk: 8 consecutive k of one row; pieces 0..127 are x (8 rows x 16), 128..639 are w (32 x 16)
+        constexpr uint32_t kPer = (kOrdRows + kOrdCols) * (kOrdChunk / 8) / kOrdThreads + 1;  // 3
+        uint4 held[kPer];
+        auto ask = [&](uint32_t k0) {
+#pragma unroll
+            for (uint32_t u = 0; u < kPer; u++) {
+                const uint32_t i = tid + u * kOrdThreads;
+                held[u] = make_uint4(0, 0, 0, 0);
+                if (i >= (kOrdRows + kOrdCols) * (kOrdChunk / 8)) continue;
+                const bool is_x = i < kOrdRows * (kOrdChunk / 8);
+                const uint32_t j = is_x ? i : i - kOrdRows * (kOrdChunk / 8);
+                const uint32_t r = j / (kOrdChunk / 8), kk = k0 + (j % (kOrdChunk / 8)) * 8;
+                const uint32_t line = is_x ? row0 + r : col0 + r;
+                if (kk < p.k && line < (is_x ? p.m : p.n))
+                    held[u] = __ldg(reinterpret_cast<const uint4 *>((is_x ? p.x : p.w) + (size_t)line * p.k + kk));
+            }
+        };
+        ask(0);
+        for (uint32_t k0 = 0; k0 < p.k; k0 += kOrdChunk) {
+#pragma unroll
+            for (uint32_t u = 0; u < kPer; u++) {
+                const uint32_t i = tid + u * kOrdThreads;
+                if (i >= (kOrdRows + kOrdCols) * (kOrdChunk / 8)) continue;
+                const bool is_x = i < kOrdRows * (kOrdChunk / 8);
+                const uint32_t j = is_x ? i : i - kOrdRows * (kOrdChunk / 8);
+                const uint32_t r = j / (kOrdChunk / 8), at = (j % (kOrdChunk / 8)) * 8;
+                float f[8];
+                widen8(held[u], f);
+#pragma unroll
+                for (int e = 0; e < 8; e++) (is_x ? xs[r] : ws[r])[at + e] = f[e];
+            }
+            __syncthreads();
+            if (k0 + kOrdChunk < p.k) ask(k0 + kOrdChunk);   // in flight under the sums below
+            const uint32_t len = min(kOrdChunk, p.k - k0);
+            if (len == kOrdChunk) {
+#pragma unroll 16
+                for (uint32_t j = 0; j < kOrdChunk; j++) sum = __fadd_rn(sum, __fmul_rn(xs[ty][j], ws[tx][j]));
+            } else {
+                for (uint32_t j = 0; j < len; j++) sum = __fadd_rn(sum, __fmul_rn(xs[ty][j], ws[tx][j]));
+            }
+            __syncthreads();
+        }
+    } else {
+        for (uint32_t k0 = 0; k0 < p.k; k0 += kOrdChunk) {
+            const uint32_t len = min(kOrdChunk, p.k - k0);
+            for (uint32_t i = tid; i < kOrdRows * kOrdChunk; i += kOrdThreads) {
+                const uint32_t r = i / kOrdChunk, j = i % kOrdChunk;
+                xs[r][j] = (row0 + r < p.m && j < len) ? widen(p.x[(size_t)(row0 + r) * p.k + k0 + j]) : 0.0f;
+            }
+            for (uint32_t i = tid; i < kOrdCols * kOrdChunk; i += kOrdThreads) {
+                const uint32_t c = i / kOrdChunk, j = i % kOrdChunk;
+                ws[c][j] = (col0 + c < p.n && j < len) ? widen(p.w[(size_t)(col0 + c) * p.k + k0 + j]) : 0.0f;
+            }
+            __syncthreads();
+            for (uint32_t j = 0; j < len; j++) sum = __fadd_rn(sum, __fmul_rn(xs[ty][j], ws[tx][j]));
+            __syncthreads();
+        }
+    }
+    pdl_launch_dependents();
+    const uint32_t row = row0 + ty, col = col0 + tx;
+    if (row < p.m && col < p.n) {
+        const size_t i = (size_t)row * p.n + col;
+        float v = sum;
+        if (p.epilogue == TS_EPI_ADD) v = __fadd_rn(v, p.a0[i]);
+        else if (p.epilogue == TS_EPI_SCALE) v = __fmul_rn(v, p.scale);
+        if (p.out_dtype == TS_F32) reinterpret_cast<float *>(p.out)[i] = v;
+        else reinterpret_cast<uint16_t *>(p.out)[i] = bf16_bits(v);
+    }
+}
+
 }  // namespace
+
+bool ordered_supports(uint32_t m, uint32_t n, uint32_t k, int epilogue) {
+    return m > 0 && n > 0 && k > 0 && epilogue != TS_EPI_SWIGLU && epilogue != TS_EPI_GEGLU;
+}
+
+int linear_ordered(const void *x, const void *w, const void *a0, void *out, uint32_t m, uint32_t n, uint32_t k,
+                   int epilogue, float scale, int out_dtype, cudaStream_t stream) {
+    PlainParams p = {(const uint16_t *)x, (const uint16_t *)w, (const float *)a0, out, m, n, k, epilogue, out_dtype, scale};
+    const dim3 grid(ceil_div(n, kOrdCols), ceil_div(m, kOrdRows));
+    const bool vec = k % 8 == 0 && aligned16(x) && aligned16(w);
+    cudaError_t e = vec ? launch(linear_ordered_kernel<true>, grid, dim3(kOrdThreads), 0, stream, pdl_enabled(), p)
+                        : launch(linear_ordered_kernel<false>, grid, dim3(kOrdThreads), 0, stream, pdl_enabled(), p);
+    if (e != cudaSuccess)
+        return fail(TS_ERR_CUDA, "launch of linear_ordered failed: %s (%d) %s", cudaGetErrorName(e), (int)e, cudaGetErrorString(e));
+    return TS_OK;
+}
 
 bool plain_supports(uint32_t m, uint32_t n, uint32_t k, int epilogue) {
     const bool gated = epilogue == TS_EPI_SWIGLU || epilogue == TS_EPI_GEGLU;

@@ -502,6 +502,38 @@ struct StreamPlan {
 
 constexpr uint32_t kSmemBudget = 225 * 1024;
 
+// Clusters of `size` blocks of this kernel (one block an SM) that the device holds at once: GPCs whose SM count is
+// not a multiple of the cluster size strand SMs, so 148 SMs hold fewer than 148 / size clusters.  Cached per
+// device and size.
+uint32_t resident_clusters(uint32_t size) {
+    static std::atomic<uint32_t> cache[256][4] = {};
+    const uint32_t slot = size == 2 ? 0 : size == 4 ? 1 : size == 8 ? 2 : 3;
+    std::atomic<uint32_t> &c = cache[current_device() & 255][slot];
+    if (const uint32_t have = c.load(std::memory_order_relaxed)) return have;
+    auto kernel = linear_stream_kernel<64, false>;
+    uint32_t found = (uint32_t)sm_count() / size;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget) == cudaSuccess) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(1, size * ((uint32_t)sm_count() / size));
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = kSmemBudget;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1;
+        attr[0].val.clusterDim.y = size;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) == cudaSuccess && n > 0) found = (uint32_t)n;
+        else cudaGetLastError();
+    } else {
+        cudaGetLastError();
+    }
+    c.store(found, std::memory_order_relaxed);
+    return found;
+}
+
 bool plan_stream(uint32_t m, uint32_t n, uint32_t k, int epilogue, StreamPlan *out) {
     StreamPlan s = {};
     s.gated = epilogue == TS_EPI_SWIGLU || epilogue == TS_EPI_GEGLU;
@@ -519,6 +551,9 @@ bool plan_stream(uint32_t m, uint32_t n, uint32_t k, int epilogue, StreamPlan *o
     uint32_t splits = 1;
     const uint32_t max_splits = std::min<uint32_t>(std::min<uint32_t>(8, s.bn / 8), s.kb_total);
     while (splits * 2 <= max_splits && s.tiles * splits * 2 <= sms) splits *= 2;
+    // ... and whose clusters are all resident at once: 16 clusters of 8 do not fit 148 SMs (a second wave doubles
+    // the launch), 16 of 4 do.
+    while (splits > 1 && s.tiles > resident_clusters(splits) && layout(splits / 2, 2).total <= kSmemBudget) splits /= 2;
     while (layout(splits, 2).total > kSmemBudget && splits * 2 <= max_splits) splits *= 2;
     if (layout(splits, 2).total > kSmemBudget) return false;
     s.splits = splits;
@@ -601,6 +636,17 @@ uint32_t stream_sumsq_parts(uint32_t m, uint32_t n, uint32_t k, int epilogue) {
 
 int linear_stream(const void *x, const void *w, const void *a0, void *out, uint32_t m, uint32_t n, uint32_t k,
                   int epilogue, float scale, int out_dtype, cudaStream_t stream, const StreamFused *fused) {
+    // 65..128 rows against a large matrix: with 128 batch columns the resident x slice forces a k split over a
+    // cluster on every one of thousands of tiles (469 us for the 151936 x 1024 unembedding against 65 us at 64
+    // rows).  Two launches of at most 64 rows each read the weights twice and still finish in a third of the time.
+    if (m > 64 && m <= 128 && (size_t)n * k >= ((size_t)16 << 20) && !fused) {
+        const bool gated = epilogue == TS_EPI_SWIGLU || epilogue == TS_EPI_GEGLU;
+        const size_t out_n = gated ? n / 2 : n, esz = out_dtype == TS_F32 ? 4 : 2;
+        int rc = linear_stream(x, w, a0, out, 64, n, k, epilogue, scale, out_dtype, stream, nullptr);
+        if (rc != TS_OK) return rc;
+        return linear_stream((const char *)x + (size_t)64 * k * 2, w, a0 ? (const char *)a0 + 64 * out_n * 4 : nullptr,
+                             (char *)out + 64 * out_n * esz, m - 64, n, k, epilogue, scale, out_dtype, stream, nullptr);
+    }
     StreamPlan s;
     if (!plan_stream(m, n, k, epilogue, &s))
         return fail(TS_ERR_BAD_INPUT, "linear (stream): unsupported shape m=%u n=%u k=%u epilogue=%d", m, n, k, epilogue);

@@ -114,6 +114,10 @@ int rope_angles(const uint32_t *positions, float *out, uint32_t count, uint32_t 
 int rope(void *x, int dtype, const float *freqs, uint32_t positions, uint32_t heads, uint32_t width, int adjacent,
          cudaStream_t stream);
 bool plain_supports(uint32_t m, uint32_t n, uint32_t k, int epilogue);
+// Sequential f32 sums in ascending k, the interpreter's order: bit-exact scores for a router (no gated epilogue).
+bool ordered_supports(uint32_t m, uint32_t n, uint32_t k, int epilogue);
+int linear_ordered(const void *x, const void *w, const void *a0, void *out, uint32_t m, uint32_t n, uint32_t k,
+                   int epilogue, float scale, int out_dtype, cudaStream_t stream);
 int linear_plain(const void *x, const void *w, const void *a0, void *out, uint32_t m, uint32_t n, uint32_t k,
                  int epilogue, float scale, int out_dtype, cudaStream_t stream);
 size_t picked_workspace_bytes(uint32_t rows, uint32_t n, uint32_t k, uint32_t count);

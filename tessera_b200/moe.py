@@ -41,7 +41,7 @@ class MoeWeights:
 
 def _cuda_route(h, w: MoeWeights, top: int):
     from . import ops
-    scores = ops.linear(h, w.router, out_dtype=torch.float32)
+    scores = ops.router_scores(h, w.router)   # the interpreter's summation order: ids are bit-exact, near ties included
     ids = ops.top_k(scores, top)
     return ids, ops.take_softmax(scores, ids)
 

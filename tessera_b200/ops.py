@@ -74,6 +74,12 @@ def linear(x, w, a0=None, *, epilogue="none", scale=1.0, out_dtype=torch.bfloat1
     return out
 
 
+def router_scores(x, router):
+    """A router's scores, f32 [rows, experts], every sum in the interpreter's order (path "ordered"): top-k over
+    them picks the interpreter's experts, near ties included."""
+    return linear(x, router, out_dtype=torch.float32, path="ordered")
+
+
 def linear_fused(x, w, a0=None, *, epilogue="none", scale=1.0, out_dtype=torch.bfloat16, out=None, rows=None,
                  next_gain=None):
     """ts_linear_fused_bf16.  rows = (partial sums of squares f32 [m, parts], eps): x is bf16(row * gain) and the

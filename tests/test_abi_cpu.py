@@ -102,3 +102,24 @@ def test_synthetic_weights_are_reproducible():
     assert np.array_equal(synth.bf16_bits(x), O.bf16_bits(x))
     total = sum(int(np.prod(synth.decoder_weight_shape(n, synth.QWEN3_0_6B))) for n in synth.decoder_weight_names(28))
     assert total == 596_049_920  # tools/parity/tests/qwen3/mod.rs:16
+
+
+def test_platform_row_reads_through_the_abi():
+    """ts_platform_info needs no device: its row is the committed platforms/cuda-b200.json (the record a maintainer
+    adds to engine/gpu/platform/platforms/), shaped like the reference's Row (platform.rs:11-29), and it refines the
+    sm_10x row's mma.sync tiles to the tcgen05 one."""
+    import json
+    from tessera_b200 import _lib
+    buf = C.create_string_buffer(4096)
+    assert _lib.lib.ts_platform_info(buf, len(buf)) == 0
+    info = json.loads(buf.value.decode())
+    row = info["row"]
+    committed = json.load(open(os.path.join(ROOT, "tessera_b200", "platforms", "cuda-b200.json")))
+    assert row == committed
+    assert set(row) >= {"matches", "tile", "bf16_tile", "pdl", "check", "note"}        # the reference's Row fields
+    assert row["matches"] == ["cuda sm_100"] and row["tile"] == [128, 256, 16] and row["pdl"] is True
+    assert row["b200"]["abi"] == _lib.lib.ts_abi_version() and row["b200"]["cluster"] == 8
+    if not torch.cuda.is_available():
+        assert info["asked"] is None
+    small = C.create_string_buffer(16)
+    assert _lib.lib.ts_platform_info(small, len(small)) == _lib.TS_ERR_BAD_INPUT

@@ -170,6 +170,59 @@ def test_qwen3_0p6b_logits_follow_golden():
     assert worst <= 1e-2
 
 
+@pytest.mark.parametrize("step_kernel", [False, True])
+def test_qwen3_0p6b_varied_tokens_and_logits_follow_golden(step_kernel):
+    """The second full-size fixture (tests/golden/qwen3_0p6b_greedy_varied.json: weights N(0, 0.05), gains 1 +- 0.1,
+    written by make_qwen3_tokens.py --varied), whose greedy ids change at every step - nothing like the first
+    fixture's fixed point, so a wrong kernel anywhere moves them.
+
+    Teacher-forced first: at each of the first 32 steps the winning logit and the probe logits within 1e-2 of the
+    largest logit, and the id equal to the checker's.  The fixture's rule (first seed with every margin above 1e-2)
+    leaves a few thin margins (0.02 on logits near 7): an id may differ there only if the checker's margin at that
+    step is below twice the logit error this very run measured, i.e. only if rounding explains it.  Then
+    free-running: the generated ids equal the checker's up to the first such thin step, and for 16 steps at least.
+    Both forms of the decode step are held to it."""
+    path = os.path.join(os.path.dirname(__file__), "golden", "qwen3_0p6b_greedy_varied.json")
+    gold = json.load(open(path))
+    cfg = gold["config"]
+    prompt = synth.prompt_tokens(cfg["vocab"], gold["prompt_len"], seed=gold["prompt_seed"])
+    assert prompt[:8].tolist() == gold["prompt_head"] and len(set(gold["tokens"][:32])) >= 16
+    from tessera_b200 import runner
+    n, at = len(prompt), np.array(gold["probe_ids"])
+
+    def fresh():
+        dec = runner.Decoder(cfg, 1, 192, 128, page=64)
+        dec.load_all(synth.decoder_weights(cfg, gold["seed"], std=gold["std"], gains=gold["gains"]))
+        assert dec.use_step_kernel(step_kernel) or not step_kernel
+        return dec
+
+    dec = fresh()
+    worst_rel, worst_abs, flips = 0.0, 0.0, []
+    for t in range(32):
+        if t == 0:
+            ids = dec.step(prompt, np.zeros(n), np.arange(n), out_rows=[n - 1])
+        else:
+            ids = dec.step([gold["tokens"][t - 1]], [0], [n + t - 1])
+        row = dec.read_logits(1)[0]
+        want_at, want_top = np.array(gold["probe_logits"][t]), gold["top_logit"][t]
+        scale = max(abs(want_top), float(np.abs(want_at).max()))
+        err = max(float(np.abs(row[at] - want_at).max()), abs(float(row.max()) - want_top))
+        worst_abs, worst_rel = max(worst_abs, err), max(worst_rel, err / scale)
+        if int(ids[0]) != gold["tokens"][t]:
+            flips.append(t)
+    dec.close()
+    print(f"largest logit error over 32 steps: {worst_rel:.2e} of the largest logit ({worst_abs:.3g} absolute); flips at {flips}")
+    assert worst_rel <= 1e-2
+    for t in flips:
+        assert gold["margins"][t] < 2 * worst_abs, (t, gold["margins"][t], worst_abs)
+    assert len(flips) <= 2
+    dec = fresh()
+    got = dec.generate([prompt.tolist()], gold["new"])[0].tolist()
+    dec.close()
+    same = next((t for t in range(32) if got[t] != gold["tokens"][t]), 32)
+    assert same >= 16 and (same == 32 or gold["margins"][same] < 2 * worst_abs), (same, got[:32])
+
+
 def test_prefix_reuse_through_the_page_pool():
     """A second prompt that shares its beginning with a retained run (engine/ir/kv/src/prefix.rs, reuse.rs): its slot
     borrows the run's pages through the table, the shared partial page is copied before the first write

@@ -2,7 +2,7 @@
 
 ts_top_1_static exists for hosts that cannot give a kernel scratch memory (a runtime whose device
 buffers were all fixed at plan time, a process with no memory budget left): it keeps its scratch
-inside the library.  Its ids are integers and must equal ts_top_k's (k = 1) exactly.  Two calls in a
+inside the library.  Its ids are integers and must equal ts_top_k's (k = 1) and the CPU checker's exactly.  Two calls in a
 row share that built-in scratch, so the second must not be disturbed by what the first left there.
 This file sorts last on purpose: a run that stops at the first failure has then already run
 everything else.
@@ -47,6 +47,29 @@ def test_two_calls_in_a_row_match_the_workspace_entry_point():
     assert np.array_equal(got_first, _regular_top1(first))
     assert np.array_equal(got_second, _regular_top1(second))
     assert got_first[5] == 100 and got_first[9] == 151936
+    import oracle as O
+    assert np.array_equal(got_first, O.top_k(first.cpu().numpy(), 1).reshape(-1))
+    assert np.array_equal(got_second, O.top_k(second.float().cpu().numpy(), 1).reshape(-1))
+
+
+def test_narrow_rows_and_dependent_launch():
+    # widths below the 64 parts a row is cut into (most parts empty), and a call with programmatic dependent
+    # launch switched on: both must still equal the workspace entry point and the checker
+    import oracle as O
+    from tessera_b200 import ops
+    rng = np.random.default_rng(32)
+    for width, pdl in ((5, False), (63, False), (40, True), (3000, True)):
+        x = torch.from_numpy(rng.standard_normal((9, width), dtype=np.float32)).cuda()
+        x[2, :] = 1.5                               # a whole row of ties: index 0 wins
+        ops.set_pdl(pdl)
+        try:
+            got = _static_top1(x)
+            again = _static_top1(x)
+        finally:
+            ops.set_pdl(False)
+        assert np.array_equal(got, again) and got[2] == 0
+        assert np.array_equal(got, _regular_top1(x))
+        assert np.array_equal(got, O.top_k(x.cpu().numpy(), 1).reshape(-1))
 
 
 def test_too_many_rows_are_refused():
