@@ -51,12 +51,16 @@ def _cuda_experts(x, ids, w: MoeWeights):
     return ops.moe_experts(x, ids, w.w_in, w.w_out, repeat=1, first=w.first)
 
 
-def _cuda_shared(h, w: MoeWeights):
+def _cuda_shared(h, w: MoeWeights, residual=None):
+    """The shared expert's rows, f32; with `residual` the down projection adds it in its epilogue, so the block's
+    output lands on the residual stream without an elementwise launch of its own."""
     from . import ops
     if w.shared_in is None:
-        return None
+        return residual
     inner = ops.linear(h, w.shared_in, epilogue="swiglu")
-    return ops.linear(inner, w.shared_out, out_dtype=torch.float32)
+    if residual is None:
+        return ops.linear(inner, w.shared_out, out_dtype=torch.float32)
+    return ops.linear(inner, w.shared_out, residual, epilogue="add", out_dtype=torch.float32)
 
 
 def _cuda_local(h_all, ids, gates, w: MoeWeights):
@@ -69,11 +73,11 @@ def _cuda_mix(y_picks, gates, add):
     return ops.moe_mix(y_picks, gates, add)
 
 
-def moe_forward(h, w: MoeWeights, top: int):
-    """Single GPU: every expert is local."""
+def moe_forward(h, w: MoeWeights, top: int, residual=None):
+    """Single GPU: every expert is local.  With `residual` (f32 [rows, H]) the result is residual + block."""
     from . import ops
     ids, gates = _cuda_route(h, w, top)
-    return ops.moe(h, ids, gates, w.w_in, w.w_out, add=_cuda_shared(h, w), first=w.first), ids, gates
+    return ops.moe(h, ids, gates, w.w_in, w.w_out, add=_cuda_shared(h, w, residual), first=w.first), ids, gates
 
 
 class ExpertParallel:
@@ -99,7 +103,16 @@ class ExpertParallel:
         counts = torch.bincount(owner, minlength=self.world)
         return order, counts
 
-    def forward_replicated(self, h, w: MoeWeights, top: int):
+    def _add(self, h, w: MoeWeights, residual):
+        """What is added to the routed rows: the shared expert's output and, when given, the residual rows."""
+        if self.shared_fn is _cuda_shared:
+            return _cuda_shared(h, w, residual)
+        add = self.shared_fn(h, w)
+        if residual is None:
+            return add
+        return residual if add is None else add + residual
+
+    def forward_replicated(self, h, w: MoeWeights, top: int, residual=None):
         """all-gather rows -> route everywhere -> local experts on all rows -> reduce-scatter.  No host reads."""
         rows, hidden = h.shape
         h_all = torch.empty((self.world * rows, hidden), dtype=h.dtype, device=h.device)
@@ -112,15 +125,16 @@ class ExpertParallel:
         else:
             y = torch.empty((rows, hidden), dtype=part.dtype, device=part.device)
             dist.reduce_scatter_tensor(y, part, group=self.group)
-        add = self.shared_fn(h, w)
+        add = self._add(h, w, residual)
         if add is not None:
             y += add
         mine = slice(self.rank * rows, (self.rank + 1) * rows)
         return y, ids[mine], gates[mine]
 
-    def forward(self, h, w: MoeWeights, top: int, scheme: str = "dispatch"):
+    def forward(self, h, w: MoeWeights, top: int, scheme: str = "dispatch", residual=None):
+        """With `residual` (f32 [rows, H]) the result is residual + block."""
         if scheme == "replicate":
-            return self.forward_replicated(h, w, top)
+            return self.forward_replicated(h, w, top, residual)
         rows, hidden = h.shape
         ids, gates = self.route_fn(h, w, top)
         order, send_counts = self.plan(ids, w.experts_total)
@@ -141,7 +155,7 @@ class ExpertParallel:
         dist.all_to_all_single(y_back, y_recv.contiguous(), send, recv, group=self.group)
         y_picks = torch.empty_like(y_back)
         y_picks[order] = y_back                           # back to pick order
-        return self.mix_fn(y_picks, gates, self.shared_fn(h, w)), ids, gates
+        return self.mix_fn(y_picks, gates, self._add(h, w, residual)), ids, gates
 
 
 class OneRankOfMany(ExpertParallel):
@@ -155,14 +169,14 @@ class OneRankOfMany(ExpertParallel):
         self.experts_fn, self.route_fn, self.shared_fn = _cuda_experts, _cuda_route, _cuda_shared
         self.mix_fn, self.local_fn = _cuda_mix, _cuda_local
 
-    def forward(self, h, w: MoeWeights, top: int, scheme: str = "replicate"):
+    def forward(self, h, w: MoeWeights, top: int, scheme: str = "replicate", residual=None):
         rows = h.shape[0]
         h_all = h.repeat(self.world, 1)
         ids, gates = self.route_fn(h_all, w, top)
         part = self.local_fn(h_all, ids, gates, w)
         mine = slice(self.rank * rows, (self.rank + 1) * rows)
         y = part[mine].clone()
-        add = self.shared_fn(h, w)
+        add = _cuda_shared(h, w, residual)
         if add is not None:
             y += add
         return y, ids[mine], gates[mine]

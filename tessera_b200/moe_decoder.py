@@ -90,11 +90,12 @@ class MoeDecoder:
                                        positions, kept, keys, heads, eps=eps, scale=d ** -0.5, out=q)
             x = ops.linear(a.view(rows, heads * d), L["wo"], x, epilogue="add", out_dtype=torch.float32, out=x)
             h = ops.rms_norm(x, L["ln2"], eps)
+            # the block's output lands on the residual rows inside its own kernels (the shared expert's down
+            # projection adds them in its epilogue, the routed mix adds that)
             if self.ep is None:
-                y, _, _ = moe_forward(h, L["moe"], c["top"])
+                x, _, _ = moe_forward(h, L["moe"], c["top"], residual=x)
             else:
-                y, _, _ = self.ep.forward(h, L["moe"], c["top"], scheme=self.scheme)
-            x = x + y
+                x, _, _ = self.ep.forward(h, L["moe"], c["top"], scheme=self.scheme, residual=x)
         return x
 
     def step_graphed(self, x: torch.Tensor, slots: torch.Tensor, positions: torch.Tensor, keys: int) -> torch.Tensor:

@@ -17,12 +17,13 @@ says which seed that was and lists the margins.  Without such a seed the last on
 margins is written.
 
 A second fixture, `python tests/golden/make_qwen3_tokens.py --varied`, writes qwen3_0p6b_greedy_varied.json:
-the same shapes and prompt with weights N(0, 0.05) and norm gains 1 +- 0.1.  With the configuration's N(0, 0.02)
+the same shapes and prompt with weights N(0, 0.035) and norm gains 1 +- 0.1.  With the configuration's N(0, 0.02)
 and gains of one the layers add little to the residual stream, the tied unembedding hands back the token that
 went in, and the greedy sequence repeats one id: a fixed point that a kernel far outside tolerance would still
-reproduce.  The larger weights make every step produce a new id (20 distinct ids in the first 20 steps), so an
-error anywhere in the stack moves the sequence.  Its rule is plain: the first seed whose first 32 margins all
-exceed 1e-2, no search beyond that.
+reproduce.  The larger weights make nearly every step produce a new id, so an error anywhere in the stack moves the
+sequence.  (Larger still is no better: at N(0, 0.05) the random stack amplifies bf16 rounding so much that two
+correct implementations differ by 3e-2 of the largest logit after 28 layers.)  Its rule is plain: the first seed
+whose first 32 margins all exceed 1e-2, no search beyond that.
 """
 import json
 import os
@@ -87,7 +88,7 @@ def greedy(cfg, seed, prompt, new, context, stop_below=None, probes=None, gains=
     return out, margins
 
 
-VARIED = dict(std=0.05, gains="near_one", min_margin=1e-2, min_distinct=16)
+VARIED = dict(std=0.035, gains="near_one", min_margin=1e-2, min_distinct=16)
 
 
 def write_varied(seeds):

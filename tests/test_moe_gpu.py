@@ -107,6 +107,30 @@ def test_shared_expert_adds_in():
     assert np.allclose(with_add, base + add, rtol=1e-6, atol=1e-6)
 
 
+def test_block_lands_on_the_residual_rows():
+    # moe_forward(..., residual=x) is x + block: the shared expert's down projection adds x in its epilogue and the
+    # routed mix adds that, with no elementwise launch in between
+    from tessera_b200 import moe
+    rng = np.random.default_rng(12)
+    rows, experts, top, hidden, ffn, shared = 40, 8, 2, 256, 128, 256
+    h = from_bits(normal_bf16(rng, (rows, hidden)))
+    w_in, w_out = _weights(rng, experts, hidden, ffn)
+    w = moe.MoeWeights(from_bits(normal_bf16(rng, (experts, hidden), 0.1)), from_bits(w_in), from_bits(w_out),
+                       from_bits(normal_bf16(rng, (2 * shared, hidden), 0.05)), from_bits(normal_bf16(rng, (hidden, shared), 0.05)),
+                       first=0, experts_total=experts)
+    x = torch.from_numpy(rng.standard_normal((rows, hidden), dtype=np.float32)).cuda()
+    base, ids, _ = moe.moe_forward(h, w, top)
+    onto, ids2, _ = moe.moe_forward(h, w, top, residual=x)
+    torch.cuda.synchronize()
+    assert torch.equal(ids, ids2)
+    assert torch.allclose(onto, base + x, rtol=1e-5, atol=1e-5)
+    w.shared_in = w.shared_out = None          # no shared expert: the residual rows are the add
+    bare, _, _ = moe.moe_forward(h, w, top)
+    onto, _, _ = moe.moe_forward(h, w, top, residual=x)
+    torch.cuda.synchronize()
+    assert torch.allclose(onto, bare + x, rtol=1e-5, atol=1e-5)
+
+
 def test_uneven_routing_many_rows_on_one_expert():
     # more rows on one expert than a batch tile holds, and experts with none
     from tessera_b200 import ops
