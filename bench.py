@@ -88,6 +88,7 @@ def parse_args():
     ap.add_argument("--path", default="auto", choices=["auto", "skinny", "umma", "stream", "pair"],
                     help="--case linear_* and --workload sweep: kernel family")
     ap.add_argument("--only-rows", type=int, default=0, help="--workload sweep: only this row count")
+    ap.add_argument("--q8", action="store_true", help="--workload sweep: also the Q8_0 weight form at the decode-sized row counts")
     return ap.parse_args()
 
 
@@ -583,6 +584,20 @@ def run_sweep(args):
                     "path": args.path, "launches": steps, "weight_copies": copies, "status": ops.device_status()}
             print(json.dumps(line), flush=True)
         del ws
+        if args.q8:   # the same shape with Q8_0 weights: 34 bytes per 32 weights
+            packed = [ops.q8_0_pack(torch.randn(n, k) * 0.02).cuda() for _ in range(min(copies, 12) if n < 100000 else 2)]
+            for m in [r for r in ([args.only_rows] if args.only_rows else SWEEP_ROWS) if r <= 64]:
+                x = bf(m, k)
+                out = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+                calls = [(lambda w=w: ops.linear_q8_0(x, w, out=out)) for w in packed]
+                steps = max(8, min(200, int(2e9 // (2.0 * m * n * k + 1e7))))
+                us = _graph_us(calls, steps)
+                byts = n * (k // 32) * 34.0 + 2.0 * m * k + 2.0 * m * n
+                print(json.dumps({"workload": "linear sweep", "form": "q8_0", "case": name, "m": m, "n": n, "k": k,
+                                  "us_per_launch": round(us, 3), "GBs": round(byts / us / 1e3, 1), "bound": "hbm",
+                                  "frac": round(byts / us / 1e3 / hbm, 4), "peak_kind": f"of {hbm_kind} copy rate",
+                                  "launches": steps, "weight_copies": len(packed), "status": ops.device_status()}), flush=True)
+            del packed
 
 
 def run_attn(args):

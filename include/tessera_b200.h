@@ -341,6 +341,25 @@ int ts_set_pdl(int enabled);
  * kind of record).  Synchronises the device. */
 int ts_device_status(void);
 
+/* ---------------------------------------------------------------------------
+ * Narrow weights, first form: Q8_0 (engine/ir/mem/src/block.rs:259-260; the matmul rules accept it through
+ * engine/plan/codegen/src/block.rs:209-215).  A matrix [n, k] (k a multiple of 32) is its elements in row-major
+ * order cut into blocks of 32: an f16 scale (little endian), then 32 signed bytes; 34 bytes a block, a row is
+ * k / 32 blocks.  ts_q8_0_pack / ts_q8_0_unpack are the form's host-side pack and unpack (block.rs:223-258:
+ * scale = max |x| / 127 as stored in f16, codes rounded ties-to-even and clamped); ts_q8_0_bytes the packed size.
+ *
+ * ts_linear_q8_0: out[m, n] = sum_k x[m, k] * w[n, k] (+ epilogue as ts_linear_bf16) for decode-sized launches:
+ * 1 <= m <= 64, n a multiple of 64, k a multiple of 256; x bf16, w packed Q8_0 on the device, f32 sums by the
+ * form's dot product (block.rs:204-221: per block the sum of x times code, times the scale).  Other sizes return
+ * TS_ERR_BAD_INPUT: dequantise (ts_q8_0_unpack) and use ts_linear_bf16.
+ * ------------------------------------------------------------------------- */
+size_t ts_q8_0_bytes(size_t elements);
+int ts_q8_0_pack(const float *data, size_t elements, void *out);
+int ts_q8_0_unpack(const void *bytes, size_t elements, float *out);
+size_t ts_linear_q8_0_workspace_bytes(uint32_t m, uint32_t n, uint32_t k);
+int ts_linear_q8_0(const void *x, const void *w_q8_0, const void *a0, void *out, uint32_t m, uint32_t n, uint32_t k,
+                   int epilogue, float scale, int out_dtype, void *workspace, size_t workspace_bytes, void *stream);
+
 /* The B200 entry of the reference's platform table plus what the current device reports, as JSON text:
  *   {"row": <the table row: matches "cuda sm_100", tile = bf16_tile = [128, 256, 16] (tcgen05.mma, M x N x K with
  *            N up to 256), pdl, check ["sm_100a"], and under "b200" what the reference's `Needs` has no field for

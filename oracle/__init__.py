@@ -125,6 +125,34 @@ def matmul(x, w, acc="f32") -> np.ndarray:
     return out
 
 
+def q8_0_pack(data) -> np.ndarray:
+    """engine/ir/mem/src/block.rs Block::pack for Q8_0: bytes of an f16 scale and 32 signed codes a block."""
+    data = _f(data).reshape(-1)
+    lib().to_q8_0_bytes.restype = C.c_size_t
+    out = np.zeros(lib().to_q8_0_bytes(_z(data.size)), np.uint8)
+    lib().to_q8_0_pack(_p(data), _z(data.size), _p(out))
+    return out
+
+
+def q8_0_unpack(packed, elements) -> np.ndarray:
+    packed = np.ascontiguousarray(packed, dtype=np.uint8)
+    out = np.empty(elements, np.float32)
+    lib().to_q8_0_unpack(_p(packed), _z(elements), _p(out))
+    return out
+
+
+def matmul_q8_0(x, packed, n) -> np.ndarray:
+    """x [m, k] times a Q8_0 matrix [n, k] transposed, every output by Form::dot (block.rs:204-221)."""
+    x = _f(x)
+    k = x.shape[-1]
+    m = x.size // k
+    packed = np.ascontiguousarray(packed, dtype=np.uint8)
+    assert k % 32 == 0 and packed.size == n * (k // 32) * 34
+    out = np.empty(x.shape[:-1] + (n,), np.float32)
+    lib().to_matmul_q8_0(_p(x), _p(packed), _p(out), _z(m), _z(n), _z(k))
+    return out
+
+
 def matmul_picked(x, table, ids, first=0) -> np.ndarray:
     """engine/ir/interp/src/cpu.rs:89-105: x [m, k], table [experts, n, k], ids [rows]."""
     x, table, ids = _f(x), _f(table), _u(ids)

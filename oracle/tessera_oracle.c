@@ -163,6 +163,97 @@ TO_API void to_matmul_bf16w(const float *x, const uint16_t *w, float *out, size_
     free(wide);
 }
 
+/* ---- Q8_0 block form: engine/ir/mem/src/block.rs:259-260 (an f16 scale, then 32 signed bytes), packed,
+ * unpacked and dotted as block.rs:204-258 does it. ------------------------------------------------------ */
+
+static uint16_t to_f16_bits(float x) { /* round to nearest even, as half::f16::from_f32 */
+    uint32_t u;
+    memcpy(&u, &x, 4);
+    uint32_t sign = (u >> 16) & 0x8000u, mant = u & 0x7FFFFFu;
+    int32_t exp = (int32_t)((u >> 23) & 0xFF);
+    if (exp == 255) return (uint16_t)(sign | 0x7C00u | (mant ? 0x200u : 0));
+    int32_t e = exp - 127 + 15;
+    if (e >= 31) return (uint16_t)(sign | 0x7C00u);
+    if (e <= 0) {
+        if (e < -10) return (uint16_t)sign;
+        mant |= 0x800000u;
+        uint32_t shift = (uint32_t)(14 - e);
+        uint32_t half = mant >> shift, rest = mant & ((1u << shift) - 1), mid = 1u << (shift - 1);
+        if (rest > mid || (rest == mid && (half & 1))) half++;
+        return (uint16_t)(sign | half);
+    }
+    uint32_t half = ((uint32_t)e << 10) | (mant >> 13), rest = mant & 0x1FFFu;
+    if (rest > 0x1000u || (rest == 0x1000u && (half & 1))) half++;
+    return (uint16_t)(sign | half);
+}
+
+static float to_f16_widen(uint16_t h) {
+    uint32_t sign = ((uint32_t)h & 0x8000u) << 16, exp = (h >> 10) & 0x1F, mant = h & 0x3FFu, u;
+    if (exp == 0) {
+        if (mant == 0) u = sign;
+        else {
+            int e = -1;
+            do { mant <<= 1; e++; } while (!(mant & 0x400u));
+            u = sign | ((uint32_t)(127 - 15 - e) << 23) | ((mant & 0x3FFu) << 13);
+        }
+    } else if (exp == 31) u = sign | 0x7F800000u | (mant << 13);
+    else u = sign | ((exp - 15 + 127) << 23) | (mant << 13);
+    float f;
+    memcpy(&f, &u, 4);
+    return f;
+}
+
+TO_API size_t to_q8_0_bytes(size_t elements) { return (elements + 31) / 32 * 34; }
+
+/* Block::pack with S = F16, C = I8, B = 32, no head: scale = max |x| / 127 stored as f16; codes see the scale
+ * as stored; round_ties_even, clamped to [-128, 127]. */
+TO_API void to_q8_0_pack(const float *data, size_t elements, uint8_t *out) {
+    memset(out, 0, to_q8_0_bytes(elements));
+    for (size_t b = 0; b * 32 < elements; b++) {
+        size_t n = elements - b * 32 < 32 ? elements - b * 32 : 32;
+        float top = 0.0f;
+        for (size_t j = 0; j < n; j++) top = fmaxf(top, fabsf(data[b * 32 + j]));
+        uint16_t bits = to_f16_bits(top / 127.0f);
+        uint8_t *at = out + b * 34;
+        at[0] = (uint8_t)(bits & 0xFF);
+        at[1] = (uint8_t)(bits >> 8);
+        float stored = to_f16_widen(bits);
+        for (size_t j = 0; j < n; j++) {
+            float scaled = stored == 0.0f ? 0.0f : data[b * 32 + j] / stored;
+            float r = rintf(scaled); /* the default rounding mode: ties to even */
+            if (r < -128.0f) r = -128.0f;
+            if (r > 127.0f) r = 127.0f;
+            at[2 + j] = (uint8_t)(int8_t)r;
+        }
+    }
+}
+
+TO_API void to_q8_0_unpack(const uint8_t *bytes, size_t elements, float *out) {
+    for (size_t i = 0; i < elements; i++) {
+        const uint8_t *at = bytes + i / 32 * 34;
+        float scale = to_f16_widen((uint16_t)(at[0] | (at[1] << 8)));
+        out[i] = scale * (float)(int8_t)at[2 + i % 32];
+    }
+}
+
+/* x [m, k] against a Q8_0 matrix [n, k] (k a multiple of 32): every output is Form::dot over its row -
+ * per block the plain sum of x times code, times the block's scale, blocks added in order. */
+TO_API void to_matmul_q8_0(const float *x, const uint8_t *w, float *out, size_t m, size_t n, size_t k) {
+    size_t row_bytes = k / 32 * 34;
+    for (size_t r = 0; r < m; r++)
+        for (size_t c = 0; c < n; c++) {
+            const uint8_t *row = w + c * row_bytes;
+            float sum = 0.0f;
+            for (size_t b = 0; b < k / 32; b++) {
+                const uint8_t *at = row + b * 34;
+                float part = 0.0f;
+                for (size_t j = 0; j < 32; j++) part = part + x[r * k + b * 32 + j] * (float)(int8_t)at[2 + j];
+                sum = sum + to_f16_widen((uint16_t)(at[0] | (at[1] << 8))) * part;
+            }
+            out[r * n + c] = sum;
+        }
+}
+
 /* matmul_picked: engine/ir/interp/src/cpu.rs:89-105.  Row r of x meets matrix
  * ids[r] - first of `table` ([experts, n, k]); an id outside the table reads zeros.
  * x has `m` rows; ids has `rows` entries, rows a multiple of m; row r reads x row

@@ -57,6 +57,11 @@ SIGNATURES = {
     "ts_device_status": (i32, []),
     "ts_wait_runs_out": (i32, [C.c_uint64, vp]),
     "ts_platform_info": (i32, [C.c_char_p, sz]),
+    "ts_q8_0_bytes": (sz, [sz]),
+    "ts_q8_0_pack": (i32, [vp, sz, vp]),
+    "ts_q8_0_unpack": (i32, [vp, sz, vp]),
+    "ts_linear_q8_0_workspace_bytes": (sz, [u32, u32, u32]),
+    "ts_linear_q8_0": (i32, [vp, vp, vp, vp, u32, u32, u32, i32, f32, i32, vp, sz, vp]),
     "ts_linear_workspace_bytes": (sz, [u32, u32, u32, i32, i32]),
     "ts_linear_bf16": (i32, [vp, vp, vp, vp, u32, u32, u32, i32, f32, i32, i32, vp, sz, vp]),
     "ts_gather_scaled_bf16": (i32, [vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, vp]),

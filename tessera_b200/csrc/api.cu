@@ -173,6 +173,32 @@ int ts_device_status(void) {
     return a ? a : b ? b : c ? c : d ? d : e ? e : f ? f : g;
 }
 
+size_t ts_q8_0_bytes(size_t elements) { return q8_0_bytes(elements); }
+
+int ts_q8_0_pack(const float *data, size_t elements, void *out) {
+    TS_REQUIRE(data && out, "q8_0 pack: NULL argument");
+    q8_0_pack(data, elements, (uint8_t *)out);
+    return TS_OK;
+}
+
+int ts_q8_0_unpack(const void *bytes, size_t elements, float *out) {
+    TS_REQUIRE(bytes && out, "q8_0 unpack: NULL argument");
+    q8_0_unpack((const uint8_t *)bytes, elements, out);
+    return TS_OK;
+}
+
+size_t ts_linear_q8_0_workspace_bytes(uint32_t m, uint32_t n, uint32_t k) { return q8_0_workspace_bytes(m, n, k); }
+
+int ts_linear_q8_0(const void *x, const void *w, const void *a0, void *out, uint32_t m, uint32_t n, uint32_t k, int epilogue,
+                   float scale, int out_dtype, void *workspace, size_t workspace_bytes, void *stream) {
+    TS_REQUIRE(x && w && out, "linear (q8_0): x, w and out must not be NULL");
+    TS_REQUIRE(aligned16(x) && aligned16(w) && aligned16(out), "linear (q8_0): x, w and out must be 16-byte aligned");
+    TS_REQUIRE(epilogue >= TS_EPI_NONE && epilogue <= TS_EPI_GEGLU, "linear (q8_0): epilogue %d is unknown", epilogue);
+    TS_REQUIRE(out_dtype == TS_BF16 || out_dtype == TS_F32, "linear (q8_0): out dtype %d is unknown", out_dtype);
+    TS_REQUIRE(epilogue != TS_EPI_ADD || a0 != nullptr, "linear (q8_0): the add epilogue needs its operand");
+    return linear_q8_0(x, w, a0, out, m, n, k, epilogue, scale, out_dtype, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
 int ts_wait_runs_out(uint64_t wait_ns, void *stream) {
     TS_REQUIRE(wait_ns > 0 && wait_ns <= 1000000000ull, "wait_runs_out: the bound must be within (0, 1 s]");
     return wait_runs_out(wait_ns, (cudaStream_t)stream);

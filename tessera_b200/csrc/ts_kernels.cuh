@@ -127,6 +127,15 @@ int picked(const void *x, const void *w, const uint32_t *ids, float *out, uint32
 int moe_mix(const float *y_picks, const float *gates, const float *add, float *out, uint32_t rows, uint32_t top,
             uint32_t width, cudaStream_t stream);
 
+// Decode-sized linear over Q8_0 weights (engine/ir/mem/src/block.rs:259-260) and the form's host-side packer.
+bool q8_0_supports(uint32_t m, uint32_t n, uint32_t k);
+size_t q8_0_workspace_bytes(uint32_t m, uint32_t n, uint32_t k);
+int linear_q8_0(const void *x, const void *w, const void *a0, void *out, uint32_t m, uint32_t n, uint32_t k, int epilogue,
+                float scale, int out_dtype, void *workspace, size_t workspace_bytes, cudaStream_t stream);
+size_t q8_0_bytes(size_t elements);
+void q8_0_pack(const float *data, size_t elements, uint8_t *out);
+void q8_0_unpack(const uint8_t *bytes, size_t elements, float *out);
+
 // The layer stack of a decode step (<= 64 rows, one per slot, head width 128) as one persistent kernel.
 struct StepKernel;
 struct StepKernelShape {

@@ -80,6 +80,33 @@ def router_scores(x, router):
     return linear(x, router, out_dtype=torch.float32, path="ordered")
 
 
+def q8_0_pack(w: torch.Tensor) -> torch.Tensor:
+    """A float matrix [n, k] (k a multiple of 32) in the reference's Q8_0 block form: uint8 [n, k / 32 * 34], on the
+    device of `w` (packed on the host by ts_q8_0_pack)."""
+    import numpy as np
+    n, k = w.shape
+    assert k % 32 == 0
+    data = np.ascontiguousarray(w.detach().float().cpu().numpy())
+    out = np.zeros(lib.ts_q8_0_bytes(data.size), np.uint8)
+    check(lib.ts_q8_0_pack(data.ctypes.data_as(C.c_void_p), data.size, out.ctypes.data_as(C.c_void_p)))
+    return torch.from_numpy(out.reshape(n, k // 32 * 34)).to(w.device)
+
+
+def linear_q8_0(x, w_q8, a0=None, *, epilogue="none", scale=1.0, out_dtype=torch.bfloat16, out=None):
+    """out[m, n] = sum_k x[m, k] w[n, k] over Q8_0 weights (uint8 [n, k / 32 * 34]): ts_linear_q8_0."""
+    m, k = x.shape
+    n = w_q8.shape[0]
+    assert w_q8.shape[1] == k // 32 * 34
+    out_n = n // 2 if epilogue in ("swiglu", "geglu") else n
+    if out is None:
+        out = torch.empty((m, out_n), dtype=out_dtype, device=x.device)
+    nbytes = lib.ts_linear_q8_0_workspace_bytes(m, n, k)
+    ws = workspace(nbytes, x.device)
+    check(lib.ts_linear_q8_0(_ptr(x), _ptr(w_q8), _ptr(a0), _ptr(out), m, n, k, EPILOGUE[epilogue], scale, _dtype_code(out_dtype),
+                             _ptr(ws), nbytes, _stream()))
+    return out
+
+
 def linear_fused(x, w, a0=None, *, epilogue="none", scale=1.0, out_dtype=torch.bfloat16, out=None, rows=None,
                  next_gain=None):
     """ts_linear_fused_bf16.  rows = (partial sums of squares f32 [m, parts], eps): x is bf16(row * gain) and the
