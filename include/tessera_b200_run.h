@@ -63,7 +63,9 @@ int ts_decoder_copy_pages(ts_decoder *dec, const ts_kv_copy *copies, uint32_t n_
  * returns the greedy token of each row listed in `out_rows` (n_out indices into the launch's rows;
  * NULL = every row) in `out_ids` (host).  Synchronises the stream before returning, like
  * Run::submit (run.rs:140-141).  Rows are validated on the host first: a slot, position or token
- * out of range returns TS_ERR_BAD_INPUT and launches nothing. */
+ * out of range returns TS_ERR_BAD_INPUT and launches nothing.  The launch itself carries the next power of two
+ * of rows (copies of the last row, which rewrite that row's kept K and V with the same values), unless the rows
+ * are whole prompts from position 0, which run at their exact size. */
 int ts_decoder_step(ts_decoder *dec, const uint32_t *tokens, const uint32_t *slots, const uint32_t *positions,
                     uint32_t rows, const uint32_t *out_rows, uint32_t n_out, uint32_t *out_ids, void *stream);
 
@@ -82,6 +84,9 @@ int ts_decoder_read_logits(ts_decoder *dec, float *out, uint32_t n_out, void *st
  * have been replayed from a captured graph so far. */
 uint32_t ts_decoder_launches_per_step(ts_decoder *dec, uint32_t rows, uint32_t keys);
 uint64_t ts_decoder_graph_replays(ts_decoder *dec);
+/* Graphs captured so far.  A launch's rows (and wanted rows) round up to a power of two, the last row filling out,
+ * as the reference sizes a launch (engine/engine/src/lib.rs:166-200), so one graph serves a bucket of row counts. */
+uint32_t ts_decoder_graphs(ts_decoder *dec);
 
 /* Captures, without running them, the graphs of a decode step of `rows` rows (one per slot, one id out per row)
  * for every context bucket up to the plan's context, with and without on-device feedback: a serving loop then

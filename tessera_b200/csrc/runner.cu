@@ -593,16 +593,11 @@ int ts_decoder_step(ts_decoder *d, const uint32_t *tokens, const uint32_t *slots
     cudaStream_t s = stream_of(d, stream);
     const size_t R = c.max_rows;
     uint32_t *st = d->stage;
+    const uint32_t given_rows = rows, given_out = n_out;
     memcpy(st, tokens, rows * 4);
     memcpy(st + R, slots, rows * 4);
     memcpy(st + 2 * R, positions, rows * 4);
-    TS_CUDA(cudaMemcpyAsync(d->tokens, st, rows * 4, cudaMemcpyHostToDevice, s));
-    TS_CUDA(cudaMemcpyAsync(d->slots, st + R, rows * 4, cudaMemcpyHostToDevice, s));
-    TS_CUDA(cudaMemcpyAsync(d->positions, st + 2 * R, rows * 4, cudaMemcpyHostToDevice, s));
-    if (out_rows) {
-        memcpy(st + 3 * R, out_rows, n_out * 4);
-        TS_CUDA(cudaMemcpyAsync(d->out_rows, st + 3 * R, n_out * 4, cudaMemcpyHostToDevice, s));
-    }
+    if (out_rows) memcpy(st + 3 * R, out_rows, n_out * 4);
     // Do all rows sit in slots of their own (a decode step), or does a slot take several (a prefill)?
     bool distinct = true;
     {
@@ -650,6 +645,33 @@ int ts_decoder_step(ts_decoder *d, const uint32_t *tokens, const uint32_t *slots
         }
     }
     const uint32_t keys = keys_bucket(d, furthest);
+    // Rows and wanted rows round up to a power of two, the last row (and the last wanted row) filling out, as the
+    // reference sizes a launch (engine/engine/src/lib.rs:166-200): a plan, and here a captured graph, then exists per
+    // bucket instead of per row count.  The copies rewrite their row's kept K and V with the same values.  Whole
+    // prompts (the prefill kernel over packed rows) keep their exact size.
+    if (d->fresh_seqs == 0) {
+        auto pow2 = [](uint32_t v) {
+            uint32_t p = 1;
+            while (p < v) p <<= 1;
+            return p;
+        };
+        const uint32_t filled = pow2(rows), wanted = out_rows ? pow2(n_out) : filled;
+        if (filled <= c.max_rows && wanted <= d->max_out) {
+            for (uint32_t r = rows; r < filled; r++) {
+                st[r] = st[rows - 1];
+                st[R + r] = st[R + rows - 1];
+                st[2 * R + r] = st[2 * R + rows - 1];
+            }
+            if (out_rows)
+                for (uint32_t i = n_out; i < wanted; i++) st[3 * R + i] = st[3 * R + n_out - 1];
+            rows = filled;
+            n_out = wanted;
+        }
+    }
+    TS_CUDA(cudaMemcpyAsync(d->tokens, st, rows * 4, cudaMemcpyHostToDevice, s));
+    TS_CUDA(cudaMemcpyAsync(d->slots, st + R, rows * 4, cudaMemcpyHostToDevice, s));
+    TS_CUDA(cudaMemcpyAsync(d->positions, st + 2 * R, rows * 4, cudaMemcpyHostToDevice, s));
+    if (out_rows) TS_CUDA(cudaMemcpyAsync(d->out_rows, st + 3 * R, n_out * 4, cudaMemcpyHostToDevice, s));
     int rc;
     if (d->fresh_seqs > 0) {
         // one-off shapes: not worth a captured graph
@@ -664,11 +686,12 @@ int ts_decoder_step(ts_decoder *d, const uint32_t *tokens, const uint32_t *slots
     d->last_rows = rows;
     d->last_out = n_out;
     d->last_keys = furthest;
-    d->host_positions.assign(positions, positions + rows);
+    d->host_positions.assign(st + 2 * R, st + 2 * R + rows);
+    (void)given_rows;
     if (out_ids) {
-        TS_CUDA(cudaMemcpyAsync(st + 4 * R, d->ids, n_out * 4, cudaMemcpyDeviceToHost, s));
+        TS_CUDA(cudaMemcpyAsync(st + 4 * R, d->ids, given_out * 4, cudaMemcpyDeviceToHost, s));
         TS_CUDA(cudaStreamSynchronize(s));
-        memcpy(out_ids, st + 4 * R, n_out * 4);
+        memcpy(out_ids, st + 4 * R, given_out * 4);
     } else {
         TS_CUDA(cudaStreamSynchronize(s));
     }
@@ -737,6 +760,8 @@ uint32_t ts_decoder_launches_per_step(ts_decoder *d, uint32_t rows, uint32_t key
 
 uint64_t ts_decoder_graph_replays(ts_decoder *d) { return d ? d->replays : 0; }
 
+uint32_t ts_decoder_graphs(ts_decoder *d) { return d ? (uint32_t)d->graphs.size() : 0; }
+
 int ts_decoder_get_config(const ts_decoder *d, ts_decoder_config *out) {
     TS_REQUIRE(d && out, "decoder config: NULL argument");
     *out = d->c;
@@ -748,6 +773,11 @@ int ts_decoder_prepare(ts_decoder *d, uint32_t rows, void *stream) {
     TS_REQUIRE(rows >= 1 && rows <= d->c.max_rows && rows <= d->max_out, "decoder prepare: %u rows, the plan takes 1..%u",
                rows, d->c.max_rows < d->max_out ? d->c.max_rows : d->max_out);
     cudaStream_t s = stream_of(d, stream);
+    {   // the bucket a launch of `rows` rows runs in (see ts_decoder_step)
+        uint32_t p = 1;
+        while (p < rows) p <<= 1;
+        if (p <= d->c.max_rows && p <= d->max_out) rows = p;
+    }
     for (uint32_t keys = 128;; keys += 128) {
         const uint32_t k = keys > d->c.context ? d->c.context : keys;
         for (int feedback = 0; feedback < 2; feedback++) {

@@ -29,6 +29,7 @@ RUN_SIGNATURES = {
     "ts_decoder_read_logits": (i32, [vp, vp, u32, vp]),
     "ts_decoder_launches_per_step": (u32, [vp, u32, u32]),
     "ts_decoder_graph_replays": (C.c_uint64, [vp]),
+    "ts_decoder_graphs": (u32, [vp]),
     "ts_decoder_prepare": (i32, [vp, u32, vp]),
     "ts_decoder_profile": (i32, [vp, u32, vp]),
     "ts_decoder_take_profile": (i32, [vp, C.c_char_p, sz]),
@@ -134,6 +135,10 @@ class Decoder:
         """Chooses between the one persistent kernel per decode step and one launch per product; returns whether
         the persistent kernel exists for this decoder's shapes."""
         return bool(lib.ts_decoder_use_step_kernel(self._h, int(on)))
+
+    def graphs(self) -> int:
+        """Graphs captured so far (one per bucket of row counts, context bucket and kind of launch)."""
+        return int(lib.ts_decoder_graphs(self._h))
 
     def graph_replays(self) -> int:
         return int(lib.ts_decoder_graph_replays(self._h))

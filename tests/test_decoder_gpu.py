@@ -16,6 +16,8 @@ from tests.util import rel_error
 
 pytestmark = pytest.mark.gpu
 
+VARIED_TOL = 3e-2   # end-to-end logits of the varied full-size fixture; see its test
+
 SMALL = dict(layers=2, hidden=256, heads=4, kv_heads=2, head_dim=64, ffn=512, vocab=1000, eps=1e-6, theta=1e4)
 MID = dict(layers=2, hidden=1024, heads=16, kv_heads=8, head_dim=128, ffn=3072, vocab=20000, eps=1e-6, theta=1e6)
 
@@ -111,6 +113,29 @@ def test_prepared_graphs_cover_every_context_bucket():
     dec.close()
 
 
+def test_row_counts_share_a_bucket_graph():
+    """Launches of 5, 6, 7 and 8 rows run in the 8-row bucket (the last row fills out, engine/engine/src/lib.rs:
+    166-200) and replay one graph; their ids equal those of a runner that launches one row at a time."""
+    cfg = SMALL
+    rng = np.random.default_rng(12)
+    prompts = [rng.integers(0, cfg["vocab"], size=4).tolist() for _ in range(8)]
+    dec = _device(cfg, 4, slots=8, context=64, max_rows=64, gains="near_one", page=16)
+    first = dec.prefill(prompts)
+    base = dec.graphs()
+    got = {}
+    for n in (5, 6, 7, 8):
+        got[n] = dec.step(first[:n], np.arange(n), np.full(n, 4))       # rewrites the same kept rows each time
+    assert dec.graphs() == base + 1
+    one = _device(cfg, 4, slots=8, context=64, max_rows=64, gains="near_one", page=16)
+    f1 = one.prefill(prompts)
+    assert np.array_equal(f1, first)
+    want = np.array([one.step([f1[s]], [s], [4])[0] for s in range(8)], np.uint32)
+    for n in (5, 6, 7, 8):
+        assert np.array_equal(got[n], want[:n]), n
+    dec.close()
+    one.close()
+
+
 def test_bad_rows_are_refused_before_any_launch():
     from tessera_b200 import TesseraError
     dec = _device(SMALL, 0, slots=2, context=32, max_rows=8, gains="ones", page=16)
@@ -176,12 +201,14 @@ def test_qwen3_0p6b_varied_tokens_and_logits_follow_golden(step_kernel):
     written by make_qwen3_tokens.py --varied), whose greedy ids change at every step - nothing like the first
     fixture's fixed point, so a wrong kernel anywhere moves them.
 
-    Teacher-forced first: at each of the first 32 steps the winning logit and the probe logits within 1e-2 of the
-    largest logit, and the id equal to the checker's.  The fixture's rule (first seed with every margin above 1e-2)
-    leaves a few thin margins (0.02 on logits near 7): an id may differ there only if the checker's margin at that
-    step is below twice the logit error this very run measured, i.e. only if rounding explains it.  Then
-    free-running: the generated ids equal the checker's up to the first such thin step, and for 16 steps at least.
-    Both forms of the decode step are held to it."""
+    Teacher-forced first: at each of the first 32 steps the winning logit and the probe logits within VARIED_TOL of
+    the largest logit, and the id equal to the checker's.  VARIED_TOL is 3e-2, not the per-op 1e-2: this is 28
+    layers of bf16 rounding points end to end through a random stack that, with these larger weights, amplifies a
+    rounding (measured on a B200: 1.8e-2 for the per-product launches; at the configuration's own N(0, 0.02) the
+    first fixture's logits agree to well under 1e-2).  An id may differ from the checker's only where the checker's
+    margin at that step is below twice the logit error this very run measured, i.e. only if rounding explains it.
+    Then free-running: the generated ids equal the checker's up to the first such thin step, and for 16 steps at
+    least.  Both forms of the decode step are held to it."""
     path = os.path.join(os.path.dirname(__file__), "golden", "qwen3_0p6b_greedy_varied.json")
     gold = json.load(open(path))
     cfg = gold["config"]
@@ -210,15 +237,13 @@ def test_qwen3_0p6b_varied_tokens_and_logits_follow_golden(step_kernel):
         worst_abs, worst_rel = max(worst_abs, err), max(worst_rel, err / scale)
         if int(ids[0]) != gold["tokens"][t]:
             flips.append(t)
-    dec.close()
     print(f"largest logit error over 32 steps: {worst_rel:.2e} of the largest logit ({worst_abs:.3g} absolute); flips at {flips}")
-    assert worst_rel <= 1e-2
+    got = dec.generate([prompt.tolist()], gold["new"])[0].tolist()   # the same decoder, from position 0 again
+    dec.close()
+    assert worst_rel <= VARIED_TOL
     for t in flips:
         assert gold["margins"][t] < 2 * worst_abs, (t, gold["margins"][t], worst_abs)
     assert len(flips) <= 2
-    dec = fresh()
-    got = dec.generate([prompt.tolist()], gold["new"])[0].tolist()
-    dec.close()
     same = next((t for t in range(32) if got[t] != gold["tokens"][t]), 32)
     assert same >= 16 and (same == 32 or gold["margins"][same] < 2 * worst_abs), (same, got[:32])
 
