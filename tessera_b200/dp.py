@@ -33,17 +33,21 @@ def max_over_ranks(seconds: float, device=None, group=None) -> float:
     return float(t.item())
 
 
-def gather_rows(local: torch.Tensor, indices: list[int], total: int, group=None) -> torch.Tensor | None:
-    """Rank 0 receives every rank's rows (e.g. embeddings or token ids) placed at their unit indices."""
+def gather_rows(local: torch.Tensor, indices: list[int], total: int, group=None, width: int | None = None) -> torch.Tensor | None:
+    """Rank 0 receives every rank's rows (e.g. embeddings or token ids) placed at their unit indices.
+
+    `width`: the largest number of rows any rank holds, when the caller already knows it (a loop that gathers
+    every step asks the ranks once, outside the loop, and the gather then never touches the host)."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     if world == 1:
         out = local.new_zeros((total,) + tuple(local.shape[1:]))
         out[torch.tensor(indices, dtype=torch.long, device=local.device)] = local
         return out
     idx = torch.tensor(indices, dtype=torch.long, device=local.device)
-    counts = [None] * world
-    dist.all_gather_object(counts, int(idx.numel()), group=group)
-    width = max(counts)
+    if width is None:
+        counts = [None] * world
+        dist.all_gather_object(counts, int(idx.numel()), group=group)
+        width = max(counts)
     pad_rows = local.new_zeros((width,) + tuple(local.shape[1:]))
     pad_rows[: idx.numel()] = local
     pad_idx = idx.new_full((width,), -1)

@@ -308,10 +308,12 @@ def test_prefix_reuse_through_the_page_pool():
 @pytest.mark.parametrize("native", [False, True])
 @pytest.mark.parametrize("page", [16, 0])
 def test_sessions_continue_kept_rows(page, native):
-    """tessera_b200/sessions.py on the device: answers that continue rows an earlier answer left (paged: borrowed
+    """The session loop on the device (the library's, ts_sessions_* calling ts_decoder_step directly; and the tests'
+    plain Python statement of it driving the same decoder): answers that continue rows an earlier answer left (paged: borrowed
     whole pages; dense: the adopted slot) equal the answers of feeding every prompt whole (the reference's
     kept_rows_resume and paged_slots_share, engine/engine/tests/engine_test.rs:331-385)."""
-    from tessera_b200.sessions import NativeSessions, Sessions
+    from tessera_b200.sessions import Sessions
+    from tests.sessions_model import Sessions as Model
     cfg, context, new = SMALL, 64, 3
     rng = np.random.default_rng(31)
     base = rng.integers(0, cfg["vocab"], size=24).tolist()
@@ -322,7 +324,7 @@ def test_sessions_continue_kept_rows(page, native):
         want.append(fresh.generate([p], new)[0].tolist())
         fresh.close()
     dec = _device(cfg, 9, slots=2, context=context, max_rows=32, gains="near_one", page=page)
-    s = (NativeSessions if native else Sessions)(dec)   # the loop in the library (ts_sessions_*), or in Python
+    s = (Sessions if native else Model)(dec)   # the loop in the library (ts_sessions_*), or the tests' Python model
     got = s.generate(prompts[:1], new) + s.generate(prompts[1:], new)   # the later three find the first one's rows
     t = s.totals()
     del s

@@ -147,12 +147,13 @@ def test_launch_by_name_with_the_reference_argument_order():
     kept = ops.Kept("dense", context, None, slots * context)
     kr = from_bits(normal_bf16(rng, (slots * context, kv_heads * width)))
     vr = from_bits(normal_bf16(rng, (slots * context, kv_heads * width)))
-    q = from_bits(normal_bf16(rng, (2, heads * width)))
+    q = from_bits(normal_bf16(rng, (2, heads * width), 0.1))
     sl, ps = dev_u32([2, 0]), dev_u32([17, 39])
     o = torch.empty_like(q)
-    rules.launch("attend_rows", [q, kr, vr, o, sl, ps, 2, context, heads, kv_heads, width, 0xFFFFFFFF], kept=kept, scale=0.1)
+    # by name the queries arrive already scaled, as in the reference (its scale is a launch of its own)
+    rules.launch("attend_rows", [q, kr, vr, o, sl, ps, 2, context, heads, kv_heads, width, 0xFFFFFFFF], kept=kept)
     want = ops.attend_rows(q.reshape(2, heads, width), kr.reshape(-1, kv_heads, width), vr.reshape(-1, kv_heads, width), sl, ps,
-                           kept, context, scale=0.1)
+                           kept, context, scale=1.0)
     assert torch.equal(o.reshape(2, heads, width), want)
     new = from_bits(normal_bf16(rng, (2, kv_heads * width)))
     rules.launch("scatter", [new, sl, ps, kr, 2, kv_heads * width], kept=kept)

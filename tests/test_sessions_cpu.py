@@ -1,9 +1,10 @@
-"""The host loop around the decode step (tessera_b200/sessions.py) against a stand-in decoder that keeps one token
+"""The host loop around the decode step (ts_sessions_*, through tessera_b200/sessions.py) against a stand-in decoder that keeps one token
 per kept row, reads a row's whole past through the page table and answers with a hash of it: an answer is right only
 if every earlier row of the sequence is where the table says, whoever wrote it.  No GPU."""
 import numpy as np
 import pytest
 
+from tessera_b200 import TesseraError
 from tessera_b200.sessions import Sessions
 
 
@@ -14,6 +15,7 @@ class KeptTokens:
         self.rows = np.full(slots * (self.pages * page if page else context), -1, np.int64)
         self.table = np.arange(slots * self.pages, dtype=np.uint32)
         self.launches = []
+        self.fed_slots = []
 
     def set_table(self, table):
         self.table = np.array(table, np.uint32)
@@ -26,6 +28,7 @@ class KeptTokens:
     def step(self, tokens, slots, positions, out_rows=None):
         assert 1 <= len(tokens) <= self.max_rows
         self.launches.append(len(tokens))
+        self.fed_slots.append(list(slots))
         for t, s, p in zip(tokens, slots, positions):   # append before anything attends (scatter.rs: K, V first)
             self.rows[self._row(s, p)] = t
         out = []
@@ -84,9 +87,9 @@ def test_reuse_spares_rows():
 
 def test_prompts_that_cannot_fit_are_refused():
     s = Sessions(KeptTokens(slots=1, context=16, max_rows=16, page=0))
-    with pytest.raises(ValueError):
+    with pytest.raises(TesseraError):
         s.generate([list(range(15))], 4)
-    with pytest.raises(ValueError):
+    with pytest.raises(TesseraError):
         s.generate([[]], 1)
 
 
@@ -118,9 +121,23 @@ def test_step_counts_of_the_reference_cases():
     assert got == [alone(base[:18] + [1, 2], 3), alone(base[:17] + [5], 3)]
 
 
-def test_fair_feeds_decodes_first_then_prompts_in_turn():
+def test_first_step_feeds_decodes_first_then_prompts_in_turn():
+    # through the library's loop: a one-token prompt is already decoding (its only row makes a token), prompts of
+    # ten and three rows share what is left of a six-row budget a token each in turn: b c b c b
+    dec = KeptTokens(slots=3, context=64, max_rows=64, page=0)
+    Sessions(dec, reuse=False, budget=6).generate([list(range(10)), [7], [1, 2, 3]], 2)
+    first = dec.fed_slots[0]
+    assert len(first) == 6 and sorted(first.count(s) for s in set(first)) == [1, 2, 3]
+    # rows of a sequence sit side by side in the launch
+    assert all(first[i] == first[i + 1] or first[i] not in first[i + 1:] for i in range(len(first) - 1))
+    tight = KeptTokens(slots=3, context=64, max_rows=4, page=0)      # the launch itself holds four rows
+    Sessions(tight, reuse=False, budget=64).generate([list(range(10)), [7], [1, 2, 3]], 2)
+    assert max(tight.launches) <= 4 and len(tight.fed_slots[0]) == 4
+
+
+def test_fair_of_the_model_feeds_decodes_first_then_prompts_in_turn():
     from collections import deque
-    from tessera_b200.sessions import _Seq, fair
+    from tests.sessions_model import _Seq, fair
     a = _Seq(0, 0, deque([7]), 9, [], 3)                 # decoding
     b = _Seq(1, 1, deque(range(10)), 0, [], 3)           # ten prompt rows
     c = _Seq(2, 2, deque(range(3)), 0, [], 3)            # three
@@ -152,7 +169,7 @@ def test_random_rounds_of_related_prompts(seed):
             prompts.append(stem[:cut] + tail)
         new = int(rng.integers(1, 5))
         assert s.generate(prompts, new) == [alone_in(context, p, new) for p in prompts]
-        assert s.kept.consistent()
+        assert s.consistent()
         asked += len(prompts)
     t = s.totals()
     assert t.hits + t.misses == asked and t.pool.live_runs == 0
@@ -163,16 +180,16 @@ def alone_in(context, prompt, new):
 
 
 @pytest.mark.parametrize("seed", range(4))
-def test_the_library_loop_equals_the_python_loop(seed):
+def test_the_library_loop_equals_the_python_model(seed):
     # ts_sessions_* (csrc/sessions.cu) driven through callbacks by the stand-in decoder: the same answers, the same
-    # launches row for row, the same steps and totals as tessera_b200.sessions.Sessions
-    from tessera_b200.sessions import NativeSessions
+    # launches row for row, the same steps and totals as the plain Python statement of the loop in tests/sessions_model.py
+    from tests.sessions_model import Sessions as Model
     rng = np.random.default_rng(200 + seed)
     page = int(rng.choice([0, 16, 64]))
     slots, context, rows = int(rng.integers(1, 4)), 128, int(rng.choice([8, 32, 128]))
     budget = int(rng.choice([1, 5, 128]))
     a, b = KeptTokens(slots, context, rows, page), KeptTokens(slots, context, rows, page)
-    py, lib = Sessions(a, budget=budget), NativeSessions(b, budget=budget)
+    py, lib = Model(a, budget=budget), Sessions(b, budget=budget)
     stems = [rng.integers(0, 900, size=100).tolist() for _ in range(3)]
     for _ in range(6):
         prompts = [stems[int(rng.integers(0, 3))][: int(rng.integers(1, 100))] + rng.integers(0, 900, size=int(rng.integers(0, 6))).tolist()
@@ -180,15 +197,13 @@ def test_the_library_loop_equals_the_python_loop(seed):
         new = int(rng.integers(1, 5))
         assert lib.generate(prompts, new) == py.generate(prompts, new)
         assert lib.consistent()
-    assert a.launches == b.launches and lib.steps == py.steps
+    assert a.launches == b.launches and a.fed_slots == b.fed_slots and lib.steps == py.steps
     tp, tl = py.totals(), lib.totals()
     assert (tp.hits, tp.misses, tp.pool.kept_runs) == (tl.hits, tl.misses, tl.pool.kept_runs)
 
 
 def test_the_library_loop_refuses_and_reports():
-    from tessera_b200 import TesseraError
-    from tessera_b200.sessions import NativeSessions
-    s = NativeSessions(KeptTokens(1, 16, 16, 0))
+    s = Sessions(KeptTokens(1, 16, 16, 0))
     with pytest.raises(TesseraError):
         s.generate([list(range(15))], 4)           # does not fit the context with its answer
     with pytest.raises(TesseraError):
@@ -199,7 +214,7 @@ def test_the_library_loop_refuses_and_reports():
             raise RuntimeError("the device fell over")
 
     with pytest.raises(RuntimeError, match="fell over"):
-        NativeSessions(Broken(1, 16, 16, 0)).generate([[1, 2, 3]], 2)
+        Sessions(Broken(1, 16, 16, 0)).generate([[1, 2, 3]], 2)
 
 
 @pytest.mark.parametrize("page", [0, 16])
@@ -207,8 +222,6 @@ def test_a_failed_step_gives_its_slots_back(page):
     # A step that fails once must not strand the active sequences' slots and pages: the same sessions then answer
     # the next request, with the answers of a decoder that never failed (the reference retires a sequence on every
     # exit path: engine/engine/src/schedule.rs finish / retire).
-    from tessera_b200.sessions import NativeSessions
-
     class FailsOnce(KeptTokens):
         armed = True
 
@@ -219,7 +232,7 @@ def test_a_failed_step_gives_its_slots_back(page):
             return super().step(*a, **k)
 
     prompts = [[5, 6, 7, 8], [9, 10], [11, 12, 13]]
-    s = NativeSessions(FailsOnce(2, 64, 16, page), reuse=False)
+    s = Sessions(FailsOnce(2, 64, 16, page), reuse=False)
     with pytest.raises(RuntimeError, match="one bad launch"):
         s.generate(prompts, 3)
     assert s.consistent()
