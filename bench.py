@@ -58,7 +58,10 @@ NCU_TRAFFIC_RATIO = {"attend_rows": 50.816 / 50.856, "linear_unembed": 340.02 / 
                      # one capture (the q,k,v shape) stands for the four streamed linears of a layer: same kernel,
                      # traffic = the weights once + x; the output stays in L2
                      "linear_qkv": 8.592 / 9.044, "linear_o": 8.592 / 9.044, "linear_gate_up": 8.592 / 9.044,
-                     "linear_down": 8.592 / 9.044}
+                     "linear_down": 8.592 / 9.044,
+                     # the long-context paged attention kernel (64 rows x 4096 keys), the one-row skinny linear and the
+                     # grouped expert kernel (one rank of eight: 16 experts' weights a launch)
+                     "attend_rows_long": 1081.5 / 1074.27, "linear_skinny": 12.62 / 12.59, "moe_grouped": 0.96}
 
 
 def parse_args():
@@ -644,6 +647,9 @@ def run_attn(args):
         print(json.dumps({"workload": "attention", "case": f"paged decode, 64 sequences of 512..8192 positions, {page}-row pages",
                           "us_per_launch": round(us, 2), "GBs": round(byts / us / 1e3, 1), "bound": "hbm",
                           "frac": round(byts / us / 1e3 / hbm, 4), "peak_kind": f"of {hbm_kind} copy rate",
+                          "traffic": round(NCU_TRAFFIC_RATIO["attend_rows_long"] * byts),
+                          "traffic_source": "dram bytes / algorithmic bytes of the ncu capture of the same kernel at 64 x 4096 "
+                                            "keys, times this launch's algorithmic bytes",
                           "positions_total": int(lengths.sum()), "launches": 20, "status": ops.device_status()}), flush=True)
         del k, v
 
@@ -753,7 +759,10 @@ def run_moe(args, rank, world, local_rank):
                 "d2h_bytes_per_step": rows * cfg["hidden"] * 4, "ms_per_step": e2e_seconds / K * 1e3},
         "roofline": {"kernel": "whole step (expert, dense and kept-row bytes of one rank)", "bound": "hbm",
                      "achieved": step_bytes / (seconds / K) / 1e9, "peak": peak, "unit": "GB/s",
-                     "frac": step_bytes / (seconds / K) / 1e9 / peak, "peak_kind": f"of {kind}", "traffic": None},
+                     "frac": step_bytes / (seconds / K) / 1e9 / peak, "peak_kind": f"of {kind}", "traffic": None,
+                     "expert_kernel_traffic": NCU_TRAFFIC_RATIO["moe_grouped"] * expert_bytes,
+                     "expert_kernel_traffic_source": "dram bytes / expert weight bytes of the ncu capture of moe_grouped_kernel "
+                                                     "(one rank of eight), times this rank's expert weight bytes per step"},
         "ep_check": check, "clocks": sampler.summary()})
 
 

@@ -66,9 +66,6 @@ struct StreamParams {
     float *ss_out;
     uint16_t *xs_out;
     const float *xs_gain;
-    // Hint (pf_bytes != 0): the next launch's weights; every block asks the L2 for its slice of them.
-    const unsigned char *pf;
-    uint64_t pf_bytes;
 };
 
 struct StreamSmem {
@@ -222,17 +219,6 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
         // touches the stage barriers before the block-wide sync: the first stages go out now, while
         // the other warps are still setting up.
         for (uint32_t it = 0; it < early; it++) load_weights(it);
-        if (p.pf_bytes) {
-            // The launch after this one finds its weights in the L2 instead of waiting on HBM behind its own ramp.
-            const uint64_t blocks = (uint64_t)gridDim.x * gridDim.y, id = (uint64_t)blockIdx.y * gridDim.x + blockIdx.x;
-            const uint64_t per = (((p.pf_bytes + blocks - 1) / blocks) + 15) & ~15ull;
-            uint64_t at = id * per;
-            const uint64_t end = at + per < p.pf_bytes ? at + per : p.pf_bytes;
-            for (; at < end; at += 16384) {
-                const uint32_t nbytes = (uint32_t)(end - at < 16384 ? end - at : 16384);
-                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.pf + at), "r"(nbytes) : "memory");
-            }
-        }
         STAMP(1);
     }
     if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
@@ -685,10 +671,6 @@ int linear_stream(const void *x, const void *w, const void *a0, void *out, uint3
         p.ss_out = fused->ss_out;
         p.xs_out = (uint16_t *)fused->xs_out;
         p.xs_gain = fused->xs_gain;
-        if (fused->next_w && fused->next_bytes && fused->next_bytes % 16 == 0 && ((uintptr_t)fused->next_w & 15) == 0) {
-            p.pf = (const unsigned char *)fused->next_w;
-            p.pf_bytes = fused->next_bytes;
-        }
     }
     p.m = m;
     p.n = n;

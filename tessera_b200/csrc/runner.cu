@@ -217,18 +217,9 @@ int enqueue(ts_decoder *d, uint32_t rows, uint32_t keys, uint32_t n_out, bool fe
     const bool fold = ss_parts != 0;
     // x_in: bf16(residual * gain) as the upstream step left it in d->h; next_gain: the gain of the norm
     // that follows this linear's output (NULL: none follows inside the layer stack).
-    static const bool prefetch_next = [] {
-        const char *e = getenv("TS_PREFETCH_NEXT");
-        return e ? atoi(e) != 0 : true;
-    }();
     auto folded = [&](bool scaled_in, const void *xin, const void *w, const void *a0, void *out, uint32_t n, uint32_t k,
-                      int epi, int out_dtype, const float *next_gain, const void *next_w = nullptr,
-                      size_t next_elems = 0) -> int {
+                      int epi, int out_dtype, const float *next_gain) -> int {
         StreamFused f;
-        if (prefetch_next) {
-            f.next_w = next_w;
-            f.next_bytes = next_elems * 2;
-        }
         if (scaled_in) {
             f.row_ss = d->sumsq;
             f.row_parts = ss_parts;
@@ -254,7 +245,7 @@ int enqueue(ts_decoder *d, uint32_t rows, uint32_t keys, uint32_t n_out, bool fe
     for (uint32_t l = 0; l < c.layers && !one_kernel; l++) {
         ts_decoder::Layer &L = d->layers[l];
         if (fold) {
-            STEP("linear_qkv", folded(true, d->h, L.wqkv, nullptr, d->qkv, d->qkv_n, H, TS_EPI_NONE, TS_BF16, nullptr, L.wo, (size_t)H * QW));
+            STEP("linear_qkv", folded(true, d->h, L.wqkv, nullptr, d->qkv, d->qkv_n, H, TS_EPI_NONE, TS_BF16, nullptr));
         } else {
             STEP("rms_norm", rms_norm(d->x, TS_F32, L.ln1, d->h, TS_BF16, rows, H, c.eps, nullptr, s));
             STEP("linear_qkv", linear(d->h, L.wqkv, nullptr, d->qkv, d->qkv_n, H, TS_EPI_NONE, TS_BF16));
@@ -291,12 +282,10 @@ int enqueue(ts_decoder *d, uint32_t rows, uint32_t keys, uint32_t n_out, bool fe
         }
         if (attend_rows_workspace_bytes(rows, keys, c.heads, c.kv_heads, D) > 0) launches++;
         if (fold) {
-            STEP("linear_o", folded(false, d->attn, L.wo, d->x, d->x, H, QW, TS_EPI_ADD, TS_F32, L.ln2, L.wgu, (size_t)2 * c.ffn * H));
-            STEP("linear_gate_up", folded(true, d->h, L.wgu, nullptr, d->act, 2 * c.ffn, H, TS_EPI_SWIGLU, TS_BF16, nullptr, L.wdown,
-                                          (size_t)H * c.ffn));
+            STEP("linear_o", folded(false, d->attn, L.wo, d->x, d->x, H, QW, TS_EPI_ADD, TS_F32, L.ln2));
+            STEP("linear_gate_up", folded(true, d->h, L.wgu, nullptr, d->act, 2 * c.ffn, H, TS_EPI_SWIGLU, TS_BF16, nullptr));
             STEP("linear_down", folded(false, d->act, L.wdown, d->x, d->x, H, c.ffn, TS_EPI_ADD, TS_F32,
-                                       l + 1 < c.layers ? d->layers[l + 1].ln1 : nullptr,
-                                       l + 1 < c.layers ? d->layers[l + 1].wqkv : nullptr, (size_t)d->qkv_n * H));
+                                       l + 1 < c.layers ? d->layers[l + 1].ln1 : nullptr));
         } else {
             STEP("linear_o", linear(d->attn, L.wo, d->x, d->x, H, QW, TS_EPI_ADD, TS_F32));
             STEP("rms_norm", rms_norm(d->x, TS_F32, L.ln2, d->h, TS_BF16, rows, H, c.eps, nullptr, s));

@@ -39,10 +39,6 @@ struct StreamFused {
     float *ss_out = nullptr;
     void *xs_out = nullptr;
     const float *xs_gain = nullptr;
-    // Hint: `next_bytes` bytes at `next_w` (a multiple of 16, 16-byte aligned) are what the launch after this one
-    // streams; the blocks of this launch ask the L2 for them, one slice each, once their own weights are on the way.
-    const void *next_w = nullptr;
-    size_t next_bytes = 0;
 };
 // Parts per row that a linear of this shape leaves in ss_out, or 0 when it cannot.
 uint32_t stream_sumsq_parts(uint32_t m, uint32_t n, uint32_t k, int epilogue);

@@ -40,10 +40,12 @@ def _dtype_code(dtype: torch.dtype) -> int:
 
 
 def workspace(nbytes: int, device) -> torch.Tensor | None:
-    """A caller-owned scratch buffer, grown on demand and reused (one per device)."""
+    """A caller-owned scratch buffer, grown on demand and reused: one per device and stream, so that launches on
+    two streams that may run side by side never share scratch."""
     if nbytes == 0:
         return None
-    key = torch.device(device).index or 0
+    dev = torch.device(device)
+    key = (dev.index or 0, torch.cuda.current_stream(dev).cuda_stream if dev.type == "cuda" else 0)
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < nbytes:
         buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)

@@ -154,7 +154,9 @@ def test_launch_by_name_with_the_reference_argument_order():
     rules.launch("attend_rows", [q, kr, vr, o, sl, ps, 2, context, heads, kv_heads, width, 0xFFFFFFFF], kept=kept)
     want = ops.attend_rows(q.reshape(2, heads, width), kr.reshape(-1, kv_heads, width), vr.reshape(-1, kv_heads, width), sl, ps,
                            kept, context, scale=1.0)
-    assert torch.equal(o.reshape(2, heads, width), want)
+    # the by-name entry does not know how many kept rows the buffers hold, so it may pick another kernel of the
+    # family than the typed call: same values to rounding, not the same bits
+    assert rel_error(widen(o.reshape(2, heads, width)), widen(want)) <= 1e-2
     new = from_bits(normal_bf16(rng, (2, kv_heads * width)))
     rules.launch("scatter", [new, sl, ps, kr, 2, kv_heads * width], kept=kept)
     assert torch.equal(kr[2 * context + 17], new[0]) and torch.equal(kr[39], new[1])
