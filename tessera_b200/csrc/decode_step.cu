@@ -66,6 +66,7 @@ constexpr uint32_t kOwn = kBatch / kCluster;   // batch columns a block owns aft
 constexpr uint32_t kXfer = 128 * kOwn * 4;     // bytes one block sends another per tile: 128 rows x 8 columns f32
 constexpr uint32_t kPrepHeads = 6;             // up to 4 query heads + k + v per item
 constexpr uint32_t kAccStages = 2;
+constexpr uint32_t kMaxItems = 2;              // attention items a worker warp may own in one phase
 
 // The union region: x slice + receive + send buffers in the linear phases, the workers' K,V tile stages in the
 // attention phase.
@@ -79,8 +80,12 @@ struct Smem {
     static_assert(uni_bytes == kWorkers * kKvStages * kKvStage, "the two uses of the union region have the same size");
     static constexpr uint32_t prep = uni + uni_bytes;                    // bf16 [kWorkers][kPrepHeads][128]
     static constexpr uint32_t red = prep + kWorkers * kPrepHeads * 256;  // f32 [kWorkers][kOwn] + inv_s [kOwn]
-    static constexpr uint32_t bars = red + (kWorkers + 1) * kOwn * 4;
-    static constexpr uint32_t n_bars = 2 * kRing + 1 + 2 * kAccStages + 2 + kWorkers * kKvStages + 5;
+    // What the control thread needs to feed a worker's key tiles: per item the kept rows of its 32-key blocks, the
+    // number of blocks and the column of its kv head (written once per step by the worker that owns the item).
+    static constexpr uint32_t ytab = red + (kWorkers + 1) * kOwn * 4;    // u32 [kWorkers][kMaxItems][32]
+    static constexpr uint32_t item_info = ytab + kWorkers * kMaxItems * 32 * 4;  // u32 [kWorkers][kMaxItems][2]: blocks, column
+    static constexpr uint32_t bars = item_info + kWorkers * kMaxItems * 2 * 4;
+    static constexpr uint32_t n_bars = 2 * kRing + 1 + 2 * kAccStages + 2 + 2 * kWorkers * kKvStages + 5;
     static constexpr uint32_t misc = bars + ((n_bars * 8 + 63) / 64) * 64;   // tmem slot, abort flag
     static constexpr uint32_t bytes = misc + 64 + 1024;                  // slack for the 1024-byte alignment
 };
@@ -135,7 +140,7 @@ struct StepParams {
 __device__ unsigned long long g_step_stamps[4][2048];
 #define STEP_STAMP(phase, k)                                                                   \
     do {                                                                                       \
-        const uint32_t c__ = blockIdx.x, i__ = (phase) * 8 + (k);                              \
+        const uint32_t c__ = blockIdx.x, i__ = (phase) * 12 + (k);                              \
         const int s__ = c__ == 0 ? 0 : c__ == 1 ? 1 : c__ == gridDim.x / 2 ? 2 : c__ == gridDim.x - 1 ? 3 : -1; \
         if (s__ >= 0 && i__ < 2048) {                                                          \
             unsigned long long t__;                                                            \
@@ -290,22 +295,6 @@ __device__ __forceinline__ uint32_t swz(uint32_t row, uint32_t c16) {
 
 // ---- worker phases -------------------------------------------------------------------------------------------
 
-// Asks L2 for the kept K and V rows this layer's attention will read (positions below each row's own), a 32-row
-// block per lane: issued while the q,k,v product runs, so that the attention phase's tile copies hit L2 instead of
-// paying HBM latency with two tiles in flight per warp.  The kept rows of earlier positions depend on nothing in
-// this step.
-__device__ __noinline__ void prefetch_kept(const StepParams &p, const LayerDev &L, uint32_t wid, uint32_t lane) {
-    const uint32_t units = p.rows * p.max_blk * 2, row_elems = p.kv_heads * 128;
-    for (uint32_t u = wid + lane * kWorkers * p.blocks; u < units; u += kWorkers * p.blocks * 32) {  // a unit per warp before a second per warp
-        const uint32_t t = u >> 1, blk = t % p.max_blk, row = t / p.max_blk;
-        const uint32_t pos = p.positions[row];
-        if (blk * 32 >= pos) continue;
-        const uint32_t n = min(32u, pos - blk * 32);
-        const uint16_t *at = ((u & 1) ? L.v_rows : L.k_rows) + (size_t)kept_row(p.kept, p.slots[row], blk * 32) * row_elems;
-        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(at), "r"(n * row_elems * 2) : "memory");
-    }
-}
-
 // Embedding rows: x = f32(row), xs = bf16(row * gain), sums of squares per 128 columns.
 __device__ __noinline__ void gather_phase(const StepParams &p, const float *gain, uint32_t wid, uint32_t lane) {
     const uint32_t nch = p.ss_parts, units = p.rows * nch;
@@ -378,35 +367,21 @@ __device__ __forceinline__ void norm_rotate(uint16_t *h, const float (&g)[4], bo
 }
 
 // One (row, kv head) of the decode attention on one warp: q, k, v of the row from the projection (bf16), per-head
-// norm and rotation, append, then flash attention over the slot's kept rows in 32-key tiles the warp fetches for
-// itself by TMA, two tiles ahead.  The products run on warp MMAs with the GRP query heads in rows 0..GRP-1 of
-// the 16-row operand.
+// norm and rotation, append, then flash attention over the slot's kept rows in 32-key tiles.  The block's control
+// thread copies the tiles into the warp's two stages by TMA and keeps them full across items (kv_full: a tile has
+// landed; kv_empty: the warp has read it), so the first tiles of the warp's next item are already on their way
+// while it finishes this one.  The products run on warp MMAs with the GRP query heads in rows 0..GRP-1 of the
+// 16-row operand.
 template <int GRP>
-__device__ __forceinline__ bool attend_item(const StepParams &p, const LayerDev &L, const CUtensorMap *map_k,
-                                            const CUtensorMap *map_v, const ItemCtx &c, const float (&qg)[4],
+__device__ __forceinline__ bool attend_item(const StepParams &p, const LayerDev &L, const ItemCtx &c, const float (&qg)[4],
                                             const float (&kg)[4], bool normed, uint32_t lane, uint8_t *stages,
-                                            uint16_t *prep, uint64_t *kv_full, uint32_t &kv_parity,
-                                            uint32_t &kv_pending, const Bounds &bd, uint32_t y_base, uint32_t stamp_phase) {
+                                            uint16_t *prep, uint64_t *kv_full, uint64_t *kv_empty, uint32_t &kv_parity,
+                                            uint32_t &kv_count, const Bounds &bd, uint32_t stamp_phase) {
     constexpr int WIDTH = 128;
     (void)stamp_phase;
     const uint32_t row = c.row, kvh = c.kvh, slot = c.slot, pos = c.pos;
     const uint32_t head0 = kvh * GRP;
     const uint32_t hi = pos + 1, n_blk = (hi + 31) / 32;
-    const int32_t x = (int32_t)(kvh * WIDTH);
-    auto issue = [&](uint32_t blk) {  // whole warp
-        const uint32_t s = blk % kKvStages;
-        const uint32_t yl = __shfl_sync(0xFFFFFFFFu, c.y_lane, blk & 31);
-        const int32_t y = (int32_t)(y_base + (blk < 32 ? yl : kept_row(p.kept, slot, blk * 32)));  // y_base: the layer's rows in the all-layers tensor
-        if (lane == 0) {
-            uint8_t *dst = stages + s * kKvStage;
-            mbar_expect_tx(&kv_full[s], kKvStage);
-            tma_load_2d(dst, map_k, &kv_full[s], x, y);
-            tma_load_2d(dst + 4096, map_k, &kv_full[s], x + 64, y);
-            tma_load_2d(dst + kKvStage / 2, map_v, &kv_full[s], x, y);
-            tma_load_2d(dst + kKvStage / 2 + 4096, map_v, &kv_full[s], x + 64, y);
-        }
-        kv_pending |= 1u << s;
-    };
     // ---- q heads, k, v of this row: four values a lane and head, asked for before the key tiles ----
     uint2 raw[GRP + 2];
 #pragma unroll
@@ -416,8 +391,6 @@ __device__ __forceinline__ bool attend_item(const StepParams &p, const LayerDev 
         raw[u] = __ldcg(reinterpret_cast<const uint2 *>(p.qkv + (size_t)row * p.qkv_n + h * WIDTH + lane * 4));
     }
     if (lane == 0 && stamp_phase) STEP_STAMP(stamp_phase, 4);
-    issue(0);
-    if (n_blk > 1) issue(1);
 #pragma unroll
     for (uint32_t u = 0; u < (uint32_t)GRP + 2; u++) *reinterpret_cast<uint2 *>(prep + u * WIDTH + lane * 4) = raw[u];
     __syncwarp();
@@ -447,12 +420,11 @@ __device__ __forceinline__ bool attend_item(const StepParams &p, const LayerDev 
 #pragma unroll
     for (int n = 0; n < 16; n++) oacc[n][0] = oacc[n][1] = 0.0f;
 
-    for (uint32_t blk = 0; blk < n_blk; blk++) {
-        const uint32_t s = blk % kKvStages;
+    for (uint32_t blk = 0; blk < n_blk; blk++, kv_count++) {
+        const uint32_t s = kv_count % kKvStages;  // the stages carry on from item to item, as the feeder's do
         ok = wait_bar(&kv_full[s], (kv_parity >> s) & 1, bd);
         if (!ok) break;
         kv_parity ^= 1u << s;
-        kv_pending &= ~(1u << s);
         if (lane == 0 && stamp_phase && blk == 0) STEP_STAMP(stamp_phase, 7);
         uint8_t *tile_k = stages + s * kKvStage;
         uint8_t *tile_v = tile_k + kKvStage / 2;
@@ -529,7 +501,7 @@ __device__ __forceinline__ bool attend_item(const StepParams &p, const LayerDev 
         // the stage is free once every lane has read it; the patches above were generic-proxy writes
         fence_async_shared();
         __syncwarp();
-        if (blk + kKvStages < n_blk) issue(blk + kKvStages);
+        if (lane == 0) mbar_arrive(&kv_empty[s]);
     }
     if (ok) {
         l_row += __shfl_xor_sync(0xFFFFFFFFu, l_row, 1);
@@ -565,12 +537,15 @@ __global__ void __launch_bounds__(kThreads, 1) decode_layers_kernel(const __grid
     uint64_t *x_full = ring_empty + kRing;
     uint64_t *acc_full = x_full + 1, *acc_empty = acc_full + kAccStages;
     uint64_t *workers_done = acc_empty + kAccStages, *phase_go = workers_done + 1;
-    uint64_t *kv_full = phase_go + 1;  // [kWorkers][kKvStages]
-    uint64_t *send_full = kv_full + kWorkers * kKvStages;  // the four warps have staged their partials
+    uint64_t *kv_full = phase_go + 1;  // [kWorkers][kKvStages]: a key tile has landed
+    uint64_t *kv_empty = kv_full + kWorkers * kKvStages;   // [kWorkers][kKvStages]: its warp has read it
+    uint64_t *send_full = kv_empty + kWorkers * kKvStages;  // the four warps have staged their partials
     uint64_t *recv_full = send_full + 1;                   // the eight blocks' partials of my columns have landed
     uint64_t *peers_free = recv_full + 1;                  // every block of the cluster has read its receive buffer
     uint64_t *red_full = peers_free + 1;                   // the four warps' sums of squares are in shared memory
     uint64_t *inv_full = red_full + 1;                     // inv_s is written
+    uint32_t *ytab = reinterpret_cast<uint32_t *>(smem + Smem::ytab);            // [kWorkers][kMaxItems][32]
+    uint32_t *item_info = reinterpret_cast<uint32_t *>(smem + Smem::item_info);  // [kWorkers][kMaxItems][2]
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + Smem::misc);
     volatile uint32_t *abort_s = tmem_slot + 1;
     const Bounds bd = {abort_s, p.sync + 1, p.wait_ns};
@@ -587,7 +562,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_layers_kernel(const __grid
         }
         mbar_init(workers_done, kWorkers);
         mbar_init(phase_go, 1);
-        for (uint32_t s = 0; s < kWorkers * kKvStages; s++) mbar_init(&kv_full[s], 1);
+        for (uint32_t s = 0; s < kWorkers * kKvStages; s++) {
+            mbar_init(&kv_full[s], 1);
+            mbar_init(&kv_empty[s], 1);
+        }
         mbar_init(send_full, kWorkers);
         mbar_init(recv_full, 1);
         mbar_init(peers_free, kCluster * kWorkers);
@@ -732,6 +710,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_layers_kernel(const __grid
                         const uint32_t s = it % kRing;
                         ok = wait_bar(&ring_full[s], (it / kRing) & 1, bd);
                         if (!ok) return;
+                        if (kb == 0) STEP_STAMP(bar, 8);
+                        if (kb + 1 == nkb) STEP_STAMP(bar, 9);
                         tc_fence_after_sync();
                         const uint64_t da = umma_desc_k_sw128(smem_addr(ring + s * kTile));
                         const uint64_t db = umma_desc_k_sw128(smem_addr(xbuf + kb * kXkb));
@@ -744,6 +724,65 @@ __global__ void __launch_bounds__(kThreads, 1) decode_layers_kernel(const __grid
                     ai++;
                 }
             };
+            // The attention phase: keeps every worker's two key-tile stages full, across the worker's items (the
+            // table of kept rows per item was left in shared memory by the workers before their first arrival).  A
+            // stage is refilled as soon as its warp has released it; the four workers are visited in turn and
+            // none is waited for.
+            uint32_t fed0 = 0, fed1 = 0, fed2 = 0, fed3 = 0;  // tiles fed to each worker so far, all layers
+            auto feed = [&](uint32_t l) {
+                const uint32_t y_base = l * p.kept_rows;  // the layer's rows in the all-layers tensor
+                uint32_t at0 = 0, at1 = 0, at2 = 0, at3 = 0;  // per worker: item * 32 + block
+                uint32_t left = 0;
+                for (uint32_t i = 0; i < kWorkers * kMaxItems; i++) left += item_info[i * 2];
+                uint64_t start = 0;
+                uint32_t idle = 0;
+                auto one = [&](uint32_t w, uint32_t &at, uint32_t &fed) __attribute__((always_inline)) {
+                    uint32_t item = at >> 5, blk = at & 31;
+                    if (item >= kMaxItems) return;
+                    uint32_t n_blk = item_info[(w * kMaxItems + item) * 2];
+                    if (blk >= n_blk) {  // this item is fed: on to the worker's next one, if it has one
+                        item++;
+                        blk = 0;
+                        at = item << 5;
+                        if (item >= kMaxItems) return;
+                        n_blk = item_info[(w * kMaxItems + item) * 2];
+                        if (n_blk == 0) {
+                            at = kMaxItems << 5;
+                            return;
+                        }
+                    }
+                    const uint32_t s = fed % kKvStages, use = fed / kKvStages;
+                    if (use > 0 && !mbar_try_wait(&kv_empty[w * kKvStages + s], (use - 1) & 1)) return;
+                    const int32_t x = (int32_t)item_info[(w * kMaxItems + item) * 2 + 1];
+                    const int32_t y = (int32_t)(y_base + ytab[(w * kMaxItems + item) * 32 + blk]);
+                    unsigned char *dst = smem + Smem::uni + (w * kKvStages + s) * kKvStage;
+                    uint64_t *full = &kv_full[w * kKvStages + s];
+                    mbar_expect_tx(full, kKvStage);
+                    tma_load_2d(dst, &p.kv_maps[0], full, x, y);
+                    tma_load_2d(dst + 4096, &p.kv_maps[0], full, x + 64, y);
+                    tma_load_2d(dst + kKvStage / 2, &p.kv_maps[1], full, x, y);
+                    tma_load_2d(dst + kKvStage / 2 + 4096, &p.kv_maps[1], full, x + 64, y);
+                    fed++;
+                    at++;
+                    left--;
+                    idle = 0;
+                };
+                while (left && ok) {
+                    one(0, at0, fed0);
+                    one(1, at1, fed1);
+                    one(2, at2, fed2);
+                    one(3, at3, fed3);
+                    if ((++idle & 63u) == 63u) {
+                        if (*abort_s) ok = false;
+                        const uint64_t now = now_ns();
+                        if (start == 0) start = now;
+                        else if (now - start > p.wait_ns) {
+                            give_up(bd);
+                            ok = false;
+                        }
+                    }
+                }
+            };
             sync_phase();  // the gather
             // One copy of the phase code, walked by a loop that is not unrolled: the kernel's instructions must stay
             // within the instruction cache, or every phase of every layer starts by fetching its code again.
@@ -751,9 +790,22 @@ __global__ void __launch_bounds__(kThreads, 1) decode_layers_kernel(const __grid
             for (uint32_t step = 0; step < 5 * L; step++) {
                 const uint32_t l = step / 5, k5 = step % 5;  // q,k,v | attention | o | gate,up | down
                 if (k5 != 1) linear(l, k5 == 0 ? LIN_QKV : k5 - 1);
+                else if (ok) feed(l);
                 if (step + 1 < 5 * L) sync_phase();  // nothing follows the last one
             }
             if (x_pending) drain_bar(x_full, xi & 1, p.wait_ns);
+            if (!ok) {  // key tiles this thread asked for must land before the block leaves
+                auto drain = [&](uint32_t w, uint32_t fed) {
+                    for (uint32_t back = 0; back < kKvStages && back < fed; back++) {
+                        const uint32_t j = fed - 1 - back;
+                        drain_bar(&kv_full[w * kKvStages + j % kKvStages], (j / kKvStages) & 1, p.wait_ns);
+                    }
+                };
+                drain(0, fed0);
+                drain(1, fed1);
+                drain(2, fed2);
+                drain(3, fed3);
+            }
         }
     } else {
         // ---- workers ----
@@ -761,11 +813,11 @@ __global__ void __launch_bounds__(kThreads, 1) decode_layers_kernel(const __grid
         const uint32_t wid = w * G + cta;  // spreads consecutive units over the blocks first
         const uint32_t row = q * 32 + lane;  // the tile row (TMEM lane) this thread owns
         uint32_t ai = 0, bar = 0, unit = 0, n_inv = 0, n_red = 0;
-        uint32_t kv_parity = 0, kv_pending = 0;  // bit s: parity of the next completion of stage s / a copy in flight
+        uint32_t kv_parity = 0, kv_count = 0;  // bit s: parity of the next completion of stage s; tiles read so far
         bool ok = true, sent = false;
         uint8_t *stages = smem + Smem::uni + w * kKvStages * kKvStage;
         uint16_t *prep = reinterpret_cast<uint16_t *>(smem + Smem::prep) + w * kPrepHeads * 128;
-        uint64_t *my_kv_full = kv_full + w * kKvStages;
+        uint64_t *my_kv_full = kv_full + w * kKvStages, *my_kv_empty = kv_empty + w * kKvStages;
         const uint32_t recv_addr = smem_addr(recv), send_addr = smem_addr(send);
         const uint32_t recv_full_addr = smem_addr(recv_full), peers_free_addr = smem_addr(peers_free);
         auto begin = [&]() {  // the barrier that ended the previous phase
@@ -857,6 +909,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_layers_kernel(const __grid
                 if (w == 0 && lane == 0) STEP_STAMP(bar, 7);
                 ok = wait_bar(recv_full, unit & 1, bd);
                 if (!ok) break;
+                if (w == 0 && lane == 0) STEP_STAMP(bar, 10);
                 // Add the eight partials of the owned columns in rank order.
                 float a[kOwn], b[kOwn];
                 auto sum_row = [&](uint32_t r, float (&out)[kOwn]) {
@@ -927,6 +980,21 @@ __global__ void __launch_bounds__(kThreads, 1) decode_layers_kernel(const __grid
             asm volatile("" : "+f"(first_item.cs[0]), "+f"(first_item.cs[1]), "+f"(first_item.sn[0]), "+f"(first_item.sn[1]));
         }
         float qg[4] = {1.0f, 1.0f, 1.0f, 1.0f}, kg[4] = {1.0f, 1.0f, 1.0f, 1.0f};
+        // The control thread's table: this warp's items (the same in every layer), the kept rows of their key blocks.
+        for (uint32_t i = 0; i < kMaxItems; i++) {
+            const uint32_t item = wid + i * kWorkers * G;
+            uint32_t n_blk = 0, col = 0;
+            if (item < items) {
+                const ItemCtx c = i == 0 ? first_item : make_item(p, item, lane);
+                ytab[(w * kMaxItems + i) * 32 + lane] = c.y_lane;
+                n_blk = c.pos / 32 + 1;
+                col = c.kvh * 128;
+            }
+            if (lane == 0) {
+                item_info[(w * kMaxItems + i) * 2] = n_blk;
+                item_info[(w * kMaxItems + i) * 2 + 1] = col;
+            }
+        }
         // phase 0: the gather
         gather_phase(p, p.layers[0].ln1, wid, lane);
         done();
@@ -947,17 +1015,16 @@ __global__ void __launch_bounds__(kThreads, 1) decode_layers_kernel(const __grid
                         kg[2 + e] = __ldg(Ly.k_norm + 64 + lane * 2 + e);
                     }
                 }
-                if (ok) prefetch_kept(p, Ly, wid, lane);
             }
             if (k5 == 1) {
                 if (ok) {
-                    const CUtensorMap *mk = &p.kv_maps[0], *mv = &p.kv_maps[1];
 #pragma unroll 1
                     for (uint32_t item = wid; item < items && ok; item += kWorkers * G) {
                         ItemCtx c = first_item;
                         if (item != wid) c = make_item(p, item, lane);
-                        ok = attend_item<GRP>(p, Ly, mk, mv, c, qg, kg, normed, lane, stages, prep, my_kv_full, kv_parity, kv_pending, bd,
-                                              l * p.kept_rows, w == 0 ? bar : 0);
+                        ok = attend_item<GRP>(p, Ly, c, qg, kg, normed, lane, stages, prep, my_kv_full, my_kv_empty, kv_parity,
+                                              kv_count, bd, w == 0 ? bar : 0);
+                        if (w == 0 && lane == 0 && item == wid) STEP_STAMP(bar, 5);
                     }
                 }
             } else {
@@ -965,10 +1032,6 @@ __global__ void __launch_bounds__(kThreads, 1) decode_layers_kernel(const __grid
                 finish(l, k5 == 0 ? LIN_QKV : k5 - 1, gain);
             }
             done();
-        }
-        if (!ok && lane == 0) {
-            for (uint32_t s = 0; s < kKvStages; s++)
-                if ((kv_pending >> s) & 1) drain_bar(&my_kv_full[s], (kv_parity >> s) & 1, p.wait_ns);
         }
     }
 
@@ -1100,6 +1163,9 @@ int step_kernel_create(const StepKernelShape &s, const StepKernelBuffers &b, Ste
                          : resident_clusters(decode_layers_kernel<4>, &clusters);
     if (rc != TS_OK) return bail(rc);
     if (clusters == 0) return bail(fail(TS_ERR_CUDA, "step kernel: no cluster of %u blocks fits this device", kCluster));
+    if (kBatch * s.kv_heads > kMaxItems * kWorkers * clusters * kCluster)
+        return bail(fail(TS_ERR_BAD_INPUT, "step kernel: %u kv heads over %u resident blocks: a worker warp would own more than %u "
+                                           "attention items", s.kv_heads, clusters * kCluster, kMaxItems));
     p.clusters = clusters;
     p.blocks = clusters * kCluster;
     p.n_layers = L;
@@ -1192,6 +1258,7 @@ uint32_t step_kernel_max_rows() { return kBatch; }
 
 int step_kernel_launch(StepKernel *k, uint32_t rows, uint32_t keys, const KeptDev &kept, cudaStream_t stream) {
     TS_REQUIRE(k && rows >= 1 && rows <= kBatch, "step kernel: %u rows, it takes 1..%u", rows, kBatch);
+    TS_REQUIRE(keys <= 32 * 32, "step kernel: %u keys, the feeder's table holds 32 blocks of 32 keys per item", keys);
     StepParams p = k->p;
     p.rows = rows;
     p.kept = kept;

@@ -474,7 +474,7 @@ int ts_decoder_create(const ts_decoder_config *config, ts_decoder **out) {
             StepKernelBuffers buffers = {layers.data(), d->embed, d->x, d->h, d->attn, d->act, d->qkv,
                                          d->tokens, d->slots, d->positions, d->inv_freq};
             rc = step_kernel_create(shape, buffers, &d->step);
-            if (const char *v = getenv("TS_STEP_KERNEL_KEYS")) d->step_keys = (uint32_t)atoi(v);
+            if (const char *v = getenv("TS_STEP_KERNEL_KEYS")) d->step_keys = std::min<uint32_t>((uint32_t)atoi(v), 1024u);
         }
     }
     if (rc != TS_OK) {
