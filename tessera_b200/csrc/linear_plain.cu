@@ -70,8 +70,10 @@ __device__ __forceinline__ void widen8(const uint4 &v, float *to) {
 // asked for one chunk ahead of the sums that use it; otherwise element by element.
 template <bool VEC>
 __global__ void __launch_bounds__(kOrdThreads) linear_ordered_kernel(const PlainParams p) {
-    __shared__ float xs[kOrdRows][kOrdChunk];
-    __shared__ float ws[kOrdCols][kOrdChunk + 1];
+    // Rows of w are 132 floats apart: the 16-byte reads of eight consecutive lanes (eight rows, the same k) then fall on
+    // 32 different banks.  The shared-memory pipe is what bounds this kernel, so both operands move 16 bytes at a time.
+    __shared__ __align__(16) float xs[kOrdRows][kOrdChunk];
+    __shared__ __align__(16) float ws[kOrdCols][kOrdChunk + 4];
     pdl_wait();
     const uint32_t tid = threadIdx.x, tx = tid % kOrdCols, ty = tid / kOrdCols;
     const uint32_t row0 = blockIdx.y * kOrdRows, col0 = blockIdx.x * kOrdCols;
@@ -105,15 +107,23 @@ __global__ void __launch_bounds__(kOrdThreads) linear_ordered_kernel(const Plain
                 const uint32_t r = j / (kOrdChunk / 8), at = (j % (kOrdChunk / 8)) * 8;
                 float f[8];
                 widen8(held[u], f);
-#pragma unroll
-                for (int e = 0; e < 8; e++) (is_x ? xs[r] : ws[r])[at + e] = f[e];
+                float *to = is_x ? &xs[r][at] : &ws[r][at];
+                *reinterpret_cast<float4 *>(to) = make_float4(f[0], f[1], f[2], f[3]);
+                *reinterpret_cast<float4 *>(to + 4) = make_float4(f[4], f[5], f[6], f[7]);
             }
             __syncthreads();
             if (k0 + kOrdChunk < p.k) ask(k0 + kOrdChunk);   // in flight under the sums below
             const uint32_t len = min(kOrdChunk, p.k - k0);
             if (len == kOrdChunk) {
-#pragma unroll 16
-                for (uint32_t j = 0; j < kOrdChunk; j++) sum = __fadd_rn(sum, __fmul_rn(xs[ty][j], ws[tx][j]));
+#pragma unroll 8
+                for (uint32_t j = 0; j < kOrdChunk; j += 4) {
+                    const float4 a = *reinterpret_cast<const float4 *>(&xs[ty][j]);
+                    const float4 b = *reinterpret_cast<const float4 *>(&ws[tx][j]);
+                    sum = __fadd_rn(sum, __fmul_rn(a.x, b.x));
+                    sum = __fadd_rn(sum, __fmul_rn(a.y, b.y));
+                    sum = __fadd_rn(sum, __fmul_rn(a.z, b.z));
+                    sum = __fadd_rn(sum, __fmul_rn(a.w, b.w));
+                }
             } else {
                 for (uint32_t j = 0; j < len; j++) sum = __fadd_rn(sum, __fmul_rn(xs[ty][j], ws[tx][j]));
             }
