@@ -53,3 +53,35 @@ def test_c_launch_refuses_bad_lists_without_a_gpu():
     assert b"no kernel is called" in lib.ts_last_error()
     assert lib.ts_launch(b"top_k", arr, 2, C.byref(shape), None, 0, None) == 3     # wrong count and NULL pointers
     assert b"ppuuu" in lib.ts_last_error()
+
+
+def test_face_builds_the_table_entry_and_its_argument_list():
+    # no launch: only what `launch` would hand ts_launch (entry name by element type and kept layout, the page table
+    # after the buffers, the layout's scalar last, a linear's rows in shape->down)
+    import torch
+    from tessera_b200 import ops, rules
+    q = torch.zeros(2, 4 * 128, dtype=torch.bfloat16)
+    kv = torch.zeros(3 * 64, 2 * 128, dtype=torch.bfloat16)
+    out, sl, ps = torch.zeros_like(q), torch.zeros(2, dtype=torch.int32), torch.zeros(2, dtype=torch.int32)
+    table = torch.arange(12, dtype=torch.int32)
+    a = dict(zip(rules.RULES["attend_rows"].params, [q, kv, kv, out, sl, ps, 2, 64, 4, 2, 128, 0xFFFFFFFF]))
+    name, args, down = rules.RULES["attend_rows"].entry(a, {"kept": ops.Kept("paged16", 4, table)})
+    assert name == "attend_rows_paged16" and down == 0
+    assert args[6] is table and args[7:] == [2, 64, 4, 2, 128, 0xFFFFFFFF, 4]
+    name, args, _ = rules.RULES["attend_rows"].entry(a, {"kept": ops.Kept("dense", 64)})
+    assert name == "attend_rows_dense" and len(args) == 13 and args[-1] == 64
+    with pytest.raises(TypeError):
+        rules.RULES["attend_rows"].entry(a, {})                       # the layout is not optional
+    with pytest.raises(TypeError):
+        rules.RULES["attend_rows"].entry(a, {"kept": ops.Kept("paged", 4, table, page=32)})   # not in the by-name table
+    s = dict(zip(rules.RULES["scatter"].params, [q, sl, ps, kv, 2, 256]))
+    name, args, _ = rules.RULES["scatter"].entry(s, {"kept": ops.Kept("paged", 4, table)})
+    assert name == "scatter_paged" and args[4] is table and args[5:] == [2, 256, 4]
+    x, w = torch.zeros(24, 256, dtype=torch.bfloat16), torch.zeros(512, 256, dtype=torch.bfloat16)
+    lin = dict(zip(rules.RULES["tiled"].params, [x, w, torch.zeros(24, 512, dtype=torch.bfloat16), 512, 256]))
+    assert rules.RULES["tiled"].entry(lin, {})[0::2] == ("tiled_bf16", 24)
+    norm = dict(zip(rules.RULES["lane_norm"].params, [torch.zeros(5, 300), torch.zeros(300), torch.zeros(5, 300, dtype=torch.bfloat16), 5, 300, 1]))
+    name, args, _ = rules.RULES["lane_norm"].entry(norm, {})
+    assert name == "lane_norm_bf16" and isinstance(args[-1], float)    # eps travels as f32 whatever the host passed
+    rope = dict(zip(rules.RULES["rope"].params, [torch.zeros(4, 2, 128, dtype=torch.bfloat16), torch.zeros(4, 128), 4, 2, 128]))
+    assert rules.RULES["rope"].entry(rope, {})[0] == "rope_bf16" and rules.RULES["rope"].written == "x"
