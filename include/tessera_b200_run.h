@@ -51,7 +51,9 @@ void ts_decoder_destroy(ts_decoder *dec);
  * [out, in]; norm gains are f32. */
 int ts_decoder_load(ts_decoder *dec, const char *name, const void *host_data, size_t bytes);
 
-/* Replaces the page table (slots * ceil(context / page) entries; every entry < that count). */
+/* Replaces the page table (slots * ceil(context / page) entries; every entry < that count).  Ordering: this call
+ * and ts_decoder_load first wait for the stream of the decoder's most recent launches (a resident loop returns
+ * without waiting), then copy; launches made after they return see the new contents. */
 int ts_decoder_set_table(ts_decoder *dec, const uint32_t *host_table, uint32_t entries);
 
 /* Applies the page copies a pool planned (ts_kv_grow: a write into a shared partial page first copies it,

@@ -63,6 +63,7 @@ struct ts_decoder {
     bool use_step = false;       // off until ts_decoder_use_step_kernel(dec, 1): slower than the launches it replaces so far
     uint32_t step_keys = 1024;   // decode steps that see more positions than this keep the per-product launches
     cudaStream_t own_stream = nullptr;  // used when the caller passes the NULL stream, which cannot capture
+    cudaStream_t last_stream = nullptr; // the stream of the most recent launches
     volatile uint32_t *gate_flag = nullptr;  // pinned; the gate kernel holds the stream until it is set
 };
 
@@ -336,7 +337,17 @@ int submit(ts_decoder *d, uint32_t rows, uint32_t keys, uint32_t n_out, bool fee
 // The legacy NULL stream cannot be captured into a graph: fall back to the runner's own stream
 // (a blocking stream, so it still orders against work on the NULL stream).
 cudaStream_t stream_of(ts_decoder *d, void *stream) {
-    return stream ? (cudaStream_t)stream : d->own_stream;
+    cudaStream_t s = stream ? (cudaStream_t)stream : d->own_stream;
+    d->last_stream = s;  // what a later table or weight update has to wait for
+    return s;
+}
+
+// Before the host overwrites something launches read (the page table, a weight): everything this decoder
+// launched last, on whatever stream, must be over.  A resident loop returns without waiting, and its launches
+// read the table without any dependency on the legacy stream the blocking copies below run on.
+int settle(ts_decoder *d) {
+    if (d->last_stream) TS_CUDA(cudaStreamSynchronize(d->last_stream));
+    return TS_OK;
 }
 
 uint32_t keys_bucket(const ts_decoder *d, uint32_t furthest) {
@@ -539,6 +550,8 @@ int ts_decoder_load(ts_decoder *d, const char *name, const void *host, size_t by
     }
     TS_REQUIRE(dst != nullptr, "decoder load: no weight is called '%s'", name);
     TS_REQUIRE(bytes == want, "decoder load: '%s' wants %zu bytes, got %zu", name, want, bytes);
+    int settled = settle(d);
+    if (settled != TS_OK) return settled;
     TS_CUDA(cudaMemcpy(dst, host, bytes, cudaMemcpyHostToDevice));
     return TS_OK;
 }
@@ -550,6 +563,8 @@ int ts_decoder_set_table(ts_decoder *d, const uint32_t *host_table, uint32_t ent
     TS_REQUIRE(entries == want, "decoder table: wants %u entries, got %u", want, entries);
     for (uint32_t i = 0; i < entries; i++)
         TS_REQUIRE(host_table[i] < want, "decoder table: entry %u names page %u of %u", i, host_table[i], want);
+    int rc = settle(d);
+    if (rc != TS_OK) return rc;
     TS_CUDA(cudaMemcpy(d->table, host_table, (size_t)entries * 4, cudaMemcpyHostToDevice));
     return TS_OK;
 }
