@@ -663,6 +663,7 @@ attend_rows_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t n_hg = p.heads / G, group = p.heads / p.kv_heads;
+    if (threadIdx.x == 0) STAMP(0);
     if (threadIdx.x == 0) {
         for (int s = 0; s < kMmaWarps; s++) {
             mbar_init(&full[s], 1);
@@ -674,10 +675,16 @@ attend_rows_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         prefetch_tensormap(&map_v);
     }
     __syncthreads();
-    if (!(p.early_keys && warp == 0)) {
+    if (threadIdx.x == 0) STAMP(1);
+    // With early keys nothing waits for the upstream launch here: the producer never needs it, and the consumers
+    // first fetch what their item needs that the projection does not write (slot, position, angles, norm gains).
+    bool upstream_seen = false;
+    if (!p.early_keys) {
         pdl_wait();
         pdl_launch_dependents();
+        upstream_seen = true;
     }
+    if (threadIdx.x == 32) STAMP(2);
 
     if (warp == 0) {
         // ---- producer: as in the scalar kernel, each tile as two 64-column halves ----
@@ -706,6 +713,8 @@ attend_rows_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                             tma_load_2d(dst + 4096, &map_k, &full[s], x + 64, (int32_t)y);
                             tma_load_2d(dst + kTmaTile, &map_v, &full[s], x, (int32_t)y);
                             tma_load_2d(dst + kTmaTile + 4096, &map_v, &full[s], x + 64, (int32_t)y);
+                            if (b0 - blk_lo + j == 0) STAMP(3);
+                            STAMP(4);
                         }
                     }
                 }
@@ -727,6 +736,11 @@ attend_rows_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             const uint32_t head0 = r.hg * G;
             const bool single = p.chunks == 1;
             if (r.lo >= r.hi) {
+                if (!upstream_seen) {
+                    pdl_wait();
+                    pdl_launch_dependents();
+                    upstream_seen = true;
+                }
                 if (!single && ct < G) {
                     size_t at = (((size_t)r.row * p.heads + head0 + ct) * p.chunks + r.chunk) * 2;
                     p.part_ml[at] = -INFINITY;
@@ -738,6 +752,20 @@ attend_rows_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                 continue;
             }
             const bool own_key_here = p.qkv && r.pos >= r.lo && r.pos < r.hi;
+            HeadTurn<WIDTH> turn = {};
+            float gq[WIDTH / 32], gk[WIDTH / 32];
+            uint32_t own_row = 0;
+            if (p.qkv) {  // none of this is the projection's output: it is in registers before the wait below ends
+                turn = head_turn<WIDTH>(p.inv_freq, r.pos, lane);
+                head_gains<WIDTH>(p.q_norm, lane, gq);
+                head_gains<WIDTH>(p.k_norm, lane, gk);
+                own_row = kept_row(p.kept, r.slot, r.pos);
+            }
+            if (!upstream_seen) {
+                pdl_wait();
+                pdl_launch_dependents();
+                upstream_seen = true;
+            }
             if (p.qkv) {
                 uint16_t *prep = reinterpret_cast<uint16_t *>(smem + Sh::prep);
                 const uint32_t per_row = p.heads + 2 * p.kv_heads, kvh = head0 / group;
@@ -751,18 +779,19 @@ attend_rows_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                         if (lane < 16) reinterpret_cast<uint4 *>(dst)[lane] = reinterpret_cast<const uint4 *>(src)[lane];
                     } else {
                         uint16_t lo[2], hi[2];
-                        norm_rope_head<WIDTH>(src, is_q ? p.q_norm : p.k_norm, p.inv_freq, r.pos, p.eps, lane, lo, hi);
+                        norm_rope_head_with<WIDTH>(src, (is_q ? p.q_norm : p.k_norm) != nullptr, is_q ? gq : gk, turn, p.eps, lane, lo, hi);
                         *reinterpret_cast<uint32_t *>(dst + lane * 2) = (uint32_t)lo[0] | ((uint32_t)lo[1] << 16);
                         *reinterpret_cast<uint32_t *>(dst + WIDTH / 2 + lane * 2) = (uint32_t)hi[0] | ((uint32_t)hi[1] << 16);
                     }
                     __syncwarp();
                     if (!is_q && head0 % group == 0 && lane < 16) {
-                        const size_t at = ((size_t)kept_row(p.kept, r.slot, r.pos) * p.kv_heads + kvh) * WIDTH;
+                        const size_t at = ((size_t)own_row * p.kv_heads + kvh) * WIDTH;
                         reinterpret_cast<uint4 *>((is_v ? p.v_out : p.k_out) + at)[lane] = reinterpret_cast<const uint4 *>(dst)[lane];
                     }
                 }
                 asm volatile("bar.sync 1, %0;" ::"n"(kMmaConsumers) : "memory");
             }
+            if (threadIdx.x == 32) STAMP(5);
             // Q as the A operand: rows 0-3 are the four heads (lanes 0-15), rows 4-15 zero.  Per 16-wide
             // k step: qa[t][0] = dims 16 t + 2 quad, +1; qa[t][1] = the same + 8.
             uint32_t qa[8][2];
@@ -791,6 +820,7 @@ attend_rows_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             const uint32_t blk_lo = r.lo / 32, blk_hi = (r.hi + 31) / 32;
             for (uint32_t blk = blk_lo + cw; blk < blk_hi; blk += kMmaWarps) {
                 if (ok) ok = mbar_wait_or_abort(&full[s], used & 1, abort_flag);
+                if (threadIdx.x == 32) { if (blk == blk_lo + cw) STAMP(6); STAMP(7); }
                 used++;
                 if (ok) {
                     uint8_t *tile_k = smem + (size_t)s * 2 * kTmaTile;
@@ -876,6 +906,7 @@ attend_rows_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty[s]);
             }
+            if (threadIdx.x == 32) STAMP(8);
             // ---- this warp's partial to shared memory, then the four warps fold ----
             l_row += __shfl_xor_sync(0xFFFFFFFFu, l_row, 1);
             l_row += __shfl_xor_sync(0xFFFFFFFFu, l_row, 2);
@@ -914,9 +945,11 @@ attend_rows_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                 }
             }
             asm volatile("bar.sync 1, %0;" ::"n"(kMmaConsumers) : "memory");
+            if (threadIdx.x == 32) STAMP(9);
         }
     }
     __syncthreads();
+    if (threadIdx.x == 0) STAMP(10);
     if (threadIdx.x == 0 && *abort_flag) atomicExch(status, TS_ERR_TIMEOUT);
 }
 
@@ -1016,6 +1049,12 @@ int launch_rows_mma(const CUtensorMap &map_k, const CUtensorMap &map_v, const Ro
 }
 
 }  // namespace
+
+#ifdef TS_DEBUG_STAMPS
+extern "C" __attribute__((visibility("default"))) int ts_debug_attend_stamps(unsigned long long *out) {
+    return cudaMemcpyFromSymbol(out, g_stamps, sizeof(unsigned long long) * 16 * 32) == cudaSuccess ? 0 : 6;
+}
+#endif
 
 bool attend_rows_fused_supports(bool contiguous, uint32_t width, uint32_t kept_rows) {
     return width == 128 && contiguous && kept_rows > 0;

@@ -8,13 +8,40 @@
 
 namespace ts {
 
-// One warp per head.  Lane l owns the pairs j = l * PER + e (e < PER = WIDTH / 64): elements j and
-// j + WIDTH / 2 of the head.  `gain` NULL: no norm.  Leaves the rotated values as bf16 bits in lo[e]
-// (element j) and hi[e] (element j + WIDTH / 2).
+// What a head's preparation needs besides the head itself, for a lane: the cosines and sines of its PER pairs'
+// angles (position * inv_freq[j], j = lane * PER + e) and, with a norm, the gains of its 2 PER elements
+// (g[e]: element j, g[PER + e]: element j + WIDTH / 2).  None of it depends on the projection, so a kernel may
+// fetch and compute it while it still waits for the projection's launch to finish.
 template <int WIDTH>
-__device__ __forceinline__ void norm_rope_head(const uint16_t *src, const float *gain, const float *inv_freq, uint32_t pos,
-                                               float eps, uint32_t lane, uint16_t (&lo)[WIDTH / 64],
-                                               uint16_t (&hi)[WIDTH / 64]) {
+struct HeadTurn {
+    float cs[WIDTH / 64], sn[WIDTH / 64];
+};
+
+template <int WIDTH>
+__device__ __forceinline__ HeadTurn<WIDTH> head_turn(const float *inv_freq, uint32_t pos, uint32_t lane) {
+    HeadTurn<WIDTH> t;
+#pragma unroll
+    for (int e = 0; e < WIDTH / 64; e++) sincosf((float)pos * inv_freq[lane * (WIDTH / 64) + e], &t.sn[e], &t.cs[e]);
+    return t;
+}
+
+template <int WIDTH>
+__device__ __forceinline__ void head_gains(const float *gain, uint32_t lane, float (&g)[WIDTH / 32]) {
+    constexpr int PER = WIDTH / 64;
+#pragma unroll
+    for (int e = 0; e < PER; e++) {
+        g[e] = gain ? gain[lane * PER + e] : 1.0f;
+        g[PER + e] = gain ? gain[lane * PER + e + WIDTH / 2] : 1.0f;
+    }
+}
+
+// One warp per head.  Lane l owns the pairs j = l * PER + e (e < PER = WIDTH / 64): elements j and
+// j + WIDTH / 2 of the head.  `normed` false: no norm (g is not read).  Leaves the rotated values as bf16 bits in
+// lo[e] (element j) and hi[e] (element j + WIDTH / 2).
+template <int WIDTH>
+__device__ __forceinline__ void norm_rope_head_with(const uint16_t *src, bool normed, const float (&g)[WIDTH / 32],
+                                                    const HeadTurn<WIDTH> &turn, float eps, uint32_t lane,
+                                                    uint16_t (&lo)[WIDTH / 64], uint16_t (&hi)[WIDTH / 64]) {
     constexpr int PER = WIDTH / 64;
     float a[PER], b[PER];
     float ss = 0.0f;
@@ -44,24 +71,31 @@ __device__ __forceinline__ void norm_rope_head(const uint16_t *src, const float 
         ss = fmaf(a[e], a[e], ss);
         ss = fmaf(b[e], b[e], ss);
     }
-    if (gain) {
+    if (normed) {
         ss = warp_sum(ss);
         const float inv = 1.0f / sqrtf(ss / (float)WIDTH + eps);
 #pragma unroll
         for (int e = 0; e < PER; e++) {
-            const uint32_t j = lane * PER + e;
-            a[e] = a[e] * (inv * gain[j]);
-            b[e] = b[e] * (inv * gain[j + WIDTH / 2]);
+            a[e] = a[e] * (inv * g[e]);
+            b[e] = b[e] * (inv * g[PER + e]);
         }
     }
 #pragma unroll
     for (int e = 0; e < PER; e++) {
-        const uint32_t j = lane * PER + e;
-        float sn, cs;
-        sincosf((float)pos * inv_freq[j], &sn, &cs);
-        lo[e] = bf16_bits(a[e] * cs - b[e] * sn);
-        hi[e] = bf16_bits(a[e] * sn + b[e] * cs);
+        lo[e] = bf16_bits(a[e] * turn.cs[e] - b[e] * turn.sn[e]);
+        hi[e] = bf16_bits(a[e] * turn.sn[e] + b[e] * turn.cs[e]);
     }
+}
+
+// The same with the gains and the angles fetched here.  `gain` NULL: no norm.
+template <int WIDTH>
+__device__ __forceinline__ void norm_rope_head(const uint16_t *src, const float *gain, const float *inv_freq, uint32_t pos,
+                                               float eps, uint32_t lane, uint16_t (&lo)[WIDTH / 64],
+                                               uint16_t (&hi)[WIDTH / 64]) {
+    float g[WIDTH / 32];
+    head_gains<WIDTH>(gain, lane, g);
+    const HeadTurn<WIDTH> turn = head_turn<WIDTH>(inv_freq, pos, lane);
+    norm_rope_head_with<WIDTH>(src, gain != nullptr, g, turn, eps, lane, lo, hi);
 }
 
 }  // namespace ts
