@@ -347,6 +347,26 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                 continue;
             }
 
+            // What the epilogue adds to the sums (the residual rows of this thread's outputs, the next norm's gain):
+            // asked for now, so that it arrives under the exchange instead of after it.  Thread (row, hcol) takes
+            // chunk / 2 consecutive batch columns of its row; with up to eight of them they wait in registers.
+            const bool active = !p.gated || row < 64;
+            const uint32_t n_idx = p.gated ? tile * 64 + row : tile * kRows + row;
+            const uint32_t per = chunk >> 1;
+            const bool early_adds = p.use_recv && p.epilogue == TS_EPI_ADD && per <= 8 && active && n_idx < out_n;
+            float4 add_lo = make_float4(0.0f, 0.0f, 0.0f, 0.0f), add_hi = add_lo;
+            float next_gain = 1.0f;
+            if (early_adds) {
+                const uint32_t m_first = rank * chunk + hcol * per;
+                float a[8];
+#pragma unroll
+                for (uint32_t j = 0; j < 8; j++)
+                    a[j] = (j < per && m_first + j < p.m) ? __ldcg(p.a0 + (size_t)(m_first + j) * out_n + n_idx) : 0.0f;
+                add_lo = make_float4(a[0], a[1], a[2], a[3]);
+                add_hi = make_float4(a[4], a[5], a[6], a[7]);
+            }
+            if (FUSED && p.xs_out && active && n_idx < out_n) next_gain = __ldg(p.xs_gain + n_idx);
+
             // The receive buffer of the previous tile must have been read by all of this block.
             if (acc_it > 0) {
                 ok = wait_bounded(recv_free, (acc_it - 1) & 1, abort_flag);
@@ -421,9 +441,6 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
 
             // Reduce the S partials of this block's columns in rank order, finish, store.  Thread
             // (row, hcol) takes chunk / 2 consecutive columns of its row.
-            const bool active = !p.gated || row < 64;
-            const uint32_t n_idx = p.gated ? tile * 64 + row : tile * kRows + row;
-            const uint32_t per = chunk >> 1;
             if (active && n_idx < out_n) {
                 for (uint32_t cc = hcol * per; cc < (hcol + 1) * per; cc += 4) {
                     const float *src = recv + row * rs + cc;
@@ -440,6 +457,8 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                     }
                     const float r4[4] = {sum.x, sum.y, sum.z, sum.w};
                     const float u4[4] = {up.x, up.y, up.z, up.w};
+                    const float4 add4 = cc == hcol * per ? add_lo : add_hi;
+                    const float e4[4] = {add4.x, add4.y, add4.z, add4.w};
                     const uint32_t m0 = rank * chunk + cc;
                     size_t at = (size_t)m0 * out_n + n_idx;
 #pragma unroll
@@ -449,10 +468,10 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                             const float f = (FUSED && p.row_ss) ? inv_s[m0 + j] : 1.0f;
                             r = r4[j] * f;
                             if (p.gated) r = (p.epilogue == TS_EPI_SWIGLU ? silu(r) : gelu_tanh(r)) * (u4[j] * f);
-                            if (p.epilogue == TS_EPI_ADD) r += p.a0[at];
+                            if (p.epilogue == TS_EPI_ADD) r += early_adds ? e4[j] : p.a0[at];
                             if (p.epilogue == TS_EPI_SCALE) r *= p.scale;
                             store_out(p.out, p.out_dtype, at, r);
-                            if (FUSED && p.xs_out) p.xs_out[at] = bf16_bits(r * p.xs_gain[n_idx]);
+                            if (FUSED && p.xs_out) p.xs_out[at] = bf16_bits(r * next_gain);
                         }
                         if (FUSED && p.ss_out) {  // the host only asks for this when n is a multiple of 128: every lane is here
                             const float t = warp_sum(r * r);
