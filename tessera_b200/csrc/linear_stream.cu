@@ -73,16 +73,21 @@ struct StreamSmem {
 };
 
 // recv: the block reduces / pairs through a receive buffer; send: it also stages its outgoing partials in a
-// buffer of the same shape, for bulk copies into the peers' receive buffers.
+// buffer of the same shape, for bulk copies into the peers' receive buffers.  With a split k every cluster owns
+// exactly one tile, so by the time a block stages its partial the weight ring is drained (the MMAs that read it have
+// completed and nothing more is copied into it): the send buffer then lies over the ring (send_over_ring) and the
+// shared memory it would have taken holds more weight stages, which is what lets all of a block's k blocks be in
+// flight before its x arrives (six for the down projection instead of four).
 __host__ __device__ inline StreamSmem stream_smem(uint32_t bn, uint32_t stages, uint32_t kb_max, bool recv, bool send,
-                                                  uint32_t splits) {
+                                                  uint32_t splits, bool send_over_ring = false) {
     StreamSmem l;
     l.a_off = 0;
     l.b_off = stages * kABytes;
     l.recv_off = l.b_off + kb_max * bn * kBlockK * 2;
     const uint32_t buf = kRows * (bn + 4 * splits) * 4;  // rows padded by 4 floats per sender
-    l.send_off = l.recv_off + (recv ? buf : 0);
-    l.bar_off = l.send_off + (send ? buf : 0);
+    const bool over = send && send_over_ring && stages * kABytes >= buf;
+    l.send_off = over ? l.a_off : l.recv_off + (recv ? buf : 0);
+    l.bar_off = l.recv_off + (recv ? buf : 0) + ((send && !over) ? buf : 0);
     // barriers (256), per-warp partial sums of squares (4 x 128 floats) and 128 row factors, slack for the
     // 1024-byte alignment
     l.total = l.bar_off + 256 + 2560 + 1024;
@@ -150,7 +155,7 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const StreamSmem L = stream_smem(BN, p.stages, p.kb_max, p.use_recv != 0, p.use_bulk != 0, p.splits);
+    const StreamSmem L = stream_smem(BN, p.stages, p.kb_max, p.use_recv != 0, p.use_bulk != 0, p.splits, p.splits > 1);
     unsigned char *smem_a = smem + L.a_off;
     unsigned char *smem_b = smem + L.b_off;
     float *recv = reinterpret_cast<float *>(smem + L.recv_off);  // [S][128][BN / S]
@@ -564,7 +569,7 @@ bool plan_stream(uint32_t m, uint32_t n, uint32_t k, int epilogue, StreamPlan *o
     const uint32_t sms = (uint32_t)sm_count();
     auto layout = [&](uint32_t splits, uint32_t stages, bool send = false) {
         const uint32_t kb_max = ceil_div(s.kb_total, splits);
-        return stream_smem(s.bn, stages, kb_max, splits > 1 || s.gated, send, splits);
+        return stream_smem(s.bn, stages, kb_max, splits > 1 || s.gated, send, splits, splits > 1);
     };
     // The largest power-of-two split that still fits one wave; more if the resident x slice needs it.
     uint32_t splits = 1;
