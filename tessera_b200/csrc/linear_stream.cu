@@ -185,17 +185,23 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
     const uint32_t half_n = p.n / 2;
     const uint32_t my_tiles = blockIdx.x < p.tiles ? (p.tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
     const uint32_t total_its = my_tiles * kbs;
+    // One tile whose k blocks all fit the ring (every decode-sized launch with a split k): all of its weights are
+    // asked for at once and credit ONE barrier, the MMA thread waits once and commits once.  A poll of a barrier
+    // that is already complete still costs about 300 clocks, a commit about 90: per k block that was a third of a
+    // microsecond on the path between x landing and the accumulator being ready.
+    const bool whole = my_tiles == 1 && p.stages >= kbs;
     // Stage `it` of this block's stream of weight tiles: tile and k block.
     auto load_weights = [&](uint32_t it) {
         const uint32_t tile = blockIdx.x + (it / kbs) * gridDim.x, kb = it % kbs, s = it % p.stages;
         const int32_t kx = (int32_t)((kb_begin + kb) * kBlockK);
-        mbar_expect_tx(&full[s], kABytes);
+        uint64_t *bar = whole ? &full[0] : &full[s];
+        if (!whole) mbar_expect_tx(bar, kABytes);
         unsigned char *dst = smem_a + s * kABytes;
         if (p.gated) {  // 64 gate rows, then their 64 up rows
-            tma_load_2d(dst, &map_w, &full[s], kx, (int32_t)(tile * 64));
-            tma_load_2d(dst + kABytes / 2, &map_w, &full[s], kx, (int32_t)(half_n + tile * 64));
+            tma_load_2d(dst, &map_w, bar, kx, (int32_t)(tile * 64));
+            tma_load_2d(dst + kABytes / 2, &map_w, bar, kx, (int32_t)(half_n + tile * 64));
         } else {
-            tma_load_2d(dst, &map_w, &full[s], kx, (int32_t)(tile * kRows));
+            tma_load_2d(dst, &map_w, bar, kx, (int32_t)(tile * kRows));
         }
     };
     const uint32_t early = min(p.stages, total_its);
@@ -223,6 +229,7 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
         // Weights never depend on the upstream kernel, and this thread is the only one that
         // touches the stage barriers before the block-wide sync: the first stages go out now, while
         // the other warps are still setting up.
+        if (whole) mbar_expect_tx(&full[0], kbs * kABytes);
         for (uint32_t it = 0; it < early; it++) load_weights(it);
         STAMP(1);
     }
@@ -255,7 +262,9 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
             }
             STAMP(3);
             pdl_launch_dependents();
-            if (ok) {  // every copy this thread issued has landed once its stage was released
+            if (ok && whole) {
+                ok = wait_bounded(&full[0], 0, abort_flag);  // every copy this thread issued has landed
+            } else if (ok) {  // every copy this thread issued has landed once its stage was released
                 for (uint32_t back = 0; back < p.stages && back < total_its; back++) {
                     const uint32_t j = total_its - 1 - back;
                     if (!wait_bounded(&empty[j % p.stages], (j / p.stages) & 1, abort_flag)) break;
@@ -270,10 +279,25 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
             STAMP(4);
             for (uint32_t acc_it = 0; acc_it < my_tiles && ok; acc_it++) {
                 const uint32_t as = acc_it % kAccStages, aph = (acc_it / kAccStages) & 1;
-                ok = wait_bounded(&acc_empty[as], aph ^ 1, abort_flag);
+                if (acc_it >= kAccStages) ok = wait_bounded(&acc_empty[as], aph ^ 1, abort_flag);  // a stage's first use waits for nobody
                 if (!ok) break;
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + as * BN;
+                if (whole) {
+                    ok = wait_bounded(&full[0], 0, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    for (uint32_t kb = 0; kb < kbs; kb++) {
+                        const uint64_t da = umma_desc_k_sw128(smem_addr(smem_a + kb * kABytes));
+                        const uint64_t db = umma_desc_k_sw128(smem_addr(smem_b + kb * kBBytes));
+#pragma unroll
+                        for (uint32_t k16 = 0; k16 < kBlockK / 16; k16++)
+                            umma_bf16(d_tmem, da + 2 * k16, db + 2 * k16, idesc, (kb | k16) != 0);
+                    }
+                    umma_commit(&acc_full[as]);
+                    STAMP(5);
+                    continue;
+                }
                 for (uint32_t kb = 0; kb < kbs; kb++, it++) {
                     const uint32_t s = it % p.stages, ph = (it / p.stages) & 1;
                     ok = wait_bounded(&full[s], ph, abort_flag);
