@@ -618,7 +618,9 @@ bool plan_stream(uint32_t m, uint32_t n, uint32_t k, int epilogue, StreamPlan *o
     // least three weight stages (or all the block's k blocks) still fit beside it.
     const uint32_t want = std::min<uint32_t>(3, s.kb_max);
     s.use_bulk = splits > 1 && layout(splits, want, true).total <= kSmemBudget;
-    uint32_t stages = 8;
+    // With a split k a block streams one tile: more stages than its k blocks would only hold shared memory that a
+    // block of the next launch (the decode attention's are 54 KB) could use to become resident early.
+    uint32_t stages = splits > 1 ? std::max<uint32_t>(2, std::min<uint32_t>(8, s.kb_max)) : 8;
     while (stages > 2 && layout(splits, stages, s.use_bulk).total > kSmemBudget) stages--;
     s.stages = stages;
     s.layout = layout(splits, stages, s.use_bulk);
