@@ -386,9 +386,13 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
             // What the epilogue adds to the sums (the residual rows of this thread's outputs, the next norm's gain):
             // asked for now, so that it arrives under the exchange instead of after it.  Thread (row, hcol) takes
             // chunk / 2 consecutive batch columns of its row; with up to eight of them they wait in registers.
-            const bool active = !p.gated || row < 64;
-            const uint32_t n_idx = p.gated ? tile * 64 + row : tile * kRows + row;
+            // Gated tiles have 64 output rows for 128 lanes: with eight or more columns a thread, the threads of the up
+            // rows take the second half of their gate row's columns instead of idling.
             const uint32_t per = chunk >> 1;
+            const bool shared_rows = p.gated && per >= 8;
+            const bool active = !p.gated || shared_rows || row < 64;
+            const uint32_t orow = p.gated ? (row & 63) : row;  // the tile's output row this thread works on
+            const uint32_t n_idx = p.gated ? tile * 64 + orow : tile * kRows + row;
             const bool early_adds = p.use_recv && p.epilogue == TS_EPI_ADD && per <= 8 && active && n_idx < out_n;
             float4 add_lo = make_float4(0.0f, 0.0f, 0.0f, 0.0f), add_hi = add_lo;
             float next_gain = 1.0f;
@@ -478,8 +482,10 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
             // Reduce the S partials of this block's columns in rank order, finish, store.  Thread
             // (row, hcol) takes chunk / 2 consecutive columns of its row.
             if (active && n_idx < out_n) {
-                for (uint32_t cc = hcol * per; cc < (hcol + 1) * per; cc += 4) {
-                    const float *src = recv + row * rs + cc;
+                const uint32_t cc_lo = hcol * per + ((shared_rows && row >= 64) ? per / 2 : 0);
+                const uint32_t cc_hi = shared_rows ? cc_lo + per / 2 : cc_lo + per;
+                for (uint32_t cc = cc_lo; cc < cc_hi; cc += 4) {
+                    const float *src = recv + orow * rs + cc;
                     float4 sum = *reinterpret_cast<const float4 *>(src);
                     float4 up = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
                     if (p.gated) up = *reinterpret_cast<const float4 *>(src + 64 * rs);
