@@ -146,7 +146,9 @@ __device__ __forceinline__ void store_out(void *out, int out_dtype, size_t at, f
 // FUSED compiles in the folded norm (row factors in, sums of squares and the scaled copy out); the plain instantiation carries
 // neither (they cost registers and a few percent of a decode step even when unused).
 template <uint32_t BN, bool FUSED>
-__global__ void __launch_bounds__(kThreads, 1)
+// (144 registers: a block of the decode attention, 128 threads x 128 registers and 54 KB, then fits the same SM as a
+// block of this kernel, so more of the next launch's blocks are resident and fetching key tiles while this one runs.)
+__global__ void __maxnreg__(144)
 linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                      const StreamParams p) {
     constexpr uint32_t CW = BN / 2;  // columns per epilogue warp
