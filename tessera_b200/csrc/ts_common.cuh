@@ -93,7 +93,7 @@ __device__ __forceinline__ float warp_max(float v) {
 }
 
 // x / (1 + e^-x) and the tanh GELU, as engine/ir/interp/src/cpu.rs:9-23 writes them.
-__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
+__device__ __forceinline__ float silu(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 __device__ __forceinline__ float gelu_tanh(float x) {
     const float coef = 0.7978846f;
     return 0.5f * x * (1.0f + tanhf(coef * (x + 0.044715f * x * x * x)));
