@@ -84,7 +84,7 @@ __host__ __device__ inline StreamSmem stream_smem(uint32_t bn, uint32_t stages, 
     l.a_off = 0;
     l.b_off = stages * kABytes;
     l.recv_off = l.b_off + kb_max * bn * kBlockK * 2;
-    const uint32_t buf = kRows * (bn + 4 * splits) * 4;  // rows padded by 4 floats per sender
+    const uint32_t buf = kRows * bn * 4;  // [sender][128 rows][chunk columns] f32, no padding (the 4-column groups of a row are swizzled)
     const bool over = send && send_over_ring && stages * kABytes >= buf;
     l.send_off = over ? l.a_off : l.recv_off + (recv ? buf : 0);
     l.bar_off = l.recv_off + (recv ? buf : 0) + ((send && !over) ? buf : 0);
@@ -330,7 +330,16 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
         const uint32_t col0 = hcol * CW;              // first batch column this thread owns
         const uint32_t out_n = p.gated ? half_n : p.n;
         const uint32_t shift = p.chunk_shift;         // chunk = 1 << shift batch columns per owner
-        const uint32_t rs = chunk + 4;                // receive-buffer row stride in floats (bank spread)
+        // Receive-buffer rows are `chunk` floats with no padding: what crosses the cluster is exactly the partial
+        // sums (with 8 columns a row, 4 floats of padding were a third of the exchange, and the exchange is bound by
+        // bytes).  Banks are spread by swizzling instead: the 4-column group g of row r sits at group g ^ f(r),
+        // f(r) = (r >> sh) & mask, chosen so that eight consecutive rows reading the same group touch 32 banks.
+        const uint32_t rs = chunk;
+        const uint32_t groups = chunk >> 2;
+        const uint32_t sw_mask = (groups < 8 ? groups : 8) - 1, sw_shift = groups == 2 ? 2 : groups == 4 ? 1 : 0;
+        auto swz = [&](uint32_t r, uint32_t col) -> uint32_t {  // float offset of column `col` (a multiple of 4) in row r
+            return (((col >> 2) ^ ((r >> sw_shift) & sw_mask)) << 2);
+        };
         const uint32_t recv_base = smem_addr(recv);
         const uint32_t bar_local = smem_addr(recv_full);
         bool ok = true;
@@ -428,7 +437,7 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                     for (uint32_t c = 0; c < CW; c += 4) {
                         const uint32_t col = col0 + c;
                         const uint32_t dest = col >> shift, within = col & (chunk - 1);
-                        *reinterpret_cast<float4 *>(send + (dest * kRows + row) * rs + within) =
+                        *reinterpret_cast<float4 *>(send + (dest * kRows + row) * rs + swz(row, within)) =
                             make_float4(v[c], v[c + 1], v[c + 2], v[c + 3]);
                     }
                     fence_async_shared();  // the copy engine reads what these threads wrote
@@ -452,7 +461,7 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                     for (uint32_t c = 0; c < CW; c += 4) {
                         const uint32_t col = col0 + c;
                         const uint32_t dest = col >> shift, within = col & (chunk - 1);
-                        const uint32_t local = recv_base + ((rank * kRows + row) * rs + within) * 4;
+                        const uint32_t local = recv_base + ((rank * kRows + row) * rs + swz(row, within)) * 4;
                         st_async_f32x4(map_to_rank(local, dest), map_to_rank(bar_local, dest), v[c], v[c + 1], v[c + 2],
                                        v[c + 3]);
                     }
@@ -468,7 +477,7 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                 // arrival per warp.
 #pragma unroll
                 for (uint32_t c = 0; c < CW; c += 4)
-                    *reinterpret_cast<float4 *>(recv + row * rs + col0 + c) = make_float4(v[c], v[c + 1], v[c + 2], v[c + 3]);
+                    *reinterpret_cast<float4 *>(recv + row * rs + swz(row, col0 + c)) = make_float4(v[c], v[c + 1], v[c + 2], v[c + 3]);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(recv_full);
             }
@@ -487,7 +496,7 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                 const uint32_t cc_lo = hcol * per + ((shared_rows && row >= 64) ? per / 2 : 0);
                 const uint32_t cc_hi = shared_rows ? cc_lo + per / 2 : cc_lo + per;
                 for (uint32_t cc = cc_lo; cc < cc_hi; cc += 4) {
-                    const float *src = recv + orow * rs + cc;
+                    const float *src = recv + orow * rs + swz(orow, cc);
                     float4 sum = *reinterpret_cast<const float4 *>(src);
                     float4 up = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
                     if (p.gated) up = *reinterpret_cast<const float4 *>(src + 64 * rs);
