@@ -237,7 +237,9 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
         mbar_init(send_full, kEpiWarps);
         // S > 1: one local arrival announces the bytes and the senders' asynchronous stores complete
         // them; S == 1: plain stores, one arrival per warp.
-        mbar_init(recv_full, S > 1 ? 1 : kEpiWarps);
+        // (with bulk copies a block's own share never leaves it: its eight warps store it straight into the receive
+        // buffer and arrive here as well)
+        mbar_init(recv_full, S > 1 ? (p.use_bulk ? 1 + kEpiWarps : 1) : kEpiWarps);
         mbar_init(recv_free, kEpiWarps);
         *abort_flag = 0;
         fence_barrier_init();
@@ -437,19 +439,24 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                     for (uint32_t c = 0; c < CW; c += 4) {
                         const uint32_t col = col0 + c;
                         const uint32_t dest = col >> shift, within = col & (chunk - 1);
-                        *reinterpret_cast<float4 *>(send + (dest * kRows + row) * rs + swz(row, within)) =
-                            make_float4(v[c], v[c + 1], v[c + 2], v[c + 3]);
+                        // the columns this block owns itself go straight where its reduce reads them
+                        float *to = dest == rank ? recv + (rank * kRows + row) * rs : send + (dest * kRows + row) * rs;
+                        *reinterpret_cast<float4 *>(to + swz(row, within)) = make_float4(v[c], v[c + 1], v[c + 2], v[c + 3]);
                     }
                     fence_async_shared();  // the copy engine reads what these threads wrote
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(send_full);
+                    if (lane == 0) {
+                        mbar_arrive(send_full);
+                        mbar_arrive(recv_full);  // this warp's part of the block's own share is in place
+                    }
                     if (warp == 2 && lane == 0) {
                         const uint32_t block_bytes = kRows * rs * 4;
-                        mbar_expect_tx(recv_full, S * block_bytes);
+                        mbar_expect_tx(recv_full, (S - 1) * block_bytes);
                         if (wait_bounded(send_full, acc_it & 1, abort_flag)) {
                             for (uint32_t d = 0; d < S; d++)
-                                bulk_copy_to_peer(map_to_rank(recv_base + rank * block_bytes, d),
-                                                  smem_addr(send) + d * block_bytes, block_bytes, map_to_rank(bar_local, d));
+                                if (d != rank)
+                                    bulk_copy_to_peer(map_to_rank(recv_base + rank * block_bytes, d),
+                                                      smem_addr(send) + d * block_bytes, block_bytes, map_to_rank(bar_local, d));
                         }
                     }
                 } else {
