@@ -50,6 +50,7 @@ struct StreamParams {
     uint32_t use_recv;       // reduce / pair through the receive buffer (S > 1 or gated)
     uint32_t use_bulk;       // S > 1: partials go out as one bulk copy per peer instead of 16-byte stores
     uint32_t chunk_shift;    // log2(BN / S): batch columns each block owns after the reduce
+    uint32_t split_shift;    // log2(S)
     int epilogue, out_dtype;
     float scale;
     const float *a0;
@@ -179,13 +180,15 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
 
     const uint32_t S = p.splits;
     const uint32_t rank = blockIdx.y;  // == cluster rank: the cluster spans grid y
-    const uint32_t kb_begin = (uint32_t)(((uint64_t)rank * p.kb_total) / S);
-    const uint32_t kb_end = (uint32_t)(((uint64_t)(rank + 1) * p.kb_total) / S);
+    // (The split is a power of two and a launch has a few thousand k blocks at most: shifts, not the 64-bit divisions
+    // that stood between a block's first instruction and its first weight copy.)
+    const uint32_t kb_begin = (rank * p.kb_total) >> p.split_shift;
+    const uint32_t kb_end = ((rank + 1) * p.kb_total) >> p.split_shift;
     const uint32_t kbs = kb_end - kb_begin;
     const uint32_t chunk = BN / S;  // batch columns this block owns after the reduce
 
     const uint32_t half_n = p.n / 2;
-    const uint32_t my_tiles = blockIdx.x < p.tiles ? (p.tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const uint32_t my_tiles = blockIdx.x >= p.tiles ? 0 : gridDim.x >= p.tiles ? 1 : (p.tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
     const uint32_t total_its = my_tiles * kbs;
     // One tile whose k blocks all fit the ring (every decode-sized launch with a split k): all of its weights are
     // asked for at once and credit ONE barrier, the MMA thread waits once and commits once.  A poll of a barrier
@@ -218,8 +221,21 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
         const uint32_t n_first = whole ? 1 : early;
         for (uint32_t s = 0; s < n_first; s++) mbar_init(&full[s], 1);
         fence_barrier_init();
-        if (whole) mbar_expect_tx(&full[0], kbs * kABytes);
-        for (uint32_t it = 0; it < early; it++) load_weights(it);
+        if (whole) {  // the block's one tile, stage kb = k block kb: no index arithmetic on the way to the first copy
+            mbar_expect_tx(&full[0], kbs * kABytes);
+            for (uint32_t kb = 0; kb < kbs; kb++) {
+                const int32_t kx = (int32_t)((kb_begin + kb) * kBlockK);
+                unsigned char *dst = smem_a + kb * kABytes;
+                if (p.gated) {
+                    tma_load_2d(dst, &map_w, &full[0], kx, (int32_t)(blockIdx.x * 64));
+                    tma_load_2d(dst + kABytes / 2, &map_w, &full[0], kx, (int32_t)(half_n + blockIdx.x * 64));
+                } else {
+                    tma_load_2d(dst, &map_w, &full[0], kx, (int32_t)(blockIdx.x * kRows));
+                }
+            }
+        } else {
+            for (uint32_t it = 0; it < early; it++) load_weights(it);
+        }
         STAMP(1);
     } else if (threadIdx.x == 64) {
         const uint32_t n_first = whole ? 1 : early;
@@ -768,6 +784,9 @@ int linear_stream(const void *x, const void *w, const void *a0, void *out, uint3
         uint32_t chunk = s.bn / s.splits, sh = 0;
         while ((1u << sh) < chunk) sh++;
         p.chunk_shift = sh;
+        uint32_t ssh = 0;
+        while ((1u << ssh) < s.splits) ssh++;
+        p.split_shift = ssh;
     }
     p.epilogue = epilogue;
     p.out_dtype = out_dtype;

@@ -150,12 +150,16 @@ bool pdl_enabled();
 // (engine/plan/run/src/marks.cuh).  Compiled out of the shipped library.
 #ifdef TS_DEBUG_STAMPS
 static __device__ unsigned long long g_stamps[16 * 32];  // one copy per translation unit
+#ifndef TS_STAMP_X
+#define TS_STAMP_X blockIdx.x   /* -DTS_STAMP_X='(gridDim.x - 1 - blockIdx.x)' stamps the last blocks instead of the first */
+#endif
 #define STAMP(slot)                                                         \
     do {                                                                    \
-        if (blockIdx.x < 4 && blockIdx.y < 4) {                             \
+        const unsigned bx__ = TS_STAMP_X;                                   \
+        if (bx__ < 4 && blockIdx.y < 4) {                                   \
             unsigned long long t__;                                         \
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__));         \
-            g_stamps[(blockIdx.x * 4 + blockIdx.y) * 32 + (slot)] = t__;    \
+            g_stamps[(bx__ * 4 + blockIdx.y) * 32 + (slot)] = t__;          \
         }                                                                   \
     } while (0)
 #else
