@@ -8,10 +8,18 @@
 // Small matrices do not have enough 128-row tiles to fill 148 SMs, so k is split over the S blocks of
 // a thread-block cluster.  Each block ends with a 128 x BN f32 partial in TMEM; the cluster reduces
 // it through distributed shared memory: block r owns batch columns [r BN/S, (r+1) BN/S), every block
-// writes its partial of those columns into block r's receive buffer (st.shared::cluster) and arrives
-// on block r's mbarrier; block r then adds the S partials in rank order (a fixed order: a re-run
-// gives the same bits), applies the epilogue (residual add, SwiGLU/GeGLU, scale) and stores.  No
-// partial sums touch global memory and nothing is launched afterwards.
+// stages its partial of those columns and sends it into block r's receive buffer (one bulk copy per
+// peer that credits r's mbarrier; its own share it stores there directly); block r then adds the S
+// partials in rank order (a fixed order: a re-run gives the same bits), applies the epilogue (residual
+// add, SwiGLU/GeGLU, scale) and stores.  No partial sums touch global memory and nothing is launched
+// afterwards.  The exchange is bound by the bytes that cross the cluster, so its buffers carry no
+// padding (a row's 4-column groups are swizzled by row for the bank spread instead).
+//
+// A decode-sized launch is a chain of latencies, not of bandwidth: what is on the path between the
+// upstream launch ending and this one's store is kept short.  The weights of a block's one tile are
+// all asked for in its first instructions and credit one barrier (a poll of a complete mbarrier still
+// costs about 300 clocks); what the epilogue adds to the sums is loaded before the exchange; in gated
+// tiles the threads of the up rows share the gate rows' columns.
 //
 // Gated epilogues pair gate row j with up row j + n/2: a gated tile is 64 gate rows and their 64 up
 // rows, so both meet in the owner's receive buffer.
